@@ -1,0 +1,49 @@
+// Gated activation of the feed-forward: out[t, i] = act(x[t, i]) * x[t, d + i].
+// Counterpart in the reference: silu_and_mul_kernel, vllm/kernels/activation_kernels.cu:26-41
+// (gelu variants :13-24, :44-51).  Here both factors are taken to float32 and the product is
+// rounded once.
+#include "common.cuh"
+
+LMSF_DEFINE_LAST_ERROR(lmsf_activation)
+
+namespace lmsf {
+
+enum { kActSilu = 0, kActGeluTanh = 1 };
+
+__device__ __forceinline__ float act_silu(float g) { return g / (1.0f + expf(-g)); }
+__device__ __forceinline__ float act_gelu_tanh(float g) {
+  const float k = 0.7978845608028654f;  // sqrt(2 / pi)
+  return 0.5f * g * (1.0f + tanhf(k * (g + 0.044715f * g * g * g)));
+}
+
+template <typename T, int ACT>
+__global__ void gated_act_kernel(T* __restrict__ out, const T* __restrict__ in, int d, long long in_stride) {
+  const T* row = in + (size_t)blockIdx.x * in_stride;
+  T* o = out + (size_t)blockIdx.x * d;
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < d; i += gridDim.y * blockDim.x) {
+    const float g = to_f32(row[i]), u = to_f32(row[d + i]);
+    o[i] = from_f32<T>((ACT == kActSilu ? act_silu(g) : act_gelu_tanh(g)) * u);
+  }
+}
+
+}  // namespace lmsf
+
+// in: [n, 2 * d] with `in_stride` elements between rows (gate first, up second); out: [n, d].
+LMSF_API int lmsf_gated_act(void* out, const void* in, int n, int d, long long in_stride, int act, int dtype,
+                            void* stream) {
+  using namespace lmsf;
+  if (n <= 0) return 0;
+  if (d <= 0 || in_stride < 2LL * d) LMSF_REFUSE("gated_act: d=%d, in_stride=%lld", d, in_stride);
+  if (act != kActSilu && act != kActGeluTanh) LMSF_REFUSE("gated_act: unknown activation code %d", act);
+  if (dtype != LMSF_F32 && dtype != LMSF_BF16) LMSF_REFUSE("gated_act: unknown dtype code %d", dtype);
+  const int threads = 256;
+  int gy = ceil_div(d, threads * 4);
+  if (gy > 64) gy = 64;
+  dim3 grid(n, gy);
+  cudaStream_t s = (cudaStream_t)stream;
+#define LMSF_GA(T, A) gated_act_kernel<T, A><<<grid, threads, 0, s>>>((T*)out, (const T*)in, d, in_stride)
+  if (dtype == LMSF_F32) { if (act == kActSilu) LMSF_GA(float, kActSilu); else LMSF_GA(float, kActGeluTanh); }
+  else { if (act == kActSilu) LMSF_GA(bf16, kActSilu); else LMSF_GA(bf16, kActGeluTanh); }
+#undef LMSF_GA
+  return LMSF_LAUNCH_STATUS();
+}

@@ -1,0 +1,79 @@
+// Shared helpers of the lmsf_b200 kernels (sm_100a only).
+//
+// Conventions of every launcher in this folder:
+//   * C ABI, returns 0 on success, a cudaError_t (> 0) from the launch, or LMSF_EBADARG (-1)
+//     when a size or option is outside what the kernel was written for; the text of the last
+//     refusal of this library is returned by <file>_last_error().
+//   * dtype codes: 0 = float32, 1 = bfloat16.  Reductions, softmax, rotation angles and
+//     residual sums are always float32 whatever the storage type.
+//   * all index tensors are int32 and live on the device; `stream` is a cudaStream_t.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#if !defined(__CUDA_ARCH__) || __CUDA_ARCH__ >= 1000
+#else
+#error "lmsf_b200 kernels are written for sm_100a only"
+#endif
+
+#define LMSF_API extern "C" __attribute__((visibility("default")))
+#define LMSF_EBADARG (-1)
+#define LMSF_F32 0
+#define LMSF_BF16 1
+
+#define LMSF_DEFINE_LAST_ERROR(prefix)                                              \
+  static thread_local char g_last_error[512] = "";                                  \
+  LMSF_API const char* prefix##_last_error() { return g_last_error; }
+
+#define LMSF_REFUSE(...)                                                            \
+  do {                                                                              \
+    snprintf(g_last_error, sizeof(g_last_error), __VA_ARGS__);                      \
+    return LMSF_EBADARG;                                                            \
+  } while (0)
+
+#define LMSF_LAUNCH_STATUS() ((int)cudaGetLastError())
+
+namespace lmsf {
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(bf16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.  `scratch` holds 33 floats.
+// The order of additions depends only on blockDim, never on the data or on other blocks.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nwarps ? scratch[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
+static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+}  // namespace lmsf

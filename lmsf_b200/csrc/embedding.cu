@@ -1,0 +1,52 @@
+// Embedding gather: out[t, :] = table[ids[t], :].
+// Counterpart in the reference: index_select in
+// core/src/model_executor/layers/vocab_parallel_embedding.rs:28-37.
+#include "common.cuh"
+
+LMSF_DEFINE_LAST_ERROR(lmsf_embedding)
+
+namespace lmsf {
+
+// One block per token.  Rows are copied as 16-byte words when the row size allows it.
+// An id outside [0, vocab) writes a row of zeros and raises *error_flag (never reads outside the table).
+template <typename W>
+__global__ void embedding_kernel(W* __restrict__ out, const W* __restrict__ table, const int* __restrict__ ids,
+                                 int row_words, int vocab, int* __restrict__ error_flag) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  W* dst = out + (size_t)t * row_words;
+  if (id < 0 || id >= vocab) {
+    if (threadIdx.x == 0 && error_flag) atomicExch(error_flag, 1);
+    W zero;
+    memset(&zero, 0, sizeof(W));
+    for (int i = threadIdx.x; i < row_words; i += blockDim.x) dst[i] = zero;
+    return;
+  }
+  const W* src = table + (size_t)id * row_words;
+  for (int i = threadIdx.x; i < row_words; i += blockDim.x) dst[i] = src[i];
+}
+
+}  // namespace lmsf
+
+LMSF_API int lmsf_embedding(void* out, const void* table, const int* ids, int n_tokens, int hidden, int vocab,
+                            int dtype, int* error_flag, void* stream) {
+  using namespace lmsf;
+  if (n_tokens <= 0) return 0;
+  if (hidden <= 0 || vocab <= 0) LMSF_REFUSE("embedding: hidden=%d vocab=%d must be positive", hidden, vocab);
+  if (dtype != LMSF_F32 && dtype != LMSF_BF16) LMSF_REFUSE("embedding: unknown dtype code %d", dtype);
+  const size_t row_bytes = (size_t)hidden * (dtype == LMSF_F32 ? 4 : 2);
+  cudaStream_t s = (cudaStream_t)stream;
+  const bool aligned16 = row_bytes % 16 == 0 && ((uintptr_t)out % 16 == 0) && ((uintptr_t)table % 16 == 0);
+  if (aligned16) {
+    const int words = (int)(row_bytes / 16);
+    const int threads = words >= 256 ? 256 : (words >= 64 ? 64 : 32);
+    embedding_kernel<uint4><<<n_tokens, threads, 0, s>>>((uint4*)out, (const uint4*)table, ids, words, vocab,
+                                                          error_flag);
+  } else if (dtype == LMSF_F32) {
+    embedding_kernel<float><<<n_tokens, 128, 0, s>>>((float*)out, (const float*)table, ids, hidden, vocab, error_flag);
+  } else {
+    embedding_kernel<unsigned short><<<n_tokens, 128, 0, s>>>((unsigned short*)out, (const unsigned short*)table, ids,
+                                                               hidden, vocab, error_flag);
+  }
+  return LMSF_LAUNCH_STATUS();
+}

@@ -1,0 +1,228 @@
+"""Python faces of the CUDA kernels in `csrc/`.
+
+Each function checks what the kernel cannot check (device, dtype, contiguity), takes the
+launching stream from torch and raises `KernelError` with the library's own message when
+the kernel refuses a size.  There is no CPU path: tensors that are not on a CUDA device
+are an error.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from typing import Optional, Tuple
+
+import torch
+
+from .csrc.build import load_library
+
+F32, BF16 = 0, 1
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float32:
+        return F32
+    if dt == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16, not {dt}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise KernelError("lmsf_b200 kernels run on CUDA tensors only; got a tensor on " + str(t.device))
+    return t.data_ptr()
+
+
+def _i32(t: Optional[torch.Tensor], name: str) -> Optional[int]:
+    if t is None:
+        return None
+    if t.dtype != torch.int32 or not t.is_contiguous():
+        raise KernelError(f"{name} must be a contiguous int32 tensor")
+    return _ptr(t)
+
+
+_FUNCS = {}
+
+
+def _func(source: str, name: str, argtypes, defines: Tuple[str, ...] = ()):
+    key = (source, name, defines)
+    f = _FUNCS.get(key)
+    if f is None:
+        lib = load_library(source, defines)
+        f = getattr(lib, name)
+        f.argtypes = argtypes
+        f.restype = c_int
+        _FUNCS[key] = f
+    return f
+
+
+def _check(rc: int, source: str, prefix: str, defines: Tuple[str, ...] = ()):
+    if rc == 0:
+        return
+    if rc < 0:
+        lib = load_library(source, defines)
+        getter = getattr(lib, prefix + "_last_error")
+        getter.restype = ctypes.c_char_p
+        raise KernelError(getter().decode())
+    raise KernelError(f"CUDA error {rc} at the launch of a kernel of {source}")
+
+
+# ----------------------------------------------------------------------------- embedding
+
+def embedding(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, error_flag: Optional[torch.Tensor] = None):
+    """out[t, :] = table[ids[t], :]; out and table share one dtype."""
+    n, hidden = out.shape
+    if table.dtype != out.dtype or table.shape[1] != hidden or not (out.is_contiguous() and table.is_contiguous()):
+        raise KernelError("embedding: out and table must be contiguous, of one dtype and one width")
+    f = _func("embedding.cu", "lmsf_embedding",
+              [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    rc = f(_ptr(out), _ptr(table), _i32(ids, "ids"), n, hidden, table.shape[0], dtype_code(out.dtype),
+           _i32(error_flag, "error_flag"), _stream())
+    _check(rc, "embedding.cu", "lmsf_embedding")
+
+
+# ----------------------------------------------------------------------------- rmsnorm
+
+def add_rmsnorm(h: torch.Tensor, x: torch.Tensor, res: Optional[torch.Tensor], w: torch.Tensor, eps: float, mode: int):
+    """mode 0: h = norm(x) w.  mode 1: res = float(x); h = norm(res) w.  mode 2: res += float(x); h = norm(res) w.
+    x, h: [n, hidden] float32 or bfloat16; res: float32; w: [hidden] of x's dtype or float32."""
+    n, hidden = x.shape
+    if h.shape != x.shape or h.dtype != x.dtype or not (x.is_contiguous() and h.is_contiguous()):
+        raise KernelError("rmsnorm: h and x must be contiguous and alike")
+    if res is not None and (res.dtype != torch.float32 or res.shape != x.shape or not res.is_contiguous()):
+        raise KernelError("rmsnorm: the residual must be contiguous float32 of x's shape")
+    if w.shape != (hidden,) or not w.is_contiguous():
+        raise KernelError(f"rmsnorm: weight of shape {tuple(w.shape)} for width {hidden}")
+    f = _func("rmsnorm.cu", "lmsf_add_rmsnorm",
+              [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p])
+    rc = f(_ptr(h), _ptr(x), _ptr(res), _ptr(w), n, hidden, float(eps), mode, dtype_code(x.dtype),
+           dtype_code(w.dtype), _stream())
+    _check(rc, "rmsnorm.cu", "lmsf_rmsnorm")
+
+
+# ----------------------------------------------------------------------------- rope + cache write
+
+def rope_cache_write(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Tensor], positions: torch.Tensor,
+                     token_seq: Optional[torch.Tensor], block_table: Optional[torch.Tensor], block_size: int,
+                     cache: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor], rot_dim: int, is_neox: bool,
+                     n_q_heads: int, n_kv_heads: int, head_dim: int, error_flag: Optional[torch.Tensor] = None):
+    """Rotates q in place; writes rotated k and v into `cache` [pages, 2, n_kv_heads, block_size, head_dim]
+    at the page that `block_table[token_seq[t], positions[t] // block_size]` names.  q, k, v: [n, heads*head_dim]
+    views whose last dimension is contiguous (row strides are free).  cache None: q only."""
+    n = q.shape[0]
+    for name, t, heads in (("q", q, n_q_heads), ("k", k, n_kv_heads), ("v", v, n_kv_heads)):
+        if t is None:
+            continue
+        if t.dim() != 2 or t.shape[1] != heads * head_dim or t.stride(1) != 1 or t.shape[0] != n:
+            raise KernelError(f"rope_cache: {name} must be [n, {heads * head_dim}] with a contiguous last dimension")
+        if t.dtype != q.dtype:
+            raise KernelError("rope_cache: q, k, v must share one dtype")
+    page_stride = 0
+    max_blocks = 0
+    if cache is not None:
+        if cache.dtype != q.dtype or not cache.is_contiguous() or tuple(cache.shape[1:]) != (2, n_kv_heads, block_size, head_dim):
+            raise KernelError(f"rope_cache: cache of shape {tuple(cache.shape)} does not match "
+                              f"[pages, 2, {n_kv_heads}, {block_size}, {head_dim}] of {q.dtype}")
+        page_stride = cache.stride(0)
+        max_blocks = block_table.shape[1]
+    if inv_freq is not None and (inv_freq.dtype != torch.float32 or inv_freq.numel() != rot_dim // 2):
+        raise KernelError("rope_cache: inv_freq must hold rot_dim / 2 float32 values")
+    f = _func("rope_cache.cu", "lmsf_rope_cache_write",
+              [c_void_p, c_void_p, c_void_p, c_longlong, c_longlong, c_longlong, c_void_p, c_void_p, c_void_p, c_int,
+               c_int, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+               c_void_p])
+    rc = f(_ptr(q), _ptr(k), _ptr(v), q.stride(0), k.stride(0) if k is not None else 0,
+           v.stride(0) if v is not None else 0, _i32(positions, "positions"), _i32(token_seq, "token_seq"),
+           _i32(block_table, "block_table"), max_blocks, block_size, _ptr(cache), page_stride, _ptr(inv_freq),
+           rot_dim, int(is_neox), n, n_q_heads, n_kv_heads, head_dim, dtype_code(q.dtype),
+           _i32(error_flag, "error_flag"), _stream())
+    _check(rc, "rope_cache.cu", "lmsf_rope_cache")
+
+
+# ----------------------------------------------------------------------------- attention (generic)
+
+def attention_generic(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
+                      block_size: int, token_seq: torch.Tensor, positions: torch.Tensor, scale: float, window: int,
+                      n_q_heads: int, n_kv_heads: int, head_dim: int):
+    """out[t] = softmax(scale q[t] K^T) V over the keys lo..positions[t] of token t's request, read from pages.
+    q, out: [n, n_q_heads * head_dim] (last dimension contiguous); window <= 0 means all keys."""
+    n = q.shape[0]
+    if q.stride(1) != 1 or out.stride(1) != 1 or q.shape[1] != n_q_heads * head_dim or out.shape != q.shape:
+        raise KernelError("attention: q and out must be [n, heads * head_dim] with a contiguous last dimension")
+    if cache.dtype != q.dtype or out.dtype != q.dtype or not cache.is_contiguous() or \
+            tuple(cache.shape[1:]) != (2, n_kv_heads, block_size, head_dim):
+        raise KernelError(f"attention: cache of shape {tuple(cache.shape)} / {cache.dtype} does not match the heads")
+    f = _func("attention_generic.cu", "lmsf_attention_generic",
+              [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_int, c_void_p,
+               c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    rc = f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache), cache.stride(0),
+           _i32(block_table, "block_table"), block_table.shape[1], block_size, _i32(token_seq, "token_seq"),
+           _i32(positions, "positions"), float(scale), int(window or 0), n, n_q_heads, n_kv_heads, head_dim,
+           dtype_code(q.dtype), _stream())
+    _check(rc, "attention_generic.cu", "lmsf_attention_generic")
+
+
+# ----------------------------------------------------------------------------- gated activation
+
+ACT_CODES = {"silu": 0, "swish": 0, "gelu_tanh": 1, "gelu_pytorch_tanh": 1}
+
+
+def gated_act(out: torch.Tensor, x: torch.Tensor, act: str = "silu"):
+    """out[t, i] = act(x[t, i]) * x[t, d + i]; x: [n, 2 d], out: [n, d] contiguous."""
+    n, d = out.shape
+    if x.shape != (n, 2 * d) or x.stride(1) != 1 or not out.is_contiguous() or x.dtype != out.dtype:
+        raise KernelError("gated_act: x must be [n, 2d] and out [n, d] of one dtype")
+    if act not in ACT_CODES:
+        raise KernelError(f"gated_act: unknown activation {act!r} (known: {', '.join(sorted(ACT_CODES))})")
+    f = _func("activation.cu", "lmsf_gated_act", [c_void_p, c_void_p, c_int, c_int, c_longlong, c_int, c_int, c_void_p])
+    rc = f(_ptr(out), _ptr(x), n, d, x.stride(0), ACT_CODES[act], dtype_code(out.dtype), _stream())
+    _check(rc, "activation.cu", "lmsf_activation")
+
+
+# ----------------------------------------------------------------------------- SIMT matrix product
+
+def gemm_tn_simt(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor):
+    """out[M, N] = a[M, K] w[N, K]^T, float32 FMA accumulation in ascending k (true 32-bit when a, w are float32)."""
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape != (M, N) or a.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError(f"gemm: shapes {tuple(a.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
+    if a.dtype != w.dtype:
+        raise KernelError("gemm: a and w must share one dtype")
+    f = _func("gemm_simt.cu", "lmsf_gemm_tn_simt",
+              [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, c_int,
+               c_void_p])
+    rc = f(_ptr(out), _ptr(a), _ptr(w), M, N, K, a.stride(0), w.stride(0), out.stride(0), dtype_code(a.dtype),
+           dtype_code(out.dtype), _stream())
+    _check(rc, "gemm_simt.cu", "lmsf_gemm_simt")
+
+
+# ----------------------------------------------------------------------------- sampling
+
+def sample(out: torch.Tensor, logits: torch.Tensor, temperature: Optional[torch.Tensor] = None,
+           seed: Optional[torch.Tensor] = None, step: Optional[torch.Tensor] = None):
+    """out[r] = greedy or temperature sample of logits[r] (float32).  temperature [rows] float32,
+    seed [rows] int64 (bit pattern of an unsigned 64-bit seed), step [rows] int32; all None: greedy."""
+    rows, vocab = logits.shape
+    if logits.dtype != torch.float32 or logits.stride(1) != 1:
+        raise KernelError("sample: logits must be float32 with a contiguous last dimension")
+    if out.dtype != torch.int32 or out.shape != (rows,) or not out.is_contiguous():
+        raise KernelError("sample: out must be int32 [rows]")
+    if temperature is not None and (temperature.dtype != torch.float32 or temperature.shape != (rows,)):
+        raise KernelError("sample: temperature must be float32 [rows]")
+    if seed is not None and (seed.dtype != torch.int64 or seed.shape != (rows,)):
+        raise KernelError("sample: seed must be int64 [rows]")
+    f = _func("sampling.cu", "lmsf_sample",
+              [c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+    rc = f(_ptr(out), _ptr(logits), logits.stride(0), rows, vocab, _ptr(temperature), _ptr(seed), _i32(step, "step"),
+           _stream())
+    _check(rc, "sampling.cu", "lmsf_sampling")

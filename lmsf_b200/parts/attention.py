@@ -1,0 +1,77 @@
+"""Grouped-query attention over the paged cache.
+
+The reference's CausalSelfAttention (core/src/model_executor/models/llama/llama.rs:45-221) projects
+q, k, v with one merged matrix, rotates q and k, scatters k and v into pages
+(core/src/model_executor/layers/attention.rs:185-207) and then runs a dense prompt attention on
+the fresh k, v or a paged decode kernel (attention.rs:209-294).  Here one step may hold prompt
+portions and decoded tokens together: k and v always go to pages first and every query reads all
+its keys from pages, so a portion that starts in the middle of a prompt needs nothing special.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional
+
+import torch
+
+from .. import kernels
+from .base import KVCacheSpec, LayerCache, Mixer, PositionEncoding, StepContext, WeightSpec, register_part
+from .linear import matmul_tn
+
+
+@register_part("mixer", "paged_attention")
+class PagedAttention(Mixer):
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                 position_encoding: Optional[PositionEncoding] = None, window: Optional[int] = None,
+                 scale: Optional[float] = None):
+        if num_heads % num_kv_heads:
+            raise ValueError(f"{num_heads} query heads cannot be grouped over {num_kv_heads} kv heads")
+        if head_dim % 16 or not (16 <= head_dim <= 256):
+            raise ValueError(f"head_dim {head_dim} is not supported: the attention kernels take multiples of 16 "
+                             f"from 16 to 256")
+        self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim = hidden_size, num_heads, num_kv_heads, head_dim
+        self.position_encoding = position_encoding
+        self.window = int(window) if window else None
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
+        self.q_size = num_heads * head_dim
+        self.kv_size = num_kv_heads * head_dim
+        self.qkv: Optional[torch.Tensor] = None
+        self.o: Optional[torch.Tensor] = None
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        return {"qkv": WeightSpec([(self.q_size, self.hidden_size), (self.kv_size, self.hidden_size),
+                                   (self.kv_size, self.hidden_size)]),
+                "o": WeightSpec([(self.hidden_size, self.q_size)])}
+
+    def cache_spec(self) -> Optional[KVCacheSpec]:
+        return KVCacheSpec(self.num_kv_heads, self.head_dim, self.window)
+
+    def prepare(self, dtype, device) -> None:
+        if self.position_encoding is not None:
+            self.position_encoding.prepare(dtype, device)
+
+    def forward(self, ctx: StepContext, h: torch.Tensor, cache: LayerCache) -> torch.Tensor:
+        group = ctx.groups[cache.group]
+        if cache.owner:
+            qkv = matmul_tn(h, self.qkv)
+            q = qkv[:, :self.q_size]
+            k = qkv[:, self.q_size:self.q_size + self.kv_size]
+            v = qkv[:, self.q_size + self.kv_size:]
+        else:  # keys and values are another call's: only the queries are needed
+            q = matmul_tn(h, self.qkv[:self.q_size])
+            k = v = None
+        fused = self.position_encoding.fused_rotary() if self.position_encoding is not None else None
+        if self.position_encoding is not None and fused is None:
+            self.position_encoding.apply(ctx, q, k, self.num_heads, self.num_kv_heads, self.head_dim)
+        inv_freq, rot_dim, is_neox = fused if fused is not None else (None, 0, True)
+        if fused is not None or cache.owner:
+            kernels.rope_cache_write(q, k, v, ctx.positions, ctx.token_seq, group.block_table, group.block_size,
+                                     cache.kv if cache.owner else None, inv_freq, rot_dim, is_neox, self.num_heads,
+                                     self.num_kv_heads, self.head_dim, ctx.error_flag)
+        out = torch.empty((ctx.n_tokens, self.q_size), dtype=h.dtype, device=h.device)
+        self.attend(ctx, out, q, cache.kv, group)
+        return matmul_tn(out, self.o)
+
+    def attend(self, ctx: StepContext, out: torch.Tensor, q: torch.Tensor, kv: torch.Tensor, group) -> None:
+        kernels.attention_generic(out, q, kv, group.block_table, group.block_size, ctx.token_seq, ctx.positions,
+                                  self.scale, self.window or 0, self.num_heads, self.num_kv_heads, self.head_dim)

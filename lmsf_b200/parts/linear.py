@@ -1,0 +1,60 @@
+"""Dense projections y = x W^T (no bias), weight stored [out, in] as in the checkpoint.
+
+The reference's linear family (core/src/model_executor/layers/linear.rs:28-106, :325-497, :499-728)
+wraps cuBLASLt and merges q, k, v (and gate, up) into one matrix by row ranges; the same merged
+layouts are used here.  bfloat16 products go to the library (cuBLAS through torch.mm), the place
+where the reference calls a library too; float32 products run on this package's own FFMA kernel so
+that no reduced-precision mode can slip in and a row's result does not depend on the batch.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence, Union
+
+import torch
+
+from .. import kernels
+from .base import Part, WeightSpec, register_part
+
+_MM_HAS_OUT_DTYPE: Optional[bool] = None
+
+
+def matmul_tn(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """x [M, K] times w [N, K] transposed -> [M, N] in `out_dtype` (default: x's dtype)."""
+    global _MM_HAS_OUT_DTYPE
+    out_dtype = out_dtype or x.dtype
+    if x.dtype == torch.float32:
+        out = torch.empty((x.shape[0], w.shape[0]), dtype=torch.float32, device=x.device)
+        kernels.gemm_tn_simt(out, x, w)
+        return out if out_dtype == torch.float32 else out.to(out_dtype)
+    if out_dtype == x.dtype:
+        return torch.mm(x, w.t())
+    if _MM_HAS_OUT_DTYPE is not False:
+        try:
+            y = torch.mm(x, w.t(), out_dtype=out_dtype)
+            _MM_HAS_OUT_DTYPE = True
+            return y
+        except (TypeError, RuntimeError):
+            if _MM_HAS_OUT_DTYPE:
+                raise
+            _MM_HAS_OUT_DTYPE = False
+    out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype, device=x.device)
+    kernels.gemm_tn_simt(out, x, w)
+    return out
+
+
+@register_part("linear", "dense")
+class Linear(Part):
+    """out_features may be a list: the sources are stacked along the output dimension."""
+
+    def __init__(self, in_features: int, out_features: Union[int, Sequence[int]], out_dtype: Optional[str] = None):
+        self.in_features = int(in_features)
+        self.out_splits: List[int] = [int(out_features)] if isinstance(out_features, int) else [int(o) for o in out_features]
+        self.out_features = sum(self.out_splits)
+        self.out_dtype = {None: None, "float32": torch.float32, "bfloat16": torch.bfloat16}[out_dtype]
+        self.weight: Optional[torch.Tensor] = None
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        return {"weight": WeightSpec([(o, self.in_features) for o in self.out_splits])}
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return matmul_tn(x, self.weight, self.out_dtype)

@@ -1,0 +1,35 @@
+"""Gated feed-forward: (act(h Wg^T) * (h Wu^T)) Wd^T, gate and up merged into one matrix.
+
+Reference: Mlp in core/src/model_executor/models/llama/llama.rs:223-274 with silu_and_mul_kernel
+(vllm/kernels/activation_kernels.cu:26-41).  The activation is a parameter here (the reference
+fixes SiLU in code although it parses `hidden_act`).
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from .. import kernels
+from .base import FeedForward, StepContext, WeightSpec, register_part
+from .linear import matmul_tn
+
+
+@register_part("feed_forward", "gated_mlp")
+class GatedMLP(FeedForward):
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu"):
+        if activation not in kernels.ACT_CODES:
+            raise ValueError(f"activation {activation!r} is not supported (known: {', '.join(sorted(kernels.ACT_CODES))})")
+        self.hidden_size, self.intermediate_size, self.activation = int(hidden_size), int(intermediate_size), activation
+        self.gate_up: Optional[torch.Tensor] = None
+        self.down: Optional[torch.Tensor] = None
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        return {"gate_up": WeightSpec([(self.intermediate_size, self.hidden_size)] * 2),
+                "down": WeightSpec([(self.hidden_size, self.intermediate_size)])}
+
+    def forward(self, ctx: StepContext, h: torch.Tensor) -> torch.Tensor:
+        gu = matmul_tn(h, self.gate_up)
+        m = torch.empty((h.shape[0], self.intermediate_size), dtype=h.dtype, device=h.device)
+        kernels.gated_act(m, gu, self.activation)
+        return matmul_tn(m, self.down)
