@@ -1,0 +1,60 @@
+"""The Python entry point: `LLM(...).generate(prompt_token_ids, SamplingParams(...))`.
+
+The reference is driven from Rust (example/examples/llm_engine_example.rs:65-151: add requests,
+loop `step` while `has_unfinished_requests`); this class is that loop with the engine's options as
+keywords named like the reference's flags (core/src/common/config.rs:11-87).
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence, Union
+
+from ..config.engine_config import EngineArgs
+from ..sampling.params import SamplingParams
+from .llm_engine import LLMEngine
+from .sequence import RequestOutput
+
+
+class LLM:
+    def __init__(self, model: str, dtype: Optional[str] = None, block_size: int = 16,
+                 gpu_memory_utilization: float = 0.9, max_model_len: Optional[int] = None,
+                 max_num_batched_tokens: Optional[int] = None, max_num_seqs: int = 256, seed: int = 0,
+                 num_gpu_blocks: Optional[int] = None, enforce_eager: bool = False, load_format: str = "auto",
+                 device: str = "cuda:0"):
+        self.engine = LLMEngine(EngineArgs(model=model, max_num_batched_tokens=max_num_batched_tokens,
+                                           max_num_seqs=max_num_seqs, max_model_len=max_model_len,
+                                           block_size=block_size, seed=seed,
+                                           gpu_memory_utilization=gpu_memory_utilization, dtype=dtype,
+                                           num_gpu_blocks=num_gpu_blocks, enforce_eager=enforce_eager),
+                                device=device, load_format=load_format)
+        self._next_id = 0
+
+    def generate(self, prompts: Optional[Union[str, Sequence[str]]] = None,
+                 sampling_params: Optional[Union[SamplingParams, Sequence[SamplingParams]]] = None,
+                 prompt_token_ids: Optional[Sequence[Sequence[int]]] = None) -> List[RequestOutput]:
+        """Runs all prompts to their end; outputs come back in the order of the prompts."""
+        if prompt_token_ids is None:
+            if prompts is None:
+                raise ValueError("give prompts or prompt_token_ids")
+            prompts = [prompts] if isinstance(prompts, str) else list(prompts)
+            n = len(prompts)
+        else:
+            n = len(prompt_token_ids)
+            prompts = [None] * n
+        if sampling_params is None:
+            sampling_params = SamplingParams()
+        params = [sampling_params] * n if isinstance(sampling_params, SamplingParams) else list(sampling_params)
+        if len(params) != n:
+            raise ValueError("one SamplingParams for all prompts, or one per prompt")
+        ids = []
+        for i in range(n):
+            rid = self._next_id
+            self._next_id += 1
+            ids.append(rid)
+            self.engine.add_request(rid, prompts[i], params[i],
+                                    prompt_token_ids[i] if prompt_token_ids is not None else None)
+        done = {}
+        while self.engine.has_unfinished_requests():
+            for out in self.engine.step():
+                if out.finished:
+                    done[out.request_id] = out
+        return [done[r] for r in ids]

@@ -1,0 +1,81 @@
+"""Requests as the engine tracks them, and what the engine reports about them.
+
+Reduced from the reference's Sequence / SequenceGroup (core/src/common/sequence.rs:36-65 states,
+:125-287 sequence, :289-469 group) to one sequence per request, and from RequestOutput /
+CompletionOutput (core/src/common/output.rs:6-55).
+"""
+from __future__ import annotations
+
+import enum
+import time
+from dataclasses import dataclass, field
+from typing import Hashable, List, Optional
+
+from ..sampling.params import SamplingParams
+
+
+class SequenceStatus(enum.Enum):
+    WAITING = "waiting"
+    RUNNING = "running"
+    FINISHED_STOPPED = "stop"          # EOS or a stop token
+    FINISHED_LENGTH = "length"         # max_tokens, max_model_len or the cache cannot hold more
+    FINISHED_ABORTED = "abort"
+    FINISHED_IGNORED = "ignored"       # never ran: the prompt cannot fit (cf. core/src/sched/scheduler.rs:367-381)
+
+    @property
+    def finished(self) -> bool:
+        return self not in (SequenceStatus.WAITING, SequenceStatus.RUNNING)
+
+
+@dataclass
+class Sequence:
+    request_id: Hashable
+    prompt_token_ids: List[int]
+    sampling_params: SamplingParams
+    arrival_time: float = field(default_factory=time.monotonic)
+    output_token_ids: List[int] = field(default_factory=list)
+    status: SequenceStatus = SequenceStatus.WAITING
+    num_computed: int = 0             # tokens whose keys and values are in the cache
+    num_preemptions: int = 0
+    seed: int = 0
+    first_token_time: Optional[float] = None
+    finish_time: Optional[float] = None
+
+    @property
+    def token_ids(self) -> List[int]:
+        return self.prompt_token_ids + self.output_token_ids
+
+    def __len__(self) -> int:
+        return len(self.prompt_token_ids) + len(self.output_token_ids)
+
+    @property
+    def num_uncomputed(self) -> int:
+        return len(self) - self.num_computed
+
+    def next_tokens(self, n: int) -> List[int]:
+        a = self.num_computed
+        if a + n <= len(self.prompt_token_ids):
+            return self.prompt_token_ids[a:a + n]
+        return self.token_ids[a:a + n]
+
+
+@dataclass
+class CompletionOutput:
+    index: int
+    text: Optional[str]
+    token_ids: List[int]
+    finish_reason: Optional[str]
+
+
+@dataclass
+class RequestOutput:
+    request_id: Hashable
+    prompt_token_ids: List[int]
+    outputs: List[CompletionOutput]
+    finished: bool
+
+    @staticmethod
+    def from_sequence(seq: Sequence, text: Optional[str] = None) -> "RequestOutput":
+        reason = seq.status.value if seq.status.finished else None
+        return RequestOutput(seq.request_id, list(seq.prompt_token_ids),
+                             [CompletionOutput(0, text, list(seq.output_token_ids), reason)], seq.status.finished)

@@ -1,0 +1,108 @@
+"""The engine end to end on the GPU: generation through the Python entry point against the plain
+implementation, sampling, preemption, long decoding."""
+import pytest
+import torch
+
+import plain_llama as P
+import util
+
+pytestmark = pytest.mark.gpu
+
+
+def _llm(name, dtype, std=0.15, **kw):
+    from lmsf_b200 import LLM
+    return LLM(util.model_folder(name, dtype, std), dtype=dtype, block_size=util.BLOCK_SIZE[name], **kw)
+
+
+@pytest.mark.parametrize("name,lengths,steps", [("A", [5, 17, 33], 8), ("B", [1, 9, 40, 64, 130], 12)])
+def test_greedy_generation_matches_the_plain_implementation(name, lengths, steps):
+    from lmsf_b200 import SamplingParams
+    cfg, w = P.load_model(util.model_folder(name, "float32", 0.15))
+    prompts = [util.random_ids(n, cfg["vocab_size"], i) for i, n in enumerate(lengths)]
+    llm = _llm(name, "float32", num_gpu_blocks=64, max_num_batched_tokens=48, max_num_seqs=4)
+    outs = llm.generate(prompt_token_ids=prompts,
+                        sampling_params=SamplingParams(temperature=0.0, max_tokens=steps, ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        ref, _ = P.generate(cfg, w, p, steps)
+        assert o.outputs[0].token_ids == ref and o.outputs[0].finish_reason == "length" and o.finished
+        assert o.prompt_token_ids == p
+
+
+def test_temperature_sampling_is_reproducible_and_independent_of_the_batch():
+    from lmsf_b200 import SamplingParams
+    name = "B"
+    cfg, w = P.load_model(util.model_folder(name, "float32", 0.15))
+    prompts = [util.random_ids(n, cfg["vocab_size"], 10 + i) for i, n in enumerate([1, 9, 40, 64, 130])]
+    sp = [SamplingParams(temperature=0.8, seed=1 + i, max_tokens=12, ignore_eos=True) for i in range(5)]
+    llm = _llm(name, "float32", num_gpu_blocks=64, max_num_batched_tokens=48, max_num_seqs=4)
+    together = [o.outputs[0].token_ids for o in llm.generate(prompt_token_ids=prompts, sampling_params=sp)]
+    alone = [llm.generate(prompt_token_ids=[p], sampling_params=s)[0].outputs[0].token_ids for p, s in zip(prompts, sp)]
+    assert together == alone
+    for p, s, got in zip(prompts, sp, together):
+        ref, _ = P.generate(cfg, w, p, 12, temperature=0.8, seed=s.seed)
+        assert got == ref
+
+
+def test_preemption_by_recompute_gives_the_same_tokens():
+    from lmsf_b200 import SamplingParams
+    name = "A"
+    cfg = util.CONFIGS[name]
+    prompts = [util.random_ids(n, cfg["vocab_size"], 20 + i) for i, n in enumerate([30, 25, 28, 20])]
+    sp = [SamplingParams(temperature=0.7 if i % 2 else 0.0, seed=5 + i, max_tokens=40, ignore_eos=True) for i in range(4)]
+    roomy = _llm(name, "float32", num_gpu_blocks=128, max_num_seqs=4)
+    want = [o.outputs[0].token_ids for o in roomy.generate(prompt_token_ids=prompts, sampling_params=sp)]
+    assert roomy.engine.scheduler.num_preemptions == 0
+    tight = _llm(name, "float32", num_gpu_blocks=22, max_num_seqs=4)       # 176 slots for up to 4 * 70 tokens
+    got = [o.outputs[0].token_ids for o in tight.generate(prompt_token_ids=prompts, sampling_params=sp)]
+    assert tight.engine.scheduler.num_preemptions > 0
+    assert got == want
+    tight.engine.cache.check_invariants()
+    assert tight.engine.cache.num_free_pages() == 22
+
+
+def test_stop_conditions_and_rejection():
+    from lmsf_b200 import SamplingParams
+    name = "A"
+    cfg, w = P.load_model(util.model_folder(name, "float32", 0.15))
+    p = util.random_ids(12, cfg["vocab_size"], 31)
+    ref, _ = P.generate(cfg, w, p, 10)
+    llm = _llm(name, "float32", num_gpu_blocks=32, max_model_len=64)
+    o = llm.generate(prompt_token_ids=[p], sampling_params=SamplingParams(temperature=0, max_tokens=10,
+                                                                           stop_token_ids=[ref[4]]))[0]
+    k = ref.index(ref[4])
+    assert o.outputs[0].token_ids == ref[:k + 1] and o.outputs[0].finish_reason == "stop"
+    # a prompt beyond max_model_len never runs; one that reaches it stops with "length"
+    outs = llm.generate(prompt_token_ids=[list(range(1, 70)), util.random_ids(60, 256, 1)],
+                        sampling_params=SamplingParams(temperature=0, max_tokens=50, ignore_eos=True))
+    assert outs[0].outputs[0].finish_reason == "ignored" and outs[0].outputs[0].token_ids == []
+    assert outs[1].outputs[0].finish_reason == "length" and len(outs[1].outputs[0].token_ids) == 4
+    with pytest.raises(ValueError):
+        llm.generate(prompt_token_ids=[[999]])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_stays_on_the_reference(dtype):
+    """300 decoded tokens fed back one by one (teacher-forced with the plain implementation's tokens)."""
+    import traces
+    name = "B"
+    cfg, w = P.load_model(util.model_folder(name, dtype, 0.15))
+    ids = util.random_ids(250, cfg["vocab_size"], 77)
+    ref = P.forward(cfg, w, ids).numpy()
+    steps = traces.whole({"x": ids}, tail=240)
+    out = traces.collect(steps, traces.run_inprocess(util.model_folder(name, dtype, 0.15), dtype, steps, 16, 256))
+    worst = max(abs(out[("x", i)] - ref[i]).max() for i in range(250))
+    assert worst <= (1e-5 if dtype == "float32" else 5e-2) * max(1.0, abs(ref).max())
+
+
+def test_bfloat16_generation_runs_and_mostly_agrees():
+    from lmsf_b200 import SamplingParams
+    name = "A"
+    cfg, w = P.load_model(util.model_folder(name, "bfloat16", 0.15))
+    p = util.random_ids(20, cfg["vocab_size"], 41)
+    o = _llm(name, "bfloat16", num_gpu_blocks=32).generate(
+        prompt_token_ids=[p], sampling_params=SamplingParams(temperature=0, max_tokens=6, ignore_eos=True))[0]
+    ref, rows = P.generate(cfg, w, p, 1)
+    top2 = torch.topk(rows[0], 2).values
+    if float(top2[0] - top2[1]) > 0.1 * float(rows[0].abs().max()):      # a clear winner must be found in bfloat16 too
+        assert o.outputs[0].token_ids[0] == ref[0]
+    assert len(o.outputs[0].token_ids) == 6

@@ -1,0 +1,263 @@
+"""Each CUDA kernel alone against a plain float32 PyTorch statement of the same operation, at sizes other
+than the tiny models' (widths that are no power of two, head sizes in steps of 16, odd head counts)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as P
+
+pytestmark = pytest.mark.gpu
+
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def dev():
+    return torch.device("cuda:0")
+
+
+def tol(dtype):
+    return dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("hidden,vocab", [(40, 50), (1000, 333), (4104, 17)])
+def test_embedding(dtype, hidden, vocab):
+    from lmsf_b200 import kernels
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(vocab, hidden, generator=g).to(DT[dtype]).to(dev())
+    ids = torch.randint(0, vocab, (37,), generator=g, dtype=torch.int32).to(dev())
+    out = torch.empty(37, hidden, dtype=DT[dtype], device=dev())
+    flag = torch.zeros(1, dtype=torch.int32, device=dev())
+    kernels.embedding(out, table, ids, flag)
+    assert torch.equal(out, table[ids.long()]) and flag.item() == 0
+    ids[5] = vocab                      # outside the table: zeros and a raised flag, no stray read
+    kernels.embedding(out, table, ids, flag)
+    assert flag.item() == 1 and torch.all(out[5] == 0) and torch.equal(out[6], table[ids[6].long()])
+
+
+@pytest.mark.parametrize("dtype,wdtype", [("float32", "float32"), ("bfloat16", "bfloat16"), ("bfloat16", "float32")])
+@pytest.mark.parametrize("hidden", [48, 1000, 5120, 11000])
+def test_add_rmsnorm(dtype, wdtype, hidden):
+    from lmsf_b200 import kernels
+    g = torch.Generator().manual_seed(1)
+    n, eps = 9, 3e-6
+    x = (torch.randn(n, hidden, generator=g) * 3).to(DT[dtype])
+    w = (1 + 0.1 * torch.randn(hidden, generator=g)).to(DT[wdtype])
+    res0 = torch.randn(n, hidden, generator=g)
+    xd, wd = x.to(dev()), w.to(dev())
+    # mode 0
+    h = torch.empty_like(xd)
+    kernels.add_rmsnorm(h, xd, None, wd, eps, 0)
+    ref = P.rms_norm(x.float(), w.float(), eps)
+    assert torch.allclose(h.float().cpu(), ref, **tol(DT[dtype]))
+    # mode 1: the residual starts as x
+    res = torch.empty(n, hidden, dtype=torch.float32, device=dev())
+    kernels.add_rmsnorm(h, xd, res, wd, eps, 1)
+    assert torch.equal(res.cpu(), x.float()) and torch.allclose(h.float().cpu(), ref, **tol(DT[dtype]))
+    # mode 2: the sum is float32 and is what gets normalised
+    res = res0.to(dev())
+    kernels.add_rmsnorm(h, xd, res, wd, eps, 2)
+    s = res0 + x.float()
+    assert torch.equal(res.cpu(), s)
+    assert torch.allclose(h.float().cpu(), P.rms_norm(s, w.float(), eps), **tol(DT[dtype]))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("d", [24, 172, 1000, 14336])
+def test_gated_act(dtype, d):
+    from lmsf_b200 import kernels
+    g = torch.Generator().manual_seed(2)
+    x = (torch.randn(7, 2 * d + 8, generator=g) * 2).to(DT[dtype]).to(dev())[:, :2 * d]   # a strided view
+    out = torch.empty(7, d, dtype=DT[dtype], device=dev())
+    kernels.gated_act(out, x, "silu")
+    xf = x.float().cpu()
+    ref = xf[:, :d] / (1 + torch.exp(-xf[:, :d])) * xf[:, d:]
+    assert torch.allclose(out.float().cpu(), ref, **tol(DT[dtype]))
+    kernels.gated_act(out, x, "gelu_tanh")
+    ref = torch.nn.functional.gelu(xf[:, :d], approximate="tanh") * xf[:, d:]
+    assert torch.allclose(out.float().cpu(), ref, **tol(DT[dtype]))
+    with pytest.raises(kernels.KernelError):
+        kernels.gated_act(out, x, "relu")
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 7, 5), (3, 130, 67), (70, 65, 129), (129, 300, 1000)])
+def test_gemm_simt_is_true_float32_and_row_independent(M, N, K):
+    from lmsf_b200 import kernels
+    g = torch.Generator().manual_seed(3)
+    a, w = torch.randn(M, K, generator=g), torch.randn(N, K, generator=g)
+    out = torch.empty(M, N, device=dev())
+    kernels.gemm_tn_simt(out, a.to(dev()), w.to(dev()))
+    ref = (a.double() @ w.double().T)
+    # float32 accumulation error grows like sqrt(K) ulps; TF32 would be off by ~1e-3 relative
+    assert (out.cpu().double() - ref).abs().max() <= 2e-6 * math.sqrt(K) * ref.abs().max()
+    one = torch.empty(1, N, device=dev())
+    kernels.gemm_tn_simt(one, a[M - 1:].to(dev()), w.to(dev()))
+    assert torch.equal(one[0], out[M - 1])              # a row does not depend on its batch
+    # bfloat16 inputs, float32 output (the plain twin of the tensor-core products)
+    ab, wb = a.bfloat16(), w.bfloat16()
+    kernels.gemm_tn_simt(out, ab.to(dev()), wb.to(dev()))
+    assert torch.allclose(out.cpu(), ab.float() @ wb.float().T, rtol=1e-4, atol=1e-4 * math.sqrt(K))
+
+
+def _paged_setup(dtype, n_q_heads, n_kv_heads, hd, bs, ctx_lens, q_lens, seed, sharp=False):
+    """Random q and paged k, v for several requests; pages handed out in a scrambled order."""
+    g = torch.Generator().manual_seed(seed)
+    S = len(ctx_lens)
+    n_pages = sum((c + bs - 1) // bs for c in ctx_lens) + 3
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    max_blocks = max((c + bs - 1) // bs for c in ctx_lens)
+    bt = torch.full((S, max_blocks), -1, dtype=torch.int32)
+    cache = torch.zeros(n_pages, 2, n_kv_heads, bs, hd)
+    ks, vs = [], []
+    for s, c in enumerate(ctx_lens):
+        k, v = torch.randn(c, n_kv_heads, hd, generator=g), torch.randn(c, n_kv_heads, hd, generator=g)
+        if sharp:            # one far key stands out for the last queries: a lost key changes the result visibly
+            k[1] *= 6.0
+        k, v = k.to(DT[dtype]).float(), v.to(DT[dtype]).float()
+        ks.append(k)
+        vs.append(v)
+        for i in range((c + bs - 1) // bs):
+            page = perm.pop()
+            bt[s, i] = page
+            n = min(bs, c - i * bs)
+            cache[page, 0, :, :n] = k[i * bs:i * bs + n].transpose(0, 1)
+            cache[page, 1, :, :n] = v[i * bs:i * bs + n].transpose(0, 1)
+    N = sum(q_lens)
+    q = torch.randn(N, n_q_heads * hd, generator=g)
+    if sharp:
+        q = q * 2.0
+    q = q.to(DT[dtype])
+    token_seq = torch.repeat_interleave(torch.arange(S, dtype=torch.int32), torch.tensor(q_lens))
+    positions = torch.cat([torch.arange(c - n, c, dtype=torch.int32) for c, n in zip(ctx_lens, q_lens)])
+    return q, cache.to(DT[dtype]), bt, token_seq, positions, ks, vs
+
+
+def _attention_reference(q, ks, vs, token_seq, positions, n_q_heads, n_kv_heads, hd, scale, window):
+    out = torch.empty(q.shape[0], n_q_heads, hd, dtype=torch.float64)
+    r = n_q_heads // n_kv_heads
+    qf = q.double().reshape(-1, n_q_heads, hd)
+    for t in range(q.shape[0]):
+        s, p = int(token_seq[t]), int(positions[t])
+        lo = max(0, p - window + 1) if window else 0
+        for h in range(n_q_heads):
+            k, v = ks[s][lo:p + 1, h // r].double(), vs[s][lo:p + 1, h // r].double()
+            w = torch.softmax((k @ qf[t, h]) * scale, dim=0)
+            out[t, h] = w @ v
+    return out.reshape(q.shape[0], -1)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nh,nkv,hd,bs,window", [(6, 2, 16, 4, 0), (5, 5, 48, 8, 0), (8, 1, 80, 16, 0),
+                                               (4, 2, 112, 32, 37), (2, 2, 256, 16, 0), (3, 1, 64, 16, 100)])
+def test_attention_generic(dtype, nh, nkv, hd, bs, window):
+    from lmsf_b200 import kernels
+    ctx_lens, q_lens = [150, 1, 67, 300], [150, 1, 5, 1]          # a whole prompt, a first token, a portion, a decode
+    q, cache, bt, token_seq, positions, ks, vs = _paged_setup(dtype, nh, nkv, hd, bs, ctx_lens, q_lens, 4, sharp=True)
+    out = torch.empty(q.shape, dtype=DT[dtype], device=dev())
+    scale = 1.0 / math.sqrt(hd)
+    kernels.attention_generic(out, q.to(dev()), cache.to(dev()), bt.to(dev()), bs, token_seq.to(dev()),
+                              positions.to(dev()), scale, window, nh, nkv, hd)
+    ref = _attention_reference(q.float(), ks, vs, token_seq, positions, nh, nkv, hd, scale, window)
+    assert torch.allclose(out.float().cpu().double(), ref, **(dict(rtol=1e-5, atol=2e-6) if dtype == "float32"
+                                                              else dict(rtol=2e-2, atol=1e-2)))
+
+
+def test_attention_refuses_sizes_it_was_not_written_for():
+    from lmsf_b200 import kernels
+    d = dev()
+    q = torch.zeros(1, 2 * 24, device=d)
+    with pytest.raises((kernels.KernelError, ValueError)):
+        kernels.attention_generic(torch.empty_like(q), q, torch.zeros(1, 2, 2, 4, 24, device=d),
+                                  torch.zeros(1, 1, dtype=torch.int32, device=d), 4,
+                                  torch.zeros(1, dtype=torch.int32, device=d), torch.zeros(1, dtype=torch.int32, device=d),
+                                  1.0, 0, 2, 2, 24)
+    q = torch.zeros(1, 272, device=d)
+    with pytest.raises(kernels.KernelError):
+        kernels.attention_generic(torch.empty_like(q), q, torch.zeros(1, 2, 1, 4, 272, device=d),
+                                  torch.zeros(1, 1, dtype=torch.int32, device=d), 4,
+                                  torch.zeros(1, dtype=torch.int32, device=d), torch.zeros(1, dtype=torch.int32, device=d),
+                                  1.0, 0, 1, 1, 272)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nh,nkv,hd,rot,neox,bs", [(4, 2, 16, 16, True, 4), (5, 1, 48, 48, True, 8),
+                                                  (3, 3, 64, 32, True, 16), (2, 1, 32, 32, False, 16)])
+def test_rope_and_cache_write(dtype, nh, nkv, hd, rot, neox, bs):
+    from lmsf_b200 import kernels
+    g = torch.Generator().manual_seed(5)
+    N, S, max_blocks = 11, 2, 40
+    positions = torch.tensor([0, 1, 2, 3, 4, 5, 6, 300, 301, 302, 303], dtype=torch.int32)
+    token_seq = torch.tensor([0] * 7 + [1] * 4, dtype=torch.int32)
+    bt = torch.full((S, max_blocks), -1, dtype=torch.int32)
+    pages = torch.randperm(50, generator=g).tolist()
+    for t in range(N):
+        s, b = int(token_seq[t]), int(positions[t]) // bs
+        if bt[s, b] < 0:
+            bt[s, b] = pages.pop()
+    width = (nh + 2 * nkv) * hd
+    qkv = torch.randn(N, width, generator=g).to(DT[dtype])
+    inv = torch.tensor([10000.0 ** (-(2.0 * i) / rot) for i in range(rot // 2)], dtype=torch.float64)
+    cache = torch.zeros(50, 2, nkv, bs, hd, dtype=DT[dtype], device=dev())
+    qkv_d = qkv.to(dev()).clone()
+    flag = torch.zeros(1, dtype=torch.int32, device=dev())
+    kernels.rope_cache_write(qkv_d[:, :nh * hd], qkv_d[:, nh * hd:(nh + nkv) * hd], qkv_d[:, (nh + nkv) * hd:],
+                             positions.to(dev()), token_seq.to(dev()), bt.to(dev()), bs, cache,
+                             inv.float().to(dev()), rot, neox, nh, nkv, hd, flag)
+    assert flag.item() == 0
+
+    def rotate(x, heads):
+        x = x.float().reshape(N, heads, hd)
+        xr = x[..., :rot]
+        if neox:
+            y = P.rotary_neox(xr, positions, inv)
+        else:                     # interleaved pairs (2i, 2i+1)
+            ang = positions.float()[:, None] * inv.float()[None, :]
+            c, s = ang.cos()[:, None, :], ang.sin()[:, None, :]
+            a, b = xr[..., 0::2], xr[..., 1::2]
+            y = torch.stack([a * c - b * s, b * c + a * s], dim=-1).reshape(N, heads, rot)
+        return torch.cat([y, x[..., rot:]], dim=-1)
+
+    q_ref, k_ref = rotate(qkv[:, :nh * hd], nh), rotate(qkv[:, nh * hd:(nh + nkv) * hd], nkv)
+    v_ref = qkv[:, (nh + nkv) * hd:].float().reshape(N, nkv, hd)
+    t_ = tol(DT[dtype])
+    assert torch.allclose(qkv_d[:, :nh * hd].float().cpu().reshape(N, nh, hd), q_ref, **t_)
+    c = cache.float().cpu()
+    for t in range(N):
+        page, slot = int(bt[int(token_seq[t]), int(positions[t]) // bs]), int(positions[t]) % bs
+        assert torch.allclose(c[page, 0, :, slot], k_ref[t], **t_)
+        assert torch.equal(c[page, 1, :, slot], v_ref[t])
+    used = {int(b) for b in bt.flatten() if b >= 0}
+    for p in range(50):
+        if p not in used:
+            assert torch.all(c[p] == 0)                 # nothing is written anywhere else
+    # a token without a page raises the flag and writes nothing
+    bt2 = bt.clone()
+    bt2[1, 300 // bs] = -1
+    kernels.rope_cache_write(qkv_d[:, :nh * hd], qkv_d[:, nh * hd:(nh + nkv) * hd], qkv_d[:, (nh + nkv) * hd:],
+                             positions.to(dev()), token_seq.to(dev()), bt2.to(dev()), bs, cache,
+                             inv.float().to(dev()), rot, neox, nh, nkv, hd, flag)
+    assert flag.item() == 2
+
+
+def test_sampling_greedy_and_temperature():
+    from lmsf_b200 import kernels
+    g = torch.Generator().manual_seed(6)
+    for vocab in (7, 320, 50001):
+        rows = 6
+        logits = torch.randn(rows, vocab, generator=g) * 3
+        logits[0, 3] = logits[0, 5] = 50.0                       # a tie: the lowest index wins
+        d = logits.to(dev())
+        out = torch.empty(rows, dtype=torch.int32, device=dev())
+        kernels.sample(out, d)
+        assert out.tolist() == [3] + [int(logits[r].argmax()) for r in range(1, rows)]
+        temp = torch.tensor([0.0, 0.8, 0.8, 1.5, 0.3, 0.8], device=dev())
+        seeds = [0, 1, 1, 2 ** 63 + 5, 77, 1]
+        steps = [0, 0, 1, 9, 3, 0]
+        seed_t = torch.from_numpy(np.asarray(seeds, dtype=np.uint64).view(np.int64)).to(dev())
+        kernels.sample(out, d, temp, seed_t, torch.tensor(steps, dtype=torch.int32, device=dev()))
+        got = out.tolist()
+        assert got[0] == 3
+        for r in range(1, rows):
+            assert got[r] == P.sample_temperature(logits[r], float(temp[r]), seeds[r], steps[r]), (vocab, r)

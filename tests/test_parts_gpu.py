@@ -1,0 +1,223 @@
+"""Each part alone against its plain formula, and the generality of the composition: a toy mixer with
+state of its own, a layer run twice and a layer that reads another layer's cache, all defined here and
+run through the unchanged step function."""
+import json
+import math
+import os
+
+import pytest
+import torch
+
+import plain_llama as P
+import util
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def test_rmsnorm_part_keeps_a_32bit_weight():
+    from lmsf_b200.parts.norm import RMSNorm
+    n = RMSNorm(hidden_size=100, eps=1e-6)
+    assert n.weight_specs()["weight"].keep_fp32
+    g = torch.Generator().manual_seed(0)
+    w = 1 + 0.2 * torch.randn(100, generator=g)
+    x = torch.randn(5, 100, generator=g).bfloat16()
+    n.set_weights({"weight": w.to(DEV)})                       # float32 weight under bfloat16 activations
+    h, res = n.forward_residual(x.to(DEV), None)
+    assert res.dtype == torch.float32 and torch.equal(res.cpu(), x.float())
+    assert torch.allclose(h.float().cpu(), P.rms_norm(x.float(), w, 1e-6), rtol=1e-2, atol=1e-2)
+    h2, res2 = n.forward_residual(x.to(DEV), res)
+    assert res2 is res and torch.equal(res.cpu(), x.float() * 2)
+
+
+def test_rotary_part_frequencies_match_the_plain_rule():
+    from lmsf_b200.parts.rope import RotaryEmbedding
+    for cfg in (util.TINY_A, util.TINY_B):
+        hd = cfg.get("head_dim") or cfg["hidden_size"] // cfg["num_attention_heads"]
+        sc = cfg.get("rope_scaling") or {}
+        r = RotaryEmbedding(rot_dim=hd, theta=cfg["rope_theta"], scaling_type=sc.get("rope_type", "default"),
+                            factor=sc.get("factor", 1.0), low_freq_factor=sc.get("low_freq_factor", 1.0),
+                            high_freq_factor=sc.get("high_freq_factor", 4.0),
+                            original_max_position_embeddings=sc.get("original_max_position_embeddings", 8192))
+        r.prepare(torch.float32, torch.device(DEV))
+        inv, rot, neox = r.fused_rotary()
+        assert rot == hd and neox and torch.equal(inv.cpu(), P.rope_inv_freq(cfg).float())
+
+
+def test_linear_and_mlp_parts():
+    from lmsf_b200.parts.linear import Linear
+    from lmsf_b200.parts.mlp import GatedMLP
+    g = torch.Generator().manual_seed(1)
+    for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 3e-2)):
+        lin = Linear(in_features=72, out_features=[40, 24])
+        assert lin.weight_specs()["weight"].shapes == [(40, 72), (24, 72)]
+        w = (torch.randn(64, 72, generator=g) * 0.2).to(dtype)
+        x = torch.randn(9, 72, generator=g).to(dtype)
+        lin.set_weights({"weight": w.to(DEV)})
+        assert torch.allclose(lin.forward(x.to(DEV)).float().cpu(), x.float() @ w.float().T, rtol=tol, atol=tol)
+        head = Linear(in_features=72, out_features=64, out_dtype="float32")
+        head.set_weights({"weight": w.to(DEV)})
+        y = head.forward(x.to(DEV))
+        assert y.dtype == torch.float32 and torch.allclose(y.cpu(), x.float() @ w.float().T, rtol=1e-4, atol=1e-4)
+        mlp = GatedMLP(hidden_size=72, intermediate_size=100)
+        gu = (torch.randn(200, 72, generator=g) * 0.2).to(dtype)
+        dn = (torch.randn(72, 100, generator=g) * 0.2).to(dtype)
+        mlp.set_weights({"gate_up": gu.to(DEV), "down": dn.to(DEV)})
+        ref = P.silu_gated_mlp(x.float(), gu[:100].float(), gu[100:].float(), dn.float())
+        assert torch.allclose(mlp.forward(None, x.to(DEV)).float().cpu(), ref, rtol=tol, atol=tol)
+
+
+# ----------------------------------------------------------------------------- a toy architecture, defined here
+
+def _register_toy():
+    from lmsf_b200.config.registry import register_architecture
+    from lmsf_b200.parts.base import (LayerCall, LayerSpec, Mixer, ModelSpec, PartSpec, StateSpec, WeightSpec,
+                                      register_part)
+    from lmsf_b200.parts.linear import matmul_tn
+
+    @register_part("mixer", "toy_decay")
+    class ToyDecayMixer(Mixer):
+        """s_t = decay * s_{t-1} + h_t W_in^T ; out_t = s_t W_out^T.  Its state is one vector per request."""
+
+        def __init__(self, hidden_size, state_size, decay):
+            self.hidden_size, self.state_size, self.decay = hidden_size, state_size, decay
+
+        def weight_specs(self):
+            return {"w_in": WeightSpec([(self.state_size, self.hidden_size)]),
+                    "w_out": WeightSpec([(self.hidden_size, self.state_size)])}
+
+        def state_spec(self):
+            return StateSpec((self.state_size,))
+
+        def forward(self, ctx, h, cache):
+            u = matmul_tn(h, self.w_in).float()
+            out = torch.empty_like(u)
+            off = 0
+            for n, slot in zip(ctx.q_lens, ctx.state_slots):
+                s = cache.state[slot]
+                for t in range(off, off + n):
+                    s = self.decay * s + u[t]
+                    out[t] = s
+                cache.state[slot] = s
+                off += n
+            return matmul_tn(out.to(h.dtype), self.w_out)
+
+    def parse(d):
+        return dict(d)
+
+    def spec(c):
+        H = c["hidden_size"]
+        norm = lambda name: PartSpec("rmsnorm", dict(hidden_size=H, eps=c["eps"]), {"weight": name})
+        rope = PartSpec("rotary", dict(rot_dim=c["head_dim"] // 2, theta=100.0, is_neox=False))   # partial, interleaved
+        def attn(i, window=None):
+            p = f"l{i}."
+            return PartSpec("paged_attention", dict(hidden_size=H, num_heads=c["heads"], num_kv_heads=c["kv_heads"],
+                                                    head_dim=c["head_dim"], position_encoding=rope, window=window),
+                            {"qkv": [p + "q", p + "k", p + "v"], "o": p + "o"})
+        def mlp(i):
+            return PartSpec("gated_mlp", dict(hidden_size=H, intermediate_size=c["inter"], activation="gelu_tanh"),
+                            {"gate_up": [f"l{i}.g", f"l{i}.u"], "down": f"l{i}.d"})
+        def layer(i, mixer):
+            return LayerSpec("pre_norm", {"mixer_norm": norm(f"l{i}.n1"), "mixer": mixer, "ffn_norm": norm(f"l{i}.n2"),
+                                          "feed_forward": mlp(i)})
+        layers = [layer(0, attn(0)),
+                  layer(1, PartSpec("toy_decay", dict(hidden_size=H, state_size=c["state"], decay=c["decay"]),
+                                    {"w_in": "l1.in", "w_out": "l1.out"})),
+                  layer(2, attn(2, window=c["window"])),
+                  layer(3, attn(3))]
+        # layer 0 runs twice (each run has a cache of its own); the last call reads the first call's cache
+        order = [LayerCall(0), LayerCall(1), LayerCall(2), LayerCall(0), LayerCall(3, cache_of=0)]
+        return ModelSpec(hidden_size=H, vocab_size=c["vocab"], max_model_len=c["max_len"],
+                         embedding=PartSpec("token_embedding", dict(vocab_size=c["vocab"], hidden_size=H), {"weight": "emb"}),
+                         layers=layers, order=order, final_norm=norm("nf"),
+                         lm_head=PartSpec("dense", dict(in_features=H, out_features=c["vocab"], out_dtype="float32"),
+                                          {"weight": "emb"}))
+
+    register_architecture("ToyMixedForTests", parse, spec)
+
+
+TOY = dict(architectures=["ToyMixedForTests"], hidden_size=48, heads=3, kv_heads=1, head_dim=32, inter=56, vocab=97,
+           state=20, decay=0.8, eps=1e-5, window=9, max_len=256)
+
+
+def _toy_reference(model, ids):
+    """The toy model on whole sequences with the plain functions."""
+    c = TOY
+    W = lambda t: t.float().cpu()
+    x = P.embedding(W(model.embedding.weight), torch.tensor(ids))
+    T = len(ids)
+    pos = torch.arange(T)
+    kv_of_call = {}
+
+    def attn(m, h, j, read_from=None):
+        nh, nkv, hd = m.num_heads, m.num_kv_heads, m.head_dim
+        qkv = h @ W(m.qkv).T
+        q = qkv[:, :nh * hd].reshape(T, nh, hd)
+        k = qkv[:, nh * hd:(nh + nkv) * hd].reshape(T, nkv, hd)
+        v = qkv[:, (nh + nkv) * hd:].reshape(T, nkv, hd)
+        rot = hd // 2
+        inv = torch.tensor([100.0 ** (-(2.0 * i) / rot) for i in range(rot // 2)], dtype=torch.float64)
+        ang = pos.float()[:, None] * inv.float()[None, :]
+        cs, sn = ang.cos()[:, None, :], ang.sin()[:, None, :]
+
+        def rotate(z):
+            a, b = z[..., 0:rot:2], z[..., 1:rot:2]
+            y = torch.stack([a * cs - b * sn, b * cs + a * sn], dim=-1).reshape(*z.shape[:-1], rot)
+            return torch.cat([y, z[..., rot:]], dim=-1)
+        q = rotate(q)
+        if read_from is None:
+            kv_of_call[j] = (rotate(k), v)
+            k, v = kv_of_call[j]
+        else:
+            k, v = kv_of_call[read_from]
+        o = P.causal_attention(q, k, v, 1.0 / math.sqrt(hd), m.window)
+        return o.reshape(T, nh * hd) @ W(m.o).T
+
+    def decay(m, h):
+        u = h @ W(m.w_in).T
+        s, out = torch.zeros(m.state_size), []
+        for t in range(T):
+            s = m.decay * s + u[t]
+            out.append(s)
+        return torch.stack(out) @ W(m.w_out).T
+
+    for j, call in enumerate(model.calls):
+        blk = model.blocks[call.layer]
+        h = P.rms_norm(x, W(blk.mixer_norm.weight), c["eps"])
+        m = blk.mixer
+        a = decay(m, h) if hasattr(m, "decay") else attn(m, h, j, call.cache_of)
+        x = x + a
+        h = P.rms_norm(x, W(blk.ffn_norm.weight), c["eps"])
+        ff = blk.feed_forward
+        gu = h @ W(ff.gate_up).T
+        I = ff.intermediate_size
+        x = x + (torch.nn.functional.gelu(gu[:, :I], approximate="tanh") * gu[:, I:]) @ W(ff.down).T
+    return P.rms_norm(x, W(model.final_norm.weight), c["eps"]) @ W(model.lm_head.weight).T
+
+
+@pytest.mark.parametrize("dtype,rel", [("float32", 2e-5), ("bfloat16", 6e-2)])
+def test_toy_architecture_is_registered_built_and_stepped(tmp_path, dtype, rel):
+    import traces
+    from lmsf_b200.cache.storage import plan_groups
+    from lmsf_b200.engine.factory import build_model
+    _register_toy()
+    (tmp_path / "config.json").write_text(json.dumps(TOY))
+    model, _, tdt = build_model(str(tmp_path), dtype, DEV, load_format="dummy", seed=3)
+    for part, _ in model.parts_with_specs():                      # larger weights: attention must matter
+        for name in part.weight_specs():
+            if not part.weight_specs()[name].keep_fp32:
+                getattr(part, name).mul_(6.0)
+    groups, where = plan_groups(model)
+    assert [(g.spec.window, g.calls) for g in groups] == [(None, [0, 3]), (9, [2])]    # two page pools
+    assert where[4] == where[0]                                                        # the shared cache
+    reqs = {f"t{i}": util.random_ids(n, TOY["vocab"], 40 + i) for i, n in enumerate([37, 5, 61, 18, 44])}
+    ref = {rid: _toy_reference(model, toks).numpy() for rid, toks in reqs.items()}
+    traces._runners[(str(tmp_path), dtype)] = (model, None, tdt)
+    results = {}
+    for mode, steps in {"whole": traces.whole(reqs), "portions": traces.portions(reqs, [5, 2, 11, 3]),
+                        "mixed": traces.mixed(reqs, seed=2, max_live=3, tail=8)}.items():
+        out = traces.run_inprocess(str(tmp_path), dtype, steps, 8, traces.max_live_tokens(steps, 8), max_live=3)
+        results[mode] = traces.collect(steps, out)
+        scale = max(1.0, max(float(abs(r).max()) for r in ref.values()))
+        worst = max(float(abs(row - ref[rid][pos]).max()) for (rid, pos), row in results[mode].items())
+        assert worst <= rel * scale, (mode, worst, scale)
