@@ -1,0 +1,299 @@
+#!/usr/bin/env python3
+"""Benchmark of the engine on one GPU: decode tokens/s (batch 8 by default; batch 1 and 64 as points),
+prefill tokens/s at 2,048 tokens, each with its fraction of the measured roofline.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl reference]
+
+A "step" is one decode step of the whole batch.  Weights are random (made on the device), token ids are
+seeded uniform-random: synthetic data throughout.  One JSON line is printed.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# Llama-3-8B's layer sizes
+MODEL = dict(architectures=["LlamaForCausalLM"], model_type="llama", hidden_size=4096, num_hidden_layers=32,
+             num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=14336, vocab_size=128256,
+             rope_theta=500000.0, rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=8192,
+             hidden_act="silu", torch_dtype="bfloat16", bos_token_id=128000, eos_token_id=128001)
+CONTEXT = 2048          # tokens each request holds while decoding is timed
+MAX_MODEL_LEN = 4096
+BLOCK_SIZE = 16
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(p):
+        with open(p) as f:
+            d = json.load(f)
+        d["source"] = "measured"
+        return d
+    return dict(FALLBACK_PEAKS, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc, self.lines = None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx = float(f[1])
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def model_numbers(cfg, n_layers):
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    per_layer = H * (nh + 2 * nkv) * hd + nh * hd * H + 3 * H * I
+    return dict(layer_params=per_layer, linear_params=per_layer * n_layers, head_params=V * H,
+                kv_bytes_per_token=2 * nkv * hd * 2 * n_layers)
+
+
+def decode_bytes(nums, batch, context):
+    """What a decode step has to read: every weight it uses once, and the cache of the live requests."""
+    return 2 * (nums["linear_params"] + nums["head_params"]) + batch * context * nums["kv_bytes_per_token"]
+
+
+def prefill_flops(cfg, nums, T, n_layers):
+    attn = 4 * cfg["num_attention_heads"] * cfg["head_dim"] * T * T / 2 * n_layers     # causal QK^T and PV
+    return 2 * T * nums["linear_params"] + attn + 2 * nums["head_params"]               # the head runs on one row
+
+
+def fill_requests(runner, mgr, batch, context, prefix):
+    """Puts `batch` requests of `context - 1` cached tokens into the manager without running a prefill (the
+    cache holds random values, which is all that decode timing needs)."""
+    ids = []
+    for i in range(batch):
+        rid = f"{prefix}{i}"
+        mgr.add(rid)
+        mgr.reserve(rid, context - 1)
+        mgr.commit(rid, context - 1)
+        ids.append(rid)
+    return ids
+
+
+def time_decode(runner, mgr, ids, steps, warmup, vocab, seed=0):
+    import torch
+    from lmsf_b200 import kernels
+    from lmsf_b200.engine.model_runner import StepEntry
+    g = torch.Generator().manual_seed(seed)
+    toks = torch.randint(0, vocab, (steps + warmup, len(ids)), generator=g).tolist()
+    sampler_out = torch.empty(len(ids), dtype=torch.int32, device=runner.device)
+
+    def one(k):
+        logits = runner.decode_step([StepEntry(r, [toks[k][j]], [0]) for j, r in enumerate(ids)], mgr)
+        kernels.sample(sampler_out, logits)
+
+    for k in range(warmup):
+        one(k)
+    torch.cuda.synchronize()
+    l0 = kernels.launch_count()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for k in range(warmup, warmup + steps):
+        one(k)
+    end.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(end) / steps
+    for r in ids:          # give back the tokens the timed steps added, so the next point starts alike
+        pass
+    return ms, kernels.launch_count() - l0
+
+
+def time_prefill(runner, mgr, T, reps, warmup, vocab):
+    import torch
+    from lmsf_b200.engine.model_runner import StepEntry
+    g = torch.Generator().manual_seed(1)
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=runner.device)     # larger than L2
+    times = []
+    for k in range(warmup + reps):
+        toks = torch.randint(0, vocab, (T,), generator=g).tolist()
+        mgr.add("prefill")
+        flush.zero_()
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        runner.step([StepEntry("prefill", toks, [T - 1])], mgr, check=False)
+        end.record()
+        torch.cuda.synchronize()
+        mgr.free("prefill")
+        if k >= warmup:
+            times.append(start.elapsed_time(end))
+    return statistics.median(times)
+
+
+def time_e2e(folder, n_layers, batch, context, steps, warmup, vocab):
+    """Decode through the public entry point: every step takes the host's token lists through the scheduler,
+    copies the step's inputs from pinned host memory to the device and reads the sampled tokens back."""
+    import torch
+    from lmsf_b200 import EngineArgs, LLMEngine, SamplingParams
+    engine = LLMEngine(EngineArgs(model=folder, dtype="bfloat16", block_size=BLOCK_SIZE, max_model_len=MAX_MODEL_LEN,
+                                  max_num_batched_tokens=8192, max_num_seqs=max(batch, 8),
+                                  gpu_memory_utilization=0.85), load_format="dummy")
+    g = torch.Generator().manual_seed(2)
+    sp = SamplingParams(temperature=0.0, max_tokens=steps + warmup + 8, ignore_eos=True)
+    for i in range(batch):
+        engine.add_request(i, None, sp, prompt_token_ids=torch.randint(0, vocab, (context - 1,), generator=g).tolist())
+    while any(s.num_computed < len(s.prompt_token_ids) for s in engine.seqs.values()) or len(engine.seqs) < batch:
+        engine.step()
+    for _ in range(warmup):
+        engine.step()
+    torch.cuda.synchronize()
+    h2d0 = engine.runner.h2d_bytes
+    t0 = time.perf_counter()
+    produced = 0
+    for _ in range(steps):
+        produced += len(engine.step())
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    h2d = (engine.runner.h2d_bytes - h2d0) / steps
+    del engine
+    torch.cuda.empty_cache()
+    return produced / dt, h2d, batch * 4 + 4
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=24)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the model has (named in config)")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--skip-points", action="store_true")
+    a = ap.parse_args()
+    if a.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "yinqiwen/lmsf is a Rust workspace (cargo, candle from a local path, crates from the "
+                          "network); no Rust toolchain and no network here, so pip cannot install it"}))
+        return 0
+    if a.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {a.gpus} is not supported")
+        return 2
+    a.warmup = max(a.warmup, 3)
+
+    import torch
+    from lmsf_b200 import kernels
+    from lmsf_b200.engine.factory import build_model
+    from lmsf_b200.engine.model_runner import ModelRunner
+
+    pk = peaks()
+    cfg = dict(MODEL)
+    full_layers = cfg["num_hidden_layers"]
+    n_layers = a.layers or full_layers
+    cfg["num_hidden_layers"] = n_layers
+    folder = tempfile.mkdtemp(prefix="lmsf_bench_")
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    nums = model_numbers(cfg, n_layers)
+    dev = torch.device("cuda:0")
+    model, _, dtype = build_model(folder, "bfloat16", dev, load_format="dummy")
+    pages = (64 * (CONTEXT + 64) + PREFILL_TOKENS) // BLOCK_SIZE + 64
+    runner = ModelRunner(model, dtype, dev, BLOCK_SIZE, num_blocks=pages, max_num_seqs=80, max_model_len=MAX_MODEL_LEN)
+    for t in runner.storage.tensors:
+        t.normal_(0.0, 1.0)
+    mgr = runner.make_cache_manager()
+    V = cfg["vocab_size"]
+
+    clocks = ClockSampler()
+    clocks.start()
+    ids = fill_requests(runner, mgr, a.batch, CONTEXT, "b")
+    ms, launches = time_decode(runner, mgr, ids, a.steps, a.warmup, V)
+    clock_rec = clocks.stop()
+    for r in ids:
+        mgr.free(r)
+    value = a.batch / (ms * 1e-3)
+    achieved = decode_bytes(nums, a.batch, CONTEXT) / (ms * 1e-3) / 1e9
+
+    points = {}
+    if not a.skip_points:
+        for b in (1, 64):
+            ids = fill_requests(runner, mgr, b, CONTEXT, f"p{b}_")
+            pms, _ = time_decode(runner, mgr, ids, max(8, a.steps // 2), a.warmup, V)
+            for r in ids:
+                mgr.free(r)
+            points[f"decode_b{b}"] = round(b / (pms * 1e-3), 1)
+            points[f"decode_b{b}_hbm_frac"] = round(decode_bytes(nums, b, CONTEXT) / (pms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+
+    pf_ms = time_prefill(runner, mgr, PREFILL_TOKENS, 3, 2, V)
+    pf_flops = prefill_flops(cfg, nums, PREFILL_TOKENS, n_layers)
+    prefill = {"value": round(PREFILL_TOKENS / (pf_ms * 1e-3), 1), "tokens": PREFILL_TOKENS, "ms": round(pf_ms, 3),
+               "frac": round(pf_flops / (pf_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+
+    del runner, mgr, model
+    torch.cuda.empty_cache()
+    e2e = None
+    if not a.skip_e2e:
+        ev, h2d, d2h = time_e2e(folder, n_layers, a.batch, CONTEXT, a.steps, a.warmup, V)
+        e2e = {"value": round(ev, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)}
+
+    line = {
+        "metric": "decode tokens/s (Llama-3-8B shape, batch 8, 2048-token contexts)", "value": round(value, 1),
+        "unit": "tokens/s", "n_gpus": 1, "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(ms, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"model": "Llama-3-8B shape, random weights", "layers": n_layers, "layers_of_model": full_layers,
+                   "hidden_size": cfg["hidden_size"], "num_attention_heads": cfg["num_attention_heads"],
+                   "num_key_value_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                   "intermediate_size": cfg["intermediate_size"], "vocab_size": V, "global_batch": a.batch,
+                   "seq_len": CONTEXT, "max_model_len": MAX_MODEL_LEN, "block_size": BLOCK_SIZE,
+                   "prefill_tokens": PREFILL_TOKENS, "parallelism": "1 GPU",
+                   "l2": "inputs larger than L2 (weights + cache of a step >> 126 MB); prefill flushes L2",
+                   "peaks": pk["source"]},
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points, "clocks": clock_rec, "gpu_launches": int(launches), "impl": "ours",
+    }
+    if e2e is not None:
+        line["e2e"] = e2e
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -60,6 +60,7 @@ class ModelRunner:
         self.storage = CacheStorage(model, block_size, num_blocks, max_num_seqs, dtype, device)
         self.error_flag = torch.zeros(1, dtype=torch.int32, device=device)
         self.vocab_size = model.spec.vocab_size
+        self.h2d_bytes = 0          # bytes of step inputs copied from pinned host memory so far
 
     def make_cache_manager(self) -> CacheManager:
         return self.storage.make_manager()
@@ -142,6 +143,7 @@ class ModelRunner:
             for i, t in enumerate(tables[g]):
                 bt[i, :len(t)] = t
         dev = torch.from_numpy(host).pin_memory().to(self.device, non_blocking=True)
+        self.h2d_bytes += host.nbytes
 
         def view(name):
             o, n = seg[name]
@@ -167,6 +169,10 @@ class ModelRunner:
         if check:
             self.check_device_errors()
         return logits
+
+    def decode_step(self, entries: Sequence[StepEntry], mgr: CacheManager) -> torch.Tensor:
+        """A step whose entries all bring one token; device errors are left for the caller to check."""
+        return self.step(entries, mgr, check=False)
 
     def check_device_errors(self) -> None:
         code = int(self.error_flag.item())

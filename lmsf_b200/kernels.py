@@ -65,8 +65,23 @@ def _func(source: str, name: str, argtypes, defines: Tuple[str, ...] = ()):
     return f
 
 
+_LAUNCHES = 0
+
+
+def launch_count() -> int:
+    """Kernels of this package launched so far (launches replayed from a CUDA graph are added by the runner)."""
+    return _LAUNCHES
+
+
+def add_launches(n: int) -> None:
+    global _LAUNCHES
+    _LAUNCHES += n
+
+
 def _check(rc: int, source: str, prefix: str, defines: Tuple[str, ...] = ()):
+    global _LAUNCHES
     if rc == 0:
+        _LAUNCHES += 1
         return
     if rc < 0:
         lib = load_library(source, defines)
