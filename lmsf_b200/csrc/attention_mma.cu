@@ -1,0 +1,299 @@
+// bfloat16 attention over the paged cache on the tensor cores (mma.sync m16n8k16, float32 scores,
+// softmax and accumulators), compiled for one head size: -DLMSF_HEAD_DIM=<multiple of 16, 16..128>.
+//
+//   decode  : one query token per request; a block serves the query heads that share one kv head
+//             (rows of the product = heads), the keys are split over blocks (grid.x) and the partial
+//             results are merged by a second kernel.  Counterpart in the reference:
+//             paged_attention_v2_kernel + reduce, vllm/kernels/attention/attention_kernels.cu:441-572.
+//   prefill : portions of prompts (any number of query tokens per request, at any position); a block
+//             serves 64 query tokens of one head and walks the keys 0..position from pages.
+//             Counterpart in the reference: the dense prompt attention of
+//             core/src/model_executor/layers/attention.rs:106-159, which materialises all scores.
+//
+// Keys and values are brought into shared memory in stages of 64 keys with cp.async (three stages in
+// flight); both kernels read them with ldmatrix.  The softmax is exact (no constant in the denominator).
+#include "attention_mma.cuh"
+
+#ifndef LMSF_HEAD_DIM
+#error "compile with -DLMSF_HEAD_DIM=<head size>"
+#endif
+
+LMSF_DEFINE_LAST_ERROR(lmsf_attention_mma)
+
+namespace lmsf {
+namespace fa {
+
+constexpr int HD = LMSF_HEAD_DIM;
+static_assert(HD % 16 == 0 && HD >= 16 && HD <= 128, "head size must be a multiple of 16 between 16 and 128");
+constexpr int kStages = 3;
+constexpr int kKSteps = HD / 16;   // k-steps of q k^T; also pairs of 8-wide output tiles of p v
+constexpr float kLog2e = 1.4426950408889634f;
+using St = Stage<HD>;
+
+struct DecodeArgs {
+  const bf16* q; long long q_stride;         // [n_tokens][n_q_heads * HD]
+  bf16* out; long long out_stride;           // [n_tokens][n_q_heads * HD]
+  float* part_o;                             // [n_seqs][n_q_heads][n_splits][HD] (n_splits > 1)
+  float* part_lse;                           // [n_seqs][n_q_heads][n_splits]
+  PagedKV kv;
+  const int* block_table; int max_blocks;
+  const int* seq_ids;                        // [grid.z] requests served (null: 0, 1, 2, ...)
+  const int* cu_q;                           // [n_seqs + 1] token offset of each request
+  const int* ctx_len;                        // [n_seqs] keys of each request, the new token's included
+  float scale; int window;
+  int n_q_heads, group;                      // group = n_q_heads / n_kv_heads
+  int n_splits;
+};
+
+// Online-softmax state of the two rows (lane / 4 and lane / 4 + 8) that a thread holds.
+struct RowState {
+  float m[2], l[2];
+};
+
+// ------------------------------------------------------------------------------------------------ decode
+__global__ void __launch_bounds__(kThreads) decode_kernel(DecodeArgs a) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  const int split = blockIdx.x;
+  const int chunks_per_kvh = (a.group + 15) / 16;
+  const int kvh = blockIdx.y / chunks_per_kvh, hchunk = blockIdx.y % chunks_per_kvh;
+  const int seq = a.seq_ids ? a.seq_ids[blockIdx.z] : blockIdx.z;
+  const int token = a.cu_q[seq];
+  const int ctx = a.ctx_len[seq];
+  const int lo = a.window > 0 ? max(0, ctx - a.window) : 0;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g4 = lane >> 2, t4 = lane & 3;
+  const int head0 = kvh * a.group + hchunk * 16;               // first query head of this block
+  const int n_heads = min(16, a.group - hchunk * 16);          // valid rows
+  const int* table = a.block_table + (size_t)seq * a.max_blocks;
+
+  // tiles of 64 keys aligned to absolute positions; this split's share of them
+  const int tile_lo = lo / kTileKeys, tile_hi = (ctx + kTileKeys - 1) / kTileKeys;
+  const int per_split = (tile_hi - tile_lo + a.n_splits - 1) / a.n_splits;
+  const int tile_begin = tile_lo + split * per_split;
+  const int tile_end = min(tile_hi, tile_begin + per_split);
+  const int n_tiles = max(0, tile_end - tile_begin);
+
+  // q fragments: rows = heads (zero beyond n_heads), all k-steps
+  uint32_t qf[kKSteps][4];
+  {
+    const bf16* qb = a.q + (size_t)token * a.q_stride + (size_t)head0 * HD;
+#pragma unroll
+    for (int ks = 0; ks < kKSteps; ++ks) {
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const int row = g4 + (r & 1) * 8, col = ks * 16 + t4 * 2 + (r >> 1) * 8;
+        qf[ks][r] = row < n_heads ? *reinterpret_cast<const uint32_t*>(qb + (size_t)row * HD + col) : 0u;
+      }
+    }
+  }
+
+  const uint32_t smem_base = smem_u32(smem);
+  for (int s = 0; s < kStages - 1; ++s) {
+    if (s < n_tiles) load_stage<HD>(smem_base + s * St::kBytes, a.kv, table, kvh, (tile_begin + s) * kTileKeys, lo, ctx);
+    cp_async_commit();
+  }
+
+  RowState st{{-INFINITY, -INFINITY}, {0.f, 0.f}};
+  float o[HD / 8][4];
+#pragma unroll
+  for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  const float sl2 = a.scale * kLog2e;
+
+  for (int i = 0; i < n_tiles; ++i) {
+    cp_async_wait<kStages - 2>();
+    __syncthreads();
+    {
+      const int nxt = i + kStages - 1;
+      if (nxt < n_tiles)
+        load_stage<HD>(smem_base + (nxt % kStages) * St::kBytes, a.kv, table, kvh, (tile_begin + nxt) * kTileKeys, lo, ctx);
+      cp_async_commit();
+    }
+    const uint32_t kbase = smem_base + (i % kStages) * St::kBytes + warp * 16 * St::kRowBytes;
+    const uint32_t vbase = kbase + kTileKeys * St::kRowBytes;
+    const int key0 = (tile_begin + i) * kTileKeys + warp * 16;   // first key of this warp's 16
+    if (key0 >= ctx || key0 + 16 <= lo) continue;                // nothing valid (uniform over the warp)
+
+    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+    for (int ks = 0; ks < kKSteps; ++ks) {
+      uint32_t b[4];
+      const int mi = lane >> 3, r = lane & 7;
+      ldmatrix_x4(b, kbase + ((mi >> 1) * 8 + r) * St::kRowBytes + (ks * 16 + (mi & 1) * 8) * 2);
+      mma_16816(s[0], qf[ks], b[0], b[1]);
+      mma_16816(s[1], qf[ks], b[2], b[3]);
+    }
+    // mask, running max, exponentials
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = key0 + j * 8 + t4 * 2 + (e & 1);
+        const float v = (key >= lo && key < ctx) ? s[j][e] * sl2 : -INFINITY;
+        s[j][e] = v;
+        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+      }
+    float alpha[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+      const float m_new = fmaxf(st.m[h], mx[h]);      // finite: at least one key of the 16 is valid
+      alpha[h] = exp2f(st.m[h] - m_new);
+      st.m[h] = m_new;
+      st.l[h] *= alpha[h];
+    }
+    uint32_t pf[4];
+    {
+      float p[2][4];
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          p[j][e] = exp2f(s[j][e] - st.m[e >> 1]);
+          st.l[e >> 1] += p[j][e];
+        }
+      pf[0] = pack_bf16(p[0][0], p[0][1]);
+      pf[1] = pack_bf16(p[0][2], p[0][3]);
+      pf[2] = pack_bf16(p[1][0], p[1][1]);
+      pf[3] = pack_bf16(p[1][2], p[1][3]);
+    }
+#pragma unroll
+    for (int n2 = 0; n2 < kKSteps; ++n2) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        o[2 * n2 + h][0] *= alpha[0]; o[2 * n2 + h][1] *= alpha[0];
+        o[2 * n2 + h][2] *= alpha[1]; o[2 * n2 + h][3] *= alpha[1];
+      }
+      uint32_t b[4];
+      const int mi = lane >> 3, r = lane & 7;
+      ldmatrix_x4_trans(b, vbase + ((mi & 1) * 8 + r) * St::kRowBytes + (n2 * 16 + (mi >> 1) * 8) * 2);
+      mma_16816(o[2 * n2], pf, b[0], b[1]);
+      mma_16816(o[2 * n2 + 1], pf, b[2], b[3]);
+    }
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+
+  // merge the four warps through shared memory (the stages are free now)
+  float* sm_o = reinterpret_cast<float*>(smem);                 // [4 warps][16 rows][HD]
+  float* sm_m = sm_o + 4 * 16 * HD;                             // [4][16]
+  float* sm_l = sm_m + 4 * 16;                                  // [4][16]
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    st.l[h] += __shfl_xor_sync(0xffffffffu, st.l[h], 1);
+    st.l[h] += __shfl_xor_sync(0xffffffffu, st.l[h], 2);
+    if (t4 == 0) {
+      sm_m[warp * 16 + g4 + h * 8] = st.m[h];
+      sm_l[warp * 16 + g4 + h * 8] = st.l[h];
+    }
+  }
+#pragma unroll
+  for (int n = 0; n < HD / 8; ++n) {
+    float* row0 = sm_o + (warp * 16 + g4) * HD + n * 8 + t4 * 2;
+    row0[0] = o[n][0]; row0[1] = o[n][1];
+    row0[8 * HD] = o[n][2]; row0[8 * HD + 1] = o[n][3];
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < n_heads * HD; idx += kThreads) {
+    const int row = idx / HD, d = idx % HD;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, sm_m[w * 16 + row]);
+    float L = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = sm_m[w * 16 + row];
+      const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
+      L += sm_l[w * 16 + row] * f;
+      acc += sm_o[(w * 16 + row) * HD + d] * f;
+    }
+    const int head = head0 + row;
+    if (a.n_splits == 1) {
+      a.out[(size_t)token * a.out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(acc / L);
+    } else {
+      const size_t pi = ((size_t)seq * a.n_q_heads + head) * a.n_splits + split;
+      a.part_o[pi * HD + d] = L > 0.f ? acc / L : 0.f;
+      if (d == 0) a.part_lse[pi] = L > 0.f ? M + log2f(L) : -INFINITY;   // base-2 log-sum-exp
+    }
+  }
+}
+
+// out = sum_s part_o[s] 2^(lse_s - max) / sum_s 2^(lse_s - max); one block per (request, head)
+__global__ void decode_merge_kernel(DecodeArgs a) {
+  const int seq = a.seq_ids ? a.seq_ids[blockIdx.y] : blockIdx.y;
+  const int head = blockIdx.x;
+  const size_t base = ((size_t)seq * a.n_q_heads + head) * a.n_splits;
+  float M = -INFINITY;
+  for (int s = 0; s < a.n_splits; ++s) M = fmaxf(M, a.part_lse[base + s]);
+  const int token = a.cu_q[seq];
+  for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+    float acc = 0.f, L = 0.f;
+    for (int s = 0; s < a.n_splits; ++s) {
+      const float lse = a.part_lse[base + s];
+      const float f = lse == -INFINITY ? 0.f : exp2f(lse - M);
+      L += f;
+      acc += a.part_o[(base + s) * HD + d] * f;
+    }
+    a.out[(size_t)token * a.out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(acc / L);
+  }
+}
+
+}  // namespace fa
+}  // namespace lmsf
+
+#include "attention_mma_prefill.cuh"
+
+LMSF_API int lmsf_attention_mma_head_dim() { return LMSF_HEAD_DIM; }
+
+// Bytes of scratch that lmsf_attention_decode needs for the given sizes (0 when n_splits == 1).
+LMSF_API long long lmsf_attention_decode_scratch_bytes(int n_seqs_total, int n_q_heads, int n_splits) {
+  if (n_splits <= 1) return 0;
+  return (long long)n_seqs_total * n_q_heads * n_splits * (lmsf::fa::HD + 1) * (long long)sizeof(float);
+}
+
+// One query token per served request.  seq_ids (may be null) lists the n_served requests among the
+// n_seqs_total rows of block_table / cu_q / ctx_len.  scratch: lmsf_attention_decode_scratch_bytes().
+LMSF_API int lmsf_attention_decode(const void* q, long long q_stride, void* out, long long out_stride,
+                                   const void* cache, long long page_stride, int block_size, int n_kv_heads,
+                                   const int* block_table, int max_blocks, const int* seq_ids, int n_served,
+                                   int n_seqs_total, const int* cu_q, const int* ctx_len, float scale, int window,
+                                   int n_q_heads, int head_dim, int n_splits, void* scratch, void* stream) {
+  using namespace lmsf;
+  using namespace lmsf::fa;
+  if (n_served <= 0) return 0;
+  if (head_dim != HD) LMSF_REFUSE("attention_decode: built for head_dim=%d, called with %d", HD, head_dim);
+  if (n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads)
+    LMSF_REFUSE("attention_decode: %d query heads cannot be grouped over %d kv heads", n_q_heads, n_kv_heads);
+  if (n_splits < 1 || n_splits > 65535) LMSF_REFUSE("attention_decode: n_splits=%d", n_splits);
+  if (n_splits > 1 && !scratch) LMSF_REFUSE("attention_decode: %d splits need scratch memory", n_splits);
+  if (block_size <= 0 || max_blocks <= 0) LMSF_REFUSE("attention_decode: bad block table geometry");
+  const int group = n_q_heads / n_kv_heads;
+  const long long gy = (long long)n_kv_heads * ((group + 15) / 16);
+  if (gy > 65535 || n_served > 65535) LMSF_REFUSE("attention_decode: too many heads or requests for one launch");
+  DecodeArgs a;
+  a.q = (const bf16*)q; a.q_stride = q_stride; a.out = (bf16*)out; a.out_stride = out_stride;
+  a.part_o = (float*)scratch;
+  a.part_lse = a.part_o ? a.part_o + (size_t)n_seqs_total * n_q_heads * n_splits * HD : nullptr;
+  a.kv = PagedKV{(const bf16*)cache, page_stride, block_size, n_kv_heads};
+  a.block_table = block_table; a.max_blocks = max_blocks; a.seq_ids = seq_ids; a.cu_q = cu_q; a.ctx_len = ctx_len;
+  a.scale = scale; a.window = window; a.n_q_heads = n_q_heads; a.group = group; a.n_splits = n_splits;
+  const int smem_stages = kStages * St::kBytes;
+  const int smem_merge = (4 * 16 * HD + 2 * 4 * 16) * (int)sizeof(float);
+  const int smem = smem_stages > smem_merge ? smem_stages : smem_merge;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  decode_kernel<<<dim3(n_splits, (unsigned)gy, n_served), kThreads, smem, s>>>(a);
+  int rc = LMSF_LAUNCH_STATUS();
+  if (rc) return rc;
+  if (n_splits > 1) {
+    decode_merge_kernel<<<dim3(n_q_heads, n_served), HD >= 64 ? 64 : 32, 0, s>>>(a);
+    rc = LMSF_LAUNCH_STATUS();
+  }
+  return rc;
+}

@@ -1,0 +1,89 @@
+// Building blocks of the bfloat16 tensor-core attention kernels: asynchronous copies of key/value
+// rows from cache pages into shared memory, ldmatrix fragment loads and the m16n8k16 product.
+#pragma once
+#include "common.cuh"
+
+namespace lmsf {
+namespace fa {
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// 16-byte asynchronous copy; src_bytes = 0 writes zeros and reads nothing.
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
+// c (16x8, float32) += a (16x16 bf16, row) * b (16x8 bf16, col)
+__device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+constexpr int kTileKeys = 64;   // keys per pipeline stage
+constexpr int kThreads = 128;   // 4 warps
+
+// Geometry of one layer's cache and of one request's block table.
+struct PagedKV {
+  const bf16* cache;        // [page][2][kv_head][slot][HD]
+  long long page_stride;    // elements between pages
+  int block_size;
+  int n_kv_heads;
+};
+
+// Shared-memory stage: kTileKeys rows of K then kTileKeys rows of V, each row HD * 2 + 16 bytes (the
+// 16 bytes of padding make the 8 rows of an ldmatrix fall into different banks for any HD).
+template <int HD> struct Stage {
+  static constexpr int kRowBytes = HD * 2 + 16;
+  static constexpr int kBytes = 2 * kTileKeys * kRowBytes;
+  static constexpr int kChunks = HD / 8;   // 16-byte chunks per row
+};
+
+// Issues the copies of keys [key0, key0 + 64) of kv head `kvh` into the stage at `stage_base`.
+// Keys outside [lo, hi) and keys whose page entry is negative are zero-filled, never read.
+template <int HD>
+__device__ __forceinline__ void load_stage(uint32_t stage_base, const PagedKV& kv, const int* __restrict__ table, int kvh,
+                                           int key0, int lo, int hi) {
+  using S = Stage<HD>;
+  const size_t v_off = (size_t)kv.n_kv_heads * kv.block_size * HD;
+  const size_t head_off = (size_t)kvh * kv.block_size * HD;
+#pragma unroll
+  for (int it = 0; it < (kTileKeys * S::kChunks) / kThreads; ++it) {
+    const int idx = threadIdx.x + it * kThreads;
+    const int row = idx / S::kChunks, c = idx % S::kChunks;
+    const int key = key0 + row;
+    const bf16* src = kv.cache;
+    int bytes = 0;
+    if (key >= lo && key < hi) {
+      const int page = table[key / kv.block_size];
+      if (page >= 0) {
+        src = kv.cache + (size_t)page * kv.page_stride + head_off + (size_t)(key % kv.block_size) * HD + c * 8;
+        bytes = 16;
+      }
+    }
+    const uint32_t dst = stage_base + row * S::kRowBytes + c * 16;
+    cp_async_16(dst, src, bytes);
+    cp_async_16(dst + kTileKeys * S::kRowBytes, bytes ? src + v_off : src, bytes);
+  }
+}
+
+}  // namespace fa
+}  // namespace lmsf

@@ -3,7 +3,10 @@
 build check compiles; at run time only what the loaded model needs is built."""
 from typing import List, Tuple
 
-VARIANTS = {}
+VARIANTS = {
+    # one build per head size that the tensor-core attention kernels take
+    "attention_mma.cu": [(f"LMSF_HEAD_DIM={hd}",) for hd in range(16, 129, 16)],
+}
 
 
 def all_variants(source: str) -> List[Tuple[str, ...]]:

@@ -16,7 +16,7 @@ import torch
 from ..cache.block_allocator import OutOfPages
 from ..cache.manager import CacheManager
 from ..cache.storage import CacheStorage, plan_groups, split_pages
-from ..parts.base import CacheGroupView, StepContext
+from ..parts.base import Q_TILE, CacheGroupView, StepContext
 from ..parts.decoder import DecoderModel
 
 
@@ -110,6 +110,9 @@ class ModelRunner:
         for e, n in zip(entries, q_lens):
             rows.extend(off + int(w) for w in e.want)
             off += n
+        dec_ids = [i for i, n in enumerate(q_lens) if n == 1]
+        tile_seq = [i for i, n in enumerate(q_lens) if n > 1 for _ in range(0, n, Q_TILE)]
+        tile_q0 = [q0 for n in q_lens if n > 1 for q0 in range(0, n, Q_TILE)]
         n_groups = len(self.storage.groups)
         tables = [[mgr.block_table(e.request_id, g) for e in entries] for g in range(n_groups)]
         max_blocks = [max(pad_blocks_to or 1, max(len(t) for t in tables[g])) for g in range(n_groups)]
@@ -118,7 +121,8 @@ class ModelRunner:
         seg = {}
         total = 0
         for name, length in [("token_ids", N), ("positions", N), ("token_seq", N), ("cu_q", S + 1), ("ctx_len", S),
-                             ("state_slot", S), ("rows", len(rows))] + \
+                             ("state_slot", S), ("rows", len(rows)), ("dec_ids", len(dec_ids)),
+                             ("tile_seq", len(tile_seq)), ("tile_q0", len(tile_q0))] + \
                             [(f"bt{g}", S * max_blocks[g]) for g in range(n_groups)]:
             seg[name] = (total, length)
             total += _align(max(length, 1))
@@ -135,8 +139,9 @@ class ModelRunner:
         put("ctx_len", np.asarray(ctx_lens, dtype=np.int32))
         slots = [mgr.state_slot(e.request_id) for e in entries]
         put("state_slot", np.asarray(slots, dtype=np.int32))
-        if rows:
-            put("rows", np.asarray(rows, dtype=np.int32))
+        for name, values in (("rows", rows), ("dec_ids", dec_ids), ("tile_seq", tile_seq), ("tile_q0", tile_q0)):
+            if values:
+                put(name, np.asarray(values, dtype=np.int32))
         for g in range(n_groups):
             o, _ = seg[f"bt{g}"]
             bt = host[o:o + S * max_blocks[g]].reshape(S, max_blocks[g])
@@ -153,7 +158,9 @@ class ModelRunner:
         ctx = StepContext(n_tokens=N, n_seqs=S, dtype=self.dtype, device=self.device, token_ids=view("token_ids"),
                           positions=view("positions"), token_seq=view("token_seq"), cu_q=view("cu_q"),
                           ctx_len=view("ctx_len"), state_slot=view("state_slot"), groups=groups, q_lens=q_lens,
-                          ctx_lens=ctx_lens, state_slots=slots, error_flag=self.error_flag)
+                          ctx_lens=ctx_lens, state_slots=slots, error_flag=self.error_flag,
+                          decode_seq_ids=view("dec_ids"), n_decode_seqs=len(dec_ids), q_tile_seq=view("tile_seq"),
+                          q_tile_q0=view("tile_q0"), n_q_tiles=len(tile_seq))
         return ctx, view("rows")
 
     # ------------------------------------------------------------------ the step

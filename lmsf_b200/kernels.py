@@ -241,3 +241,80 @@ def sample(out: torch.Tensor, logits: torch.Tensor, temperature: Optional[torch.
     rc = f(_ptr(out), _ptr(logits), logits.stride(0), rows, vocab, _ptr(temperature), _ptr(seed), _i32(step, "step"),
            _stream())
     _check(rc, "sampling.cu", "lmsf_sampling")
+
+
+# ----------------------------------------------------------------------------- tensor-core attention (bfloat16)
+
+MMA_MAX_HEAD_DIM = 128
+
+
+def mma_attention_supported(dtype: torch.dtype, head_dim: int) -> bool:
+    return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= MMA_MAX_HEAD_DIM
+
+
+def _mma_defines(head_dim: int) -> Tuple[str, ...]:
+    return (f"LMSF_HEAD_DIM={head_dim}",)
+
+
+def _check_paged(q, out, cache, n_q_heads, n_kv_heads, head_dim, block_size, what):
+    if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
+        raise KernelError(f"{what}: bfloat16 only")
+    if q.stride(1) != 1 or out.stride(1) != 1 or q.shape[1] != n_q_heads * head_dim or out.shape != q.shape:
+        raise KernelError(f"{what}: q and out must be [n, heads * head_dim] with a contiguous last dimension")
+    if not cache.is_contiguous() or tuple(cache.shape[1:]) != (2, n_kv_heads, block_size, head_dim):
+        raise KernelError(f"{what}: cache of shape {tuple(cache.shape)} does not match the heads")
+    if (q.data_ptr() | out.data_ptr()) % 4 or (q.stride(0) | out.stride(0)) % 2 or cache.data_ptr() % 16:
+        raise KernelError(f"{what}: q/out rows must be 4-byte aligned and the cache 16-byte aligned")
+
+
+def decode_num_splits(n_served: int, n_kv_heads: int, group: int, max_ctx: int, sm_count: int) -> int:
+    """Blocks over the keys so that about two waves of blocks fill the GPU, each split at least 256 keys."""
+    per_split = n_served * n_kv_heads * ((group + 15) // 16)
+    want = -(-2 * sm_count // max(1, per_split))
+    return max(1, min(want, -(-max_ctx // 256), 64))
+
+
+def attention_decode_scratch_floats(n_seqs_total: int, n_q_heads: int, n_splits: int, head_dim: int) -> int:
+    return 0 if n_splits <= 1 else n_seqs_total * n_q_heads * n_splits * (head_dim + 1)
+
+
+def attention_decode(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
+                     block_size: int, seq_ids: Optional[torch.Tensor], n_served: int, cu_q: torch.Tensor,
+                     ctx_len: torch.Tensor, scale: float, window: int, n_q_heads: int, n_kv_heads: int,
+                     head_dim: int, n_splits: int, scratch: Optional[torch.Tensor]):
+    """Attention of requests that bring ONE query token each (row cu_q[s] of q), over their ctx_len[s] keys
+    in pages.  seq_ids: int32 [n_served] rows of the block table that are served (None: all, in order).
+    scratch: float32, at least attention_decode_scratch_floats(...) values when n_splits > 1."""
+    _check_paged(q, out, cache, n_q_heads, n_kv_heads, head_dim, block_size, "attention_decode")
+    n_total = block_table.shape[0]
+    need = attention_decode_scratch_floats(n_total, n_q_heads, n_splits, head_dim)
+    if need and (scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need):
+        raise KernelError(f"attention_decode: {n_splits} splits need {need} float32 values of scratch")
+    d = _mma_defines(head_dim)
+    f = _func("attention_mma.cu", "lmsf_attention_decode",
+              [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_void_p, c_int,
+               c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_void_p, c_void_p], d)
+    rc = f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache), cache.stride(0), block_size, n_kv_heads,
+           _i32(block_table, "block_table"), block_table.shape[1], _i32(seq_ids, "seq_ids"), n_served, n_total,
+           _i32(cu_q, "cu_q"), _i32(ctx_len, "ctx_len"), float(scale), int(window or 0), n_q_heads, head_dim,
+           n_splits, _ptr(scratch) if need else None, _stream())
+    _check(rc, "attention_mma.cu", "lmsf_attention_mma", d)
+    if n_splits > 1:
+        add_launches(1)
+
+
+def attention_prefill(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
+                      block_size: int, tile_seq: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int, cu_q: torch.Tensor,
+                      ctx_len: torch.Tensor, scale: float, window: int, n_q_heads: int, n_kv_heads: int, head_dim: int):
+    """Attention of prompt portions.  Tile i covers the query tokens tile_q0[i] .. tile_q0[i] + 63 (counted
+    inside the portion) of request tile_seq[i]."""
+    _check_paged(q, out, cache, n_q_heads, n_kv_heads, head_dim, block_size, "attention_prefill")
+    d = _mma_defines(head_dim)
+    f = _func("attention_mma.cu", "lmsf_attention_prefill",
+              [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_void_p, c_int,
+               c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_void_p], d)
+    rc = f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache), cache.stride(0), block_size, n_kv_heads,
+           _i32(block_table, "block_table"), block_table.shape[1], _i32(tile_seq, "tile_seq"),
+           _i32(tile_q0, "tile_q0"), n_tiles, _i32(cu_q, "cu_q"), _i32(ctx_len, "ctx_len"), float(scale),
+           int(window or 0), n_q_heads, head_dim, _stream())
+    _check(rc, "attention_mma.cu", "lmsf_attention_mma", d)

@@ -73,5 +73,33 @@ class PagedAttention(Mixer):
         return matmul_tn(out, self.o)
 
     def attend(self, ctx: StepContext, out: torch.Tensor, q: torch.Tensor, kv: torch.Tensor, group) -> None:
+        """bfloat16 with a head size up to 128: single tokens go to the split-key decode kernel, longer portions
+        to the tiled prefill kernel (both on the tensor cores).  Everything else, float32 included, runs on the
+        generic kernel, which is also their plain twin."""
+        if kernels.mma_attention_supported(q.dtype, self.head_dim) and not ctx.extras.get("force_generic_attention"):
+            if ctx.n_decode_seqs:
+                sm = ctx.extras.get("sm_count")
+                if sm is None:
+                    sm = ctx.extras["sm_count"] = torch.cuda.get_device_properties(q.device).multi_processor_count
+                max_ctx = ctx.extras.get("decode_max_ctx")
+                if max_ctx is None:
+                    max_ctx = ctx.extras["decode_max_ctx"] = max(c for c, n in zip(ctx.ctx_lens, ctx.q_lens) if n == 1)
+                visible = min(max_ctx, self.window) if self.window else max_ctx
+                splits = kernels.decode_num_splits(ctx.n_decode_seqs, self.num_kv_heads,
+                                                   self.num_heads // self.num_kv_heads, visible, sm)
+                need = kernels.attention_decode_scratch_floats(ctx.n_seqs, self.num_heads, splits, self.head_dim)
+                scratch = ctx.extras.get("decode_scratch")
+                if need and (scratch is None or scratch.numel() < need):
+                    scratch = ctx.extras["decode_scratch"] = torch.empty(need, dtype=torch.float32, device=q.device)
+                all_decode = ctx.n_decode_seqs == ctx.n_seqs
+                kernels.attention_decode(out, q, kv, group.block_table, group.block_size,
+                                         None if all_decode else ctx.decode_seq_ids, ctx.n_decode_seqs, ctx.cu_q,
+                                         ctx.ctx_len, self.scale, self.window or 0, self.num_heads,
+                                         self.num_kv_heads, self.head_dim, splits, scratch if need else None)
+            if ctx.n_q_tiles:
+                kernels.attention_prefill(out, q, kv, group.block_table, group.block_size, ctx.q_tile_seq,
+                                          ctx.q_tile_q0, ctx.n_q_tiles, ctx.cu_q, ctx.ctx_len, self.scale,
+                                          self.window or 0, self.num_heads, self.num_kv_heads, self.head_dim)
+            return
         kernels.attention_generic(out, q, kv, group.block_table, group.block_size, ctx.token_seq, ctx.positions,
                                   self.scale, self.window or 0, self.num_heads, self.num_kv_heads, self.head_dim)

@@ -122,6 +122,12 @@ class StepContext:
     ctx_lens: List[int] = field(default_factory=list)
     state_slots: List[int] = field(default_factory=list)
     error_flag: Optional[torch.Tensor] = None
+    # geometry of the batch for kernels that treat single tokens and portions apart
+    decode_seq_ids: Optional[torch.Tensor] = None      # int32: requests that bring one token
+    n_decode_seqs: int = 0
+    q_tile_seq: Optional[torch.Tensor] = None          # int32: request of each 64-token tile of a longer portion
+    q_tile_q0: Optional[torch.Tensor] = None           # int32: first token of the tile inside its portion
+    n_q_tiles: int = 0
     extras: Dict[str, Any] = field(default_factory=dict)   # per-step scratch that kernels share across layers
 
     @property
@@ -136,6 +142,8 @@ class StepContext:
     def decode_only(self) -> bool:
         return self.max_q_len <= 1
 
+
+Q_TILE = 64      # query tokens per tile in StepContext.q_tile_*
 
 # ----------------------------------------------------------------------------- interfaces
 

@@ -262,3 +262,38 @@ def test_sampling_greedy_and_temperature():
         assert got[0] == 3
         for r in range(1, rows):
             assert got[r] == P.sample_temperature(logits[r], float(temp[r]), seeds[r], steps[r]), (vocab, r)
+
+
+@pytest.mark.parametrize("nh,nkv,hd,bs,window", [(8, 2, 128, 16, 0), (6, 2, 16, 8, 0), (5, 5, 48, 16, 0), (3, 1, 80, 32, 0),
+                                               (20, 1, 64, 16, 0), (4, 2, 112, 16, 70), (4, 4, 96, 4, 200)])
+def test_attention_tensor_core_kernels(nh, nkv, hd, bs, window):
+    """Decode (split over the keys, every split count) and prefill (tiles of 64 queries) against float64."""
+    from lmsf_b200 import kernels
+    assert kernels.mma_attention_supported(torch.bfloat16, hd)
+    # a long decode, a first token, a portion in the middle of a prompt, a whole prompt, a 2-token portion, a decode
+    ctx_lens, q_lens = [1500, 1, 700, 130, 65, 64], [1, 1, 201, 130, 2, 1]
+    q, cache, bt, token_seq, positions, ks, vs = _paged_setup("bfloat16", nh, nkv, hd, bs, ctx_lens, q_lens, 9, sharp=True)
+    scale = 1.0 / math.sqrt(hd)
+    ref = _attention_reference(q.float(), ks, vs, token_seq, positions, nh, nkv, hd, scale, window)
+    d = dev()
+    qd, cd, btd = q.to(d), cache.to(d), bt.to(d)
+    cu = torch.tensor([0] + list(np.cumsum(q_lens)), dtype=torch.int32, device=d)
+    cl = torch.tensor(ctx_lens, dtype=torch.int32, device=d)
+    dec = [i for i, n in enumerate(q_lens) if n == 1]
+    tiles = [(i, q0) for i, n in enumerate(q_lens) if n > 1 for q0 in range(0, n, 64)]
+    tol_abs = 2e-2 * ref.abs().max().item()
+    for splits in (1, 2, 5, 24):
+        out = torch.zeros(q.shape, dtype=torch.bfloat16, device=d)
+        scratch = torch.empty(max(1, kernels.attention_decode_scratch_floats(len(q_lens), nh, splits, hd)),
+                              dtype=torch.float32, device=d)
+        kernels.attention_decode(out, qd, cd, btd, bs, torch.tensor(dec, dtype=torch.int32, device=d), len(dec), cu, cl,
+                                 scale, window, nh, nkv, hd, splits, scratch)
+        kernels.attention_prefill(out, qd, cd, btd, bs, torch.tensor([t[0] for t in tiles], dtype=torch.int32, device=d),
+                                  torch.tensor([t[1] for t in tiles], dtype=torch.int32, device=d), len(tiles), cu, cl,
+                                  scale, window, nh, nkv, hd)
+        err = (out.float().cpu().double() - ref).abs()
+        assert err.max().item() <= tol_abs, (splits, err.max().item(), int(err.argmax()) // (nh * hd))
+    # the generic kernel is their plain twin: same inputs, same answer within bfloat16 rounding
+    out2 = torch.empty_like(out)
+    kernels.attention_generic(out2, qd, cd, btd, bs, token_seq.to(d), positions.to(d), scale, window, nh, nkv, hd)
+    assert (out2.float() - out.float()).abs().max().item() <= tol_abs
