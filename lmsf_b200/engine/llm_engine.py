@@ -48,7 +48,8 @@ class LLMEngine:
         self.runner = ModelRunner(self.model, self.dtype, self.device, args.block_size,
                                   num_blocks=args.num_gpu_blocks, max_num_seqs=args.max_num_seqs,
                                   gpu_memory_utilization=args.gpu_memory_utilization,
-                                  max_model_len=self.max_model_len, activation_reserve_bytes=act_bytes)
+                                  max_model_len=self.max_model_len, activation_reserve_bytes=act_bytes,
+                                  enforce_eager=args.enforce_eager)
         self.cache = self.runner.make_cache_manager()
         if self.cache.groups and all(g.window is None for g in self.cache.groups) and \
                 args.block_size * self.cache.num_total_pages(0) < self.max_model_len and args.num_gpu_blocks is None:

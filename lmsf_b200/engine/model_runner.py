@@ -18,6 +18,7 @@ from ..cache.manager import CacheManager
 from ..cache.storage import CacheStorage, plan_groups, split_pages
 from ..parts.base import Q_TILE, CacheGroupView, StepContext
 from ..parts.decoder import DecoderModel
+from .. import kernels
 
 
 @dataclass
@@ -32,6 +33,22 @@ class StepError(RuntimeError):
     pass
 
 
+@dataclass
+class _HostBatch:
+    pinned: torch.Tensor
+    event: "torch.cuda.Event"
+    total: int
+    seg: dict
+    N: int
+    S: int
+    q_lens: List[int]
+    ctx_lens: List[int]
+    slots: List[int]
+    max_blocks: List[int]
+    n_dec: int
+    n_tiles: int
+
+
 def _align(n: int, a: int = 4) -> int:
     return (n + a - 1) // a * a
 
@@ -40,7 +57,7 @@ class ModelRunner:
     def __init__(self, model: DecoderModel, dtype: torch.dtype, device: torch.device, block_size: int,
                  num_blocks: Optional[List[int]] = None, max_num_seqs: int = 256,
                  gpu_memory_utilization: float = 0.9, max_model_len: Optional[int] = None,
-                 activation_reserve_bytes: int = 0):
+                 activation_reserve_bytes: int = 0, enforce_eager: bool = False):
         if device.type != "cuda":
             raise StepError("lmsf_b200 runs on a CUDA device only; there is no CPU path")
         self.model, self.dtype, self.device, self.block_size = model, dtype, device, block_size
@@ -61,15 +78,25 @@ class ModelRunner:
         self.error_flag = torch.zeros(1, dtype=torch.int32, device=device)
         self.vocab_size = model.spec.vocab_size
         self.h2d_bytes = 0          # bytes of step inputs copied from pinned host memory so far
+        self.sm_count = torch.cuda.get_device_properties(device).multi_processor_count
+        self._ring = [(None, None)] * 4
+        self._ring_pos = 0
+        # CUDA graphs of decode steps
+        self.enforce_eager = enforce_eager
+        self.max_graph_batch = max_num_seqs
+        self.static_blocks = (self.max_model_len + block_size - 1) // block_size
+        self.graph_safe = all(getattr(b.mixer, "graph_safe", False) for b in model.blocks if b.mixer is not None)
+        self._graphs = {}
+        self._seen_sizes = set()
+        self._graph_pool = None
 
     def make_cache_manager(self) -> CacheManager:
         return self.storage.make_manager()
 
     # ------------------------------------------------------------------ building a batch
-    def build_context(self, entries: Sequence[StepEntry], mgr: CacheManager,
-                      pad_blocks_to: Optional[int] = None) -> Tuple[StepContext, torch.Tensor]:
-        """Reserves the pages the entries need (all or nothing) and lays the batch out on the device.
-        Returns the context and the int32 rows of the step's tokens whose logits are wanted."""
+    def _prepare(self, entries: Sequence[StepEntry], mgr: CacheManager, static_blocks: Optional[int] = None) -> "_HostBatch":
+        """Checks the entries, reserves the pages they need (all or nothing) and lays the batch out in one
+        int32 host buffer whose segments are 16-byte aligned."""
         if not entries:
             raise StepError("a step needs at least one entry")
         seen = set()
@@ -115,9 +142,8 @@ class ModelRunner:
         tile_q0 = [q0 for n in q_lens if n > 1 for q0 in range(0, n, Q_TILE)]
         n_groups = len(self.storage.groups)
         tables = [[mgr.block_table(e.request_id, g) for e in entries] for g in range(n_groups)]
-        max_blocks = [max(pad_blocks_to or 1, max(len(t) for t in tables[g])) for g in range(n_groups)]
+        max_blocks = [max(static_blocks or 1, max(len(t) for t in tables[g])) for g in range(n_groups)]
 
-        # one int32 buffer, every segment 16-byte aligned
         seg = {}
         total = 0
         for name, length in [("token_ids", N), ("positions", N), ("token_seq", N), ("cu_q", S + 1), ("ctx_len", S),
@@ -126,7 +152,9 @@ class ModelRunner:
                             [(f"bt{g}", S * max_blocks[g]) for g in range(n_groups)]:
             seg[name] = (total, length)
             total += _align(max(length, 1))
-        host = np.full(total, -1, dtype=np.int32)
+        pinned, event = self._pinned_buffer(total)
+        host = pinned.numpy()
+        host[:total] = -1
 
         def put(name, values):
             o, n = seg[name]
@@ -147,35 +175,102 @@ class ModelRunner:
             bt = host[o:o + S * max_blocks[g]].reshape(S, max_blocks[g])
             for i, t in enumerate(tables[g]):
                 bt[i, :len(t)] = t
-        dev = torch.from_numpy(host).pin_memory().to(self.device, non_blocking=True)
-        self.h2d_bytes += host.nbytes
+        return _HostBatch(pinned, event, total, seg, N, S, q_lens, ctx_lens, slots, max_blocks, len(dec_ids),
+                          len(tile_seq))
 
+    def _pinned_buffer(self, n_ints: int):
+        """A pinned host buffer from a small ring; a buffer is used again only after the copy that last read it."""
+        self._ring_pos = (self._ring_pos + 1) % len(self._ring)
+        buf, event = self._ring[self._ring_pos]
+        if event is not None:
+            event.synchronize()
+        if buf is None or buf.numel() < n_ints:
+            buf = torch.empty(max(n_ints, 4096), dtype=torch.int32).pin_memory()
+        event = torch.cuda.Event()
+        self._ring[self._ring_pos] = (buf, event)
+        return buf, event
+
+    def _upload(self, hb: "_HostBatch", dev: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if dev is None:
+            dev = torch.empty(hb.total, dtype=torch.int32, device=self.device)
+        dev.copy_(hb.pinned[:hb.total], non_blocking=True)
+        hb.event.record()
+        self.h2d_bytes += hb.total * 4
+        return dev
+
+    def _context(self, hb: "_HostBatch", dev: torch.Tensor) -> Tuple[StepContext, torch.Tensor]:
         def view(name):
-            o, n = seg[name]
+            o, n = hb.seg[name]
             return dev[o:o + n]
 
-        groups = [CacheGroupView(view(f"bt{g}").view(S, max_blocks[g]), self.block_size) for g in range(n_groups)]
-        ctx = StepContext(n_tokens=N, n_seqs=S, dtype=self.dtype, device=self.device, token_ids=view("token_ids"),
+        groups = [CacheGroupView(view(f"bt{g}").view(hb.S, hb.max_blocks[g]), self.block_size)
+                  for g in range(len(hb.max_blocks))]
+        ctx = StepContext(n_tokens=hb.N, n_seqs=hb.S, dtype=self.dtype, device=self.device, token_ids=view("token_ids"),
                           positions=view("positions"), token_seq=view("token_seq"), cu_q=view("cu_q"),
-                          ctx_len=view("ctx_len"), state_slot=view("state_slot"), groups=groups, q_lens=q_lens,
-                          ctx_lens=ctx_lens, state_slots=slots, error_flag=self.error_flag,
-                          decode_seq_ids=view("dec_ids"), n_decode_seqs=len(dec_ids), q_tile_seq=view("tile_seq"),
-                          q_tile_q0=view("tile_q0"), n_q_tiles=len(tile_seq))
+                          ctx_len=view("ctx_len"), state_slot=view("state_slot"), groups=groups, q_lens=hb.q_lens,
+                          ctx_lens=hb.ctx_lens, state_slots=hb.slots, error_flag=self.error_flag,
+                          decode_seq_ids=view("dec_ids"), n_decode_seqs=hb.n_dec, q_tile_seq=view("tile_seq"),
+                          q_tile_q0=view("tile_q0"), n_q_tiles=hb.n_tiles)
+        ctx.extras["sm_count"] = self.sm_count
         return ctx, view("rows")
 
+    def build_context(self, entries: Sequence[StepEntry], mgr: CacheManager) -> Tuple[StepContext, torch.Tensor]:
+        """The context of a step and the rows of its tokens whose logits are wanted (pages are reserved)."""
+        hb = self._prepare(entries, mgr)
+        return self._context(hb, self._upload(hb))
+
     # ------------------------------------------------------------------ the step
+    def _graph_eligible(self, entries: Sequence[StepEntry]) -> bool:
+        return (not self.enforce_eager and self.graph_safe and len(entries) <= self.max_graph_batch
+                and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries))
+
     @torch.inference_mode()
     def step(self, entries: Sequence[StepEntry], mgr: CacheManager, check: bool = True) -> torch.Tensor:
         """Runs the entries as one batch; returns float32 logits [wanted, vocab] on the device, in the order
-        of the entries and of their `want`.  Afterwards the tokens count as cached (`mgr.commit`)."""
-        ctx, rows = self.build_context(entries, mgr)
+        of the entries and of their `want`.  Afterwards the tokens count as cached (`mgr.commit`).
+
+        A batch in which every request brings one token and wants its logits is replayed from a CUDA graph
+        (one graph per batch size, captured the second time the size is seen); the returned tensor is then
+        the graph's own output buffer and holds its values until the next step of the same size."""
+        graph_mode = self._graph_eligible(entries)
+        hb = self._prepare(entries, mgr, self.static_blocks if graph_mode else None)
         self.storage.zero_state_slots(mgr.take_fresh_slots())
-        logits = self.model.forward(ctx, self.storage.layer_caches, rows)
+        if graph_mode and (hb.S in self._graphs or hb.S in self._seen_sizes):
+            logits = self._replay(hb)
+        else:
+            if graph_mode:
+                self._seen_sizes.add(hb.S)
+            ctx, rows = self._context(hb, self._upload(hb))
+            logits = self.model.forward(ctx, self.storage.layer_caches, rows)
         for e in entries:
             mgr.commit(e.request_id, len(e.tokens))
         if check:
             self.check_device_errors()
         return logits
+
+    def _replay(self, hb: "_HostBatch") -> torch.Tensor:
+        g = self._graphs.get(hb.S)
+        if g is None:
+            static_in = self._upload(hb)
+            ctx, rows = self._context(hb, static_in)
+            ctx.extras["decode_max_ctx"] = self.max_model_len      # launch geometry must not depend on the step
+            torch.cuda.synchronize(self.device)
+            if self._graph_pool is None:
+                self._graph_pool = torch.cuda.graph_pool_handle()
+            graph = torch.cuda.CUDAGraph()
+            before = kernels.launch_count()
+            with torch.cuda.graph(graph, pool=self._graph_pool):
+                static_out = self.model.forward(ctx, self.storage.layer_caches, rows)
+            n_launches = kernels.launch_count() - before
+            kernels.add_launches(-n_launches)                      # recorded, not run
+            g = self._graphs[hb.S] = (graph, static_in, static_out, n_launches, hb.total)
+        graph, static_in, static_out, n_launches, total = g
+        if total != hb.total:
+            raise StepError("the layout of a replayed batch changed")
+        self._upload(hb, static_in)
+        graph.replay()
+        kernels.add_launches(n_launches)
+        return static_out
 
     def decode_step(self, entries: Sequence[StepEntry], mgr: CacheManager) -> torch.Tensor:
         """A step whose entries all bring one token; device errors are left for the caller to check."""

@@ -21,6 +21,8 @@ from .linear import matmul_tn
 
 @register_part("mixer", "paged_attention")
 class PagedAttention(Mixer):
+    graph_safe = True      # launch geometry depends on the batch's size only: a decode step can be replayed
+
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position_encoding: Optional[PositionEncoding] = None, window: Optional[int] = None,
                  scale: Optional[float] = None):
