@@ -246,6 +246,23 @@ __global__ void decode_merge_kernel(DecodeArgs a) {
 
 LMSF_API int lmsf_attention_mma_head_dim() { return LMSF_HEAD_DIM; }
 
+static int decode_smem_bytes() {
+  using namespace lmsf::fa;
+  const int smem_stages = kStages * St::kBytes;
+  const int smem_merge = (4 * 16 * HD + 2 * 4 * 16) * (int)sizeof(float);
+  return smem_stages > smem_merge ? smem_stages : smem_merge;
+}
+
+// Blocks of the decode kernel that one SM holds at a time (0 on error); used to size the key splits.
+LMSF_API int lmsf_attention_decode_blocks_per_sm() {
+  using namespace lmsf::fa;
+  const int smem = decode_smem_bytes();
+  if (cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return 0;
+  int n = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, decode_kernel, kThreads, smem) != cudaSuccess) return 0;
+  return n;
+}
+
 // Bytes of scratch that lmsf_attention_decode needs for the given sizes (0 when n_splits == 1).
 LMSF_API long long lmsf_attention_decode_scratch_bytes(int n_seqs_total, int n_q_heads, int n_splits) {
   if (n_splits <= 1) return 0;
@@ -278,9 +295,7 @@ LMSF_API int lmsf_attention_decode(const void* q, long long q_stride, void* out,
   a.kv = PagedKV{(const bf16*)cache, page_stride, block_size, n_kv_heads};
   a.block_table = block_table; a.max_blocks = max_blocks; a.seq_ids = seq_ids; a.cu_q = cu_q; a.ctx_len = ctx_len;
   a.scale = scale; a.window = window; a.n_q_heads = n_q_heads; a.group = group; a.n_splits = n_splits;
-  const int smem_stages = kStages * St::kBytes;
-  const int smem_merge = (4 * 16 * HD + 2 * 4 * 16) * (int)sizeof(float);
-  const int smem = smem_stages > smem_merge ? smem_stages : smem_merge;
+  const int smem = decode_smem_bytes();
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);

@@ -267,11 +267,25 @@ def _check_paged(q, out, cache, n_q_heads, n_kv_heads, head_dim, block_size, wha
         raise KernelError(f"{what}: q/out rows must be 4-byte aligned and the cache 16-byte aligned")
 
 
-def decode_num_splits(n_served: int, n_kv_heads: int, group: int, max_ctx: int, sm_count: int) -> int:
-    """Blocks over the keys so that about two waves of blocks fill the GPU, each split at least 256 keys."""
-    per_split = n_served * n_kv_heads * ((group + 15) // 16)
-    want = -(-2 * sm_count // max(1, per_split))
-    return max(1, min(want, -(-max_ctx // 256), 64))
+_DECODE_BLOCKS_PER_SM = {}
+
+
+def decode_blocks_per_sm(head_dim: int) -> int:
+    n = _DECODE_BLOCKS_PER_SM.get(head_dim)
+    if n is None:
+        lib = load_library("attention_mma.cu", _mma_defines(head_dim))
+        lib.lmsf_attention_decode_blocks_per_sm.restype = c_int
+        n = _DECODE_BLOCKS_PER_SM[head_dim] = max(1, lib.lmsf_attention_decode_blocks_per_sm())
+    return n
+
+
+def decode_num_splits(n_served: int, n_kv_heads: int, group: int, max_ctx: int, sm_count: int,
+                      blocks_per_sm: int = 2) -> int:
+    """Into how many blocks the keys of a request are split: as many as fit the GPU in ONE wave of blocks
+    (a second, partly filled wave would cost as much as a full one), each split at least 128 keys."""
+    base = n_served * n_kv_heads * ((group + 15) // 16)
+    resident = sm_count * blocks_per_sm
+    return max(1, min(resident // max(1, base), -(-max_ctx // 128), 64))
 
 
 def attention_decode_scratch_floats(n_seqs_total: int, n_q_heads: int, n_splits: int, head_dim: int) -> int:
