@@ -312,3 +312,53 @@ LMSF_API int lmsf_attention_decode(const void* q, long long q_stride, void* out,
   }
   return rc;
 }
+
+// ------------------------------------------------------------------------------------------------
+// The variant that allocates nothing (see attention_decode_static.h).
+#include "attention_decode_static.h"
+
+#include <mutex>
+
+namespace {
+constexpr long long kStaticScratchBytes = 8ll << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+constexpr int kMaxDevices = 64;
+void* g_static_scratch_ptr[kMaxDevices] = {};   // device address of the array, per device
+std::mutex g_static_scratch_mutex;
+}  // namespace
+
+LMSF_API long long lmsf_attention_decode_static_capacity() { return kStaticScratchBytes; }
+
+LMSF_API int lmsf_attention_decode_static(const void* q, long long q_stride, void* out, long long out_stride,
+                                          const void* cache, long long page_stride, int block_size, int n_kv_heads,
+                                          const int* block_table, int max_blocks, const int* seq_ids, int n_served,
+                                          int n_seqs_total, const int* cu_q, const int* ctx_len, float scale,
+                                          int window, int n_q_heads, int head_dim, int n_splits, void* stream) {
+  if (n_seqs_total <= 0 || n_q_heads <= 0 || n_splits < 1)
+    LMSF_REFUSE("attention_decode_static: n_seqs_total=%d n_q_heads=%d n_splits=%d", n_seqs_total, n_q_heads, n_splits);
+  const long long need = lmsf_attention_decode_scratch_bytes(n_seqs_total, n_q_heads, n_splits);
+  if (need > kStaticScratchBytes)
+    LMSF_REFUSE("attention_decode_static: %d requests x %d heads x %d splits need %lld bytes of scratch, the static "
+                "array holds %lld; use fewer splits or lmsf_attention_decode with scratch of your own",
+                n_seqs_total, n_q_heads, n_splits, need, kStaticScratchBytes);
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) LMSF_REFUSE("attention_decode_static: device ordinal %d is not supported", dev);
+  void* scratch = nullptr;
+  {
+    // In host code the array's name is only a handle: the address a kernel can use has to be asked for,
+    // once per device, with that device current.
+    std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+    if (g_static_scratch_ptr[dev] == nullptr) {
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_static_scratch);
+      if (e != cudaSuccess) return (int)e;
+      g_static_scratch_ptr[dev] = p;
+    }
+    scratch = g_static_scratch_ptr[dev];
+  }
+  return lmsf_attention_decode(q, q_stride, out, out_stride, cache, page_stride, block_size, n_kv_heads, block_table,
+                               max_blocks, seq_ids, n_served, n_seqs_total, cu_q, ctx_len, scale, window, n_q_heads,
+                               head_dim, n_splits, need > 0 ? scratch : nullptr, stream);
+}
