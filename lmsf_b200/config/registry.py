@@ -33,11 +33,17 @@ def register_architecture(name: str, parse_config, build_spec, aliases=()) -> Ar
     return arch
 
 
+def _load_builtin() -> None:
+    from .. import models  # noqa: F401  (importing the package registers the built-in architectures)
+
+
 def registered_architectures() -> List[str]:
+    _load_builtin()
     return sorted({a.name for a in _ARCHITECTURES.values()})
 
 
 def resolve_architecture(config_dict: Dict[str, Any]) -> Architecture:
+    _load_builtin()
     names = list(config_dict.get("architectures") or [])
     if config_dict.get("model_type"):
         names.append(config_dict["model_type"])
