@@ -292,7 +292,8 @@ LMSF_API int lmsf_attention_decode(const void* q, long long q_stride, void* out,
   a.q = (const bf16*)q; a.q_stride = q_stride; a.out = (bf16*)out; a.out_stride = out_stride;
   a.part_o = (float*)scratch;
   a.part_lse = a.part_o ? a.part_o + (size_t)n_seqs_total * n_q_heads * n_splits * HD : nullptr;
-  a.kv = PagedKV{(const bf16*)cache, page_stride, block_size, n_kv_heads};
+  if (!make_paged_kv(a.kv, cache, page_stride, block_size, n_kv_heads))
+    LMSF_REFUSE("attention: block_size=%d must be a power of two", block_size);
   a.block_table = block_table; a.max_blocks = max_blocks; a.seq_ids = seq_ids; a.cu_q = cu_q; a.ctx_len = ctx_len;
   a.scale = scale; a.window = window; a.n_q_heads = n_q_heads; a.group = group; a.n_splits = n_splits;
   const int smem = decode_smem_bytes();

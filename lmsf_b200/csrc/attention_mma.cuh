@@ -41,13 +41,21 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 constexpr int kTileKeys = 64;   // keys per pipeline stage
 constexpr int kThreads = 128;   // 4 warps
 
-// Geometry of one layer's cache and of one request's block table.
+// Geometry of one layer's cache and of one request's block table.  block_size is a power of two.
 struct PagedKV {
   const bf16* cache;        // [page][2][kv_head][slot][HD]
   long long page_stride;    // elements between pages
-  int block_size;
+  int block_size, block_shift;
   int n_kv_heads;
 };
+
+__host__ inline bool make_paged_kv(PagedKV& kv, const void* cache, long long page_stride, int block_size, int n_kv_heads) {
+  if (block_size <= 0 || (block_size & (block_size - 1))) return false;
+  int sh = 0;
+  while ((1 << sh) < block_size) ++sh;
+  kv = PagedKV{(const bf16*)cache, page_stride, block_size, sh, n_kv_heads};
+  return true;
+}
 
 // Shared-memory stage: kTileKeys rows of K then kTileKeys rows of V, each row HD * 2 + 16 bytes (the
 // 16 bytes of padding make the 8 rows of an ldmatrix fall into different banks for any HD).
@@ -59,29 +67,55 @@ template <int HD> struct Stage {
 
 // Issues the copies of keys [key0, key0 + 64) of kv head `kvh` into the stage at `stage_base`.
 // Keys outside [lo, hi) and keys whose page entry is negative are zero-filled, never read.
+// A thread copies one 16-byte column of several CONSECUTIVE rows, so that it looks its page up once per
+// page rather than once per row; a warp's copies of one pass cover whole rows (coalesced).
 template <int HD>
 __device__ __forceinline__ void load_stage(uint32_t stage_base, const PagedKV& kv, const int* __restrict__ table, int kvh,
                                            int key0, int lo, int hi) {
   using S = Stage<HD>;
   const size_t v_off = (size_t)kv.n_kv_heads * kv.block_size * HD;
   const size_t head_off = (size_t)kvh * kv.block_size * HD;
+  const int mask = kv.block_size - 1;
+  if constexpr (kThreads % S::kChunks == 0) {
+    constexpr int kRowsPerThread = kTileKeys * S::kChunks / kThreads;   // = kChunks / 2
+    const int c = threadIdx.x % S::kChunks, row0 = (threadIdx.x / S::kChunks) * kRowsPerThread;
+    const bf16* page_ptr = nullptr;
+    bool have_page = false;                         // page_ptr belongs to the page of the current row
 #pragma unroll
-  for (int it = 0; it < (kTileKeys * S::kChunks) / kThreads; ++it) {
-    const int idx = threadIdx.x + it * kThreads;
-    const int row = idx / S::kChunks, c = idx % S::kChunks;
-    const int key = key0 + row;
-    const bf16* src = kv.cache;
-    int bytes = 0;
-    if (key >= lo && key < hi) {
-      const int page = table[key / kv.block_size];
-      if (page >= 0) {
-        src = kv.cache + (size_t)page * kv.page_stride + head_off + (size_t)(key % kv.block_size) * HD + c * 8;
-        bytes = 16;
+    for (int it = 0; it < kRowsPerThread; ++it) {
+      const int row = row0 + it, key = key0 + row, slot = key & mask;
+      const bool in_range = key >= lo && key < hi;
+      if (slot == 0) have_page = false;
+      if (in_range && !have_page) {
+        const int page = table[key >> kv.block_shift];
+        page_ptr = page >= 0 ? kv.cache + (size_t)page * kv.page_stride + head_off + c * 8 : nullptr;
+        have_page = true;
       }
+      const bool ok = in_range && page_ptr != nullptr;
+      const bf16* src = ok ? page_ptr + (size_t)slot * HD : kv.cache;
+      const uint32_t dst = stage_base + row * S::kRowBytes + c * 16;
+      cp_async_16(dst, src, ok ? 16 : 0);
+      cp_async_16(dst + kTileKeys * S::kRowBytes, ok ? src + v_off : src, ok ? 16 : 0);
     }
-    const uint32_t dst = stage_base + row * S::kRowBytes + c * 16;
-    cp_async_16(dst, src, bytes);
-    cp_async_16(dst + kTileKeys * S::kRowBytes, bytes ? src + v_off : src, bytes);
+  } else {
+#pragma unroll
+    for (int it = 0; it < (kTileKeys * S::kChunks) / kThreads; ++it) {
+      const int idx = threadIdx.x + it * kThreads;
+      const int row = idx / S::kChunks, c = idx % S::kChunks;
+      const int key = key0 + row;
+      const bf16* src = kv.cache;
+      int bytes = 0;
+      if (key >= lo && key < hi) {
+        const int page = table[key >> kv.block_shift];
+        if (page >= 0) {
+          src = kv.cache + (size_t)page * kv.page_stride + head_off + (size_t)(key & mask) * HD + c * 8;
+          bytes = 16;
+        }
+      }
+      const uint32_t dst = stage_base + row * S::kRowBytes + c * 16;
+      cp_async_16(dst, src, bytes);
+      cp_async_16(dst + kTileKeys * S::kRowBytes, bytes ? src + v_off : src, bytes);
+    }
   }
 }
 

@@ -186,7 +186,8 @@ LMSF_API int lmsf_attention_prefill(const void* q, long long q_stride, void* out
   if (block_size <= 0 || max_blocks <= 0) LMSF_REFUSE("attention_prefill: bad block table geometry");
   PrefillArgs a;
   a.q = (const bf16*)q; a.q_stride = q_stride; a.out = (bf16*)out; a.out_stride = out_stride;
-  a.kv = PagedKV{(const bf16*)cache, page_stride, block_size, n_kv_heads};
+  if (!make_paged_kv(a.kv, cache, page_stride, block_size, n_kv_heads))
+    LMSF_REFUSE("attention: block_size=%d must be a power of two", block_size);
   a.block_table = block_table; a.max_blocks = max_blocks; a.tile_seq = tile_seq; a.tile_q0 = tile_q0;
   a.cu_q = cu_q; a.ctx_len = ctx_len; a.scale = scale; a.window = window; a.n_q_heads = n_q_heads;
   a.group = n_q_heads / n_kv_heads;
