@@ -187,7 +187,11 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--kv-stages", type=int, default=0, help="pipeline depth of the attention kernels (default: the build's)")
     a = ap.parse_args()
+    if a.kv_stages:
+        from lmsf_b200 import kernels
+        kernels.MMA_KV_STAGES = a.kv_stages
     dev = torch.device("cuda:0")
     pk = peaks()
     timer = Timer(dev, flush=not a.no_flush)

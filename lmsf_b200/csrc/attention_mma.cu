@@ -25,7 +25,10 @@ namespace fa {
 
 constexpr int HD = LMSF_HEAD_DIM;
 static_assert(HD % 16 == 0 && HD >= 16 && HD <= 128, "head size must be a multiple of 16 between 16 and 128");
-constexpr int kStages = 3;
+#ifndef LMSF_KV_STAGES
+#define LMSF_KV_STAGES 3
+#endif
+constexpr int kStages = LMSF_KV_STAGES;   // stages of 64 keys in flight per block
 constexpr int kKSteps = HD / 16;   // k-steps of q k^T; also pairs of 8-wide output tiles of p v
 constexpr float kLog2e = 1.4426950408889634f;
 using St = Stage<HD>;

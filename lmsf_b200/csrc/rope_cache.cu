@@ -8,6 +8,7 @@
 //
 // Cache layout of one layer: [page][2 (k, v)][kv_head][slot][head_dim].
 #include "common.cuh"
+#include <type_traits>
 
 LMSF_DEFINE_LAST_ERROR(lmsf_rope_cache)
 
@@ -99,6 +100,76 @@ __global__ void rope_cache_kernel(RopeCacheArgs a) {
   }
 }
 
+// Vectorised variant for NeoX pairing: work items of 16 bytes (VEC elements), spread over gridDim.y blocks
+// per token.  Needs rot_dim / 2, head_dim - rot_dim and all row strides to be multiples of VEC and 16-byte
+// aligned pointers.  Same arithmetic as the kernel above, element by element.
+template <typename T, int VEC>
+__global__ void rope_cache_vec_kernel(RopeCacheArgs a) {
+  extern __shared__ float cs[];  // cos[rot/2], sin[rot/2]
+  const int t = blockIdx.x;
+  const int pos = a.positions[t];
+  const int half = a.inv_freq ? a.rot_dim / 2 : 0;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    float s, c;
+    sincosf((float)pos * a.inv_freq[i], &s, &c);
+    cs[i] = c;
+    cs[half + i] = s;
+  }
+  __syncthreads();
+  const int hd = a.head_dim;
+  T* kc = nullptr;
+  T* vc = nullptr;
+  if (a.cache) {
+    const int page = a.block_table[(size_t)a.token_seq[t] * a.max_blocks + pos / a.block_size];
+    if (page < 0) {
+      if (threadIdx.x == 0 && blockIdx.y == 0 && a.error_flag) atomicExch(a.error_flag, 2);
+    } else {
+      kc = (T*)a.cache + (size_t)page * a.page_stride + (size_t)(pos % a.block_size) * hd;
+      vc = kc + (size_t)a.n_kv_heads * a.block_size * hd;
+    }
+  }
+  T* q = (T*)a.q + (size_t)t * a.q_stride;
+  const T* k = (const T*)a.k + (size_t)t * a.k_stride;
+  const T* v = (const T*)a.v + (size_t)t * a.v_stride;
+  const size_t head_pitch = (size_t)a.block_size * hd;
+  const int rot = 2 * half, hv = half / VEC, tail_v = (hd - rot) / VEC, hd_v = hd / VEC;
+  const int n_qrot = a.n_q_heads * hv;
+  const int n_krot = kc ? a.n_kv_heads * hv : 0;
+  const int n_ktail = kc ? a.n_kv_heads * tail_v : 0;
+  const int n_v = kc ? a.n_kv_heads * hd_v : 0;
+  const int total = n_qrot + n_krot + n_ktail + n_v;
+  typedef typename std::conditional<VEC == 8, uint4, float4>::type Raw;
+  for (int w = blockIdx.y * blockDim.x + threadIdx.x; w < total; w += gridDim.y * blockDim.x) {
+    if (w < n_qrot + n_krot) {
+      const bool is_q = w < n_qrot;
+      const int u = is_q ? w : w - n_qrot;
+      const int head = u / hv, i0 = (u % hv) * VEC;
+      const T* src = is_q ? q + (size_t)head * hd : k + (size_t)head * hd;
+      T* dst = is_q ? q + (size_t)head * hd : kc + head * head_pitch;
+      Raw xr = *reinterpret_cast<const Raw*>(src + i0), yr = *reinterpret_cast<const Raw*>(src + half + i0);
+      T* xe = reinterpret_cast<T*>(&xr);
+      T* ye = reinterpret_cast<T*>(&yr);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        const float c = cs[i0 + e], s = cs[half + i0 + e];
+        const float x = to_f32(xe[e]), y = to_f32(ye[e]);
+        xe[e] = from_f32<T>(x * c - y * s);
+        ye[e] = from_f32<T>(y * c + x * s);
+      }
+      *reinterpret_cast<Raw*>(dst + i0) = xr;
+      *reinterpret_cast<Raw*>(dst + half + i0) = yr;
+    } else if (w < n_qrot + n_krot + n_ktail) {
+      const int u = w - n_qrot - n_krot;
+      const int g = u / tail_v, i0 = rot + (u % tail_v) * VEC;
+      *reinterpret_cast<Raw*>(kc + g * head_pitch + i0) = *reinterpret_cast<const Raw*>(k + (size_t)g * hd + i0);
+    } else {
+      const int u = w - n_qrot - n_krot - n_ktail;
+      const int g = u / hd_v, i0 = (u % hd_v) * VEC;
+      *reinterpret_cast<Raw*>(vc + g * head_pitch + i0) = *reinterpret_cast<const Raw*>(v + (size_t)g * hd + i0);
+    }
+  }
+}
+
 }  // namespace lmsf
 
 LMSF_API int lmsf_rope_cache_write(void* q, const void* k, const void* v, long long q_stride, long long k_stride,
@@ -117,10 +188,24 @@ LMSF_API int lmsf_rope_cache_write(void* q, const void* k, const void* v, long l
   if (dtype != LMSF_F32 && dtype != LMSF_BF16) LMSF_REFUSE("rope_cache: unknown dtype code %d", dtype);
   RopeCacheArgs a{q, k, v, q_stride, k_stride, v_stride, positions, token_seq, block_table, max_blocks, block_size,
                   cache, page_stride, inv_freq, rot_dim, is_neox, n_q_heads, n_kv_heads, head_dim, error_flag};
+  cudaStream_t s = (cudaStream_t)stream;
+  const size_t smem = inv_freq ? (size_t)rot_dim * sizeof(float) : 0;
+  const int vec = dtype == LMSF_F32 ? 4 : 8;
+  const int rot = inv_freq ? rot_dim : 0;
+  const bool vec_ok = (is_neox || !inv_freq) && (rot / 2) % vec == 0 && (head_dim - rot) % vec == 0 &&
+                      q_stride % vec == 0 && (!cache || (k_stride % vec == 0 && v_stride % vec == 0 && page_stride % vec == 0)) &&
+                      ((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)cache) % 16 == 0;
+  if (vec_ok) {
+    const int items = (n_q_heads * (rot / 2) + (cache ? n_kv_heads * (rot / 2 + (head_dim - rot) + head_dim) : 0)) / vec;
+    int gy = ceil_div(items > 0 ? items : 1, 128);
+    if (gy > 8) gy = 8;
+    dim3 grid(n_tokens, gy);
+    if (dtype == LMSF_F32) rope_cache_vec_kernel<float, 4><<<grid, 128, smem, s>>>(a);
+    else rope_cache_vec_kernel<bf16, 8><<<grid, 128, smem, s>>>(a);
+    return LMSF_LAUNCH_STATUS();
+  }
   const int work = (n_q_heads + 2 * n_kv_heads) * head_dim / 2;
   const int threads = work >= 1024 ? 256 : (work >= 256 ? 128 : 64);
-  const size_t smem = inv_freq ? (size_t)rot_dim * sizeof(float) : 0;
-  cudaStream_t s = (cudaStream_t)stream;
   if (dtype == LMSF_F32) rope_cache_kernel<float><<<n_tokens, threads, smem, s>>>(a);
   else rope_cache_kernel<bf16><<<n_tokens, threads, smem, s>>>(a);
   return LMSF_LAUNCH_STATUS();
