@@ -77,6 +77,149 @@ __global__ void sample_kernel(int* __restrict__ out, const float* __restrict__ l
   }
 }
 
+// ---------------------------------------------------------------------------------------------- penalties
+// One thread per (row, token) pair that occurs in the row's prompt or output.  Order as in the reference
+// (core/src/model_executor/layers/sampler.rs:48-137): repetition first (x > 0 ? x / r : x * r, for tokens of the
+// prompt or the output), then x -= frequency * count_in_output, then x -= presence * (count_in_output > 0).
+__global__ void penalties_kernel(float* __restrict__ logits, long long row_stride, const int* __restrict__ rows,
+                                 const int* __restrict__ tokens, const int* __restrict__ out_counts, int n,
+                                 const float* __restrict__ presence, const float* __restrict__ frequency,
+                                 const float* __restrict__ repetition) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int r = rows[i];
+  float* p = logits + (size_t)r * row_stride + tokens[i];
+  float x = *p;
+  const float rep = repetition[r];
+  x = x > 0.f ? x / rep : x * rep;
+  const int c = out_counts[i];
+  x -= frequency[r] * (float)c;
+  if (c > 0) x -= presence[r];
+  *p = x;
+}
+
+// ---------------------------------------------------------------------------------------------- filters
+// Order-preserving map of a float to an unsigned key (larger float, larger key).
+__device__ __forceinline__ uint32_t float_key(float x) {
+  const uint32_t u = __float_as_uint(x);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+__device__ __forceinline__ float block_sum_f(float v, float* scratch) { return block_sum(v, scratch); }
+__device__ __forceinline__ float block_max_f(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nwarps ? scratch[lane] : -INFINITY;
+    t = warp_max(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
+// Temperature sampling with top-k, top-p and min-p, one block per row.  With z = logits / T:
+//   top-k keeps the k largest z (ties at the k-th value are all kept);
+//   top-p keeps a token iff the probability mass of the strictly larger kept tokens is < p
+//         (the reference removes the ascending prefix whose cumulative mass is <= 1 - p,
+//         core/src/model_executor/layers/sampler.rs:139-210: the same set when values are distinct);
+//   min-p keeps z >= max z + log(min_p) (sampler.rs:305-312);
+// and the token is drawn among the kept ones by the exponential race of sample_kernel.
+// Thresholds are found by bisection over the 32-bit keys with block-wide sums in a fixed order, so the
+// kept set, and with it the draw, is reproducible.
+__global__ void sample_filtered_kernel(int* __restrict__ out, const float* __restrict__ logits, long long row_stride,
+                                       int vocab, const float* __restrict__ temperature,
+                                       const unsigned long long* __restrict__ seed, const int* __restrict__ step,
+                                       const int* __restrict__ top_k, const float* __restrict__ top_p,
+                                       const float* __restrict__ min_p, const int* __restrict__ row_ids) {
+  __shared__ float scratch[33];
+  __shared__ Best sh[32];
+  const int r = row_ids ? row_ids[blockIdx.x] : blockIdx.x;
+  const float* row = logits + (size_t)r * row_stride;
+  const float T = temperature[r];
+  const float invT = 1.0f / T;
+  const int k = top_k ? top_k[r] : -1;
+  const float p = top_p ? top_p[r] : 1.0f;
+  const float mp = min_p ? min_p[r] : 0.0f;
+
+  float m = -INFINITY;
+  for (int v = threadIdx.x; v < vocab; v += blockDim.x) {
+    const float z = row[v] * invT;
+    if (z == z) m = fmaxf(m, z);
+  }
+  m = block_max_f(m, scratch);
+
+  uint32_t key_min = 0u;                     // tokens with key >= key_min are kept
+  if (k > 0 && k < vocab) {                  // largest key with count(key_v >= key) >= k
+    uint32_t lo = 0u, hi = 0xffffffffu;
+    while (lo < hi) {
+      const uint32_t mid = lo + (uint32_t)(((unsigned long long)hi - lo + 1ull) >> 1);
+      float cnt = 0.f;
+      for (int v = threadIdx.x; v < vocab; v += blockDim.x) {
+        const float z = row[v] * invT;
+        cnt += (z == z && float_key(z) >= mid) ? 1.f : 0.f;
+      }
+      cnt = block_sum_f(cnt, scratch);
+      if (cnt >= (float)k) lo = mid; else hi = mid - 1u;
+    }
+    key_min = lo;
+  }
+  if (p < 1.0f) {
+    float Z = 0.f;
+    for (int v = threadIdx.x; v < vocab; v += blockDim.x) {
+      const float z = row[v] * invT;
+      if (z == z && float_key(z) >= key_min) Z += expf(z - m);
+    }
+    Z = block_sum_f(Z, scratch);
+    const float target = p * Z;              // kept iff mass of strictly larger keys < p * Z
+    uint32_t lo = key_min, hi = float_key(m);   // smallest key whose mass_gt < target; key(m) always qualifies
+    while (lo < hi) {
+      const uint32_t mid = lo + ((hi - lo) >> 1);
+      float mass = 0.f;
+      for (int v = threadIdx.x; v < vocab; v += blockDim.x) {
+        const float z = row[v] * invT;
+        if (z == z && float_key(z) > mid) mass += expf(z - m);
+      }
+      mass = block_sum_f(mass, scratch);
+      if (mass < target) hi = mid; else lo = mid + 1u;
+    }
+    key_min = lo;
+  }
+  if (mp > 0.0f) {
+    const uint32_t kmp = float_key(m + logf(mp));
+    if (kmp > key_min) key_min = kmp;
+  }
+
+  const uint32_t slo = (uint32_t)(seed[r] & 0xffffffffull), shi = (uint32_t)(seed[r] >> 32);
+  const uint32_t st = (uint32_t)step[r];
+  Best b{-INFINITY, 0x7fffffff};
+  for (int v = threadIdx.x; v < vocab; v += blockDim.x) {
+    const float z = row[v] * invT;
+    if (z != z || float_key(z) < key_min) continue;
+    b = better(b, Best{(double)row[v] / (double)T + neg_log_exponential(slo, shi, st, (uint32_t)v), v});
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    Best other{__shfl_xor_sync(0xffffffffu, b.score, o), __shfl_xor_sync(0xffffffffu, b.index, o)};
+    b = better(b, other);
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __syncthreads();
+  if (lane == 0) sh[warp] = b;
+  __syncthreads();
+  if (warp == 0) {
+    const int nw = blockDim.x >> 5;
+    b = lane < nw ? sh[lane] : Best{-INFINITY, 0x7fffffff};
+    for (int o = 16; o > 0; o >>= 1) {
+      Best other{__shfl_xor_sync(0xffffffffu, b.score, o), __shfl_xor_sync(0xffffffffu, b.index, o)};
+      b = better(b, other);
+    }
+    if (lane == 0) out[r] = b.index == 0x7fffffff ? 0 : b.index;
+  }
+}
+
 }  // namespace lmsf
 
 // logits: [rows, vocab] float32; temperature [rows] float32, seed [rows] uint64, step [rows] int32
@@ -88,5 +231,32 @@ LMSF_API int lmsf_sample(int* out, const float* logits, long long row_stride, in
   if (vocab <= 0 || row_stride < vocab) LMSF_REFUSE("sample: vocab=%d, row_stride=%lld", vocab, row_stride);
   const int threads = vocab >= 8192 ? 1024 : 256;
   sample_kernel<<<rows, threads, 0, (cudaStream_t)stream>>>(out, logits, row_stride, vocab, temperature, seed, step);
+  return LMSF_LAUNCH_STATUS();
+}
+
+// logits are changed in place.  rows/tokens/out_counts: [n] int32; presence/frequency/repetition: [n_rows] float32.
+LMSF_API int lmsf_apply_penalties(float* logits, long long row_stride, const int* rows, const int* tokens,
+                                  const int* out_counts, int n, const float* presence, const float* frequency,
+                                  const float* repetition, void* stream) {
+  using namespace lmsf;
+  if (n <= 0) return 0;
+  penalties_kernel<<<ceil_div(n, 256), 256, 0, (cudaStream_t)stream>>>(logits, row_stride, rows, tokens, out_counts, n,
+                                                                       presence, frequency, repetition);
+  return LMSF_LAUNCH_STATUS();
+}
+
+// The rows listed in row_ids (null: rows 0 .. n_rows-1) are sampled at their temperature (> 0) among the
+// tokens that their top_k (<= 0: off), top_p (1: off) and min_p (0: off) keep; out[row] receives the token.
+// All per-row arrays are indexed by row.  top_k, top_p, min_p may be null (off for all rows).
+LMSF_API int lmsf_sample_filtered(int* out, const float* logits, long long row_stride, int rows, int vocab,
+                                  const float* temperature, const unsigned long long* seed, const int* step,
+                                  const int* top_k, const float* top_p, const float* min_p, const int* row_ids,
+                                  void* stream) {
+  using namespace lmsf;
+  if (rows <= 0) return 0;
+  if (vocab <= 0 || row_stride < vocab) LMSF_REFUSE("sample_filtered: vocab=%d, row_stride=%lld", vocab, row_stride);
+  if (!temperature || !seed || !step) LMSF_REFUSE("sample_filtered: temperature, seed and step are needed");
+  sample_filtered_kernel<<<rows, 1024, 0, (cudaStream_t)stream>>>(out, logits, row_stride, vocab, temperature, seed,
+                                                                  step, top_k, top_p, min_p, row_ids);
   return LMSF_LAUNCH_STATUS();
 }

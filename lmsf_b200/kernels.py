@@ -243,6 +243,41 @@ def sample(out: torch.Tensor, logits: torch.Tensor, temperature: Optional[torch.
     _check(rc, "sampling.cu", "lmsf_sampling")
 
 
+def apply_penalties(logits: torch.Tensor, rows: torch.Tensor, tokens: torch.Tensor, out_counts: torch.Tensor,
+                    presence: torch.Tensor, frequency: torch.Tensor, repetition: torch.Tensor):
+    """In place on float32 logits [n_rows, vocab]: for every listed (row, token) pair the repetition, frequency
+    and presence penalties of that row; out_counts is how often the token occurs in the row's output so far
+    (0: it occurs in the prompt only).  presence / frequency / repetition: float32 [n_rows]."""
+    if logits.dtype != torch.float32 or logits.stride(1) != 1:
+        raise KernelError("apply_penalties: logits must be float32 with a contiguous last dimension")
+    n = rows.numel()
+    for t in (presence, frequency, repetition):
+        if t.dtype != torch.float32 or t.shape != (logits.shape[0],):
+            raise KernelError("apply_penalties: per-row penalties must be float32 [n_rows]")
+    f = _func("sampling.cu", "lmsf_apply_penalties",
+              [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+    rc = f(_ptr(logits), logits.stride(0), _i32(rows, "rows"), _i32(tokens, "tokens"), _i32(out_counts, "out_counts"),
+           n, _ptr(presence), _ptr(frequency), _ptr(repetition), _stream())
+    _check(rc, "sampling.cu", "lmsf_sampling")
+
+
+def sample_filtered(out: torch.Tensor, logits: torch.Tensor, temperature: torch.Tensor, seed: torch.Tensor,
+                    step: torch.Tensor, top_k: Optional[torch.Tensor], top_p: Optional[torch.Tensor],
+                    min_p: Optional[torch.Tensor], row_ids: Optional[torch.Tensor] = None):
+    """Temperature sampling of the rows in row_ids (None: all) among the tokens kept by top_k (int32, <= 0 off),
+    top_p (float32, 1 off) and min_p (float32, 0 off); per-row arrays are indexed by row."""
+    rows, vocab = logits.shape
+    if logits.dtype != torch.float32 or logits.stride(1) != 1 or out.dtype != torch.int32 or out.shape != (rows,):
+        raise KernelError("sample_filtered: logits float32 [rows, vocab], out int32 [rows]")
+    n = rows if row_ids is None else row_ids.numel()
+    f = _func("sampling.cu", "lmsf_sample_filtered",
+              [c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+               c_void_p, c_void_p])
+    rc = f(_ptr(out), _ptr(logits), logits.stride(0), n, vocab, _ptr(temperature), _ptr(seed), _i32(step, "step"),
+           _i32(top_k, "top_k"), _ptr(top_p), _ptr(min_p), _i32(row_ids, "row_ids"), _stream())
+    _check(rc, "sampling.cu", "lmsf_sampling")
+
+
 # ----------------------------------------------------------------------------- tensor-core attention (bfloat16)
 
 MMA_MAX_HEAD_DIM = 128

@@ -229,3 +229,47 @@ def generate(cfg, weights, prompt, n_tokens, temperature=0.0, seed=0, dtype=torc
         out.append(tok)
         ids.append(tok)
     return out, torch.stack(rows)
+
+
+def apply_penalties(logits_row, prompt, output, presence, frequency, repetition):
+    """core/src/model_executor/layers/sampler.rs:48-137: repetition on tokens of prompt or output
+    (x > 0 ? x / r : x * r), then x -= frequency * count(output), then x -= presence * [count(output) > 0]."""
+    x = logits_row.clone().double()
+    seen = set(prompt) | set(output)
+    for t in seen:
+        x[t] = x[t] / repetition if x[t] > 0 else x[t] * repetition
+    for t in set(output):
+        c = output.count(t)
+        x[t] -= frequency * c
+        x[t] -= presence
+    return x.float()
+
+
+def filter_logits(z, top_k=-1, top_p=1.0, min_p=0.0):
+    """z = logits / T.  top-k then top-p on the ascending sort (core/src/model_executor/layers/sampler.rs:139-210):
+    values below the k-th largest go to -inf; of the rest the ascending prefix whose cumulative probability is
+    <= 1 - p goes to -inf, the largest always stays.  min-p (sampler.rs:305-312): probability < min_p * largest."""
+    z = z.clone().double()
+    V = len(z)
+    srt, idx = torch.sort(z)
+    if 0 < top_k < V:
+        kth = srt[V - top_k]
+        srt = srt.masked_fill(srt < kth, float("-inf"))
+    if top_p < 1.0:
+        probs = torch.softmax(srt, dim=-1)
+        cum = torch.cumsum(probs, dim=-1)
+        mask = cum <= 1.0 - top_p
+        mask[-1] = False
+        srt = srt.masked_fill(mask, float("-inf"))
+    out = torch.empty_like(z)
+    out[idx] = srt
+    if min_p > 0.0:
+        probs = torch.softmax(out, dim=-1)
+        out = out.masked_fill(probs < min_p * probs.max(), float("-inf"))
+    return out
+
+
+def sample_filtered(logits_row, temperature, seed, step, top_k=-1, top_p=1.0, min_p=0.0):
+    z = filter_logits(logits_row.double() / temperature, top_k, top_p, min_p).numpy()
+    score = z - np.log(exponential_noise(seed, step, len(z)))
+    return int(np.argmax(score))

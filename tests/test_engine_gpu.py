@@ -106,3 +106,27 @@ def test_bfloat16_generation_runs_and_mostly_agrees():
     if float(top2[0] - top2[1]) > 0.1 * float(rows[0].abs().max()):      # a clear winner must be found in bfloat16 too
         assert o.outputs[0].token_ids[0] == ref[0]
     assert len(o.outputs[0].token_ids) == 6
+
+
+def test_top_k_top_p_and_penalties_through_the_entry_point():
+    """The reference example's own options (temperature 0.8, top-k 5, presence penalty 0.2) and the others."""
+    from lmsf_b200 import SamplingParams
+    name = "A"
+    cfg, w = P.load_model(util.model_folder(name, "float32", 0.15))
+    prompt = util.random_ids(14, cfg["vocab_size"], 51)
+    sp = SamplingParams(temperature=0.8, top_k=5, top_p=0.9, min_p=0.02, presence_penalty=0.2, frequency_penalty=0.1,
+                        repetition_penalty=1.3, seed=9, max_tokens=10, ignore_eos=True)
+    llm = _llm(name, "float32", num_gpu_blocks=32)
+    got = llm.generate(prompt_token_ids=[prompt], sampling_params=sp)[0].outputs[0].token_ids
+    ids, out = list(prompt), []
+    for step in range(10):
+        row = P.forward(cfg, w, ids)[-1]
+        row = P.apply_penalties(row, prompt, out, 0.2, 0.1, 1.3)
+        tok = P.sample_filtered(row, 0.8, 9, step, 5, 0.9, 0.02)
+        out.append(tok)
+        ids.append(tok)
+    assert got == out
+    # a greedy request beside it is not disturbed
+    both = llm.generate(prompt_token_ids=[prompt, prompt],
+                        sampling_params=[sp, SamplingParams(temperature=0, max_tokens=5, ignore_eos=True)])
+    assert both[0].outputs[0].token_ids == out and both[1].outputs[0].token_ids == P.generate(cfg, w, prompt, 5)[0]

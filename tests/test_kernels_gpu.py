@@ -297,3 +297,53 @@ def test_attention_tensor_core_kernels(nh, nkv, hd, bs, window):
     out2 = torch.empty_like(out)
     kernels.attention_generic(out2, qd, cd, btd, bs, token_seq.to(d), positions.to(d), scale, window, nh, nkv, hd)
     assert (out2.float() - out.float()).abs().max().item() <= tol_abs
+
+
+def test_sampling_filters_and_penalties():
+    from lmsf_b200 import kernels
+    g = torch.Generator().manual_seed(7)
+    d = dev()
+    for vocab in (50, 1000, 32003):
+        rows = 8
+        logits = torch.randn(rows, vocab, generator=g) * 2.5
+        temps = [0.7, 1.0, 0.9, 1.3, 0.8, 0.5, 1.0, 2.0]
+        ks = [5, -1, 40, 1, -1, 3, vocab + 5, -1]
+        ps = [1.0, 0.9, 0.5, 1.0, 0.2, 0.8, 1.0, 0.95]
+        mps = [0.0, 0.0, 0.0, 0.0, 0.05, 0.1, 0.3, 0.0]
+        seeds = [3, 4, 5, 6, 7, 8, 9, 2 ** 40 + 1]
+        ld = logits.to(d)
+        seed_t = torch.from_numpy(np.asarray(seeds, dtype=np.uint64).view(np.int64)).to(d)
+        for step in range(6):
+            out = torch.full((rows,), -1, dtype=torch.int32, device=d)
+            steps = torch.full((rows,), step, dtype=torch.int32, device=d)
+            kernels.sample_filtered(out, ld, torch.tensor(temps, device=d), seed_t, steps,
+                                    torch.tensor(ks, dtype=torch.int32, device=d), torch.tensor(ps, device=d),
+                                    torch.tensor(mps, device=d))
+            got = out.tolist()
+            for r in range(rows):
+                want = P.sample_filtered(logits[r], temps[r], seeds[r], step, ks[r], ps[r], mps[r])
+                assert got[r] == want, (vocab, step, r)
+                kept = P.filter_logits(logits[r].double() / temps[r], ks[r], ps[r], mps[r])
+                assert torch.isfinite(kept[got[r]])
+        # only some rows, through row_ids: the others keep what they had
+        out = torch.full((rows,), -7, dtype=torch.int32, device=d)
+        kernels.sample_filtered(out, ld, torch.tensor(temps, device=d), seed_t,
+                                torch.zeros(rows, dtype=torch.int32, device=d),
+                                torch.tensor(ks, dtype=torch.int32, device=d), torch.tensor(ps, device=d),
+                                torch.tensor(mps, device=d), torch.tensor([2, 5], dtype=torch.int32, device=d))
+        got = out.tolist()
+        assert [got[i] for i in (0, 1, 3, 4, 6, 7)] == [-7] * 6 and got[2] >= 0 and got[5] >= 0
+    # penalties
+    vocab = 300
+    logits = torch.randn(2, vocab, generator=g) * 2
+    prompt, output = [5, 9, 9, 200], [9, 17, 17, 17, 250]
+    pres, freq, rep = 0.4, 0.3, 1.7
+    want = P.apply_penalties(logits[1], prompt, output, pres, freq, rep)
+    seen = sorted(set(prompt) | set(output))
+    ld = logits.to(d).clone()
+    kernels.apply_penalties(ld, torch.tensor([1] * len(seen), dtype=torch.int32, device=d),
+                            torch.tensor(seen, dtype=torch.int32, device=d),
+                            torch.tensor([output.count(t) for t in seen], dtype=torch.int32, device=d),
+                            torch.tensor([0.0, pres], device=d), torch.tensor([0.0, freq], device=d),
+                            torch.tensor([1.0, rep], device=d))
+    assert torch.equal(ld[0].cpu(), logits[0]) and torch.allclose(ld[1].cpu(), want, rtol=1e-6, atol=1e-6)
