@@ -147,6 +147,19 @@ def bench_gemm(args, dev, timer, pk):
                 frac_bf16=flops / t / 1e12 / pk["bf16_tflops"], frac_hbm=nbytes / t / 1e9 / pk["hbm_gbs"])
 
 
+def bench_gemm_skinny(args, dev, timer, pk):
+    from lmsf_b200 import kernels
+    M, N, K = args.m, args.n, args.k
+    x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+    w = torch.randn(N, K, device=dev, dtype=torch.bfloat16)
+    fuse = "silu" if args.fuse_act else None
+    out = torch.empty(M, N // 2 if fuse else N, device=dev, dtype=torch.bfloat16)
+    t = timer.run(lambda: kernels.gemm_skinny(out, x, w, fuse), args.warmup, args.iters)
+    nbytes = 2 * (M * K + N * K + out.numel())
+    return dict(kernel="gemm_skinny", m=M, n=N, k=K, fused_act=bool(fuse), us=t * 1e6, gbs=nbytes / t / 1e9,
+                frac_hbm=nbytes / t / 1e9 / pk["hbm_gbs"])
+
+
 def bench_sampling(args, dev, timer, pk):
     from lmsf_b200 import kernels
     rows, V = args.batch, args.vocab
@@ -164,7 +177,7 @@ def bench_sampling(args, dev, timer, pk):
 
 BENCHES = {"decode_attention": bench_decode_attention, "prefill_attention": bench_prefill_attention,
            "add_rmsnorm": bench_rmsnorm, "gated_act": bench_gated_act, "rope_cache_write": bench_rope_cache,
-           "gemm": bench_gemm, "sampling": bench_sampling}
+           "gemm": bench_gemm, "gemm_skinny": bench_gemm_skinny, "sampling": bench_sampling}
 
 
 def main() -> int:
@@ -184,11 +197,16 @@ def main() -> int:
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=28672)
     ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--fuse-act", action="store_true", help="gemm_skinny: W = [gate; up], fused silu(gate) * up")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--skinny-defines", default="", help="comma-separated -D constants for gemm_skinny.cu")
     ap.add_argument("--kv-stages", type=int, default=0, help="pipeline depth of the attention kernels (default: the build's)")
     a = ap.parse_args()
+    if a.skinny_defines:
+        from lmsf_b200 import kernels
+        kernels.SKINNY_DEFINES = tuple(a.skinny_defines.split(","))
     if a.kv_stages:
         from lmsf_b200 import kernels
         kernels.MMA_KV_STAGES = a.kv_stages

@@ -1,0 +1,223 @@
+// out[M, N] = x[M, K] * W[N, K]^T for a handful of rows (M <= 16, bfloat16): the matrix product of a
+// decode step, where every weight is read once and the time is the time to stream W from memory.
+// Optionally fused with the gated activation of the feed-forward: W = [gate; up] stacked along N and
+// out[m, n] = act(x . gate_n) * (x . up_n).
+//
+// Counterpart in the reference: cublasLtMatmul for every M (tops/csrc/tops/tensorrt_llm/common/
+// cublasMMWrapper.cpp:122-209) followed by silu_and_mul_kernel (vllm/kernels/activation_kernels.cu:26-41).
+//
+// Shape of the kernel: the weight rows are the M side of mma.sync m16n8k16 (16 output features per
+// block), the tokens are its N side (8 per tile).  The 4 warps of a block split K among themselves; each
+// warp streams its 16 x K/4 slice of W through a private ring of cp.async stages (16 rows x 128 k, each row
+// 256 contiguous bytes of memory, swizzled in 16-byte chunks, read back with ldmatrix) and needs no block-wide barrier until the end,
+// where the four partial sums are added in a fixed order.  The matching 64 k of x travel in the same
+// stages (8 or 16 rows), so no load of the inner loop waits on anything but its stage.
+#include "attention_mma.cuh"   // cp.async, ldmatrix and mma helpers
+
+LMSF_DEFINE_LAST_ERROR(lmsf_gemm_skinny)
+
+namespace lmsf {
+namespace skinny {
+
+using namespace lmsf::fa;
+
+constexpr int kWarps = 4;
+#ifndef LMSF_SKINNY_CH
+#define LMSF_SKINNY_CH 2
+#endif
+constexpr int CH = LMSF_SKINNY_CH;          // a stage holds 64 * CH values of k per row
+constexpr int kChunkK = 64 * CH;            // k per stage
+constexpr int kRowBytes = kChunkK * 2;      // bytes of one row in a stage (contiguous in memory)
+constexpr int kCPR = 8 * CH;                // 16-byte chunks per row
+constexpr int kStageBytes = 16 * kRowBytes; // one group of 16 rows
+
+struct Args {
+  const bf16* x; long long ldx;
+  const bf16* w; long long ldw;
+  void* out; long long ldo;
+  int M, N, K;
+  int up_offset;      // FUSE: row of W where the "up" half starts (= N of the output)
+  int act;            // FUSE: 0 silu, 1 gelu_tanh
+  int out_f32;
+};
+
+__device__ __forceinline__ float act_apply(float g, int act) {
+  if (act == 0) return g / (1.0f + expf(-g));
+  const float k = 0.7978845608028654f;
+  return 0.5f * g * (1.0f + tanhf(k * (g + 0.044715f * g * g * g)));
+}
+
+// Copies `n_rows_stage` rows x k [k0, k0 + kChunkK) into a stage: row r of the stage comes from `base + r * ld`
+// when `r < n_valid`, else it is zero-filled.  One warp instruction copies whole rows or half rows, so that
+// memory sees contiguous requests of kRowBytes.  16-byte chunk c of row r lands at chunk c ^ (r & 7).
+template <int N_ROWS>
+__device__ __forceinline__ void issue_rows(uint32_t stage, const bf16* __restrict__ base, long long ld, int n_valid,
+                                           int k0, int K, int lane) {
+  constexpr int kLanesPerRow = kCPR < 32 ? kCPR : 32;
+  constexpr int kRowsPerInstr = 32 / kLanesPerRow;
+  constexpr int kChunkPasses = kCPR / kLanesPerRow;
+#pragma unroll
+  for (int i = 0; i < N_ROWS / kRowsPerInstr; ++i) {
+    const int r = lane / kLanesPerRow + kRowsPerInstr * i;
+    const bool ok = r < n_valid;
+#pragma unroll
+    for (int j = 0; j < kChunkPasses; ++j) {
+      const int c = lane % kLanesPerRow + j * kLanesPerRow;
+      const bool okc = ok && k0 + c * 8 < K;          // K is a multiple of 8: a chunk is inside or outside
+      const bf16* src = okc ? base + (size_t)r * ld + k0 + c * 8 : base;
+      cp_async_16(stage + r * kRowBytes + ((c ^ (r & 7)) << 4), src, okc ? 16 : 0);
+    }
+  }
+}
+
+template <int NT, int GROUPS, int STAGES>
+__global__ void __launch_bounds__(kWarps * 32) skinny_kernel(Args a) {
+  constexpr int kStage = GROUPS * kStageBytes + NT * 8 * kRowBytes;      // W group(s), then x
+  extern __shared__ __align__(128) unsigned char smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g4 = lane >> 2, t4 = lane & 3;
+  const int n0 = blockIdx.x * 16;
+  const int n_chunks_total = (a.K + kChunkK - 1) / kChunkK;
+  const int per_warp = (n_chunks_total + kWarps - 1) / kWarps;
+  const int c_begin = warp * per_warp, c_end = min(n_chunks_total, c_begin + per_warp);
+  const int n_chunks = max(0, c_end - c_begin);
+  const uint32_t ring = smem_u32(smem) + warp * (STAGES * kStage);
+  const int rows_total = GROUPS == 2 ? a.up_offset : a.N;       // rows of one group
+
+  auto issue = [&](int c) {
+    const uint32_t st = ring + (c % STAGES) * kStage;
+    const int k0 = (c_begin + c) * kChunkK;
+    issue_rows<16>(st, a.w + (size_t)n0 * a.ldw, a.ldw, rows_total - n0, k0, a.K, lane);
+    if (GROUPS == 2)
+      issue_rows<16>(st + kStageBytes, a.w + (size_t)(a.up_offset + n0) * a.ldw, a.ldw, rows_total - n0, k0, a.K, lane);
+    issue_rows<8 * NT>(st + GROUPS * kStageBytes, a.x, a.ldx, a.M, k0, a.K, lane);
+  };
+  for (int s = 0; s < STAGES - 1; ++s) {
+    if (s < n_chunks) issue(s);
+    cp_async_commit();
+  }
+
+  float acc[GROUPS][NT][4];
+#pragma unroll
+  for (int g = 0; g < GROUPS; ++g)
+#pragma unroll
+    for (int t = 0; t < NT; ++t) acc[g][t][0] = acc[g][t][1] = acc[g][t][2] = acc[g][t][3] = 0.f;
+
+  for (int c = 0; c < n_chunks; ++c) {
+    cp_async_wait<STAGES - 2>();
+    __syncwarp();
+    if (c + STAGES - 1 < n_chunks) issue(c + STAGES - 1);
+    cp_async_commit();
+    const uint32_t st = ring + (c % STAGES) * kStage;
+    const uint32_t xs = st + GROUPS * kStageBytes;
+    const int mi = lane >> 3, r = lane & 7;
+#pragma unroll
+    for (int kp = 0; kp < 2 * CH; ++kp) {          // pairs of k-steps (32 values of k)
+      uint32_t xf[2][NT][2];
+      if (NT == 1) {
+        uint32_t b[4];
+        ldmatrix_x4(b, xs + r * kRowBytes + (((kp * 4 + mi) ^ (r & 7)) << 4));
+        xf[0][0][0] = b[0]; xf[0][0][1] = b[1];
+        xf[1][0][0] = b[2]; xf[1][0][1] = b[3];
+      } else {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t b[4];
+          const int row = (mi >> 1) * 8 + r;
+          ldmatrix_x4(b, xs + row * kRowBytes + ((((kp * 2 + h) * 2 + (mi & 1)) ^ (row & 7)) << 4));
+          xf[h][0][0] = b[0]; xf[h][0][1] = b[1];
+          xf[h][NT - 1][0] = b[2]; xf[h][NT - 1][1] = b[3];
+        }
+      }
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int row = (mi & 1) * 8 + r, chunk = (kp * 2 + h) * 2 + (mi >> 1);
+#pragma unroll
+        for (int g = 0; g < GROUPS; ++g) {
+          uint32_t af[4];
+          ldmatrix_x4(af, st + g * kStageBytes + row * kRowBytes + ((chunk ^ (row & 7)) << 4));
+#pragma unroll
+          for (int t = 0; t < NT; ++t) mma_16816(acc[g][t], af, xf[h][t][0], xf[h][t][1]);
+        }
+      }
+    }
+  }
+  cp_async_wait<0>();
+  __syncwarp();
+
+  // partial sums of the four warps: [warp][group][row 16][token 8 NT], added in warp order
+  float* part = reinterpret_cast<float*>(smem + warp * (STAGES * kStage));
+#pragma unroll
+  for (int g = 0; g < GROUPS; ++g)
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+      float* base = part + g * (16 * 8 * NT);
+      base[g4 * (8 * NT) + t * 8 + t4 * 2] = acc[g][t][0];
+      base[g4 * (8 * NT) + t * 8 + t4 * 2 + 1] = acc[g][t][1];
+      base[(g4 + 8) * (8 * NT) + t * 8 + t4 * 2] = acc[g][t][2];
+      base[(g4 + 8) * (8 * NT) + t * 8 + t4 * 2 + 1] = acc[g][t][3];
+    }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < 16 * 8 * NT; idx += kWarps * 32) {
+    const int m = idx / 16, row = idx % 16;          // consecutive threads write consecutive n
+    if (m >= a.M || n0 + row >= rows_total) continue;
+    float v[GROUPS];
+#pragma unroll
+    for (int g = 0; g < GROUPS; ++g) {
+      float s = 0.f;
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w)
+        s += reinterpret_cast<const float*>(smem + w * (STAGES * kStage))[g * (16 * 8 * NT) + row * (8 * NT) + m];
+      v[g] = s;
+    }
+    const float r = GROUPS == 2 ? act_apply(v[0], a.act) * v[GROUPS - 1] : v[0];
+    if (a.out_f32) reinterpret_cast<float*>(a.out)[(size_t)m * a.ldo + n0 + row] = r;
+    else reinterpret_cast<bf16*>(a.out)[(size_t)m * a.ldo + n0 + row] = __float2bfloat16_rn(r);
+  }
+}
+
+template <int NT, int GROUPS, int STAGES>
+static int launch(const Args& a, int rows, cudaStream_t s) {
+  const int smem = kWarps * STAGES * (GROUPS * kStageBytes + NT * 8 * kRowBytes);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(skinny_kernel<NT, GROUPS, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  skinny_kernel<NT, GROUPS, STAGES><<<ceil_div(rows, 16), kWarps * 32, smem, s>>>(a);
+  return LMSF_LAUNCH_STATUS();
+}
+
+#ifndef LMSF_SKINNY_STAGES
+#define LMSF_SKINNY_STAGES (CH == 1 ? 6 : (CH == 2 ? 4 : 3))
+#endif
+constexpr int kStagesPlain = LMSF_SKINNY_STAGES;
+constexpr int kStagesFused = CH == 1 ? 3 : (CH == 2 ? 3 : 2);
+
+}  // namespace skinny
+}  // namespace lmsf
+
+// x: [M, K] bfloat16 (M <= 16), w: [N, K] bfloat16, out: [M, N] bfloat16 or float32.  K % 8 == 0.
+// fuse_act < 0: plain product.  fuse_act = 0 (silu) or 1 (gelu_tanh): w is [2 * N_out, K] (gate rows first),
+// out is [M, N_out] = act(x gate^T) * (x up^T), N = 2 * N_out.
+LMSF_API int lmsf_gemm_skinny(void* out, const void* x, const void* w, int M, int N, int K, long long ldx, long long ldw,
+                              long long ldo, int fuse_act, int out_f32, void* stream) {
+  using namespace lmsf;
+  using namespace lmsf::skinny;
+  if (M <= 0 || N <= 0) return 0;
+  if (M > 16) LMSF_REFUSE("gemm_skinny: M=%d, this kernel takes at most 16 rows", M);
+  if (K <= 0 || K % 8) LMSF_REFUSE("gemm_skinny: K=%d must be a positive multiple of 8", K);
+  if (fuse_act > 1) LMSF_REFUSE("gemm_skinny: unknown activation code %d", fuse_act);
+  if (fuse_act >= 0 && N % 2) LMSF_REFUSE("gemm_skinny: a gated product needs an even N, got %d", N);
+  if (ldx < K || ldw < K || ldx % 8 || ldw % 8 || ((uintptr_t)x % 16) || ((uintptr_t)w % 16))
+    LMSF_REFUSE("gemm_skinny: the rows of x and w must be 16-byte aligned");
+  Args a{(const bf16*)x, ldx, (const bf16*)w, ldw, out, ldo, M, N, K, fuse_act >= 0 ? N / 2 : 0, fuse_act, out_f32};
+  cudaStream_t s = (cudaStream_t)stream;
+  if (fuse_act >= 0) {
+    if (ldo < N / 2) LMSF_REFUSE("gemm_skinny: ldo is smaller than the output row");
+    return M <= 8 ? launch<1, 2, kStagesFused>(a, N / 2, s) : launch<2, 2, kStagesFused>(a, N / 2, s);
+  }
+  if (ldo < N) LMSF_REFUSE("gemm_skinny: ldo is smaller than the output row");
+  return M <= 8 ? launch<1, 1, kStagesPlain>(a, N, s) : launch<2, 1, kStagesPlain>(a, N, s);
+}

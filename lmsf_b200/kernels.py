@@ -221,6 +221,38 @@ def gemm_tn_simt(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor):
     _check(rc, "gemm_simt.cu", "lmsf_gemm_simt")
 
 
+# ----------------------------------------------------------------------------- weight-streaming product (M <= 16)
+
+SKINNY_MAX_M = 16
+SKINNY_DEFINES: Tuple[str, ...] = ()      # build-time constants of gemm_skinny.cu (experiments override them)
+
+
+def gemm_skinny_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 and 0 < x.shape[0] <= SKINNY_MAX_M
+            and x.shape[1] % 8 == 0 and x.stride(1) == 1 and w.stride(1) == 1 and w.stride(0) % 8 == 0
+            and x.stride(0) % 8 == 0 and w.data_ptr() % 16 == 0 and x.data_ptr() % 16 == 0)
+
+
+def gemm_skinny(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, fuse_act: Optional[str] = None):
+    """out[M, N] = x[M, K] w[N, K]^T for M <= 16 (bfloat16 in, bfloat16 or float32 out).  With fuse_act
+    ("silu", "gelu_tanh") w is [2 N_out, K] (gate rows, then up rows) and out[M, N_out] = act(x gate^T) * (x up^T)."""
+    M, K = x.shape
+    N = w.shape[0]
+    n_out = N // 2 if fuse_act else N
+    if not gemm_skinny_supported(x, w) or w.shape[1] != K or out.shape != (M, n_out) or out.stride(1) != 1:
+        raise KernelError(f"gemm_skinny: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)} are not taken")
+    if out.dtype not in (torch.bfloat16, torch.float32):
+        raise KernelError("gemm_skinny: out must be bfloat16 or float32")
+    if fuse_act is not None and fuse_act not in ACT_CODES:
+        raise KernelError(f"gemm_skinny: unknown activation {fuse_act!r}")
+    f = _func("gemm_skinny.cu", "lmsf_gemm_skinny",
+              [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, c_int, c_void_p],
+              SKINNY_DEFINES)
+    rc = f(_ptr(out), _ptr(x), _ptr(w), M, N, K, x.stride(0), w.stride(0), out.stride(0),
+           ACT_CODES[fuse_act] if fuse_act else -1, int(out.dtype == torch.float32), _stream())
+    _check(rc, "gemm_skinny.cu", "lmsf_gemm_skinny", SKINNY_DEFINES)
+
+
 # ----------------------------------------------------------------------------- sampling
 
 def sample(out: torch.Tensor, logits: torch.Tensor, temperature: Optional[torch.Tensor] = None,

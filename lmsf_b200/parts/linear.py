@@ -2,8 +2,9 @@
 
 The reference's linear family (core/src/model_executor/layers/linear.rs:28-106, :325-497, :499-728)
 wraps cuBLASLt and merges q, k, v (and gate, up) into one matrix by row ranges; the same merged
-layouts are used here.  bfloat16 products go to the library (cuBLAS through torch.mm), the place
-where the reference calls a library too; float32 products run on this package's own FFMA kernel so
+layouts are used here.  bfloat16 products of more than 16 rows go to the library (cuBLAS through torch.mm),
+the place where the reference calls a library too; products of up to 16 rows (decode steps) run on
+this package's weight-streaming kernel (csrc/gemm_skinny.cu); float32 products run on this package's own FFMA kernel so
 that no reduced-precision mode can slip in and a row's result does not depend on the batch.
 """
 from __future__ import annotations
@@ -16,6 +17,7 @@ from .. import kernels
 from .base import Part, WeightSpec, register_part
 
 _MM_HAS_OUT_DTYPE: Optional[bool] = None
+USE_SKINNY = True     # bfloat16 products of up to 16 rows run on this package's weight-streaming kernel
 
 
 def matmul_tn(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
@@ -26,6 +28,10 @@ def matmul_tn(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype]
         out = torch.empty((x.shape[0], w.shape[0]), dtype=torch.float32, device=x.device)
         kernels.gemm_tn_simt(out, x, w)
         return out if out_dtype == torch.float32 else out.to(out_dtype)
+    if USE_SKINNY and kernels.gemm_skinny_supported(x, w) and out_dtype in (torch.bfloat16, torch.float32):
+        out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype, device=x.device)
+        kernels.gemm_skinny(out, x, w)
+        return out
     if out_dtype == x.dtype:
         return torch.mm(x, w.t())
     if _MM_HAS_OUT_DTYPE is not False:

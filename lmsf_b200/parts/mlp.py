@@ -12,6 +12,7 @@ import torch
 
 from .. import kernels
 from .base import FeedForward, StepContext, WeightSpec, register_part
+from . import linear
 from .linear import matmul_tn
 
 
@@ -29,6 +30,11 @@ class GatedMLP(FeedForward):
                 "down": WeightSpec([(self.hidden_size, self.intermediate_size)])}
 
     def forward(self, ctx: StepContext, h: torch.Tensor) -> torch.Tensor:
+        if linear.USE_SKINNY and kernels.gemm_skinny_supported(h, self.gate_up):
+            # a decode step: gate, up and the activation in one pass over the weights
+            m = torch.empty((h.shape[0], self.intermediate_size), dtype=h.dtype, device=h.device)
+            kernels.gemm_skinny(m, h, self.gate_up, fuse_act=self.activation)
+            return matmul_tn(m, self.down)
         gu = matmul_tn(h, self.gate_up)
         m = torch.empty((h.shape[0], self.intermediate_size), dtype=h.dtype, device=h.device)
         kernels.gated_act(m, gu, self.activation)

@@ -347,3 +347,28 @@ def test_sampling_filters_and_penalties():
                             torch.tensor([0.0, pres], device=d), torch.tensor([0.0, freq], device=d),
                             torch.tensor([1.0, rep], device=d))
     assert torch.equal(ld[0].cpu(), logits[0]) and torch.allclose(ld[1].cpu(), want, rtol=1e-6, atol=1e-6)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 48, 64), (8, 4096, 4096), (5, 1000, 320), (16, 6144, 1024), (13, 28, 14336 // 7)])
+def test_gemm_skinny_against_its_plain_twin(M, N, K):
+    from lmsf_b200 import kernels
+    g = torch.Generator().manual_seed(11)
+    d = dev()
+    x = (torch.randn(M, K, generator=g)).bfloat16().to(d)
+    w = (torch.randn(N, K, generator=g) * 0.1).bfloat16().to(d)
+    ref = torch.empty(M, N, device=d)
+    kernels.gemm_tn_simt(ref, x, w)                     # bfloat16 in, float32 FMA accumulation
+    for odt in (torch.bfloat16, torch.float32):
+        out = torch.empty(M, N, dtype=odt, device=d)
+        kernels.gemm_skinny(out, x, w)
+        tol_ = 1e-4 if odt == torch.float32 else 1e-2
+        assert torch.allclose(out.float(), ref, rtol=tol_, atol=tol_ * ref.abs().max().item())
+    if N % 2 == 0:                                      # gate rows first, up rows second
+        out = torch.empty(M, N // 2, dtype=torch.bfloat16, device=d)
+        kernels.gemm_skinny(out, x, w, fuse_act="silu")
+        gte, up = ref[:, :N // 2], ref[:, N // 2:]
+        want = gte / (1 + torch.exp(-gte)) * up
+        assert torch.allclose(out.float(), want, rtol=1e-2, atol=1e-2 * want.abs().max().item())
+    with pytest.raises(kernels.KernelError):
+        kernels.gemm_skinny(torch.empty(17, N, dtype=torch.bfloat16, device=d),
+                            torch.zeros(17, K, dtype=torch.bfloat16, device=d), w)
