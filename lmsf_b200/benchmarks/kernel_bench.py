@@ -4,7 +4,7 @@
     python -m lmsf_b200.benchmarks.kernel_bench --kernel all
 
 Timing: CUDA events around `--iters` launches after `--warmup` launches; between launches a buffer larger
-than L2 is overwritten, so every launch starts with a cold L2.  Peaks come from MEASURED_PEAKS.json at the
+than L2 is read, so every launch starts with an L2 that holds none of its data (and no dirty lines).  Peaks come from MEASURED_PEAKS.json at the
 repository root when it exists.  Defaults are Llama-3-8B's layer sizes.
 """
 from __future__ import annotations
@@ -39,7 +39,7 @@ class Timer:
         times = []
         for _ in range(iters):
             if self.flush_buf is not None:
-                self.flush_buf.zero_()
+                self.flush_buf.max()           # a READ of 256 MB: L2 ends up full of clean lines of another buffer
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
             fn()

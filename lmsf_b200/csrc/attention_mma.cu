@@ -57,6 +57,8 @@ struct RowState {
 __global__ void __launch_bounds__(kThreads) decode_kernel(DecodeArgs a) {
   extern __shared__ __align__(16) unsigned char smem[];
   const int split = blockIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();
   const int chunks_per_kvh = (a.group + 15) / 16;
   const int kvh = blockIdx.y / chunks_per_kvh, hchunk = blockIdx.y % chunks_per_kvh;
   const int seq = a.seq_ids ? a.seq_ids[blockIdx.z] : blockIdx.z;
@@ -224,6 +226,8 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(DecodeArgs a) {
 
 // out = sum_s part_o[s] 2^(lse_s - max) / sum_s 2^(lse_s - max); one block per (request, head)
 __global__ void decode_merge_kernel(DecodeArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int seq = a.seq_ids ? a.seq_ids[blockIdx.y] : blockIdx.y;
   const int head = blockIdx.x;
   const size_t base = ((size_t)seq * a.n_q_heads + head) * a.n_splits;
@@ -307,13 +311,9 @@ LMSF_API int lmsf_attention_decode(const void* q, long long q_stride, void* out,
     configured = true;
   }
   cudaStream_t s = (cudaStream_t)stream;
-  decode_kernel<<<dim3(n_splits, (unsigned)gy, n_served), kThreads, smem, s>>>(a);
-  int rc = LMSF_LAUNCH_STATUS();
+  int rc = launch_pdl(decode_kernel, dim3(n_splits, (unsigned)gy, n_served), dim3(kThreads), smem, s, a);
   if (rc) return rc;
-  if (n_splits > 1) {
-    decode_merge_kernel<<<dim3(n_q_heads, n_served), HD >= 64 ? 64 : 32, 0, s>>>(a);
-    rc = LMSF_LAUNCH_STATUS();
-  }
+  if (n_splits > 1) rc = launch_pdl(decode_merge_kernel, dim3(n_q_heads, n_served), dim3(HD >= 64 ? 64 : 32), 0, s, a);
   return rc;
 }
 

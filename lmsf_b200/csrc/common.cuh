@@ -12,6 +12,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #if !defined(__CUDA_ARCH__) || __CUDA_ARCH__ >= 1000
 #else
@@ -75,5 +76,40 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 }
 
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// ---- programmatic dependent launch -------------------------------------------------------------------
+// A kernel launched through launch_pdl may start while the kernel before it in the stream is still
+// draining: everything it does before pdl_wait() overlaps that kernel's tail.  Rules for such kernels:
+// before pdl_wait() read only data that no kernel of the step writes (weights, constants) and write
+// nothing to global memory; call pdl_launch_dependents() once the block has started, so that the next
+// kernel may be scheduled as soon as every block of this one is resident.
+// LMSF_PDL=0 in the environment turns the overlap off (plain stream order).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+static inline int pdl_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("LMSF_PDL");
+    v = (e && e[0] == '0') ? 0 : 1;
+  }
+  return v;
+}
+
+template <typename... KArgs, typename... Args>
+static inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled();
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return (int)cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
 
 }  // namespace lmsf

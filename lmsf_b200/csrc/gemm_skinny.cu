@@ -65,7 +65,11 @@ __device__ __forceinline__ void issue_rows(uint32_t stage, const bf16* __restric
       const int c = lane % kLanesPerRow + j * kLanesPerRow;
       const bool okc = ok && k0 + c * 8 < K;          // K is a multiple of 8: a chunk is inside or outside
       const bf16* src = okc ? base + (size_t)r * ld + k0 + c * 8 : base;
+#ifdef LMSF_SKINNY_L2_HINT
+      cp_async_16_l2_256(stage + r * kRowBytes + ((c ^ (r & 7)) << 4), src, okc ? 16 : 0);
+#else
       cp_async_16(stage + r * kRowBytes + ((c ^ (r & 7)) << 4), src, okc ? 16 : 0);
+#endif
     }
   }
 }
@@ -78,22 +82,38 @@ __global__ void __launch_bounds__(kWarps * 32) skinny_kernel(Args a) {
   const int g4 = lane >> 2, t4 = lane & 3;
   const int n0 = blockIdx.x * 16;
   const int n_chunks_total = (a.K + kChunkK - 1) / kChunkK;
+#ifdef LMSF_SKINNY_CONTIGUOUS_K
   const int per_warp = (n_chunks_total + kWarps - 1) / kWarps;
-  const int c_begin = warp * per_warp, c_end = min(n_chunks_total, c_begin + per_warp);
-  const int n_chunks = max(0, c_end - c_begin);
+  const int c_begin = warp * per_warp, c_stride = 1;
+  const int n_chunks = max(0, min(n_chunks_total, c_begin + per_warp) - c_begin);
+#else
+  // chunk c of warp w is chunk w + 4 c of the row: the four warps walk the same kilobyte of every row together
+  const int c_begin = warp, c_stride = kWarps;
+  const int n_chunks = (n_chunks_total - warp + kWarps - 1) / kWarps;
+#endif
   const uint32_t ring = smem_u32(smem) + warp * (STAGES * kStage);
   const int rows_total = GROUPS == 2 ? a.up_offset : a.N;       // rows of one group
 
-  auto issue = [&](int c) {
+  auto issue_w = [&](int c) {
     const uint32_t st = ring + (c % STAGES) * kStage;
-    const int k0 = (c_begin + c) * kChunkK;
+    const int k0 = (c_begin + c * c_stride) * kChunkK;
     issue_rows<16>(st, a.w + (size_t)n0 * a.ldw, a.ldw, rows_total - n0, k0, a.K, lane);
     if (GROUPS == 2)
       issue_rows<16>(st + kStageBytes, a.w + (size_t)(a.up_offset + n0) * a.ldw, a.ldw, rows_total - n0, k0, a.K, lane);
-    issue_rows<8 * NT>(st + GROUPS * kStageBytes, a.x, a.ldx, a.M, k0, a.K, lane);
   };
+  auto issue_x = [&](int c) {
+    const uint32_t st = ring + (c % STAGES) * kStage;
+    issue_rows<8 * NT>(st + GROUPS * kStageBytes, a.x, a.ldx, a.M, (c_begin + c * c_stride) * kChunkK, a.K, lane);
+  };
+  auto issue = [&](int c) { issue_w(c); issue_x(c); };
+  // The weights do not depend on the kernel before this one: their first stages are requested while that
+  // kernel may still be running; x is read only after it has finished.
+  pdl_launch_dependents();
+  for (int s = 0; s < STAGES - 1; ++s)
+    if (s < n_chunks) issue_w(s);
+  pdl_wait();
   for (int s = 0; s < STAGES - 1; ++s) {
-    if (s < n_chunks) issue(s);
+    if (s < n_chunks) issue_x(s);
     cp_async_commit();
   }
 
@@ -185,8 +205,7 @@ static int launch(const Args& a, int rows, cudaStream_t s) {
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  skinny_kernel<NT, GROUPS, STAGES><<<ceil_div(rows, 16), kWarps * 32, smem, s>>>(a);
-  return LMSF_LAUNCH_STATUS();
+  return launch_pdl(skinny_kernel<NT, GROUPS, STAGES>, dim3(ceil_div(rows, 16)), dim3(kWarps * 32), smem, s, a);
 }
 
 #ifndef LMSF_SKINNY_STAGES

@@ -82,6 +82,8 @@ __global__ void add_rmsnorm_vec_kernel(T* __restrict__ h_out, const T* __restric
   const size_t base = (size_t)blockIdx.x * hidden;
   float v[ITERS][8];
   float ss = 0.f;
+  pdl_launch_dependents();
+  pdl_wait();
 #pragma unroll
   for (int it = 0; it < ITERS; ++it) {
     const int i = (it * blockDim.x + threadIdx.x) * 8;
@@ -133,11 +135,11 @@ static int launch(void* h, const void* x, float* res, const void* w, int n, int 
     const int vecs = hidden / 8;
     if (vecs <= 1024) {
       const int threads = ((vecs + 31) / 32) * 32;
-      add_rmsnorm_vec_kernel<T, WT, 1><<<n, threads, 0, s>>>((T*)h, (const T*)x, res, (const WT*)w, hidden, eps, mode);
-    } else {
-      add_rmsnorm_vec_kernel<T, WT, 2><<<n, 1024, 0, s>>>((T*)h, (const T*)x, res, (const WT*)w, hidden, eps, mode);
+      return launch_pdl(add_rmsnorm_vec_kernel<T, WT, 1>, dim3(n), dim3(threads), 0, s, (T*)h, (const T*)x, res,
+                        (const WT*)w, hidden, eps, mode);
     }
-    return LMSF_LAUNCH_STATUS();
+    return launch_pdl(add_rmsnorm_vec_kernel<T, WT, 2>, dim3(n), dim3(1024), 0, s, (T*)h, (const T*)x, res,
+                      (const WT*)w, hidden, eps, mode);
   }
   int threads = hidden >= 4096 ? 512 : (hidden >= 1024 ? 256 : 128);
   const size_t smem = (size_t)hidden * 4;

@@ -107,6 +107,8 @@ template <typename T, int VEC>
 __global__ void rope_cache_vec_kernel(RopeCacheArgs a) {
   extern __shared__ float cs[];  // cos[rot/2], sin[rot/2]
   const int t = blockIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();
   const int pos = a.positions[t];
   const int half = a.inv_freq ? a.rot_dim / 2 : 0;
   for (int i = threadIdx.x; i < half; i += blockDim.x) {
@@ -200,9 +202,8 @@ LMSF_API int lmsf_rope_cache_write(void* q, const void* k, const void* v, long l
     int gy = ceil_div(items > 0 ? items : 1, 128);
     if (gy > 8) gy = 8;
     dim3 grid(n_tokens, gy);
-    if (dtype == LMSF_F32) rope_cache_vec_kernel<float, 4><<<grid, 128, smem, s>>>(a);
-    else rope_cache_vec_kernel<bf16, 8><<<grid, 128, smem, s>>>(a);
-    return LMSF_LAUNCH_STATUS();
+    if (dtype == LMSF_F32) return launch_pdl(rope_cache_vec_kernel<float, 4>, grid, dim3(128), smem, s, a);
+    return launch_pdl(rope_cache_vec_kernel<bf16, 8>, grid, dim3(128), smem, s, a);
   }
   const int work = (n_q_heads + 2 * n_kv_heads) * head_dim / 2;
   const int threads = work >= 1024 ? 256 : (work >= 256 ? 128 : 64);
