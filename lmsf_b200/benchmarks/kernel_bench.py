@@ -89,11 +89,18 @@ def bench_prefill_attention(args, dev, timer, pk):
     n_tiles = (T + 63) // 64
     ts = torch.zeros(n_tiles, dtype=torch.int32, device=dev)
     tq = torch.arange(0, T, 64, dtype=torch.int32, device=dev)
-    fn = lambda: kernels.attention_prefill(out, q, cache, bt, args.block_size, ts, tq, n_tiles, cu, cl,
-                                           1 / math.sqrt(hd), 0, nh, nkv, hd)
+    if args.tc:
+        n_tiles = (T + 127) // 128
+        ts = torch.zeros(n_tiles, dtype=torch.int32, device=dev)
+        tq = torch.arange(0, T, 128, dtype=torch.int32, device=dev)
+        fn = lambda: kernels.attention_prefill_tc(out, q, cache, bt, args.block_size, ts, tq, n_tiles, cu, cl,
+                                                  1 / math.sqrt(hd), 0, nh, nkv, hd)
+    else:
+        fn = lambda: kernels.attention_prefill(out, q, cache, bt, args.block_size, ts, tq, n_tiles, cu, cl,
+                                               1 / math.sqrt(hd), 0, nh, nkv, hd)
     t = timer.run(fn, args.warmup, args.iters)
     flops = 4 * nh * hd * T * T / 2
-    return dict(kernel="prefill_attention", tokens=T, us=t * 1e6, tflops=flops / t / 1e12,
+    return dict(kernel="prefill_attention_tcgen05" if args.tc else "prefill_attention", tokens=T, us=t * 1e6, tflops=flops / t / 1e12,
                 frac_bf16=flops / t / 1e12 / pk["bf16_tflops"])
 
 
@@ -201,6 +208,7 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--tc", action="store_true", help="prefill_attention: the tcgen05 kernel instead of the mma.sync one")
     ap.add_argument("--skinny-defines", default="", help="comma-separated -D constants for gemm_skinny.cu")
     ap.add_argument("--kv-stages", type=int, default=0, help="pipeline depth of the attention kernels (default: the build's)")
     a = ap.parse_args()

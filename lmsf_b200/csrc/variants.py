@@ -6,6 +6,7 @@ from typing import List, Tuple
 VARIANTS = {
     # one build per head size that the tensor-core attention kernels take
     "attention_mma.cu": [(f"LMSF_HEAD_DIM={hd}",) for hd in range(16, 129, 16)],
+    "attention_tc.cu": [("LMSF_HEAD_DIM=64",), ("LMSF_HEAD_DIM=128",)],
 }
 
 

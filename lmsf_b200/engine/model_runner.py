@@ -47,6 +47,7 @@ class _HostBatch:
     max_blocks: List[int]
     n_dec: int
     n_tiles: int
+    n_tiles128: int = 0
 
 
 def _align(n: int, a: int = 4) -> int:
@@ -140,6 +141,8 @@ class ModelRunner:
         dec_ids = [i for i, n in enumerate(q_lens) if n == 1]
         tile_seq = [i for i, n in enumerate(q_lens) if n > 1 for _ in range(0, n, Q_TILE)]
         tile_q0 = [q0 for n in q_lens if n > 1 for q0 in range(0, n, Q_TILE)]
+        tile128_seq = [i for i, n in enumerate(q_lens) if n > 1 for _ in range(0, n, 2 * Q_TILE)]
+        tile128_q0 = [q0 for n in q_lens if n > 1 for q0 in range(0, n, 2 * Q_TILE)]
         n_groups = len(self.storage.groups)
         tables = [[mgr.block_table(e.request_id, g) for e in entries] for g in range(n_groups)]
         max_blocks = [max(static_blocks or 1, max(len(t) for t in tables[g])) for g in range(n_groups)]
@@ -148,7 +151,8 @@ class ModelRunner:
         total = 0
         for name, length in [("token_ids", N), ("positions", N), ("token_seq", N), ("cu_q", S + 1), ("ctx_len", S),
                              ("state_slot", S), ("rows", len(rows)), ("dec_ids", len(dec_ids)),
-                             ("tile_seq", len(tile_seq)), ("tile_q0", len(tile_q0))] + \
+                             ("tile_seq", len(tile_seq)), ("tile_q0", len(tile_q0)), ("tile128_seq", len(tile128_seq)),
+                             ("tile128_q0", len(tile128_q0))] + \
                             [(f"bt{g}", S * max_blocks[g]) for g in range(n_groups)]:
             seg[name] = (total, length)
             total += _align(max(length, 1))
@@ -167,7 +171,8 @@ class ModelRunner:
         put("ctx_len", np.asarray(ctx_lens, dtype=np.int32))
         slots = [mgr.state_slot(e.request_id) for e in entries]
         put("state_slot", np.asarray(slots, dtype=np.int32))
-        for name, values in (("rows", rows), ("dec_ids", dec_ids), ("tile_seq", tile_seq), ("tile_q0", tile_q0)):
+        for name, values in (("rows", rows), ("dec_ids", dec_ids), ("tile_seq", tile_seq), ("tile_q0", tile_q0),
+                             ("tile128_seq", tile128_seq), ("tile128_q0", tile128_q0)):
             if values:
                 put(name, np.asarray(values, dtype=np.int32))
         for g in range(n_groups):
@@ -176,7 +181,7 @@ class ModelRunner:
             for i, t in enumerate(tables[g]):
                 bt[i, :len(t)] = t
         return _HostBatch(pinned, event, total, seg, N, S, q_lens, ctx_lens, slots, max_blocks, len(dec_ids),
-                          len(tile_seq))
+                          len(tile_seq), len(tile128_seq))
 
     def _pinned_buffer(self, n_ints: int):
         """A pinned host buffer from a small ring; a buffer is used again only after the copy that last read it."""
@@ -210,7 +215,8 @@ class ModelRunner:
                           ctx_len=view("ctx_len"), state_slot=view("state_slot"), groups=groups, q_lens=hb.q_lens,
                           ctx_lens=hb.ctx_lens, state_slots=hb.slots, error_flag=self.error_flag,
                           decode_seq_ids=view("dec_ids"), n_decode_seqs=hb.n_dec, q_tile_seq=view("tile_seq"),
-                          q_tile_q0=view("tile_q0"), n_q_tiles=hb.n_tiles)
+                          q_tile_q0=view("tile_q0"), n_q_tiles=hb.n_tiles, q_tile128_seq=view("tile128_seq"),
+                          q_tile128_q0=view("tile128_q0"), n_q_tiles128=hb.n_tiles128)
         ctx.extras["sm_count"] = self.sm_count
         return ctx, view("rows")
 
@@ -281,5 +287,6 @@ class ModelRunner:
         if code:
             self.error_flag.zero_()
             what = {1: "a token id outside the vocabulary reached the embedding",
-                    2: "a token was to be cached at a position that has no page"}.get(code, f"code {code}")
+                    2: "a token was to be cached at a position that has no page",
+                    3: "a tensor-core attention block gave up waiting for its own products"}.get(code, f"code {code}")
             raise StepError(f"the device reported an error during the step: {what}")

@@ -404,3 +404,31 @@ def attention_prefill(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, b
            _i32(tile_q0, "tile_q0"), n_tiles, _i32(cu_q, "cu_q"), _i32(ctx_len, "ctx_len"), float(scale),
            int(window or 0), n_q_heads, head_dim, _stream())
     _check(rc, "attention_mma.cu", "lmsf_attention_mma", d)
+
+
+# ----------------------------------------------------------------------------- tcgen05 prefill attention
+
+TC_HEAD_DIMS = (64, 128)
+TC_Q_TILE = 128
+
+
+def tc_attention_supported(dtype: torch.dtype, head_dim: int) -> bool:
+    return dtype == torch.bfloat16 and head_dim in TC_HEAD_DIMS
+
+
+def attention_prefill_tc(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
+                         block_size: int, tile_seq: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int, cu_q: torch.Tensor,
+                         ctx_len: torch.Tensor, scale: float, window: int, n_q_heads: int, n_kv_heads: int, head_dim: int,
+                         error_flag: Optional[torch.Tensor] = None):
+    """Attention of prompt portions on tcgen05 tensor cores (head size 64 or 128).  Tile i covers the query
+    tokens tile_q0[i] .. tile_q0[i] + 127 (counted inside the portion) of request tile_seq[i]."""
+    _check_paged(q, out, cache, n_q_heads, n_kv_heads, head_dim, block_size, "attention_prefill_tc")
+    d = _mma_defines(head_dim)[:1]
+    f = _func("attention_tc.cu", "lmsf_attention_prefill_tc",
+              [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_void_p, c_int,
+               c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_void_p, c_void_p], d)
+    rc = f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache), cache.stride(0), block_size, n_kv_heads,
+           _i32(block_table, "block_table"), block_table.shape[1], _i32(tile_seq, "tile_seq"),
+           _i32(tile_q0, "tile_q0"), n_tiles, _i32(cu_q, "cu_q"), _i32(ctx_len, "ctx_len"), float(scale),
+           int(window or 0), n_q_heads, head_dim, _i32(error_flag, "error_flag"), _stream())
+    _check(rc, "attention_tc.cu", "lmsf_attention_tc", d)

@@ -19,6 +19,9 @@ from .base import KVCacheSpec, LayerCache, Mixer, PositionEncoding, StepContext,
 from .linear import matmul_tn
 
 
+USE_TC_PREFILL = True     # head sizes 64 and 128: prompt portions run on the tcgen05 kernel (csrc/attention_tc.cu)
+
+
 @register_part("mixer", "paged_attention")
 class PagedAttention(Mixer):
     graph_safe = True      # launch geometry depends on the batch's size only: a decode step can be replayed
@@ -76,7 +79,8 @@ class PagedAttention(Mixer):
 
     def attend(self, ctx: StepContext, out: torch.Tensor, q: torch.Tensor, kv: torch.Tensor, group) -> None:
         """bfloat16 with a head size up to 128: single tokens go to the split-key decode kernel, longer portions
-        to the tiled prefill kernel (both on the tensor cores).  Everything else, float32 included, runs on the
+        to a tiled prefill kernel (tcgen05 with accumulators in tensor memory for head sizes 64 and 128,
+        mma.sync otherwise).  Everything else, float32 included, runs on the
         generic kernel, which is also their plain twin."""
         if kernels.mma_attention_supported(q.dtype, self.head_dim) and not ctx.extras.get("force_generic_attention"):
             if ctx.n_decode_seqs:
@@ -99,7 +103,12 @@ class PagedAttention(Mixer):
                                          None if all_decode else ctx.decode_seq_ids, ctx.n_decode_seqs, ctx.cu_q,
                                          ctx.ctx_len, self.scale, self.window or 0, self.num_heads,
                                          self.num_kv_heads, self.head_dim, splits, scratch if need else None)
-            if ctx.n_q_tiles:
+            if ctx.n_q_tiles and USE_TC_PREFILL and kernels.tc_attention_supported(q.dtype, self.head_dim):
+                kernels.attention_prefill_tc(out, q, kv, group.block_table, group.block_size, ctx.q_tile128_seq,
+                                             ctx.q_tile128_q0, ctx.n_q_tiles128, ctx.cu_q, ctx.ctx_len, self.scale,
+                                             self.window or 0, self.num_heads, self.num_kv_heads, self.head_dim,
+                                             ctx.error_flag)
+            elif ctx.n_q_tiles:
                 kernels.attention_prefill(out, q, kv, group.block_table, group.block_size, ctx.q_tile_seq,
                                           ctx.q_tile_q0, ctx.n_q_tiles, ctx.cu_q, ctx.ctx_len, self.scale,
                                           self.window or 0, self.num_heads, self.num_kv_heads, self.head_dim)

@@ -128,6 +128,9 @@ class StepContext:
     q_tile_seq: Optional[torch.Tensor] = None          # int32: request of each 64-token tile of a longer portion
     q_tile_q0: Optional[torch.Tensor] = None           # int32: first token of the tile inside its portion
     n_q_tiles: int = 0
+    q_tile128_seq: Optional[torch.Tensor] = None       # the same in tiles of 128 tokens
+    q_tile128_q0: Optional[torch.Tensor] = None
+    n_q_tiles128: int = 0
     extras: Dict[str, Any] = field(default_factory=dict)   # per-step scratch that kernels share across layers
 
     @property

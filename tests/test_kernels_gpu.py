@@ -372,3 +372,35 @@ def test_gemm_skinny_against_its_plain_twin(M, N, K):
     with pytest.raises(kernels.KernelError):
         kernels.gemm_skinny(torch.empty(17, N, dtype=torch.bfloat16, device=d),
                             torch.zeros(17, K, dtype=torch.bfloat16, device=d), w)
+
+
+@pytest.mark.parametrize("nh,nkv,hd,bs,window", [(8, 2, 128, 16, 0), (4, 4, 64, 16, 0), (6, 1, 128, 8, 0), (4, 2, 64, 32, 90),
+                                               (2, 1, 128, 16, 300)])
+def test_attention_tcgen05_prefill(nh, nkv, hd, bs, window):
+    """The tcgen05 prefill kernel against float64 and against its mma.sync twin."""
+    from lmsf_b200 import kernels
+    assert kernels.tc_attention_supported(torch.bfloat16, hd)
+    # a portion in the middle of a long prompt, a whole prompt, a 2-token portion, a portion of exactly one tile, a long one
+    ctx_lens, q_lens = [700, 130, 65, 128, 1100], [201, 130, 2, 128, 1000]
+    q, cache, bt, token_seq, positions, ks, vs = _paged_setup("bfloat16", nh, nkv, hd, bs, ctx_lens, q_lens, 13, sharp=True)
+    scale = 1.0 / math.sqrt(hd)
+    ref = _attention_reference(q.float(), ks, vs, token_seq, positions, nh, nkv, hd, scale, window)
+    d = dev()
+    qd, cd, btd = q.to(d), cache.to(d), bt.to(d)
+    cu = torch.tensor([0] + list(np.cumsum(q_lens)), dtype=torch.int32, device=d)
+    cl = torch.tensor(ctx_lens, dtype=torch.int32, device=d)
+    tiles = [(i, q0) for i, n in enumerate(q_lens) for q0 in range(0, n, 128)]
+    flag = torch.zeros(1, dtype=torch.int32, device=d)
+    out = torch.zeros(q.shape, dtype=torch.bfloat16, device=d)
+    kernels.attention_prefill_tc(out, qd, cd, btd, bs, torch.tensor([t[0] for t in tiles], dtype=torch.int32, device=d),
+                                 torch.tensor([t[1] for t in tiles], dtype=torch.int32, device=d), len(tiles), cu, cl,
+                                 scale, window, nh, nkv, hd, flag)
+    assert flag.item() == 0
+    err = (out.float().cpu().double() - ref).abs()
+    assert err.max().item() <= 2e-2 * ref.abs().max().item(), (err.max().item(), int(err.argmax()) // (nh * hd))
+    tiles64 = [(i, q0) for i, n in enumerate(q_lens) for q0 in range(0, n, 64)]
+    out2 = torch.zeros_like(out)
+    kernels.attention_prefill(out2, qd, cd, btd, bs, torch.tensor([t[0] for t in tiles64], dtype=torch.int32, device=d),
+                              torch.tensor([t[1] for t in tiles64], dtype=torch.int32, device=d), len(tiles64), cu, cl,
+                              scale, window, nh, nkv, hd)
+    assert (out2.float() - out.float()).abs().max().item() <= 2e-2 * ref.abs().max().item()
