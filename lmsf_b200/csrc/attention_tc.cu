@@ -7,7 +7,8 @@
 //
 // One block of 128 threads serves 128 query tokens of one head.  Per tile of 64 keys:
 //   1. k and v rows are gathered from their pages into shared memory with cp.async, in the 128-byte
-//      swizzled layout that the tensor core reads (k: K-major, v: MN-major; two tiles in flight);
+//      swizzled layout that the tensor core reads (k: K-major, v: MN-major); the next tile's rows are
+//      requested while this tile's scores are computed;
 //   2. one thread issues S = Q K^T (M 128, N 64, K head size) into tensor memory and commits to an mbarrier;
 //   3. every thread owns one query row: it reads its 64 scores with tcgen05.ld, masks, updates the running
 //      maximum (the accumulator is rescaled only when the maximum grew by more than 2^8, which keeps the
@@ -106,6 +107,11 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
                  "r"(r[28]),"r"(r[29]),"r"(r[30]),"r"(r[31]) : "memory");
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
+__device__ __forceinline__ float ex2_approx(float x) {      // 2^x, 0 for -inf
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -150,7 +156,9 @@ __global__ void __launch_bounds__(128) prefill_tc_kernel(Args a) {
   const uint32_t mbar_s = smem_u32(&mbar_s_mem), mbar_o = smem_u32(&mbar_o_mem);
   const int tid = threadIdx.x, warp = tid >> 5;
 
-  const int seq = a.tile_seq[blockIdx.x], q0 = a.tile_q0[blockIdx.x];
+  // the tile list is walked backwards: the last tiles of a portion see the most keys and should start first
+  const int tile = gridDim.x - 1 - blockIdx.x;
+  const int seq = a.tile_seq[tile], q0 = a.tile_q0[tile];
   const int head = blockIdx.y, kvh = head / a.group;
   const int tok0 = a.cu_q[seq], n = a.cu_q[seq + 1] - tok0, ctx = a.ctx_len[seq];
   const int start = ctx - n;
@@ -203,18 +211,12 @@ __global__ void __launch_bounds__(128) prefill_tc_kernel(Args a) {
   for (int j = 0; j < n_tiles; ++j) {
     const uint32_t stage = sStage0 + (j & 1) * kStageBytes;
     const uint32_t sK = stage, sV = stage + kKSlot, sP = stage;    // P takes the k tile's place once S is done
-    // (a) the product before this one has finished: O may be touched, the other stage may be overwritten
-    if (j > 0 && !mbar_wait(mbar_o, (uint32_t)((j - 1) & 1))) failed = true;
-    // (b) next tile's loads
-    if (j + 1 < n_tiles)
-      load_kv_tile(sStage0 + ((j + 1) & 1) * kStageBytes, a.kv, table, kvh, (tile_begin + j + 1) * BN, lo, hi);
-    cp_async_commit();
-    // (c) this tile has landed
-    cp_async_wait<1>();
+    // (a) this tile (and, the first time, Q) has landed
+    cp_async_wait<0>();
     fence_async_smem();
     tc_fence_before();
     if (__syncthreads_or(failed)) { failed = true; break; }
-    // (d) S = Q K^T
+    // (b) S = Q K^T; it runs behind the previous tile's O += P V on the tensor pipe
     if (tid == 0) {
       tc_fence_after();
       constexpr uint32_t idesc = instr_desc(BM, BN, 0);
@@ -225,6 +227,12 @@ __global__ void __launch_bounds__(128) prefill_tc_kernel(Args a) {
       }
       umma_commit(mbar_s);
     }
+    // (c) the product before this one has finished: O may be touched, the other stage may be overwritten
+    if (j > 0 && !mbar_wait(mbar_o, (uint32_t)((j - 1) & 1))) failed = true;
+    // (d) next tile's loads, while S is being computed
+    if (j + 1 < n_tiles)
+      load_kv_tile(sStage0 + ((j + 1) & 1) * kStageBytes, a.kv, table, kvh, (tile_begin + j + 1) * BN, lo, hi);
+    cp_async_commit();
     // (e) softmax of this thread's row
     if (!mbar_wait(mbar_s, (uint32_t)(j & 1))) failed = true;
     tc_fence_after();
@@ -239,13 +247,20 @@ __global__ void __launch_bounds__(128) prefill_tc_kernel(Args a) {
       for (int i = 0; i < 32; ++i) s[32 + i] = __uint_as_float(r[i]);
     }
     const int key0 = (tile_begin + j) * BN;
-    float mx = -INFINITY;
+    // Only tiles that reach past some row's position (the diagonal) or before its window need the mask;
+    // the test is the same for the whole block.
+    const bool need_mask = key0 + BN - 1 > start + q0 || (a.window > 0 && key0 < start + q0 + rows_valid - a.window);
+    if (need_mask) {
 #pragma unroll
-    for (int i = 0; i < BN; ++i) {
-      const int key = key0 + i;
-      s[i] = (key <= pos && key >= row_lo) ? s[i] * sl2 : -INFINITY;
-      mx = fmaxf(mx, s[i]);
+      for (int i = 0; i < BN; ++i) {
+        const int key = key0 + i;
+        if (key > pos || key < row_lo) s[i] = -INFINITY;
+      }
     }
+    float mx = s[0];
+#pragma unroll
+    for (int i = 1; i < BN; ++i) mx = fmaxf(mx, s[i]);
+    mx *= sl2;                                                // scores enter the exponent as s * scale * log2(e)
     float alpha = 1.f;
     const bool grow = mx > m_run + kRescaleThreshold;         // also true for the first keys a row sees
     if (grow) {
@@ -263,21 +278,24 @@ __global__ void __launch_bounds__(128) prefill_tc_kernel(Args a) {
         tmem_st32(t_row + kOCol + c0, r);
       }
     }
-    const float m_use = m_run == -INFINITY ? 0.f : m_run;
+    const float neg_m = m_run == -INFINITY ? 0.f : -m_run;
     {
       const int row = tid;
+      float l0 = 0.f, l1 = 0.f;
 #pragma unroll
       for (int c = 0; c < BN / 8; ++c) {
         uint32_t w[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const float p0 = exp2f(s[c * 8 + 2 * e] - m_use), p1 = exp2f(s[c * 8 + 2 * e + 1] - m_use);
-          l_run += p0 + p1;
+          const float p0 = ex2_approx(fmaf(s[c * 8 + 2 * e], sl2, neg_m)), p1 = ex2_approx(fmaf(s[c * 8 + 2 * e + 1], sl2, neg_m));
+          l0 += p0;
+          l1 += p1;
           w[e] = pack_bf16(p0, p1);
         }
         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sP + row * 128 + ((c ^ (row & 7)) << 4)),
                      "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
       }
+      l_run += l0 + l1;
     }
     fence_async_smem();
     tc_fence_before();
