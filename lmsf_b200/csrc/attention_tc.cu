@@ -31,6 +31,14 @@ namespace tc {
 
 using namespace lmsf::fa;
 
+#ifdef LMSF_TC_TIMING
+// Development aid: thread 127 of every block adds the cycles it spent in each phase of the loop.
+__device__ long long* g_timing = nullptr;
+#define LMSF_T(i) do { if (tid == 127) { const long long now_ = clock64(); tacc[i] += now_ - tlast; tlast = now_; } } while (0)
+#else
+#define LMSF_T(i) do {} while (0)
+#endif
+
 constexpr int HD = LMSF_HEAD_DIM;
 static_assert(HD == 64 || HD == 128, "the tcgen05 attention kernel takes head sizes 64 and 128");
 constexpr int BM = 128;                    // query rows per block
@@ -118,8 +126,22 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 
 // k and v of keys [key0, key0 + 64) of kv head kvh into a stage: [64-wide block of the head][key][128 bytes],
 // 16-byte chunk c of a row at chunk c ^ (key & 7).  Keys outside [lo, hi) or without a page are zero-filled.
+constexpr int kNoPrefetch = -2;    // `page_hint` of load_kv_tile: look the page up now
+
+// The page that holds the first row this thread copies of tile [key0, key0 + 64), or -1.  With a block size of
+// at least the rows a thread copies (and both powers of two) all of a thread's rows of a tile share that page.
+__device__ __forceinline__ int tile_page(const PagedKV& kv, const int* __restrict__ table, int key0, int lo, int hi) {
+  constexpr int kChunks = HD / 8;
+  constexpr int kRowsPerThread = BN * kChunks / 128;
+  const int key = key0 + (threadIdx.x / kChunks) * kRowsPerThread;
+  // a row range that straddles lo or hi still lies in one page; rows outside [lo, hi) are zero-filled anyway
+  const int probe = min(max(key, lo), hi - 1);
+  if (probe < key || probe >= key + kRowsPerThread) return -1;
+  return table[probe >> kv.block_shift];
+}
+
 __device__ __forceinline__ void load_kv_tile(uint32_t stage, const PagedKV& kv, const int* __restrict__ table, int kvh,
-                                             int key0, int lo, int hi) {
+                                             int key0, int lo, int hi, int page_hint) {
   constexpr int kChunks = HD / 8;                       // 16-byte chunks per row
   constexpr int kRowsPerThread = BN * kChunks / 128;    // consecutive rows per thread
   const size_t v_off = (size_t)kv.n_kv_heads * kv.block_size * HD;
@@ -129,15 +151,34 @@ __device__ __forceinline__ void load_kv_tile(uint32_t stage, const PagedKV& kv, 
   const uint32_t col = (c / 8) * (BN * 128);
   const bf16* page_ptr = nullptr;
   bool have_page = false;
+  if (page_hint != kNoPrefetch) {
+    page_ptr = page_hint >= 0 ? kv.cache + (size_t)page_hint * kv.page_stride + head_off + c * 8 : nullptr;
+    have_page = true;
+    if (key0 >= lo && key0 + BN <= hi && page_ptr != nullptr) {
+      // the common case: every key of the tile is wanted and this thread's rows sit in one page, one after
+      // the other: the addresses are the first one plus constants
+      const bf16* src = page_ptr + (size_t)((key0 + row0) & mask) * HD;
+      const uint32_t dst = stage + col + row0 * 128;                   // row0 is a multiple of 8 or kRowsPerThread <= 8
+#pragma unroll
+      for (int it = 0; it < kRowsPerThread; ++it) {
+        const uint32_t d = dst + it * 128 + (((c & 7) ^ ((row0 + it) & 7)) << 4);
+        cp_async_16(d, src + it * HD, 16);
+        cp_async_16(d + kKSlot, src + v_off + it * HD, 16);
+      }
+      return;
+    }
+  }
 #pragma unroll
   for (int it = 0; it < kRowsPerThread; ++it) {
     const int row = row0 + it, key = key0 + row, slot = key & mask;
     const bool in_range = key >= lo && key < hi;
-    if (slot == 0) have_page = false;
-    if (in_range && !have_page) {
-      const int page = table[key >> kv.block_shift];
-      page_ptr = page >= 0 ? kv.cache + (size_t)page * kv.page_stride + head_off + c * 8 : nullptr;
-      have_page = true;
+    if (page_hint == kNoPrefetch) {
+      if (slot == 0) have_page = false;
+      if (in_range && !have_page) {
+        const int page = table[key >> kv.block_shift];
+        page_ptr = page >= 0 ? kv.cache + (size_t)page * kv.page_stride + head_off + c * 8 : nullptr;
+        have_page = true;
+      }
     }
     const bool ok = in_range && page_ptr != nullptr;
     const bf16* src = ok ? page_ptr + (size_t)slot * HD : kv.cache;
@@ -195,8 +236,13 @@ __global__ void __launch_bounds__(128) prefill_tc_kernel(Args a) {
       cp_async_16(sQ + (c / 8) * (BM * 128) + row * 128 + (((c & 7) ^ (row & 7)) << 4), src, ok ? 16 : 0);
     }
   }
-  load_kv_tile(sStage0, a.kv, table, kvh, tile_begin * BN, lo, hi);
+  load_kv_tile(sStage0, a.kv, table, kvh, tile_begin * BN, lo, hi, kNoPrefetch);
   cp_async_commit();
+  // Page numbers are looked up one tile ahead of the copies that use them, so that the copies of the loop
+  // never wait on the block table.
+  constexpr int kRowsPerThread = BN * (HD / 8) / 128;
+  const bool prefetch_pages = a.kv.block_size >= kRowsPerThread;
+  int next_page = (prefetch_pages && n_tiles > 1) ? tile_page(a.kv, table, (tile_begin + 1) * BN, lo, hi) : kNoPrefetch;
 
   tc_fence_before();
   __syncthreads();
@@ -208,7 +254,12 @@ __global__ void __launch_bounds__(128) prefill_tc_kernel(Args a) {
   const float sl2 = a.scale * kLog2e;
   bool failed = false;
 
+#ifdef LMSF_TC_TIMING
+  long long tacc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  long long tlast = clock64();
+#endif
   for (int j = 0; j < n_tiles; ++j) {
+    LMSF_T(7);
     const uint32_t stage = sStage0 + (j & 1) * kStageBytes;
     const uint32_t sK = stage, sV = stage + kKSlot, sP = stage;    // P takes the k tile's place once S is done
     // (a) this tile (and, the first time, Q) has landed
@@ -216,6 +267,7 @@ __global__ void __launch_bounds__(128) prefill_tc_kernel(Args a) {
     fence_async_smem();
     tc_fence_before();
     if (__syncthreads_or(failed)) { failed = true; break; }
+    LMSF_T(0);
     // (b) S = Q K^T; it runs behind the previous tile's O += P V on the tensor pipe
     if (tid == 0) {
       tc_fence_after();
@@ -229,13 +281,17 @@ __global__ void __launch_bounds__(128) prefill_tc_kernel(Args a) {
     }
     // (c) the product before this one has finished: O may be touched, the other stage may be overwritten
     if (j > 0 && !mbar_wait(mbar_o, (uint32_t)((j - 1) & 1))) failed = true;
+    LMSF_T(1);
     // (d) next tile's loads, while S is being computed
     if (j + 1 < n_tiles)
-      load_kv_tile(sStage0 + ((j + 1) & 1) * kStageBytes, a.kv, table, kvh, (tile_begin + j + 1) * BN, lo, hi);
+      load_kv_tile(sStage0 + ((j + 1) & 1) * kStageBytes, a.kv, table, kvh, (tile_begin + j + 1) * BN, lo, hi, next_page);
     cp_async_commit();
+    if (prefetch_pages && j + 2 < n_tiles) next_page = tile_page(a.kv, table, (tile_begin + j + 2) * BN, lo, hi);
+    LMSF_T(2);
     // (e) softmax of this thread's row
     if (!mbar_wait(mbar_s, (uint32_t)(j & 1))) failed = true;
     tc_fence_after();
+    LMSF_T(3);
     float s[BN];
     {
       uint32_t r[32];
@@ -246,6 +302,7 @@ __global__ void __launch_bounds__(128) prefill_tc_kernel(Args a) {
 #pragma unroll
       for (int i = 0; i < 32; ++i) s[32 + i] = __uint_as_float(r[i]);
     }
+    LMSF_T(4);
     const int key0 = (tile_begin + j) * BN;
     // Only tiles that reach past some row's position (the diagonal) or before its window need the mask;
     // the test is the same for the whole block.
@@ -297,9 +354,11 @@ __global__ void __launch_bounds__(128) prefill_tc_kernel(Args a) {
       }
       l_run += l0 + l1;
     }
+    LMSF_T(5);
     fence_async_smem();
     tc_fence_before();
     if (__syncthreads_or(failed)) { failed = true; break; }
+    LMSF_T(6);
     // (f) O += P V
     if (tid == 0) {
       tc_fence_after();
@@ -312,6 +371,13 @@ __global__ void __launch_bounds__(128) prefill_tc_kernel(Args a) {
     }
   }
   cp_async_wait<0>();
+#ifdef LMSF_TC_TIMING
+  if (tid == 127 && g_timing) {
+    long long* t = g_timing + ((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 9;
+    for (int i = 0; i < 8; ++i) t[i] = tacc[i];
+    t[8] = n_tiles;
+  }
+#endif
 
   if (!failed && n_tiles > 0 && !mbar_wait(mbar_o, (uint32_t)((n_tiles - 1) & 1))) failed = true;
   failed = __syncthreads_or(failed);
@@ -346,6 +412,12 @@ __global__ void __launch_bounds__(128) prefill_tc_kernel(Args a) {
 }  // namespace lmsf
 
 LMSF_API int lmsf_attention_tc_head_dim() { return LMSF_HEAD_DIM; }
+
+#ifdef LMSF_TC_TIMING
+LMSF_API int lmsf_attention_tc_set_timing(long long* buf) {
+  return (int)cudaMemcpyToSymbol(lmsf::tc::g_timing, &buf, sizeof(buf));
+}
+#endif
 
 // tile_seq / tile_q0: one entry per 128 query tokens of each portion.  q and out rows must be 16-byte aligned.
 LMSF_API int lmsf_attention_prefill_tc(const void* q, long long q_stride, void* out, long long out_stride,
