@@ -8,8 +8,8 @@
 //
 // Shape of the kernel: the weight rows are the M side of mma.sync m16n8k16 (16 output features per
 // block), the tokens are its N side (8 per tile).  The 4 warps of a block split K among themselves; each
-// warp streams its 16 x K/4 slice of W through a private ring of cp.async stages (16 rows x 128 k, each row
-// 256 contiguous bytes of memory, swizzled in 16-byte chunks, read back with ldmatrix) and needs no block-wide barrier until the end,
+// warp streams its 16 x K/4 slice of W through a private ring of cp.async stages (16 rows x 64 k, each row
+// 128 contiguous bytes of memory, swizzled in 16-byte chunks, read back with ldmatrix) and needs no block-wide barrier until the end,
 // where the four partial sums are added in a fixed order.  The matching 64 k of x travel in the same
 // stages (8 or 16 rows), so no load of the inner loop waits on anything but its stage.
 #include "attention_mma.cuh"   // cp.async, ldmatrix and mma helpers
@@ -23,7 +23,7 @@ using namespace lmsf::fa;
 
 constexpr int kWarps = 4;
 #ifndef LMSF_SKINNY_CH
-#define LMSF_SKINNY_CH 2
+#define LMSF_SKINNY_CH 1
 #endif
 constexpr int CH = LMSF_SKINNY_CH;          // a stage holds 64 * CH values of k per row
 constexpr int kChunkK = 64 * CH;            // k per stage
@@ -212,7 +212,10 @@ static int launch(const Args& a, int rows, cudaStream_t s) {
 #define LMSF_SKINNY_STAGES (CH == 1 ? 6 : (CH == 2 ? 4 : 3))
 #endif
 constexpr int kStagesPlain = LMSF_SKINNY_STAGES;
-constexpr int kStagesFused = CH == 1 ? 3 : (CH == 2 ? 3 : 2);
+#ifndef LMSF_SKINNY_STAGES_FUSED
+#define LMSF_SKINNY_STAGES_FUSED (CH == 1 ? 3 : 2)
+#endif
+constexpr int kStagesFused = LMSF_SKINNY_STAGES_FUSED;
 
 }  // namespace skinny
 }  // namespace lmsf
