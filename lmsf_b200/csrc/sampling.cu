@@ -40,41 +40,71 @@ __device__ __forceinline__ Best better(Best a, Best b) {
   return a;
 }
 
-// One block per row.  temperature < 1e-5 selects greedy (core/src/common/sampling_params.rs:156-164).
-__global__ void sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long long row_stride, int vocab,
-                              const float* __restrict__ temperature, const unsigned long long* __restrict__ seed,
-                              const int* __restrict__ step) {
-  __shared__ Best sh[32];
-  const int r = blockIdx.x;
-  const float* row = logits + (size_t)r * row_stride;
-  const float T = temperature ? temperature[r] : 0.f;
-  const bool greedy = T < 1e-5f;
-  const uint32_t slo = seed ? (uint32_t)(seed[r] & 0xffffffffull) : 0u, shi = seed ? (uint32_t)(seed[r] >> 32) : 0u;
-  const uint32_t st = step ? (uint32_t)step[r] : 0u;
-  Best b{-INFINITY, 0x7fffffff};
-  for (int v = threadIdx.x; v < vocab; v += blockDim.x) {
-    const float x = row[v];
-    if (x != x) continue;  // a NaN never wins
-    double s = (double)x;
-    if (!greedy) s = s / (double)T + neg_log_exponential(slo, shi, st, (uint32_t)v);
-    b = better(b, Best{s, v});
-  }
+__device__ __forceinline__ Best block_best(Best b, Best* sh) {
   for (int o = 16; o > 0; o >>= 1) {
     Best other{__shfl_xor_sync(0xffffffffu, b.score, o), __shfl_xor_sync(0xffffffffu, b.index, o)};
     b = better(b, other);
   }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __syncthreads();
   if (lane == 0) sh[warp] = b;
   __syncthreads();
-  if (warp == 0) {
-    const int nw = blockDim.x >> 5;
-    b = lane < nw ? sh[lane] : Best{-INFINITY, 0x7fffffff};
-    for (int o = 16; o > 0; o >>= 1) {
-      Best other{__shfl_xor_sync(0xffffffffu, b.score, o), __shfl_xor_sync(0xffffffffu, b.index, o)};
-      b = better(b, other);
-    }
-    if (lane == 0) out[r] = b.index == 0x7fffffff ? 0 : b.index;
+  const int nw = blockDim.x >> 5;
+  b = lane < nw ? sh[lane] : Best{-INFINITY, 0x7fffffff};
+  for (int o = 16; o > 0; o >>= 1) {
+    Best other{__shfl_xor_sync(0xffffffffu, b.score, o), __shfl_xor_sync(0xffffffffu, b.index, o)};
+    b = better(b, other);
   }
+  return b;      // valid in warp 0
+}
+
+// gridDim = (rows, parts): block (r, p) scans its share of row r and leaves its best in partial[r][p];
+// with parts == 1 it writes out[r] itself.  temperature < 1e-5 selects greedy
+// (core/src/common/sampling_params.rs:156-164), which compares the float32 logits as they are.
+__global__ void sample_kernel(int* __restrict__ out, Best* __restrict__ partial, const float* __restrict__ logits,
+                              long long row_stride, int vocab, const float* __restrict__ temperature,
+                              const unsigned long long* __restrict__ seed, const int* __restrict__ step) {
+  __shared__ Best sh[32];
+  const int r = blockIdx.x;
+  const float* row = logits + (size_t)r * row_stride;
+  const float T = temperature ? temperature[r] : 0.f;
+  const bool greedy = T < 1e-5f;
+  const int per = (vocab + gridDim.y - 1) / gridDim.y;
+  const int v0 = blockIdx.y * per, v1 = min(vocab, v0 + per);
+  Best b{-INFINITY, 0x7fffffff};
+  if (greedy) {
+    float best = -INFINITY;
+    int arg = 0x7fffffff;
+    for (int v = v0 + threadIdx.x; v < v1; v += blockDim.x) {
+      const float x = row[v];
+      if (x > best) { best = x; arg = v; }      // ascending v per thread: the first of equal values stays
+    }
+    b = Best{(double)best, arg};
+  } else {
+    const uint32_t slo = (uint32_t)(seed[r] & 0xffffffffull), shi = (uint32_t)(seed[r] >> 32);
+    const uint32_t st = step ? (uint32_t)step[r] : 0u;
+    for (int v = v0 + threadIdx.x; v < v1; v += blockDim.x) {
+      const float x = row[v];
+      if (x != x) continue;  // a NaN never wins
+      b = better(b, Best{(double)x / (double)T + neg_log_exponential(slo, shi, st, (uint32_t)v), v});
+    }
+  }
+  b = block_best(b, sh);
+  if (threadIdx.x == 0) {
+    if (gridDim.y == 1) out[r] = b.index == 0x7fffffff ? 0 : b.index;
+    else partial[(size_t)r * gridDim.y + blockIdx.y] = b;
+  }
+}
+
+__global__ void sample_final_kernel(int* __restrict__ out, const Best* __restrict__ partial, int parts) {
+  const int r = blockIdx.x;
+  Best b{-INFINITY, 0x7fffffff};
+  if ((int)threadIdx.x < parts) b = partial[(size_t)r * parts + threadIdx.x];
+  for (int o = 16; o > 0; o >>= 1) {
+    Best other{__shfl_xor_sync(0xffffffffu, b.score, o), __shfl_xor_sync(0xffffffffu, b.index, o)};
+    b = better(b, other);
+  }
+  if (threadIdx.x == 0) out[r] = b.index == 0x7fffffff ? 0 : b.index;
 }
 
 // ---------------------------------------------------------------------------------------------- penalties
@@ -223,14 +253,23 @@ __global__ void sample_filtered_kernel(int* __restrict__ out, const float* __res
 }  // namespace lmsf
 
 // logits: [rows, vocab] float32; temperature [rows] float32, seed [rows] uint64, step [rows] int32
-// (all three may be null: greedy).  out: [rows] int32.
+// (all three may be null: greedy).  out: [rows] int32.  A row is scanned by `parts` blocks (1..32); with
+// parts > 1, scratch must hold rows * parts * 16 bytes.
 LMSF_API int lmsf_sample(int* out, const float* logits, long long row_stride, int rows, int vocab,
-                         const float* temperature, const unsigned long long* seed, const int* step, void* stream) {
+                         const float* temperature, const unsigned long long* seed, const int* step, int parts,
+                         void* scratch, void* stream) {
   using namespace lmsf;
   if (rows <= 0) return 0;
   if (vocab <= 0 || row_stride < vocab) LMSF_REFUSE("sample: vocab=%d, row_stride=%lld", vocab, row_stride);
-  const int threads = vocab >= 8192 ? 1024 : 256;
-  sample_kernel<<<rows, threads, 0, (cudaStream_t)stream>>>(out, logits, row_stride, vocab, temperature, seed, step);
+  if (parts < 1 || parts > 32) LMSF_REFUSE("sample: parts=%d must be between 1 and 32", parts);
+  if (parts > 1 && !scratch) LMSF_REFUSE("sample: %d parts need scratch memory", parts);
+  if (temperature && !seed) LMSF_REFUSE("sample: temperature sampling needs seeds");
+  const int threads = vocab / parts >= 4096 ? 512 : 256;
+  cudaStream_t s = (cudaStream_t)stream;
+  sample_kernel<<<dim3(rows, parts), threads, 0, s>>>(out, (Best*)scratch, logits, row_stride, vocab, temperature, seed, step);
+  int rc = LMSF_LAUNCH_STATUS();
+  if (rc || parts == 1) return rc;
+  sample_final_kernel<<<rows, 32, 0, s>>>(out, (const Best*)scratch, parts);
   return LMSF_LAUNCH_STATUS();
 }
 

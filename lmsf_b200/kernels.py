@@ -268,11 +268,15 @@ def sample(out: torch.Tensor, logits: torch.Tensor, temperature: Optional[torch.
         raise KernelError("sample: temperature must be float32 [rows]")
     if seed is not None and (seed.dtype != torch.int64 or seed.shape != (rows,)):
         raise KernelError("sample: seed must be int64 [rows]")
+    parts = 1 if vocab < 16384 else min(32, max(1, vocab // 8192))
+    scratch = torch.empty(rows * parts * 2, dtype=torch.float64, device=logits.device) if parts > 1 else None
     f = _func("sampling.cu", "lmsf_sample",
-              [c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+              [c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p])
     rc = f(_ptr(out), _ptr(logits), logits.stride(0), rows, vocab, _ptr(temperature), _ptr(seed), _i32(step, "step"),
-           _stream())
+           parts, _ptr(scratch), _stream())
     _check(rc, "sampling.cu", "lmsf_sampling")
+    if parts > 1:
+        add_launches(1)
 
 
 def apply_penalties(logits: torch.Tensor, rows: torch.Tensor, tokens: torch.Tensor, out_counts: torch.Tensor,
