@@ -71,6 +71,7 @@ class EngineArgs:
     dtype: Optional[str] = None
     num_gpu_blocks: Optional[int] = None
     enforce_eager: bool = False
+    no_async_scheduling: bool = False
 
     @staticmethod
     def add_cli_args(p: argparse.ArgumentParser) -> argparse.ArgumentParser:
@@ -88,6 +89,8 @@ class EngineArgs:
         p.add_argument("--num-gpu-blocks", type=int, default=None,
                        help="number of cache pages, instead of deriving it from free memory")
         p.add_argument("--enforce-eager", action="store_true", help="never replay decode steps as CUDA graphs")
+        p.add_argument("--no-async-scheduling", action="store_true",
+                       help="read every batch's tokens before the next batch is scheduled")
         return p
 
     @staticmethod
@@ -95,7 +98,8 @@ class EngineArgs:
         return EngineArgs(model=ns.model, max_num_batched_tokens=ns.max_num_batched_tokens,
                           max_num_seqs=ns.max_num_seqs, max_model_len=ns.max_model_len, block_size=ns.block_size,
                           seed=ns.seed, gpu_memory_utilization=ns.gpu_memory_utilization, dtype=ns.dtype,
-                          num_gpu_blocks=ns.num_gpu_blocks, enforce_eager=ns.enforce_eager)
+                          num_gpu_blocks=ns.num_gpu_blocks, enforce_eager=ns.enforce_eager,
+                          no_async_scheduling=ns.no_async_scheduling)
 
 
 def resolve_max_model_len(user_value: Optional[int], derived: int) -> int:

@@ -26,7 +26,21 @@ __global__ void embedding_kernel(W* __restrict__ out, const W* __restrict__ tabl
   for (int i = threadIdx.x; i < row_words; i += blockDim.x) dst[i] = src[i];
 }
 
+// token_ids[dst[i]] = source[src[i]] for every i with dst[i] >= 0: puts tokens that were sampled on the device
+// into the next step's input without a round trip to the host.
+__global__ void patch_tokens_kernel(int* __restrict__ token_ids, const int* __restrict__ dst, const int* __restrict__ src,
+                                    const int* __restrict__ source, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n && dst[i] >= 0) token_ids[dst[i]] = source[src[i]];
+}
+
 }  // namespace lmsf
+
+LMSF_API int lmsf_patch_tokens(int* token_ids, const int* dst, const int* src, const int* source, int n, void* stream) {
+  if (n <= 0) return 0;
+  lmsf::patch_tokens_kernel<<<(n + 127) / 128, 128, 0, (cudaStream_t)stream>>>(token_ids, dst, src, source, n);
+  return LMSF_LAUNCH_STATUS();
+}
 
 LMSF_API int lmsf_embedding(void* out, const void* table, const int* ids, int n_tokens, int hidden, int vocab,
                             int dtype, int* error_flag, void* stream) {

@@ -19,12 +19,14 @@ class LLM:
                  gpu_memory_utilization: float = 0.9, max_model_len: Optional[int] = None,
                  max_num_batched_tokens: Optional[int] = None, max_num_seqs: int = 256, seed: int = 0,
                  num_gpu_blocks: Optional[int] = None, enforce_eager: bool = False, load_format: str = "auto",
+                 async_scheduling: bool = True,
                  device: str = "cuda:0"):
         self.engine = LLMEngine(EngineArgs(model=model, max_num_batched_tokens=max_num_batched_tokens,
                                            max_num_seqs=max_num_seqs, max_model_len=max_model_len,
                                            block_size=block_size, seed=seed,
                                            gpu_memory_utilization=gpu_memory_utilization, dtype=dtype,
-                                           num_gpu_blocks=num_gpu_blocks, enforce_eager=enforce_eager),
+                                           num_gpu_blocks=num_gpu_blocks, enforce_eager=enforce_eager,
+                                           no_async_scheduling=not async_scheduling),
                                 device=device, load_format=load_format)
         self._next_id = 0
 

@@ -35,6 +35,16 @@ class StepStats:
     step_ms: float = 0.0
 
 
+@dataclass
+class _InFlight:
+    """A batch that has been launched and whose sampled tokens have not been read."""
+    sampled: List[Sequence]
+    row_of: Dict[Hashable, int]
+    tokens_dev: Optional[torch.Tensor] = None
+    host: Optional[torch.Tensor] = None
+    event: Optional["torch.cuda.Event"] = None
+
+
 class LLMEngine:
     def __init__(self, args: EngineArgs, device: str = "cuda:0", load_format: str = "auto"):
         self.args = args
@@ -64,6 +74,10 @@ class LLMEngine:
         self.seqs: Dict[Hashable, Sequence] = {}
         self.last_stats = StepStats()
         self._auto_id = 0
+        self.async_scheduling = not args.no_async_scheduling
+        self._inflight: Optional[_InFlight] = None
+        self._result_ring = [None] * 4
+        self._result_pos = 0
 
     @staticmethod
     def _load_tokenizer(model_dir: str):
@@ -104,11 +118,13 @@ class LLMEngine:
         self.scheduler.add_seq(seq)
 
     def abort_request(self, request_id: Hashable) -> None:
-        self.scheduler.abort_seq(request_id)
+        seq = self.scheduler.abort_seq(request_id)
+        if seq is None and request_id in self.seqs:      # e.g. held out of both queues
+            self.seqs[request_id].status = SequenceStatus.FINISHED_ABORTED
         self.seqs.pop(request_id, None)
 
     def has_unfinished_requests(self) -> bool:
-        return self.scheduler.has_unfinished_seqs()
+        return self.scheduler.has_unfinished_seqs() or self._inflight is not None
 
     def get_num_unfinished_requests(self) -> int:
         return self.scheduler.get_num_unfinished_seqs()
@@ -120,58 +136,121 @@ class LLMEngine:
         last = seq.output_token_ids[-1]
         if last in sp.stop_token_ids:
             seq.status = SequenceStatus.FINISHED_STOPPED
-        elif len(seq) >= self.max_model_len:
+        elif len(seq.prompt_token_ids) + len(seq.output_token_ids) >= self.max_model_len:
             seq.status = SequenceStatus.FINISHED_LENGTH
         elif len(seq.output_token_ids) >= sp.max_tokens:
             seq.status = SequenceStatus.FINISHED_LENGTH
         elif not sp.ignore_eos and last in self.eos_token_ids:
             seq.status = SequenceStatus.FINISHED_STOPPED
 
-    def step(self) -> List[RequestOutput]:
+    # A step has two halves.  `_launch` schedules, runs the batch and samples on the device; `_retire` reads the
+    # sampled tokens, appends them, tests the stop conditions and frees what finished.  With
+    # `async_scheduling` (the default) a step launches batch k + 1 BEFORE it retires batch k: the host's work
+    # for the next batch overlaps the device's work on this one, and a request's newest token goes from the
+    # sampler to the next batch's input on the device (`StepEntry.last_from`).  A request that turns out to
+    # have stopped at batch k has then already been run once more; that result is dropped at the next retire.
+    # Requests with penalties need their token history on the host, so steps that hold one run in order.
+
+    def _will_finish_by_length(self, seq: Sequence) -> bool:
+        n_out = len(seq.output_token_ids) + seq.num_pending
+        return n_out >= seq.sampling_params.max_tokens or len(seq) >= self.max_model_len
+
+    def _launch(self, outputs: List[RequestOutput]) -> Optional["_InFlight"]:
         t0 = time.perf_counter()
+        for seq in self.scheduler.running:
+            seq.hold = seq.num_pending > 0 and self._will_finish_by_length(seq)
         sched: SchedulerOutputs = self.scheduler.schedule()
-        outputs: List[RequestOutput] = []
         for seq in sched.ignored:
             seq.finish_time = time.monotonic()
             outputs.append(self._output(seq))
             self.seqs.pop(seq.request_id, None)
         stats = StepStats(num_preempted=len(sched.preempted))
+        flight = None
         if not sched.is_empty:
             entries, sampled = [], []
+            prev = self._inflight
             for e in sched.entries:
+                last_from = None
+                if e.seq.covers_pending(e.num_tokens):
+                    last_from = prev.row_of[e.seq.request_id]
                 entries.append(StepEntry(e.seq.request_id, e.seq.next_tokens(e.num_tokens),
-                                         [e.num_tokens - 1] if e.wants_logits else []))
+                                         [e.num_tokens - 1] if e.wants_logits else [], last_from))
                 if e.wants_logits:
                     sampled.append(e.seq)
                 if e.num_tokens == 1 and e.start >= len(e.seq.prompt_token_ids):
                     stats.num_decode_tokens += 1
                 else:
                     stats.num_prefill_tokens += e.num_tokens
-            logits = self.runner.step(entries, self.cache, check=False)
-            tokens: List[int] = []
+            logits = self.runner.step(entries, self.cache, check=False,
+                                      pending_tokens=prev.tokens_dev if prev is not None else None)
+            flight = _InFlight(sampled=sampled, row_of={s.request_id: i for i, s in enumerate(sampled)})
             if sampled:
-                tok = self.sampler.sample(logits, [s.sampling_params for s in sampled], [s.seed for s in sampled],
-                                          [len(s.output_token_ids) for s in sampled], sampled)
-                tokens = tok.tolist()                 # the step's one device-to-host read
-            self.runner.check_device_errors()
+                flight.tokens_dev = self.sampler.sample(
+                    logits, [s.sampling_params for s in sampled], [s.seed for s in sampled],
+                    [len(s.output_token_ids) + s.num_pending for s in sampled], sampled)
+            # tokens and the device's error word travel to pinned memory behind the step
+            n = len(sampled)
+            flight.host = self._result_buffer(n + 1)
+            if n:
+                flight.host[:n].copy_(flight.tokens_dev, non_blocking=True)
+            flight.host[n:n + 1].copy_(self.runner.error_flag, non_blocking=True)
+            flight.event = torch.cuda.Event()
+            flight.event.record()
             for e in sched.entries:
                 e.seq.num_computed += e.num_tokens
-            now = time.monotonic()
-            for seq, t in zip(sampled, tokens):
-                seq.output_token_ids.append(int(t))
-                if seq.first_token_time is None:
-                    seq.first_token_time = now
-                self._check_stop(seq)
-                if seq.status.finished:
-                    seq.finish_time = now
-                    self.scheduler.free_seq(seq)
-                    self.seqs.pop(seq.request_id, None)
-                outputs.append(self._output(seq))
+            for s in sampled:
+                s.num_pending += 1
         stats.num_running = len(self.scheduler.running)
         stats.num_waiting = len(self.scheduler.waiting)
         stats.free_pages = self.cache.num_free_pages(0) if self.cache.groups else 0
         stats.step_ms = (time.perf_counter() - t0) * 1e3
         self.last_stats = stats
+        return flight
+
+    def _result_buffer(self, n: int) -> torch.Tensor:
+        self._result_pos = (self._result_pos + 1) % len(self._result_ring)
+        buf = self._result_ring[self._result_pos]
+        if buf is None or buf.numel() < n:
+            buf = self._result_ring[self._result_pos] = torch.empty(max(n, 512), dtype=torch.int32).pin_memory()
+        return buf
+
+    def _retire(self, flight: Optional["_InFlight"], outputs: List[RequestOutput]) -> None:
+        if flight is None:
+            return
+        flight.event.synchronize()
+        n = len(flight.sampled)
+        values = flight.host[:n + 1].tolist()
+        if values[n]:
+            self.runner.check_device_errors()
+        now = time.monotonic()
+        for seq, t in zip(flight.sampled, values[:n]):
+            seq.num_pending -= 1
+            if seq.status.finished:          # stopped at an earlier token (or aborted): this one is dropped
+                continue
+            seq.output_token_ids.append(int(t))
+            if seq.first_token_time is None:
+                seq.first_token_time = now
+            self._check_stop(seq)
+            if seq.status.finished:
+                seq.finish_time = now
+                self.scheduler.free_seq(seq)
+                self.seqs.pop(seq.request_id, None)
+            outputs.append(self._output(seq))
+
+    def step(self) -> List[RequestOutput]:
+        """Runs one batch.  Returns an output for every request that received a token (with async scheduling:
+        the tokens of the batch launched by the PREVIOUS call; keep calling while has_unfinished_requests())."""
+        outputs: List[RequestOutput] = []
+        overlap = self.async_scheduling and not any(s.sampling_params.penalties_active for s in self.seqs.values())
+        if not overlap and self._inflight is not None:
+            self._retire(self._inflight, outputs)
+            self._inflight = None
+        flight = self._launch(outputs)
+        if overlap:
+            self._retire(self._inflight, outputs)
+            self._inflight = flight
+        else:
+            self._retire(flight, outputs)
         return outputs
 
     def _output(self, seq: Sequence) -> RequestOutput:

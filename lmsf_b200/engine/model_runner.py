@@ -23,10 +23,13 @@ from .. import kernels
 
 @dataclass
 class StepEntry:
-    """The next tokens of one request; `want`: places among them whose logits are asked for."""
+    """The next tokens of one request; `want`: places among them whose logits are asked for.
+    `last_from`: when not None, the entry's LAST token is not known on the host yet: it is element `last_from`
+    of the device tensor given to `step(..., pending_tokens=...)` (the value in `tokens` is a placeholder)."""
     request_id: Hashable
     tokens: Sequence[int]
     want: Sequence[int] = field(default_factory=list)
+    last_from: Optional[int] = None
 
 
 class StepError(RuntimeError):
@@ -48,6 +51,7 @@ class _HostBatch:
     n_dec: int
     n_tiles: int
     n_tiles128: int = 0
+    has_patches: bool = False
 
 
 def _align(n: int, a: int = 4) -> int:
@@ -138,6 +142,11 @@ class ModelRunner:
         for e, n in zip(entries, q_lens):
             rows.extend(off + int(w) for w in e.want)
             off += n
+        patch_dst, patch_src, off = [], [], 0
+        for e, n in zip(entries, q_lens):
+            patch_dst.append(off + n - 1 if e.last_from is not None else -1)
+            patch_src.append(e.last_from if e.last_from is not None else 0)
+            off += n
         dec_ids = [i for i, n in enumerate(q_lens) if n == 1]
         tile_seq = [i for i, n in enumerate(q_lens) if n > 1 for _ in range(0, n, Q_TILE)]
         tile_q0 = [q0 for n in q_lens if n > 1 for q0 in range(0, n, Q_TILE)]
@@ -150,7 +159,8 @@ class ModelRunner:
         seg = {}
         total = 0
         for name, length in [("token_ids", N), ("positions", N), ("token_seq", N), ("cu_q", S + 1), ("ctx_len", S),
-                             ("state_slot", S), ("rows", len(rows)), ("dec_ids", len(dec_ids)),
+                             ("state_slot", S), ("patch_dst", S), ("patch_src", S), ("rows", len(rows)),
+                             ("dec_ids", len(dec_ids)),
                              ("tile_seq", len(tile_seq)), ("tile_q0", len(tile_q0)), ("tile128_seq", len(tile128_seq)),
                              ("tile128_q0", len(tile128_q0))] + \
                             [(f"bt{g}", S * max_blocks[g]) for g in range(n_groups)]:
@@ -171,6 +181,8 @@ class ModelRunner:
         put("ctx_len", np.asarray(ctx_lens, dtype=np.int32))
         slots = [mgr.state_slot(e.request_id) for e in entries]
         put("state_slot", np.asarray(slots, dtype=np.int32))
+        put("patch_dst", np.asarray(patch_dst, dtype=np.int32))
+        put("patch_src", np.asarray(patch_src, dtype=np.int32))
         for name, values in (("rows", rows), ("dec_ids", dec_ids), ("tile_seq", tile_seq), ("tile_q0", tile_q0),
                              ("tile128_seq", tile128_seq), ("tile128_q0", tile128_q0)):
             if values:
@@ -181,7 +193,7 @@ class ModelRunner:
             for i, t in enumerate(tables[g]):
                 bt[i, :len(t)] = t
         return _HostBatch(pinned, event, total, seg, N, S, q_lens, ctx_lens, slots, max_blocks, len(dec_ids),
-                          len(tile_seq), len(tile128_seq))
+                          len(tile_seq), len(tile128_seq), any(d >= 0 for d in patch_dst))
 
     def _pinned_buffer(self, n_ints: int):
         """A pinned host buffer from a small ring; a buffer is used again only after the copy that last read it."""
@@ -230,8 +242,17 @@ class ModelRunner:
         return (not self.enforce_eager and self.graph_safe and len(entries) <= self.max_graph_batch
                 and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries))
 
+    def _patch(self, hb: "_HostBatch", dev: torch.Tensor, pending_tokens: Optional[torch.Tensor]) -> None:
+        if not hb.has_patches:
+            return
+        if pending_tokens is None:
+            raise StepError("an entry names a pending token but no pending_tokens tensor was given")
+        seg = lambda name: dev[hb.seg[name][0]:hb.seg[name][0] + hb.seg[name][1]]
+        kernels.patch_tokens(seg("token_ids"), seg("patch_dst"), seg("patch_src"), pending_tokens)
+
     @torch.inference_mode()
-    def step(self, entries: Sequence[StepEntry], mgr: CacheManager, check: bool = True) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], mgr: CacheManager, check: bool = True,
+             pending_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Runs the entries as one batch; returns float32 logits [wanted, vocab] on the device, in the order
         of the entries and of their `want`.  Afterwards the tokens count as cached (`mgr.commit`).
 
@@ -242,11 +263,13 @@ class ModelRunner:
         hb = self._prepare(entries, mgr, self.static_blocks if graph_mode else None)
         self.storage.zero_state_slots(mgr.take_fresh_slots())
         if graph_mode and (hb.S in self._graphs or hb.S in self._seen_sizes):
-            logits = self._replay(hb)
+            logits = self._replay(hb, pending_tokens)
         else:
             if graph_mode:
                 self._seen_sizes.add(hb.S)
-            ctx, rows = self._context(hb, self._upload(hb))
+            dev = self._upload(hb)
+            self._patch(hb, dev, pending_tokens)
+            ctx, rows = self._context(hb, dev)
             logits = self.model.forward(ctx, self.storage.layer_caches, rows)
         for e in entries:
             mgr.commit(e.request_id, len(e.tokens))
@@ -254,7 +277,7 @@ class ModelRunner:
             self.check_device_errors()
         return logits
 
-    def _replay(self, hb: "_HostBatch") -> torch.Tensor:
+    def _replay(self, hb: "_HostBatch", pending_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         g = self._graphs.get(hb.S)
         if g is None:
             static_in = self._upload(hb)
@@ -274,6 +297,7 @@ class ModelRunner:
         if total != hb.total:
             raise StepError("the layout of a replayed batch changed")
         self._upload(hb, static_in)
+        self._patch(hb, static_in, pending_tokens)
         graph.replay()
         kernels.add_launches(n_launches)
         return static_out

@@ -122,7 +122,14 @@ class Scheduler:
         i = 0
         while i < len(self.running) and budget > 0:
             seq = self.running[i]
+            if seq.hold or seq.num_uncomputed <= 0:      # waits for a token that is still on the device
+                i += 1
+                continue
             n = min(seq.num_uncomputed, budget)
+            if seq.num_pending > 1 or (seq.num_pending and n < seq.num_uncomputed):
+                # only the newest pending token can be taken from the device, and only as a portion's last token
+                i += 1
+                continue
             lack = seq.num_computed + n - self.cache.num_reserved(seq.request_id)
             preempted_self = False
             while lack > 0 and not self.cache.can_reserve(seq.request_id, lack):
@@ -150,6 +157,8 @@ class Scheduler:
         # 2. admissions, first come first served; nothing is admitted in a step that preempted
         while self.waiting and budget > 0 and not out.preempted:
             seq = self.waiting[0]
+            if seq.num_pending:          # preempted with a token still on the device: next step
+                break
             if len(seq) > self.config.max_model_len or not self._fits_alone(len(seq)):
                 self.waiting.popleft()
                 seq.status = SequenceStatus.FINISHED_IGNORED

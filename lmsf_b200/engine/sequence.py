@@ -38,6 +38,8 @@ class Sequence:
     num_computed: int = 0             # tokens whose keys and values are in the cache
     num_preemptions: int = 0
     seed: int = 0
+    num_pending: int = 0              # tokens sampled on the device whose values the host has not read yet
+    hold: bool = False                # not to be scheduled before its pending token is known
     first_token_time: Optional[float] = None
     finish_time: Optional[float] = None
 
@@ -46,17 +48,26 @@ class Sequence:
         return self.prompt_token_ids + self.output_token_ids
 
     def __len__(self) -> int:
-        return len(self.prompt_token_ids) + len(self.output_token_ids)
+        """Tokens of the request, those that are sampled but not read yet included."""
+        return len(self.prompt_token_ids) + len(self.output_token_ids) + self.num_pending
 
     @property
     def num_uncomputed(self) -> int:
         return len(self) - self.num_computed
 
     def next_tokens(self, n: int) -> List[int]:
+        """The next n tokens to run; a token that is still pending on the device appears as 0 (a placeholder
+        that the step function overwrites on the device)."""
         a = self.num_computed
         if a + n <= len(self.prompt_token_ids):
             return self.prompt_token_ids[a:a + n]
-        return self.token_ids[a:a + n]
+        known = self.token_ids
+        toks = known[a:a + n]
+        return toks + [0] * (n - len(toks))
+
+    def covers_pending(self, n: int) -> bool:
+        """Whether the next n tokens reach into the tokens that the host does not know yet."""
+        return self.num_computed + n > len(self.prompt_token_ids) + len(self.output_token_ids)
 
 
 @dataclass

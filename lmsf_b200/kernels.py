@@ -105,6 +105,13 @@ def embedding(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, error_f
     _check(rc, "embedding.cu", "lmsf_embedding")
 
 
+def patch_tokens(token_ids: torch.Tensor, dst: torch.Tensor, src: torch.Tensor, source: torch.Tensor):
+    """token_ids[dst[i]] = source[src[i]] wherever dst[i] >= 0 (all int32, on the device)."""
+    f = _func("embedding.cu", "lmsf_patch_tokens", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p])
+    rc = f(_i32(token_ids, "token_ids"), _i32(dst, "dst"), _i32(src, "src"), _i32(source, "source"), dst.numel(), _stream())
+    _check(rc, "embedding.cu", "lmsf_embedding")
+
+
 # ----------------------------------------------------------------------------- rmsnorm
 
 def add_rmsnorm(h: torch.Tensor, x: torch.Tensor, res: Optional[torch.Tensor], w: torch.Tensor, eps: float, mode: int):
