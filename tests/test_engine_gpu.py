@@ -130,3 +130,57 @@ def test_top_k_top_p_and_penalties_through_the_entry_point():
     both = llm.generate(prompt_token_ids=[prompt, prompt],
                         sampling_params=[sp, SamplingParams(temperature=0, max_tokens=5, ignore_eos=True)])
     assert both[0].outputs[0].token_ids == out and both[1].outputs[0].token_ids == P.generate(cfg, w, prompt, 5)[0]
+
+
+def test_async_scheduling_gives_the_same_tokens_and_drops_what_ran_past_a_stop():
+    """With async scheduling the next batch is launched before the last one's tokens are read; a request that
+    stopped has then been run once more and that result must vanish."""
+    from lmsf_b200 import SamplingParams
+    name = "A"
+    cfg, w = P.load_model(util.model_folder(name, "float32", 0.15))
+    prompts = [util.random_ids(n, cfg["vocab_size"], 60 + i) for i, n in enumerate([9, 30, 4, 21])]
+    refs = [P.generate(cfg, w, p, 14)[0] for p in prompts]
+    # request 0 stops on its 5th token, request 2 on its 1st; the others run to max_tokens
+    sps = [SamplingParams(temperature=0, max_tokens=14, stop_token_ids=[refs[0][4]]),
+           SamplingParams(temperature=0, max_tokens=14, ignore_eos=True),
+           SamplingParams(temperature=0, max_tokens=14, stop_token_ids=[refs[2][0]]),
+           SamplingParams(temperature=0.9, seed=3, max_tokens=9, ignore_eos=True)]
+    results = {}
+    for mode in (True, False):
+        llm = _llm(name, "float32", num_gpu_blocks=40, max_num_batched_tokens=16, max_num_seqs=4, async_scheduling=mode)
+        outs = llm.generate(prompt_token_ids=prompts, sampling_params=sps)
+        results[mode] = [(o.outputs[0].token_ids, o.outputs[0].finish_reason) for o in outs]
+        llm.engine.cache.check_invariants()
+        assert llm.engine.cache.num_free_pages() == 40 and not llm.engine.has_unfinished_requests()
+    assert results[True] == results[False]
+    got = results[True]
+    assert got[0] == (refs[0][:refs[0].index(refs[0][4]) + 1], "stop")
+    assert got[1] == (refs[1], "length")
+    assert got[2] == (refs[2][:1], "stop")
+    assert got[3][0] == P.generate(cfg, w, prompts[3], 9, temperature=0.9, seed=3)[0]
+
+
+def test_engine_step_api_and_abort():
+    from lmsf_b200 import EngineArgs, LLMEngine, SamplingParams
+    name = "A"
+    engine = LLMEngine(EngineArgs(model=util.model_folder(name, "float32", 0.15), dtype="float32", block_size=8,
+                                  num_gpu_blocks=32, max_num_seqs=4))
+    sp = SamplingParams(temperature=0, max_tokens=30, ignore_eos=True)
+    engine.add_request("a", None, sp, prompt_token_ids=[5, 6, 7])
+    engine.add_request("b", None, sp, prompt_token_ids=[8, 9])
+    with pytest.raises(KeyError):
+        engine.add_request("a", None, sp, prompt_token_ids=[1])
+    assert engine.get_num_unfinished_requests() == 2
+    seen = {"a": 0, "b": 0}
+    for _ in range(6):
+        for out in engine.step():
+            seen[out.request_id] = len(out.outputs[0].token_ids)
+    assert seen["a"] >= 4 and seen["b"] >= 4
+    engine.abort_request("a")
+    while engine.has_unfinished_requests():
+        for out in engine.step():
+            assert out.request_id == "b"
+            seen["b"] = len(out.outputs[0].token_ids)
+    assert seen["b"] == 30
+    engine.cache.check_invariants()
+    assert engine.cache.num_free_pages() == 32

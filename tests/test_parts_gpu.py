@@ -221,3 +221,127 @@ def test_toy_architecture_is_registered_built_and_stepped(tmp_path, dtype, rel):
         scale = max(1.0, max(float(abs(r).max()) for r in ref.values()))
         worst = max(float(abs(row - ref[rid][pos]).max()) for (rid, pos), row in results[mode].items())
         assert worst <= rel * scale, (mode, worst, scale)
+
+
+def _hand_context(q_lens, ctx_lens, block_size, n_pages, seed=0):
+    """A StepContext and block table made by hand, the way ModelRunner lays a batch out."""
+    from lmsf_b200.parts.base import CacheGroupView, StepContext
+    g = torch.Generator().manual_seed(seed)
+    S, N = len(q_lens), sum(q_lens)
+    max_blocks = max((c + block_size - 1) // block_size for c in ctx_lens)
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    bt = torch.full((S, max_blocks), -1, dtype=torch.int32)
+    for s, c in enumerate(ctx_lens):
+        for i in range((c + block_size - 1) // block_size):
+            bt[s, i] = perm.pop()
+    dev = torch.device(DEV)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    positions = [p for c, n in zip(ctx_lens, q_lens) for p in range(c - n, c)]
+    token_seq = [s for s, n in enumerate(q_lens) for _ in range(n)]
+    cu = [0]
+    for n in q_lens:
+        cu.append(cu[-1] + n)
+    tiles = [(s, q0) for s, n in enumerate(q_lens) if n > 1 for q0 in range(0, n, 64)]
+    tiles128 = [(s, q0) for s, n in enumerate(q_lens) if n > 1 for q0 in range(0, n, 128)]
+    dec = [s for s, n in enumerate(q_lens) if n == 1]
+    ctx = StepContext(n_tokens=N, n_seqs=S, dtype=torch.float32, device=dev, token_ids=i32([0] * N), positions=i32(positions),
+                      token_seq=i32(token_seq), cu_q=i32(cu), ctx_len=i32(ctx_lens), state_slot=i32(list(range(S))),
+                      groups=[CacheGroupView(bt.to(dev), block_size)], q_lens=list(q_lens), ctx_lens=list(ctx_lens),
+                      state_slots=list(range(S)), error_flag=torch.zeros(1, dtype=torch.int32, device=dev),
+                      decode_seq_ids=i32(dec), n_decode_seqs=len(dec), q_tile_seq=i32([t[0] for t in tiles]),
+                      q_tile_q0=i32([t[1] for t in tiles]), n_q_tiles=len(tiles), q_tile128_seq=i32([t[0] for t in tiles128]),
+                      q_tile128_q0=i32([t[1] for t in tiles128]), n_q_tiles128=len(tiles128))
+    return ctx, bt
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 4e-2)])
+@pytest.mark.parametrize("nh,nkv,hd,window", [(4, 2, 16, None), (3, 1, 64, None), (2, 2, 48, 7)])
+def test_attention_mixer_alone_over_two_steps(dtype, tol, nh, nkv, hd, window):
+    """The mixer part by itself: a whole prompt in step one, then a portion and a decoded token of two requests in
+    step two, against the plain attention block on whole sequences."""
+    from lmsf_b200.parts.attention import PagedAttention
+    from lmsf_b200.parts.base import LayerCache
+    from lmsf_b200.parts.rope import RotaryEmbedding
+    H, bs = 40, 8
+    g = torch.Generator().manual_seed(5)
+    rope = RotaryEmbedding(rot_dim=hd, theta=1000.0)
+    att = PagedAttention(hidden_size=H, num_heads=nh, num_kv_heads=nkv, head_dim=hd, position_encoding=rope, window=window)
+    wq, wk, wv = (torch.randn(nh * hd, H, generator=g) * 0.3, torch.randn(nkv * hd, H, generator=g) * 0.3,
+                  torch.randn(nkv * hd, H, generator=g) * 0.3)
+    wo = torch.randn(H, nh * hd, generator=g) * 0.3
+    r = lambda t: t.to(dtype).float()
+    att.set_weights({"qkv": torch.cat([wq, wk, wv]).to(dtype).to(DEV), "o": wo.to(dtype).to(DEV)})
+    att.prepare(dtype, torch.device(DEV))
+    assert att.cache_spec().window == window and att.weight_specs()["qkv"].shapes[1] == (nkv * hd, H)
+    lens = [21, 13]
+    hs = [torch.randn(n, H, generator=g).to(dtype) for n in lens]
+    cfg = dict(hidden_size=H, num_attention_heads=nh, num_key_value_heads=nkv, head_dim=hd, rope_theta=1000.0, sliding_window=window)
+    w = {"q_proj.weight": r(wq), "k_proj.weight": r(wk), "v_proj.weight": r(wv), "o_proj.weight": r(wo)}
+    refs = [P.attention_block(cfg, w, "", h.float(), torch.arange(n), P.rope_inv_freq(cfg)) for h, n in zip(hs, lens)]
+    kv = torch.zeros(12, 2, nkv, bs, hd, dtype=dtype, device=DEV)
+    cache = LayerCache(kv=kv, group=0, owner=True)
+    # step one: request 0 up to token 15, request 1 up to token 12
+    ctx, bt = _hand_context([15, 12], [21, 13], bs, 12)        # tables sized for the final lengths
+    ctx.ctx_len.copy_(torch.tensor([15, 12], dtype=torch.int32))
+    ctx.positions.copy_(torch.tensor(list(range(15)) + list(range(12)), dtype=torch.int32))
+    ctx.ctx_lens[:] = [15, 12]
+    out1 = att.forward(ctx, torch.cat([hs[0][:15], hs[1][:12]]).to(DEV), cache).float().cpu()
+    # step two: 6 more tokens of request 0 (a portion), 1 token of request 1 (a decode), same pages
+    ctx2, _ = _hand_context([6, 1], [21, 13], bs, 12)
+    ctx2.groups[0].block_table.copy_(bt)
+    out2 = att.forward(ctx2, torch.cat([hs[0][15:], hs[1][12:]]).to(DEV), cache).float().cpu()
+    got = [torch.cat([out1[:15], out2[:6]]), torch.cat([out1[15:], out2[6:]])]
+    for a, b in zip(got, refs):
+        assert (a - b).abs().max() <= tol * max(1.0, b.abs().max()), (a - b).abs().max()
+    assert ctx.error_flag.item() == 0 and ctx2.error_flag.item() == 0
+
+
+def test_embedding_rotary_apply_and_block_arrangement():
+    from lmsf_b200.parts.base import Block, FeedForward, LayerCache, Mixer, Norm, build_part, PartSpec
+    from lmsf_b200.parts.block import PreNormBlock
+    from lmsf_b200.parts.embedding import TokenEmbedding
+    from lmsf_b200.parts.rope import RotaryEmbedding
+    dev = torch.device(DEV)
+    g = torch.Generator().manual_seed(2)
+    # embedding
+    emb = TokenEmbedding(vocab_size=37, hidden_size=24)
+    table = torch.randn(37, 24, generator=g)
+    emb.set_weights({"weight": table.to(dev)})
+    ctx, _ = _hand_context([5], [5], 4, 4)
+    ids = torch.tensor([3, 36, 0, 7, 7], dtype=torch.int32, device=dev)
+    ctx.token_ids.copy_(ids)
+    assert torch.equal(emb.forward(ctx).cpu(), table[ids.cpu().long()])
+    # rotary applied on its own (the path of a mixer that cannot fuse it): partial width, interleaved pairs
+    rope = RotaryEmbedding(rot_dim=8, theta=50.0, is_neox=False)
+    rope.prepare(torch.float32, dev)
+    q = torch.randn(5, 2 * 16, generator=g)
+    qd = q.to(dev).clone()
+    rope.apply(ctx, qd, None, 2, 0, 16)
+    inv = torch.tensor([50.0 ** (-(2.0 * i) / 8) for i in range(4)])
+    ang = torch.arange(5).float()[:, None] * inv[None, :]
+    x = q.reshape(5, 2, 16)
+    a, b = x[..., 0:8:2], x[..., 1:8:2]
+    rot = torch.stack([a * ang.cos()[:, None] - b * ang.sin()[:, None], b * ang.cos()[:, None] + a * ang.sin()[:, None]], -1).reshape(5, 2, 8)
+    assert torch.allclose(qd.cpu().reshape(5, 2, 16), torch.cat([rot, x[..., 8:]], -1), atol=1e-5)
+    # the pre-norm arrangement with stand-in parts: h = n1(x + res); a = mix(h); h2 = n2(a + res'); out = ff(h2)
+    calls = []
+
+    class N(Norm):
+        def __init__(self, k): self.k = k
+        def forward_residual(self, x, res):
+            res = x.float() if res is None else res + x.float()
+            calls.append(("norm", self.k))
+            return (res * self.k).to(x.dtype), res
+
+    class M(Mixer):
+        def forward(self, ctx, h, cache): calls.append("mixer"); return h + 1
+
+    class F(FeedForward):
+        def forward(self, ctx, h): calls.append("ffn"); return h * 2
+
+    blk = PreNormBlock({"mixer_norm": N(2.0), "mixer": M(), "ffn_norm": N(3.0), "feed_forward": F()})
+    x0 = torch.ones(2, 3)
+    y, res = blk.forward(None, x0, None, LayerCache())
+    assert calls == [("norm", 2.0), "mixer", ("norm", 3.0), "ffn"]
+    assert torch.equal(res, x0 + (x0 * 2 + 1)) and torch.equal(y, (res * 3.0) * 2)
+    assert PreNormBlock.ROLES == {"mixer_norm": "norm", "mixer": "mixer", "ffn_norm": "norm", "feed_forward": "feed_forward"}
