@@ -25,6 +25,17 @@ MODEL = dict(architectures=["LlamaForCausalLM"], model_type="llama", hidden_size
              num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=14336, vocab_size=128256,
              rope_theta=500000.0, rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=8192,
              hidden_act="silu", torch_dtype="bfloat16", bos_token_id=128000, eos_token_id=128001)
+MODELS = {
+    "llama3-8b": MODEL,
+    # Llama-3.2-1B's and Llama-2-13B's layer sizes
+    "llama3.2-1b": dict(MODEL, hidden_size=2048, num_hidden_layers=16, num_attention_heads=32, num_key_value_heads=8,
+                        head_dim=64, intermediate_size=8192, tie_word_embeddings=True, max_position_embeddings=131072,
+                        rope_scaling=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                                          original_max_position_embeddings=8192)),
+    "llama2-13b": dict(MODEL, hidden_size=5120, num_hidden_layers=40, num_attention_heads=40, num_key_value_heads=40,
+                       head_dim=128, intermediate_size=13824, vocab_size=32000, rope_theta=10000.0,
+                       max_position_embeddings=4096, bos_token_id=1, eos_token_id=2),
+}
 CONTEXT = 2048          # tokens each request holds while decoding is timed
 MAX_MODEL_LEN = 4096
 BLOCK_SIZE = 16
@@ -139,8 +150,6 @@ def time_decode(runner, mgr, ids, steps, warmup, vocab, seed=0):
     end.record()
     torch.cuda.synchronize()
     ms = start.elapsed_time(end) / steps
-    for r in ids:          # give back the tokens the timed steps added, so the next point starts alike
-        pass
     return ms, kernels.launch_count() - l0
 
 
@@ -171,7 +180,7 @@ def time_e2e(folder, n_layers, batch, context, steps, warmup, vocab):
     copies the step's inputs from pinned host memory to the device and reads the sampled tokens back."""
     import torch
     from lmsf_b200 import EngineArgs, LLMEngine, SamplingParams
-    engine = LLMEngine(EngineArgs(model=folder, dtype="bfloat16", block_size=BLOCK_SIZE, max_model_len=MAX_MODEL_LEN,
+    engine = LLMEngine(EngineArgs(model=folder, dtype="bfloat16", block_size=BLOCK_SIZE, max_model_len=max(MAX_MODEL_LEN, context + 64),
                                   max_num_batched_tokens=8192, max_num_seqs=max(batch, 8),
                                   gpu_memory_utilization=0.85), load_format="dummy")
     g = torch.Generator().manual_seed(2)
@@ -196,6 +205,44 @@ def time_e2e(folder, n_layers, batch, context, steps, warmup, vocab):
     return produced / dt, h2d, batch * 4 + 4
 
 
+def serve(cfg, n_layers, n_requests, decode_tokens, budget):
+    """Continuous batching through the engine: requests with seeded uniform-random prompt lengths in [128, 2048],
+    `decode_tokens` generated tokens each.  Prints its own JSON line (not the line of the contract)."""
+    import random
+
+    import torch
+    from lmsf_b200 import EngineArgs, LLMEngine, SamplingParams
+    cfg = dict(cfg, num_hidden_layers=n_layers)
+    folder = tempfile.mkdtemp(prefix="lmsf_bench_")
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    engine = LLMEngine(EngineArgs(model=folder, dtype="bfloat16", block_size=BLOCK_SIZE, max_model_len=MAX_MODEL_LEN,
+                                  max_num_batched_tokens=budget, max_num_seqs=n_requests, gpu_memory_utilization=0.85),
+                       load_format="dummy")
+    rng = random.Random(0)
+    lens = [rng.randint(128, 2048) for _ in range(n_requests)]
+    g = torch.Generator().manual_seed(3)
+    sp = SamplingParams(temperature=0.0, max_tokens=decode_tokens, ignore_eos=True)
+    for rep in range(2):                       # the first pass warms up (compilation, graphs); the second is timed
+        for i, n in enumerate(lens):
+            engine.add_request((rep, i), None, sp, prompt_token_ids=torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist())
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        steps = generated = preempted = 0
+        while engine.has_unfinished_requests():
+            generated += len(engine.step())
+            preempted += engine.last_stats.num_preempted
+            steps += 1
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+    print(json.dumps({"metric": "generated tokens/s under continuous batching", "value": round(generated / dt, 1),
+                      "unit": "tokens/s", "requests": n_requests, "prompt_tokens": sum(lens), "generated_tokens": generated,
+                      "total_tokens_per_s": round((generated + sum(lens)) / dt, 1), "seconds": round(dt, 3), "steps": steps,
+                      "preemptions": preempted, "max_num_batched_tokens": budget, "layers": n_layers,
+                      "layers_of_model": cfg["num_hidden_layers"], "dtype": "bf16", "data": "synthetic", "impl": "ours"}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -206,6 +253,11 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--model", default="llama3-8b", choices=sorted(MODELS), help="whose layer sizes to run")
+    ap.add_argument("--context", type=int, default=CONTEXT, help="tokens each request holds while decoding is timed")
+    ap.add_argument("--serve", action="store_true",
+                    help="instead of the contract's line: 64 requests of 128..2048 prompt tokens and 256 generated "
+                         "tokens each through the engine's continuous batching")
     a = ap.parse_args()
     if a.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -223,7 +275,10 @@ def main() -> int:
     from lmsf_b200.engine.model_runner import ModelRunner
 
     pk = peaks()
-    cfg = dict(MODEL)
+    cfg = dict(MODELS[a.model])
+    if a.serve:
+        return serve(cfg, a.layers or cfg["num_hidden_layers"], 64, 256, 2048)
+    ctx_len = a.context
     full_layers = cfg["num_hidden_layers"]
     n_layers = a.layers or full_layers
     cfg["num_hidden_layers"] = n_layers
@@ -233,8 +288,9 @@ def main() -> int:
     nums = model_numbers(cfg, n_layers)
     dev = torch.device("cuda:0")
     model, _, dtype = build_model(folder, "bfloat16", dev, load_format="dummy")
-    pages = (64 * (CONTEXT + 64) + PREFILL_TOKENS) // BLOCK_SIZE + 64
-    runner = ModelRunner(model, dtype, dev, BLOCK_SIZE, num_blocks=pages, max_num_seqs=80, max_model_len=MAX_MODEL_LEN)
+    max_batch = 64 if not a.skip_points else a.batch
+    pages = (max_batch * (ctx_len + 64) + PREFILL_TOKENS) // BLOCK_SIZE + 64
+    runner = ModelRunner(model, dtype, dev, BLOCK_SIZE, num_blocks=pages, max_num_seqs=80, max_model_len=max(MAX_MODEL_LEN, ctx_len + 64))
     for t in runner.storage.tensors:
         t.normal_(0.0, 1.0)
     mgr = runner.make_cache_manager()
@@ -242,23 +298,23 @@ def main() -> int:
 
     clocks = ClockSampler()
     clocks.start()
-    ids = fill_requests(runner, mgr, a.batch, CONTEXT, "b")
+    ids = fill_requests(runner, mgr, a.batch, ctx_len, "b")
     ms, launches = time_decode(runner, mgr, ids, a.steps, a.warmup, V)
     clock_rec = clocks.stop()
     for r in ids:
         mgr.free(r)
     value = a.batch / (ms * 1e-3)
-    achieved = decode_bytes(nums, a.batch, CONTEXT) / (ms * 1e-3) / 1e9
+    achieved = decode_bytes(nums, a.batch, ctx_len) / (ms * 1e-3) / 1e9
 
     points = {}
     if not a.skip_points:
         for b in (1, 64):
-            ids = fill_requests(runner, mgr, b, CONTEXT, f"p{b}_")
+            ids = fill_requests(runner, mgr, b, ctx_len, f"p{b}_")
             pms, _ = time_decode(runner, mgr, ids, max(8, a.steps // 2), a.warmup, V)
             for r in ids:
                 mgr.free(r)
             points[f"decode_b{b}"] = round(b / (pms * 1e-3), 1)
-            points[f"decode_b{b}_hbm_frac"] = round(decode_bytes(nums, b, CONTEXT) / (pms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+            points[f"decode_b{b}_hbm_frac"] = round(decode_bytes(nums, b, ctx_len) / (pms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
 
     pf_ms = time_prefill(runner, mgr, PREFILL_TOKENS, 3, 2, V)
     pf_flops = prefill_flops(cfg, nums, PREFILL_TOKENS, n_layers)
@@ -269,18 +325,18 @@ def main() -> int:
     torch.cuda.empty_cache()
     e2e = None
     if not a.skip_e2e:
-        ev, h2d, d2h = time_e2e(folder, n_layers, a.batch, CONTEXT, a.steps, a.warmup, V)
+        ev, h2d, d2h = time_e2e(folder, n_layers, a.batch, ctx_len, a.steps, a.warmup, V)
         e2e = {"value": round(ev, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)}
 
     line = {
-        "metric": "decode tokens/s (Llama-3-8B shape, batch 8, 2048-token contexts)", "value": round(value, 1),
+        "metric": f"decode tokens/s ({a.model} shape, batch {a.batch}, {ctx_len}-token contexts)", "value": round(value, 1),
         "unit": "tokens/s", "n_gpus": 1, "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(ms, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"model": "Llama-3-8B shape, random weights", "layers": n_layers, "layers_of_model": full_layers,
+        "config": {"model": f"{a.model} shape, random weights", "layers": n_layers, "layers_of_model": full_layers,
                    "hidden_size": cfg["hidden_size"], "num_attention_heads": cfg["num_attention_heads"],
                    "num_key_value_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
                    "intermediate_size": cfg["intermediate_size"], "vocab_size": V, "global_batch": a.batch,
-                   "seq_len": CONTEXT, "max_model_len": MAX_MODEL_LEN, "block_size": BLOCK_SIZE,
+                   "seq_len": ctx_len, "max_model_len": MAX_MODEL_LEN, "block_size": BLOCK_SIZE,
                    "prefill_tokens": PREFILL_TOKENS, "parallelism": "1 GPU",
                    "l2": "inputs larger than L2 (weights + cache of a step >> 126 MB); prefill flushes L2",
                    "peaks": pk["source"]},
