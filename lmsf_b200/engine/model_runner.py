@@ -94,6 +94,7 @@ class ModelRunner:
         self._graphs = {}
         self._seen_sizes = set()
         self._graph_pool = None
+        self._capture_stream = None
 
     def make_cache_manager(self) -> CacheManager:
         return self.storage.make_manager()
@@ -111,10 +112,6 @@ class ModelRunner:
             seen.add(e.request_id)
             if len(e.tokens) == 0:
                 raise StepError(f"request {e.request_id!r} brings no tokens")
-            for t in e.tokens:
-                if not (0 <= int(t) < self.vocab_size):
-                    raise StepError(f"request {e.request_id!r}: token id {t} is outside the vocabulary "
-                                    f"(0..{self.vocab_size - 1})")
             for w in e.want:
                 if not (0 <= int(w) < len(e.tokens)):
                     raise StepError(f"request {e.request_id!r}: wanted place {w} is outside its {len(e.tokens)} tokens")
@@ -174,7 +171,16 @@ class ModelRunner:
             o, n = seg[name]
             host[o:o + n] = values
 
-        put("token_ids", np.fromiter((int(t) for e in entries for t in e.tokens), dtype=np.int32, count=N))
+        tok = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries])
+        if tok.min() < 0 or tok.max() >= self.vocab_size:
+            for e in entries:
+                bad = [int(t) for t in e.tokens if not (0 <= int(t) < self.vocab_size)]
+                if bad:
+                    for rid in reserved:
+                        mgr.rollback(rid)
+                    raise StepError(f"request {e.request_id!r}: token id {bad[0]} is outside the vocabulary "
+                                    f"(0..{self.vocab_size - 1})")
+        put("token_ids", tok.astype(np.int32))
         put("positions", np.concatenate([np.arange(s, s + n, dtype=np.int32) for s, n in zip(starts, q_lens)]))
         put("token_seq", np.repeat(np.arange(S, dtype=np.int32), q_lens))
         put("cu_q", np.concatenate([[0], np.cumsum(q_lens)]).astype(np.int32))
@@ -283,13 +289,22 @@ class ModelRunner:
             static_in = self._upload(hb)
             ctx, rows = self._context(hb, static_in)
             ctx.extras["decode_max_ctx"] = self.max_model_len      # launch geometry must not depend on the step
-            torch.cuda.synchronize(self.device)
             if self._graph_pool is None:
                 self._graph_pool = torch.cuda.graph_pool_handle()
+                self._capture_stream = torch.cuda.Stream(self.device)
+            # Captured on a side stream with capture_begin / capture_end directly: the torch.cuda.graph context
+            # would also empty the allocator's cache, which costs milliseconds for every batch size.
             graph = torch.cuda.CUDAGraph()
             before = kernels.launch_count()
-            with torch.cuda.graph(graph, pool=self._graph_pool):
-                static_out = self.model.forward(ctx, self.storage.layer_caches, rows)
+            side = self._capture_stream
+            side.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(side):
+                graph.capture_begin(pool=self._graph_pool)
+                try:
+                    static_out = self.model.forward(ctx, self.storage.layer_caches, rows)
+                finally:
+                    graph.capture_end()
+            torch.cuda.current_stream(self.device).wait_stream(side)
             n_launches = kernels.launch_count() - before
             kernels.add_launches(-n_launches)                      # recorded, not run
             g = self._graphs[hb.S] = (graph, static_in, static_out, n_launches, hb.total)

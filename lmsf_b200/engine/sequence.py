@@ -59,10 +59,13 @@ class Sequence:
         """The next n tokens to run; a token that is still pending on the device appears as 0 (a placeholder
         that the step function overwrites on the device)."""
         a = self.num_computed
-        if a + n <= len(self.prompt_token_ids):
+        n_prompt = len(self.prompt_token_ids)
+        if a + n <= n_prompt:
             return self.prompt_token_ids[a:a + n]
-        known = self.token_ids
-        toks = known[a:a + n]
+        if a >= n_prompt:
+            toks = self.output_token_ids[a - n_prompt:a - n_prompt + n]
+        else:
+            toks = self.prompt_token_ids[a:] + self.output_token_ids[:a + n - n_prompt]
         return toks + [0] * (n - len(toks))
 
     def covers_pending(self, n: int) -> bool:
