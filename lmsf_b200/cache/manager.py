@@ -15,13 +15,18 @@ table per request, pages claimed as the request grows and given back when it end
   the caller before they are used.
 
 A table entry i covers positions [i * block_size, (i + 1) * block_size).
+
+The bookkeeping is native (csrc/host_runtime.cpp, as the reference's is Rust); this class is its face and
+maps request ids of any hashable type to the integers that the library knows.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+import ctypes
+from dataclasses import dataclass
 from typing import Dict, Hashable, List, Optional, Sequence
 
-from .block_allocator import BlockAllocator, OutOfPages
+from . import native
+from .block_allocator import OutOfPages
 
 
 @dataclass(frozen=True)
@@ -30,12 +35,19 @@ class GroupSpec:
     window: Optional[int] = None
 
 
-@dataclass
-class _Request:
-    tables: List[List[int]]
-    num_tokens: int = 0          # positions committed (their keys are in the cache)
-    num_reserved: int = 0        # positions that have pages (>= num_tokens)
-    slot: int = -1
+class _PoolView:
+    """What tests and statistics read of one group's pool."""
+
+    def __init__(self, mgr: "CacheManager", g: int):
+        self._mgr, self._g = mgr, g
+
+    @property
+    def num_free(self) -> int:
+        return self._mgr.num_free_pages(self._g)
+
+    @property
+    def num_blocks(self) -> int:
+        return self._mgr.num_total_pages(self._g)
 
 
 class CacheManager:
@@ -44,140 +56,136 @@ class CacheManager:
             raise ValueError("one page count per group")
         if block_size <= 0:
             raise ValueError("block_size must be positive")
+        if any(int(n) <= 0 for n in num_blocks):
+            raise ValueError("a page pool needs at least one page")
         self.groups = list(groups)
         self.block_size = int(block_size)
-        self.pools = [BlockAllocator(n) for n in num_blocks]
         self.num_state_slots = int(num_state_slots)
-        self._free_slots = list(range(self.num_state_slots - 1, -1, -1))
-        self._fresh_slots: List[int] = []
-        self._reqs: Dict[Hashable, _Request] = {}
+        self._lib = native.lib()
+        G = len(self.groups)
+        windows = (ctypes.c_int * max(G, 1))(*[g.window or 0 for g in self.groups])
+        blocks = (ctypes.c_int * max(G, 1))(*[int(n) for n in num_blocks])
+        self._h = self._lib.lmsf_cm_create(G, windows, blocks, self.block_size, self.num_state_slots)
+        if not self._h:
+            raise ValueError("the cache manager could not be created from these sizes")
+        self.pools = [_PoolView(self, g) for g in range(G)]
+        self._ids: Dict[Hashable, int] = {}
+        self._next_id = 1
+        self._scratch = (ctypes.c_int * max(G, 1))()
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            self._lib.lmsf_cm_destroy(self._h)
+            self._h = None
+
+    def handle(self) -> int:
+        """The native object, for the batch builder."""
+        return self._h
+
+    def native_id(self, rid) -> int:
+        return self._ids[rid]
+
+    def _id(self, rid) -> int:
+        try:
+            return self._ids[rid]
+        except KeyError:
+            raise KeyError(f"request {rid!r} is not live") from None
 
     # ------------------------------------------------------------------ requests
     def has(self, rid) -> bool:
-        return rid in self._reqs
+        return rid in self._ids
 
     def can_add(self) -> bool:
-        return bool(self._free_slots)
+        return bool(self._lib.lmsf_cm_can_add(self._h))
 
     def add(self, rid) -> int:
         """Registers a request; returns its state slot."""
-        if rid in self._reqs:
+        if rid in self._ids:
             raise KeyError(f"request {rid!r} is already live")
-        if not self._free_slots:
+        nid = self._next_id
+        slot = self._lib.lmsf_cm_add(self._h, nid)
+        if slot < 0:
             raise OutOfPages("no free state slot")
-        slot = self._free_slots.pop()
-        self._fresh_slots.append(slot)
-        self._reqs[rid] = _Request(tables=[[] for _ in self.groups], slot=slot)
+        self._next_id += 1
+        self._ids[rid] = nid
         return slot
 
     def free(self, rid) -> None:
         """Gives back everything the request holds."""
-        r = self._reqs.pop(rid)
-        for g, table in enumerate(r.tables):
-            for b in reversed(table):
-                if b >= 0:
-                    self.pools[g].free(b)
-        if r.slot in self._fresh_slots:
-            self._fresh_slots.remove(r.slot)
-        self._free_slots.append(r.slot)
+        nid = self._id(rid)
+        rc = self._lib.lmsf_cm_free(self._h, nid)
+        del self._ids[rid]
+        if rc != 0:
+            raise ValueError(f"request {rid!r}: a page was given back twice")
 
     def take_fresh_slots(self) -> List[int]:
-        out, self._fresh_slots = self._fresh_slots, []
-        return out
+        buf = (ctypes.c_int * max(self.num_state_slots, 1))()
+        n = self._lib.lmsf_cm_take_fresh_slots(self._h, buf, len(buf))
+        return list(buf[:n])
 
     # ------------------------------------------------------------------ pages
-    def _first_needed_entry(self, g: int, start: int) -> int:
-        """First table entry that a query at position >= start may still read."""
-        w = self.groups[g].window
-        if w is None:
-            return 0
-        return max(0, start - w + 1) // self.block_size
-
     def pages_needed(self, rid, n: int) -> List[int]:
         """Per group, how many new pages `reserve(rid, n)` would claim."""
-        r = self._reqs[rid]
-        end = r.num_reserved + n
-        entries = (end + self.block_size - 1) // self.block_size
-        return [max(0, entries - len(t)) for t in r.tables]
+        self._lib.lmsf_cm_pages_needed(self._h, self._id(rid), int(n), self._scratch)
+        return list(self._scratch[:len(self.groups)])
 
     def can_reserve(self, rid, n: int, headroom: int = 0) -> bool:
-        return all(p.num_free - need >= headroom for p, need in zip(self.pools, self.pages_needed(rid, n)))
+        return self._lib.lmsf_cm_can_reserve(self._h, self._id(rid), int(n), int(headroom)) == 1
 
     def reserve(self, rid, n: int) -> None:
         """Claims pages so that positions up to num_reserved + n have one.  All or nothing."""
-        need = self.pages_needed(rid, n)
-        for g, k in enumerate(need):
-            if self.pools[g].num_free < k:
-                raise OutOfPages(f"group {g}: {k} pages needed, {self.pools[g].num_free} free")
-        r = self._reqs[rid]
-        for g, k in enumerate(need):
-            for _ in range(k):
-                r.tables[g].append(self.pools[g].allocate())
-        r.num_reserved += n
+        rc = self._lib.lmsf_cm_reserve(self._h, self._id(rid), int(n))
+        if rc == -1:
+            raise OutOfPages(f"request {rid!r}: not enough free pages for {n} more positions")
+        if rc != 0:
+            raise ValueError(f"reserve({rid!r}, {n}) was refused ({rc})")
 
     def commit(self, rid, n: int) -> None:
         """The keys of n more positions are in the cache.  Window groups give back the pages that no
         later query can reach."""
-        r = self._reqs[rid]
-        if r.num_tokens + n > r.num_reserved:
-            raise ValueError(f"request {rid!r}: commit of {n} tokens beyond the {r.num_reserved} reserved")
-        r.num_tokens += n
-        for g, table in enumerate(r.tables):
-            if self.groups[g].window is None:
-                continue
-            first = self._first_needed_entry(g, r.num_tokens)
-            for i in range(min(first, len(table))):
-                if table[i] >= 0:
-                    self.pools[g].free(table[i])
-                    table[i] = -1
+        rc = self._lib.lmsf_cm_commit(self._h, self._id(rid), int(n))
+        if rc == -4:
+            raise ValueError(f"request {rid!r}: commit of {n} tokens beyond the {self.num_reserved(rid)} reserved")
+        if rc != 0:
+            raise ValueError(f"commit({rid!r}, {n}) failed ({rc})")
 
     def rollback(self, rid) -> None:
         """Forgets a reservation that was not committed (a step that did not run)."""
-        r = self._reqs[rid]
-        entries = (r.num_tokens + self.block_size - 1) // self.block_size
-        for g, table in enumerate(r.tables):
-            while len(table) > entries:
-                b = table.pop()
-                if b >= 0:
-                    self.pools[g].free(b)
-        r.num_reserved = r.num_tokens
+        if self._lib.lmsf_cm_rollback(self._h, self._id(rid)) != 0:
+            raise ValueError(f"rollback({rid!r}) failed")
 
     # ------------------------------------------------------------------ views
     def num_tokens(self, rid) -> int:
-        return self._reqs[rid].num_tokens
+        return self._lib.lmsf_cm_query(self._h, self._id(rid), 0, 0)
 
     def num_reserved(self, rid) -> int:
-        return self._reqs[rid].num_reserved
+        return self._lib.lmsf_cm_query(self._h, self._id(rid), 1, 0)
 
     def state_slot(self, rid) -> int:
-        return self._reqs[rid].slot
+        return self._lib.lmsf_cm_query(self._h, self._id(rid), 2, 0)
 
     def block_table(self, rid, group: int) -> List[int]:
-        return self._reqs[rid].tables[group]
+        nid = self._id(rid)
+        n = self._lib.lmsf_cm_query(self._h, nid, 3, int(group))
+        buf = (ctypes.c_int * max(n, 1))()
+        self._lib.lmsf_cm_table(self._h, nid, int(group), buf, n)
+        return list(buf[:n])
 
     def num_free_pages(self, group: int = 0) -> int:
-        return self.pools[group].num_free
+        return self._lib.lmsf_cm_num_free(self._h, int(group))
 
     def num_total_pages(self, group: int = 0) -> int:
-        return self.pools[group].num_blocks
+        return self._lib.lmsf_cm_num_total(self._h, int(group))
 
     def live_requests(self) -> List[Hashable]:
-        return list(self._reqs)
+        return list(self._ids)
 
     def check_invariants(self) -> None:
         """No page lost, held twice or both free and held (used by tests)."""
-        for g, pool in enumerate(self.pools):
-            held = [b for r in self._reqs.values() for b in r.tables[g] if b >= 0]
-            if len(held) != len(set(held)):
-                raise AssertionError(f"group {g}: a page is held twice")
-            free = set(pool._free)
-            if len(free) != len(pool._free):
-                raise AssertionError(f"group {g}: a page is twice in the free list")
-            if free & set(held):
-                raise AssertionError(f"group {g}: a page is both free and held")
-            if len(free) + len(held) != pool.num_blocks:
-                raise AssertionError(f"group {g}: {pool.num_blocks - len(free) - len(held)} pages are lost")
-        slots = [r.slot for r in self._reqs.values()]
-        if len(slots) != len(set(slots)) or set(slots) & set(self._free_slots) or \
-                len(slots) + len(self._free_slots) != self.num_state_slots:
-            raise AssertionError("state slots are lost or held twice")
+        rc = self._lib.lmsf_cm_check(self._h)
+        if rc:
+            what = {1: "a page is held twice", 2: "a page is twice in the free list", 3: "a page is both free and held",
+                    4: "pages are lost", 5: "state slots are lost or held twice"}.get(rc, str(rc))
+            raise AssertionError(what)
+        if self._lib.lmsf_cm_num_live(self._h) != len(self._ids):
+            raise AssertionError("the native manager and its face disagree on the live requests")

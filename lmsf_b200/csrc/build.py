@@ -1,6 +1,6 @@
-"""Compiles the CUDA sources of this folder for sm_100a with nvcc and loads them with ctypes.
+"""Compiles the sources of this folder (CUDA for sm_100a with nvcc, host C++ with g++) and loads them with ctypes.
 
-Every `.cu` file becomes one shared library with a C ABI, built the first time one of its
+Every `.cu` or `.cpp` file becomes one shared library with a C ABI, built the first time one of its
 functions is asked for and cached under `_build/` next to the sources (or under the
 system's temporary folder if that is not writable).  The cache key is a hash of the
 source, the shared headers and the flags, so an edited file is rebuilt and a stale
@@ -31,6 +31,16 @@ _lock = threading.Lock()
 
 class BuildError(RuntimeError):
     pass
+
+
+HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden"]
+
+
+def _gxx() -> str:
+    for cand in (os.environ.get("CXX"), shutil.which("g++"), shutil.which("c++")):
+        if cand and os.path.isfile(cand) and os.access(cand, os.X_OK):
+            return cand
+    raise BuildError("no C++ compiler was found (looked at $CXX, g++, c++); the host runtime of lmsf_b200 cannot be built")
 
 
 def _nvcc() -> str:
@@ -76,7 +86,8 @@ def _key(source: str, defines: Tuple[str, ...]) -> str:
         with open(os.path.join(CSRC_DIR, name), "rb") as f:
             h.update(name.encode())
             h.update(f.read())
-    h.update(" ".join([*ARCH_FLAGS, *BASE_FLAGS, *defines]).encode())
+    flags = HOST_FLAGS if source.endswith(".cpp") else [*ARCH_FLAGS, *BASE_FLAGS]
+    h.update(" ".join([*flags, *defines]).encode())
     return h.hexdigest()[:16]
 
 
@@ -91,10 +102,15 @@ def compile_source(source: str, defines: Tuple[str, ...] = (), verbose: bool = T
     out = library_path(source, defines)
     if os.path.isfile(out):
         return out
-    cmd = [_nvcc(), *ARCH_FLAGS, *BASE_FLAGS, *extra_flags, *[f"-D{d}" for d in defines], "-I", CSRC_DIR,
-           os.path.join(CSRC_DIR, source), "-o", out + f".tmp{os.getpid()}", "-lcudart"]
+    if source.endswith(".cpp"):      # host code: the C++ compiler alone
+        cmd = [_gxx(), *HOST_FLAGS, *extra_flags, *[f"-D{d}" for d in defines], "-I", CSRC_DIR,
+               os.path.join(CSRC_DIR, source), "-o", out + f".tmp{os.getpid()}"]
+    else:
+        cmd = [_nvcc(), *ARCH_FLAGS, *BASE_FLAGS, *extra_flags, *[f"-D{d}" for d in defines], "-I", CSRC_DIR,
+               os.path.join(CSRC_DIR, source), "-o", out + f".tmp{os.getpid()}", "-lcudart"]
     if verbose:
-        print(f"[lmsf_b200] compiling {source} {' '.join(defines)} for sm_100a ...", file=sys.stderr, flush=True)
+        what = "for the host" if source.endswith(".cpp") else "for sm_100a"
+        print(f"[lmsf_b200] compiling {source} {' '.join(defines)} {what} ...", file=sys.stderr, flush=True)
     t0 = time.time()
     proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     while True:
@@ -109,7 +125,7 @@ def compile_source(source: str, defines: Tuple[str, ...] = (), verbose: bool = T
             os.remove(out + f".tmp{os.getpid()}")
         except OSError:
             pass
-        raise BuildError(f"nvcc failed on {source}:\n{' '.join(cmd)}\n{log}")
+        raise BuildError(f"the compiler failed on {source}:\n{' '.join(cmd)}\n{log}")
     os.replace(out + f".tmp{os.getpid()}", out)
     if verbose:
         print(f"[lmsf_b200]   built {os.path.basename(out)} in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
@@ -128,4 +144,4 @@ def load_library(source: str, defines: Tuple[str, ...] = ()) -> ctypes.CDLL:
 
 
 def all_sources() -> Iterable[str]:
-    return sorted(f for f in os.listdir(CSRC_DIR) if f.endswith(".cu"))
+    return sorted(f for f in os.listdir(CSRC_DIR) if f.endswith((".cu", ".cpp")))

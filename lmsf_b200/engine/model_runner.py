@@ -14,6 +14,7 @@ import numpy as np
 import torch
 
 from ..cache.block_allocator import OutOfPages
+from ..cache import native
 from ..cache.manager import CacheManager
 from ..cache.storage import CacheStorage, plan_groups, split_pages
 from ..parts.base import Q_TILE, CacheGroupView, StepContext
@@ -129,77 +130,47 @@ class ModelRunner:
                 mgr.rollback(rid)
             raise
 
+        # the layout itself is made by the native runtime, straight into pinned memory
         S = len(entries)
-        q_lens = [len(e.tokens) for e in entries]
-        starts = [mgr.num_tokens(e.request_id) for e in entries]
-        ctx_lens = [s + n for s, n in zip(starts, q_lens)]
-        N = sum(q_lens)
-        rows: List[int] = []
-        off = 0
-        for e, n in zip(entries, q_lens):
-            rows.extend(off + int(w) for w in e.want)
-            off += n
-        patch_dst, patch_src, off = [], [], 0
-        for e, n in zip(entries, q_lens):
-            patch_dst.append(off + n - 1 if e.last_from is not None else -1)
-            patch_src.append(e.last_from if e.last_from is not None else 0)
-            off += n
-        dec_ids = [i for i, n in enumerate(q_lens) if n == 1]
-        tile_seq = [i for i, n in enumerate(q_lens) if n > 1 for _ in range(0, n, Q_TILE)]
-        tile_q0 = [q0 for n in q_lens if n > 1 for q0 in range(0, n, Q_TILE)]
-        tile128_seq = [i for i, n in enumerate(q_lens) if n > 1 for _ in range(0, n, 2 * Q_TILE)]
-        tile128_q0 = [q0 for n in q_lens if n > 1 for q0 in range(0, n, 2 * Q_TILE)]
         n_groups = len(self.storage.groups)
-        tables = [[mgr.block_table(e.request_id, g) for e in entries] for g in range(n_groups)]
-        max_blocks = [max(static_blocks or 1, max(len(t) for t in tables[g])) for g in range(n_groups)]
-
-        seg = {}
-        total = 0
-        for name, length in [("token_ids", N), ("positions", N), ("token_seq", N), ("cu_q", S + 1), ("ctx_len", S),
-                             ("state_slot", S), ("patch_dst", S), ("patch_src", S), ("rows", len(rows)),
-                             ("dec_ids", len(dec_ids)),
-                             ("tile_seq", len(tile_seq)), ("tile_q0", len(tile_q0)), ("tile128_seq", len(tile128_seq)),
-                             ("tile128_q0", len(tile128_q0))] + \
-                            [(f"bt{g}", S * max_blocks[g]) for g in range(n_groups)]:
-            seg[name] = (total, length)
-            total += _align(max(length, 1))
-        pinned, event = self._pinned_buffer(total)
-        host = pinned.numpy()
-        host[:total] = -1
-
-        def put(name, values):
-            o, n = seg[name]
-            host[o:o + n] = values
-
+        q_lens = [len(e.tokens) for e in entries]
         tok = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries])
         if tok.min() < 0 or tok.max() >= self.vocab_size:
+            for rid in reserved:
+                mgr.rollback(rid)
             for e in entries:
                 bad = [int(t) for t in e.tokens if not (0 <= int(t) < self.vocab_size)]
                 if bad:
-                    for rid in reserved:
-                        mgr.rollback(rid)
                     raise StepError(f"request {e.request_id!r}: token id {bad[0]} is outside the vocabulary "
                                     f"(0..{self.vocab_size - 1})")
-        put("token_ids", tok.astype(np.int32))
-        put("positions", np.concatenate([np.arange(s, s + n, dtype=np.int32) for s, n in zip(starts, q_lens)]))
-        put("token_seq", np.repeat(np.arange(S, dtype=np.int32), q_lens))
-        put("cu_q", np.concatenate([[0], np.cumsum(q_lens)]).astype(np.int32))
-        put("ctx_len", np.asarray(ctx_lens, dtype=np.int32))
-        slots = [mgr.state_slot(e.request_id) for e in entries]
-        put("state_slot", np.asarray(slots, dtype=np.int32))
-        put("patch_dst", np.asarray(patch_dst, dtype=np.int32))
-        put("patch_src", np.asarray(patch_src, dtype=np.int32))
-        for name, values in (("rows", rows), ("dec_ids", dec_ids), ("tile_seq", tile_seq), ("tile_q0", tile_q0),
-                             ("tile128_seq", tile128_seq), ("tile128_q0", tile128_q0)):
-            if values:
-                put(name, np.asarray(values, dtype=np.int32))
-        for g in range(n_groups):
-            o, _ = seg[f"bt{g}"]
-            bt = host[o:o + S * max_blocks[g]].reshape(S, max_blocks[g])
-            for i, t in enumerate(tables[g]):
-                bt[i, :len(t)] = t
-        return _HostBatch(pinned, event, total, seg, N, S, q_lens, ctx_lens, slots, max_blocks, len(dec_ids),
-                          len(tile_seq), len(tile128_seq), any(d >= 0 for d in patch_dst))
+        tok = np.ascontiguousarray(tok, dtype=np.int32)
+        rids = np.fromiter((mgr.native_id(e.request_id) for e in entries), dtype=np.int64, count=S)
+        q_arr = np.asarray(q_lens, dtype=np.int32)
+        want_counts = np.fromiter((len(e.want) for e in entries), dtype=np.int32, count=S)
+        want_flat = np.fromiter((int(w) for e in entries for w in e.want), dtype=np.int32, count=int(want_counts.sum()))
+        last_from = np.fromiter((-1 if e.last_from is None else int(e.last_from) for e in entries), dtype=np.int32, count=S)
+        seg_arr = np.zeros(2 * (14 + max(n_groups, 1)), dtype=np.int32)
+        info = np.zeros(7 + max(n_groups, 1), dtype=np.int32)
+        ctx_arr = np.zeros(S, dtype=np.int32)
+        ptr = lambda arr: arr.ctypes.data
+        lib, h = native.lib(), mgr.handle()
+        args = (h, S, ptr(rids), ptr(q_arr), ptr(tok), ptr(want_counts), ptr(want_flat), ptr(last_from),
+                int(static_blocks or 0), Q_TILE)
+        rc = lib.lmsf_cm_build_batch(*args, None, 0, ptr(seg_arr), ptr(info), ptr(ctx_arr))
+        if rc != 0:
+            raise StepError(f"the batch could not be laid out ({rc})")
+        total = int(info[6])
+        pinned, event = self._pinned_buffer(total)
+        rc = lib.lmsf_cm_build_batch(*args, pinned.data_ptr(), pinned.numel(), ptr(seg_arr), ptr(info), ptr(ctx_arr))
+        if rc != 0:
+            raise StepError(f"the batch could not be laid out ({rc})")
+        names = ["token_ids", "positions", "token_seq", "cu_q", "ctx_len", "state_slot", "patch_dst", "patch_src", "rows",
+                 "dec_ids", "tile_seq", "tile_q0", "tile128_seq", "tile128_q0"] + [f"bt{g}" for g in range(n_groups)]
+        seg = {name: (int(seg_arr[2 * i]), int(seg_arr[2 * i + 1])) for i, name in enumerate(names)}
+        slots = pinned[seg["state_slot"][0]:seg["state_slot"][0] + S].tolist()
+        return _HostBatch(pinned, event, total, seg, int(info[0]), S, q_lens, ctx_arr.tolist(), slots,
+                          [int(info[7 + g]) for g in range(n_groups)], int(info[2]), int(info[3]), int(info[4]),
+                          bool(info[5]))
 
     def _pinned_buffer(self, n_ints: int):
         """A pinned host buffer from a small ring; a buffer is used again only after the copy that last read it."""
