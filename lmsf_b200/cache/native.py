@@ -36,7 +36,7 @@ def lib():
             "lmsf_cm_live": (c_int, [c_void_p, P_I64, c_int]),
             "lmsf_cm_check": (c_int, [c_void_p]),
             "lmsf_cm_build_batch": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                            c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p]),
+                                            c_int, c_int, c_int, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p]),
             "lmsf_pool_create": (c_void_p, [c_int]),
             "lmsf_pool_destroy": (None, [c_void_p]),
             "lmsf_pool_allocate": (c_int, [c_void_p]),

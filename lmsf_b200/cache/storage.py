@@ -73,8 +73,10 @@ class CacheStorage:
             raise ValueError(f"the model has {len(self.groups)} cache groups, {len(num_blocks)} page counts given")
         self.num_blocks = list(num_blocks)
         self.num_state_slots = num_state_slots
-        self.tensors = [torch.zeros((len(gl.calls), n, 2, gl.spec.num_kv_heads, block_size, gl.spec.head_dim),
+        # one page more than the pool knows: the "null page" that stand-in requests of a padded batch write to
+        self.tensors = [torch.zeros((len(gl.calls), n + 1, 2, gl.spec.num_kv_heads, block_size, gl.spec.head_dim),
                                     dtype=dtype, device=device) for gl, n in zip(self.groups, num_blocks)]
+        self.null_pages = list(num_blocks)
         self.layer_caches: List[LayerCache] = []
         self.state_tensors: List[Optional[torch.Tensor]] = []
         for j, call in enumerate(model.calls):

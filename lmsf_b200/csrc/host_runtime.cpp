@@ -282,16 +282,21 @@ LMSF_HOST_API int lmsf_cm_check(void* h) {
 //   7 patch_src[S]  8 rows[R]  9 dec_ids[n_dec]  10 tile_seq[T64]  11 tile_q0[T64]  12 tile128_seq[T128]
 //   13 tile128_q0[T128]  14.. block table of group g [S * max_blocks[g]]
 // info: 0 N, 1 R, 2 n_dec, 3 T64, 4 T128, 5 has_patches, 6 total ints, 7.. max_blocks per group.
+// With pad_to > S the batch is filled up to pad_to requests with stand-ins that bring one token (id 0 at
+// position 0) and whose block tables name null_pages[g], a page outside the pools: a decode batch can then be
+// replayed from a graph captured for a rounder size.  Their logits rows come after the real ones.
 // With out == nullptr only the sizes are computed.  Returns 0, -2 for an unknown request, -4 when cap is too small.
 LMSF_HOST_API int lmsf_cm_build_batch(void* h, int S, const int64_t* rids, const int* q_lens, const int* tokens_flat,
                                       const int* want_counts, const int* want_flat, const int* last_from,
-                                      int static_blocks, int q_tile, int* out, long long cap, int* seg, int* info,
-                                      int* ctx_lens_out) {
+                                      int static_blocks, int q_tile, int pad_to, const int* null_pages, int* out,
+                                      long long cap, int* seg, int* info, int* ctx_lens_out) {
   Manager& m = *M(h);
   const int G = (int)m.pools.size();
+  const int n_real = S;
+  const int n_pad = pad_to > S ? pad_to - S : 0;
   std::vector<const Request*> rq(S);
-  long long N = 0, R = 0;
-  int n_dec = 0, t64 = 0, t128 = 0, has_patches = 0;
+  long long N = n_pad, R = n_pad;
+  int n_dec = n_pad, t64 = 0, t128 = 0, has_patches = 0;
   std::vector<int> max_blocks(G, std::max(static_blocks, 1));
   for (int s = 0; s < S; ++s) {
     auto it = m.reqs.find(rids[s]);
@@ -305,6 +310,7 @@ LMSF_HOST_API int lmsf_cm_build_batch(void* h, int S, const int64_t* rids, const
     for (int g = 0; g < G; ++g) max_blocks[g] = std::max<int>(max_blocks[g], (int)rq[s]->tables[g].size());
   }
   auto align4 = [](long long n) { return (std::max<long long>(n, 1) + 3) / 4 * 4; };
+  S += n_pad;                                   // from here on S counts the stand-ins too
   const long long lens[14] = {N, N, N, S + 1, S, S, S, S, R, n_dec, t64, t64, t128, t128};
   long long total = 0;
   for (int i = 0; i < 14; ++i) { seg[2 * i] = (int)total; seg[2 * i + 1] = (int)lens[i]; total += align4(lens[i]); }
@@ -323,10 +329,10 @@ LMSF_HOST_API int lmsf_cm_build_batch(void* h, int S, const int64_t* rids, const
   int* cu_q = out + seg[6]; int* ctx_len = out + seg[8]; int* state_slot = out + seg[10];
   int* patch_dst = out + seg[12]; int* patch_src = out + seg[14]; int* rows = out + seg[16]; int* dec_ids = out + seg[18];
   int* tile_seq = out + seg[20]; int* tile_q0 = out + seg[22]; int* tile128_seq = out + seg[24]; int* tile128_q0 = out + seg[26];
-  std::memcpy(token_ids, tokens_flat, sizeof(int) * N);
+  std::memcpy(token_ids, tokens_flat, sizeof(int) * (N - n_pad));
   int off = 0, r = 0, w = 0, d = 0, a = 0, b = 0;
   cu_q[0] = 0;
-  for (int s = 0; s < S; ++s) {
+  for (int s = 0; s < n_real; ++s) {
     const int n = q_lens[s], start = rq[s]->num_tokens;
     for (int i = 0; i < n; ++i) { positions[off + i] = start + i; token_seq[off + i] = s; }
     cu_q[s + 1] = off + n;
@@ -347,6 +353,18 @@ LMSF_HOST_API int lmsf_cm_build_batch(void* h, int S, const int64_t* rids, const
       std::copy(t.begin(), t.end(), bt);
     }
     off += n;
+  }
+  for (int s = n_real; s < S; ++s) {            // stand-ins
+    token_ids[off] = 0; positions[off] = 0; token_seq[off] = s;
+    cu_q[s + 1] = off + 1;
+    ctx_len[s] = 1;
+    ctx_lens_out[s] = 1;
+    state_slot[s] = 0;
+    patch_dst[s] = -1; patch_src[s] = 0;
+    rows[r++] = off;
+    dec_ids[d++] = s;
+    for (int g = 0; g < G; ++g) out[seg[2 * (14 + g)] + (long long)s * max_blocks[g]] = null_pages[g];
+    off += 1;
   }
   return 0;
 }

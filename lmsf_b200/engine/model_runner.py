@@ -101,7 +101,8 @@ class ModelRunner:
         return self.storage.make_manager()
 
     # ------------------------------------------------------------------ building a batch
-    def _prepare(self, entries: Sequence[StepEntry], mgr: CacheManager, static_blocks: Optional[int] = None) -> "_HostBatch":
+    def _prepare(self, entries: Sequence[StepEntry], mgr: CacheManager, static_blocks: Optional[int] = None,
+                 pad_to: int = 0) -> "_HostBatch":
         """Checks the entries, reserves the pages they need (all or nothing) and lays the batch out in one
         int32 host buffer whose segments are 16-byte aligned."""
         if not entries:
@@ -151,11 +152,13 @@ class ModelRunner:
         last_from = np.fromiter((-1 if e.last_from is None else int(e.last_from) for e in entries), dtype=np.int32, count=S)
         seg_arr = np.zeros(2 * (14 + max(n_groups, 1)), dtype=np.int32)
         info = np.zeros(7 + max(n_groups, 1), dtype=np.int32)
-        ctx_arr = np.zeros(S, dtype=np.int32)
+        S_pad = max(S, pad_to)
+        ctx_arr = np.zeros(S_pad, dtype=np.int32)
+        null_pages = np.asarray(self.storage.null_pages or [0], dtype=np.int32)
         ptr = lambda arr: arr.ctypes.data
         lib, h = native.lib(), mgr.handle()
         args = (h, S, ptr(rids), ptr(q_arr), ptr(tok), ptr(want_counts), ptr(want_flat), ptr(last_from),
-                int(static_blocks or 0), Q_TILE)
+                int(static_blocks or 0), Q_TILE, int(pad_to), ptr(null_pages))
         rc = lib.lmsf_cm_build_batch(*args, None, 0, ptr(seg_arr), ptr(info), ptr(ctx_arr))
         if rc != 0:
             raise StepError(f"the batch could not be laid out ({rc})")
@@ -167,8 +170,8 @@ class ModelRunner:
         names = ["token_ids", "positions", "token_seq", "cu_q", "ctx_len", "state_slot", "patch_dst", "patch_src", "rows",
                  "dec_ids", "tile_seq", "tile_q0", "tile128_seq", "tile128_q0"] + [f"bt{g}" for g in range(n_groups)]
         seg = {name: (int(seg_arr[2 * i]), int(seg_arr[2 * i + 1])) for i, name in enumerate(names)}
-        slots = pinned[seg["state_slot"][0]:seg["state_slot"][0] + S].tolist()
-        return _HostBatch(pinned, event, total, seg, int(info[0]), S, q_lens, ctx_arr.tolist(), slots,
+        slots = pinned[seg["state_slot"][0]:seg["state_slot"][0] + S_pad].tolist()
+        return _HostBatch(pinned, event, total, seg, int(info[0]), S_pad, q_lens + [1] * (S_pad - S), ctx_arr.tolist(), slots,
                           [int(info[7 + g]) for g in range(n_groups)], int(info[2]), int(info[3]), int(info[4]),
                           bool(info[5]))
 
@@ -215,6 +218,15 @@ class ModelRunner:
         return self._context(hb, self._upload(hb))
 
     # ------------------------------------------------------------------ the step
+    @staticmethod
+    def graph_batch_size(n: int) -> int:
+        """Decode batches are replayed from graphs of these sizes: 1, 2, 4, then multiples of 8."""
+        if n <= 2:
+            return n
+        if n <= 4:
+            return 4
+        return (n + 7) // 8 * 8
+
     def _graph_eligible(self, entries: Sequence[StepEntry]) -> bool:
         return (not self.enforce_eager and self.graph_safe and len(entries) <= self.max_graph_batch
                 and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries))
@@ -234,10 +246,12 @@ class ModelRunner:
         of the entries and of their `want`.  Afterwards the tokens count as cached (`mgr.commit`).
 
         A batch in which every request brings one token and wants its logits is replayed from a CUDA graph
-        (one graph per batch size, captured the second time the size is seen); the returned tensor is then
-        the graph's own output buffer and holds its values until the next step of the same size."""
+        (batch sizes are rounded up to 1, 2, 4 or a multiple of 8 with stand-in requests that touch only a
+        spare page; a graph is captured the second time its size is seen); the returned tensor is then a view
+        of the graph's own output buffer and holds its values until the next step of the same size."""
         graph_mode = self._graph_eligible(entries)
-        hb = self._prepare(entries, mgr, self.static_blocks if graph_mode else None)
+        hb = self._prepare(entries, mgr, self.static_blocks if graph_mode else None,
+                           self.graph_batch_size(len(entries)) if graph_mode else 0)
         self.storage.zero_state_slots(mgr.take_fresh_slots())
         if graph_mode and (hb.S in self._graphs or hb.S in self._seen_sizes):
             logits = self._replay(hb, pending_tokens)
@@ -252,7 +266,7 @@ class ModelRunner:
             mgr.commit(e.request_id, len(e.tokens))
         if check:
             self.check_device_errors()
-        return logits
+        return logits[:len(entries)] if graph_mode else logits
 
     def _replay(self, hb: "_HostBatch", pending_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         g = self._graphs.get(hb.S)
