@@ -88,11 +88,11 @@ def bench_prefill_attention(args, dev, timer, pk):
     cl = torch.tensor([T], dtype=torch.int32, device=dev)
     n_tiles = (T + 63) // 64
     ts = torch.zeros(n_tiles, dtype=torch.int32, device=dev)
-    tq = torch.arange(0, T, 64, dtype=torch.int32, device=dev)
+    tq = torch.arange(0, T, 64, dtype=torch.int32, device=dev).flip(0).contiguous()      # longest tiles first
     if args.tc:
         n_tiles = (T + 127) // 128
         ts = torch.zeros(n_tiles, dtype=torch.int32, device=dev)
-        tq = torch.arange(0, T, 128, dtype=torch.int32, device=dev)
+        tq = torch.arange(0, T, 128, dtype=torch.int32, device=dev).flip(0).contiguous()     # longest tiles first
         fn = lambda: kernels.attention_prefill_tc(out, q, cache, bt, args.block_size, ts, tq, n_tiles, cu, cl,
                                                   1 / math.sqrt(hd), 0, nh, nkv, hd)
     else:

@@ -20,8 +20,10 @@ struct PrefillArgs {
 // that holds ctx keys after this step sits at position ctx - n + i and sees keys lo..position.
 __global__ void __launch_bounds__(kThreads) prefill_kernel(PrefillArgs a) {
   extern __shared__ __align__(16) unsigned char smem[];
-  const int seq = a.tile_seq[blockIdx.x], q0 = a.tile_q0[blockIdx.x];
-  const int head = blockIdx.y, kvh = head / a.group;
+  // blocks start in the order (all heads of tile 0, all heads of tile 1, ...); the caller lists the tiles that
+  // see the most keys first
+  const int seq = a.tile_seq[blockIdx.y], q0 = a.tile_q0[blockIdx.y];
+  const int head = blockIdx.x, kvh = head / a.group;
   const int tok0 = a.cu_q[seq], n = a.cu_q[seq + 1] - tok0, ctx = a.ctx_len[seq];
   const int start = ctx - n;                                    // position of the portion's first token
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -182,7 +184,7 @@ LMSF_API int lmsf_attention_prefill(const void* q, long long q_stride, void* out
   if (head_dim != HD) LMSF_REFUSE("attention_prefill: built for head_dim=%d, called with %d", HD, head_dim);
   if (n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads)
     LMSF_REFUSE("attention_prefill: %d query heads cannot be grouped over %d kv heads", n_q_heads, n_kv_heads);
-  if (n_q_heads > 65535) LMSF_REFUSE("attention_prefill: more than 65535 query heads");
+  if (n_tiles > 65535) LMSF_REFUSE("attention_prefill: more than 65535 query tiles in one launch");
   if (block_size <= 0 || max_blocks <= 0) LMSF_REFUSE("attention_prefill: bad block table geometry");
   PrefillArgs a;
   a.q = (const bf16*)q; a.q_stride = q_stride; a.out = (bf16*)out; a.out_stride = out_stride;
@@ -198,6 +200,6 @@ LMSF_API int lmsf_attention_prefill(const void* q, long long q_stride, void* out
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  prefill_kernel<<<dim3(n_tiles, n_q_heads), kThreads, smem, (cudaStream_t)stream>>>(a);
+  prefill_kernel<<<dim3(n_q_heads, n_tiles), kThreads, smem, (cudaStream_t)stream>>>(a);
   return LMSF_LAUNCH_STATUS();
 }

@@ -197,10 +197,11 @@ __global__ void __launch_bounds__(128) prefill_tc_kernel(Args a) {
   const uint32_t mbar_s = smem_u32(&mbar_s_mem), mbar_o = smem_u32(&mbar_o_mem);
   const int tid = threadIdx.x, warp = tid >> 5;
 
-  // the tile list is walked backwards: the last tiles of a portion see the most keys and should start first
-  const int tile = gridDim.x - 1 - blockIdx.x;
+  // blocks start in the order (all heads of tile 0, all heads of tile 1, ...); the caller lists the tiles that
+  // see the most keys first, so the longest blocks are not left for the end
+  const int tile = blockIdx.y;
   const int seq = a.tile_seq[tile], q0 = a.tile_q0[tile];
-  const int head = blockIdx.y, kvh = head / a.group;
+  const int head = blockIdx.x, kvh = head / a.group;
   const int tok0 = a.cu_q[seq], n = a.cu_q[seq + 1] - tok0, ctx = a.ctx_len[seq];
   const int start = ctx - n;
   const int rows_valid = min(BM, n - q0);
@@ -373,7 +374,7 @@ __global__ void __launch_bounds__(128) prefill_tc_kernel(Args a) {
   cp_async_wait<0>();
 #ifdef LMSF_TC_TIMING
   if (tid == 127 && g_timing) {
-    long long* t = g_timing + ((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 9;
+    long long* t = g_timing + ((size_t)blockIdx.x * gridDim.y + blockIdx.y) * 9;
     for (int i = 0; i < 8; ++i) t[i] = tacc[i];
     t[8] = n_tiles;
   }
@@ -419,7 +420,8 @@ LMSF_API int lmsf_attention_tc_set_timing(long long* buf) {
 }
 #endif
 
-// tile_seq / tile_q0: one entry per 128 query tokens of each portion.  q and out rows must be 16-byte aligned.
+// tile_seq / tile_q0: one entry per 128 query tokens of each portion, best listed with the tiles that see the
+// most keys first.  q and out rows must be 16-byte aligned.
 LMSF_API int lmsf_attention_prefill_tc(const void* q, long long q_stride, void* out, long long out_stride,
                                        const void* cache, long long page_stride, int block_size, int n_kv_heads,
                                        const int* block_table, int max_blocks, const int* tile_seq, const int* tile_q0,
@@ -431,7 +433,7 @@ LMSF_API int lmsf_attention_prefill_tc(const void* q, long long q_stride, void* 
   if (head_dim != HD) LMSF_REFUSE("attention_prefill_tc: built for head_dim=%d, called with %d", HD, head_dim);
   if (n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads)
     LMSF_REFUSE("attention_prefill_tc: %d query heads cannot be grouped over %d kv heads", n_q_heads, n_kv_heads);
-  if (n_q_heads > 65535) LMSF_REFUSE("attention_prefill_tc: more than 65535 query heads");
+  if (n_tiles > 65535) LMSF_REFUSE("attention_prefill_tc: more than 65535 query tiles in one launch");
   if (max_blocks <= 0) LMSF_REFUSE("attention_prefill_tc: bad block table geometry");
   if (q_stride % 8 || out_stride % 8 || ((uintptr_t)q | (uintptr_t)out | (uintptr_t)cache) % 16 || page_stride % 8)
     LMSF_REFUSE("attention_prefill_tc: q, out and the cache must be 16-byte aligned with row strides that are multiples of 8");
@@ -448,6 +450,6 @@ LMSF_API int lmsf_attention_prefill_tc(const void* q, long long q_stride, void* 
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  prefill_tc_kernel<<<dim3(n_tiles, n_q_heads), 128, kSmemBytes, (cudaStream_t)stream>>>(a);
+  prefill_tc_kernel<<<dim3(n_q_heads, n_tiles), 128, kSmemBytes, (cudaStream_t)stream>>>(a);
   return LMSF_LAUNCH_STATUS();
 }

@@ -354,6 +354,23 @@ LMSF_HOST_API int lmsf_cm_build_batch(void* h, int S, const int64_t* rids, const
     }
     off += n;
   }
+  // Query tiles in the order of the keys they see, most first: the kernels start blocks in list order, and a
+  // prompt's last tiles are its longest.
+  auto sort_tiles = [&](int* tseq, int* tq0, int count, int tile) {
+    std::vector<int> idx(count), key(count);
+    for (int i = 0; i < count; ++i) {
+      idx[i] = i;
+      const int sq = tseq[i];
+      key[i] = rq[sq]->num_tokens + std::min(tq0[i] + tile, q_lens[sq]);
+    }
+    std::stable_sort(idx.begin(), idx.end(), [&](int x, int y) { return key[x] > key[y]; });
+    std::vector<int> a2(count), b2(count);
+    for (int i = 0; i < count; ++i) { a2[i] = tseq[idx[i]]; b2[i] = tq0[idx[i]]; }
+    std::copy(a2.begin(), a2.end(), tseq);
+    std::copy(b2.begin(), b2.end(), tq0);
+  };
+  sort_tiles(tile_seq, tile_q0, a, q_tile);
+  sort_tiles(tile128_seq, tile128_q0, b, 2 * q_tile);
   for (int s = n_real; s < S; ++s) {            // stand-ins
     token_ids[off] = 0; positions[off] = 0; token_seq[off] = s;
     cu_q[s + 1] = off + 1;
