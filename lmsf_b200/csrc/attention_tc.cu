@@ -5,19 +5,30 @@
 // Counterpart in the reference: the dense float32 prompt attention of
 // core/src/model_executor/layers/attention.rs:106-159.
 //
-// One block of 128 threads serves 128 query tokens of one head.  Per tile of 64 keys:
-//   1. k and v rows are gathered from their pages into shared memory with cp.async, in the 128-byte
-//      swizzled layout that the tensor core reads (k: K-major, v: MN-major); the next tile's rows are
-//      requested while this tile's scores are computed;
-//   2. one thread issues S = Q K^T (M 128, N 64, K head size) into tensor memory and commits to an mbarrier;
-//   3. every thread owns one query row: it reads its 64 scores with tcgen05.ld, masks, updates the running
-//      maximum (the accumulator is rescaled only when the maximum grew by more than 2^8, which keeps the
-//      sums exact and saves most read-modify-writes of tensor memory), exponentiates in float32 and writes
-//      P as bfloat16 into the shared memory that held the k tile;
-//   4. one thread issues O += P V (M 128, N head size, K 64) and commits.
-// Two blocks share an SM (96 KB of shared memory and 256 columns of tensor memory each), so one block's
-// softmax overlaps the other's products.  Every wait on an mbarrier is bounded: when it runs out the
-// block raises *error_flag (code 3), frees its tensor memory and returns.
+// One block serves 128 query tokens of TWO query heads that share a kv head (one head where the group has an
+// odd head left over), so that every k and v tile is fetched once for both.  Its warps have three roles:
+//   * two producer warps, one for k and one for v, bring tiles of 64 keys from their pages into rings of shared-memory stages
+//     with tensor-map copies (cp.async.bulk.tensor, one box per page and 64 head elements, 128-byte swizzled
+//     by the copy engine; k is read K-major, v MN-major); the copies' bytes are counted on mbarriers.  Pages
+//     of fewer than 8 keys are gathered with cp.async instead;
+//   * an issuing warp launches, for each head, S = Q K^T (M 128, N 64, K head size) into one of the head's two
+//     score buffers in tensor memory and, when the head's P is ready, O += P V (M 128, N head size, K 64);
+//     completion goes to mbarriers through tcgen05.commit.  The scores of tile j + 1 are computed while tile
+//     j's softmax runs, and a k stage is free again as soon as both heads' scores are done;
+//   * two groups of four softmax warps, one per head, one query row per thread: tcgen05.ld of the row's 64
+//     scores, mask, running maximum (the accumulator is rescaled only when the maximum grew by more than 2^8,
+//     which keeps the sums exact and saves most read-modify-writes of tensor memory), exponentials in
+//     float32, P as bfloat16 into the head's own tile of shared memory.
+// One block per SM: all 512 columns of tensor memory (2 x 2 score buffers of 64, 2 accumulators of 128) and
+// about 190 KB of shared memory.  Every wait on an mbarrier is bounded: when one runs out the block raises
+// *error_flag (code 3), frees its tensor memory and returns.
+#include <cuda.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+#include <type_traits>
+
 #include "attention_mma.cuh"
 
 #ifndef LMSF_HEAD_DIM
@@ -31,27 +42,43 @@ namespace tc {
 
 using namespace lmsf::fa;
 
+// -DLMSF_TC_TIMING (development aid): lane 0 of warp 0 (softmax), of the k producer and of the issuing warp adds the
+// clock cycles of its phases to a buffer given by lmsf_attention_tc_set_timing, 16 counters per block; the block
+// with the most keys also writes a timeline of its first 64 tiles behind the counters (offset 2^20).
 #ifdef LMSF_TC_TIMING
-// Development aid: thread 127 of every block adds the cycles it spent in each phase of the loop.
 __device__ long long* g_timing = nullptr;
-#define LMSF_T(i) do { if (tid == 127) { const long long now_ = clock64(); tacc[i] += now_ - tlast; tlast = now_; } } while (0)
+#define LMSF_T_BEGIN() long long tlast_ = clock64(); long long tacc_[16] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}
+#define LMSF_T(i) do { const long long now_ = clock64(); tacc_[i] += now_ - tlast_; tlast_ = now_; } while (0)
+#define LMSF_TRACE(role, j, k) do { if (g_timing && blockIdx.x == 0 && blockIdx.y == gridDim.y - 1 && (threadIdx.x & 31) == 0 && (j) < 64) g_timing[1 << 20 | ((role) * 64 + (j)) * 4 + (k)] = clock64(); } while (0)
+#define LMSF_T_END() do { if (g_timing && (threadIdx.x & 31) == 0 && ((threadIdx.x >> 5) == 0 || (threadIdx.x >> 5) == 8 || (threadIdx.x >> 5) == 10)) { \
+    long long* out_ = g_timing + ((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 16; \
+    for (int i_ = 0; i_ < 16; ++i_) if (tacc_[i_]) out_[i_] += tacc_[i_]; } } while (0)
 #else
+#define LMSF_TRACE(role, j, k) do {} while (0)
+#define LMSF_T_BEGIN() do {} while (0)
 #define LMSF_T(i) do {} while (0)
+#define LMSF_T_END() do {} while (0)
 #endif
+
 
 constexpr int HD = LMSF_HEAD_DIM;
 static_assert(HD == 64 || HD == 128, "the tcgen05 attention kernel takes head sizes 64 and 128");
-constexpr int BM = 128;                    // query rows per block
-constexpr int BN = 64;                     // keys per tile
+constexpr int BM = 128;                    // query rows per head and block
+constexpr int BN = 128;                    // keys per tile
 constexpr int kHB = HD / 64;               // 64-wide blocks of the head dimension
-constexpr int kQBytes = kHB * BM * 128;
+#ifndef LMSF_TC_STAGES
+#define LMSF_TC_STAGES 2
+#endif
+constexpr int kStages = LMSF_TC_STAGES;    // k tiles in flight, and v tiles
+constexpr int kQBytes = kHB * BM * 128;    // one head's queries
 constexpr int kKBytes = kHB * BN * 128;    // one k (or v) tile
-constexpr int kPBytes = BM * 128;          // P: 128 rows x 64 keys, written over the k tile once S is done
-constexpr int kKSlot = kKBytes > kPBytes ? kKBytes : kPBytes;
-constexpr int kStageBytes = kKSlot + kKBytes;   // k (later P), then v
-constexpr int kSmemBytes = kQBytes + 2 * kStageBytes + 1024;   // + slack for the 1024-byte alignment
-constexpr uint32_t kTmemCols = 256;        // S: columns [0, 64), O: columns [128, 128 + HD)
-constexpr uint32_t kOCol = 128;
+constexpr int kOffK = 2 * kQBytes, kOffV = kOffK + kStages * kKBytes;
+constexpr int kSmemBytes = kOffV + kStages * kKBytes + 1024;   // + slack for the 1024-byte alignment
+static_assert(kSmemBytes <= 227 * 1024, "too many stages for the shared memory of an SM");
+// Tensor memory, 512 columns: S of head x in [128x, 128x + 128), and P (bfloat16 pairs) over its first 64
+// columns once the scores are in registers; O of head x in [256 + 128x, +HD).
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kOCol = 256;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;  // in log2 units
 constexpr int kWaitLimit = 1 << 22;
@@ -66,6 +93,8 @@ struct Args {
   float scale; int window;
   int n_q_heads, group;
   int* error_flag;
+  int use_tma;      // k and v tiles come by tensor-map copies (block_size >= 8), else by cp.async
+  int rows_box;     // keys per tensor-map copy: min(block_size, 64)
 };
 
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
@@ -86,15 +115,13 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t da, uint64_t db, 
   asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
                ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
 }
+// the same with the A operand in tensor memory (row m in lane m, two bfloat16 per column)
+__device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+               ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t mbar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar) : "memory");
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t mbar, uint32_t parity) {
-  uint32_t done = 0;
-  for (int it = 0; it < kWaitLimit && !done; ++it)
-    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.b32 %0, 1, 0, p;\n}\n"
-                 : "=r"(done) : "r"(mbar), "r"(parity) : "memory");
-  return done != 0;
 }
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,"
@@ -124,289 +151,490 @@ __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.a
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-// k and v of keys [key0, key0 + 64) of kv head kvh into a stage: [64-wide block of the head][key][128 bytes],
-// 16-byte chunk c of a row at chunk c ^ (key & 7).  Keys outside [lo, hi) or without a page are zero-filled.
-constexpr int kNoPrefetch = -2;    // `page_hint` of load_kv_tile: look the page up now
+// ---- roles ---------------------------------------------------------------------------------------------
+// warps 0-3: softmax of the first head, one query row per thread (thread t owns lane t % 128 of tensor memory)
+// warps 4-7: softmax of the second head
+// warp 8   : producer of k tiles
+// warp 9   : producer of v tiles
+// warp 10  : issues the tensor-core products
+constexpr int kSoftmaxThreads = 128;       // per head
+constexpr int kThreadsTotal = 352;
 
-// The page that holds the first row this thread copies of tile [key0, key0 + 64), or -1.  With a block size of
-// at least the rows a thread copies (and both powers of two) all of a thread's rows of a tile share that page.
-__device__ __forceinline__ int tile_page(const PagedKV& kv, const int* __restrict__ table, int key0, int lo, int hi) {
+__device__ __forceinline__ bool mbar_wait_f(uint32_t mbar, uint32_t parity, volatile int* failed) {
+  uint32_t done = 0;
+  for (int it = 0; it < kWaitLimit && !done; ++it) {
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.b32 %0, 1, 0, p;\n}\n"
+                 : "=r"(done) : "r"(mbar), "r"(parity) : "memory");
+    if (!done && *failed) return false;
+  }
+  if (!done) *failed = 1;
+  return done != 0;
+}
+// the same without the early way out: used to let a block's own copies land before it ends
+__device__ __forceinline__ void mbar_wait_drain(uint32_t mbar, uint32_t parity) {
+  uint32_t done = 0;
+  for (int it = 0; it < kWaitLimit && !done; ++it)
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.b32 %0, 1, 0, p;\n}\n"
+                 : "=r"(done) : "r"(mbar), "r"(parity) : "memory");
+}
+__device__ __forceinline__ void mbar_init(uint32_t mbar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(mbar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t mbar) {
+  asm volatile("{\n.reg .b64 st;\nmbarrier.arrive.shared::cta.b64 st, [%0];\n}\n" ::"r"(mbar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t mbar, uint32_t bytes) {
+  asm volatile("{\n.reg .b64 st;\nmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n}\n" ::"r"(mbar), "r"(bytes) : "memory");
+}
+// the barrier gets one arrival when all cp.async of this thread so far have landed
+__device__ __forceinline__ void cp_async_arrive(uint32_t mbar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(mbar) : "memory");
+}
+// One box of the cache's tensor map (64 head elements x rows_box keys of one k or v head of one page) into
+// shared memory, 128-byte swizzled by the copy engine; its bytes are counted on the mbarrier.
+__device__ __forceinline__ void tma_load_box(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint32_t mbar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(mbar) : "memory");
+}
+
+// Where pages are too small for tensor-map copies: the producer warp's cp.async gather of k (or v) of keys
+// [key0, key0 + 64) of kv head kvh into a tile: [64-wide block of the head][key][128 bytes], 16-byte chunk c of
+// a row at chunk c ^ (key & 7).  Keys outside [lo, hi) or without a page are zero-filled.
+__device__ __forceinline__ void gather_tile(uint32_t dst_tile, const PagedKV& kv, const int* __restrict__ table, int max_blocks,
+                                            int kvh, bool is_v, int key0, int lo, int hi, int lane) {
   constexpr int kChunks = HD / 8;
-  constexpr int kRowsPerThread = BN * kChunks / 128;
-  const int key = key0 + (threadIdx.x / kChunks) * kRowsPerThread;
-  // a row range that straddles lo or hi still lies in one page; rows outside [lo, hi) are zero-filled anyway
-  const int probe = min(max(key, lo), hi - 1);
-  if (probe < key || probe >= key + kRowsPerThread) return -1;
-  return table[probe >> kv.block_shift];
-}
-
-__device__ __forceinline__ void load_kv_tile(uint32_t stage, const PagedKV& kv, const int* __restrict__ table, int kvh,
-                                             int key0, int lo, int hi, int page_hint) {
-  constexpr int kChunks = HD / 8;                       // 16-byte chunks per row
-  constexpr int kRowsPerThread = BN * kChunks / 128;    // consecutive rows per thread
-  const size_t v_off = (size_t)kv.n_kv_heads * kv.block_size * HD;
-  const size_t head_off = (size_t)kvh * kv.block_size * HD;
+  constexpr int kRowsPerPass = 32 / kChunks;
+  const size_t head_off = ((size_t)(is_v ? kv.n_kv_heads : 0) + kvh) * kv.block_size * HD;
   const int mask = kv.block_size - 1;
-  const int c = threadIdx.x % kChunks, row0 = (threadIdx.x / kChunks) * kRowsPerThread;
+  const int c = lane % kChunks, r0 = lane / kChunks;
   const uint32_t col = (c / 8) * (BN * 128);
-  const bf16* page_ptr = nullptr;
-  bool have_page = false;
-  if (page_hint != kNoPrefetch) {
-    page_ptr = page_hint >= 0 ? kv.cache + (size_t)page_hint * kv.page_stride + head_off + c * 8 : nullptr;
-    have_page = true;
-    if (key0 >= lo && key0 + BN <= hi && page_ptr != nullptr) {
-      // the common case: every key of the tile is wanted and this thread's rows sit in one page, one after
-      // the other: the addresses are the first one plus constants
-      const bf16* src = page_ptr + (size_t)((key0 + row0) & mask) * HD;
-      const uint32_t dst = stage + col + row0 * 128;                   // row0 is a multiple of 8 or kRowsPerThread <= 8
-#pragma unroll
-      for (int it = 0; it < kRowsPerThread; ++it) {
-        const uint32_t d = dst + it * 128 + (((c & 7) ^ ((row0 + it) & 7)) << 4);
-        cp_async_16(d, src + it * HD, 16);
-        cp_async_16(d + kKSlot, src + v_off + it * HD, 16);
-      }
-      return;
-    }
-  }
-#pragma unroll
-  for (int it = 0; it < kRowsPerThread; ++it) {
-    const int row = row0 + it, key = key0 + row, slot = key & mask;
-    const bool in_range = key >= lo && key < hi;
-    if (page_hint == kNoPrefetch) {
-      if (slot == 0) have_page = false;
-      if (in_range && !have_page) {
-        const int page = table[key >> kv.block_shift];
-        page_ptr = page >= 0 ? kv.cache + (size_t)page * kv.page_stride + head_off + c * 8 : nullptr;
-        have_page = true;
-      }
-    }
-    const bool ok = in_range && page_ptr != nullptr;
-    const bf16* src = ok ? page_ptr + (size_t)slot * HD : kv.cache;
-    const uint32_t dst = stage + col + row * 128 + (((c & 7) ^ (row & 7)) << 4);
-    cp_async_16(dst, src, ok ? 16 : 0);
-    cp_async_16(dst + kKSlot, ok ? src + v_off : src, ok ? 16 : 0);
+#pragma unroll 4
+  for (int p = 0; p < BN / kRowsPerPass; ++p) {
+    const int row = p * kRowsPerPass + r0, key = key0 + row, blk = key >> kv.block_shift;
+    const int page = (key >= lo && key < hi && blk < max_blocks) ? table[blk] : -1;
+    const bool ok = page >= 0;
+    const bf16* src = ok ? kv.cache + (size_t)page * kv.page_stride + head_off + (size_t)(key & mask) * HD + c * 8 : kv.cache;
+    cp_async_16(dst_tile + col + row * 128 + (((c & 7) ^ (row & 7)) << 4), src, ok ? 16 : 0);
   }
 }
 
-__global__ void __launch_bounds__(128) prefill_tc_kernel(Args a) {
+__global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args a, const __grid_constant__ CUtensorMap kv_map) {
   extern __shared__ unsigned char smem_raw[];
-  __shared__ __align__(8) uint64_t mbar_s_mem, mbar_o_mem;
+  // k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages], s_full[head], p_full[head], o_done[head]
+  __shared__ __align__(8) uint64_t bars[4 * kStages + 6];
   __shared__ uint32_t tmem_base_mem;
+  __shared__ int failed_mem;
+  volatile int* failed = &failed_mem;
   const uint32_t smem = (smem_u32(smem_raw) + 1023u) & ~1023u;     // the swizzle pattern is a function of the address
-  const uint32_t sQ = smem, sStage0 = smem + kQBytes;
-  const uint32_t mbar_s = smem_u32(&mbar_s_mem), mbar_o = smem_u32(&mbar_o_mem);
-  const int tid = threadIdx.x, warp = tid >> 5;
+  const uint32_t sQ = smem, sK = smem + kOffK, sV = smem + kOffV;
+  const uint32_t bar0 = smem_u32(&bars[0]);
+  auto k_full = [&](int s) { return bar0 + 8u * s; };
+  auto k_empty = [&](int s) { return bar0 + 8u * (kStages + s); };
+  auto v_full = [&](int s) { return bar0 + 8u * (2 * kStages + s); };
+  auto v_empty = [&](int s) { return bar0 + 8u * (3 * kStages + s); };
+  auto s_full = [&](int x) { return bar0 + 8u * (4 * kStages + x); };
+  auto p_full = [&](int x) { return bar0 + 8u * (4 * kStages + 2 + x); };
+  auto o_done = [&](int x) { return bar0 + 8u * (4 * kStages + 4 + x); };
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
   // blocks start in the order (all heads of tile 0, all heads of tile 1, ...); the caller lists the tiles that
   // see the most keys first, so the longest blocks are not left for the end
   const int tile = blockIdx.y;
   const int seq = a.tile_seq[tile], q0 = a.tile_q0[tile];
-  const int head = blockIdx.x, kvh = head / a.group;
+  const int pairs = (a.group + 1) / 2;                          // blocks per kv head
+  const int kvh = blockIdx.x / pairs, pair = blockIdx.x % pairs;
+  const int head0 = kvh * a.group + 2 * pair;
+  const bool two = 2 * pair + 1 < a.group;                      // the block has a second head
   const int tok0 = a.cu_q[seq], n = a.cu_q[seq + 1] - tok0, ctx = a.ctx_len[seq];
   const int start = ctx - n;
   const int rows_valid = min(BM, n - q0);
   const int hi = start + q0 + rows_valid;                       // keys < hi are visible to the tile's last row
   const int lo = a.window > 0 ? max(0, start + q0 - a.window + 1) : 0;
   const int* table = a.block_table + (size_t)seq * a.max_blocks;
-  const bool row_ok = tid < rows_valid;
-  const int pos = start + q0 + min(tid, rows_valid - 1);         // this thread's query position
-  const int row_lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+  const int tile_begin = lo / BN, tile_end = (hi + BN - 1) / BN;
+  const int n_tiles = tile_end - tile_begin;
 
   if (tid == 0) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(mbar_s));
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(mbar_o));
+    // a tile is full after one arrival that announces the copies' bytes (tensor-map copies), or after one
+    // arrival of each producer lane when its cp.async have landed
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(k_full(s), a.use_tma ? 1 : 32);
+      mbar_init(v_full(s), a.use_tma ? 1 : 32);
+      mbar_init(k_empty(s), 1);
+      mbar_init(v_empty(s), 1);
+    }
+    for (int x = 0; x < 2; ++x) {
+      mbar_init(s_full(x), 1);
+      mbar_init(p_full(x), kSoftmaxThreads);
+      mbar_init(o_done(x), 1);
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    failed_mem = 0;
   }
   if (warp == 0) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_mem)), "r"(kTmemCols));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
   }
-
-  const int tile_begin = lo / BN, tile_end = (hi + BN - 1) / BN;
-  const int n_tiles = tile_end - tile_begin;
-
-  // Q tile: [64-wide block][row][128 bytes], rows beyond the portion are zero
-  {
+  if (warp < 8 && (warp < 4 || two)) {
+    // Q tile of this group's head: [64-wide block][row][128 bytes], rows beyond the portion are zero
     constexpr int kChunks = HD / 8;
+    const int x = warp >> 2, t = tid & 127;
 #pragma unroll
-    for (int it = 0; it < BM * kChunks / 128; ++it) {
-      const int idx = tid + it * 128;
+    for (int it = 0; it < BM * kChunks / kSoftmaxThreads; ++it) {
+      const int idx = t + it * kSoftmaxThreads;
       const int row = idx / kChunks, c = idx % kChunks;
       const bool ok = row < rows_valid;
-      const bf16* src = ok ? a.q + (size_t)(tok0 + q0 + row) * a.q_stride + (size_t)head * HD + c * 8 : a.q;
-      cp_async_16(sQ + (c / 8) * (BM * 128) + row * 128 + (((c & 7) ^ (row & 7)) << 4), src, ok ? 16 : 0);
+      const bf16* src = ok ? a.q + (size_t)(tok0 + q0 + row) * a.q_stride + (size_t)(head0 + x) * HD + c * 8 : a.q;
+      cp_async_16(sQ + x * kQBytes + (c / 8) * (BM * 128) + row * 128 + (((c & 7) ^ (row & 7)) << 4), src, ok ? 16 : 0);
     }
+    cp_async_commit();
+    cp_async_wait<0>();
+    fence_async_smem();
   }
-  load_kv_tile(sStage0, a.kv, table, kvh, tile_begin * BN, lo, hi, kNoPrefetch);
-  cp_async_commit();
-  // Page numbers are looked up one tile ahead of the copies that use them, so that the copies of the loop
-  // never wait on the block table.
-  constexpr int kRowsPerThread = BN * (HD / 8) / 128;
-  const bool prefetch_pages = a.kv.block_size >= kRowsPerThread;
-  int next_page = (prefetch_pages && n_tiles > 1) ? tile_page(a.kv, table, (tile_begin + 1) * BN, lo, hi) : kNoPrefetch;
-
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_base_mem;
-  const uint32_t t_row = tmem + ((uint32_t)(warp * 32) << 16);      // this warp's 32 lanes
 
-  float m_run = -INFINITY, l_run = 0.f;
-  const float sl2 = a.scale * kLog2e;
-  bool failed = false;
-
-#ifdef LMSF_TC_TIMING
-  long long tacc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  long long tlast = clock64();
-#endif
-  for (int j = 0; j < n_tiles; ++j) {
-    LMSF_T(7);
-    const uint32_t stage = sStage0 + (j & 1) * kStageBytes;
-    const uint32_t sK = stage, sV = stage + kKSlot, sP = stage;    // P takes the k tile's place once S is done
-    // (a) this tile (and, the first time, Q) has landed
-    cp_async_wait<0>();
-    fence_async_smem();
-    tc_fence_before();
-    if (__syncthreads_or(failed)) { failed = true; break; }
-    LMSF_T(0);
-    // (b) S = Q K^T; it runs behind the previous tile's O += P V on the tensor pipe
-    if (tid == 0) {
-      tc_fence_after();
-      constexpr uint32_t idesc = instr_desc(BM, BN, 0);
+  if (warp == 8 || warp == 9) {
+    // ------------------------------------------------------------------ producers: warp 8 of k, warp 9 of v
+    const bool is_v = warp == 9;
+    auto full = [&](int s) { return is_v ? v_full(s) : k_full(s); };
+    auto empty = [&](int s) { return is_v ? v_empty(s) : k_empty(s); };
+    const uint32_t ring = is_v ? sV : sK;
+    LMSF_T_BEGIN();
+    if (a.use_tma) {
+      // Lane i copies box i of a tile: keys [i * rows_box, (i + 1) * rows_box), which lie in one page.  A key
+      // range without a page (beyond the sequence, or before the window) is read from page 0 instead: all its
+      // keys are masked, and the softmax warps clear those rows of v.
+      const int n_box = BN / a.rows_box;
+      const int head_row = (is_v ? a.kv.n_kv_heads : 0) + kvh;
+      auto fetch_page = [&](int t) {
+        const int blk = ((tile_begin + t) * BN + lane * a.rows_box) >> a.kv.block_shift;
+        return (t < n_tiles && lane < n_box && blk < a.max_blocks) ? table[blk] : -1;
+      };
+      int page = fetch_page(0);
+      int issued = 0;                                            // tiles whose copies were issued
+      for (int t = 0; t < n_tiles; ++t) {
+        const int s = t % kStages;
+        const int slot0 = ((tile_begin + t) * BN + lane * a.rows_box) & (a.kv.block_size - 1);
+        const uint32_t dst = ring + s * kKBytes + lane * a.rows_box * 128;
+        if (t >= kStages && !mbar_wait_f(empty(s), (uint32_t)((t / kStages - 1) & 1), failed)) break;
+        LMSF_T(6);
+        const int next_page = fetch_page(t + 1);
+        if (lane == 0) mbar_arrive_expect_tx(full(s), kKBytes);
+        __syncwarp();
+        if (lane < n_box) {
+#pragma unroll
+          for (int hb = 0; hb < kHB; ++hb)
+            tma_load_box(dst + hb * (BN * 128), &kv_map, hb * 64, slot0, head_row, max(page, 0), full(s));
+        }
+        issued = t + 1;
+        page = next_page;
+        LMSF_T(7);
+      }
+      // no copy of this block may be in flight when it ends, whichever way the loop was left
+      for (int t = max(0, issued - kStages); t < issued; ++t) mbar_wait_drain(full(t % kStages), (uint32_t)((t / kStages) & 1));
+      LMSF_T_END();
+    } else {
+      for (int t = 0; t < n_tiles; ++t) {
+        const int s = t % kStages;
+        if (t >= kStages && !mbar_wait_f(empty(s), (uint32_t)((t / kStages - 1) & 1), failed)) break;
+        gather_tile(ring + s * kKBytes, a.kv, table, a.max_blocks, kvh, is_v, (tile_begin + t) * BN, lo, hi, lane);
+        cp_async_arrive(full(s));
+      }
+      cp_async_wait<0>();
+    }
+  } else if (warp == 10) {
+    // ------------------------------------------------------------------ tensor-core issue
+    constexpr uint32_t idesc_s = instr_desc(BM, BN, 0), idesc_o = instr_desc(BM, HD, 1);
+    LMSF_T_BEGIN();
+    const int nx = two ? 2 : 1;
+    auto issue_s = [&](int x, int j) {                          // S of head x and tile j
+      const uint32_t q = sQ + x * kQBytes, k = sK + (j % kStages) * kKBytes;
 #pragma unroll
       for (int ks = 0; ks < HD / 16; ++ks) {
         const uint32_t off_a = (ks / 4) * (BM * 128) + (ks % 4) * 32, off_b = (ks / 4) * (BN * 128) + (ks % 4) * 32;
-        umma(tmem, smem_desc(sQ + off_a, 16, 1024), smem_desc(sK + off_b, 16, 1024), idesc, ks > 0);
+        umma(tmem + x * BN, smem_desc(q + off_a, 16, 1024), smem_desc(k + off_b, 16, 1024), idesc_s, ks > 0);
       }
-      umma_commit(mbar_s);
-    }
-    // (c) the product before this one has finished: O may be touched, the other stage may be overwritten
-    if (j > 0 && !mbar_wait(mbar_o, (uint32_t)((j - 1) & 1))) failed = true;
-    LMSF_T(1);
-    // (d) next tile's loads, while S is being computed
-    if (j + 1 < n_tiles)
-      load_kv_tile(sStage0 + ((j + 1) & 1) * kStageBytes, a.kv, table, kvh, (tile_begin + j + 1) * BN, lo, hi, next_page);
-    cp_async_commit();
-    if (prefetch_pages && j + 2 < n_tiles) next_page = tile_page(a.kv, table, (tile_begin + j + 2) * BN, lo, hi);
-    LMSF_T(2);
-    // (e) softmax of this thread's row
-    if (!mbar_wait(mbar_s, (uint32_t)(j & 1))) failed = true;
-    tc_fence_after();
-    LMSF_T(3);
-    float s[BN];
-    {
-      uint32_t r[32];
-      tmem_ld32(t_row, r);
+      umma_commit(s_full(x));
+    };
+    auto issue_pv = [&](int x, int j) {                         // O of head x += P V of tile j, P from tensor memory
+      const uint32_t v = sV + (j % kStages) * kKBytes;
 #pragma unroll
-      for (int i = 0; i < 32; ++i) s[i] = __uint_as_float(r[i]);
-      tmem_ld32(t_row + 32, r);
-#pragma unroll
-      for (int i = 0; i < 32; ++i) s[32 + i] = __uint_as_float(r[i]);
-    }
-    LMSF_T(4);
-    const int key0 = (tile_begin + j) * BN;
-    // Only tiles that reach past some row's position (the diagonal) or before its window need the mask;
-    // the test is the same for the whole block.
-    const bool need_mask = key0 + BN - 1 > start + q0 || (a.window > 0 && key0 < start + q0 + rows_valid - a.window);
-    if (need_mask) {
-#pragma unroll
-      for (int i = 0; i < BN; ++i) {
-        const int key = key0 + i;
-        if (key > pos || key < row_lo) s[i] = -INFINITY;
+      for (int ks = 0; ks < BN / 16; ++ks)
+        umma_ts(tmem + kOCol + x * 128, tmem + x * BN + ks * 8, smem_desc(v + ks * 16 * 128, BN * 128, 1024), idesc_o,
+                (j > 0 || ks > 0) ? 1u : 0u);
+    };
+    bool ok = n_tiles > 0 && mbar_wait_f(k_full(0), 0u, failed);
+    if (ok) {
+      fence_async_smem();
+      tc_fence_after();
+      if (lane == 0) {
+        for (int x = 0; x < nx; ++x) issue_s(x, 0);
+        umma_commit(k_empty(0));
       }
+      __syncwarp();
     }
-    float mx = s[0];
+    // The two heads take turns: while one head's softmax runs, the tensor core works on the other head's
+    // P V and on its next scores.  S of tile j + 1 may overwrite P of tile j because the products of one
+    // thread are executed in the order of their issue.
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int s = j % kStages, s1 = (j + 1) % kStages;
+      const bool more = j + 1 < n_tiles;
+      for (int x = 0; x < nx && ok; ++x) {
+        ok = mbar_wait_f(p_full(x), (uint32_t)(j & 1), failed);
+        if (x == 0) LMSF_TRACE(3, j, 0);
+        if (ok && x == 0) ok = mbar_wait_f(v_full(s), (uint32_t)((j / kStages) & 1), failed);
+        if (x == 0) LMSF_TRACE(3, j, 1);
+        LMSF_T(4);
+        LMSF_TRACE(2, j, 2 * x);
+        if (!ok) break;
+        fence_async_smem();
+        tc_fence_after();
+        if (lane == 0) {
+          issue_pv(x, j);
+          if (!more) umma_commit(o_done(x));
+        }
+        __syncwarp();
+        LMSF_T(5);
+        if (x == 0) LMSF_TRACE(3, j, 2);
+        if (more) {
+          if (x == 0) {
+            ok = mbar_wait_f(k_full(s1), (uint32_t)(((j + 1) / kStages) & 1), failed);
+            LMSF_TRACE(3, j, 3);
+            LMSF_T(9);
+            if (!ok) break;
+            fence_async_smem();
+            tc_fence_after();
+          }
+          if (lane == 0) issue_s(x, j + 1);
+          __syncwarp();
+          LMSF_TRACE(2, j, 2 * x + 1);
+          LMSF_T(3);
+        }
+      }
+      if (!ok) break;
+      if (lane == 0) {
+        umma_commit(v_empty(s));
+        if (more) umma_commit(k_empty(s1));
+      }
+      __syncwarp();
+    }
+    LMSF_T_END();
+  } else if (warp < 4 || two) {
+    // ------------------------------------------------------------------ softmax of head x
+    const int x = warp >> 2, row = tid & 127;
+    const bool row_ok = row < rows_valid;
+    const int pos = start + q0 + min(row, rows_valid - 1);         // this thread's query position
+    const int row_lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+    const uint32_t t_row = tmem + ((uint32_t)((warp & 3) * 32) << 16);   // this warp's 32 lanes of tensor memory
+    const uint32_t t_s = t_row + x * BN, t_o = t_row + kOCol + x * 128;
+    float m_run = -INFINITY, l_run = 0.f;
+    const float sl2 = a.scale * kLog2e;
+    bool ok = true;
+    LMSF_T_BEGIN();
+    for (int j = 0; j < n_tiles; ++j) {
+      // S of tile j is complete, and with it every product issued before it: P V of tile j - 1 too
+      ok = mbar_wait_f(s_full(x), (uint32_t)(j & 1), failed);
+      if (!ok) break;
+#ifdef LMSF_TC_TIMING
+      __syncwarp();
+#endif
+      LMSF_T(0);
+      if ((warp & 3) == 0) LMSF_TRACE(x, j, 0);
+      tc_fence_after();
+      LMSF_T(15);
+      const int key0 = (tile_begin + j) * BN;
+      // Only tiles that reach past some row's position (the diagonal) or before its window need the mask;
+      // the test is the same for the whole block.
+      const bool need_mask = key0 + BN - 1 > start + q0 || (a.window > 0 && key0 < start + q0 + rows_valid - a.window);
+      // 32 scores of this row; in a tile on the diagonal or at the window's edge, keys that the row does not see
+      // become -inf (the choice is made per tile, so that the common tile runs without the tests)
+      auto load32 = [&](int col, float (&dst)[32], auto masked) {
+        uint32_t r[32];
+        tmem_ld32(t_s + col, r);
 #pragma unroll
-    for (int i = 1; i < BN; ++i) mx = fmaxf(mx, s[i]);
-    mx *= sl2;                                                // scores enter the exponent as s * scale * log2(e)
-    float alpha = 1.f;
-    const bool grow = mx > m_run + kRescaleThreshold;         // also true for the first keys a row sees
-    if (grow) {
-      alpha = exp2f(m_run - mx);                              // 0 when m_run is -inf
-      m_run = mx;
-      l_run *= alpha;
+        for (int i = 0; i < 32; ++i) {
+          if constexpr (decltype(masked)::value) {
+            const int key = key0 + col + i;
+            dst[i] = ((key > pos) | (key < row_lo)) ? -INFINITY : __uint_as_float(r[i]);
+          } else {
+            dst[i] = __uint_as_float(r[i]);
+          }
+        }
+      };
+      // the first 64 scores stay in registers; the other 64 are read twice, for the maximum and for P
+      float s0[32], s1[32], mx;
+      auto row_max = [&](auto masked) {
+        load32(0, s0, masked);
+        load32(32, s1, masked);
+        float m0 = s0[0], m1 = s1[0];
+#pragma unroll
+        for (int i = 1; i < 32; ++i) {
+          m0 = fmaxf(m0, s0[i]);
+          m1 = fmaxf(m1, s1[i]);
+        }
+        float t[32];
+        load32(64, t, masked);
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          m0 = fmaxf(m0, t[i]);
+          m1 = fmaxf(m1, t[i + 1]);
+        }
+        load32(96, t, masked);
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          m0 = fmaxf(m0, t[i]);
+          m1 = fmaxf(m1, t[i + 1]);
+        }
+        return fmaxf(m0, m1);
+      };
+      if (need_mask) mx = row_max(std::true_type{});
+      else mx = row_max(std::false_type{});
+      mx *= sl2;                                                // scores enter the exponent as s * scale * log2(e)
+      float alpha = 1.f;
+      const bool grow = mx > m_run + kRescaleThreshold;         // also true for the first keys a row sees
+      if (grow) {
+        alpha = exp2f(m_run - mx);                              // 0 when m_run is -inf
+        m_run = mx;
+        l_run *= alpha;
+      }
+      if (j > 0 && __any_sync(0xffffffffu, grow)) {             // rescale this warp's rows of O
+#pragma unroll
+        for (int c0 = 0; c0 < HD; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld32(t_o + c0, r);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+          tmem_st32(t_o + c0, r);
+        }
+      }
+      if (key0 < lo || key0 + BN > hi) {
+        // rows of v whose keys no query of the tile sees hold whatever their page holds: clear them, so that
+        // their zero weights cannot meet a value that is not finite (both heads' warps do, with the same zeros)
+        const uint32_t v = sV + (j % kStages) * kKBytes;
+        const int r_lo = lo - key0, r_hi = hi - key0;
+        ok = mbar_wait_f(v_full(j % kStages), (uint32_t)((j / kStages) & 1), failed);   // the tile's v has landed
+        if (!ok) break;
+        for (int idx = row; idx < kHB * BN * 8; idx += kSoftmaxThreads) {
+          const int r = (idx >> 3) % BN;
+          if (r < r_lo || r >= r_hi)
+            asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(v + (idx >> 3) * 128 + (idx & 7) * 16), "r"(0) : "memory");
+        }
+        fence_async_smem();
+      }
+      LMSF_T(11);
+      // P as bfloat16 pairs over the first 64 columns of S: keys 2c and 2c + 1 in column c
+      const float neg_m = m_run == -INFINITY ? 0.f : -m_run;
+      float l0 = 0.f, l1 = 0.f;
+      auto exp_pack = [&](const float (&src)[32], uint32_t* dst) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float p0 = ex2_approx(fmaf(src[2 * i], sl2, neg_m)), p1 = ex2_approx(fmaf(src[2 * i + 1], sl2, neg_m));
+          l0 += p0;
+          l1 += p1;
+          dst[i] = pack_bf16(p0, p1);
+        }
+      };
+      {
+        uint32_t w[32];
+        exp_pack(s0, w);
+        exp_pack(s1, w + 16);
+        tmem_st32(t_s, w);                                      // columns [0, 32): keys 0..63, already in registers
+      }
+      LMSF_T(12);
+      {
+        uint32_t w[32];
+        float t[32];
+        if (need_mask) load32(64, t, std::true_type{});
+        else load32(64, t, std::false_type{});
+        exp_pack(t, w);
+        if (need_mask) load32(96, t, std::true_type{});
+        else load32(96, t, std::false_type{});
+        exp_pack(t, w + 16);
+        tmem_st32(t_s + 32, w);                                 // columns [32, 64): keys 64..127
+      }
+      LMSF_T(13);
+      l_run += l0 + l1;
+      tc_fence_before();
+      mbar_arrive(p_full(x));
+      if ((warp & 3) == 0) LMSF_TRACE(x, j, 1);
+      LMSF_T(1);
     }
-    if (j > 0 && __any_sync(0xffffffffu, grow)) {             // rescale this warp's rows of O
+    if (ok && n_tiles > 0) ok = mbar_wait_f(o_done(x), 0u, failed);
+    if (ok && n_tiles > 0) {
+      tc_fence_after();
+      const float inv = 1.0f / l_run;
+      bf16* dst = a.out + (size_t)(tok0 + q0 + row) * a.out_stride + (size_t)(head0 + x) * HD;
 #pragma unroll
       for (int c0 = 0; c0 < HD; c0 += 32) {
         uint32_t r[32];
-        tmem_ld32(t_row + kOCol + c0, r);
+        tmem_ld32(t_o + c0, r);                                 // every lane of the warp takes part
+        if (row_ok) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-        tmem_st32(t_row + kOCol + c0, r);
-      }
-    }
-    const float neg_m = m_run == -INFINITY ? 0.f : -m_run;
-    {
-      const int row = tid;
-      float l0 = 0.f, l1 = 0.f;
-#pragma unroll
-      for (int c = 0; c < BN / 8; ++c) {
-        uint32_t w[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float p0 = ex2_approx(fmaf(s[c * 8 + 2 * e], sl2, neg_m)), p1 = ex2_approx(fmaf(s[c * 8 + 2 * e + 1], sl2, neg_m));
-          l0 += p0;
-          l1 += p1;
-          w[e] = pack_bf16(p0, p1);
-        }
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sP + row * 128 + ((c ^ (row & 7)) << 4)),
-                     "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
-      }
-      l_run += l0 + l1;
-    }
-    LMSF_T(5);
-    fence_async_smem();
-    tc_fence_before();
-    if (__syncthreads_or(failed)) { failed = true; break; }
-    LMSF_T(6);
-    // (f) O += P V
-    if (tid == 0) {
-      tc_fence_after();
-      constexpr uint32_t idesc = instr_desc(BM, HD, 1);
-#pragma unroll
-      for (int ks = 0; ks < BN / 16; ++ks)
-        umma(tmem + kOCol, smem_desc(sP + ks * 32, 16, 1024), smem_desc(sV + ks * 16 * 128, BN * 128, 1024), idesc,
-             (j > 0 || ks > 0) ? 1u : 0u);
-      umma_commit(mbar_o);
-    }
-  }
-  cp_async_wait<0>();
-#ifdef LMSF_TC_TIMING
-  if (tid == 127 && g_timing) {
-    long long* t = g_timing + ((size_t)blockIdx.x * gridDim.y + blockIdx.y) * 9;
-    for (int i = 0; i < 8; ++i) t[i] = tacc[i];
-    t[8] = n_tiles;
-  }
-#endif
-
-  if (!failed && n_tiles > 0 && !mbar_wait(mbar_o, (uint32_t)((n_tiles - 1) & 1))) failed = true;
-  failed = __syncthreads_or(failed);
-  tc_fence_after();
-  if (!failed && n_tiles > 0) {
-    const float inv = 1.0f / l_run;
-    bf16* dst = a.out + (size_t)(tok0 + q0 + tid) * a.out_stride + (size_t)head * HD;
-#pragma unroll
-    for (int c0 = 0; c0 < HD; c0 += 32) {
-      uint32_t r[32];
-      tmem_ld32(t_row + kOCol + c0, r);                       // every lane of the warp takes part
-      if (row_ok) {
-#pragma unroll
-        for (int i = 0; i < 32; i += 8) {
-          uint4 v;
-          v.x = pack_bf16(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
-          v.y = pack_bf16(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
-          v.z = pack_bf16(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
-          v.w = pack_bf16(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
-          *reinterpret_cast<uint4*>(dst + c0 + i) = v;
+          for (int i = 0; i < 32; i += 8) {
+            uint4 v;
+            v.x = pack_bf16(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
+            v.y = pack_bf16(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+            v.z = pack_bf16(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
+            v.w = pack_bf16(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + c0 + i) = v;
+          }
         }
       }
     }
+    LMSF_T_END();
   }
-  if (failed && tid == 0 && a.error_flag) atomicExch(a.error_flag, 3);
   tc_fence_before();
   __syncthreads();
+  if (*failed && tid == 0 && a.error_flag) atomicExch(a.error_flag, 3);
   if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols));
+}
+
+// ---- tensor maps of the cache --------------------------------------------------------------------------
+// One layer's cache is a 4-d tensor for the copy engine: (head element, slot, k heads then v heads, page).
+// A box is 64 elements x rows_box slots; the engine writes it 128-byte swizzled.  cuTensorMapEncodeTiled is
+// looked up in the driver at run time, so this library does not link against it.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return (EncodeTiledFn)p;
+  }();
+  return fn;
+}
+
+// The map of a cache, made once per (address, geometry).  Returns nullptr and sets *why on failure.
+inline const CUtensorMap* cache_tensor_map(const void* cache, long long page_stride, int block_size, int n_kv_heads,
+                                           long long n_pages, int rows_box, const char** why) {
+  using Key = std::tuple<const void*, long long, int, int, long long>;
+  static std::map<Key, CUtensorMap> maps;
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
+  const Key key{cache, page_stride, block_size, n_kv_heads, n_pages};
+  auto it = maps.find(key);
+  if (it != maps.end()) return &it->second;
+  EncodeTiledFn encode = encode_tiled_fn();
+  if (!encode) { *why = "the driver has no cuTensorMapEncodeTiled"; return nullptr; }
+  const cuuint64_t dims[4] = {(cuuint64_t)HD, (cuuint64_t)block_size, (cuuint64_t)(2 * n_kv_heads), (cuuint64_t)n_pages};
+  const cuuint64_t strides[3] = {(cuuint64_t)HD * 2, (cuuint64_t)block_size * HD * 2, (cuuint64_t)page_stride * 2};
+  const cuuint32_t box[4] = {64, (cuuint32_t)rows_box, 1, 1};
+  const cuuint32_t elem_strides[4] = {1, 1, 1, 1};
+  CUtensorMap m;
+  const CUresult r = encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(cache), dims, strides, box, elem_strides,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { *why = "cuTensorMapEncodeTiled refused the cache's geometry"; return nullptr; }
+  return &maps.emplace(key, m).first->second;
 }
 
 }  // namespace tc
@@ -420,11 +648,12 @@ LMSF_API int lmsf_attention_tc_set_timing(long long* buf) {
 }
 #endif
 
+
 // tile_seq / tile_q0: one entry per 128 query tokens of each portion, best listed with the tiles that see the
 // most keys first.  q and out rows must be 16-byte aligned.
 LMSF_API int lmsf_attention_prefill_tc(const void* q, long long q_stride, void* out, long long out_stride,
-                                       const void* cache, long long page_stride, int block_size, int n_kv_heads,
-                                       const int* block_table, int max_blocks, const int* tile_seq, const int* tile_q0,
+                                       const void* cache, long long page_stride, long long n_pages, int block_size,
+                                       int n_kv_heads, const int* block_table, int max_blocks, const int* tile_seq, const int* tile_q0,
                                        int n_tiles, const int* cu_q, const int* ctx_len, float scale, int window,
                                        int n_q_heads, int head_dim, int* error_flag, void* stream) {
   using namespace lmsf;
@@ -444,12 +673,24 @@ LMSF_API int lmsf_attention_prefill_tc(const void* q, long long q_stride, void* 
   a.block_table = block_table; a.max_blocks = max_blocks; a.tile_seq = tile_seq; a.tile_q0 = tile_q0;
   a.cu_q = cu_q; a.ctx_len = ctx_len; a.scale = scale; a.window = window; a.n_q_heads = n_q_heads;
   a.group = n_q_heads / n_kv_heads; a.error_flag = error_flag;
+  // pages of 8 keys and more come by tensor-map copies (a box of rows_box keys starts on a 1024-byte
+  // boundary of the swizzled tile); smaller pages by cp.async
+  a.rows_box = block_size < BN ? block_size : BN;
+  a.use_tma = block_size >= 8 && n_pages > 0;
+  CUtensorMap kv_map;
+  memset(&kv_map, 0, sizeof(kv_map));
+  if (a.use_tma) {
+    const char* why = "";
+    const CUtensorMap* m = cache_tensor_map(cache, page_stride, block_size, n_kv_heads, n_pages, a.rows_box, &why);
+    if (!m) LMSF_REFUSE("attention_prefill_tc: %s", why);
+    kv_map = *m;
+  }
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  prefill_tc_kernel<<<dim3(n_q_heads, n_tiles), 128, kSmemBytes, (cudaStream_t)stream>>>(a);
+  prefill_tc_kernel<<<dim3(n_kv_heads * ((a.group + 1) / 2), n_tiles), kThreadsTotal, kSmemBytes, (cudaStream_t)stream>>>(a, kv_map);
   return LMSF_LAUNCH_STATUS();
 }

@@ -101,15 +101,16 @@ def test_gemm_simt_is_true_float32_and_row_independent(M, N, K):
     assert torch.allclose(out.cpu(), ab.float() @ wb.float().T, rtol=1e-4, atol=1e-4 * math.sqrt(K))
 
 
-def _paged_setup(dtype, n_q_heads, n_kv_heads, hd, bs, ctx_lens, q_lens, seed, sharp=False):
-    """Random q and paged k, v for several requests; pages handed out in a scrambled order."""
+def _paged_setup(dtype, n_q_heads, n_kv_heads, hd, bs, ctx_lens, q_lens, seed, sharp=False, poison=False):
+    """Random q and paged k, v for several requests; pages handed out in a scrambled order.  With `poison`,
+    every slot that holds no key (the rest of a last page, spare pages) is NaN: a kernel must not let it in."""
     g = torch.Generator().manual_seed(seed)
     S = len(ctx_lens)
     n_pages = sum((c + bs - 1) // bs for c in ctx_lens) + 3
     perm = torch.randperm(n_pages, generator=g).tolist()
     max_blocks = max((c + bs - 1) // bs for c in ctx_lens)
     bt = torch.full((S, max_blocks), -1, dtype=torch.int32)
-    cache = torch.zeros(n_pages, 2, n_kv_heads, bs, hd)
+    cache = torch.full((n_pages, 2, n_kv_heads, bs, hd), float('nan') if poison else 0.0)
     ks, vs = [], []
     for s, c in enumerate(ctx_lens):
         k, v = torch.randn(c, n_kv_heads, hd, generator=g), torch.randn(c, n_kv_heads, hd, generator=g)
@@ -375,14 +376,18 @@ def test_gemm_skinny_against_its_plain_twin(M, N, K):
 
 
 @pytest.mark.parametrize("nh,nkv,hd,bs,window", [(8, 2, 128, 16, 0), (4, 4, 64, 16, 0), (6, 1, 128, 8, 0), (4, 2, 64, 32, 90),
-                                               (2, 1, 128, 16, 300)])
+                                               (2, 1, 128, 16, 300), (3, 1, 128, 4, 0), (6, 2, 64, 128, 0), (5, 1, 128, 256, 200),
+                                               (2, 2, 64, 2, 70)])
 def test_attention_tcgen05_prefill(nh, nkv, hd, bs, window):
-    """The tcgen05 prefill kernel against float64 and against its mma.sync twin."""
+    """The tcgen05 prefill kernel against float64 and against its mma.sync twin: even and odd groups of heads,
+    pages from 2 to 256 keys (tensor-map copies from 8 keys on, cp.async below), windows; slots that hold no key
+    are NaN."""
     from lmsf_b200 import kernels
     assert kernels.tc_attention_supported(torch.bfloat16, hd)
     # a portion in the middle of a long prompt, a whole prompt, a 2-token portion, a portion of exactly one tile, a long one
     ctx_lens, q_lens = [700, 130, 65, 128, 1100], [201, 130, 2, 128, 1000]
-    q, cache, bt, token_seq, positions, ks, vs = _paged_setup("bfloat16", nh, nkv, hd, bs, ctx_lens, q_lens, 13, sharp=True)
+    q, cache, bt, token_seq, positions, ks, vs = _paged_setup("bfloat16", nh, nkv, hd, bs, ctx_lens, q_lens, 13, sharp=True,
+                                                              poison=True)
     scale = 1.0 / math.sqrt(hd)
     ref = _attention_reference(q.float(), ks, vs, token_seq, positions, nh, nkv, hd, scale, window)
     d = dev()
