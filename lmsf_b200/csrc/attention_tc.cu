@@ -111,17 +111,25 @@ __host__ __device__ constexpr uint32_t instr_desc(int M, int N, int b_mn_major) 
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(N >> 3) << 17) |
          ((uint32_t)(M >> 4) << 24);
 }
-__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
-  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-               ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+// The whole issuing warp runs the code around a product, so that addresses and descriptors are the same in
+// every lane; the instruction itself is executed by the one lane for which `leader` is set.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n.reg .pred p;\nelect.sync _|p, 0xffffffff;\nselp.b32 %0, 1, 0, p;\n}\n" : "=r"(pred));
+  return pred != 0;
+}
+__device__ __forceinline__ void umma(bool leader, uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n.reg .pred p, q;\nsetp.ne.b32 p, %4, 0;\nsetp.ne.b32 q, %5, 0;\n@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+               ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"((uint32_t)leader) : "memory");
 }
 // the same with the A operand in tensor memory (row m in lane m, two bfloat16 per column)
-__device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t accumulate) {
-  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
-               ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+__device__ __forceinline__ void umma_ts(bool leader, uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n.reg .pred p, q;\nsetp.ne.b32 p, %4, 0;\nsetp.ne.b32 q, %5, 0;\n@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+               ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate), "r"((uint32_t)leader) : "memory");
 }
-__device__ __forceinline__ void umma_commit(uint32_t mbar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar) : "memory");
+__device__ __forceinline__ void umma_commit(bool leader, uint32_t mbar) {
+  asm volatile("{\n.reg .pred q;\nsetp.ne.b32 q, %1, 0;\n@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n}\n"
+               ::"r"(mbar), "r"((uint32_t)leader) : "memory");
 }
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,"
@@ -142,6 +150,35 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
                  "r"(r[28]),"r"(r[29]),"r"(r[30]),"r"(r[31]) : "memory");
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
+// 32 columns of this thread's lane into floats; the values may be used after tmem_wait_ld()
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, float* r) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,"
+               "%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+               : "=f"(r[0]),"=f"(r[1]),"=f"(r[2]),"=f"(r[3]),"=f"(r[4]),"=f"(r[5]),"=f"(r[6]),"=f"(r[7]),"=f"(r[8]),"=f"(r[9]),
+                 "=f"(r[10]),"=f"(r[11]),"=f"(r[12]),"=f"(r[13]),"=f"(r[14]),"=f"(r[15]),"=f"(r[16]),"=f"(r[17]),"=f"(r[18]),
+                 "=f"(r[19]),"=f"(r[20]),"=f"(r[21]),"=f"(r[22]),"=f"(r[23]),"=f"(r[24]),"=f"(r[25]),"=f"(r[26]),"=f"(r[27]),
+                 "=f"(r[28]),"=f"(r[29]),"=f"(r[30]),"=f"(r[31])
+               : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st32_issue(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,"
+               "%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
+               ::"r"(taddr), "r"(r[0]),"r"(r[1]),"r"(r[2]),"r"(r[3]),"r"(r[4]),"r"(r[5]),"r"(r[6]),"r"(r[7]),"r"(r[8]),"r"(r[9]),
+                 "r"(r[10]),"r"(r[11]),"r"(r[12]),"r"(r[13]),"r"(r[14]),"r"(r[15]),"r"(r[16]),"r"(r[17]),"r"(r[18]),
+                 "r"(r[19]),"r"(r[20]),"r"(r[21]),"r"(r[22]),"r"(r[23]),"r"(r[24]),"r"(r[25]),"r"(r[26]),"r"(r[27]),
+                 "r"(r[28]),"r"(r[29]),"r"(r[30]),"r"(r[31]) : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// Registers move between warpgroups after the launch: the softmax warps hold a row of 128 scores each.
+constexpr int kRegsSoftmax = 224, kRegsOther = 56;
+template <int N> __device__ __forceinline__ void regs_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N> __device__ __forceinline__ void regs_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
 __device__ __forceinline__ float ex2_approx(float x) {      // 2^x, 0 for -inf
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -157,8 +194,9 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 // warp 8   : producer of k tiles
 // warp 9   : producer of v tiles
 // warp 10  : issues the tensor-core products
+// warp 11  : idle
 constexpr int kSoftmaxThreads = 128;       // per head
-constexpr int kThreadsTotal = 352;
+constexpr int kThreadsTotal = 384;     // three warpgroups; warp 11 only gives its registers away
 
 __device__ __forceinline__ bool mbar_wait_f(uint32_t mbar, uint32_t parity, volatile int* failed) {
   uint32_t done = 0;
@@ -297,6 +335,8 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
   tc_fence_after();
   const uint32_t tmem = tmem_base_mem;
 
+  if (warp >= 8) {
+  regs_dec<kRegsOther>();
   if (warp == 8 || warp == 9) {
     // ------------------------------------------------------------------ producers: warp 8 of k, warp 9 of v
     const bool is_v = warp == 9;
@@ -351,31 +391,32 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
     constexpr uint32_t idesc_s = instr_desc(BM, BN, 0), idesc_o = instr_desc(BM, HD, 1);
     LMSF_T_BEGIN();
     const int nx = two ? 2 : 1;
+    const bool leader = elect_one();
+    // descriptors of the first 16 head elements (S) or keys (P V) of each operand; a later slice of 16 adds
+    // its byte offset / 16 to the address field
+    const uint64_t dq0 = smem_desc(sQ, 16, 1024), dk0 = smem_desc(sK, 16, 1024), dv0 = smem_desc(sV, BN * 128, 1024);
     auto issue_s = [&](int x, int j) {                          // S of head x and tile j
-      const uint32_t q = sQ + x * kQBytes, k = sK + (j % kStages) * kKBytes;
+      const uint64_t dq = dq0 + (uint64_t)((x * kQBytes) >> 4), dk = dk0 + (uint64_t)(((j % kStages) * kKBytes) >> 4);
 #pragma unroll
       for (int ks = 0; ks < HD / 16; ++ks) {
         const uint32_t off_a = (ks / 4) * (BM * 128) + (ks % 4) * 32, off_b = (ks / 4) * (BN * 128) + (ks % 4) * 32;
-        umma(tmem + x * BN, smem_desc(q + off_a, 16, 1024), smem_desc(k + off_b, 16, 1024), idesc_s, ks > 0);
+        umma(leader, tmem + x * BN, dq + (off_a >> 4), dk + (off_b >> 4), idesc_s, ks > 0);
       }
-      umma_commit(s_full(x));
+      umma_commit(leader, s_full(x));
     };
     auto issue_pv = [&](int x, int j) {                         // O of head x += P V of tile j, P from tensor memory
-      const uint32_t v = sV + (j % kStages) * kKBytes;
+      const uint64_t dv = dv0 + (uint64_t)(((j % kStages) * kKBytes) >> 4);
 #pragma unroll
       for (int ks = 0; ks < BN / 16; ++ks)
-        umma_ts(tmem + kOCol + x * 128, tmem + x * BN + ks * 8, smem_desc(v + ks * 16 * 128, BN * 128, 1024), idesc_o,
+        umma_ts(leader, tmem + kOCol + x * 128, tmem + x * BN + ks * 8, dv + ((ks * 16 * 128) >> 4), idesc_o,
                 (j > 0 || ks > 0) ? 1u : 0u);
     };
     bool ok = n_tiles > 0 && mbar_wait_f(k_full(0), 0u, failed);
     if (ok) {
       fence_async_smem();
       tc_fence_after();
-      if (lane == 0) {
-        for (int x = 0; x < nx; ++x) issue_s(x, 0);
-        umma_commit(k_empty(0));
-      }
-      __syncwarp();
+      for (int x = 0; x < nx; ++x) issue_s(x, 0);
+      umma_commit(leader, k_empty(0));
     }
     // The two heads take turns: while one head's softmax runs, the tensor core works on the other head's
     // P V and on its next scores.  S of tile j + 1 may overwrite P of tile j because the products of one
@@ -385,46 +426,37 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
       const bool more = j + 1 < n_tiles;
       for (int x = 0; x < nx && ok; ++x) {
         ok = mbar_wait_f(p_full(x), (uint32_t)(j & 1), failed);
-        if (x == 0) LMSF_TRACE(3, j, 0);
         if (ok && x == 0) ok = mbar_wait_f(v_full(s), (uint32_t)((j / kStages) & 1), failed);
-        if (x == 0) LMSF_TRACE(3, j, 1);
         LMSF_T(4);
         LMSF_TRACE(2, j, 2 * x);
         if (!ok) break;
         fence_async_smem();
         tc_fence_after();
-        if (lane == 0) {
-          issue_pv(x, j);
-          if (!more) umma_commit(o_done(x));
-        }
-        __syncwarp();
+        issue_pv(x, j);
+        if (!more) umma_commit(leader, o_done(x));
         LMSF_T(5);
-        if (x == 0) LMSF_TRACE(3, j, 2);
         if (more) {
           if (x == 0) {
             ok = mbar_wait_f(k_full(s1), (uint32_t)(((j + 1) / kStages) & 1), failed);
-            LMSF_TRACE(3, j, 3);
             LMSF_T(9);
             if (!ok) break;
             fence_async_smem();
             tc_fence_after();
           }
-          if (lane == 0) issue_s(x, j + 1);
-          __syncwarp();
+          issue_s(x, j + 1);
           LMSF_TRACE(2, j, 2 * x + 1);
           LMSF_T(3);
         }
       }
       if (!ok) break;
-      if (lane == 0) {
-        umma_commit(v_empty(s));
-        if (more) umma_commit(k_empty(s1));
-      }
-      __syncwarp();
+      umma_commit(leader, v_empty(s));
+      if (more) umma_commit(leader, k_empty(s1));
     }
     LMSF_T_END();
+  }
   } else if (warp < 4 || two) {
     // ------------------------------------------------------------------ softmax of head x
+    regs_inc<kRegsSoftmax>();
     const int x = warp >> 2, row = tid & 127;
     const bool row_ok = row < rows_valid;
     const int pos = start + q0 + min(row, rows_valid - 1);         // this thread's query position
@@ -450,49 +482,26 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
       // Only tiles that reach past some row's position (the diagonal) or before its window need the mask;
       // the test is the same for the whole block.
       const bool need_mask = key0 + BN - 1 > start + q0 || (a.window > 0 && key0 < start + q0 + rows_valid - a.window);
-      // 32 scores of this row; in a tile on the diagonal or at the window's edge, keys that the row does not see
-      // become -inf (the choice is made per tile, so that the common tile runs without the tests)
-      auto load32 = [&](int col, float (&dst)[32], auto masked) {
-        uint32_t r[32];
-        tmem_ld32(t_s + col, r);
+      // the row's 128 scores: four loads in flight, one wait
+      float sc[BN];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          if constexpr (decltype(masked)::value) {
-            const int key = key0 + col + i;
-            dst[i] = ((key > pos) | (key < row_lo)) ? -INFINITY : __uint_as_float(r[i]);
-          } else {
-            dst[i] = __uint_as_float(r[i]);
-          }
-        }
-      };
-      // the first 64 scores stay in registers; the other 64 are read twice, for the maximum and for P
-      float s0[32], s1[32], mx;
-      auto row_max = [&](auto masked) {
-        load32(0, s0, masked);
-        load32(32, s1, masked);
-        float m0 = s0[0], m1 = s1[0];
+      for (int c0 = 0; c0 < BN; c0 += 32) tmem_ld32_issue(t_s + c0, sc + c0);
+      tmem_wait_ld();
+      if (need_mask) {      // keys that the row does not see become -inf; most tiles skip the test
 #pragma unroll
-        for (int i = 1; i < 32; ++i) {
-          m0 = fmaxf(m0, s0[i]);
-          m1 = fmaxf(m1, s1[i]);
+        for (int i = 0; i < BN; ++i) {
+          const int key = key0 + i;
+          if ((key > pos) | (key < row_lo)) sc[i] = -INFINITY;
         }
-        float t[32];
-        load32(64, t, masked);
+      }
+      float mx0 = fmax3(sc[0], sc[1], sc[2]), mx1 = fmax3(sc[3], sc[4], sc[5]);
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          m0 = fmaxf(m0, t[i]);
-          m1 = fmaxf(m1, t[i + 1]);
-        }
-        load32(96, t, masked);
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          m0 = fmaxf(m0, t[i]);
-          m1 = fmaxf(m1, t[i + 1]);
-        }
-        return fmaxf(m0, m1);
-      };
-      if (need_mask) mx = row_max(std::true_type{});
-      else mx = row_max(std::false_type{});
+      for (int i = 6; i + 3 < BN; i += 4) {
+        mx0 = fmax3(mx0, sc[i], sc[i + 1]);
+        mx1 = fmax3(mx1, sc[i + 2], sc[i + 3]);
+      }
+      float mx = fmax3(mx0, mx1, fmaxf(sc[BN - 2], sc[BN - 1]));
+      LMSF_T(10);
       mx *= sl2;                                                // scores enter the exponent as s * scale * log2(e)
       float alpha = 1.f;
       const bool grow = mx > m_run + kRescaleThreshold;         // also true for the first keys a row sees
@@ -529,35 +538,21 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
       // P as bfloat16 pairs over the first 64 columns of S: keys 2c and 2c + 1 in column c
       const float neg_m = m_run == -INFINITY ? 0.f : -m_run;
       float l0 = 0.f, l1 = 0.f;
-      auto exp_pack = [&](const float (&src)[32], uint32_t* dst) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float p0 = ex2_approx(fmaf(src[2 * i], sl2, neg_m)), p1 = ex2_approx(fmaf(src[2 * i + 1], sl2, neg_m));
+      for (int h = 0; h < 2; ++h) {
+        uint32_t w[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float p0 = ex2_approx(fmaf(sc[h * 64 + 2 * i], sl2, neg_m)), p1 = ex2_approx(fmaf(sc[h * 64 + 2 * i + 1], sl2, neg_m));
           l0 += p0;
           l1 += p1;
-          dst[i] = pack_bf16(p0, p1);
+          w[i] = pack_bf16(p0, p1);
         }
-      };
-      {
-        uint32_t w[32];
-        exp_pack(s0, w);
-        exp_pack(s1, w + 16);
-        tmem_st32(t_s, w);                                      // columns [0, 32): keys 0..63, already in registers
+        tmem_st32_issue(t_s + h * 32, w);
       }
-      LMSF_T(12);
-      {
-        uint32_t w[32];
-        float t[32];
-        if (need_mask) load32(64, t, std::true_type{});
-        else load32(64, t, std::false_type{});
-        exp_pack(t, w);
-        if (need_mask) load32(96, t, std::true_type{});
-        else load32(96, t, std::false_type{});
-        exp_pack(t, w + 16);
-        tmem_st32(t_s + 32, w);                                 // columns [32, 64): keys 64..127
-      }
-      LMSF_T(13);
+      tmem_wait_st();
       l_run += l0 + l1;
+      LMSF_T(12);
       tc_fence_before();
       mbar_arrive(p_full(x));
       if ((warp & 3) == 0) LMSF_TRACE(x, j, 1);
@@ -586,6 +581,8 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
       }
     }
     LMSF_T_END();
+  } else {
+    regs_dec<kRegsOther>();
   }
   tc_fence_before();
   __syncthreads();
