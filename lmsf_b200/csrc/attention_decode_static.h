@@ -16,15 +16,17 @@
 // allocating routine.
 //
 // Limits and rules.
-//   * n_seqs_total * n_q_heads * n_splits * (head_dim + 1) * 4 bytes must fit in 8 MiB; a larger
+//   * 256 KiB of counters + n_seqs_total * n_q_heads * n_splits * (head_dim + 1) * 4 bytes must fit in 8 MiB; a larger
 //     request is refused with LMSF_EBADARG and a message (lmsf_attention_mma_last_error()).
 //   * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with
 //     that device current) and sets the kernel's shared-memory limit.  Make that first call
 //     outside any stream capture.
-//   * All calls share the one array, and it keeps what the last call left in it.  Nothing in it
-//     has to start at zero: every value that a call reads was written by that same call.  Two
-//     calls that overlap on the GPU (different streams, no ordering between them) race on it and
-//     give wrong results; order them.
+//   * All calls share the one array, and it keeps what the last call left in it.  The partial
+//     results that a call reads were written by that same call.  The counters at the array's start
+//     (one per request and group of heads: how many key splits have delivered) start as zeros, as static
+//     storage does, and every call that completes leaves them zero again.  Two calls that overlap
+//     on the GPU (different streams, no ordering between them) race on the array and give wrong
+//     results; order them.
 #pragma once
 #include "common.cuh"
 

@@ -38,6 +38,7 @@ struct DecodeArgs {
   bf16* out; long long out_stride;           // [n_tokens][n_q_heads * HD]
   float* part_o;                             // [n_seqs][n_q_heads][n_splits][HD] (n_splits > 1)
   float* part_lse;                           // [n_seqs][n_q_heads][n_splits]
+  unsigned* counters;                        // [n_seqs][grid.y]: splits that have delivered; zero between launches
   PagedKV kv;
   const int* block_table; int max_blocks;
   const int* seq_ids;                        // [grid.z] requests served (null: 0, 1, 2, ...)
@@ -54,11 +55,17 @@ struct RowState {
 };
 
 // ------------------------------------------------------------------------------------------------ decode
+constexpr int kTableCache = 512;           // block-table entries of a split that are kept in shared memory
+constexpr int kMergeWeights = 4096;        // (heads of a block) x splits whose weights fit the shared memory used for adding up
+
 __global__ void __launch_bounds__(kThreads) decode_kernel(DecodeArgs a) {
   extern __shared__ __align__(16) unsigned char smem[];
+  __shared__ int s_table[kTableCache];
+  __shared__ int s_is_last;
   const int split = blockIdx.x;
   pdl_launch_dependents();
-  pdl_wait();
+  // Until pdl_wait() only what no kernel of this step writes is read: the step's tables, and keys that were
+  // cached before this step.  The kernel before this one writes the new token's key, value and query.
   const int chunks_per_kvh = (a.group + 15) / 16;
   const int kvh = blockIdx.y / chunks_per_kvh, hchunk = blockIdx.y % chunks_per_kvh;
   const int seq = a.seq_ids ? a.seq_ids[blockIdx.z] : blockIdx.z;
@@ -78,6 +85,33 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(DecodeArgs a) {
   const int tile_end = min(tile_hi, tile_begin + per_split);
   const int n_tiles = max(0, tile_end - tile_begin);
 
+  // the split's slice of the block table goes to shared memory, so that no copy of the loop waits for a
+  // table entry from global memory
+  int table_off = 0;
+  if (n_tiles > 0) {
+    const int blk0 = (tile_begin * kTileKeys) >> a.kv.block_shift;
+    const int blk1 = min(a.max_blocks, ((min(ctx, tile_end * kTileKeys) - 1) >> a.kv.block_shift) + 1);
+    if (blk1 - blk0 <= kTableCache) {
+      for (int i = threadIdx.x; i < blk1 - blk0; i += kThreads) s_table[i] = table[blk0 + i];
+      __syncthreads();
+      table = s_table;
+      table_off = blk0;
+    }
+  }
+
+  const uint32_t smem_base = smem_u32(smem);
+  // first stages: tiles that end before the new token are requested now, the others after the wait
+  const int safe_end = (ctx - 1) / kTileKeys;                  // tiles below this index hold only older keys
+  for (int s = 0; s < kStages - 1; ++s)
+    if (s < n_tiles && tile_begin + s < safe_end)
+      load_stage<HD>(smem_base + s * St::kBytes, a.kv, table, kvh, (tile_begin + s) * kTileKeys, lo, ctx, table_off);
+  pdl_wait();
+  for (int s = 0; s < kStages - 1; ++s) {
+    if (s < n_tiles && tile_begin + s >= safe_end)
+      load_stage<HD>(smem_base + s * St::kBytes, a.kv, table, kvh, (tile_begin + s) * kTileKeys, lo, ctx, table_off);
+    cp_async_commit();
+  }
+
   // q fragments: rows = heads (zero beyond n_heads), all k-steps
   uint32_t qf[kKSteps][4];
   {
@@ -92,12 +126,6 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(DecodeArgs a) {
     }
   }
 
-  const uint32_t smem_base = smem_u32(smem);
-  for (int s = 0; s < kStages - 1; ++s) {
-    if (s < n_tiles) load_stage<HD>(smem_base + s * St::kBytes, a.kv, table, kvh, (tile_begin + s) * kTileKeys, lo, ctx);
-    cp_async_commit();
-  }
-
   RowState st{{-INFINITY, -INFINITY}, {0.f, 0.f}};
   float o[HD / 8][4];
 #pragma unroll
@@ -110,7 +138,7 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(DecodeArgs a) {
     {
       const int nxt = i + kStages - 1;
       if (nxt < n_tiles)
-        load_stage<HD>(smem_base + (nxt % kStages) * St::kBytes, a.kv, table, kvh, (tile_begin + nxt) * kTileKeys, lo, ctx);
+        load_stage<HD>(smem_base + (nxt % kStages) * St::kBytes, a.kv, table, kvh, (tile_begin + nxt) * kTileKeys, lo, ctx, table_off);
       cp_async_commit();
     }
     const uint32_t kbase = smem_base + (i % kStages) * St::kBytes + warp * 16 * St::kRowBytes;
@@ -222,27 +250,77 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(DecodeArgs a) {
       if (d == 0) a.part_lse[pi] = L > 0.f ? M + log2f(L) : -INFINITY;   // base-2 log-sum-exp
     }
   }
-}
+  if (a.n_splits == 1) return;
 
-// out = sum_s part_o[s] 2^(lse_s - max) / sum_s 2^(lse_s - max); one block per (request, head)
-__global__ void decode_merge_kernel(DecodeArgs a) {
-  pdl_launch_dependents();
-  pdl_wait();
-  const int seq = a.seq_ids ? a.seq_ids[blockIdx.y] : blockIdx.y;
-  const int head = blockIdx.x;
-  const size_t base = ((size_t)seq * a.n_q_heads + head) * a.n_splits;
-  float M = -INFINITY;
-  for (int s = 0; s < a.n_splits; ++s) M = fmaxf(M, a.part_lse[base + s]);
-  const int token = a.cu_q[seq];
-  for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+  // The split that delivers last adds the splits up, always in the order of the splits:
+  // out = sum_s part_o[s] 2^(lse_s - max) / sum_s 2^(lse_s - max).
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned* cnt = a.counters + (size_t)seq * gridDim.y + blockIdx.y;
+    const unsigned before = atomicAdd(cnt, 1u);
+    s_is_last = before == (unsigned)a.n_splits - 1;
+    if (s_is_last) *cnt = 0;                 // every split has counted: the counter is left as it was found
+  }
+  __syncthreads();
+  if (!s_is_last) return;
+  __threadfence();
+  const size_t base0 = ((size_t)seq * a.n_q_heads + head0) * a.n_splits;      // the block's heads are consecutive
+  const int n_w = n_heads * a.n_splits;
+  float* s_w = reinterpret_cast<float*>(smem);                                   // the stages are free
+  if (n_w <= kMergeWeights) {
+    // weights of all splits first (log-sum-exp values arrive together, not one after the other), then the sums
+    for (int i = threadIdx.x; i < n_w; i += kThreads) s_w[i] = __ldcg(a.part_lse + base0 + i);
+    __syncthreads();
+    for (int row = warp; row < n_heads; row += 4) {
+      float* w = s_w + row * a.n_splits;
+      float M = -INFINITY;
+      for (int s = lane; s < a.n_splits; s += 32) M = fmaxf(M, w[s]);
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
+      float L = 0.f;
+      for (int s = lane; s < a.n_splits; s += 32) {
+        const float f = w[s] == -INFINITY ? 0.f : exp2f(w[s] - M);
+        w[s] = f;
+        L += f;
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) L += __shfl_xor_sync(0xffffffffu, L, off);
+      const float inv = 1.0f / L;
+      for (int s = lane; s < a.n_splits; s += 32) w[s] *= inv;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < n_heads * HD; idx += kThreads) {
+      const int row = idx / HD, d = idx % HD;
+      const float* po = a.part_o + (base0 + (size_t)row * a.n_splits) * HD + d;
+      const float* w = s_w + row * a.n_splits;
+      float acc = 0.f;
+      int s = 0;
+      for (; s + 8 <= a.n_splits; s += 8) {
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = __ldcg(po + (size_t)(s + u) * HD);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) acc += v[u] * w[s + u];
+      }
+      for (; s < a.n_splits; ++s) acc += __ldcg(po + (size_t)s * HD) * w[s];
+      a.out[(size_t)token * a.out_stride + (size_t)(head0 + row) * HD + d] = __float2bfloat16_rn(acc);
+    }
+    return;
+  }
+  for (int idx = threadIdx.x; idx < n_heads * HD; idx += kThreads) {
+    const int row = idx / HD, d = idx % HD;
+    const size_t base = base0 + (size_t)row * a.n_splits;
+    float M = -INFINITY;
+    for (int s = 0; s < a.n_splits; ++s) M = fmaxf(M, __ldcg(a.part_lse + base + s));
     float acc = 0.f, L = 0.f;
     for (int s = 0; s < a.n_splits; ++s) {
-      const float lse = a.part_lse[base + s];
+      const float lse = __ldcg(a.part_lse + base + s);
       const float f = lse == -INFINITY ? 0.f : exp2f(lse - M);
       L += f;
-      acc += a.part_o[(base + s) * HD + d] * f;
+      acc += __ldcg(a.part_o + (base + s) * HD + d) * f;
     }
-    a.out[(size_t)token * a.out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(acc / L);
+    a.out[(size_t)token * a.out_stride + (size_t)(head0 + row) * HD + d] = __float2bfloat16_rn(acc / L);
   }
 }
 
@@ -257,7 +335,9 @@ static int decode_smem_bytes() {
   using namespace lmsf::fa;
   const int smem_stages = kStages * St::kBytes;
   const int smem_merge = (4 * 16 * HD + 2 * 4 * 16) * (int)sizeof(float);
-  return smem_stages > smem_merge ? smem_stages : smem_merge;
+  const int smem_weights = kMergeWeights * (int)sizeof(float);     // weights of the splits when they are added up
+  const int m = smem_stages > smem_merge ? smem_stages : smem_merge;
+  return m > smem_weights ? m : smem_weights;
 }
 
 // Blocks of the decode kernel that one SM holds at a time (0 on error); used to size the key splits.
@@ -270,14 +350,19 @@ LMSF_API int lmsf_attention_decode_blocks_per_sm() {
   return n;
 }
 
-// Bytes of scratch that lmsf_attention_decode needs for the given sizes (0 when n_splits == 1).
+// Bytes of scratch that lmsf_attention_decode needs for the given sizes (0 when n_splits == 1): counters of
+// the splits that have delivered (one per request and group of heads, always the first kDecodeCounterBytes,
+// whatever the sizes of a call, so that calls of different sizes can share one buffer), then partial results.
+constexpr long long kDecodeCounterSlots = 65536;
+constexpr long long kDecodeCounterBytes = kDecodeCounterSlots * (long long)sizeof(unsigned);
 LMSF_API long long lmsf_attention_decode_scratch_bytes(int n_seqs_total, int n_q_heads, int n_splits) {
   if (n_splits <= 1) return 0;
-  return (long long)n_seqs_total * n_q_heads * n_splits * (lmsf::fa::HD + 1) * (long long)sizeof(float);
+  return kDecodeCounterBytes + (long long)n_seqs_total * n_q_heads * n_splits * (lmsf::fa::HD + 1) * (long long)sizeof(float);
 }
 
 // One query token per served request.  seq_ids (may be null) lists the n_served requests among the
-// n_seqs_total rows of block_table / cu_q / ctx_len.  scratch: lmsf_attention_decode_scratch_bytes().
+// n_seqs_total rows of block_table / cu_q / ctx_len.  scratch: lmsf_attention_decode_scratch_bytes(), zero when
+// it is first used; a launch that completes leaves its counters zero again, so the same memory serves every call.
 LMSF_API int lmsf_attention_decode(const void* q, long long q_stride, void* out, long long out_stride,
                                    const void* cache, long long page_stride, int block_size, int n_kv_heads,
                                    const int* block_table, int max_blocks, const int* seq_ids, int n_served,
@@ -297,7 +382,11 @@ LMSF_API int lmsf_attention_decode(const void* q, long long q_stride, void* out,
   if (gy > 65535 || n_served > 65535) LMSF_REFUSE("attention_decode: too many heads or requests for one launch");
   DecodeArgs a;
   a.q = (const bf16*)q; a.q_stride = q_stride; a.out = (bf16*)out; a.out_stride = out_stride;
-  a.part_o = (float*)scratch;
+  if (n_splits > 1 && (long long)n_seqs_total * gy > kDecodeCounterSlots)
+    LMSF_REFUSE("attention_decode: %d requests x %lld head groups exceed the %lld split counters; use n_splits=1",
+                n_seqs_total, gy, kDecodeCounterSlots);
+  a.counters = (unsigned*)scratch;
+  a.part_o = scratch ? reinterpret_cast<float*>((unsigned char*)scratch + kDecodeCounterBytes) : nullptr;
   a.part_lse = a.part_o ? a.part_o + (size_t)n_seqs_total * n_q_heads * n_splits * HD : nullptr;
   if (!make_paged_kv(a.kv, cache, page_stride, block_size, n_kv_heads))
     LMSF_REFUSE("attention: block_size=%d must be a power of two", block_size);
@@ -311,10 +400,7 @@ LMSF_API int lmsf_attention_decode(const void* q, long long q_stride, void* out,
     configured = true;
   }
   cudaStream_t s = (cudaStream_t)stream;
-  int rc = launch_pdl(decode_kernel, dim3(n_splits, (unsigned)gy, n_served), dim3(kThreads), smem, s, a);
-  if (rc) return rc;
-  if (n_splits > 1) rc = launch_pdl(decode_merge_kernel, dim3(n_q_heads, n_served), dim3(HD >= 64 ? 64 : 32), 0, s, a);
-  return rc;
+  return launch_pdl(decode_kernel, dim3(n_splits, (unsigned)gy, n_served), dim3(kThreads), smem, s, a);
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -73,9 +73,10 @@ template <int HD> struct Stage {
 // Keys outside [lo, hi) and keys whose page entry is negative are zero-filled, never read.
 // A thread copies one 16-byte column of several CONSECUTIVE rows, so that it looks its page up once per
 // page rather than once per row; a warp's copies of one pass cover whole rows (coalesced).
+// `table` may be a copy of a slice of the request's block table: entry i of it is block i + table_off.
 template <int HD>
 __device__ __forceinline__ void load_stage(uint32_t stage_base, const PagedKV& kv, const int* __restrict__ table, int kvh,
-                                           int key0, int lo, int hi) {
+                                           int key0, int lo, int hi, int table_off = 0) {
   using S = Stage<HD>;
   const size_t v_off = (size_t)kv.n_kv_heads * kv.block_size * HD;
   const size_t head_off = (size_t)kvh * kv.block_size * HD;
@@ -91,7 +92,7 @@ __device__ __forceinline__ void load_stage(uint32_t stage_base, const PagedKV& k
       const bool in_range = key >= lo && key < hi;
       if (slot == 0) have_page = false;
       if (in_range && !have_page) {
-        const int page = table[key >> kv.block_shift];
+        const int page = table[(key >> kv.block_shift) - table_off];
         page_ptr = page >= 0 ? kv.cache + (size_t)page * kv.page_stride + head_off + c * 8 : nullptr;
         have_page = true;
       }
@@ -110,7 +111,7 @@ __device__ __forceinline__ void load_stage(uint32_t stage_base, const PagedKV& k
       const bf16* src = kv.cache;
       int bytes = 0;
       if (key >= lo && key < hi) {
-        const int page = table[key >> kv.block_shift];
+        const int page = table[(key >> kv.block_shift) - table_off];
         if (page >= 0) {
           src = kv.cache + (size_t)page * kv.page_stride + head_off + (size_t)(key & mask) * HD + c * 8;
           bytes = 16;

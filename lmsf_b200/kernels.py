@@ -371,8 +371,11 @@ def decode_num_splits(n_served: int, n_kv_heads: int, group: int, max_ctx: int, 
     return max(1, min(resident // max(1, base), -(-max_ctx // 128), 64))
 
 
+DECODE_COUNTER_SLOTS = 65536     # counters of delivered splits at the start of the scratch (attention_mma.cu)
+
+
 def attention_decode_scratch_floats(n_seqs_total: int, n_q_heads: int, n_splits: int, head_dim: int) -> int:
-    return 0 if n_splits <= 1 else n_seqs_total * n_q_heads * n_splits * (head_dim + 1)
+    return 0 if n_splits <= 1 else DECODE_COUNTER_SLOTS + n_seqs_total * n_q_heads * n_splits * (head_dim + 1)
 
 
 def attention_decode(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
@@ -381,7 +384,8 @@ def attention_decode(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, bl
                      head_dim: int, n_splits: int, scratch: Optional[torch.Tensor]):
     """Attention of requests that bring ONE query token each (row cu_q[s] of q), over their ctx_len[s] keys
     in pages.  seq_ids: int32 [n_served] rows of the block table that are served (None: all, in order).
-    scratch: float32, at least attention_decode_scratch_floats(...) values when n_splits > 1."""
+    scratch: float32, at least attention_decode_scratch_floats(...) values when n_splits > 1, all zero when it is
+    first used (torch.zeros); the kernel leaves its counters zero, so one buffer serves every later call."""
     _check_paged(q, out, cache, n_q_heads, n_kv_heads, head_dim, block_size, "attention_decode")
     n_total = block_table.shape[0]
     need = attention_decode_scratch_floats(n_total, n_q_heads, n_splits, head_dim)
@@ -396,8 +400,6 @@ def attention_decode(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, bl
            _i32(cu_q, "cu_q"), _i32(ctx_len, "ctx_len"), float(scale), int(window or 0), n_q_heads, head_dim,
            n_splits, _ptr(scratch) if need else None, _stream())
     _check(rc, "attention_mma.cu", "lmsf_attention_mma", d)
-    if n_splits > 1:
-        add_launches(1)
 
 
 def attention_prefill(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,

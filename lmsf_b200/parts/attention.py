@@ -97,7 +97,7 @@ class PagedAttention(Mixer):
                 need = kernels.attention_decode_scratch_floats(ctx.n_seqs, self.num_heads, splits, self.head_dim)
                 scratch = ctx.extras.get("decode_scratch")
                 if need and (scratch is None or scratch.numel() < need):
-                    scratch = ctx.extras["decode_scratch"] = torch.empty(need, dtype=torch.float32, device=q.device)
+                    scratch = ctx.extras["decode_scratch"] = torch.zeros(need, dtype=torch.float32, device=q.device)
                 all_decode = ctx.n_decode_seqs == ctx.n_seqs
                 kernels.attention_decode(out, q, kv, group.block_table, group.block_size,
                                          None if all_decode else ctx.decode_seq_ids, ctx.n_decode_seqs, ctx.cu_q,

@@ -285,7 +285,7 @@ def test_attention_tensor_core_kernels(nh, nkv, hd, bs, window):
     tol_abs = 2e-2 * ref.abs().max().item()
     for splits in (1, 2, 5, 24):
         out = torch.zeros(q.shape, dtype=torch.bfloat16, device=d)
-        scratch = torch.empty(max(1, kernels.attention_decode_scratch_floats(len(q_lens), nh, splits, hd)),
+        scratch = torch.zeros(max(1, kernels.attention_decode_scratch_floats(len(q_lens), nh, splits, hd)),
                               dtype=torch.float32, device=d)
         kernels.attention_decode(out, qd, cd, btd, bs, torch.tensor(dec, dtype=torch.int32, device=d), len(dec), cu, cl,
                                  scale, window, nh, nkv, hd, splits, scratch)

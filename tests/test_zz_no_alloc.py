@@ -48,7 +48,7 @@ def test_static_scratch_variant_matches_the_ordinary_entry_point_twice_in_a_row(
         q, cache, bt, cu, cl = _case(nh, nkv, hd, bs, ctx_lens, seed)
         scale = 1.0 / math.sqrt(hd)
         want = torch.zeros_like(q)
-        scratch = torch.empty(kernels.attention_decode_scratch_floats(len(ctx_lens), nh, splits, hd),
+        scratch = torch.zeros(kernels.attention_decode_scratch_floats(len(ctx_lens), nh, splits, hd),
                               dtype=torch.float32, device=q.device)
         kernels.attention_decode(want, q, cache, bt, bs, None, len(ctx_lens), cu, cl, scale, 0, nh, nkv, hd, splits, scratch)
         got = torch.zeros_like(q)
