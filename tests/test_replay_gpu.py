@@ -13,7 +13,7 @@ pytestmark = pytest.mark.gpu
 
 # max |difference| allowed, as a fraction of the largest reference logit
 REL = {"float32": 1e-5, "bfloat16": 5e-2}
-LENGTHS = {"A": [5, 17, 33, 70], "B": [1, 9, 40, 64, 130], "W": [3, 50, 90, 41]}
+LENGTHS = {"A": [5, 17, 33, 70], "B": [1, 9, 40, 64, 130], "W": [3, 50, 90, 41], "C": [2, 60, 140, 300]}
 
 
 def requests_for(name, seed=0):
@@ -42,7 +42,7 @@ def check(rows, ref, dtype, reqs):
 
 @pytest.mark.parametrize("std", [0.02, 0.15])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "W"])
+@pytest.mark.parametrize("name", ["A", "B", "W", "C"])
 def test_every_way_of_cutting_agrees_with_the_plain_implementation(name, dtype, std):
     reqs = requests_for(name)
     ref = reference(name, dtype, std, reqs)

@@ -23,8 +23,15 @@ TINY_W = dict(architectures=["LlamaForCausalLM"], model_type="llama", hidden_siz
               rope_theta=10000.0, rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=512,
               sliding_window=24, hidden_act="silu", bos_token_id=1, eos_token_id=2)
 
-BLOCK_SIZE = {"A": 8, "B": 16, "W": 16}
-CONFIGS = {"A": TINY_A, "B": TINY_B, "W": TINY_W}
+# a fourth one with the head size of the tcgen05 attention kernel, an odd group of query heads (a pair and a single
+# head per block) and prompts that span several 128-token query tiles
+TINY_C = dict(architectures=["LlamaForCausalLM"], model_type="llama", hidden_size=80, num_hidden_layers=2,
+              num_attention_heads=6, num_key_value_heads=2, head_dim=64, intermediate_size=112, vocab_size=391,
+              rope_theta=10000.0, rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=512,
+              hidden_act="silu", bos_token_id=1, eos_token_id=2)
+
+BLOCK_SIZE = {"A": 8, "B": 16, "W": 16, "C": 16}
+CONFIGS = {"A": TINY_A, "B": TINY_B, "W": TINY_W, "C": TINY_C}
 
 _folders = {}
 
