@@ -91,7 +91,7 @@ class ModelRunner:
         self.enforce_eager = enforce_eager
         self.max_graph_batch = max_num_seqs
         self.static_blocks = (self.max_model_len + block_size - 1) // block_size
-        self.graph_safe = all(getattr(b.mixer, "graph_safe", False) for b in model.blocks if b.mixer is not None)
+        self.graph_safe = all(getattr(part, "graph_safe", False) for part, _ in model.parts_with_specs())
         self._graphs = {}
         self._seen_sizes = set()
         self._graph_pool = None

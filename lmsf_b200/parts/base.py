@@ -154,6 +154,11 @@ Q_TILE = 64      # query tokens per tile in StepContext.q_tile_*
 class Part:
     """Base of every part.  A part declares its weights, receives them, and computes."""
 
+    # True when the part's work in a step of single tokens depends on the batch's size only (no value read back
+    # to the host, no launch whose shape depends on the data): only then may such a step be captured as a CUDA
+    # graph and replayed.  A part that does not say so keeps its model on eager steps.
+    graph_safe = False
+
     def weight_specs(self) -> Dict[str, WeightSpec]:
         return {}
 
@@ -249,7 +254,18 @@ def build_part(family: str, spec: PartSpec) -> Part:
     params = dict(spec.params)
     # a nested PartSpec is built first; its key names its family
     # (e.g. params["position_encoding"] of an attention mixer)
+    nested = []
     for k, v in list(params.items()):
         if isinstance(v, PartSpec):
             params[k] = build_part(k, v)
-    return part_class(family, spec.kind)(**params)
+            nested.append((params[k], v))
+    part = part_class(family, spec.kind)(**params)
+    part.nested_parts = nested        # parts with weights of their own are loaded like any other
+    return part
+
+
+def with_nested(part: Part, spec: PartSpec):
+    """(part, spec) and, after it, every part nested inside it with its own spec."""
+    yield part, spec
+    for child, child_spec in getattr(part, "nested_parts", ()):
+        yield from with_nested(child, child_spec)

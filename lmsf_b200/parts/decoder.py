@@ -13,7 +13,7 @@ import torch
 
 from .. import kernels
 from .base import (Block, KVCacheSpec, LayerCache, ModelSpec, Part, PartSpec, StateSpec, StepContext, build_part,
-                   part_class)
+                   part_class, with_nested)
 
 
 class DecoderModel:
@@ -21,7 +21,7 @@ class DecoderModel:
         self.spec = spec
         self.embedding = build_part("embedding", spec.embedding)
         self.blocks: List[Block] = []
-        self._owned: List[Tuple[Part, PartSpec]] = [(self.embedding, spec.embedding)]
+        self._owned: List[Tuple[Part, PartSpec]] = list(with_nested(self.embedding, spec.embedding))
         for ls in spec.layers:
             cls = part_class("block", ls.block)
             missing = [r for r in cls.ROLES if r not in ls.parts]
@@ -30,11 +30,11 @@ class DecoderModel:
             parts = {}
             for role, family in cls.ROLES.items():
                 parts[role] = build_part(family, ls.parts[role])
-                self._owned.append((parts[role], ls.parts[role]))
+                self._owned += list(with_nested(parts[role], ls.parts[role]))
             self.blocks.append(cls(parts, **ls.block_params))
         self.final_norm = build_part("norm", spec.final_norm)
         self.lm_head = build_part("linear", spec.lm_head)
-        self._owned += [(self.final_norm, spec.final_norm), (self.lm_head, spec.lm_head)]
+        self._owned += [*with_nested(self.final_norm, spec.final_norm), *with_nested(self.lm_head, spec.lm_head)]
         self.calls = list(spec.order)
         for j, call in enumerate(self.calls):
             if not (0 <= call.layer < len(self.blocks)):

@@ -11,6 +11,8 @@ from .base import Part, StepContext, WeightSpec, register_part
 
 @register_part("embedding", "token_embedding")
 class TokenEmbedding(Part):
+    graph_safe = True
+
     def __init__(self, vocab_size: int, hidden_size: int):
         self.vocab_size, self.hidden_size = int(vocab_size), int(hidden_size)
         self.weight: Optional[torch.Tensor] = None

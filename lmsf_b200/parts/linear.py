@@ -51,6 +51,7 @@ def matmul_tn(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype]
 @register_part("linear", "dense")
 class Linear(Part):
     """out_features may be a list: the sources are stacked along the output dimension."""
+    graph_safe = True
 
     def __init__(self, in_features: int, out_features: Union[int, Sequence[int]], out_dtype: Optional[str] = None):
         self.in_features = int(in_features)

@@ -18,6 +18,8 @@ from .linear import matmul_tn
 
 @register_part("feed_forward", "gated_mlp")
 class GatedMLP(FeedForward):
+    graph_safe = True
+
     def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu"):
         if activation not in kernels.ACT_CODES:
             raise ValueError(f"activation {activation!r} is not supported (known: {', '.join(sorted(kernels.ACT_CODES))})")

@@ -16,6 +16,8 @@ from .base import Norm, WeightSpec, register_part
 
 @register_part("norm", "rmsnorm")
 class RMSNorm(Norm):
+    graph_safe = True
+
     def __init__(self, hidden_size: int, eps: float):
         self.hidden_size = int(hidden_size)
         self.eps = float(eps)

@@ -48,6 +48,8 @@ def rope_inverse_frequencies(rot_dim: int, theta: float, scaling_type: str = "de
 
 @register_part("position_encoding", "rotary")
 class RotaryEmbedding(PositionEncoding):
+    graph_safe = True
+
     def __init__(self, rot_dim: int, theta: float = 10000.0, is_neox: bool = True, scaling_type: str = "default",
                  factor: float = 1.0, low_freq_factor: float = 1.0, high_freq_factor: float = 4.0,
                  original_max_position_embeddings: int = 8192):
@@ -76,6 +78,8 @@ class RotaryEmbedding(PositionEncoding):
 
 @register_part("position_encoding", "none")
 class NoPositionEncoding(PositionEncoding):
+    graph_safe = True
+
     def __init__(self):
         pass
 

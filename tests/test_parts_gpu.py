@@ -223,6 +223,136 @@ def test_toy_architecture_is_registered_built_and_stepped(tmp_path, dtype, rel):
         assert worst <= rel * scale, (mode, worst, scale)
 
 
+# ----------------------------------------------------------------------------- a second toy: routing and another position encoding
+
+def _register_toy_routed():
+    from lmsf_b200.config.registry import register_architecture
+    from lmsf_b200.parts.base import (FeedForward, LayerCall, LayerSpec, ModelSpec, PartSpec, PositionEncoding, WeightSpec,
+                                      register_part)
+    from lmsf_b200.parts.linear import matmul_tn
+
+    @register_part("position_encoding", "toy_learned_shift")
+    class ToyLearnedShift(PositionEncoding):
+        """q and k of every head get a learned vector of their position added (no rotation: the cache-write
+        kernel cannot apply it, so the attention part calls apply() before it writes k)."""
+
+        def __init__(self, max_positions, head_dim):
+            self.max_positions, self.head_dim = max_positions, head_dim
+
+        def weight_specs(self):
+            return {"table": WeightSpec([(self.max_positions, self.head_dim)])}
+
+        def apply(self, ctx, q, k, n_q_heads, n_kv_heads, head_dim):
+            shift = self.table[ctx.positions.long()]                       # [n, head_dim]
+            q.view(-1, n_q_heads, head_dim).add_(shift[:, None, :])
+            if k is not None:
+                k.view(-1, n_kv_heads, head_dim).add_(shift[:, None, :])
+
+    @register_part("feed_forward", "toy_top1_experts")
+    class ToyTop1Experts(FeedForward):
+        """Router logits in float32; every token goes through the one expert with the largest logit, scaled by
+        its softmax weight."""
+
+        def __init__(self, hidden_size, inter, n_experts):
+            self.hidden_size, self.inter, self.n_experts = hidden_size, inter, n_experts
+
+        def weight_specs(self):
+            return {"router": WeightSpec([(self.n_experts, self.hidden_size)]),
+                    "up": WeightSpec([(self.n_experts * self.inter, self.hidden_size)]),
+                    "down": WeightSpec([(self.n_experts * self.hidden_size, self.inter)])}
+
+        def forward(self, ctx, h):
+            logits = h.float() @ self.router.float().T
+            weight, expert = torch.softmax(logits, dim=-1).max(dim=-1)
+            out = torch.zeros_like(h)
+            for e in range(self.n_experts):
+                rows = (expert == e).nonzero().flatten()
+                if rows.numel() == 0:
+                    continue
+                up = self.up[e * self.inter:(e + 1) * self.inter]
+                down = self.down[e * self.hidden_size:(e + 1) * self.hidden_size]
+                m = torch.relu(matmul_tn(h[rows].contiguous(), up))
+                out[rows] = (matmul_tn(m, down).float() * weight[rows, None]).to(h.dtype)
+            return out
+
+    def spec(c):
+        H = c["hidden_size"]
+        norm = lambda name: PartSpec("rmsnorm", dict(hidden_size=H, eps=c["eps"]), {"weight": name})
+        def layer(i):
+            shift = PartSpec("toy_learned_shift", dict(max_positions=c["max_len"], head_dim=c["head_dim"]), {"table": f"l{i}.pos"})
+            attn = PartSpec("paged_attention", dict(hidden_size=H, num_heads=c["heads"], num_kv_heads=c["kv_heads"],
+                                                    head_dim=c["head_dim"], position_encoding=shift),
+                            {"qkv": [f"l{i}.q", f"l{i}.k", f"l{i}.v"], "o": f"l{i}.o"})
+            ffn = PartSpec("toy_top1_experts", dict(hidden_size=H, inter=c["inter"], n_experts=c["experts"]),
+                           {"router": f"l{i}.r", "up": f"l{i}.u", "down": f"l{i}.d"})
+            return LayerSpec("pre_norm", {"mixer_norm": norm(f"l{i}.n1"), "mixer": attn, "ffn_norm": norm(f"l{i}.n2"),
+                                          "feed_forward": ffn})
+        n = c["layers"]
+        return ModelSpec(hidden_size=H, vocab_size=c["vocab"], max_model_len=c["max_len"],
+                         embedding=PartSpec("token_embedding", dict(vocab_size=c["vocab"], hidden_size=H), {"weight": "emb"}),
+                         layers=[layer(i) for i in range(n)], order=[LayerCall(i) for i in range(n)], final_norm=norm("nf"),
+                         lm_head=PartSpec("dense", dict(in_features=H, out_features=c["vocab"], out_dtype="float32"),
+                                          {"weight": "head"}))
+
+    register_architecture("ToyRoutedForTests", dict, spec)
+
+
+TOY_ROUTED = dict(architectures=["ToyRoutedForTests"], hidden_size=40, heads=4, kv_heads=2, head_dim=16, inter=24, experts=3,
+                  layers=2, vocab=83, eps=1e-6, max_len=128)
+
+
+def _toy_routed_reference(model, ids):
+    c = TOY_ROUTED
+    W = lambda t: t.float().cpu()
+    x = P.embedding(W(model.embedding.weight), torch.tensor(ids))
+    T = len(ids)
+    for blk in model.blocks:
+        m, ff = blk.mixer, blk.feed_forward
+        h = P.rms_norm(x, W(blk.mixer_norm.weight), c["eps"])
+        nh, nkv, hd = m.num_heads, m.num_kv_heads, m.head_dim
+        qkv = h @ W(m.qkv).T
+        shift = W(m.position_encoding.table)[:T]
+        q = qkv[:, :nh * hd].reshape(T, nh, hd) + shift[:, None, :]
+        k = qkv[:, nh * hd:(nh + nkv) * hd].reshape(T, nkv, hd) + shift[:, None, :]
+        v = qkv[:, (nh + nkv) * hd:].reshape(T, nkv, hd)
+        x = x + P.causal_attention(q, k, v, 1.0 / math.sqrt(hd), None).reshape(T, nh * hd) @ W(m.o).T
+        h = P.rms_norm(x, W(blk.ffn_norm.weight), c["eps"])
+        weight, expert = torch.softmax(h @ W(ff.router).T, dim=-1).max(dim=-1)
+        out = torch.zeros_like(h)
+        for t in range(T):
+            e = int(expert[t])
+            up, down = W(ff.up)[e * ff.inter:(e + 1) * ff.inter], W(ff.down)[e * ff.hidden_size:(e + 1) * ff.hidden_size]
+            out[t] = (torch.relu(h[t] @ up.T) @ down.T) * weight[t]
+        x = x + out
+    return P.rms_norm(x, W(model.final_norm.weight), c["eps"]) @ W(model.lm_head.weight).T
+
+
+def test_toy_routing_and_another_position_encoding_need_no_change_to_the_package(tmp_path):
+    """A feed-forward that routes tokens to experts and a position encoding that is no rotation, both defined here."""
+    import traces
+    from lmsf_b200.engine.factory import build_model
+    _register_toy_routed()
+    (tmp_path / "config.json").write_text(json.dumps(TOY_ROUTED))
+    model, _, tdt = build_model(str(tmp_path), "float32", DEV, load_format="dummy", seed=5)
+    for part, _ in model.parts_with_specs():
+        for name, ws in part.weight_specs().items():
+            getattr(part, name).mul_(8.0 if name != "router" else 40.0)        # attention and the routing must matter
+    reqs = {f"t{i}": util.random_ids(n, TOY_ROUTED["vocab"], 70 + i) for i, n in enumerate([29, 3, 50, 17])}
+    ref = {rid: _toy_routed_reference(model, toks).numpy() for rid, toks in reqs.items()}
+    experts_used = set()
+    for blk in model.blocks:      # the routing is not trivial: more than one expert is chosen
+        experts_used |= set(torch.randn(64, TOY_ROUTED["hidden_size"], device=DEV).matmul(blk.feed_forward.router.float().T).argmax(-1).tolist())
+    assert len(experts_used) > 1
+    traces._runners[(str(tmp_path), "float32")] = (model, None, tdt)
+    for mode, steps in {"whole": traces.whole(reqs), "portions": traces.portions(reqs, [4, 2, 9]),
+                        "mixed": traces.mixed(reqs, seed=4, max_live=3, tail=6)}.items():
+        out = traces.run_inprocess(str(tmp_path), "float32", steps, 8, traces.max_live_tokens(steps, 8), max_live=3)
+        rows = traces.collect(steps, out)
+        scale = max(1.0, max(float(abs(r).max()) for r in ref.values()))
+        worst = max(float(abs(row - ref[rid][pos]).max()) for (rid, pos), row in rows.items())
+        assert worst <= 5e-5 * scale, (mode, worst, scale)
+
+
 def _hand_context(q_lens, ctx_lens, block_size, n_pages, seed=0):
     """A StepContext and block table made by hand, the way ModelRunner lays a batch out."""
     from lmsf_b200.parts.base import CacheGroupView, StepContext
