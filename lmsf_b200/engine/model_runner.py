@@ -81,7 +81,7 @@ class ModelRunner:
         elif isinstance(num_blocks, int):
             num_blocks = [num_blocks] * len(groups)
         self.storage = CacheStorage(model, block_size, num_blocks, max_num_seqs, dtype, device)
-        self.error_flag = torch.zeros(1, dtype=torch.int32, device=device)
+        self.error_flag = kernels.error_word(device)      # shared with the kernels that have no step context
         self.vocab_size = model.spec.vocab_size
         self.h2d_bytes = 0          # bytes of step inputs copied from pinned host memory so far
         self.sm_count = torch.cuda.get_device_properties(device).multi_processor_count
@@ -312,5 +312,6 @@ class ModelRunner:
             self.error_flag.zero_()
             what = {1: "a token id outside the vocabulary reached the embedding",
                     2: "a token was to be cached at a position that has no page",
-                    3: "a tensor-core attention block gave up waiting for its own products"}.get(code, f"code {code}")
+                    3: "a tensor-core attention block gave up waiting for its own products",
+                    4: "a block of the streaming matrix product gave up waiting for its own copies or products"}.get(code, f"code {code}")
             raise StepError(f"the device reported an error during the step: {what}")

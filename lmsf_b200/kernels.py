@@ -8,6 +8,7 @@ are an error.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Optional, Tuple
 
@@ -258,6 +259,55 @@ def gemm_skinny(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, fuse_act: O
     rc = f(_ptr(out), _ptr(x), _ptr(w), M, N, K, x.stride(0), w.stride(0), out.stride(0),
            ACT_CODES[fuse_act] if fuse_act else -1, int(out.dtype == torch.float32), _stream())
     _check(rc, "gemm_skinny.cu", "lmsf_gemm_skinny", SKINNY_DEFINES)
+
+
+# ----------------------------------------------------------------------------- streaming product on tcgen05 (17..128 rows)
+
+STREAM_MAX_M = 128
+STREAM_CTAS_PER_SM = int(os.environ.get("LMSF_GS_CTAS_PER_SM", "1"))
+STREAM_DEFINES: Tuple[str, ...] = tuple(d for d in os.environ.get("LMSF_GS_DEFINES", "").split(",") if d)
+_ERROR_WORDS = {}
+_STREAM_STATE = {}
+
+
+def error_word(device) -> torch.Tensor:
+    """The int32 word of a device in which kernels report errors that they cannot return (a wait that ran out,
+    an id outside a table); the model runner reads and clears it after a step."""
+    key = torch.device(device).index or 0
+    w = _ERROR_WORDS.get(key)
+    if w is None:
+        w = _ERROR_WORDS[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return w
+
+
+def gemm_stream_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 and 0 < x.shape[0] <= STREAM_MAX_M
+            and x.shape[1] % 8 == 0 and x.stride(1) == 1 and w.stride(1) == 1 and w.stride(0) % 8 == 0
+            and x.stride(0) % 8 == 0 and w.data_ptr() % 16 == 0 and x.data_ptr() % 16 == 0)
+
+
+def gemm_stream(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor):
+    """out[M, N] = x[M, K] w[N, K]^T for M <= 128 (bfloat16 in, bfloat16 or float32 out): W streamed once through
+    tensor-map copies and tcgen05 products, one persistent block per SM (csrc/gemm_stream.cu)."""
+    M, K = x.shape
+    N = w.shape[0]
+    if not gemm_stream_supported(x, w) or w.shape[1] != K or out.shape != (M, N) or out.stride(1) != 1:
+        raise KernelError(f"gemm_stream: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)} are not taken")
+    if out.dtype not in (torch.bfloat16, torch.float32):
+        raise KernelError("gemm_stream: out must be bfloat16 or float32")
+    key = x.device.index or 0
+    st = _STREAM_STATE.get(key)
+    if st is None:
+        n_ctas = STREAM_CTAS_PER_SM * torch.cuda.get_device_properties(x.device).multi_processor_count
+        ws = torch.zeros((1 << 16) + n_ctas * 2 * STREAM_MAX_M * 128, dtype=torch.float32, device=x.device)
+        st = _STREAM_STATE[key] = (n_ctas, ws)
+    n_ctas, ws = st
+    f = _func("gemm_stream.cu", "lmsf_gemm_stream",
+              [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, c_void_p,
+               c_longlong, c_int, c_void_p, c_void_p], STREAM_DEFINES)
+    rc = f(_ptr(out), _ptr(x), _ptr(w), M, N, K, x.stride(0), w.stride(0), out.stride(0), int(out.dtype == torch.float32),
+           _ptr(ws), ws.numel(), n_ctas, _ptr(error_word(x.device)), _stream())
+    _check(rc, "gemm_stream.cu", "lmsf_gemm_stream", STREAM_DEFINES)
 
 
 # ----------------------------------------------------------------------------- sampling
