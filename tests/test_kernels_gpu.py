@@ -375,6 +375,42 @@ def test_gemm_skinny_against_its_plain_twin(M, N, K):
                             torch.zeros(17, K, dtype=torch.bfloat16, device=d), w)
 
 
+def test_attention_kernels_on_a_long_prompt_and_a_long_context():
+    """6,000 tokens in one portion (47 key tiles per block: the rings of stages and the barriers' phases wrap many
+    times) on both prefill kernels, and one decoded token over 16,000 keys in 1, 7 and 64 splits; a sample of rows
+    is compared with float64."""
+    from lmsf_b200 import kernels
+    nh, nkv, hd, bs = 4, 2, 128, 16
+    T = 6000
+    q, cache, bt, token_seq, positions, ks, vs = _paged_setup("bfloat16", nh, nkv, hd, bs, [T, 16000], [T, 1], 21, sharp=True,
+                                                              poison=True)
+    scale = 1.0 / math.sqrt(hd)
+    d = dev()
+    qd, cd, btd = q.to(d), cache.to(d), bt.to(d)
+    cu = torch.tensor([0, T, T + 1], dtype=torch.int32, device=d)
+    cl = torch.tensor([T, 16000], dtype=torch.int32, device=d)
+    rows = sorted(set([0, 1, 127, 128, 129, 2047, 4095, 4096, T - 2, T - 1, T] + list(range(3, T, 487))))
+    sub = torch.tensor(rows)
+    ref = _attention_reference(q.float()[sub], ks, vs, token_seq[sub], positions[sub], nh, nkv, hd, scale, 0)
+    tol = 2e-2 * ref.abs().max().item()
+    flag = torch.zeros(1, dtype=torch.int32, device=d)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=d)
+    out_tc = torch.zeros(q.shape, dtype=torch.bfloat16, device=d)
+    kernels.attention_prefill_tc(out_tc, qd, cd, btd, bs, i32([0] * ((T + 127) // 128)), i32(list(range(0, T, 128))),
+                                 (T + 127) // 128, cu, cl, scale, 0, nh, nkv, hd, flag)
+    assert flag.item() == 0
+    out_mma = torch.zeros_like(out_tc)
+    kernels.attention_prefill(out_mma, qd, cd, btd, bs, i32([0] * ((T + 63) // 64)), i32(list(range(0, T, 64))),
+                              (T + 63) // 64, cu, cl, scale, 0, nh, nkv, hd)
+    assert (out_tc[:T].float() - out_mma[:T].float()).abs().max().item() <= tol
+    for splits in (1, 7, 64):
+        out = out_tc.clone()
+        scratch = torch.zeros(max(1, kernels.attention_decode_scratch_floats(2, nh, splits, hd)), dtype=torch.float32, device=d)
+        kernels.attention_decode(out, qd, cd, btd, bs, i32([1]), 1, cu, cl, scale, 0, nh, nkv, hd, splits, scratch)
+        err = (out.float().cpu().double()[sub] - ref).abs()
+        assert err.max().item() <= tol, (splits, err.max().item(), rows[int(err.argmax()) // (nh * hd)])
+
+
 @pytest.mark.parametrize("M,N,K", [(64, 4096, 4096), (17, 200, 64), (128, 6144, 1024), (33, 1000, 328), (100, 28, 14336),
                                    (1, 130, 4096), (48, 128 * 150, 64)])
 def test_gemm_stream_tcgen05_against_its_plain_twin(M, N, K):
