@@ -209,8 +209,9 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(DecodeArgs a) {
   __syncthreads();
 
   // merge the four warps through shared memory (the stages are free now)
-  float* sm_o = reinterpret_cast<float*>(smem);                 // [4 warps][16 rows][HD]
-  float* sm_m = sm_o + 4 * 16 * HD;                             // [4][16]
+  constexpr int kOS = HD + 8;                                   // padded row: rows fall into different banks
+  float* sm_o = reinterpret_cast<float*>(smem);                 // [4 warps][16 rows][kOS]
+  float* sm_m = sm_o + 4 * 16 * kOS;                            // [4][16]
   float* sm_l = sm_m + 4 * 16;                                  // [4][16]
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
@@ -221,11 +222,12 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(DecodeArgs a) {
       sm_l[warp * 16 + g4 + h * 8] = st.l[h];
     }
   }
+  // only the rows of heads that exist are written (4 of the 16 for a group of 4)
 #pragma unroll
   for (int n = 0; n < HD / 8; ++n) {
-    float* row0 = sm_o + (warp * 16 + g4) * HD + n * 8 + t4 * 2;
-    row0[0] = o[n][0]; row0[1] = o[n][1];
-    row0[8 * HD] = o[n][2]; row0[8 * HD + 1] = o[n][3];
+    float* row0 = sm_o + (warp * 16 + g4) * kOS + n * 8 + t4 * 2;
+    if (g4 < n_heads) *reinterpret_cast<float2*>(row0) = make_float2(o[n][0], o[n][1]);
+    if (g4 + 8 < n_heads) *reinterpret_cast<float2*>(row0 + 8 * kOS) = make_float2(o[n][2], o[n][3]);
   }
   __syncthreads();
   for (int idx = threadIdx.x; idx < n_heads * HD; idx += kThreads) {
@@ -239,7 +241,7 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(DecodeArgs a) {
       const float mw = sm_m[w * 16 + row];
       const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
       L += sm_l[w * 16 + row] * f;
-      acc += sm_o[(w * 16 + row) * HD + d] * f;
+      acc += sm_o[(w * 16 + row) * kOS + d] * f;
     }
     const int head = head0 + row;
     if (a.n_splits == 1) {
@@ -334,7 +336,7 @@ LMSF_API int lmsf_attention_mma_head_dim() { return LMSF_HEAD_DIM; }
 static int decode_smem_bytes() {
   using namespace lmsf::fa;
   const int smem_stages = kStages * St::kBytes;
-  const int smem_merge = (4 * 16 * HD + 2 * 4 * 16) * (int)sizeof(float);
+  const int smem_merge = (4 * 16 * (HD + 8) + 2 * 4 * 16) * (int)sizeof(float);
   const int smem_weights = kMergeWeights * (int)sizeof(float);     // weights of the splits when they are added up
   const int m = smem_stages > smem_merge ? smem_stages : smem_merge;
   return m > smem_weights ? m : smem_weights;
