@@ -47,6 +47,7 @@ struct DecodeArgs {
   float scale; int window;
   int n_q_heads, group;                      // group = n_q_heads / n_kv_heads
   int n_splits;
+  int cluster;                               // the splits of a request and group of heads form a thread-block cluster
 };
 
 // Online-softmax state of the two rows (lane / 4 and lane / 4 + 8) that a thread holds.
@@ -55,6 +56,16 @@ struct RowState {
 };
 
 // ------------------------------------------------------------------------------------------------ decode
+constexpr int kMaxClusterSplits = 8;       // splits that add up through distributed shared memory
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// stores v at the same shared-memory offset as `local` in block `rank` of the cluster
+__device__ __forceinline__ void st_cluster_f32(const float* local, unsigned rank, float v) {
+  unsigned remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local)), "r"(rank));
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+}
 constexpr int kTableCache = 512;           // block-table entries of a split that are kept in shared memory
 constexpr int kMergeWeights = 4096;        // (heads of a block) x splits whose weights fit the shared memory used for adding up
 
@@ -207,12 +218,15 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(DecodeArgs a) {
   }
   cp_async_wait<0>();
   __syncthreads();
+  if (a.cluster) cluster_sync_all();        // the stages of every block of the cluster are free: split 0's will hold all parts
 
   // merge the four warps through shared memory (the stages are free now)
   constexpr int kOS = HD + 8;                                   // padded row: rows fall into different banks
   float* sm_o = reinterpret_cast<float*>(smem);                 // [4 warps][16 rows][kOS]
   float* sm_m = sm_o + 4 * 16 * kOS;                            // [4][16]
   float* sm_l = sm_m + 4 * 16;                                  // [4][16]
+  constexpr int kPS = 16 * HD + 16;                             // one split's part: 16 rows of HD values, 16 log-sum-exp
+  float* sm_part = sm_l + 4 * 16;                               // [splits][kPS], used in block 0 of a cluster
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     st.l[h] += __shfl_xor_sync(0xffffffffu, st.l[h], 1);
@@ -246,6 +260,9 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(DecodeArgs a) {
     const int head = head0 + row;
     if (a.n_splits == 1) {
       a.out[(size_t)token * a.out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(acc / L);
+    } else if (a.cluster) {
+      st_cluster_f32(sm_part + split * kPS + row * HD + d, 0, L > 0.f ? acc / L : 0.f);
+      if (d == 0) st_cluster_f32(sm_part + split * kPS + 16 * HD + row, 0, L > 0.f ? M + log2f(L) : -INFINITY);
     } else {
       const size_t pi = ((size_t)seq * a.n_q_heads + head) * a.n_splits + split;
       a.part_o[pi * HD + d] = L > 0.f ? acc / L : 0.f;
@@ -253,6 +270,25 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(DecodeArgs a) {
     }
   }
   if (a.n_splits == 1) return;
+  if (a.cluster) {
+    // all parts are in the shared memory of split 0, which adds them up in the order of the splits
+    cluster_sync_all();
+    if (split != 0) return;
+    for (int idx = threadIdx.x; idx < n_heads * HD; idx += kThreads) {
+      const int row = idx / HD, d = idx % HD;
+      float M = -INFINITY;
+      for (int s = 0; s < a.n_splits; ++s) M = fmaxf(M, sm_part[s * kPS + 16 * HD + row]);
+      float acc = 0.f, L = 0.f;
+      for (int s = 0; s < a.n_splits; ++s) {
+        const float lse = sm_part[s * kPS + 16 * HD + row];
+        const float f = lse == -INFINITY ? 0.f : exp2f(lse - M);
+        L += f;
+        acc += sm_part[s * kPS + row * HD + d] * f;
+      }
+      a.out[(size_t)token * a.out_stride + (size_t)(head0 + row) * HD + d] = __float2bfloat16_rn(acc / L);
+    }
+    return;
+  }
 
   // The split that delivers last adds the splits up, always in the order of the splits:
   // out = sum_s part_o[s] 2^(lse_s - max) / sum_s 2^(lse_s - max).
@@ -333,12 +369,24 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(DecodeArgs a) {
 
 LMSF_API int lmsf_attention_mma_head_dim() { return LMSF_HEAD_DIM; }
 
+// LMSF_DECODE_CLUSTER=0 in the environment sends every split count through global memory.
+static int cluster_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("LMSF_DECODE_CLUSTER");
+    v = (e && e[0] == '0') ? 0 : 1;
+  }
+  return v;
+}
+
 static int decode_smem_bytes() {
   using namespace lmsf::fa;
   const int smem_stages = kStages * St::kBytes;
   const int smem_merge = (4 * 16 * (HD + 8) + 2 * 4 * 16) * (int)sizeof(float);
   const int smem_weights = kMergeWeights * (int)sizeof(float);     // weights of the splits when they are added up
-  const int m = smem_stages > smem_merge ? smem_stages : smem_merge;
+  const int smem_cluster = smem_merge + kMaxClusterSplits * (16 * HD + 16) * (int)sizeof(float);   // + the parts of a cluster
+  int m = smem_stages > smem_merge ? smem_stages : smem_merge;
+  if (smem_cluster > m) m = smem_cluster;
   return m > smem_weights ? m : smem_weights;
 }
 
@@ -402,7 +450,23 @@ LMSF_API int lmsf_attention_decode(const void* q, long long q_stride, void* out,
     configured = true;
   }
   cudaStream_t s = (cudaStream_t)stream;
-  return launch_pdl(decode_kernel, dim3(n_splits, (unsigned)gy, n_served), dim3(kThreads), smem, s, a);
+  a.cluster = n_splits >= 2 && n_splits <= kMaxClusterSplits && cluster_enabled();
+  if (!a.cluster) return launch_pdl(decode_kernel, dim3(n_splits, (unsigned)gy, n_served), dim3(kThreads), smem, s, a);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(n_splits, (unsigned)gy, n_served);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled();
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.x = n_splits;
+  attr[1].val.clusterDim.y = 1;
+  attr[1].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  return (int)cudaLaunchKernelEx(&cfg, decode_kernel, a);
 }
 
 // ------------------------------------------------------------------------------------------------
