@@ -7,21 +7,22 @@
 //
 // One block serves 128 query tokens of TWO query heads that share a kv head (one head where the group has an
 // odd head left over), so that every k and v tile is fetched once for both.  Its warps have three roles:
-//   * two producer warps, one for k and one for v, bring tiles of 64 keys from their pages into rings of shared-memory stages
-//     with tensor-map copies (cp.async.bulk.tensor, one box per page and 64 head elements, 128-byte swizzled
-//     by the copy engine; k is read K-major, v MN-major); the copies' bytes are counted on mbarriers.  Pages
-//     of fewer than 8 keys are gathered with cp.async instead;
-//   * an issuing warp launches, for each head, S = Q K^T (M 128, N 64, K head size) into one of the head's two
-//     score buffers in tensor memory and, when the head's P is ready, O += P V (M 128, N head size, K 64);
-//     completion goes to mbarriers through tcgen05.commit.  The scores of tile j + 1 are computed while tile
-//     j's softmax runs, and a k stage is free again as soon as both heads' scores are done;
-//   * two groups of four softmax warps, one per head, one query row per thread: tcgen05.ld of the row's 64
-//     scores, mask, running maximum (the accumulator is rescaled only when the maximum grew by more than 2^8,
-//     which keeps the sums exact and saves most read-modify-writes of tensor memory), exponentials in
-//     float32, P as bfloat16 into the head's own tile of shared memory.
-// One block per SM: all 512 columns of tensor memory (2 x 2 score buffers of 64, 2 accumulators of 128) and
-// about 190 KB of shared memory.  Every wait on an mbarrier is bounded: when one runs out the block raises
-// *error_flag (code 3), frees its tensor memory and returns.
+//   * two producer warps, one for k and one for v, bring tiles of 128 keys from their pages into rings of
+//     shared-memory stages with tensor-map copies (cp.async.bulk.tensor, one box per page and 64 head
+//     elements, 128-byte swizzled by the copy engine; k is read K-major, v MN-major); the copies' bytes are
+//     counted on mbarriers.  Pages of fewer than 8 keys are gathered with cp.async instead;
+//   * an issuing warp launches, for each head, S = Q K^T (M 128, N 128, K head size) into the head's score
+//     buffer in tensor memory and, when the head's P is ready, O += P V (M 128, N head size, K 128) with P
+//     read from tensor memory; completion goes to mbarriers through tcgen05.commit.  The two heads take turns:
+//     one head's products run while the other head's softmax is computed;
+//   * two groups of four softmax warps, one per head, one query row per thread, with registers moved to them
+//     from the other warps (setmaxnreg): tcgen05.ld of the row's 128 scores, mask where the tile needs one,
+//     running maximum (the accumulator is rescaled only when the maximum grew by more than 2^8, which keeps the
+//     sums exact and saves most read-modify-writes of tensor memory), exponentials in float32, P as bfloat16
+//     pairs written over the first 64 columns of S (tcgen05.st).
+// One block per SM: all 512 columns of tensor memory (S or P of two heads, 128 each; O of two heads, 128 each)
+// and about 193 KB of shared memory (Q of two heads, two stages of k, two of v).  Every wait on an mbarrier is
+// bounded: when one runs out the block raises *error_flag (code 3), frees its tensor memory and returns.
 #include <type_traits>
 
 #include "attention_mma.cuh"
@@ -38,23 +39,6 @@ namespace tc {
 
 using namespace lmsf::fa;
 
-// -DLMSF_TC_TIMING (development aid): lane 0 of warp 0 (softmax), of the k producer and of the issuing warp adds the
-// clock cycles of its phases to a buffer given by lmsf_attention_tc_set_timing, 16 counters per block; the block
-// with the most keys also writes a timeline of its first 64 tiles behind the counters (offset 2^20).
-#ifdef LMSF_TC_TIMING
-__device__ long long* g_timing = nullptr;
-#define LMSF_T_BEGIN() long long tlast_ = clock64(); long long tacc_[16] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}
-#define LMSF_T(i) do { const long long now_ = clock64(); tacc_[i] += now_ - tlast_; tlast_ = now_; } while (0)
-#define LMSF_TRACE(role, j, k) do { if (g_timing && blockIdx.x == 0 && blockIdx.y == gridDim.y - 1 && (threadIdx.x & 31) == 0 && (j) < 64) g_timing[1 << 20 | ((role) * 64 + (j)) * 4 + (k)] = clock64(); } while (0)
-#define LMSF_T_END() do { if (g_timing && (threadIdx.x & 31) == 0 && ((threadIdx.x >> 5) == 0 || (threadIdx.x >> 5) == 8 || (threadIdx.x >> 5) == 10)) { \
-    long long* out_ = g_timing + ((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 16; \
-    for (int i_ = 0; i_ < 16; ++i_) if (tacc_[i_]) out_[i_] += tacc_[i_]; } } while (0)
-#else
-#define LMSF_TRACE(role, j, k) do {} while (0)
-#define LMSF_T_BEGIN() do {} while (0)
-#define LMSF_T(i) do {} while (0)
-#define LMSF_T_END() do {} while (0)
-#endif
 
 
 constexpr int HD = LMSF_HEAD_DIM;
@@ -221,7 +205,6 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
     auto full = [&](int s) { return is_v ? v_full(s) : k_full(s); };
     auto empty = [&](int s) { return is_v ? v_empty(s) : k_empty(s); };
     const uint32_t ring = is_v ? sV : sK;
-    LMSF_T_BEGIN();
     if (a.use_tma) {
       // Lane i copies box i of a tile: keys [i * rows_box, (i + 1) * rows_box), which lie in one page.  A key
       // range without a page (beyond the sequence, or before the window) is read from page 0 instead: all its
@@ -239,7 +222,6 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
         const int slot0 = ((tile_begin + t) * BN + lane * a.rows_box) & (a.kv.block_size - 1);
         const uint32_t dst = ring + s * kKBytes + lane * a.rows_box * 128;
         if (t >= kStages && !mbar_wait_f(empty(s), (uint32_t)((t / kStages - 1) & 1), failed)) break;
-        LMSF_T(6);
         const int next_page = fetch_page(t + 1);
         if (lane == 0) mbar_arrive_expect_tx(full(s), kKBytes);
         __syncwarp();
@@ -250,11 +232,9 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
         }
         issued = t + 1;
         page = next_page;
-        LMSF_T(7);
       }
       // no copy of this block may be in flight when it ends, whichever way the loop was left
       for (int t = max(0, issued - kStages); t < issued; ++t) mbar_wait_drain(full(t % kStages), (uint32_t)((t / kStages) & 1));
-      LMSF_T_END();
     } else {
       for (int t = 0; t < n_tiles; ++t) {
         const int s = t % kStages;
@@ -267,7 +247,6 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
   } else if (warp == 10) {
     // ------------------------------------------------------------------ tensor-core issue
     constexpr uint32_t idesc_s = instr_desc(BM, BN, 0), idesc_o = instr_desc(BM, HD, 1);
-    LMSF_T_BEGIN();
     const int nx = two ? 2 : 1;
     const bool leader = elect_one();
     // descriptors of the first 16 head elements (S) or keys (P V) of each operand; a later slice of 16 adds
@@ -305,32 +284,25 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
       for (int x = 0; x < nx && ok; ++x) {
         ok = mbar_wait_f(p_full(x), (uint32_t)(j & 1), failed);
         if (ok && x == 0) ok = mbar_wait_f(v_full(s), (uint32_t)((j / kStages) & 1), failed);
-        LMSF_T(4);
-        LMSF_TRACE(2, j, 2 * x);
         if (!ok) break;
         fence_async_smem();
         tc_fence_after();
         issue_pv(x, j);
         if (!more) umma_commit(leader, o_done(x));
-        LMSF_T(5);
         if (more) {
           if (x == 0) {
             ok = mbar_wait_f(k_full(s1), (uint32_t)(((j + 1) / kStages) & 1), failed);
-            LMSF_T(9);
             if (!ok) break;
             fence_async_smem();
             tc_fence_after();
           }
           issue_s(x, j + 1);
-          LMSF_TRACE(2, j, 2 * x + 1);
-          LMSF_T(3);
         }
       }
       if (!ok) break;
       umma_commit(leader, v_empty(s));
       if (more) umma_commit(leader, k_empty(s1));
     }
-    LMSF_T_END();
   }
   } else if (warp < 4 || two) {
     // ------------------------------------------------------------------ softmax of head x
@@ -344,18 +316,11 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
     float m_run = -INFINITY, l_run = 0.f;
     const float sl2 = a.scale * kLog2e;
     bool ok = true;
-    LMSF_T_BEGIN();
     for (int j = 0; j < n_tiles; ++j) {
       // S of tile j is complete, and with it every product issued before it: P V of tile j - 1 too
       ok = mbar_wait_f(s_full(x), (uint32_t)(j & 1), failed);
       if (!ok) break;
-#ifdef LMSF_TC_TIMING
-      __syncwarp();
-#endif
-      LMSF_T(0);
-      if ((warp & 3) == 0) LMSF_TRACE(x, j, 0);
       tc_fence_after();
-      LMSF_T(15);
       const int key0 = (tile_begin + j) * BN;
       // Only tiles that reach past some row's position (the diagonal) or before its window need the mask;
       // the test is the same for the whole block.
@@ -379,7 +344,6 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
         mx1 = fmax3(mx1, sc[i + 2], sc[i + 3]);
       }
       float mx = fmax3(mx0, mx1, fmaxf(sc[BN - 2], sc[BN - 1]));
-      LMSF_T(10);
       mx *= sl2;                                                // scores enter the exponent as s * scale * log2(e)
       float alpha = 1.f;
       const bool grow = mx > m_run + kRescaleThreshold;         // also true for the first keys a row sees
@@ -412,7 +376,6 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
         }
         fence_async_smem();
       }
-      LMSF_T(11);
       // P as bfloat16 pairs over the first 64 columns of S: keys 2c and 2c + 1 in column c
       const float neg_m = m_run == -INFINITY ? 0.f : -m_run;
       float l0 = 0.f, l1 = 0.f;
@@ -430,11 +393,8 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
       }
       tmem_wait_st();
       l_run += l0 + l1;
-      LMSF_T(12);
       tc_fence_before();
       mbar_arrive(p_full(x));
-      if ((warp & 3) == 0) LMSF_TRACE(x, j, 1);
-      LMSF_T(1);
     }
     if (ok && n_tiles > 0) ok = mbar_wait_f(o_done(x), 0u, failed);
     if (ok && n_tiles > 0) {
@@ -458,7 +418,6 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
         }
       }
     }
-    LMSF_T_END();
   } else {
     regs_dec<kRegsOther>();
   }
@@ -501,11 +460,6 @@ inline const CUtensorMap* cache_tensor_map(const void* cache, long long page_str
 
 LMSF_API int lmsf_attention_tc_head_dim() { return LMSF_HEAD_DIM; }
 
-#ifdef LMSF_TC_TIMING
-LMSF_API int lmsf_attention_tc_set_timing(long long* buf) {
-  return (int)cudaMemcpyToSymbol(lmsf::tc::g_timing, &buf, sizeof(buf));
-}
-#endif
 
 
 // tile_seq / tile_q0: one entry per 128 query tokens of each portion, best listed with the tiles that see the
