@@ -5,8 +5,9 @@
 // Counterpart in the reference: the dense float32 prompt attention of
 // core/src/model_executor/layers/attention.rs:106-159.
 //
-// One block serves 128 query tokens of TWO query heads that share a kv head (one head where the group has an
-// odd head left over), so that every k and v tile is fetched once for both.  Its warps have three roles:
+// One block serves two items that share their keys: 128 query tokens of TWO query heads of one kv head, or, for a
+// head that is left over (an odd group, or no grouping), two consecutive tiles of 128 query tokens of that head; so
+// every k and v tile is fetched once for both.  Its warps have three roles:
 //   * two producer warps, one for k and one for v, bring tiles of 128 keys from their pages into rings of
 //     shared-memory stages with tensor-map copies (cp.async.bulk.tensor, one box per page and 64 head
 //     elements, 128-byte swizzled by the copy engine; k is read K-major, v MN-major); the copies' bytes are
@@ -145,15 +146,32 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
   const int pairs = (a.group + 1) / 2;                          // blocks per kv head
   const int kvh = blockIdx.x / pairs, pair = blockIdx.x % pairs;
   const int head0 = kvh * a.group + 2 * pair;
-  const bool two = 2 * pair + 1 < a.group;                      // the block has a second head
+  const bool two_heads = 2 * pair + 1 < a.group;                // the block has a second head of the same kv head
   const int tok0 = a.cu_q[seq], n = a.cu_q[seq + 1] - tok0, ctx = a.ctx_len[seq];
   const int start = ctx - n;
-  const int rows_valid = min(BM, n - q0);
-  const int hi = start + q0 + rows_valid;                       // keys < hi are visible to the tile's last row
-  const int lo = a.window > 0 ? max(0, start + q0 - a.window + 1) : 0;
-  const int* table = a.block_table + (size_t)seq * a.max_blocks;
-  const int tile_begin = lo / BN, tile_end = (hi + BN - 1) / BN;
+  // A head that is left over (an odd group, or no grouping at all) takes two query tiles instead: this one and
+  // the 128 tokens behind it.  The block of that second tile has nothing left to do.
+  if (!two_heads && (q0 & (2 * BM - 1)) != 0) return;
+  const bool two = two_heads || q0 + BM < n;                    // the block has a second item
+  // item x: a head and 128 query tokens; it sees the keys [lo, hi) in the tiles [tb, te)
+  struct Item { int head, q0, rows, hi, lo, tb, te; };
+  Item it[2];
+#pragma unroll
+  for (int x = 0; x < 2; ++x) {
+    it[x].head = head0 + (two_heads ? x : 0);
+    it[x].q0 = q0 + (two_heads ? 0 : x * BM);
+    it[x].rows = max(0, min(BM, n - it[x].q0));
+    it[x].hi = start + it[x].q0 + it[x].rows;                   // keys < hi are visible to the item's last row
+    it[x].lo = a.window > 0 ? max(0, start + it[x].q0 - a.window + 1) : 0;
+    it[x].tb = it[x].lo / BN;
+    it[x].te = (it[x].hi + BN - 1) / BN;
+  }
+  // the block walks the tiles that either item sees; item x takes part in tile t when tb <= t < te
+  const int lo = it[0].lo, hi = two ? it[1].hi : it[0].hi;      // the second item is never behind the first
+  const int tile_begin = it[0].tb, tile_end = two ? it[1].te : it[0].te;
   const int n_tiles = tile_end - tile_begin;
+  auto active = [&](int x, int t) { return (x == 0 || two) && t >= it[x].tb && t < it[x].te; };
+  const int* table = a.block_table + (size_t)seq * a.max_blocks;
 
   if (tid == 0) {
     // a tile is full after one arrival that announces the copies' bytes (tensor-map copies), or after one
@@ -177,15 +195,15 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
   }
   if (warp < 8 && (warp < 4 || two)) {
-    // Q tile of this group's head: [64-wide block][row][128 bytes], rows beyond the portion are zero
+    // Q tile of this group's item: [64-wide block][row][128 bytes], rows beyond the portion are zero
     constexpr int kChunks = HD / 8;
     const int x = warp >> 2, t = tid & 127;
 #pragma unroll
-    for (int it = 0; it < BM * kChunks / kSoftmaxThreads; ++it) {
-      const int idx = t + it * kSoftmaxThreads;
+    for (int i = 0; i < BM * kChunks / kSoftmaxThreads; ++i) {
+      const int idx = t + i * kSoftmaxThreads;
       const int row = idx / kChunks, c = idx % kChunks;
-      const bool ok = row < rows_valid;
-      const bf16* src = ok ? a.q + (size_t)(tok0 + q0 + row) * a.q_stride + (size_t)(head0 + x) * HD + c * 8 : a.q;
+      const bool ok = row < it[x].rows;
+      const bf16* src = ok ? a.q + (size_t)(tok0 + it[x].q0 + row) * a.q_stride + (size_t)it[x].head * HD + c * 8 : a.q;
       cp_async_16(sQ + x * kQBytes + (c / 8) * (BM * 128) + row * 128 + (((c & 7) ^ (row & 7)) << 4), src, ok ? 16 : 0);
     }
     cp_async_commit();
@@ -252,7 +270,8 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
     // descriptors of the first 16 head elements (S) or keys (P V) of each operand; a later slice of 16 adds
     // its byte offset / 16 to the address field
     const uint64_t dq0 = smem_desc(sQ, 16, 1024), dk0 = smem_desc(sK, 16, 1024), dv0 = smem_desc(sV, BN * 128, 1024);
-    auto issue_s = [&](int x, int j) {                          // S of head x and tile j
+    // jx: how many tiles item x has had; j: tile counted from the block's first
+    auto issue_s = [&](int x, int j) {                          // S of item x and tile j
       const uint64_t dq = dq0 + (uint64_t)((x * kQBytes) >> 4), dk = dk0 + (uint64_t)(((j % kStages) * kKBytes) >> 4);
 #pragma unroll
       for (int ks = 0; ks < HD / 16; ++ks) {
@@ -261,41 +280,52 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
       }
       umma_commit(leader, s_full(x));
     };
-    auto issue_pv = [&](int x, int j) {                         // O of head x += P V of tile j, P from tensor memory
+    auto issue_pv = [&](int x, int j, int jx) {                 // O of item x += P V of tile j, P from tensor memory
       const uint64_t dv = dv0 + (uint64_t)(((j % kStages) * kKBytes) >> 4);
 #pragma unroll
       for (int ks = 0; ks < BN / 16; ++ks)
         umma_ts(leader, tmem + kOCol + x * 128, tmem + x * BN + ks * 8, dv + ((ks * 16 * 128) >> 4), idesc_o,
-                (j > 0 || ks > 0) ? 1u : 0u);
+                (jx > 0 || ks > 0) ? 1u : 0u);
     };
-    bool ok = n_tiles > 0 && mbar_wait_f(k_full(0), 0u, failed);
-    if (ok) {
+    // the k tile of tile j is waited for once, before the first S that reads it
+    int k_ready = -1;
+    auto k_wait = [&](int j) {
+      if (k_ready >= j) return true;
+      if (!mbar_wait_f(k_full(j % kStages), (uint32_t)((j / kStages) & 1), failed)) return false;
       fence_async_smem();
       tc_fence_after();
-      for (int x = 0; x < nx; ++x) issue_s(x, 0);
+      k_ready = j;
+      return true;
+    };
+    bool ok = n_tiles > 0 && k_wait(0);
+    if (ok) {
+      for (int x = 0; x < nx; ++x)
+        if (active(x, tile_begin)) issue_s(x, 0);
       umma_commit(leader, k_empty(0));
     }
-    // The two heads take turns: while one head's softmax runs, the tensor core works on the other head's
-    // P V and on its next scores.  S of tile j + 1 may overwrite P of tile j because the products of one
+    // The two items take turns: while one item's softmax runs, the tensor core works on the other item's
+    // P V and on its next scores.  S of the next tile may overwrite P of this one because the products of one
     // thread are executed in the order of their issue.
+    int jx[2] = {0, 0};
     for (int j = 0; j < n_tiles && ok; ++j) {
-      const int s = j % kStages, s1 = (j + 1) % kStages;
+      const int s = j % kStages, s1 = (j + 1) % kStages, t = tile_begin + j;
       const bool more = j + 1 < n_tiles;
+      bool v_ready = false;
       for (int x = 0; x < nx && ok; ++x) {
-        ok = mbar_wait_f(p_full(x), (uint32_t)(j & 1), failed);
-        if (ok && x == 0) ok = mbar_wait_f(v_full(s), (uint32_t)((j / kStages) & 1), failed);
-        if (!ok) break;
-        fence_async_smem();
-        tc_fence_after();
-        issue_pv(x, j);
-        if (!more) umma_commit(leader, o_done(x));
-        if (more) {
-          if (x == 0) {
-            ok = mbar_wait_f(k_full(s1), (uint32_t)(((j + 1) / kStages) & 1), failed);
-            if (!ok) break;
-            fence_async_smem();
-            tc_fence_after();
-          }
+        if (active(x, t)) {
+          ok = mbar_wait_f(p_full(x), (uint32_t)(jx[x] & 1), failed);
+          if (ok && !v_ready) ok = mbar_wait_f(v_full(s), (uint32_t)((j / kStages) & 1), failed);
+          if (!ok) break;
+          v_ready = true;
+          fence_async_smem();
+          tc_fence_after();
+          issue_pv(x, j, jx[x]);
+          ++jx[x];
+          if (!active(x, t + 1)) umma_commit(leader, o_done(x));     // the item's last tile
+        }
+        if (more && active(x, t + 1)) {
+          ok = k_wait(j + 1);
+          if (!ok) break;
           issue_s(x, j + 1);
         }
       }
@@ -308,23 +338,26 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
     // ------------------------------------------------------------------ softmax of head x
     regs_inc<kRegsSoftmax>();
     const int x = warp >> 2, row = tid & 127;
-    const bool row_ok = row < rows_valid;
-    const int pos = start + q0 + min(row, rows_valid - 1);         // this thread's query position
+    const Item me = it[x];
+    const bool row_ok = row < me.rows;
+    const int pos = start + me.q0 + min(row, me.rows - 1);         // this thread's query position
     const int row_lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
     const uint32_t t_row = tmem + ((uint32_t)((warp & 3) * 32) << 16);   // this warp's 32 lanes of tensor memory
     const uint32_t t_s = t_row + x * BN, t_o = t_row + kOCol + x * 128;
     float m_run = -INFINITY, l_run = 0.f;
     const float sl2 = a.scale * kLog2e;
+    const int my_tiles = me.te - me.tb;
     bool ok = true;
-    for (int j = 0; j < n_tiles; ++j) {
-      // S of tile j is complete, and with it every product issued before it: P V of tile j - 1 too
+    for (int j = 0; j < my_tiles; ++j) {                           // j counts this item's tiles
+      // S of the tile is complete, and with it every product issued before it: P V of the tile before too
       ok = mbar_wait_f(s_full(x), (uint32_t)(j & 1), failed);
       if (!ok) break;
       tc_fence_after();
-      const int key0 = (tile_begin + j) * BN;
+      const int key0 = (me.tb + j) * BN;
+      const int ju = me.tb + j - tile_begin;                       // the tile counted from the block's first: its stage
       // Only tiles that reach past some row's position (the diagonal) or before its window need the mask;
-      // the test is the same for the whole block.
-      const bool need_mask = key0 + BN - 1 > start + q0 || (a.window > 0 && key0 < start + q0 + rows_valid - a.window);
+      // the test is the same for the whole group of warps.
+      const bool need_mask = key0 + BN - 1 > start + me.q0 || (a.window > 0 && key0 < start + me.q0 + me.rows - a.window);
       // the row's 128 scores: four loads in flight, one wait
       float sc[BN];
 #pragma unroll
@@ -364,10 +397,10 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
       }
       if (key0 < lo || key0 + BN > hi) {
         // rows of v whose keys no query of the tile sees hold whatever their page holds: clear them, so that
-        // their zero weights cannot meet a value that is not finite (both heads' warps do, with the same zeros)
-        const uint32_t v = sV + (j % kStages) * kKBytes;
+        // their zero weights cannot meet a value that is not finite (both items' warps do, with the same zeros)
+        const uint32_t v = sV + (ju % kStages) * kKBytes;
         const int r_lo = lo - key0, r_hi = hi - key0;
-        ok = mbar_wait_f(v_full(j % kStages), (uint32_t)((j / kStages) & 1), failed);   // the tile's v has landed
+        ok = mbar_wait_f(v_full(ju % kStages), (uint32_t)((ju / kStages) & 1), failed);   // the tile's v has landed
         if (!ok) break;
         for (int idx = row; idx < kHB * BN * 8; idx += kSoftmaxThreads) {
           const int r = (idx >> 3) % BN;
@@ -396,11 +429,11 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
       tc_fence_before();
       mbar_arrive(p_full(x));
     }
-    if (ok && n_tiles > 0) ok = mbar_wait_f(o_done(x), 0u, failed);
-    if (ok && n_tiles > 0) {
+    if (ok && my_tiles > 0) ok = mbar_wait_f(o_done(x), 0u, failed);
+    if (ok && my_tiles > 0) {
       tc_fence_after();
       const float inv = 1.0f / l_run;
-      bf16* dst = a.out + (size_t)(tok0 + q0 + row) * a.out_stride + (size_t)(head0 + x) * HD;
+      bf16* dst = a.out + (size_t)(tok0 + me.q0 + row) * a.out_stride + (size_t)me.head * HD;
 #pragma unroll
       for (int c0 = 0; c0 < HD; c0 += 32) {
         uint32_t r[32];
