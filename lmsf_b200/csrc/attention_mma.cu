@@ -80,6 +80,12 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(DecodeArgs a) {
   const int chunks_per_kvh = (a.group + 15) / 16;
   const int kvh = blockIdx.y / chunks_per_kvh, hchunk = blockIdx.y % chunks_per_kvh;
   const int seq = a.seq_ids ? a.seq_ids[blockIdx.z] : blockIdx.z;
+  const int* table = a.block_table + (size_t)seq * a.max_blocks;
+  // The head of the request's block table goes to shared memory at once, beside the loads of its lengths: for
+  // contexts of up to kTableCache pages no copy of the loop waits for a table entry from global memory, and
+  // the entries do not have to wait for the lengths either.
+  const int n_head = min(a.max_blocks, kTableCache);
+  for (int i = threadIdx.x; i < n_head; i += kThreads) s_table[i] = table[i];
   const int token = a.cu_q[seq];
   const int ctx = a.ctx_len[seq];
   const int lo = a.window > 0 ? max(0, ctx - a.window) : 0;
@@ -87,7 +93,6 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(DecodeArgs a) {
   const int g4 = lane >> 2, t4 = lane & 3;
   const int head0 = kvh * a.group + hchunk * 16;               // first query head of this block
   const int n_heads = min(16, a.group - hchunk * 16);          // valid rows
-  const int* table = a.block_table + (size_t)seq * a.max_blocks;
 
   // tiles of 64 keys aligned to absolute positions; this split's share of them
   const int tile_lo = lo / kTileKeys, tile_hi = (ctx + kTileKeys - 1) / kTileKeys;
@@ -96,13 +101,16 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(DecodeArgs a) {
   const int tile_end = min(tile_hi, tile_begin + per_split);
   const int n_tiles = max(0, tile_end - tile_begin);
 
-  // the split's slice of the block table goes to shared memory, so that no copy of the loop waits for a
-  // table entry from global memory
+  // a split beyond the cached head of the table copies its own slice (or, if that is too long, reads the table
+  // in global memory)
   int table_off = 0;
-  if (n_tiles > 0) {
+  {
     const int blk0 = (tile_begin * kTileKeys) >> a.kv.block_shift;
-    const int blk1 = min(a.max_blocks, ((min(ctx, tile_end * kTileKeys) - 1) >> a.kv.block_shift) + 1);
-    if (blk1 - blk0 <= kTableCache) {
+    const int blk1 = n_tiles > 0 ? min(a.max_blocks, ((min(ctx, tile_end * kTileKeys) - 1) >> a.kv.block_shift) + 1) : 0;
+    __syncthreads();
+    if (blk1 <= n_head) {
+      table = s_table;
+    } else if (blk1 - blk0 <= kTableCache) {
       for (int i = threadIdx.x; i < blk1 - blk0; i += kThreads) s_table[i] = table[blk0 + i];
       __syncthreads();
       table = s_table;
