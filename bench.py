@@ -40,7 +40,8 @@ CONTEXT = 2048          # tokens each request holds while decoding is timed
 MAX_MODEL_LEN = 4096
 BLOCK_SIZE = 16
 PREFILL_TOKENS = 2048
-E2E_WARMUP = 16         # untimed steps of the end-to-end run: the first steps after the prompts run slower
+E2E_WARMUP = 16         # untimed steps of the end-to-end run at least: the first steps after the prompts run slower
+E2E_WARMUP_SECONDS = 0.3
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -185,13 +186,19 @@ def time_e2e(folder, n_layers, batch, context, steps, warmup, vocab):
                                   max_num_batched_tokens=8192, max_num_seqs=max(batch, 8),
                                   gpu_memory_utilization=0.85), load_format="dummy")
     g = torch.Generator().manual_seed(2)
-    sp = SamplingParams(temperature=0.0, max_tokens=steps + max(warmup, E2E_WARMUP) + 8, ignore_eos=True)
+    # Untimed steps: at least max(warmup, E2E_WARMUP), and on until E2E_WARMUP_SECONDS have passed (the clocks need
+    # that long to settle after the prompts), as far as the context length leaves room.
+    room = max(MAX_MODEL_LEN, context + 64) - context - steps - 8
+    warm_min, warm_max = max(warmup, E2E_WARMUP), max(max(warmup, E2E_WARMUP), min(room, 512))
+    sp = SamplingParams(temperature=0.0, max_tokens=steps + warm_max + 8, ignore_eos=True)
     for i in range(batch):
         engine.add_request(i, None, sp, prompt_token_ids=torch.randint(0, vocab, (context - 1,), generator=g).tolist())
     while any(s.num_computed < len(s.prompt_token_ids) for s in engine.seqs.values()) or len(engine.seqs) < batch:
         engine.step()
-    for _ in range(max(warmup, E2E_WARMUP)):      # the first steps after the prompts run slower (clocks settle)
+    t_warm, n_warm = time.perf_counter(), 0
+    while n_warm < warm_min or (n_warm < warm_max and time.perf_counter() - t_warm < E2E_WARMUP_SECONDS):
         engine.step()
+        n_warm += 1
     torch.cuda.synchronize()
     h2d0 = engine.runner.h2d_bytes
     t0 = time.perf_counter()
@@ -338,7 +345,7 @@ def main() -> int:
                    "num_key_value_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
                    "intermediate_size": cfg["intermediate_size"], "vocab_size": V, "global_batch": a.batch,
                    "seq_len": ctx_len, "max_model_len": MAX_MODEL_LEN, "block_size": BLOCK_SIZE,
-                   "prefill_tokens": PREFILL_TOKENS, "e2e_warmup": max(a.warmup, E2E_WARMUP), "parallelism": "1 GPU",
+                   "prefill_tokens": PREFILL_TOKENS, "e2e_warmup": f">= {max(a.warmup, E2E_WARMUP)} steps, up to {E2E_WARMUP_SECONDS} s", "parallelism": "1 GPU",
                    "l2": "inputs larger than L2 (weights + cache of a step >> 126 MB); prefill flushes L2",
                    "peaks": pk["source"]},
         "prefill": prefill,
