@@ -40,24 +40,22 @@ namespace tc {
 
 using namespace lmsf::fa;
 
-
-
 constexpr int HD = LMSF_HEAD_DIM;
 static_assert(HD == 64 || HD == 128, "the tcgen05 attention kernel takes head sizes 64 and 128");
-constexpr int BM = 128;                    // query rows per head and block
+constexpr int BM = 128;                    // query rows per item (a head and 128 tokens)
 constexpr int BN = 128;                    // keys per tile
 constexpr int kHB = HD / 64;               // 64-wide blocks of the head dimension
 #ifndef LMSF_TC_STAGES
 #define LMSF_TC_STAGES 2
 #endif
 constexpr int kStages = LMSF_TC_STAGES;    // k tiles in flight, and v tiles
-constexpr int kQBytes = kHB * BM * 128;    // one head's queries
+constexpr int kQBytes = kHB * BM * 128;    // one item's queries
 constexpr int kKBytes = kHB * BN * 128;    // one k (or v) tile
 constexpr int kOffK = 2 * kQBytes, kOffV = kOffK + kStages * kKBytes;
 constexpr int kSmemBytes = kOffV + kStages * kKBytes + 1024;   // + slack for the 1024-byte alignment
 static_assert(kSmemBytes <= 227 * 1024, "too many stages for the shared memory of an SM");
-// Tensor memory, 512 columns: S of head x in [128x, 128x + 128), and P (bfloat16 pairs) over its first 64
-// columns once the scores are in registers; O of head x in [256 + 128x, +HD).
+// Tensor memory, 512 columns: S of item x in [128x, 128x + 128), and P (bfloat16 pairs) over its first 64
+// columns once the scores are in registers; O of item x in [256 + 128x, +HD).
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kOCol = 256;
 constexpr float kLog2e = 1.4426950408889634f;
@@ -74,7 +72,7 @@ struct Args {
   int n_q_heads, group;
   int* error_flag;
   int use_tma;      // k and v tiles come by tensor-map copies (block_size >= 8), else by cp.async
-  int rows_box;     // keys per tensor-map copy: min(block_size, 64)
+  int rows_box;     // keys per tensor-map copy: min(block_size, 128)
 };
 
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
@@ -90,17 +88,17 @@ __device__ __forceinline__ float ex2_approx(float x) {      // 2^x, 0 for -inf
   return y;
 }
 // ---- roles ---------------------------------------------------------------------------------------------
-// warps 0-3: softmax of the first head, one query row per thread (thread t owns lane t % 128 of tensor memory)
-// warps 4-7: softmax of the second head
+// warps 0-3: softmax of the first item, one query row per thread (thread t owns lane t % 128 of tensor memory)
+// warps 4-7: softmax of the second item
 // warp 8   : producer of k tiles
 // warp 9   : producer of v tiles
 // warp 10  : issues the tensor-core products
 // warp 11  : idle
-constexpr int kSoftmaxThreads = 128;       // per head
+constexpr int kSoftmaxThreads = 128;       // per item
 constexpr int kThreadsTotal = 384;     // three warpgroups; warp 11 only gives its registers away
 
 // Where pages are too small for tensor-map copies: the producer warp's cp.async gather of k (or v) of keys
-// [key0, key0 + 64) of kv head kvh into a tile: [64-wide block of the head][key][128 bytes], 16-byte chunk c of
+// [key0, key0 + 128) of kv head kvh into a tile: [64-wide block of the head][key][128 bytes], 16-byte chunk c of
 // a row at chunk c ^ (key & 7).  Keys outside [lo, hi) or without a page are zero-filled.
 __device__ __forceinline__ void gather_tile(uint32_t dst_tile, const PagedKV& kv, const int* __restrict__ table, int max_blocks,
                                             int kvh, bool is_v, int key0, int lo, int hi, int lane) {
@@ -122,7 +120,7 @@ __device__ __forceinline__ void gather_tile(uint32_t dst_tile, const PagedKV& kv
 
 __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args a, const __grid_constant__ CUtensorMap kv_map) {
   extern __shared__ unsigned char smem_raw[];
-  // k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages], s_full[head], p_full[head], o_done[head]
+  // k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages], s_full[item], p_full[item], o_done[item]
   __shared__ __align__(8) uint64_t bars[4 * kStages + 6];
   __shared__ uint32_t tmem_base_mem;
   __shared__ int failed_mem;
