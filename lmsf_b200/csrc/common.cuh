@@ -75,6 +75,11 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   return scratch[32];
 }
 
+// One rotated pair (x, y) -> (x c - y s, y c + x s), every product and sum rounded on its own (no fused
+// multiply-add), so that every kernel that rotates gives the same bits.
+__device__ __forceinline__ float rot_first(float x, float y, float c, float s) { return __fsub_rn(__fmul_rn(x, c), __fmul_rn(y, s)); }
+__device__ __forceinline__ float rot_second(float x, float y, float c, float s) { return __fadd_rn(__fmul_rn(y, c), __fmul_rn(x, s)); }
+
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
 // ---- programmatic dependent launch -------------------------------------------------------------------

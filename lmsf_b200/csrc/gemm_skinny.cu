@@ -3,6 +3,10 @@
 // Optionally fused with the gated activation of the feed-forward: W = [gate; up] stacked along N and
 // out[m, n] = act(x . gate_n) * (x . up_n).
 //
+// A third form serves the merged q, k, v projection of single tokens: the rows of q and k are rotated in the
+// epilogue (rotary position encoding), q goes to its buffer and k and v straight into their cache pages, so that
+// no kernel has to run between the projection and the attention.
+//
 // Counterpart in the reference: cublasLtMatmul for every M (tops/csrc/tops/tensorrt_llm/common/
 // cublasMMWrapper.cpp:122-209) followed by silu_and_mul_kernel (vllm/kernels/activation_kernels.cu:26-41).
 //
@@ -39,6 +43,13 @@ struct Args {
   int up_offset;      // FUSE: row of W where the "up" half starts (= N of the output)
   int act;            // FUSE: 0 silu, 1 gelu_tanh
   int out_f32;
+  // the fused q/k/v form (ROPE): out is q [M, n_q_heads * head_dim]
+  const int* positions; const int* token_seq;   // [M]
+  const int* block_table; int max_blocks, block_size;
+  bf16* cache; long long page_stride;           // one layer's pages [page][2][kv_head][slot][head_dim]
+  const float* inv_freq; int rot_dim, is_neox;
+  int n_q_heads, n_kv_heads, head_dim;
+  int* error_flag;
 };
 
 __device__ __forceinline__ float act_apply(float g, int act) {
@@ -50,9 +61,11 @@ __device__ __forceinline__ float act_apply(float g, int act) {
 // Copies `n_rows_stage` rows x k [k0, k0 + kChunkK) into a stage: row r of the stage comes from `base + r * ld`
 // when `r < n_valid`, else it is zero-filled.  One warp instruction copies whole rows or half rows, so that
 // memory sees contiguous requests of kRowBytes.  16-byte chunk c of row r lands at chunk c ^ (r & 7).
+// `hi_off`: rows 8.. of the stage come from `hi_off` rows further down (the fused q/k/v form pairs a head's
+// features i and i + rot/2 in one block).
 template <int N_ROWS>
 __device__ __forceinline__ void issue_rows(uint32_t stage, const bf16* __restrict__ base, long long ld, int n_valid,
-                                           int k0, int K, int lane) {
+                                           int k0, int K, int lane, int hi_off = 0) {
   constexpr int kLanesPerRow = kCPR < 32 ? kCPR : 32;
   constexpr int kRowsPerInstr = 32 / kLanesPerRow;
   constexpr int kChunkPasses = kCPR / kLanesPerRow;
@@ -64,7 +77,7 @@ __device__ __forceinline__ void issue_rows(uint32_t stage, const bf16* __restric
     for (int j = 0; j < kChunkPasses; ++j) {
       const int c = lane % kLanesPerRow + j * kLanesPerRow;
       const bool okc = ok && k0 + c * 8 < K;          // K is a multiple of 8: a chunk is inside or outside
-      const bf16* src = okc ? base + (size_t)r * ld + k0 + c * 8 : base;
+      const bf16* src = okc ? base + (size_t)(r + (r >= 8 ? hi_off : 0)) * ld + k0 + c * 8 : base;
 #ifdef LMSF_SKINNY_L2_HINT
       cp_async_16_l2_256(stage + r * kRowBytes + ((c ^ (r & 7)) << 4), src, okc ? 16 : 0);
 #else
@@ -74,7 +87,7 @@ __device__ __forceinline__ void issue_rows(uint32_t stage, const bf16* __restric
   }
 }
 
-template <int NT, int GROUPS, int STAGES>
+template <int NT, int GROUPS, int STAGES, bool ROPE = false>
 __global__ void __launch_bounds__(kWarps * 32) skinny_kernel(Args a) {
   constexpr int kStage = GROUPS * kStageBytes + NT * 8 * kRowBytes;      // W group(s), then x
   extern __shared__ __align__(128) unsigned char smem[];
@@ -93,11 +106,24 @@ __global__ void __launch_bounds__(kWarps * 32) skinny_kernel(Args a) {
 #endif
   const uint32_t ring = smem_u32(smem) + warp * (STAGES * kStage);
   const int rows_total = GROUPS == 2 ? a.up_offset : a.N;       // rows of one group
+  // ROPE: rows 0..7 of the block are features f0.., rows 8..15 features f1..: a rotated pair sits 8 rows apart
+  int f0 = n0, f1 = n0 + 8;
+  bool pair8 = false;                                            // the block holds NeoX pairs (i, i + rot/2)
+  if (ROPE && a.inv_freq && a.is_neox) {
+    const int head = n0 / a.head_dim, j = (n0 % a.head_dim) / 16;
+    if (head < a.n_q_heads + a.n_kv_heads && j * 16 < a.rot_dim) {
+      f0 = head * a.head_dim + 8 * j;
+      f1 = f0 + a.rot_dim / 2;
+      pair8 = true;
+    }
+  }
+  const int hi_off = f1 - f0 - 8;
 
   auto issue_w = [&](int c) {
     const uint32_t st = ring + (c % STAGES) * kStage;
     const int k0 = (c_begin + c * c_stride) * kChunkK;
-    issue_rows<16>(st, a.w + (size_t)n0 * a.ldw, a.ldw, rows_total - n0, k0, a.K, lane);
+    if (ROPE) issue_rows<16>(st, a.w + (size_t)f0 * a.ldw, a.ldw, 16, k0, a.K, lane, hi_off);
+    else issue_rows<16>(st, a.w + (size_t)n0 * a.ldw, a.ldw, rows_total - n0, k0, a.K, lane);
     if (GROUPS == 2)
       issue_rows<16>(st + kStageBytes, a.w + (size_t)(a.up_offset + n0) * a.ldw, a.ldw, rows_total - n0, k0, a.K, lane);
   };
@@ -115,6 +141,21 @@ __global__ void __launch_bounds__(kWarps * 32) skinny_kernel(Args a) {
   for (int s = 0; s < STAGES - 1; ++s) {
     if (s < n_chunks) issue_x(s);
     cp_async_commit();
+  }
+
+  // ROPE: where this thread's results go (one token per pass of the epilogue), asked for before the loop
+  int e_pos[NT], e_page[NT];
+  if (ROPE) {
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+      const int m = (threadIdx.x + t * kWarps * 32) / 16;
+      e_pos[t] = m < a.M ? a.positions[m] : 0;
+      e_page[t] = -1;
+      if (m < a.M && f0 >= a.n_q_heads * a.head_dim) {            // a block of k or v features
+        const int blk = e_pos[t] / a.block_size;
+        e_page[t] = blk < a.max_blocks ? a.block_table[(size_t)a.token_seq[m] * a.max_blocks + blk] : -1;
+      }
+    }
   }
 
   float acc[GROUPS][NT][4];
@@ -178,6 +219,43 @@ __global__ void __launch_bounds__(kWarps * 32) skinny_kernel(Args a) {
       base[(g4 + 8) * (8 * NT) + t * 8 + t4 * 2 + 1] = acc[g][t][3];
     }
   __syncthreads();
+  if constexpr (ROPE) {
+    // one (token, feature) per thread and pass; the partner of a rotated pair is 8 lanes away (NeoX) or the neighbour
+    const int q_size = a.n_q_heads * a.head_dim, kv_size = a.n_kv_heads * a.head_dim;
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+      const int idx = threadIdx.x + t * kWarps * 32;
+      const int m = idx / 16, row = idx % 16;
+      float sum = 0.f;
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w)
+        sum += reinterpret_cast<const float*>(smem + w * (STAGES * kStage))[row * (8 * NT) + m];
+      const float val = __bfloat162float(__float2bfloat16_rn(sum));      // what the plain product would have stored
+      const float other = __shfl_xor_sync(0xffffffffu, val, pair8 ? 8 : 1);
+      if (m >= a.M) continue;
+      const int n = row < 8 ? f0 + row : f1 + row - 8;                  // feature among q, k, v
+      const int d = n % a.head_dim;
+      const bool is_v = n >= q_size + kv_size;
+      float r = val;
+      if (a.inv_freq && !is_v && d < a.rot_dim) {
+        const bool first = a.is_neox ? d < a.rot_dim / 2 : (d & 1) == 0;
+        const int i = a.is_neox ? d % (a.rot_dim / 2) : d / 2;
+        float sn, cs;
+        sincosf((float)e_pos[t] * a.inv_freq[i], &sn, &cs);
+        const float x = first ? val : other, y = first ? other : val;
+        r = first ? rot_first(x, y, cs, sn) : rot_second(x, y, cs, sn);
+      }
+      if (n < q_size) {
+        reinterpret_cast<bf16*>(a.out)[(size_t)m * a.ldo + n] = __float2bfloat16_rn(r);
+      } else if (e_page[t] < 0) {
+        if (a.error_flag) atomicExch(a.error_flag, 2);                   // the token has no page
+      } else {
+        const int g = (n - q_size - (is_v ? kv_size : 0)) / a.head_dim;
+        bf16* page = a.cache + (size_t)e_page[t] * a.page_stride + (is_v ? (size_t)a.n_kv_heads * a.block_size * a.head_dim : 0);
+        page[((size_t)g * a.block_size + e_pos[t] % a.block_size) * a.head_dim + d] = __float2bfloat16_rn(r);
+      }
+    }
+  } else {
   for (int idx = threadIdx.x; idx < 16 * 8 * NT; idx += kWarps * 32) {
     const int m = idx / 16, row = idx % 16;          // consecutive threads write consecutive n
     if (m >= a.M || n0 + row >= rows_total) continue;
@@ -194,18 +272,19 @@ __global__ void __launch_bounds__(kWarps * 32) skinny_kernel(Args a) {
     if (a.out_f32) reinterpret_cast<float*>(a.out)[(size_t)m * a.ldo + n0 + row] = r;
     else reinterpret_cast<bf16*>(a.out)[(size_t)m * a.ldo + n0 + row] = __float2bfloat16_rn(r);
   }
+  }
 }
 
-template <int NT, int GROUPS, int STAGES>
+template <int NT, int GROUPS, int STAGES, bool ROPE = false>
 static int launch(const Args& a, int rows, cudaStream_t s) {
   const int smem = kWarps * STAGES * (GROUPS * kStageBytes + NT * 8 * kRowBytes);
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(skinny_kernel<NT, GROUPS, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(skinny_kernel<NT, GROUPS, STAGES, ROPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  return launch_pdl(skinny_kernel<NT, GROUPS, STAGES>, dim3(ceil_div(rows, 16)), dim3(kWarps * 32), smem, s, a);
+  return launch_pdl(skinny_kernel<NT, GROUPS, STAGES, ROPE>, dim3(ceil_div(rows, 16)), dim3(kWarps * 32), smem, s, a);
 }
 
 #ifndef LMSF_SKINNY_STAGES
@@ -234,7 +313,9 @@ LMSF_API int lmsf_gemm_skinny(void* out, const void* x, const void* w, int M, in
   if (fuse_act >= 0 && N % 2) LMSF_REFUSE("gemm_skinny: a gated product needs an even N, got %d", N);
   if (ldx < K || ldw < K || ldx % 8 || ldw % 8 || ((uintptr_t)x % 16) || ((uintptr_t)w % 16))
     LMSF_REFUSE("gemm_skinny: the rows of x and w must be 16-byte aligned");
-  Args a{(const bf16*)x, ldx, (const bf16*)w, ldw, out, ldo, M, N, K, fuse_act >= 0 ? N / 2 : 0, fuse_act, out_f32};
+  Args a{};
+  a.x = (const bf16*)x; a.ldx = ldx; a.w = (const bf16*)w; a.ldw = ldw; a.out = out; a.ldo = ldo; a.M = M; a.N = N; a.K = K;
+  a.up_offset = fuse_act >= 0 ? N / 2 : 0; a.act = fuse_act; a.out_f32 = out_f32;
   cudaStream_t s = (cudaStream_t)stream;
   if (fuse_act >= 0) {
     if (ldo < N / 2) LMSF_REFUSE("gemm_skinny: ldo is smaller than the output row");
@@ -242,4 +323,38 @@ LMSF_API int lmsf_gemm_skinny(void* out, const void* x, const void* w, int M, in
   }
   if (ldo < N) LMSF_REFUSE("gemm_skinny: ldo is smaller than the output row");
   return M <= 8 ? launch<1, 1, kStagesPlain>(a, N, s) : launch<2, 1, kStagesPlain>(a, N, s);
+}
+
+// The merged q, k, v projection of M <= 16 single tokens with the rotary encoding and the cache write in its
+// epilogue.  w: [(n_q_heads + 2 n_kv_heads) * head_dim, K]; q_out: [M, n_q_heads * head_dim] bfloat16, rotated;
+// k (rotated) and v go to the pages of `cache` ([page][2][kv_head][slot][head_dim]) that block_table names for
+// positions[m] of request token_seq[m].  inv_freq: [rot_dim / 2] float32 or null (no rotation).  Results are those
+// of lmsf_gemm_skinny (bfloat16 out) followed by the rotary / cache-write kernel, bit for bit.
+LMSF_API int lmsf_gemm_skinny_qkv_rope(void* q_out, long long ldq, const void* x, long long ldx, const void* w, long long ldw,
+                                       int M, int K, const int* positions, const int* token_seq, const int* block_table,
+                                       int max_blocks, int block_size, void* cache, long long page_stride,
+                                       const float* inv_freq, int rot_dim, int is_neox, int n_q_heads, int n_kv_heads,
+                                       int head_dim, int* error_flag, void* stream) {
+  using namespace lmsf;
+  using namespace lmsf::skinny;
+  if (M <= 0) return 0;
+  if (M > 16) LMSF_REFUSE("gemm_skinny_qkv_rope: M=%d, this kernel takes at most 16 rows", M);
+  if (K <= 0 || K % 8) LMSF_REFUSE("gemm_skinny_qkv_rope: K=%d must be a positive multiple of 8", K);
+  if (ldx < K || ldw < K || ldx % 8 || ldw % 8 || ((uintptr_t)x % 16) || ((uintptr_t)w % 16))
+    LMSF_REFUSE("gemm_skinny_qkv_rope: the rows of x and w must be 16-byte aligned");
+  if (head_dim <= 0 || head_dim % 16 || n_q_heads <= 0 || n_kv_heads <= 0)
+    LMSF_REFUSE("gemm_skinny_qkv_rope: head_dim=%d must be a multiple of 16", head_dim);
+  if (inv_freq && (rot_dim <= 0 || rot_dim > head_dim || rot_dim % (is_neox ? 16 : 2)))
+    LMSF_REFUSE("gemm_skinny_qkv_rope: rot_dim=%d is not taken (NeoX pairs need a multiple of 16)", rot_dim);
+  if (ldq < (long long)n_q_heads * head_dim || block_size <= 0 || max_blocks <= 0 || !cache)
+    LMSF_REFUSE("gemm_skinny_qkv_rope: bad q or cache geometry");
+  Args a{};
+  a.x = (const bf16*)x; a.ldx = ldx; a.w = (const bf16*)w; a.ldw = ldw; a.out = q_out; a.ldo = ldq;
+  a.M = M; a.N = (n_q_heads + 2 * n_kv_heads) * head_dim; a.K = K; a.act = -1;
+  a.positions = positions; a.token_seq = token_seq; a.block_table = block_table; a.max_blocks = max_blocks;
+  a.block_size = block_size; a.cache = (bf16*)cache; a.page_stride = page_stride; a.inv_freq = inv_freq;
+  a.rot_dim = inv_freq ? rot_dim : 0; a.is_neox = is_neox; a.n_q_heads = n_q_heads; a.n_kv_heads = n_kv_heads;
+  a.head_dim = head_dim; a.error_flag = error_flag;
+  cudaStream_t s = (cudaStream_t)stream;
+  return M <= 8 ? launch<1, 1, kStagesPlain, true>(a, a.N, s) : launch<2, 1, kStagesPlain, true>(a, a.N, s);
 }

@@ -75,15 +75,15 @@ __global__ void rope_cache_kernel(RopeCacheArgs a) {
     if (head < a.n_q_heads) {
       T* p = q + (size_t)head * hd;
       const float x = to_f32(p[ix]), y = to_f32(p[iy]);
-      p[ix] = from_f32<T>(x * c - y * s);
-      p[iy] = from_f32<T>(y * c + x * s);
+      p[ix] = from_f32<T>(rot_first(x, y, c, s));
+      p[iy] = from_f32<T>(rot_second(x, y, c, s));
     } else if (kc) {
       const int g = head - a.n_q_heads;
       const T* p = k + (size_t)g * hd;
       const float x = to_f32(p[ix]), y = to_f32(p[iy]);
       T* d = kc + g * head_pitch;
-      d[ix] = from_f32<T>(x * c - y * s);
-      d[iy] = from_f32<T>(y * c + x * s);
+      d[ix] = from_f32<T>(rot_first(x, y, c, s));
+      d[iy] = from_f32<T>(rot_second(x, y, c, s));
     }
   }
   if (!kc) return;
@@ -155,8 +155,8 @@ __global__ void rope_cache_vec_kernel(RopeCacheArgs a) {
       for (int e = 0; e < VEC; ++e) {
         const float c = cs[i0 + e], s = cs[half + i0 + e];
         const float x = to_f32(xe[e]), y = to_f32(ye[e]);
-        xe[e] = from_f32<T>(x * c - y * s);
-        ye[e] = from_f32<T>(y * c + x * s);
+        xe[e] = from_f32<T>(rot_first(x, y, c, s));
+        ye[e] = from_f32<T>(rot_second(x, y, c, s));
       }
       *reinterpret_cast<Raw*>(dst + i0) = xr;
       *reinterpret_cast<Raw*>(dst + half + i0) = yr;

@@ -261,6 +261,37 @@ def gemm_skinny(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, fuse_act: O
     _check(rc, "gemm_skinny.cu", "lmsf_gemm_skinny", SKINNY_DEFINES)
 
 
+def gemm_skinny_qkv_rope_supported(x: torch.Tensor, w: torch.Tensor, head_dim: int, rot_dim: int, is_neox: bool) -> bool:
+    return (gemm_skinny_supported(x, w) and head_dim % 16 == 0
+            and (rot_dim == 0 or (rot_dim % 16 == 0 if is_neox else rot_dim % 2 == 0)))
+
+
+def gemm_skinny_qkv_rope(q_out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, positions: torch.Tensor, token_seq: torch.Tensor,
+                         block_table: torch.Tensor, block_size: int, cache: torch.Tensor, inv_freq: Optional[torch.Tensor],
+                         rot_dim: int, is_neox: bool, n_q_heads: int, n_kv_heads: int, head_dim: int,
+                         error_flag: Optional[torch.Tensor] = None):
+    """The merged q, k, v projection of up to 16 single tokens (x [M, K] bfloat16, w [(heads + 2 kv heads) * head_dim, K])
+    with the rotary encoding and the cache write in its epilogue: q_out [M, heads * head_dim] gets the rotated q, the
+    pages of `cache` the rotated k and v.  The same values as gemm_skinny followed by rope_cache_write."""
+    M, K = x.shape
+    if (not gemm_skinny_qkv_rope_supported(x, w, head_dim, rot_dim if inv_freq is not None else 0, is_neox)
+            or w.shape != ((n_q_heads + 2 * n_kv_heads) * head_dim, K) or q_out.shape != (M, n_q_heads * head_dim)
+            or q_out.dtype != torch.bfloat16 or q_out.stride(1) != 1):
+        raise KernelError(f"gemm_skinny_qkv_rope: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(q_out.shape)} are not taken")
+    if not cache.is_contiguous() or tuple(cache.shape[1:]) != (2, n_kv_heads, block_size, head_dim) or cache.dtype != torch.bfloat16:
+        raise KernelError(f"gemm_skinny_qkv_rope: cache of shape {tuple(cache.shape)} does not match the heads")
+    if inv_freq is not None and (inv_freq.dtype != torch.float32 or inv_freq.numel() != rot_dim // 2):
+        raise KernelError("gemm_skinny_qkv_rope: inv_freq must be float32 [rot_dim / 2]")
+    f = _func("gemm_skinny.cu", "lmsf_gemm_skinny_qkv_rope",
+              [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p,
+               c_int, c_int, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p], SKINNY_DEFINES)
+    rc = f(_ptr(q_out), q_out.stride(0), _ptr(x), x.stride(0), _ptr(w), w.stride(0), M, K, _i32(positions, "positions"),
+           _i32(token_seq, "token_seq"), _i32(block_table, "block_table"), block_table.shape[1], block_size, _ptr(cache),
+           cache.stride(0), _ptr(inv_freq) if inv_freq is not None else None, int(rot_dim), int(bool(is_neox)), n_q_heads,
+           n_kv_heads, head_dim, _i32(error_flag, "error_flag"), _stream())
+    _check(rc, "gemm_skinny.cu", "lmsf_gemm_skinny", SKINNY_DEFINES)
+
+
 # ----------------------------------------------------------------------------- streaming product on tcgen05 (17..128 rows)
 
 STREAM_MAX_M = 128

@@ -16,10 +16,12 @@ import torch
 
 from .. import kernels
 from .base import KVCacheSpec, LayerCache, Mixer, PositionEncoding, StepContext, WeightSpec, register_part
+from . import linear
 from .linear import matmul_tn
 
 
 USE_TC_PREFILL = True     # head sizes 64 and 128: prompt portions run on the tcgen05 kernel (csrc/attention_tc.cu)
+FUSE_QKV_ROPE = True      # up to 16 single tokens: rotary encoding and cache write in the q/k/v product's epilogue
 
 
 @register_part("mixer", "paged_attention")
@@ -57,6 +59,19 @@ class PagedAttention(Mixer):
 
     def forward(self, ctx: StepContext, h: torch.Tensor, cache: LayerCache) -> torch.Tensor:
         group = ctx.groups[cache.group]
+        fused = self.position_encoding.fused_rotary() if self.position_encoding is not None else None
+        if (FUSE_QKV_ROPE and cache.owner and linear.USE_SKINNY and (fused is not None or self.position_encoding is None)
+                and kernels.gemm_skinny_qkv_rope_supported(h, self.qkv, self.head_dim, fused[1] if fused else 0,
+                                                           fused[2] if fused else True)):
+            # a few single tokens (a decode step): projection, rotation and cache write in one kernel
+            inv_freq, rot_dim, is_neox = fused if fused is not None else (None, 0, True)
+            q = torch.empty((ctx.n_tokens, self.q_size), dtype=h.dtype, device=h.device)
+            kernels.gemm_skinny_qkv_rope(q, h, self.qkv, ctx.positions, ctx.token_seq, group.block_table, group.block_size,
+                                         cache.kv, inv_freq, rot_dim, is_neox, self.num_heads, self.num_kv_heads,
+                                         self.head_dim, ctx.error_flag)
+            out = torch.empty((ctx.n_tokens, self.q_size), dtype=h.dtype, device=h.device)
+            self.attend(ctx, out, q, cache.kv, group)
+            return matmul_tn(out, self.o)
         if cache.owner:
             qkv = matmul_tn(h, self.qkv)
             q = qkv[:, :self.q_size]
@@ -65,7 +80,6 @@ class PagedAttention(Mixer):
         else:  # keys and values are another call's: only the queries are needed
             q = matmul_tn(h, self.qkv[:self.q_size])
             k = v = None
-        fused = self.position_encoding.fused_rotary() if self.position_encoding is not None else None
         if self.position_encoding is not None and fused is None:
             self.position_encoding.apply(ctx, q, k, self.num_heads, self.num_kv_heads, self.head_dim)
         inv_freq, rot_dim, is_neox = fused if fused is not None else (None, 0, True)

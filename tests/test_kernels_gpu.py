@@ -411,6 +411,49 @@ def test_attention_kernels_on_a_long_prompt_and_a_long_context():
         assert err.max().item() <= tol, (splits, err.max().item(), rows[int(err.argmax()) // (nh * hd)])
 
 
+@pytest.mark.parametrize("M,nh,nkv,hd,rot,neox,K", [(8, 4, 2, 128, 128, True, 512), (1, 3, 1, 64, 64, True, 200), (13, 2, 2, 64, 32, True, 96),
+                                                    (5, 6, 3, 32, 32, False, 64), (16, 2, 1, 48, 24, False, 128), (7, 2, 2, 16, 0, True, 64)])
+def test_fused_qkv_rotary_cache_write_equals_the_three_steps(M, nh, nkv, hd, rot, neox, K):
+    """The q/k/v projection with rotation and cache write in its epilogue against the product, then the
+    rotary / cache-write kernel: the same bits in q and in the pages."""
+    from lmsf_b200 import kernels
+    g = torch.Generator().manual_seed(31)
+    d = dev()
+    bs, n_pages, max_blocks = 8, 40, 6
+    x = torch.randn(M, K, generator=g).bfloat16().to(d)
+    w = (torch.randn((nh + 2 * nkv) * hd, K, generator=g) * 0.2).bfloat16().to(d)
+    inv_freq = (1.0 / (10000.0 ** (torch.arange(0, rot, 2).float() / rot))).to(d) if rot else None
+    n_seqs = 3
+    token_seq = torch.tensor([i % n_seqs for i in range(M)], dtype=torch.int32, device=d)
+    # distinct positions per request; pages handed out at random
+    positions = torch.tensor([(i // n_seqs) * 5 + (i % n_seqs) * 3 for i in range(M)], dtype=torch.int32, device=d)
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    bt = torch.tensor([[perm.pop() for _ in range(max_blocks)] for _ in range(n_seqs)], dtype=torch.int32, device=d)
+    q_size, kv_size = nh * hd, nkv * hd
+    # the three steps
+    qkv = torch.empty(M, q_size + 2 * kv_size, dtype=torch.bfloat16, device=d)
+    kernels.gemm_skinny(qkv, x, w)
+    cache_ref = torch.zeros(n_pages, 2, nkv, bs, hd, dtype=torch.bfloat16, device=d)
+    flag = torch.zeros(1, dtype=torch.int32, device=d)
+    q_ref = qkv[:, :q_size]
+    kernels.rope_cache_write(q_ref, qkv[:, q_size:q_size + kv_size], qkv[:, q_size + kv_size:], positions, token_seq, bt, bs,
+                             cache_ref, inv_freq, rot, neox, nh, nkv, hd, flag)
+    # the one kernel
+    cache = torch.zeros_like(cache_ref)
+    q = torch.full((M, q_size), float("nan"), dtype=torch.bfloat16, device=d)
+    kernels.gemm_skinny_qkv_rope(q, x, w, positions, token_seq, bt, bs, cache, inv_freq, rot, neox, nh, nkv, hd, flag)
+    assert flag.item() == 0
+    assert torch.equal(q.view(torch.int16), q_ref.contiguous().view(torch.int16))
+    assert torch.equal(cache.view(torch.int16), cache_ref.view(torch.int16))
+    # a token without a page raises the error word and writes nothing
+    bt2 = bt.clone()
+    bt2[int(token_seq[0]), int(positions[0]) // bs] = -1
+    cache2 = torch.zeros_like(cache_ref)
+    kernels.gemm_skinny_qkv_rope(q, x, w, positions, token_seq, bt2, bs, cache2, inv_freq, rot, neox, nh, nkv, hd, flag)
+    assert flag.item() == 2
+    flag.zero_()
+
+
 @pytest.mark.parametrize("M,N,K", [(64, 4096, 4096), (17, 200, 64), (128, 6144, 1024), (33, 1000, 328), (100, 28, 14336),
                                    (1, 130, 4096), (48, 128 * 150, 64)])
 def test_gemm_stream_tcgen05_against_its_plain_twin(M, N, K):
