@@ -344,7 +344,7 @@ def main() -> int:
                    "hidden_size": cfg["hidden_size"], "num_attention_heads": cfg["num_attention_heads"],
                    "num_key_value_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
                    "intermediate_size": cfg["intermediate_size"], "vocab_size": V, "global_batch": a.batch,
-                   "seq_len": ctx_len, "max_model_len": MAX_MODEL_LEN, "block_size": BLOCK_SIZE,
+                   "seq_len": ctx_len, "max_model_len": max(MAX_MODEL_LEN, ctx_len + 64), "block_size": BLOCK_SIZE,
                    "prefill_tokens": PREFILL_TOKENS, "e2e_warmup": f">= {max(a.warmup, E2E_WARMUP)} steps, up to {E2E_WARMUP_SECONDS} s", "parallelism": "1 GPU",
                    "l2": "inputs larger than L2 (weights + cache of a step >> 126 MB); prefill flushes L2",
                    "peaks": pk["source"]},
