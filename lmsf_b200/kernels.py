@@ -295,7 +295,6 @@ def gemm_skinny_qkv_rope(q_out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, 
 # ----------------------------------------------------------------------------- streaming product on tcgen05 (17..128 rows)
 
 STREAM_MAX_M = 128
-STREAM_CTAS_PER_SM = int(os.environ.get("LMSF_GS_CTAS_PER_SM", "1"))
 STREAM_DEFINES: Tuple[str, ...] = tuple(d for d in os.environ.get("LMSF_GS_DEFINES", "").split(",") if d)
 _ERROR_WORDS = {}
 _STREAM_STATE = {}
@@ -319,7 +318,8 @@ def gemm_stream_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
 
 def gemm_stream(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor):
     """out[M, N] = x[M, K] w[N, K]^T for M <= 128 (bfloat16 in, bfloat16 or float32 out): W streamed once through
-    tensor-map copies and tcgen05 products, one persistent block per SM (csrc/gemm_stream.cu)."""
+    tensor-map copies and tcgen05 products by small blocks; the blocks that share a tile of W add up through the
+    shared memory of their thread-block cluster (csrc/gemm_stream.cu)."""
     M, K = x.shape
     N = w.shape[0]
     if not gemm_stream_supported(x, w) or w.shape[1] != K or out.shape != (M, N) or out.stride(1) != 1:
@@ -327,17 +327,14 @@ def gemm_stream(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor):
     if out.dtype not in (torch.bfloat16, torch.float32):
         raise KernelError("gemm_stream: out must be bfloat16 or float32")
     key = x.device.index or 0
-    st = _STREAM_STATE.get(key)
-    if st is None:
-        n_ctas = STREAM_CTAS_PER_SM * torch.cuda.get_device_properties(x.device).multi_processor_count
-        ws = torch.zeros((1 << 16) + n_ctas * 2 * STREAM_MAX_M * 128, dtype=torch.float32, device=x.device)
-        st = _STREAM_STATE[key] = (n_ctas, ws)
-    n_ctas, ws = st
+    n_sms = _STREAM_STATE.get(key)
+    if n_sms is None:
+        n_sms = _STREAM_STATE[key] = torch.cuda.get_device_properties(x.device).multi_processor_count
     f = _func("gemm_stream.cu", "lmsf_gemm_stream",
-              [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, c_void_p,
-               c_longlong, c_int, c_void_p, c_void_p], STREAM_DEFINES)
+              [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, c_int,
+               c_void_p, c_void_p], STREAM_DEFINES)
     rc = f(_ptr(out), _ptr(x), _ptr(w), M, N, K, x.stride(0), w.stride(0), out.stride(0), int(out.dtype == torch.float32),
-           _ptr(ws), ws.numel(), n_ctas, _ptr(error_word(x.device)), _stream())
+           n_sms, _ptr(error_word(x.device)), _stream())
     _check(rc, "gemm_stream.cu", "lmsf_gemm_stream", STREAM_DEFINES)
 
 

@@ -457,8 +457,8 @@ def test_fused_qkv_rotary_cache_write_equals_the_three_steps(M, nh, nkv, hd, rot
 @pytest.mark.parametrize("M,N,K", [(64, 4096, 4096), (17, 200, 64), (128, 6144, 1024), (33, 1000, 328), (100, 28, 14336),
                                    (1, 130, 4096), (48, 128 * 150, 64)])
 def test_gemm_stream_tcgen05_against_its_plain_twin(M, N, K):
-    """The streaming tcgen05 product: tiles dealt out to the persistent blocks so that some hold whole tiles and
-    some share them (partial sums added by the second kernel), ragged M, N and K."""
+    """The streaming tcgen05 product: tiles held by one block and tiles shared by the 2 to 8 blocks of a cluster,
+    ragged M, N and K; a row's result does not depend on the rows beside it."""
     from lmsf_b200 import kernels
     g = torch.Generator().manual_seed(12)
     d = dev()
@@ -473,6 +473,10 @@ def test_gemm_stream_tcgen05_against_its_plain_twin(M, N, K):
         assert flag.item() == 0
         tol_ = 1e-4 if odt == torch.float32 else 1e-2
         assert torch.allclose(out.float(), ref, rtol=tol_, atol=tol_ * ref.abs().max().item())
+    if M > 1:
+        alone = torch.empty(M // 2, N, dtype=torch.float32, device=d)
+        kernels.gemm_stream(alone, x[:M // 2], w)
+        assert torch.equal(alone, out[:M // 2])
     # strided operands (a slice of a wider matrix), as the merged projections are used
     wide = torch.randn(M, K + 64, generator=g).bfloat16().to(d)
     out = torch.empty(M, N, dtype=torch.bfloat16, device=d)
