@@ -2,8 +2,9 @@
 // softmax and accumulators), compiled for one head size: -DLMSF_HEAD_DIM=<multiple of 16, 16..128>.
 //
 //   decode  : one query token per request; a block serves the query heads that share one kv head
-//             (rows of the product = heads), the keys are split over blocks (grid.x) and the partial
-//             results are merged by a second kernel.  Counterpart in the reference:
+//             (rows of the product = heads), the keys are split over blocks (grid.x); up to 8 splits add
+//             up through the shared memory of their cluster, more through scratch memory, where the block
+//             that delivers last adds them.  Counterpart in the reference:
 //             paged_attention_v2_kernel + reduce, vllm/kernels/attention/attention_kernels.cu:441-572.
 //   prefill : portions of prompts (any number of query tokens per request, at any position); a block
 //             serves 64 query tokens of one head and walks the keys 0..position from pages.
