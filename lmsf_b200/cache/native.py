@@ -1,7 +1,6 @@
 """ctypes face of csrc/host_runtime.cpp (compiled with g++ on first use)."""
 from __future__ import annotations
 
-import ctypes
 from ctypes import POINTER, c_int, c_int64, c_longlong, c_void_p
 
 from ..csrc.build import load_library

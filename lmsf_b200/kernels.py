@@ -8,7 +8,6 @@ are an error.
 from __future__ import annotations
 
 import ctypes
-import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Optional, Tuple
 
@@ -295,7 +294,6 @@ def gemm_skinny_qkv_rope(q_out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, 
 # ----------------------------------------------------------------------------- streaming product on tcgen05 (17..128 rows)
 
 STREAM_MAX_M = 128
-STREAM_DEFINES: Tuple[str, ...] = tuple(d for d in os.environ.get("LMSF_GS_DEFINES", "").split(",") if d)
 _ERROR_WORDS = {}
 _STREAM_STATE = {}
 
@@ -332,10 +330,10 @@ def gemm_stream(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor):
         n_sms = _STREAM_STATE[key] = torch.cuda.get_device_properties(x.device).multi_processor_count
     f = _func("gemm_stream.cu", "lmsf_gemm_stream",
               [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, c_int,
-               c_void_p, c_void_p], STREAM_DEFINES)
+               c_void_p, c_void_p])
     rc = f(_ptr(out), _ptr(x), _ptr(w), M, N, K, x.stride(0), w.stride(0), out.stride(0), int(out.dtype == torch.float32),
            n_sms, _ptr(error_word(x.device)), _stream())
-    _check(rc, "gemm_stream.cu", "lmsf_gemm_stream", STREAM_DEFINES)
+    _check(rc, "gemm_stream.cu", "lmsf_gemm_stream")
 
 
 # ----------------------------------------------------------------------------- sampling

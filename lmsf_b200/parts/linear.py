@@ -20,7 +20,6 @@ _MM_HAS_OUT_DTYPE: Optional[bool] = None
 USE_SKINNY = True     # bfloat16 products of up to 16 rows run on this package's weight-streaming kernel
 USE_STREAM = False    # True: products of 17 to 128 rows run on the tcgen05 streaming kernel (csrc/gemm_stream.cu)
                       # instead of the library; measured slower than the library inside a step, so it is off
-STREAM_MIN_N = 0      # ... for weights of at least this many rows
 
 
 def matmul_tn(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
@@ -35,7 +34,7 @@ def matmul_tn(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype]
         out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype, device=x.device)
         kernels.gemm_skinny(out, x, w)
         return out
-    if (USE_STREAM and w.shape[0] >= STREAM_MIN_N and x.shape[0] <= kernels.STREAM_MAX_M
+    if (USE_STREAM and x.shape[0] <= kernels.STREAM_MAX_M
             and kernels.gemm_stream_supported(x, w) and out_dtype in (torch.bfloat16, torch.float32)):
         out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype, device=x.device)
         kernels.gemm_stream(out, x, w)

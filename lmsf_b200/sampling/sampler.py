@@ -8,7 +8,7 @@ finds the kept set by bisection instead of sorting the vocabulary (csrc/sampling
 from __future__ import annotations
 
 from collections import Counter
-from typing import List, Optional, Sequence
+from typing import Sequence
 
 import numpy as np
 import torch

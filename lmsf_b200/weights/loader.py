@@ -18,7 +18,7 @@ from typing import Dict, List, Tuple
 
 import torch
 
-from ..parts.base import ModelSpec, WeightSpec
+from ..parts.base import WeightSpec
 from .safetensors_io import TensorEntry, open_model_tensors
 
 

@@ -12,7 +12,7 @@ import json
 import mmap
 import os
 import struct
-from typing import Callable, Dict, Iterable, Iterator, List, Tuple
+from typing import Callable, Dict, List, Tuple
 
 import torch
 

@@ -1,6 +1,5 @@
 """Configuration and registry (no GPU)."""
 import json
-import os
 
 import pytest
 

@@ -3,7 +3,6 @@ state of its own, a layer run twice and a layer that reads another layer's cache
 run through the unchanged step function."""
 import json
 import math
-import os
 
 import pytest
 import torch
@@ -427,7 +426,7 @@ def test_attention_mixer_alone_over_two_steps(dtype, tol, nh, nkv, hd, window):
 
 
 def test_embedding_rotary_apply_and_block_arrangement():
-    from lmsf_b200.parts.base import Block, FeedForward, LayerCache, Mixer, Norm, build_part, PartSpec
+    from lmsf_b200.parts.base import FeedForward, LayerCache, Mixer, Norm, PartSpec
     from lmsf_b200.parts.block import PreNormBlock
     from lmsf_b200.parts.embedding import TokenEmbedding
     from lmsf_b200.parts.rope import RotaryEmbedding

@@ -3,7 +3,6 @@ small vocabulary: the kernels at the sizes that serving uses (tcgen05 prefill at
 weight-streaming products, CUDA graphs), against the plain implementation, in float32 and in bfloat16."""
 import numpy as np
 import pytest
-import torch
 
 import plain_llama as P
 import traces

@@ -3,7 +3,6 @@ one by one, in portions of changing size, and mixed with other requests so that 
 float32 and bfloat16, on tiny configurations that differ in every size."""
 import numpy as np
 import pytest
-import torch
 
 import plain_llama as P
 import traces

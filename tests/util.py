@@ -1,9 +1,6 @@
 """Tiny configurations, model folders and trace helpers shared by the tests."""
-import os
 import random
 import tempfile
-
-import torch
 
 # Two tiny Llama configurations that differ in every size and option.
 TINY_A = dict(architectures=["LlamaForCausalLM"], model_type="llama", hidden_size=64, num_hidden_layers=2,
