@@ -406,11 +406,11 @@ def mma_attention_supported(dtype: torch.dtype, head_dim: int) -> bool:
     return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= MMA_MAX_HEAD_DIM
 
 
-MMA_KV_STAGES = 3      # pipeline depth of the attention kernels (a build-time constant of attention_mma.cu)
+MMA_KV_STAGES = None   # pipeline depth of the attention kernels, a build-time constant of attention_mma.cu (None: its own choice)
 
 
 def _mma_defines(head_dim: int) -> Tuple[str, ...]:
-    if MMA_KV_STAGES == 3:
+    if MMA_KV_STAGES is None:
         return (f"LMSF_HEAD_DIM={head_dim}",)
     return (f"LMSF_HEAD_DIM={head_dim}", f"LMSF_KV_STAGES={MMA_KV_STAGES}")
 
