@@ -412,6 +412,29 @@ LMSF_API int lmsf_attention_decode_blocks_per_sm() {
   return n;
 }
 
+// Clusters of `cluster_size` blocks of the decode kernel that the device holds at a time (0 on error): the splits of
+// a request and kv head form a cluster, and a launch with more clusters than this runs in two waves.
+LMSF_API int lmsf_attention_decode_max_clusters(int cluster_size) {
+  using namespace lmsf::fa;
+  if (cluster_size < 1 || cluster_size > kMaxClusterSplits) return 0;
+  const int smem = decode_smem_bytes();
+  if (cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)cluster_size, 1024, 1);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = (size_t)smem;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)cluster_size;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, decode_kernel, &cfg) != cudaSuccess) return 0;
+  return n;
+}
+
 // Bytes of scratch that lmsf_attention_decode needs for the given sizes (0 when n_splits == 1): counters of
 // the splits that have delivered (one per request and group of heads, always the first kDecodeCounterBytes,
 // whatever the sizes of a call, so that calls of different sizes can share one buffer), then partial results.
