@@ -227,6 +227,15 @@ class ModelRunner:
             return 4
         return (n + 7) // 8 * 8
 
+    def graph_context_bucket(self, max_ctx: int) -> int:
+        """The launch geometry of a captured decode step (how the keys are split over blocks) is chosen for a
+        context length; a graph serves all steps whose longest context lies in the same bucket: powers of two
+        from 1,024 up to the longest context the model takes."""
+        b = 1024
+        while b < max_ctx and b < self.max_model_len:
+            b *= 2
+        return min(b, max(self.max_model_len, 1))
+
     def _graph_eligible(self, entries: Sequence[StepEntry]) -> bool:
         return (not self.enforce_eager and self.graph_safe and len(entries) <= self.max_graph_batch
                 and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries))
@@ -247,17 +256,19 @@ class ModelRunner:
 
         A batch in which every request brings one token and wants its logits is replayed from a CUDA graph
         (batch sizes are rounded up to 1, 2, 4 or a multiple of 8 with stand-in requests that touch only a
-        spare page; a graph is captured the second time its size is seen); the returned tensor is then a view
+        spare page; there is a graph per batch size and bucket of context lengths, captured the second time
+        the pair is seen); the returned tensor is then a view
         of the graph's own output buffer and holds its values until the next step of the same size."""
         graph_mode = self._graph_eligible(entries)
         hb = self._prepare(entries, mgr, self.static_blocks if graph_mode else None,
                            self.graph_batch_size(len(entries)) if graph_mode else 0)
         self.storage.zero_state_slots(mgr.take_fresh_slots())
-        if graph_mode and (hb.S in self._graphs or hb.S in self._seen_sizes):
-            logits = self._replay(hb, pending_tokens)
+        key = (hb.S, self.graph_context_bucket(max(hb.ctx_lens))) if graph_mode else None
+        if graph_mode and (key in self._graphs or key in self._seen_sizes):
+            logits = self._replay(hb, key, pending_tokens)
         else:
             if graph_mode:
-                self._seen_sizes.add(hb.S)
+                self._seen_sizes.add(key)
             dev = self._upload(hb)
             self._patch(hb, dev, pending_tokens)
             ctx, rows = self._context(hb, dev)
@@ -268,12 +279,12 @@ class ModelRunner:
             self.check_device_errors()
         return logits[:len(entries)] if graph_mode else logits
 
-    def _replay(self, hb: "_HostBatch", pending_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
-        g = self._graphs.get(hb.S)
+    def _replay(self, hb: "_HostBatch", key: Tuple[int, int], pending_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
+        g = self._graphs.get(key)
         if g is None:
             static_in = self._upload(hb)
             ctx, rows = self._context(hb, static_in)
-            ctx.extras["decode_max_ctx"] = self.max_model_len      # launch geometry must not depend on the step
+            ctx.extras["decode_max_ctx"] = key[1]      # launch geometry must not depend on the step, only on its bucket
             if self._graph_pool is None:
                 self._graph_pool = torch.cuda.graph_pool_handle()
                 self._capture_stream = torch.cuda.Stream(self.device)
@@ -292,7 +303,7 @@ class ModelRunner:
             torch.cuda.current_stream(self.device).wait_stream(side)
             n_launches = kernels.launch_count() - before
             kernels.add_launches(-n_launches)                      # recorded, not run
-            g = self._graphs[hb.S] = (graph, static_in, static_out, n_launches, hb.total)
+            g = self._graphs[key] = (graph, static_in, static_out, n_launches, hb.total)
         graph, static_in, static_out, n_launches, total = g
         if total != hb.total:
             raise StepError("the layout of a replayed batch changed")

@@ -94,6 +94,26 @@ def test_long_decoding_stays_on_the_reference(dtype):
     assert worst <= (1e-5 if dtype == "float32" else 5e-2) * max(1.0, abs(ref).max())
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decoding_across_a_bucket_of_context_lengths(dtype):
+    """Decode steps are replayed from a graph per batch size and bucket of context lengths (1,024, 2,048, ...):
+    a request that grows from 1,016 to 1,040 tokens runs eagerly, from the first bucket's graph, eagerly again and
+    from the second bucket's graph, and stays on the plain implementation throughout."""
+    import tempfile
+    import traces
+    from lmsf_b200.weights import write_random_model
+    cfg_d = dict(util.TINY_C, max_position_embeddings=4096)
+    with tempfile.TemporaryDirectory(prefix="lmsf_bucket_") as folder:
+        write_random_model(folder, cfg_d, seed=5, dtype=dtype, std=0.05)
+        cfg, w = P.load_model(folder)
+        ids = util.random_ids(1040, cfg["vocab_size"], 78)
+        ref = P.forward(cfg, w, ids).numpy()
+        steps = traces.whole({"x": ids}, tail=24)
+        out = traces.collect(steps, traces.run_inprocess(folder, dtype, steps, 16, 1040 + 16))
+    worst = max(abs(out[("x", i)] - ref[i]).max() for i in range(1040 - 24, 1040))
+    assert worst <= (1e-5 if dtype == "float32" else 5e-2) * max(1.0, abs(ref).max())
+
+
 def test_bfloat16_generation_runs_and_mostly_agrees():
     from lmsf_b200 import SamplingParams
     name = "A"
