@@ -204,3 +204,47 @@ def test_engine_step_api_and_abort():
     assert seen["b"] == 30
     engine.cache.check_invariants()
     assert engine.cache.num_free_pages() == 32
+
+
+@pytest.mark.parametrize("seed", [3, 5, 6, 9, 10, 11])
+def test_random_workloads_through_the_engine(seed):
+    """Requests that arrive over time, random prompt and output lengths, greedy or seeded sampling, a random token
+    budget, few pages (seeds 6, 9, 10 and 11 preempt) and synchronous or asynchronous scheduling: every request
+    gets the plain implementation's tokens and every page comes back."""
+    import random
+    from lmsf_b200 import EngineArgs, LLMEngine, SamplingParams
+    rng = random.Random(seed)
+    name = rng.choice(["A", "B", "W", "C"])
+    cfgd, bs = util.CONFIGS[name], util.BLOCK_SIZE[name]
+    folder = util.model_folder(name, "float32", 0.15)
+    cfg, w = P.load_model(folder)
+    n_req = rng.randint(3, 9)
+    max_len = min(cfgd["max_position_embeddings"], 120)
+    prompts = [util.random_ids(rng.randint(1, 60), cfgd["vocab_size"], seed * 50 + i) for i in range(n_req)]
+    gens = [rng.randint(1, 30) for _ in range(n_req)]
+    pages = max(-(-max(len(p) + g for p, g in zip(prompts, gens)) // bs) + 2, rng.randint(6, 40))
+    budget, max_seqs, async_s = rng.choice([8, 16, 33, 64, 256]), rng.choice([2, 3, 4, 8]), rng.random() < 0.5
+    eng = LLMEngine(EngineArgs(model=folder, dtype="float32", block_size=bs, num_gpu_blocks=pages,
+                               max_num_batched_tokens=budget, max_num_seqs=max_seqs, max_model_len=max_len,
+                               no_async_scheduling=not async_s))
+    sps = [SamplingParams(temperature=0.0 if rng.random() < 0.6 else 0.8, seed=seed * 7 + i, max_tokens=g, ignore_eos=True)
+           for i, g in enumerate(gens)]
+    arrivals = sorted((rng.randint(0, 12), i) for i in range(n_req))
+    results, step, ai = {}, 0, 0
+    while ai < len(arrivals) or eng.has_unfinished_requests():
+        while ai < len(arrivals) and arrivals[ai][0] <= step:
+            i = arrivals[ai][1]
+            eng.add_request(i, None, sps[i], prompt_token_ids=prompts[i])
+            ai += 1
+        for o in eng.step():
+            if o.finished:
+                results[o.request_id] = o.outputs[0].token_ids
+        step += 1
+        assert step < 5000
+    if seed in (6, 9, 10, 11):
+        assert eng.scheduler.num_preemptions > 0
+    for i in range(n_req):
+        ref, _ = P.generate(cfg, w, prompts[i], gens[i], temperature=sps[i].temperature, seed=sps[i].seed)
+        assert results[i] == ref, (i, len(prompts[i]), gens[i], sps[i].temperature)
+    eng.cache.check_invariants()
+    assert eng.cache.num_free_pages() == pages
