@@ -59,3 +59,27 @@ def test_random_configurations(seed, dtype):
             worst = max(float(np.abs(row - ref[rid][pos]).max()) for (rid, pos), row in rows.items())
             assert worst <= REL[dtype] * scale, (f"{mode}: max |diff| {worst:.3e} at logit scale {scale:.3f}; {cfg}, "
                                                 f"pages of {bs}, prompts of {lengths}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("hidden,inter,vocab,hd", [(33, 21, 55, 16), (7, 5, 11, 16), (50, 99, 211, 32)])
+def test_odd_widths(hidden, inter, vocab, hd, dtype):
+    """Widths, feed-forward sizes and vocabularies that are odd or no multiple of 8: the vectorised kernels and the
+    weight-streaming products must step aside for their plain forms, never give a wrong result."""
+    from lmsf_b200 import models  # noqa: F401
+    from lmsf_b200.weights import write_random_model
+    cfg = dict(architectures=["LlamaForCausalLM"], model_type="llama", hidden_size=hidden, num_hidden_layers=2,
+               num_attention_heads=3, num_key_value_heads=1, head_dim=hd, intermediate_size=inter, vocab_size=vocab,
+               rope_theta=10000.0, rms_norm_eps=1e-5, tie_word_embeddings=hidden % 2 == 0, max_position_embeddings=256,
+               hidden_act="silu", bos_token_id=1, eos_token_id=2)
+    with tempfile.TemporaryDirectory(prefix="lmsf_fuzz_") as folder:
+        write_random_model(folder, dict(cfg), seed=1, dtype=dtype, std=0.05)
+        reqs = {f"r{i}": util.random_ids(n, vocab, i) for i, n in enumerate([3, 40, 129, 17])}
+        c, w = P.load_model(folder)
+        ref = {rid: P.forward(c, w, t).numpy() for rid, t in reqs.items()}
+        scale = max(1.0, max(float(np.abs(r).max()) for r in ref.values()))
+        for steps in (traces.whole(reqs, tail=32), traces.mixed(reqs, seed=3)):
+            out = traces.run_inprocess(folder, dtype, steps, 16, traces.max_live_tokens(steps, round_to=16))
+            rows = traces.collect(steps, out)
+            worst = max(float(np.abs(row - ref[rid][pos]).max()) for (rid, pos), row in rows.items())
+            assert worst <= REL[dtype] * scale, f"max |diff| {worst:.3e} at logit scale {scale:.3f}"
