@@ -402,16 +402,6 @@ static int decode_smem_bytes() {
   return m > smem_weights ? m : smem_weights;
 }
 
-// Blocks of the decode kernel that one SM holds at a time (0 on error); used to size the key splits.
-LMSF_API int lmsf_attention_decode_blocks_per_sm() {
-  using namespace lmsf::fa;
-  const int smem = decode_smem_bytes();
-  if (cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return 0;
-  int n = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, decode_kernel, kThreads, smem) != cudaSuccess) return 0;
-  return n;
-}
-
 // Clusters of `cluster_size` blocks of the decode kernel that the device holds at a time (0 on error): the splits of
 // a request and kv head form a cluster, and a launch with more clusters than this runs in two waves.
 LMSF_API int lmsf_attention_decode_max_clusters(int cluster_size) {

@@ -84,7 +84,6 @@ class ModelRunner:
         self.error_flag = kernels.error_word(device)      # shared with the kernels that have no step context
         self.vocab_size = model.spec.vocab_size
         self.h2d_bytes = 0          # bytes of step inputs copied from pinned host memory so far
-        self.sm_count = torch.cuda.get_device_properties(device).multi_processor_count
         self._ring = [(None, None)] * 4
         self._ring_pos = 0
         # CUDA graphs of decode steps
@@ -209,7 +208,6 @@ class ModelRunner:
                           decode_seq_ids=view("dec_ids"), n_decode_seqs=hb.n_dec, q_tile_seq=view("tile_seq"),
                           q_tile_q0=view("tile_q0"), n_q_tiles=hb.n_tiles, q_tile128_seq=view("tile128_seq"),
                           q_tile128_q0=view("tile128_q0"), n_q_tiles128=hb.n_tiles128)
-        ctx.extras["sm_count"] = self.sm_count
         return ctx, view("rows")
 
     def build_context(self, entries: Sequence[StepEntry], mgr: CacheManager) -> Tuple[StepContext, torch.Tensor]:

@@ -426,16 +426,6 @@ def _check_paged(q, out, cache, n_q_heads, n_kv_heads, head_dim, block_size, wha
         raise KernelError(f"{what}: q/out rows must be 4-byte aligned and the cache 16-byte aligned")
 
 
-_DECODE_BLOCKS_PER_SM = {}
-
-
-def decode_blocks_per_sm(head_dim: int) -> int:
-    n = _DECODE_BLOCKS_PER_SM.get(head_dim)
-    if n is None:
-        lib = load_library("attention_mma.cu", _mma_defines(head_dim))
-        lib.lmsf_attention_decode_blocks_per_sm.restype = c_int
-        n = _DECODE_BLOCKS_PER_SM[head_dim] = max(1, lib.lmsf_attention_decode_blocks_per_sm())
-    return n
 
 
 _DECODE_MAX_CLUSTERS = {}

@@ -98,9 +98,6 @@ class PagedAttention(Mixer):
         generic kernel, which is also their plain twin."""
         if kernels.mma_attention_supported(q.dtype, self.head_dim) and not ctx.extras.get("force_generic_attention"):
             if ctx.n_decode_seqs:
-                sm = ctx.extras.get("sm_count")
-                if sm is None:
-                    sm = ctx.extras["sm_count"] = torch.cuda.get_device_properties(q.device).multi_processor_count
                 max_ctx = ctx.extras.get("decode_max_ctx")
                 if max_ctx is None:
                     max_ctx = ctx.extras["decode_max_ctx"] = max(c for c, n in zip(ctx.ctx_lens, ctx.q_lens) if n == 1)
