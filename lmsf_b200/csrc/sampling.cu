@@ -151,6 +151,100 @@ __device__ __forceinline__ float block_max_f(float v, float* scratch) {
   return scratch[32];
 }
 
+// Calls f(index, value) for every value of the row, the block's threads sharing the work; 16 bytes per load when the
+// row is aligned (a thread with one 4-byte load in flight at a time would wait for L2 most of the time).
+template <typename F>
+__device__ __forceinline__ void for_each_value(const float* __restrict__ row, int vocab, F f) {
+  if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+    const int n4 = vocab >> 2;
+    const float4* r4 = reinterpret_cast<const float4*>(row);
+#pragma unroll 2
+    for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+      const float4 x = r4[i];
+      f(4 * i, x.x);
+      f(4 * i + 1, x.y);
+      f(4 * i + 2, x.z);
+      f(4 * i + 3, x.w);
+    }
+    for (int v = (n4 << 2) + threadIdx.x; v < vocab; v += blockDim.x) f(v, row[v]);
+  } else {
+    for (int v = threadIdx.x; v < vocab; v += blockDim.x) f(v, row[v]);
+  }
+}
+
+// Block-wide sum of 64-bit integers (any order gives the same sum); the result is valid in every thread.
+__device__ __forceinline__ unsigned long long block_sum_u64(unsigned long long v, unsigned long long* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  unsigned long long t = 0ull;
+  for (int w = 0; w < nwarps; ++w) t += scratch[w];
+  return t;
+}
+
+constexpr int kSelBits = 6;                  // key bits settled per pass over the row
+constexpr int kSelBins = 1 << kSelBits;
+constexpr float kMassOne = 1099511627776.0f; // 2^40: probabilities relative to the largest are summed as integers
+
+// One pass of the selection: among the row's values whose key is at least `key_floor` and whose bits above
+// (shift + width) equal `prefix`, how many fall into each value of the next `width` bits and (MASS) how much
+// probability, as integers, so that the sums do not depend on the order.  Each warp counts into bins of its
+// own (lanes of one warp may meet in a bin, warps never), then the warps' bins are added.
+template <bool MASS>
+__device__ __forceinline__ void select_pass(const float* __restrict__ row, int vocab, float invT, float m, uint32_t key_floor,
+                                            uint32_t prefix, int shift, int width, unsigned (*w_cnt)[kSelBins],
+                                            unsigned long long (*w_mass)[kSelBins], unsigned* cnt, unsigned long long* mass) {
+  const int warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+  for (int i = threadIdx.x; i < nwarps * kSelBins; i += blockDim.x) {
+    w_cnt[0][i] = 0u;
+    if (MASS) w_mass[0][i] = 0ull;
+  }
+  __syncthreads();
+  const int top = shift + width;
+  const uint32_t dmask = (1u << width) - 1u;
+  // a thread sums runs of values that fall into the same bin in registers (in the first passes most values share a
+  // few bins) and adds a run to its warp's bins when the bin changes
+  uint32_t run_d = 0xffffffffu;
+  unsigned run_c = 0u;
+  unsigned long long run_m = 0ull;
+  auto flush = [&]() {
+    if (run_c == 0u) return;
+    atomicAdd(&w_cnt[warp][run_d], run_c);
+    if (MASS) atomicAdd(&w_mass[warp][run_d], run_m);
+  };
+  for_each_value(row, vocab, [&](int, float x) {
+    const float z = x * invT;
+    if (z != z) return;
+    const uint32_t key = float_key(z);
+    if (key < key_floor) return;
+    if (top < 32 && (key >> top) != prefix) return;
+    const uint32_t d = (key >> shift) & dmask;
+    if (d != run_d) {
+      flush();
+      run_d = d;
+      run_c = 0u;
+      run_m = 0ull;
+    }
+    ++run_c;
+    if (MASS) run_m += (unsigned long long)(expf(z - m) * kMassOne);
+  });
+  flush();
+  __syncthreads();
+  if (threadIdx.x < kSelBins) {
+    unsigned c = 0u;
+    unsigned long long ms = 0ull;
+    for (int w = 0; w < nwarps; ++w) {
+      c += w_cnt[w][threadIdx.x];
+      if (MASS) ms += w_mass[w][threadIdx.x];
+    }
+    cnt[threadIdx.x] = c;
+    if (MASS) mass[threadIdx.x] = ms;
+  }
+  __syncthreads();
+}
+
 // Temperature sampling with top-k, top-p and min-p, one block per row.  With z = logits / T:
 //   top-k keeps the k largest z (ties at the k-th value are all kept);
 //   top-p keeps a token iff the probability mass of the strictly larger kept tokens is < p
@@ -158,15 +252,22 @@ __device__ __forceinline__ float block_max_f(float v, float* scratch) {
 //         core/src/model_executor/layers/sampler.rs:139-210: the same set when values are distinct);
 //   min-p keeps z >= max z + log(min_p) (sampler.rs:305-312);
 // and the token is drawn among the kept ones by the exponential race of sample_kernel.
-// Thresholds are found by bisection over the 32-bit keys with block-wide sums in a fixed order, so the
-// kept set, and with it the draw, is reproducible.
-__global__ void sample_filtered_kernel(int* __restrict__ out, const float* __restrict__ logits, long long row_stride,
+// A value's order-preserving 32-bit key is settled six bits per pass over the row (six passes for a threshold
+// instead of the 32 of a bisection): the pass counts, for every value of the next six bits, the values (and their
+// probability) under the prefix found so far.  Counts and probabilities are integers, so the kept set, and with
+// it the draw, is reproducible.
+__global__ void __launch_bounds__(1024) sample_filtered_kernel(int* __restrict__ out, const float* __restrict__ logits, long long row_stride,
                                        int vocab, const float* __restrict__ temperature,
                                        const unsigned long long* __restrict__ seed, const int* __restrict__ step,
                                        const int* __restrict__ top_k, const float* __restrict__ top_p,
                                        const float* __restrict__ min_p, const int* __restrict__ row_ids) {
   __shared__ float scratch[33];
+  __shared__ unsigned long long scratch64[32];
   __shared__ Best sh[32];
+  __shared__ unsigned w_cnt[32][kSelBins];
+  __shared__ unsigned long long w_mass[32][kSelBins];
+  __shared__ unsigned cnt[kSelBins];
+  __shared__ unsigned long long mass[kSelBins];
   const int r = row_ids ? row_ids[blockIdx.x] : blockIdx.x;
   const float* row = logits + (size_t)r * row_stride;
   const float T = temperature[r];
@@ -176,47 +277,61 @@ __global__ void sample_filtered_kernel(int* __restrict__ out, const float* __res
   const float mp = min_p ? min_p[r] : 0.0f;
 
   float m = -INFINITY;
-  for (int v = threadIdx.x; v < vocab; v += blockDim.x) {
-    const float z = row[v] * invT;
+  for_each_value(row, vocab, [&](int, float x) {
+    const float z = x * invT;
     if (z == z) m = fmaxf(m, z);
-  }
+  });
   m = block_max_f(m, scratch);
 
   uint32_t key_min = 0u;                     // tokens with key >= key_min are kept
-  if (k > 0 && k < vocab) {                  // largest key with count(key_v >= key) >= k
-    uint32_t lo = 0u, hi = 0xffffffffu;
-    while (lo < hi) {
-      const uint32_t mid = lo + (uint32_t)(((unsigned long long)hi - lo + 1ull) >> 1);
-      float cnt = 0.f;
-      for (int v = threadIdx.x; v < vocab; v += blockDim.x) {
-        const float z = row[v] * invT;
-        cnt += (z == z && float_key(z) >= mid) ? 1.f : 0.f;
+  if (k > 0 && k < vocab) {                  // the key of the k-th largest value
+    uint32_t prefix = 0u;
+    unsigned above = 0u;                     // values whose settled bits are larger than the prefix's
+    bool enough = true;
+    for (int shift = 32 - kSelBits; enough; shift = shift >= kSelBits ? shift - kSelBits : 0) {
+      const int width = shift == 0 && (32 % kSelBits) ? 32 % kSelBits : kSelBits;
+      select_pass<false>(row, vocab, invT, m, 0u, prefix, shift, width, w_cnt, w_mass, cnt, mass);
+      unsigned c = above;
+      int d = (1 << width) - 1;
+      for (; d >= 0; --d) {
+        if (c + cnt[d] >= (unsigned)k) break;
+        c += cnt[d];
       }
-      cnt = block_sum_f(cnt, scratch);
-      if (cnt >= (float)k) lo = mid; else hi = mid - 1u;
+      if (d < 0) { enough = false; break; }  // fewer than k values in all: everything is kept
+      above = c;
+      prefix = (prefix << width) | (uint32_t)d;
+      if (shift == 0) break;
     }
-    key_min = lo;
+    key_min = enough ? prefix : 0u;
   }
   if (p < 1.0f) {
-    float Z = 0.f;
-    for (int v = threadIdx.x; v < vocab; v += blockDim.x) {
-      const float z = row[v] * invT;
-      if (z == z && float_key(z) >= key_min) Z += expf(z - m);
-    }
-    Z = block_sum_f(Z, scratch);
-    const float target = p * Z;              // kept iff mass of strictly larger keys < p * Z
-    uint32_t lo = key_min, hi = float_key(m);   // smallest key whose mass_gt < target; key(m) always qualifies
-    while (lo < hi) {
-      const uint32_t mid = lo + ((hi - lo) >> 1);
-      float mass = 0.f;
-      for (int v = threadIdx.x; v < vocab; v += blockDim.x) {
-        const float z = row[v] * invT;
-        if (z == z && float_key(z) > mid) mass += expf(z - m);
+    unsigned long long Z = 0ull;
+    for_each_value(row, vocab, [&](int, float x) {
+      const float z = x * invT;
+      if (z == z && float_key(z) >= key_min) Z += (unsigned long long)(expf(z - m) * kMassOne);
+    });
+    Z = block_sum_u64(Z, scratch64);
+    const unsigned long long target = (unsigned long long)((double)p * (double)Z);   // kept iff mass of strictly larger keys < p * Z
+    // the smallest key of a kept token: the lowest value that still has less than the target above it
+    uint32_t prefix = 0u;
+    unsigned long long above = 0ull;         // probability of the values whose settled bits are larger than the prefix's
+    for (int shift = 32 - kSelBits;; shift = shift >= kSelBits ? shift - kSelBits : 0) {
+      const int width = shift == 0 && (32 % kSelBits) ? 32 % kSelBits : kSelBits;
+      select_pass<true>(row, vocab, invT, m, key_min, prefix, shift, width, w_cnt, w_mass, cnt, mass);
+      unsigned long long a_run = above, a_best = above;
+      int best = -1;
+      for (int d = (1 << width) - 1; d >= 0; --d) {
+        if (cnt[d] > 0u) {
+          if (a_run < target || best < 0) { best = d; a_best = a_run; }   // (the largest value is always kept)
+          else break;
+        }
+        a_run += mass[d];
       }
-      mass = block_sum_f(mass, scratch);
-      if (mass < target) hi = mid; else lo = mid + 1u;
+      if (best < 0) break;                   // no value at all (every logit NaN)
+      above = a_best;
+      prefix = (prefix << width) | (uint32_t)best;
+      if (shift == 0) { key_min = prefix; break; }
     }
-    key_min = lo;
   }
   if (mp > 0.0f) {
     const uint32_t kmp = float_key(m + logf(mp));
@@ -226,11 +341,11 @@ __global__ void sample_filtered_kernel(int* __restrict__ out, const float* __res
   const uint32_t slo = (uint32_t)(seed[r] & 0xffffffffull), shi = (uint32_t)(seed[r] >> 32);
   const uint32_t st = (uint32_t)step[r];
   Best b{-INFINITY, 0x7fffffff};
-  for (int v = threadIdx.x; v < vocab; v += blockDim.x) {
-    const float z = row[v] * invT;
-    if (z != z || float_key(z) < key_min) continue;
-    b = better(b, Best{(double)row[v] / (double)T + neg_log_exponential(slo, shi, st, (uint32_t)v), v});
-  }
+  for_each_value(row, vocab, [&](int v, float x) {
+    const float z = x * invT;
+    if (z != z || float_key(z) < key_min) return;
+    b = better(b, Best{(double)x / (double)T + neg_log_exponential(slo, shi, st, (uint32_t)v), v});
+  });
   for (int o = 16; o > 0; o >>= 1) {
     Best other{__shfl_xor_sync(0xffffffffu, b.score, o), __shfl_xor_sync(0xffffffffu, b.index, o)};
     b = better(b, other);

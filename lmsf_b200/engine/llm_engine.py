@@ -149,7 +149,8 @@ class LLMEngine:
     # for the next batch overlaps the device's work on this one, and a request's newest token goes from the
     # sampler to the next batch's input on the device (`StepEntry.last_from`).  A request that turns out to
     # have stopped at batch k has then already been run once more; that result is dropped at the next retire.
-    # Requests with penalties need their token history on the host, so steps that hold one run in order.
+    # Requests with penalties need their token history on the host when they are sampled: a batch that holds one
+    # launches its model step first, then retires the batch before it, then samples.
 
     def _will_finish_by_length(self, seq: Sequence) -> bool:
         n_out = len(seq.output_token_ids) + seq.num_pending
@@ -184,6 +185,11 @@ class LLMEngine:
             logits = self.runner.step(entries, self.cache, check=False,
                                       pending_tokens=prev.tokens_dev if prev is not None else None)
             flight = _InFlight(sampled=sampled, row_of={s.request_id: i for i, s in enumerate(sampled)})
+            if prev is not None and any(s.sampling_params.penalties_active for s in sampled):
+                # penalties count the tokens so far: the batch before is retired (its tokens read) between this
+                # batch's model step, which is already running, and its sampling, which is launched behind it
+                self._retire(prev, outputs)
+                self._inflight = None
             if sampled:
                 flight.tokens_dev = self.sampler.sample(
                     logits, [s.sampling_params for s in sampled], [s.seed for s in sampled],
@@ -241,7 +247,7 @@ class LLMEngine:
         """Runs one batch.  Returns an output for every request that received a token (with async scheduling:
         the tokens of the batch launched by the PREVIOUS call; keep calling while has_unfinished_requests())."""
         outputs: List[RequestOutput] = []
-        overlap = self.async_scheduling and not any(s.sampling_params.penalties_active for s in self.seqs.values())
+        overlap = self.async_scheduling
         if not overlap and self._inflight is not None:
             self._retire(self._inflight, outputs)
             self._inflight = None

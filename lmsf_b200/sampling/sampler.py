@@ -7,8 +7,8 @@ finds the kept set by bisection instead of sorting the vocabulary (csrc/sampling
 """
 from __future__ import annotations
 
-from collections import Counter
-from typing import Sequence
+import weakref
+from typing import Dict, Sequence, Tuple
 
 import numpy as np
 import torch
@@ -17,9 +17,58 @@ from .. import kernels
 from .params import SamplingParams
 
 
+class _TokenHistory:
+    """The distinct tokens of one request (prompt and output) with how often each occurs in the output, kept up
+    to date by looking only at the output tokens that are new since the last step."""
+
+    def __init__(self, prompt_token_ids: Sequence[int]):
+        distinct = np.unique(np.asarray(prompt_token_ids, dtype=np.int32))
+        self.n = int(distinct.shape[0])
+        cap = max(64, 2 * self.n)
+        self.tokens = np.zeros(cap, dtype=np.int32)
+        self.counts = np.zeros(cap, dtype=np.int32)
+        self.tokens[:self.n] = distinct
+        self.where: Dict[int, int] = {int(t): i for i, t in enumerate(distinct.tolist())}
+        self.seen_outputs = 0
+
+    def update(self, output_token_ids: Sequence[int]) -> Tuple[np.ndarray, np.ndarray]:
+        if len(output_token_ids) < self.seen_outputs:      # the output was cut back: count it again
+            self.counts[:self.n] = 0
+            self.seen_outputs = 0
+        for t in output_token_ids[self.seen_outputs:]:
+            i = self.where.get(t)
+            if i is None:
+                if self.n == self.tokens.shape[0]:
+                    self.tokens = np.concatenate([self.tokens, np.zeros_like(self.tokens)])
+                    self.counts = np.concatenate([self.counts, np.zeros_like(self.counts)])
+                i = self.where[t] = self.n
+                self.tokens[i] = t
+                self.n += 1
+            self.counts[i] += 1
+        self.seen_outputs = len(output_token_ids)
+        # copies: the arrays go to the device asynchronously and change again at the next step
+        return self.tokens[:self.n].copy(), self.counts[:self.n].copy()
+
+
 class Sampler:
     def __init__(self, device: torch.device):
         self.device = device
+        # token histories of the requests with penalties, by the identity of the request object; an entry goes
+        # when its object does
+        self._histories: Dict[int, Tuple["weakref.ref", _TokenHistory]] = {}
+
+    def _history(self, seq) -> _TokenHistory:
+        key = id(seq)
+        entry = self._histories.get(key)
+        if entry is not None and entry[0]() is seq:
+            return entry[1]
+        hist = _TokenHistory(seq.prompt_token_ids)
+        try:
+            ref = weakref.ref(seq, lambda _r, k=key, d=self._histories: d.pop(k, None))
+        except TypeError:              # an object that cannot be referred to weakly: no memory between steps
+            return hist
+        self._histories[key] = (ref, hist)
+        return hist
 
     def require_filters(self) -> None:
         """top_k, top_p, min_p and the penalties are built in; nothing to check."""
@@ -32,17 +81,14 @@ class Sampler:
         for r, (p, seq) in enumerate(zip(params, seqs)):
             if not p.penalties_active:
                 continue
-            out_counts = Counter(seq.output_token_ids)
-            seen = set(seq.prompt_token_ids) | set(out_counts)
-            for t in seen:
-                rows.append(r)
-                toks.append(t)
-                counts.append(out_counts.get(t, 0))
+            t, c = self._history(seq).update(seq.output_token_ids)
+            rows.append(np.full(t.shape[0], r, dtype=np.int32))
+            toks.append(t)
+            counts.append(c)
         if not rows:
             return
-        n = len(params)
-        kernels.apply_penalties(logits, self._dev(rows, torch.int32), self._dev(toks, torch.int32),
-                                self._dev(counts, torch.int32),
+        dev = lambda a: torch.from_numpy(np.concatenate(a)).to(self.device, non_blocking=True)
+        kernels.apply_penalties(logits, dev(rows), dev(toks), dev(counts),
                                 self._dev([p.presence_penalty for p in params], torch.float32),
                                 self._dev([p.frequency_penalty for p in params], torch.float32),
                                 self._dev([p.repetition_penalty for p in params], torch.float32))
