@@ -46,8 +46,7 @@ class _TokenHistory:
                 self.n += 1
             self.counts[i] += 1
         self.seen_outputs = len(output_token_ids)
-        # copies: the arrays go to the device asynchronously and change again at the next step
-        return self.tokens[:self.n].copy(), self.counts[:self.n].copy()
+        return self.tokens[:self.n], self.counts[:self.n]       # views: the caller copies them at once
 
 
 class Sampler:
@@ -77,21 +76,27 @@ class Sampler:
         return torch.tensor(values, dtype=dtype).to(self.device, non_blocking=True)
 
     def _apply_penalties(self, logits: torch.Tensor, params: Sequence[SamplingParams], seqs) -> None:
-        rows, toks, counts = [], [], []
+        which, toks, counts = [], [], []
         for r, (p, seq) in enumerate(zip(params, seqs)):
             if not p.penalties_active:
                 continue
             t, c = self._history(seq).update(seq.output_token_ids)
-            rows.append(np.full(t.shape[0], r, dtype=np.int32))
+            which.append(r)
             toks.append(t)
             counts.append(c)
-        if not rows:
+        if not which:
             return
-        dev = lambda a: torch.from_numpy(np.concatenate(a)).to(self.device, non_blocking=True)
-        kernels.apply_penalties(logits, dev(rows), dev(toks), dev(counts),
-                                self._dev([p.presence_penalty for p in params], torch.float32),
-                                self._dev([p.frequency_penalty for p in params], torch.float32),
-                                self._dev([p.repetition_penalty for p in params], torch.float32))
+        # one upload of integers [rows; tokens; counts] and one of the rows' three penalties
+        lengths = [t.shape[0] for t in toks]
+        n = sum(lengths)
+        ints = np.empty((3, n), dtype=np.int32)
+        ints[0] = np.repeat(np.asarray(which, dtype=np.int32), lengths)
+        np.concatenate(toks, out=ints[1])
+        np.concatenate(counts, out=ints[2])
+        ints_dev = torch.from_numpy(ints).to(self.device, non_blocking=True)
+        pen = self._dev([[p.presence_penalty for p in params], [p.frequency_penalty for p in params],
+                         [p.repetition_penalty for p in params]], torch.float32)
+        kernels.apply_penalties(logits, ints_dev[0], ints_dev[1], ints_dev[2], pen[0], pen[1], pen[2])
 
     @torch.inference_mode()
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
@@ -111,15 +116,20 @@ class Sampler:
         if all(p.greedy for p in params):
             kernels.sample(out, logits)
             return out
-        temp = self._dev([p.temperature for p in params], torch.float32)
+        filtered = [r for r, p in enumerate(params) if p.filters_active]
+        # one upload of the rows' floats and one of their integers
+        if filtered:
+            f = self._dev([[p.temperature for p in params], [p.top_p for p in params], [p.min_p for p in params]], torch.float32)
+            i = self._dev([list(steps), [p.top_k for p in params]], torch.int32)
+        else:
+            f = self._dev([[p.temperature for p in params]], torch.float32)
+            i = self._dev([list(steps)], torch.int32)
+        temp, step = f[0], i[0]
         seed = torch.from_numpy(np.asarray([s & 0xFFFFFFFFFFFFFFFF for s in seeds], dtype=np.uint64).view(np.int64)
                                 ).to(self.device, non_blocking=True)
-        step = self._dev(list(steps), torch.int32)
-        kernels.sample(out, logits, temp, seed, step)
-        filtered = [r for r, p in enumerate(params) if p.filters_active]
+        if len(filtered) < rows:
+            kernels.sample(out, logits, temp, seed, step)
         if filtered:
-            kernels.sample_filtered(out, logits, temp, seed, step, self._dev([p.top_k for p in params], torch.int32),
-                                    self._dev([p.top_p for p in params], torch.float32),
-                                    self._dev([p.min_p for p in params], torch.float32),
+            kernels.sample_filtered(out, logits, temp, seed, step, i[1], f[1], f[2],
                                     None if len(filtered) == rows else self._dev(filtered, torch.int32))
         return out
