@@ -89,7 +89,6 @@ class ModelRunner:
         # CUDA graphs of decode steps
         self.enforce_eager = enforce_eager
         self.max_graph_batch = max_num_seqs
-        self.static_blocks = (self.max_model_len + block_size - 1) // block_size
         self.graph_safe = all(getattr(part, "graph_safe", False) for part, _ in model.parts_with_specs())
         self._graphs = {}
         self._seen_sizes = set()
@@ -258,10 +257,12 @@ class ModelRunner:
         the pair is seen); the returned tensor is then a view
         of the graph's own output buffer and holds its values until the next step of the same size."""
         graph_mode = self._graph_eligible(entries)
-        hb = self._prepare(entries, mgr, self.static_blocks if graph_mode else None,
+        bucket = self.graph_context_bucket(max(mgr.num_tokens(e.request_id) + 1 for e in entries)) if graph_mode else 0
+        # a graph's block tables are as wide as its bucket of context lengths needs, not as the longest context allowed
+        hb = self._prepare(entries, mgr, (bucket + self.block_size - 1) // self.block_size if graph_mode else None,
                            self.graph_batch_size(len(entries)) if graph_mode else 0)
         self.storage.zero_state_slots(mgr.take_fresh_slots())
-        key = (hb.S, self.graph_context_bucket(max(hb.ctx_lens))) if graph_mode else None
+        key = (hb.S, bucket) if graph_mode else None
         if graph_mode and (key in self._graphs or key in self._seen_sizes):
             logits = self._replay(hb, key, pending_tokens)
         else:
