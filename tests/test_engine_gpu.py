@@ -248,3 +248,34 @@ def test_random_workloads_through_the_engine(seed):
         assert results[i] == ref, (i, len(prompts[i]), gens[i], sps[i].temperature)
     eng.cache.check_invariants()
     assert eng.cache.num_free_pages() == pages
+
+
+def test_penalties_give_the_same_tokens_with_and_without_overlap():
+    """A batch with penalties retires the batch before it between its model step and its sampling; the tokens must be
+    those of steps that run strictly in order, also when requests stop early, arrive late and pages are scarce."""
+    from lmsf_b200 import EngineArgs, LLMEngine, SamplingParams
+    name = "A"
+    cfgd, bs = util.CONFIGS[name], util.BLOCK_SIZE[name]
+    folder = util.model_folder(name, "float32", 0.15)
+    prompts = [util.random_ids(n, cfgd["vocab_size"], 300 + i) for i, n in enumerate([12, 40, 7, 33, 21, 5])]
+    sps = [SamplingParams(temperature=0.9 if i % 3 else 0.0, seed=40 + i, max_tokens=10 + 4 * i, top_k=20 if i % 2 else -1,
+                          presence_penalty=0.3 if i != 2 else 0.0, frequency_penalty=0.2, repetition_penalty=1.2,
+                          stop_token_ids=[3, 17, 41, 77, 100, 150]) for i in range(len(prompts))]
+    got = {}
+    for no_async in (True, False):
+        eng = LLMEngine(EngineArgs(model=folder, dtype="float32", block_size=bs, num_gpu_blocks=14, max_num_batched_tokens=32,
+                                   max_num_seqs=4, max_model_len=120, no_async_scheduling=no_async))
+        res, step, nxt = {}, 0, 0
+        while nxt < len(prompts) or eng.has_unfinished_requests():
+            if nxt < len(prompts) and step % 3 == 0:
+                eng.add_request(nxt, None, sps[nxt], prompt_token_ids=prompts[nxt])
+                nxt += 1
+            for o in eng.step():
+                if o.finished:
+                    res[o.request_id] = (o.outputs[0].token_ids, o.outputs[0].finish_reason)
+            step += 1
+            assert step < 2000
+        eng.cache.check_invariants()
+        assert eng.cache.num_free_pages() == 14
+        got[no_async] = res
+    assert got[True] == got[False]
