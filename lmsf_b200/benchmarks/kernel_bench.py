@@ -195,9 +195,48 @@ def bench_sampling(args, dev, timer, pk):
                 greedy_gbs=nbytes / t0 / 1e9, frac_hbm=nbytes / t0 / 1e9 / pk["hbm_gbs"])
 
 
+def bench_sampling_filtered(args, dev, timer, pk):
+    """Top-k 50 and top-p 0.9 over logits that are peaked like a trained model's (a few large values per row)."""
+    from lmsf_b200 import kernels
+    rows, V = args.batch, args.vocab
+    logits = torch.randn(rows, V, device=dev)
+    logits[:, :64] += torch.linspace(12.0, 4.0, 64, device=dev)
+    out = torch.empty(rows, dtype=torch.int32, device=dev)
+    temp = torch.full((rows,), 0.8, device=dev)
+    seed = torch.arange(rows, dtype=torch.int64, device=dev)
+    step = torch.zeros(rows, dtype=torch.int32, device=dev)
+    top_k = torch.full((rows,), 50, dtype=torch.int32, device=dev)
+    top_p = torch.full((rows,), 0.9, device=dev)
+    min_p = torch.zeros(rows, device=dev)
+    t = timer.run(lambda: kernels.sample_filtered(out, logits, temp, seed, step, top_k, top_p, min_p), args.warmup, args.iters)
+    t_p = timer.run(lambda: kernels.sample_filtered(out, logits, temp, seed, step, None, top_p, None), args.warmup, args.iters)
+    return dict(kernel="sample_filtered", rows=rows, vocab=V, top_k_top_p_us=t * 1e6, top_p_only_us=t_p * 1e6)
+
+
+def bench_gemm_skinny_qkv(args, dev, timer, pk):
+    """The merged q/k/v product of a decode step with the rotary encoding and the cache write in its epilogue."""
+    from lmsf_b200 import kernels
+    M, K, nh, nkv, hd, bs = args.m, args.hidden, args.heads, args.kv_heads, args.head_dim, args.block_size
+    x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+    w = torch.randn((nh + 2 * nkv) * hd, K, device=dev, dtype=torch.bfloat16) * 0.02
+    q = torch.empty(M, nh * hd, device=dev, dtype=torch.bfloat16)
+    cache = torch.zeros(M + 1, 2, nkv, bs, hd, device=dev, dtype=torch.bfloat16)
+    bt = torch.arange(M, dtype=torch.int32, device=dev).view(M, 1)
+    pos = torch.arange(M, dtype=torch.int32, device=dev) % bs
+    seq = torch.arange(M, dtype=torch.int32, device=dev)
+    inv = torch.tensor([500000.0 ** (-(2.0 * i) / hd) for i in range(hd // 2)], dtype=torch.float32, device=dev)
+    flag = kernels.error_word(dev)
+    fn = lambda: kernels.gemm_skinny_qkv_rope(q, x, w, pos, seq, bt, bs, cache, inv, hd, True, nh, nkv, hd, flag)
+    t = timer.run(fn, args.warmup, args.iters)
+    nbytes = 2 * (M * K + w.numel() + M * (nh + 2 * nkv) * hd)
+    return dict(kernel="gemm_skinny_qkv_rope", m=M, n=w.shape[0], k=K, us=t * 1e6, gbs=nbytes / t / 1e9,
+                frac_hbm=nbytes / t / 1e9 / pk["hbm_gbs"])
+
+
 BENCHES = {"decode_attention": bench_decode_attention, "prefill_attention": bench_prefill_attention,
            "add_rmsnorm": bench_rmsnorm, "gated_act": bench_gated_act, "rope_cache_write": bench_rope_cache,
-           "gemm": bench_gemm, "gemm_skinny": bench_gemm_skinny, "gemm_stream": bench_gemm_stream, "sampling": bench_sampling}
+           "gemm": bench_gemm, "gemm_skinny": bench_gemm_skinny, "gemm_stream": bench_gemm_stream, "sampling": bench_sampling, "sampling_filtered": bench_sampling_filtered,
+           "gemm_skinny_qkv": bench_gemm_skinny_qkv}
 
 
 def main() -> int:

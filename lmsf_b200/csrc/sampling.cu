@@ -187,13 +187,14 @@ __device__ __forceinline__ unsigned long long block_sum_u64(unsigned long long v
 constexpr int kSelBits = 6;                  // key bits settled per pass over the row
 constexpr int kSelBins = 1 << kSelBits;
 constexpr float kMassOne = 1099511627776.0f; // 2^40: probabilities relative to the largest are summed as integers
+constexpr int kCompact = 2048;                // what top-k keeps moves to shared memory when it is at most this many values
 
-// One pass of the selection: among the row's values whose key is at least `key_floor` and whose bits above
+// One pass of the selection: among the values that `scan` visits whose key is at least `key_floor` and whose bits above
 // (shift + width) equal `prefix`, how many fall into each value of the next `width` bits and (MASS) how much
 // probability, as integers, so that the sums do not depend on the order.  Each warp counts into bins of its
 // own (lanes of one warp may meet in a bin, warps never), then the warps' bins are added.
-template <bool MASS>
-__device__ __forceinline__ void select_pass(const float* __restrict__ row, int vocab, float invT, float m, uint32_t key_floor,
+template <bool MASS, typename Scan>
+__device__ __forceinline__ void select_pass(Scan scan, float invT, float m, uint32_t key_floor,
                                             uint32_t prefix, int shift, int width, unsigned (*w_cnt)[kSelBins],
                                             unsigned long long (*w_mass)[kSelBins], unsigned* cnt, unsigned long long* mass) {
   const int warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
@@ -214,7 +215,7 @@ __device__ __forceinline__ void select_pass(const float* __restrict__ row, int v
     atomicAdd(&w_cnt[warp][run_d], run_c);
     if (MASS) atomicAdd(&w_mass[warp][run_d], run_m);
   };
-  for_each_value(row, vocab, [&](int, float x) {
+  scan([&](int, float x) {
     const float z = x * invT;
     if (z != z) return;
     const uint32_t key = float_key(z);
@@ -255,7 +256,8 @@ __device__ __forceinline__ void select_pass(const float* __restrict__ row, int v
 // A value's order-preserving 32-bit key is settled six bits per pass over the row (six passes for a threshold
 // instead of the 32 of a bisection): the pass counts, for every value of the next six bits, the values (and their
 // probability) under the prefix found so far.  Counts and probabilities are integers, so the kept set, and with
-// it the draw, is reproducible.
+// it the draw, is reproducible.  When top-k leaves at most kCompact values they move to shared memory, and the top-p
+// passes and the draw visit only those.
 __global__ void __launch_bounds__(1024) sample_filtered_kernel(int* __restrict__ out, const float* __restrict__ logits, long long row_stride,
                                        int vocab, const float* __restrict__ temperature,
                                        const unsigned long long* __restrict__ seed, const int* __restrict__ step,
@@ -268,6 +270,9 @@ __global__ void __launch_bounds__(1024) sample_filtered_kernel(int* __restrict__
   __shared__ unsigned long long w_mass[32][kSelBins];
   __shared__ unsigned cnt[kSelBins];
   __shared__ unsigned long long mass[kSelBins];
+  __shared__ float c_val[kCompact];          // the values that top-k keeps, when they are few, and their places
+  __shared__ int c_idx[kCompact];
+  __shared__ int c_n;
   const int r = row_ids ? row_ids[blockIdx.x] : blockIdx.x;
   const float* row = logits + (size_t)r * row_stride;
   const float T = temperature[r];
@@ -283,14 +288,24 @@ __global__ void __launch_bounds__(1024) sample_filtered_kernel(int* __restrict__
   });
   m = block_max_f(m, scratch);
 
+  // what the later passes visit: the whole row, or (after top-k has left few values) those values in shared memory
+  bool compact = false;
+  auto scan = [&](auto f) {
+    if (compact) {
+      for (int i = threadIdx.x; i < c_n; i += blockDim.x) f(c_idx[i], c_val[i]);
+    } else {
+      for_each_value(row, vocab, f);
+    }
+  };
   uint32_t key_min = 0u;                     // tokens with key >= key_min are kept
   if (k > 0 && k < vocab) {                  // the key of the k-th largest value
     uint32_t prefix = 0u;
     unsigned above = 0u;                     // values whose settled bits are larger than the prefix's
+    unsigned kept = 0u;                      // values with key >= the prefix (at the end: what top-k keeps)
     bool enough = true;
     for (int shift = 32 - kSelBits; enough; shift = shift >= kSelBits ? shift - kSelBits : 0) {
       const int width = shift == 0 && (32 % kSelBits) ? 32 % kSelBits : kSelBits;
-      select_pass<false>(row, vocab, invT, m, 0u, prefix, shift, width, w_cnt, w_mass, cnt, mass);
+      select_pass<false>(scan, invT, m, 0u, prefix, shift, width, w_cnt, w_mass, cnt, mass);
       unsigned c = above;
       int d = (1 << width) - 1;
       for (; d >= 0; --d) {
@@ -299,14 +314,32 @@ __global__ void __launch_bounds__(1024) sample_filtered_kernel(int* __restrict__
       }
       if (d < 0) { enough = false; break; }  // fewer than k values in all: everything is kept
       above = c;
+      kept = c + cnt[d];
       prefix = (prefix << width) | (uint32_t)d;
       if (shift == 0) break;
     }
     key_min = enough ? prefix : 0u;
+    if (enough && kept <= (unsigned)kCompact) {
+      // the kept values move to shared memory (in any order: what follows sums integers and breaks ties by place)
+      if (threadIdx.x == 0) c_n = 0;
+      __syncthreads();
+      for_each_value(row, vocab, [&](int v, float x) {
+        const float z = x * invT;
+        if (z == z && float_key(z) >= key_min) {
+          const int i = atomicAdd(&c_n, 1);
+          if (i < kCompact) {
+            c_val[i] = x;
+            c_idx[i] = v;
+          }
+        }
+      });
+      __syncthreads();
+      compact = true;
+    }
   }
   if (p < 1.0f) {
     unsigned long long Z = 0ull;
-    for_each_value(row, vocab, [&](int, float x) {
+    scan([&](int, float x) {
       const float z = x * invT;
       if (z == z && float_key(z) >= key_min) Z += (unsigned long long)(expf(z - m) * kMassOne);
     });
@@ -317,7 +350,7 @@ __global__ void __launch_bounds__(1024) sample_filtered_kernel(int* __restrict__
     unsigned long long above = 0ull;         // probability of the values whose settled bits are larger than the prefix's
     for (int shift = 32 - kSelBits;; shift = shift >= kSelBits ? shift - kSelBits : 0) {
       const int width = shift == 0 && (32 % kSelBits) ? 32 % kSelBits : kSelBits;
-      select_pass<true>(row, vocab, invT, m, key_min, prefix, shift, width, w_cnt, w_mass, cnt, mass);
+      select_pass<true>(scan, invT, m, key_min, prefix, shift, width, w_cnt, w_mass, cnt, mass);
       unsigned long long a_run = above, a_best = above;
       int best = -1;
       for (int d = (1 << width) - 1; d >= 0; --d) {
@@ -341,7 +374,7 @@ __global__ void __launch_bounds__(1024) sample_filtered_kernel(int* __restrict__
   const uint32_t slo = (uint32_t)(seed[r] & 0xffffffffull), shi = (uint32_t)(seed[r] >> 32);
   const uint32_t st = (uint32_t)step[r];
   Best b{-INFINITY, 0x7fffffff};
-  for_each_value(row, vocab, [&](int v, float x) {
+  scan([&](int v, float x) {
     const float z = x * invT;
     if (z != z || float_key(z) < key_min) return;
     b = better(b, Best{(double)x / (double)T + neg_log_exponential(slo, shi, st, (uint32_t)v), v});
