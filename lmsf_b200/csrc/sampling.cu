@@ -151,24 +151,24 @@ __device__ __forceinline__ float block_max_f(float v, float* scratch) {
   return scratch[32];
 }
 
-// Calls f(index, value) for every value of the row, the block's threads sharing the work; 16 bytes per load when the
+// Calls f(base + index, value) for every value of the row, the block's threads sharing the work; 16 bytes per load when the
 // row is aligned (a thread with one 4-byte load in flight at a time would wait for L2 most of the time).
 template <typename F>
-__device__ __forceinline__ void for_each_value(const float* __restrict__ row, int vocab, F f) {
+__device__ __forceinline__ void for_each_value(const float* __restrict__ row, int vocab, F f, int base = 0) {
   if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
     const int n4 = vocab >> 2;
     const float4* r4 = reinterpret_cast<const float4*>(row);
 #pragma unroll 2
     for (int i = threadIdx.x; i < n4; i += blockDim.x) {
       const float4 x = r4[i];
-      f(4 * i, x.x);
-      f(4 * i + 1, x.y);
-      f(4 * i + 2, x.z);
-      f(4 * i + 3, x.w);
+      f(base + 4 * i, x.x);
+      f(base + 4 * i + 1, x.y);
+      f(base + 4 * i + 2, x.z);
+      f(base + 4 * i + 3, x.w);
     }
-    for (int v = (n4 << 2) + threadIdx.x; v < vocab; v += blockDim.x) f(v, row[v]);
+    for (int v = (n4 << 2) + threadIdx.x; v < vocab; v += blockDim.x) f(base + v, row[v]);
   } else {
-    for (int v = threadIdx.x; v < vocab; v += blockDim.x) f(v, row[v]);
+    for (int v = threadIdx.x; v < vocab; v += blockDim.x) f(base + v, row[v]);
   }
 }
 
@@ -184,6 +184,27 @@ __device__ __forceinline__ unsigned long long block_sum_u64(unsigned long long v
   return t;
 }
 
+// A row may be shared by the blocks of a thread-block cluster (gridDim.x of them, each with its share of the
+// vocabulary); what they count is exchanged through their shared memory.
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_addr(const void* local, unsigned rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(local)), "r"(rank));
+  return remote;
+}
+__device__ __forceinline__ unsigned ld_cluster_u32(const unsigned* local, unsigned rank) {
+  unsigned v;
+  asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(cluster_addr(local, rank)) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned long long ld_cluster_u64(const unsigned long long* local, unsigned rank) {
+  unsigned long long v;
+  asm volatile("ld.shared::cluster.u64 %0, [%1];" : "=l"(v) : "r"(cluster_addr(local, rank)) : "memory");
+  return v;
+}
+
 constexpr int kSelBits = 6;                  // key bits settled per pass over the row
 constexpr int kSelBins = 1 << kSelBits;
 constexpr float kMassOne = 1099511627776.0f; // 2^40: probabilities relative to the largest are summed as integers
@@ -196,7 +217,8 @@ constexpr int kCompact = 2048;                // what top-k keeps moves to share
 template <bool MASS, typename Scan>
 __device__ __forceinline__ void select_pass(Scan scan, float invT, float m, uint32_t key_floor,
                                             uint32_t prefix, int shift, int width, unsigned (*w_cnt)[kSelBins],
-                                            unsigned long long (*w_mass)[kSelBins], unsigned* cnt, unsigned long long* mass) {
+                                            unsigned long long (*w_mass)[kSelBins], unsigned* cnt, unsigned long long* mass,
+                                            unsigned (*x_cnt)[kSelBins], unsigned long long (*x_mass)[kSelBins], int& phase) {
   const int warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
   for (int i = threadIdx.x; i < nwarps * kSelBins; i += blockDim.x) {
     w_cnt[0][i] = 0u;
@@ -233,6 +255,7 @@ __device__ __forceinline__ void select_pass(Scan scan, float invT, float m, uint
   });
   flush();
   __syncthreads();
+  const int R = gridDim.x, par = phase & 1;
   if (threadIdx.x < kSelBins) {
     unsigned c = 0u;
     unsigned long long ms = 0ull;
@@ -240,13 +263,35 @@ __device__ __forceinline__ void select_pass(Scan scan, float invT, float m, uint
       c += w_cnt[w][threadIdx.x];
       if (MASS) ms += w_mass[w][threadIdx.x];
     }
-    cnt[threadIdx.x] = c;
-    if (MASS) mass[threadIdx.x] = ms;
+    if (R == 1) {
+      cnt[threadIdx.x] = c;
+      if (MASS) mass[threadIdx.x] = ms;
+    } else {
+      x_cnt[par][threadIdx.x] = c;
+      if (MASS) x_mass[par][threadIdx.x] = ms;
+    }
+  }
+  if (R > 1) {
+    // The blocks' bins are added by every block (integers: the same totals everywhere).  The exchange arrays
+    // alternate from pass to pass, so a block that is ahead does not write what a block behind still reads.
+    cluster_sync_all();
+    if (threadIdx.x < kSelBins) {
+      unsigned c = 0u;
+      unsigned long long ms = 0ull;
+      for (int q = 0; q < R; ++q) {
+        c += ld_cluster_u32(&x_cnt[par][threadIdx.x], (unsigned)q);
+        if (MASS) ms += ld_cluster_u64(&x_mass[par][threadIdx.x], (unsigned)q);
+      }
+      cnt[threadIdx.x] = c;
+      if (MASS) mass[threadIdx.x] = ms;
+    }
+    ++phase;
   }
   __syncthreads();
 }
 
-// Temperature sampling with top-k, top-p and min-p, one block per row.  With z = logits / T:
+// Temperature sampling with top-k, top-p and min-p; a row is served by the blocks of one thread-block cluster
+// (gridDim.x of them, one when there are many rows).  With z = logits / T:
 //   top-k keeps the k largest z (ties at the k-th value are all kept);
 //   top-p keeps a token iff the probability mass of the strictly larger kept tokens is < p
 //         (the reference removes the ascending prefix whose cumulative mass is <= 1 - p,
@@ -273,8 +318,16 @@ __global__ void __launch_bounds__(1024) sample_filtered_kernel(int* __restrict__
   __shared__ float c_val[kCompact];          // the values that top-k keeps, when they are few, and their places
   __shared__ int c_idx[kCompact];
   __shared__ int c_n;
-  const int r = row_ids ? row_ids[blockIdx.x] : blockIdx.x;
-  const float* row = logits + (size_t)r * row_stride;
+  __shared__ unsigned x_cnt[2][kSelBins];    // what the blocks of a cluster exchange, alternating from one exchange to the next
+  __shared__ unsigned long long x_mass[2][kSelBins];
+  __shared__ unsigned long long x_scalar[2][2];
+  const int r = row_ids ? row_ids[blockIdx.y] : blockIdx.y;
+  const int R = gridDim.x, rank = blockIdx.x;                    // the blocks that share the row, and this one among them
+  int phase = 0;                             // exchanges so far (the same in every block of the cluster)
+  const int per = (((vocab + R - 1) / R) + 3) & ~3;             // a share starts at a multiple of 4 values
+  const int v0 = min(vocab, rank * per), n_mine = min(vocab, v0 + per) - v0;
+  const float* row_all = logits + (size_t)r * row_stride;
+  const float* row = row_all + v0;           // this block's share of the row
   const float T = temperature[r];
   const float invT = 1.0f / T;
   const int k = top_k ? top_k[r] : -1;
@@ -282,11 +335,17 @@ __global__ void __launch_bounds__(1024) sample_filtered_kernel(int* __restrict__
   const float mp = min_p ? min_p[r] : 0.0f;
 
   float m = -INFINITY;
-  for_each_value(row, vocab, [&](int, float x) {
+  for_each_value(row, n_mine, [&](int, float x) {
     const float z = x * invT;
     if (z == z) m = fmaxf(m, z);
   });
   m = block_max_f(m, scratch);
+  if (R > 1) {
+    if (threadIdx.x == 0) x_scalar[phase & 1][0] = (unsigned long long)__float_as_uint(m);
+    cluster_sync_all();
+    for (int q = 0; q < R; ++q) m = fmaxf(m, __uint_as_float((unsigned)ld_cluster_u64(&x_scalar[phase & 1][0], (unsigned)q)));
+    ++phase;
+  }
 
   // what the later passes visit: the whole row, or (after top-k has left few values) those values in shared memory
   bool compact = false;
@@ -294,7 +353,7 @@ __global__ void __launch_bounds__(1024) sample_filtered_kernel(int* __restrict__
     if (compact) {
       for (int i = threadIdx.x; i < c_n; i += blockDim.x) f(c_idx[i], c_val[i]);
     } else {
-      for_each_value(row, vocab, f);
+      for_each_value(row, n_mine, f, v0);
     }
   };
   uint32_t key_min = 0u;                     // tokens with key >= key_min are kept
@@ -305,7 +364,7 @@ __global__ void __launch_bounds__(1024) sample_filtered_kernel(int* __restrict__
     bool enough = true;
     for (int shift = 32 - kSelBits; enough; shift = shift >= kSelBits ? shift - kSelBits : 0) {
       const int width = shift == 0 && (32 % kSelBits) ? 32 % kSelBits : kSelBits;
-      select_pass<false>(scan, invT, m, 0u, prefix, shift, width, w_cnt, w_mass, cnt, mass);
+      select_pass<false>(scan, invT, m, 0u, prefix, shift, width, w_cnt, w_mass, cnt, mass, x_cnt, x_mass, phase);
       unsigned c = above;
       int d = (1 << width) - 1;
       for (; d >= 0; --d) {
@@ -323,7 +382,7 @@ __global__ void __launch_bounds__(1024) sample_filtered_kernel(int* __restrict__
       // the kept values move to shared memory (in any order: what follows sums integers and breaks ties by place)
       if (threadIdx.x == 0) c_n = 0;
       __syncthreads();
-      for_each_value(row, vocab, [&](int v, float x) {
+      for_each_value(row, n_mine, [&](int v, float x) {
         const float z = x * invT;
         if (z == z && float_key(z) >= key_min) {
           const int i = atomicAdd(&c_n, 1);
@@ -332,7 +391,7 @@ __global__ void __launch_bounds__(1024) sample_filtered_kernel(int* __restrict__
             c_idx[i] = v;
           }
         }
-      });
+      }, v0);
       __syncthreads();
       compact = true;
     }
@@ -344,13 +403,20 @@ __global__ void __launch_bounds__(1024) sample_filtered_kernel(int* __restrict__
       if (z == z && float_key(z) >= key_min) Z += (unsigned long long)(expf(z - m) * kMassOne);
     });
     Z = block_sum_u64(Z, scratch64);
+    if (R > 1) {
+      if (threadIdx.x == 0) x_scalar[phase & 1][0] = Z;
+      cluster_sync_all();
+      Z = 0ull;
+      for (int q = 0; q < R; ++q) Z += ld_cluster_u64(&x_scalar[phase & 1][0], (unsigned)q);
+      ++phase;
+    }
     const unsigned long long target = (unsigned long long)((double)p * (double)Z);   // kept iff mass of strictly larger keys < p * Z
     // the smallest key of a kept token: the lowest value that still has less than the target above it
     uint32_t prefix = 0u;
     unsigned long long above = 0ull;         // probability of the values whose settled bits are larger than the prefix's
     for (int shift = 32 - kSelBits;; shift = shift >= kSelBits ? shift - kSelBits : 0) {
       const int width = shift == 0 && (32 % kSelBits) ? 32 % kSelBits : kSelBits;
-      select_pass<true>(scan, invT, m, key_min, prefix, shift, width, w_cnt, w_mass, cnt, mass);
+      select_pass<true>(scan, invT, m, key_min, prefix, shift, width, w_cnt, w_mass, cnt, mass, x_cnt, x_mass, phase);
       unsigned long long a_run = above, a_best = above;
       int best = -1;
       for (int d = (1 << width) - 1; d >= 0; --d) {
@@ -394,7 +460,27 @@ __global__ void __launch_bounds__(1024) sample_filtered_kernel(int* __restrict__
       Best other{__shfl_xor_sync(0xffffffffu, b.score, o), __shfl_xor_sync(0xffffffffu, b.index, o)};
       b = better(b, other);
     }
-    if (lane == 0) out[r] = b.index == 0x7fffffff ? 0 : b.index;
+    if (lane == 0) {
+      if (R == 1) {
+        out[r] = b.index == 0x7fffffff ? 0 : b.index;
+      } else {
+        x_scalar[phase & 1][0] = (unsigned long long)__double_as_longlong(b.score);
+        x_scalar[phase & 1][1] = (unsigned long long)(unsigned)b.index;
+      }
+    }
+  }
+  if (R > 1) {
+    cluster_sync_all();
+    if (rank == 0 && threadIdx.x == 0) {     // the blocks' winners meet in the first block
+      Best w{-INFINITY, 0x7fffffff};
+      for (int q = 0; q < R; ++q) {
+        const Best o{__longlong_as_double((long long)ld_cluster_u64(&x_scalar[phase & 1][0], (unsigned)q)),
+                     (int)(unsigned)ld_cluster_u64(&x_scalar[phase & 1][1], (unsigned)q)};
+        w = better(w, o);
+      }
+      out[r] = w.index == 0x7fffffff ? 0 : w.index;
+    }
+    cluster_sync_all();                      // no block leaves while the first one still reads its shared memory
   }
 }
 
@@ -443,7 +529,28 @@ LMSF_API int lmsf_sample_filtered(int* out, const float* logits, long long row_s
   if (rows <= 0) return 0;
   if (vocab <= 0 || row_stride < vocab) LMSF_REFUSE("sample_filtered: vocab=%d, row_stride=%lld", vocab, row_stride);
   if (!temperature || !seed || !step) LMSF_REFUSE("sample_filtered: temperature, seed and step are needed");
-  sample_filtered_kernel<<<rows, 1024, 0, (cudaStream_t)stream>>>(out, logits, row_stride, vocab, temperature, seed,
-                                                                  step, top_k, top_p, min_p, row_ids);
-  return LMSF_LAUNCH_STATUS();
+  // A row is shared by as many blocks (a thread-block cluster, at most 8) as leaves every row its blocks at once.
+  static int n_sms = 0;
+  if (n_sms == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+      n_sms = 1;
+  }
+  int share = n_sms / rows;
+  share = share < 1 ? 1 : share > 8 ? 8 : share;
+  if (vocab < 4096 * share) share = vocab < 8192 ? 1 : vocab / 4096;      // a share is at least 4096 values
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)share, (unsigned)rows, 1);
+  cfg.blockDim = dim3(1024);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)share;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return (int)cudaLaunchKernelEx(&cfg, sample_filtered_kernel, out, logits, row_stride, vocab, temperature, seed, step, top_k,
+                                 top_p, min_p, row_ids);
 }
