@@ -529,6 +529,7 @@ LMSF_API int lmsf_sample_filtered(int* out, const float* logits, long long row_s
   if (rows <= 0) return 0;
   if (vocab <= 0 || row_stride < vocab) LMSF_REFUSE("sample_filtered: vocab=%d, row_stride=%lld", vocab, row_stride);
   if (!temperature || !seed || !step) LMSF_REFUSE("sample_filtered: temperature, seed and step are needed");
+  if (rows > 65535) LMSF_REFUSE("sample_filtered: %d rows are more than one launch takes (65535)", rows);
   // A row is shared by as many blocks (a thread-block cluster, at most 8) as leaves every row its blocks at once.
   static int n_sms = 0;
   if (n_sms == 0) {
