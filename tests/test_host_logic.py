@@ -59,3 +59,25 @@ def test_token_history_counts_like_a_recount():
         t, c = h.update(out[:3])              # the output was cut back (never happens in the engine): counted again
         assert dict(zip(t.tolist(), c.tolist())) == {tok: Counter(out[:3]).get(tok, 0) for tok in set(prompt) | set(out)}
         assert t.dtype == np.int32 and c.dtype == np.int32
+
+
+def test_histories_go_with_their_requests():
+    import gc
+    import torch
+    from lmsf_b200.engine.sequence import Sequence
+    from lmsf_b200.sampling.params import SamplingParams
+    from lmsf_b200.sampling.sampler import Sampler
+    sampler = Sampler(torch.device("cpu"))
+    a = Sequence("a", [3, 4, 4], SamplingParams(presence_penalty=0.5))
+    b = Sequence("b", [9], SamplingParams(presence_penalty=0.5))
+    ha = sampler._history(a)
+    assert sampler._history(a) is ha and sampler._history(b) is not ha and len(sampler._histories) == 2
+    del a, ha
+    gc.collect()
+    assert len(sampler._histories) == 1       # the entry went with the request object
+    class Plain:                              # an object without weak references: served, but nothing is kept
+        __slots__ = ("prompt_token_ids", "output_token_ids")
+    p = Plain()
+    p.prompt_token_ids, p.output_token_ids = [1, 2], [2]
+    t, c = sampler._history(p).update(p.output_token_ids)
+    assert dict(zip(t.tolist(), c.tolist())) == {1: 0, 2: 1} and len(sampler._histories) == 1
