@@ -103,6 +103,24 @@ class Scheduler:
                 return False
         return True
 
+    def _portion_that_fits(self, seq: Sequence, n: int) -> int:
+        """A portion's pages are all held until its step is over, also those that a window will give back right
+        after it: a portion of n tokens that needs more pages than a windowed group has can never run, however many
+        other requests are preempted.  Such a portion is halved until the pages it adds, beside those the request
+        holds, fit the group; the rest of the prompt follows in the next steps, when the window has moved on."""
+        if all(spec.window is None for spec in self.cache.groups):
+            return n
+        rid = seq.request_id
+        windowed = [g for g, spec in enumerate(self.cache.groups) if spec.window is not None]
+        need = self.cache.pages_needed(rid, n)
+        if all(need[g] <= self.cache.num_free_pages(g) for g in windowed):
+            return n                        # the usual case: the pages are there right now
+        held = {g: sum(1 for p in self.cache.block_table(rid, g) if p >= 0) for g in windowed}
+        while n > 1 and not all(need[g] + held[g] <= self.cache.num_total_pages(g) for g in windowed):
+            n = max(1, n // 2)
+            need = self.cache.pages_needed(rid, n)
+        return n
+
     def _preempt(self, seq: Sequence, out: SchedulerOutputs) -> None:
         self.running.remove(seq)
         self._release(seq)
@@ -125,7 +143,7 @@ class Scheduler:
             if seq.hold or seq.num_uncomputed <= 0:      # waits for a token that is still on the device
                 i += 1
                 continue
-            n = min(seq.num_uncomputed, budget)
+            n = self._portion_that_fits(seq, min(seq.num_uncomputed, budget))
             if seq.num_pending > 1 or (seq.num_pending and n < seq.num_uncomputed):
                 # only the newest pending token can be taken from the device, and only as a portion's last token
                 i += 1
@@ -166,8 +184,8 @@ class Scheduler:
                 continue
             if len(self.running) >= self.config.max_num_seqs or not self.cache.can_add():
                 break
-            n = min(seq.num_uncomputed, budget)
             self.cache.add(seq.request_id)
+            n = self._portion_that_fits(seq, min(seq.num_uncomputed, budget))
             need = self.cache.pages_needed(seq.request_id, n)
             idle = not self.running          # an empty engine admits its first request without a watermark
             if any(self.cache.num_free_pages(g) - k < (0 if idle else self.watermark_pages[g])

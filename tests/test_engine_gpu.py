@@ -279,3 +279,19 @@ def test_penalties_give_the_same_tokens_with_and_without_overlap():
         assert eng.cache.num_free_pages() == 14
         got[no_async] = res
     assert got[True] == got[False]
+
+
+def test_a_windowed_prompt_longer_than_the_cache_runs_in_portions():
+    """Sliding window of 24 keys, 4 pages of 16 tokens: a 90-token prompt cannot hold its pages all at once, so the
+    scheduler cuts it to what the pages hold and the window gives pages back between the portions."""
+    from lmsf_b200 import SamplingParams
+    name = "W"
+    cfg, w = P.load_model(util.model_folder(name, "float32", 0.15))
+    prompts = [util.random_ids(90, cfg["vocab_size"], 61), util.random_ids(50, cfg["vocab_size"], 62)]
+    llm = _llm(name, "float32", num_gpu_blocks=4, max_num_batched_tokens=256, max_num_seqs=2, max_model_len=120)
+    outs = llm.generate(prompt_token_ids=prompts, sampling_params=SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        ref, _ = P.generate(cfg, w, p, 8)
+        assert o.outputs[0].token_ids == ref
+    llm.engine.cache.check_invariants()
+    assert llm.engine.cache.num_free_pages() == 4

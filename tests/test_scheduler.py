@@ -162,3 +162,49 @@ def test_random_workloads_finish_and_lose_no_page():
             steps += 1
             assert steps < 2000
         assert len(done) == 12 and all(p.num_free == p.num_blocks for p in cache.pools)
+
+
+def test_a_windowed_prompt_longer_than_the_cache_is_cut_to_what_the_pages_hold():
+    """6 pages of 4 tokens and a window of 4: a 30-token prompt never holds more than a few pages once it runs, but a
+    portion's pages are all held until its step is over.  The portion is cut to what fits (it used to wait for ever),
+    and the rest follows as the window gives pages back."""
+    sched, cache = make(pages=6, bs=4, budget=200, max_seqs=3, max_len=64, window=4)
+    a = seq(0, 30, 0.0, max_tokens=5)
+    sched.add_seq(a)
+    done, steps, portions = [], 0, []
+    while sched.has_unfinished_seqs():
+        out = sched.schedule()
+        assert out.entries, "the request must make progress in every step"
+        portions.append(out.entries[0].num_tokens)
+        done += run_step(sched, cache, out)
+        cache.check_invariants()
+        steps += 1
+        assert steps < 100
+    assert portions[0] < 30 and sum(portions[:portions.index(1)]) == 30     # the prompt in several portions, then single tokens
+    assert done == [a] and len(a.output_token_ids) == 5
+    assert all(p.num_free == p.num_blocks for p in cache.pools)
+
+
+def test_many_random_workloads_with_windows_aborts_and_late_arrivals():
+    for seed in range(300):
+        rng = random.Random(seed)
+        sched, cache = make(pages=rng.randint(4, 40), bs=rng.choice([1, 2, 4, 8, 16]), budget=rng.choice([1, 2, 8, 16, 48, 200]),
+                            max_seqs=rng.randint(1, 9), max_len=rng.choice([16, 64, 256]), window=rng.choice([None, None, 4, 12, 40]))
+        pending = [seq(i, rng.randint(1, 60), float(i), max_tokens=rng.randint(1, 30)) for i in range(rng.randint(1, 20))]
+        steps = 0
+        while pending or sched.has_unfinished_seqs():
+            for _ in range(rng.randint(0, 3)):
+                if pending:
+                    sched.add_seq(pending.pop(0))
+            if rng.random() < 0.03 and sched.running:
+                sched.abort_seq(rng.choice(sched.running).request_id)
+            if not sched.has_unfinished_seqs():
+                continue
+            out = sched.schedule()
+            assert out.num_batched_tokens <= sched.config.max_num_batched_tokens
+            assert out.entries or out.ignored or out.preempted, f"seed {seed}: a step in which nothing happens"
+            run_step(sched, cache, out)
+            cache.check_invariants()
+            steps += 1
+            assert steps < 5000, f"seed {seed}: no end"
+        assert all(p.num_free == p.num_blocks for p in cache.pools), f"seed {seed}: pages lost"
