@@ -70,6 +70,7 @@ class LLMEngine:
         self.scheduler = Scheduler(self.scheduler_config, self.cache)
         self.sampler = Sampler(self.device)
         self.eos_token_ids = set(self.model.spec.eos_token_ids)
+        self.vocab_size = self.model.spec.vocab_size
         self.tokenizer = self._load_tokenizer(args.model)
         self.seqs: Dict[Hashable, Sequence] = {}
         self.last_stats = StepStats()
@@ -78,6 +79,33 @@ class LLMEngine:
         self._inflight: Optional[_InFlight] = None
         self._result_ring = [None] * 4
         self._result_pos = 0
+
+    @classmethod
+    def from_parts(cls, runner, cache, scheduler_config: SchedulerConfig, sampler, vocab_size: int,
+                   eos_token_ids: Seq[int], max_model_len: int, async_scheduling: bool = True, seed: int = 0) -> "LLMEngine":
+        """An engine around a runner, a cache manager and a sampler that already exist (no model is loaded): the
+        host-side tests drive the scheduling, the overlapped steps and the stop rules this way with a stand-in
+        runner.  `runner` needs `step(entries, cache, check=, pending_tokens=)`, `error_flag` and
+        `check_device_errors()`; `sampler` needs `sample(...)` and `require_filters()`."""
+        eng = cls.__new__(cls)
+        eng.args = EngineArgs(model="", seed=seed)
+        eng.device = torch.device("cpu")
+        eng.model = eng.model_config = eng.dtype = None
+        eng.vocab_size = int(vocab_size)
+        eng.max_model_len = int(max_model_len)
+        eng.scheduler_config = scheduler_config
+        eng.runner, eng.cache, eng.sampler = runner, cache, sampler
+        eng.scheduler = Scheduler(scheduler_config, cache)
+        eng.eos_token_ids = set(eos_token_ids)
+        eng.tokenizer = None
+        eng.seqs = {}
+        eng.last_stats = StepStats()
+        eng._auto_id = 0
+        eng.async_scheduling = bool(async_scheduling)
+        eng._inflight = None
+        eng._result_ring = [None] * 4
+        eng._result_pos = 0
+        return eng
 
     @staticmethod
     def _load_tokenizer(model_dir: str):
@@ -102,7 +130,7 @@ class LLMEngine:
         ids = [int(t) for t in prompt_token_ids]
         if not ids:
             raise ValueError("a request needs at least one prompt token")
-        vocab = self.model.spec.vocab_size
+        vocab = self.vocab_size
         bad = [t for t in ids if not (0 <= t < vocab)]
         if bad:
             raise ValueError(f"prompt token ids {bad[:5]} are outside the vocabulary (0..{vocab - 1})")
@@ -217,7 +245,9 @@ class LLMEngine:
         self._result_pos = (self._result_pos + 1) % len(self._result_ring)
         buf = self._result_ring[self._result_pos]
         if buf is None or buf.numel() < n:
-            buf = self._result_ring[self._result_pos] = torch.empty(max(n, 512), dtype=torch.int32).pin_memory()
+            buf = self._result_ring[self._result_pos] = torch.empty(max(n, 512), dtype=torch.int32)
+            if self.device.type == "cuda":
+                buf = self._result_ring[self._result_pos] = buf.pin_memory()
         return buf
 
     def _retire(self, flight: Optional["_InFlight"], outputs: List[RequestOutput]) -> None:

@@ -85,9 +85,13 @@ class Scheduler:
         return len(self.waiting) + len(self.running)
 
     def free_seq(self, seq: Sequence) -> None:
-        """A finished request leaves the running queue and gives back what it holds."""
-        if seq in self.running:
-            self.running.remove(seq)
+        """A finished request leaves its queue and gives back what it holds.  It is usually running; it waits when
+        it was preempted while its last token was still on its way from the device and that token ended it."""
+        for q in (self.running, self.waiting):
+            for i, other in enumerate(q):
+                if other is seq:
+                    del q[i]
+                    break
         self._release(seq)
 
     def _release(self, seq: Sequence) -> None:
