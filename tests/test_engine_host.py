@@ -148,3 +148,43 @@ def test_a_request_that_ends_while_preempted_does_not_come_back():
     run_workload(337)
     run_workload(264)
     run_workload(391)
+
+
+def test_several_cache_groups_with_and_without_windows():
+    """Layers with different needs have page pools of their own: a request runs only when every group has its pages."""
+    for seed in range(200):
+        rng = random.Random(10_000 + seed)
+        bs = rng.choice([1, 2, 4, 8, 16])
+        windows = [rng.choice([None, 4, 12, 40]) for _ in range(rng.randint(2, 3))]
+        pages = [rng.randint(3, 40) for _ in windows]
+        max_len, max_seqs = rng.choice([16, 48, 128]), rng.randint(1, 8)
+        cache = CacheManager([GroupSpec(w) for w in windows], pages, bs, max_seqs)
+        eng = LLMEngine.from_parts(StandInRunner(max_len), cache, SchedulerConfig.new(rng.choice([1, 2, 8, 16, 48, 200]), max_seqs, max_len),
+                                   StandInSampler(), VOCAB, [EOS], max_len, async_scheduling=rng.random() < 0.7)
+        reqs = [([rng.randrange(VOCAB) for _ in range(rng.randint(1, 40))],
+                 SamplingParams(temperature=0.0, max_tokens=rng.randint(1, 25), ignore_eos=rng.random() < 0.5,
+                                stop_token_ids=[rng.randrange(VOCAB) for _ in range(rng.choice([0, 0, 3, 10]))]))
+                for _ in range(rng.randint(1, 14))]
+        pending, results, steps = list(range(len(reqs))), {}, 0
+        while pending or eng.has_unfinished_requests():
+            for _ in range(rng.randint(0, 3)):
+                if pending:
+                    i = pending.pop(0)
+                    eng.add_request(i, None, reqs[i][1], prompt_token_ids=reqs[i][0])
+            for o in eng.step():
+                if o.finished:
+                    assert o.request_id not in results
+                    results[o.request_id] = (list(o.outputs[0].token_ids), o.outputs[0].finish_reason)
+            cache.check_invariants()
+            steps += 1
+            assert steps < 6000, f"seed {seed}: no end"
+        assert all(cache.num_free_pages(g) == pages[g] for g in range(len(pages))), f"seed {seed}: pages lost"
+        for i, (prompt, sp) in enumerate(reqs):
+            want, got = expected(prompt, sp, max_len), results.get(i)
+            if got == (want[0], want[1]):
+                continue
+            total = len(prompt) + len(want[0])
+            too_large = len(prompt) > max_len or any((total if w is None else min(total, w + 2 * bs)) > pages[g] * bs - bs
+                                                     for g, w in enumerate(windows))
+            assert too_large and got is not None and got[1] in ("length", "ignored") and got[0] == want[0][:len(got[0])], \
+                f"seed {seed}: request {i} (prompt of {len(prompt)}) got {got}, the model gives {want}"
