@@ -148,8 +148,9 @@ def paged_attention(out, q, key_cache, value_cache, block_tables_i32, context_le
                     num_kv_heads, force=None, workspace=None):
     """Decode attention of one token per request, v1 or v2 chosen by the reference's own rule
     (core/src/model_executor/layers/attention.rs:255-257); `force` = "v1" / "v2" overrides it.
-    q, out: [seqs, heads, head]."""
+    q, out: [seqs, heads, head]; q may be a view whose rows are strided (the kernels take q_stride)."""
     n, nh, hd = q.shape
+    assert q.is_cuda and q.stride(2) == 1 and q.stride(1) == hd
     parts = -(-max_context_len // PARTITION_SIZE)
     use_v1 = max_context_len <= 8192 and (parts == 1 or n * nh > 512)
     if force is not None:
@@ -160,7 +161,7 @@ def paged_attention(out, q, key_cache, value_cache, block_tables_i32, context_le
                   kv_block_stride=key_cache.stride(0), kv_head_stride=key_cache.stride(1),
                   max_context_len=max_context_len, scale=scale, scalar_type=scalar_type(q.dtype))
     if use_v1:
-        lib().paged_attention_v1(_c(out).data_ptr(), _c(q).data_ptr(), key_cache.data_ptr(), value_cache.data_ptr(),
+        lib().paged_attention_v1(_c(out).data_ptr(), q.data_ptr(), key_cache.data_ptr(), value_cache.data_ptr(),
                                  _c(block_tables_i32).data_ptr(), _c(context_lens_i32).data_ptr(), None,
                                  PagedAttentionV1Params(**common))
         return "v1"
@@ -170,7 +171,7 @@ def paged_attention(out, q, key_cache, value_cache, block_tables_i32, context_le
                      torch.empty((n, nh, parts), dtype=torch.float32, device=q.device))
     tmp_out, exp_sums, max_logits = workspace
     lib().paged_attention_v2(_c(out).data_ptr(), exp_sums.data_ptr(), max_logits.data_ptr(), tmp_out.data_ptr(),
-                             _c(q).data_ptr(), key_cache.data_ptr(), value_cache.data_ptr(),
+                             q.data_ptr(), key_cache.data_ptr(), value_cache.data_ptr(),
                              _c(block_tables_i32).data_ptr(), _c(context_lens_i32).data_ptr(), None,
                              PagedAttentionV2Params(**common))
     return "v2"

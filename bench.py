@@ -251,6 +251,123 @@ def serve(cfg, n_layers, n_requests, decode_tokens, budget):
     return 0
 
 
+def reference_arm(a) -> int:
+    """The comparison arm: one step of the same model, batch and context made of yinqiwen/lmsf's own CUDA kernels
+    (built unmodified for sm_100a into baseline/_ref) in the reference's order, with the library products the
+    reference calls.  The Rust engine around them cannot be built here (no cargo, no network); nothing of
+    lmsf_b200 runs on this path."""
+    try:
+        from baseline import build_ref
+        build_ref.ensure_built()
+    except Exception as e:                                  # no sources, no compiler: say so and leave
+        print(json.dumps({"impl": "reference", "unavailable": " ".join(str(e).split())[:300]}))
+        return 0
+    import torch
+    if not torch.cuda.is_available():
+        print(json.dumps({"impl": "reference", "unavailable": "no CUDA device here; the reference's kernels are built"}))
+        return 0
+    from baseline.reference_step import DecodeBatch, ReferenceLlama
+    a.warmup = max(a.warmup, 3)
+    pk = peaks()
+    cfg = dict(MODELS[a.model])
+    full_layers = cfg["num_hidden_layers"]
+    n_layers = a.layers or full_layers
+    ctx_len, V = a.context, cfg["vocab_size"]
+    nums = model_numbers(cfg, n_layers)
+    dev = torch.device("cuda:0")
+    max_batch = 64 if not a.skip_points else a.batch
+    per_seq = -(-(ctx_len + 600) // BLOCK_SIZE)
+    pages = max_batch * per_seq + PREFILL_TOKENS // BLOCK_SIZE + 8
+    model = ReferenceLlama(cfg, n_layers, pages, BLOCK_SIZE, dev)
+    g = torch.Generator().manual_seed(0)
+
+    def decode(batch, steps, warmup, e2e=False):
+        db = DecodeBatch(model, batch, ctx_len)
+        toks = torch.randint(0, V, (steps + warmup, batch), generator=g).tolist()
+        for k in range(warmup):
+            db.step(toks[k], read_back=e2e)
+        torch.cuda.synchronize()
+        l0 = model.launches
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        start.record()
+        for k in range(warmup, warmup + steps):
+            db.step(toks[k], read_back=e2e)
+        end.record()
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        return start.elapsed_time(end) / steps, wall / steps, model.launches - l0, db
+
+    clocks = ClockSampler()
+    clocks.start()
+    ms, _, launches, _ = decode(a.batch, a.steps, a.warmup)
+    clock_rec = clocks.stop()
+    value = a.batch / (ms * 1e-3)
+    achieved = decode_bytes(nums, a.batch, ctx_len) / (ms * 1e-3) / 1e9
+    points = {}
+    if not a.skip_points:
+        for b in (1, 64):
+            pms, _, _, _ = decode(b, max(8, a.steps // 2), a.warmup)
+            points[f"decode_b{b}"] = round(b / (pms * 1e-3), 1)
+            points[f"decode_b{b}_hbm_frac"] = round(decode_bytes(nums, b, ctx_len) / (pms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+
+    # prefill of one prompt
+    T = PREFILL_TOKENS
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    first = max_batch * per_seq
+    pos = torch.arange(T, dtype=torch.int64, device=dev)
+    slots = (first * BLOCK_SIZE + pos).contiguous()
+    times = []
+    for k in range(2 + 3):
+        ids = torch.randint(0, V, (T,), generator=g).to(dev)
+        flush.zero_()
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        model.prefill(ids, pos, slots)
+        end.record()
+        torch.cuda.synchronize()
+        if k >= 2:
+            times.append(start.elapsed_time(end))
+    pf_ms = statistics.median(times)
+    pf_flops = prefill_flops(cfg, nums, T, n_layers)
+    prefill = {"value": round(T / (pf_ms * 1e-3), 1), "tokens": T, "ms": round(pf_ms, 3),
+               "frac": round(pf_flops / (pf_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+    del flush
+    model._bufs.clear()
+    torch.cuda.empty_cache()
+
+    e2e = None
+    if not a.skip_e2e:
+        _, wall, _, db = decode(a.batch, a.steps, max(a.warmup, E2E_WARMUP), e2e=True)
+        e2e = {"value": round(a.batch / wall, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(db.h2d_bytes),
+               "d2h_bytes_per_step": int(db.d2h_bytes)}
+
+    line = {
+        "metric": f"decode tokens/s ({a.model} shape, batch {a.batch}, {ctx_len}-token contexts)", "value": round(value, 1),
+        "unit": "tokens/s", "n_gpus": 1, "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(ms, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"model": f"{a.model} shape, random weights", "layers": n_layers, "layers_of_model": full_layers,
+                   "hidden_size": cfg["hidden_size"], "num_attention_heads": cfg["num_attention_heads"],
+                   "num_key_value_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                   "intermediate_size": cfg["intermediate_size"], "vocab_size": V, "global_batch": a.batch,
+                   "seq_len": ctx_len, "max_model_len": max(MAX_MODEL_LEN, ctx_len + 64), "block_size": BLOCK_SIZE,
+                   "prefill_tokens": PREFILL_TOKENS, "e2e_warmup": f">= {max(a.warmup, E2E_WARMUP)} steps", "parallelism": "1 GPU",
+                   "l2": "inputs larger than L2 (weights + cache of a step >> 126 MB); prefill flushes L2",
+                   "peaks": pk["source"],
+                   "arm": "the reference's CUDA kernels (unmodified, sm_100a) in its order, torch.mm (cuBLAS) products, "
+                          "no CUDA graph; its Rust engine cannot be built here"},
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points, "clocks": clock_rec, "gpu_launches": int(launches), "impl": "reference",
+    }
+    if e2e is not None:
+        line["e2e"] = e2e
+    print(json.dumps(line))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -268,10 +385,10 @@ def main() -> int:
                          "tokens each through the engine's continuous batching")
     a = ap.parse_args()
     if a.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "yinqiwen/lmsf is a Rust workspace (cargo, candle from a local path, crates from the "
-                          "network); no Rust toolchain and no network here, so pip cannot install it"}))
-        return 0
+        if a.gpus != 1:
+            print(f"bench.py: the comparison arm runs on one GPU; --gpus {a.gpus} is not supported")
+            return 2
+        return reference_arm(a)
     if a.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {a.gpus} is not supported")
         return 2

@@ -1,8 +1,13 @@
 """Plain, slow implementation of the Llama decoder used as the oracle of the tests.
 
-It rests on the formulas of yinqiwen/lmsf's sources only: the reference is Rust on
-top of a CUDA-only tensor library and can neither be imported nor compiled on a CPU
-box, so there is no golden output of the reference itself to compare with.
+It is written from the formulas of yinqiwen/lmsf's sources (each function cites file:line).  The reference's
+model code is Rust on top of a CUDA-only tensor library and can neither be imported nor compiled on a CPU box,
+so there is no golden output of its whole model.  Its CUDA kernels, however, compile unmodified, and
+tests/golden/reference_kernels_f32.npz holds what they returned on a B200 (made by
+tests/golden/make_reference_kernel_goldens.py): tests/test_golden_reference_kernels.py pins `rms_norm` (with and
+without the residual sum), `rotary_neox`, the gated SiLU of `silu_gated_mlp` and `causal_attention` to those
+outputs.  What the reference has no code for (rope_theta from config.json, llama3 frequency scaling, tied head,
+the keying of the sampler's noise) rests on the formulas alone.
 
 Whole sequences, no cache, one function per part, all arithmetic in one float type
 (float32 by default, float64 to bound rounding).  Nothing here imports the product
