@@ -18,6 +18,8 @@
 // Limits and rules.
 //   * 256 KiB of counters + n_seqs_total * n_q_heads * n_splits * (head_dim + 1) * 4 bytes must fit in 8 MiB; a larger
 //     request is refused with LMSF_EBADARG and a message (lmsf_attention_mma_last_error()).
+//   * The values of seq_ids must be below n_seqs_total; without seq_ids, n_served must not exceed it (the scratch
+//     is indexed by the request's row).  The second is checked, the first cannot be on the host.
 //   * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with
 //     that device current) and sets the kernel's shared-memory limit.  Make that first call
 //     outside any stream capture.

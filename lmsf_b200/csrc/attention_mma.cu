@@ -451,6 +451,9 @@ LMSF_API int lmsf_attention_decode(const void* q, long long q_stride, void* out,
     LMSF_REFUSE("attention_decode: %d query heads cannot be grouped over %d kv heads", n_q_heads, n_kv_heads);
   if (n_splits < 1 || n_splits > 65535) LMSF_REFUSE("attention_decode: n_splits=%d", n_splits);
   if (n_splits > 1 && !scratch) LMSF_REFUSE("attention_decode: %d splits need scratch memory", n_splits);
+  if (!seq_ids && n_served > n_seqs_total)
+    LMSF_REFUSE("attention_decode: n_served=%d exceeds n_seqs_total=%d, the rows the scratch was sized for", n_served,
+                n_seqs_total);
   if (block_size <= 0 || max_blocks <= 0) LMSF_REFUSE("attention_decode: bad block table geometry");
   const int group = n_q_heads / n_kv_heads;
   const long long gy = (long long)n_kv_heads * ((group + 15) / 16);

@@ -142,25 +142,36 @@ def silu_gated_mlp(h, w_gate, w_up, w_down):
     return ((g / (1.0 + torch.exp(-g))) * u) @ w_down.T
 
 
-def attention_block(cfg, w, prefix, h, positions, inv_freq):
+def _identity(x):
+    return x
+
+
+def attention_block(cfg, w, prefix, h, positions, inv_freq, r=_identity):
     """q,k,v projections, rotary on q and k, causal attention, output projection
-    (core/src/model_executor/models/llama/llama.rs:95-135)."""
+    (core/src/model_executor/models/llama/llama.rs:95-135).  r rounds what the engine stores (see forward)."""
     nh, hd = cfg["num_attention_heads"], head_dim_of(cfg)
     nkv = cfg.get("num_key_value_heads") or nh
     T = h.shape[0]
-    q = (h @ w[prefix + "q_proj.weight"].T).reshape(T, nh, hd)
-    k = (h @ w[prefix + "k_proj.weight"].T).reshape(T, nkv, hd)
-    v = (h @ w[prefix + "v_proj.weight"].T).reshape(T, nkv, hd)
-    q = rotary_neox(q, positions, inv_freq)
-    k = rotary_neox(k, positions, inv_freq)
-    o = causal_attention(q, k, v, 1.0 / math.sqrt(hd), cfg.get("sliding_window"))
-    return o.reshape(T, nh * hd) @ w[prefix + "o_proj.weight"].T
+    q = r(h @ w[prefix + "q_proj.weight"].T).reshape(T, nh, hd)
+    k = r(h @ w[prefix + "k_proj.weight"].T).reshape(T, nkv, hd)
+    v = r(h @ w[prefix + "v_proj.weight"].T).reshape(T, nkv, hd)
+    q = r(rotary_neox(q, positions, inv_freq))
+    k = r(rotary_neox(k, positions, inv_freq))
+    o = r(causal_attention(q, k, v, 1.0 / math.sqrt(hd), cfg.get("sliding_window")))
+    return r(o.reshape(T, nh * hd) @ w[prefix + "o_proj.weight"].T)
 
 
-def forward(cfg, weights, token_ids, dtype=torch.float32):
+def forward(cfg, weights, token_ids, dtype=torch.float32, stored=None):
     """Logits [T, vocab] of one whole sequence (core/src/model_executor/models/llama/llama.rs:397-476;
-    the residual adds that the reference folds into the next norm are written out)."""
+    the residual adds that the reference folds into the next norm are written out).
+
+    `stored` (e.g. torch.bfloat16) rounds every tensor that a bfloat16 engine writes to memory to that type and
+    back: the outputs of norms, projections, the rotation, the attention and the gated product.  The sums inside
+    a product or a softmax and the residual stream stay in `dtype`.  It states what a bfloat16 run may differ by
+    from exact arithmetic, so that a comparison with it can be held to a tighter bound than one with the exact
+    result; the formulas are the same."""
     w = {k: v.to(dtype) for k, v in weights.items()}
+    r = _identity if stored is None else (lambda x: x.to(stored).to(dtype))
     ids = torch.as_tensor(token_ids, dtype=torch.long)
     positions = torch.arange(len(ids))
     inv_freq = rope_inv_freq(cfg)
@@ -168,12 +179,16 @@ def forward(cfg, weights, token_ids, dtype=torch.float32):
     x = embedding(w["model.embed_tokens.weight"], ids)
     for i in range(cfg["num_hidden_layers"]):
         p = f"model.layers.{i}."
-        h = rms_norm(x, w[p + "input_layernorm.weight"], eps)
-        x = x + attention_block(cfg, w, p + "self_attn.", h, positions, inv_freq)
-        h = rms_norm(x, w[p + "post_attention_layernorm.weight"], eps)
-        x = x + silu_gated_mlp(h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
-                               w[p + "mlp.down_proj.weight"])
-    x = rms_norm(x, w["model.norm.weight"], eps)
+        h = r(rms_norm(x, w[p + "input_layernorm.weight"], eps))
+        x = x + attention_block(cfg, w, p + "self_attn.", h, positions, inv_freq, r)
+        h = r(rms_norm(x, w[p + "post_attention_layernorm.weight"], eps))
+        if stored is None:
+            x = x + silu_gated_mlp(h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
+                                   w[p + "mlp.down_proj.weight"])
+        else:
+            g, u = r(h @ w[p + "mlp.gate_proj.weight"].T), r(h @ w[p + "mlp.up_proj.weight"].T)
+            x = x + r(r((g / (1.0 + torch.exp(-g))) * u) @ w[p + "mlp.down_proj.weight"].T)
+    x = r(rms_norm(x, w["model.norm.weight"], eps))
     head = w["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings", False) else w["lm_head.weight"]
     return x @ head.T
 

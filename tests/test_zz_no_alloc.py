@@ -39,12 +39,20 @@ def _case(nh, nkv, hd, bs, ctx_lens, seed):
 
 
 def test_static_scratch_variant_matches_the_ordinary_entry_point_twice_in_a_row():
+    """More than 8 key splits add their partial results up through the scratch (up to 8 meet in the shared memory
+    of a thread-block cluster and never touch it), so the cases with 12, 24 and 16 splits are the ones in which
+    the kernels really read and write the static array: a wrong device address, counters that a call did not
+    leave at zero or partial results left over from the call before would change their output.  The calls differ
+    in the number of requests, of heads and of splits, so each finds the array as another geometry left it; one
+    call that stays inside a cluster (6 splits) runs in between."""
     from lmsf_b200 import kernels
-    nh, nkv, hd, bs = 8, 2, 64, 16
+    hd, bs = 64, 16
     lib, f = _symbol(hd)
     assert lib.lmsf_attention_decode_static_capacity() == 8 << 20
     stream = torch.cuda.current_stream().cuda_stream
-    for ctx_lens, splits, seed in (([900, 65, 1, 400], 6, 1), ([130, 777, 300], 3, 2)):
+    cases = ((8, 2, [900, 65, 1, 400], 12, 1), (4, 4, [130, 777, 300], 24, 2), (8, 2, [900, 65, 1, 400], 6, 3),
+             (12, 3, [513, 2, 1030, 64, 257], 16, 4), (8, 2, [900, 65, 1, 400], 12, 1))
+    for nh, nkv, ctx_lens, splits, seed in cases:
         q, cache, bt, cu, cl = _case(nh, nkv, hd, bs, ctx_lens, seed)
         scale = 1.0 / math.sqrt(hd)
         want = torch.zeros_like(q)
@@ -57,8 +65,28 @@ def test_static_scratch_variant_matches_the_ordinary_entry_point_twice_in_a_row(
                nh, hd, splits, stream)
         assert rc == 0, lib.lmsf_attention_mma_last_error()
         torch.cuda.synchronize()
-        assert torch.allclose(got.float(), want.float(), rtol=2e-2, atol=2e-2)
-        assert torch.equal(got, want)          # the same kernels in the same order: not a bit may differ
+        assert torch.allclose(got.float(), want.float(), rtol=2e-2, atol=2e-2), (nh, splits)
+        assert torch.equal(got, want), (nh, splits)     # the same kernels in the same order: not a bit may differ
+        # and both agree with the plain twin that needs no scratch at all
+        plain = torch.zeros_like(q)
+        token_seq = torch.arange(len(ctx_lens), dtype=torch.int32, device=q.device)
+        kernels.attention_generic(plain, q, cache, bt, bs, token_seq, (cl - 1).contiguous(), scale, 0, nh, nkv, hd)
+        assert float((got.float() - plain.float()).abs().max()) <= 2e-2 * float(plain.float().abs().max()), (nh, splits)
+
+
+def test_static_scratch_variant_refuses_more_served_requests_than_rows():
+    """Without seq_ids the kernels index the scratch by the served request's number: more served requests than
+    rows of the block table would run past what was sized."""
+    nh, nkv, hd, bs = 8, 2, 64, 16
+    lib, f = _symbol(hd)
+    q, cache, bt, cu, cl = _case(nh, nkv, hd, bs, [100, 50], 3)
+    out = torch.zeros_like(q)
+    rc = f(q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), cache.data_ptr(), cache.stride(0), bs, nkv,
+           bt.data_ptr(), bt.shape[1], None, 2, 1, cu.data_ptr(), cl.data_ptr(), 0.125, 0, nh, hd, 12,
+           torch.cuda.current_stream().cuda_stream)
+    assert rc == -1 and "n_served" in lib.lmsf_attention_mma_last_error().decode()
+    torch.cuda.synchronize()
+    assert torch.all(out == 0)
 
 
 def test_static_scratch_variant_refuses_what_does_not_fit():
