@@ -14,7 +14,7 @@ def __getattr__(name):   # the engine pulls in torch and CUDA; load it when aske
     if name in ("LLMEngine",):
         from .engine.llm_engine import LLMEngine
         return LLMEngine
-    if name in ("RequestOutput", "CompletionOutput"):
+    if name in ("RequestOutput", "CompletionOutput", "RequestMetrics"):
         from .engine import sequence
         return getattr(sequence, name)
     raise AttributeError(name)

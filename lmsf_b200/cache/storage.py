@@ -86,7 +86,8 @@ class CacheStorage:
                 lc.kv, lc.group = self.tensors[g][i], g
             st: Optional[StateSpec] = model.call_state_spec(j)
             if st is not None:
-                lc.state = torch.zeros((max(1, num_state_slots), *st.shape), dtype=st.dtype, device=device)
+                # one slot more than the manager hands out: the "null slot" of a padded batch's stand-in requests
+                lc.state = torch.zeros((num_state_slots + 1, *st.shape), dtype=st.dtype, device=device)
             self.state_tensors.append(lc.state)
             self.layer_caches.append(lc)
 

@@ -51,9 +51,12 @@ class SchedulerConfig:
 
     @staticmethod
     def new(max_num_batched_tokens: Optional[int], max_num_seqs: int, max_model_len: int) -> "SchedulerConfig":
-        # default as core/src/common/config.rs:301-307
+        # The reference defaults to max(max_model_len, 2048) because it runs a prompt in one piece
+        # (core/src/common/config.rs:301-307).  Prompts are cut into portions here, so the budget of a step need
+        # not cover a whole prompt: 8,192 tokens at most keep the activations of a step small whatever the
+        # model's context length is.
         if max_num_batched_tokens is None:
-            max_num_batched_tokens = max(max_model_len, 2048)
+            max_num_batched_tokens = min(max(max_model_len, 2048), 8192)
         if max_num_batched_tokens <= 0 or max_num_seqs <= 0:
             raise ConfigError("max_num_batched_tokens and max_num_seqs must be positive")
         return SchedulerConfig(max_num_batched_tokens, max_num_seqs, max_model_len)

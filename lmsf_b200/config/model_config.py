@@ -96,10 +96,10 @@ class LlamaConfig:
         if self.num_attention_heads % self.num_key_value_heads:
             raise ConfigError(f"num_attention_heads {self.num_attention_heads} is not a multiple of "
                               f"num_key_value_heads {self.num_key_value_heads}")
-        if self.hidden_act not in ("silu", "swish"):
-            raise ConfigError(f"hidden_act {self.hidden_act!r} is not supported by the Llama feed-forward (silu)")
-        if self.attention_bias or self.mlp_bias:
-            raise ConfigError("attention_bias / mlp_bias are not supported: the Llama projections carry no bias")
+        if self.hidden_act not in ("silu", "swish", "gelu_tanh", "gelu_pytorch_tanh"):
+            raise ConfigError(f"hidden_act {self.hidden_act!r} is not supported by the gated feed-forward "
+                              f"(silu, gelu_pytorch_tanh)")
+        self.attention_bias, self.mlp_bias = bool(self.attention_bias), bool(self.mlp_bias)
         if not (self.rms_norm_eps > 0):
             raise ConfigError(f"rms_norm_eps must be positive, got {self.rms_norm_eps}")
         if self.sliding_window is not None and self.sliding_window <= 0:
@@ -153,7 +153,7 @@ class LlamaConfig:
             "head_dim": self.head_dim, "intermediate_size": self.intermediate_size, "vocab_size": self.vocab_size,
             "hidden_act": self.hidden_act, "max_position_embeddings": self.max_position_embeddings,
             "rms_norm_eps": self.rms_norm_eps, "rope_theta": self.rope_theta,
-            "tie_word_embeddings": self.tie_word_embeddings, "attention_bias": False, "mlp_bias": False,
+            "tie_word_embeddings": self.tie_word_embeddings, "attention_bias": self.attention_bias, "mlp_bias": self.mlp_bias,
             "bos_token_id": self.bos_token_id,
             "eos_token_id": self.eos_token_ids[0] if len(self.eos_token_ids) == 1 else list(self.eos_token_ids),
             "torch_dtype": self.torch_dtype,

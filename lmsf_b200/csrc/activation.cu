@@ -46,7 +46,32 @@ __global__ void gated_act_vec_kernel(bf16* __restrict__ out, const bf16* __restr
   }
 }
 
+// x[t, i] += bias[i], the sum taken in float32 and rounded once to x's type.
+template <typename T>
+__global__ void bias_add_kernel(T* __restrict__ x, const T* __restrict__ bias, int d, long long stride) {
+  T* row = x + (size_t)blockIdx.x * stride;
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < d; i += gridDim.y * blockDim.x)
+    row[i] = from_f32<T>(to_f32(row[i]) + to_f32(bias[i]));
+}
+
 }  // namespace lmsf
+
+// x: [n, d] with `stride` elements between rows, bias: [d] of x's type; in place.  The projections of a model whose
+// config.json asks for biases (attention_bias, mlp_bias) add them with this kernel after the product; the
+// reference's linear layer does the same as a separate broadcast add (core/src/model_executor/layers/linear.rs:100-104).
+LMSF_API int lmsf_bias_add(void* x, const void* bias, int n, int d, long long stride, int dtype, void* stream) {
+  using namespace lmsf;
+  if (n <= 0) return 0;
+  if (d <= 0 || stride < d) LMSF_REFUSE("bias_add: d=%d, stride=%lld", d, stride);
+  if (dtype != LMSF_F32 && dtype != LMSF_BF16) LMSF_REFUSE("bias_add: unknown dtype code %d", dtype);
+  int gy = ceil_div(d, 256 * 4);
+  if (gy > 64) gy = 64;
+  dim3 grid(n, gy);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == LMSF_F32) bias_add_kernel<float><<<grid, 256, 0, s>>>((float*)x, (const float*)bias, d, stride);
+  else bias_add_kernel<bf16><<<grid, 256, 0, s>>>((bf16*)x, (const bf16*)bias, d, stride);
+  return LMSF_LAUNCH_STATUS();
+}
 
 // in: [n, 2 * d] with `in_stride` elements between rows (gate first, up second); out: [n, d].
 LMSF_API int lmsf_gated_act(void* out, const void* in, int n, int d, long long in_stride, int act, int dtype,

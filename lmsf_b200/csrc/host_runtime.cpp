@@ -283,7 +283,8 @@ LMSF_HOST_API int lmsf_cm_check(void* h) {
 //   13 tile128_q0[T128]  14.. block table of group g [S * max_blocks[g]]
 // info: 0 N, 1 R, 2 n_dec, 3 T64, 4 T128, 5 has_patches, 6 total ints, 7.. max_blocks per group.
 // With pad_to > S the batch is filled up to pad_to requests with stand-ins that bring one token (id 0 at
-// position 0) and whose block tables name null_pages[g], a page outside the pools: a decode batch can then be
+// position 0), whose block tables name null_pages[g], a page outside the pools, and whose state slot is n_slots,
+// one past the slots of real requests (the state tensors have that row to spare): a decode batch can then be
 // replayed from a graph captured for a rounder size.  Their logits rows come after the real ones.
 // With out == nullptr only the sizes are computed.  Returns 0, -2 for an unknown request, -4 when cap is too small.
 LMSF_HOST_API int lmsf_cm_build_batch(void* h, int S, const int64_t* rids, const int* q_lens, const int* tokens_flat,
@@ -376,7 +377,7 @@ LMSF_HOST_API int lmsf_cm_build_batch(void* h, int S, const int64_t* rids, const
     cu_q[s + 1] = off + 1;
     ctx_len[s] = 1;
     ctx_lens_out[s] = 1;
-    state_slot[s] = 0;
+    state_slot[s] = m.n_slots;                  // the spare slot behind the real ones: no request's state
     patch_dst[s] = -1; patch_src[s] = 0;
     rows[r++] = off;
     dec_ids[d++] = s;

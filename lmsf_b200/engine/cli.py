@@ -58,7 +58,8 @@ def main(argv=None) -> int:
             if out.finished:
                 c = out.outputs[0]
                 print(json.dumps({"request_id": out.request_id, "finish_reason": c.finish_reason,
-                                  "token_ids": c.token_ids, "text": c.text}))
+                                  "token_ids": c.token_ids, "text": c.text,
+                                  "metrics": out.metrics.summary(len(c.token_ids))}))
         steps += 1
         if ns.step_stats:
             print(json.dumps(asdict(engine.last_stats)), file=sys.stderr)

@@ -54,7 +54,14 @@ class LLMEngine:
         self.max_model_len = resolve_max_model_len(args.max_model_len, self.model.spec.max_model_len)
         self.cache_config = CacheConfig(args.block_size, args.gpu_memory_utilization, args.num_gpu_blocks)
         self.scheduler_config = SchedulerConfig.new(args.max_num_batched_tokens, args.max_num_seqs, self.max_model_len)
-        act_bytes = self.scheduler_config.max_num_batched_tokens * self.model.spec.hidden_size * 64
+        # what a step of the largest allowed batch keeps alive beside the cache: per token the widest part's
+        # intermediates and a few rows of the model's width (hidden state, branch output, float32 residual),
+        # and the float32 logits of every request; half as much again for the allocator's slack
+        esize = torch.empty(0, dtype=self.dtype).element_size()
+        widest = max([part.activation_width() for part, _ in self.model.parts_with_specs()] + [0])
+        per_token = (widest + 4 * self.model.spec.hidden_size) * esize + 8 * self.model.spec.hidden_size
+        act_bytes = int(1.5 * (self.scheduler_config.max_num_batched_tokens * per_token
+                               + 2 * args.max_num_seqs * self.model.spec.vocab_size * 4))
         self.runner = ModelRunner(self.model, self.dtype, self.device, args.block_size,
                                   num_blocks=args.num_gpu_blocks, max_num_seqs=args.max_num_seqs,
                                   gpu_memory_utilization=args.gpu_memory_utilization,

@@ -82,14 +82,34 @@ class CompletionOutput:
 
 
 @dataclass
+class RequestMetrics:
+    """Times of a request on the engine's monotonic clock, as the reference keeps them
+    (core/src/common/sequence.rs:13-33): arrival, first token, finish."""
+    arrival_time: float
+    first_token_time: Optional[float]
+    finished_time: Optional[float]
+
+    def summary(self, n_generated: int) -> dict:
+        """Seconds to the first token, seconds per token after it, seconds to the end."""
+        ttft = None if self.first_token_time is None else self.first_token_time - self.arrival_time
+        end = None if self.finished_time is None else self.finished_time - self.arrival_time
+        tpot = None
+        if ttft is not None and end is not None and n_generated > 1:
+            tpot = (end - ttft) / (n_generated - 1)
+        return {"ttft_s": ttft, "tpot_s": tpot, "finished_s": end}
+
+
+@dataclass
 class RequestOutput:
     request_id: Hashable
     prompt_token_ids: List[int]
     outputs: List[CompletionOutput]
     finished: bool
+    metrics: Optional[RequestMetrics] = None
 
     @staticmethod
     def from_sequence(seq: Sequence, text: Optional[str] = None) -> "RequestOutput":
         reason = seq.status.value if seq.status.finished else None
         return RequestOutput(seq.request_id, list(seq.prompt_token_ids),
-                             [CompletionOutput(0, text, list(seq.output_token_ids), reason)], seq.status.finished)
+                             [CompletionOutput(0, text, list(seq.output_token_ids), reason)], seq.status.finished,
+                             RequestMetrics(seq.arrival_time, seq.first_token_time, seq.finish_time))

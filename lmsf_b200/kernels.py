@@ -210,6 +210,16 @@ def gated_act(out: torch.Tensor, x: torch.Tensor, act: str = "silu"):
     _check(rc, "activation.cu", "lmsf_activation")
 
 
+def bias_add(x: torch.Tensor, bias: torch.Tensor):
+    """x[t, :] += bias in place (sum in float32); x: [n, d] with a contiguous last dimension, bias: [d] of x's dtype."""
+    n, d = x.shape
+    if bias.shape != (d,) or bias.dtype != x.dtype or x.stride(1) != 1 or not bias.is_contiguous():
+        raise KernelError(f"bias_add: x {tuple(x.shape)} / {x.dtype} and bias {tuple(bias.shape)} / {bias.dtype} do not match")
+    f = _func("activation.cu", "lmsf_bias_add", [c_void_p, c_void_p, c_int, c_int, c_longlong, c_int, c_void_p])
+    rc = f(_ptr(x), _ptr(bias), n, d, x.stride(0), dtype_code(x.dtype), _stream())
+    _check(rc, "activation.cu", "lmsf_activation")
+
+
 # ----------------------------------------------------------------------------- SIMT matrix product
 
 def gemm_tn_simt(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor):

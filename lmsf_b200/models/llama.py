@@ -22,23 +22,28 @@ def llama_spec(cfg: LlamaConfig) -> ModelSpec:
     layers = []
     for i in range(cfg.num_hidden_layers):
         p = f"model.layers.{i}."
+        attn_w = {"qkv": [p + "self_attn.q_proj.weight", p + "self_attn.k_proj.weight", p + "self_attn.v_proj.weight"],
+                  "o": p + "self_attn.o_proj.weight"}
+        if cfg.attention_bias:
+            attn_w.update(qkv_bias=[p + "self_attn.q_proj.bias", p + "self_attn.k_proj.bias", p + "self_attn.v_proj.bias"],
+                          o_bias=p + "self_attn.o_proj.bias")
+        mlp_w = {"gate_up": [p + "mlp.gate_proj.weight", p + "mlp.up_proj.weight"], "down": p + "mlp.down_proj.weight"}
+        if cfg.mlp_bias:
+            mlp_w.update(gate_up_bias=[p + "mlp.gate_proj.bias", p + "mlp.up_proj.bias"], down_bias=p + "mlp.down_proj.bias")
         layers.append(LayerSpec("pre_norm", {
             "mixer_norm": PartSpec("rmsnorm", dict(hidden_size=cfg.hidden_size, eps=cfg.rms_norm_eps),
                                    {"weight": p + "input_layernorm.weight"}),
             "mixer": PartSpec("paged_attention",
                               dict(hidden_size=cfg.hidden_size, num_heads=cfg.num_attention_heads,
                                    num_kv_heads=cfg.num_key_value_heads, head_dim=cfg.head_dim,
-                                   position_encoding=rope, window=cfg.sliding_window),
-                              {"qkv": [p + "self_attn.q_proj.weight", p + "self_attn.k_proj.weight",
-                                       p + "self_attn.v_proj.weight"],
-                               "o": p + "self_attn.o_proj.weight"}),
+                                   position_encoding=rope, window=cfg.sliding_window, bias=cfg.attention_bias),
+                              attn_w),
             "ffn_norm": PartSpec("rmsnorm", dict(hidden_size=cfg.hidden_size, eps=cfg.rms_norm_eps),
                                  {"weight": p + "post_attention_layernorm.weight"}),
             "feed_forward": PartSpec("gated_mlp",
                                      dict(hidden_size=cfg.hidden_size, intermediate_size=cfg.intermediate_size,
-                                          activation=cfg.hidden_act),
-                                     {"gate_up": [p + "mlp.gate_proj.weight", p + "mlp.up_proj.weight"],
-                                      "down": p + "mlp.down_proj.weight"}),
+                                          activation=cfg.hidden_act, bias=cfg.mlp_bias),
+                                     mlp_w),
         }))
     head_name = "model.embed_tokens.weight" if cfg.tie_word_embeddings else "lm_head.weight"
     ignored = [r".*\.rotary_emb\.inv_freq$"]

@@ -30,7 +30,7 @@ class PagedAttention(Mixer):
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position_encoding: Optional[PositionEncoding] = None, window: Optional[int] = None,
-                 scale: Optional[float] = None):
+                 scale: Optional[float] = None, bias: bool = False):
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} query heads cannot be grouped over {num_kv_heads} kv heads")
         if head_dim % 16 or not (16 <= head_dim <= 256):
@@ -42,16 +42,26 @@ class PagedAttention(Mixer):
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
         self.q_size = num_heads * head_dim
         self.kv_size = num_kv_heads * head_dim
+        self.has_bias = bool(bias)
         self.qkv: Optional[torch.Tensor] = None
         self.o: Optional[torch.Tensor] = None
+        self.qkv_bias: Optional[torch.Tensor] = None
+        self.o_bias: Optional[torch.Tensor] = None
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
-        return {"qkv": WeightSpec([(self.q_size, self.hidden_size), (self.kv_size, self.hidden_size),
-                                   (self.kv_size, self.hidden_size)]),
-                "o": WeightSpec([(self.hidden_size, self.q_size)])}
+        specs = {"qkv": WeightSpec([(self.q_size, self.hidden_size), (self.kv_size, self.hidden_size),
+                                    (self.kv_size, self.hidden_size)]),
+                 "o": WeightSpec([(self.hidden_size, self.q_size)])}
+        if self.has_bias:
+            specs["qkv_bias"] = WeightSpec([(self.q_size,), (self.kv_size,), (self.kv_size,)])
+            specs["o_bias"] = WeightSpec([(self.hidden_size,)])
+        return specs
 
     def cache_spec(self) -> Optional[KVCacheSpec]:
         return KVCacheSpec(self.num_kv_heads, self.head_dim, self.window)
+
+    def activation_width(self) -> int:
+        return 2 * self.q_size + 2 * self.kv_size           # q, k, v and the attention's output
 
     def prepare(self, dtype, device) -> None:
         if self.position_encoding is not None:
@@ -60,7 +70,7 @@ class PagedAttention(Mixer):
     def forward(self, ctx: StepContext, h: torch.Tensor, cache: LayerCache) -> torch.Tensor:
         group = ctx.groups[cache.group]
         fused = self.position_encoding.fused_rotary() if self.position_encoding is not None else None
-        if (FUSE_QKV_ROPE and cache.owner and linear.USE_SKINNY and (fused is not None or self.position_encoding is None)
+        if (FUSE_QKV_ROPE and cache.owner and linear.USE_SKINNY and self.qkv_bias is None and (fused is not None or self.position_encoding is None)
                 and kernels.gemm_skinny_qkv_rope_supported(h, self.qkv, self.head_dim, fused[1] if fused else 0,
                                                            fused[2] if fused else True)):
             # a few single tokens (a decode step): projection, rotation and cache write in one kernel
@@ -71,14 +81,14 @@ class PagedAttention(Mixer):
                                          self.head_dim, ctx.error_flag)
             out = torch.empty((ctx.n_tokens, self.q_size), dtype=h.dtype, device=h.device)
             self.attend(ctx, out, q, cache.kv, group)
-            return matmul_tn(out, self.o)
+            return matmul_tn(out, self.o, bias=self.o_bias)
         if cache.owner:
-            qkv = matmul_tn(h, self.qkv)
+            qkv = matmul_tn(h, self.qkv, bias=self.qkv_bias)
             q = qkv[:, :self.q_size]
             k = qkv[:, self.q_size:self.q_size + self.kv_size]
             v = qkv[:, self.q_size + self.kv_size:]
         else:  # keys and values are another call's: only the queries are needed
-            q = matmul_tn(h, self.qkv[:self.q_size])
+            q = matmul_tn(h, self.qkv[:self.q_size], bias=None if self.qkv_bias is None else self.qkv_bias[:self.q_size])
             k = v = None
         if self.position_encoding is not None and fused is None:
             self.position_encoding.apply(ctx, q, k, self.num_heads, self.num_kv_heads, self.head_dim)
@@ -89,7 +99,7 @@ class PagedAttention(Mixer):
                                      self.num_kv_heads, self.head_dim, ctx.error_flag)
         out = torch.empty((ctx.n_tokens, self.q_size), dtype=h.dtype, device=h.device)
         self.attend(ctx, out, q, cache.kv, group)
-        return matmul_tn(out, self.o)
+        return matmul_tn(out, self.o, bias=self.o_bias)
 
     def attend(self, ctx: StepContext, out: torch.Tensor, q: torch.Tensor, kv: torch.Tensor, group) -> None:
         """bfloat16 with a head size up to 128: single tokens go to the split-key decode kernel, longer portions

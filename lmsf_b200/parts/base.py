@@ -169,6 +169,11 @@ class Part:
     def prepare(self, dtype: torch.dtype, device: torch.device) -> None:
         """Builds device constants (tables) once the run dtype and device are known."""
 
+    def activation_width(self) -> int:
+        """How many values per token the part keeps alive at its widest (its intermediate tensors); the engine
+        sizes the memory it leaves free for a step's activations from the widest part."""
+        return 0
+
 
 class Norm(Part):
     def forward(self, x: torch.Tensor) -> torch.Tensor:

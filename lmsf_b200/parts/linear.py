@@ -1,4 +1,4 @@
-"""Dense projections y = x W^T (no bias), weight stored [out, in] as in the checkpoint.
+"""Dense projections y = x W^T (+ b where the model has biases), weight stored [out, in] as in the checkpoint.
 
 The reference's linear family (core/src/model_executor/layers/linear.rs:28-106, :325-497, :499-728)
 wraps cuBLASLt and merges q, k, v (and gate, up) into one matrix by row ranges; the same merged
@@ -16,14 +16,27 @@ import torch
 from .. import kernels
 from .base import Part, WeightSpec, register_part
 
+# Library products must add up in float32: with torch's default a split-k bfloat16 product may add its partial sums
+# in bfloat16, and a row's result would then depend on how many rows share the product (on how a prompt was cut).
+torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+
 _MM_HAS_OUT_DTYPE: Optional[bool] = None
 USE_SKINNY = True     # bfloat16 products of up to 16 rows run on this package's weight-streaming kernel
 USE_STREAM = False    # True: products of 17 to 128 rows run on the tcgen05 streaming kernel (csrc/gemm_stream.cu)
                       # instead of the library; measured slower than the library inside a step, so it is off
 
 
-def matmul_tn(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-    """x [M, K] times w [N, K] transposed -> [M, N] in `out_dtype` (default: x's dtype)."""
+def matmul_tn(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+              bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x [M, K] times w [N, K] transposed -> [M, N] in `out_dtype` (default: x's dtype), plus `bias` [N] if given
+    (added by a kernel of its own after the product, as the reference adds it: layers/linear.rs:100-104)."""
+    y = _product_tn(x, w, out_dtype)
+    if bias is not None:
+        kernels.bias_add(y, bias if bias.dtype == y.dtype else bias.to(y.dtype))
+    return y
+
+
+def _product_tn(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     global _MM_HAS_OUT_DTYPE
     out_dtype = out_dtype or x.dtype
     if x.dtype == torch.float32:
@@ -60,15 +73,21 @@ class Linear(Part):
     """out_features may be a list: the sources are stacked along the output dimension."""
     graph_safe = True
 
-    def __init__(self, in_features: int, out_features: Union[int, Sequence[int]], out_dtype: Optional[str] = None):
+    def __init__(self, in_features: int, out_features: Union[int, Sequence[int]], out_dtype: Optional[str] = None,
+                 bias: bool = False):
         self.in_features = int(in_features)
+        self.has_bias = bool(bias)
+        self.bias: Optional[torch.Tensor] = None
         self.out_splits: List[int] = [int(out_features)] if isinstance(out_features, int) else [int(o) for o in out_features]
         self.out_features = sum(self.out_splits)
         self.out_dtype = {None: None, "float32": torch.float32, "bfloat16": torch.bfloat16}[out_dtype]
         self.weight: Optional[torch.Tensor] = None
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
-        return {"weight": WeightSpec([(o, self.in_features) for o in self.out_splits])}
+        specs = {"weight": WeightSpec([(o, self.in_features) for o in self.out_splits])}
+        if self.has_bias:
+            specs["bias"] = WeightSpec([(o,) for o in self.out_splits])
+        return specs
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return matmul_tn(x, self.weight, self.out_dtype)
+        return matmul_tn(x, self.weight, self.out_dtype, self.bias)

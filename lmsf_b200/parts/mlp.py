@@ -20,24 +20,34 @@ from .linear import matmul_tn
 class GatedMLP(FeedForward):
     graph_safe = True
 
-    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu"):
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu", bias: bool = False):
         if activation not in kernels.ACT_CODES:
             raise ValueError(f"activation {activation!r} is not supported (known: {', '.join(sorted(kernels.ACT_CODES))})")
         self.hidden_size, self.intermediate_size, self.activation = int(hidden_size), int(intermediate_size), activation
+        self.has_bias = bool(bias)
         self.gate_up: Optional[torch.Tensor] = None
         self.down: Optional[torch.Tensor] = None
+        self.gate_up_bias: Optional[torch.Tensor] = None
+        self.down_bias: Optional[torch.Tensor] = None
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
-        return {"gate_up": WeightSpec([(self.intermediate_size, self.hidden_size)] * 2),
-                "down": WeightSpec([(self.hidden_size, self.intermediate_size)])}
+        specs = {"gate_up": WeightSpec([(self.intermediate_size, self.hidden_size)] * 2),
+                 "down": WeightSpec([(self.hidden_size, self.intermediate_size)])}
+        if self.has_bias:
+            specs["gate_up_bias"] = WeightSpec([(self.intermediate_size,)] * 2)
+            specs["down_bias"] = WeightSpec([(self.hidden_size,)])
+        return specs
+
+    def activation_width(self) -> int:
+        return 3 * self.intermediate_size                    # gate, up and their product
 
     def forward(self, ctx: StepContext, h: torch.Tensor) -> torch.Tensor:
-        if linear.USE_SKINNY and kernels.gemm_skinny_supported(h, self.gate_up):
+        if linear.USE_SKINNY and self.gate_up_bias is None and kernels.gemm_skinny_supported(h, self.gate_up):
             # a decode step: gate, up and the activation in one pass over the weights
             m = torch.empty((h.shape[0], self.intermediate_size), dtype=h.dtype, device=h.device)
             kernels.gemm_skinny(m, h, self.gate_up, fuse_act=self.activation)
             return matmul_tn(m, self.down)
-        gu = matmul_tn(h, self.gate_up)
+        gu = matmul_tn(h, self.gate_up, bias=self.gate_up_bias)
         m = torch.empty((h.shape[0], self.intermediate_size), dtype=h.dtype, device=h.device)
         kernels.gated_act(m, gu, self.activation)
-        return matmul_tn(m, self.down)
+        return matmul_tn(m, self.down, bias=self.down_bias)

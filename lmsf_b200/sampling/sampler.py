@@ -3,7 +3,8 @@
 Order of the reference's Sampler::forward (core/src/model_executor/layers/sampler.rs:839-971): penalties,
 temperature, top-k / top-p, min-p, then greedy (argmax) or random (exponential race) sampling.  Greedy and
 plain temperature rows go through one kernel; rows with top-k / top-p / min-p through a second one that
-finds the kept set by bisection instead of sorting the vocabulary (csrc/sampling.cu).
+finds the kept set by radix selection (six bits of an order-preserving key per pass) instead of sorting the
+vocabulary (csrc/sampling.cu).
 """
 from __future__ import annotations
 

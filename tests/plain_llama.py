@@ -142,6 +142,23 @@ def silu_gated_mlp(h, w_gate, w_up, w_down):
     return ((g / (1.0 + torch.exp(-g))) * u) @ w_down.T
 
 
+def gate_activation(g, name):
+    """silu: x / (1 + e^-x) (vllm/kernels/activation_kernels.cu:26-29); gelu_pytorch_tanh: the tanh form
+    0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))) (activation_kernels.cu:44-51, gelu_new / gelu_fast family)."""
+    if name in ("silu", "swish"):
+        return g / (1.0 + torch.exp(-g))
+    if name in ("gelu_tanh", "gelu_pytorch_tanh"):
+        return 0.5 * g * (1.0 + torch.tanh(0.7978845608028654 * (g + 0.044715 * g * g * g)))
+    raise ValueError(name)
+
+
+def linear(x, w, name):
+    """x W^T + b; the bias is there only when config.json asks for it (core/src/model_executor/layers/linear.rs:95-104)."""
+    y = x @ w[name + ".weight"].T
+    b = w.get(name + ".bias")
+    return y if b is None else y + b
+
+
 def _identity(x):
     return x
 
@@ -152,13 +169,13 @@ def attention_block(cfg, w, prefix, h, positions, inv_freq, r=_identity):
     nh, hd = cfg["num_attention_heads"], head_dim_of(cfg)
     nkv = cfg.get("num_key_value_heads") or nh
     T = h.shape[0]
-    q = r(h @ w[prefix + "q_proj.weight"].T).reshape(T, nh, hd)
-    k = r(h @ w[prefix + "k_proj.weight"].T).reshape(T, nkv, hd)
-    v = r(h @ w[prefix + "v_proj.weight"].T).reshape(T, nkv, hd)
+    q = r(linear(h, w, prefix + "q_proj")).reshape(T, nh, hd)
+    k = r(linear(h, w, prefix + "k_proj")).reshape(T, nkv, hd)
+    v = r(linear(h, w, prefix + "v_proj")).reshape(T, nkv, hd)
     q = r(rotary_neox(q, positions, inv_freq))
     k = r(rotary_neox(k, positions, inv_freq))
     o = r(causal_attention(q, k, v, 1.0 / math.sqrt(hd), cfg.get("sliding_window")))
-    return r(o.reshape(T, nh * hd) @ w[prefix + "o_proj.weight"].T)
+    return r(linear(o.reshape(T, nh * hd), w, prefix + "o_proj"))
 
 
 def forward(cfg, weights, token_ids, dtype=torch.float32, stored=None):
@@ -182,12 +199,13 @@ def forward(cfg, weights, token_ids, dtype=torch.float32, stored=None):
         h = r(rms_norm(x, w[p + "input_layernorm.weight"], eps))
         x = x + attention_block(cfg, w, p + "self_attn.", h, positions, inv_freq, r)
         h = r(rms_norm(x, w[p + "post_attention_layernorm.weight"], eps))
-        if stored is None:
+        act = cfg.get("hidden_act", "silu")
+        if stored is None and act == "silu" and not cfg.get("mlp_bias"):
             x = x + silu_gated_mlp(h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
                                    w[p + "mlp.down_proj.weight"])
         else:
-            g, u = r(h @ w[p + "mlp.gate_proj.weight"].T), r(h @ w[p + "mlp.up_proj.weight"].T)
-            x = x + r(r((g / (1.0 + torch.exp(-g))) * u) @ w[p + "mlp.down_proj.weight"].T)
+            g, u = r(linear(h, w, p + "mlp.gate_proj")), r(linear(h, w, p + "mlp.up_proj"))
+            x = x + r(linear(r(gate_activation(g, act) * u), w, p + "mlp.down_proj"))
     x = r(rms_norm(x, w["model.norm.weight"], eps))
     head = w["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings", False) else w["lm_head.weight"]
     return x @ head.T

@@ -76,7 +76,7 @@ def check_batch(rng, window):
     assert v["positions"].tolist() == [starts[s] + j for s in range(S_pad) for j in range(q[s])]
     assert v["token_seq"].tolist() == [s for s in range(S_pad) for _ in range(q[s])]
     assert v["ctx_len"].tolist() == [starts[s] + q[s] for s in range(S_pad)] == ctx[:S_pad].tolist()
-    assert v["state_slot"].tolist() == [mgr.state_slot(e["id"]) for e in entries] + [0] * (S_pad - S)
+    assert v["state_slot"].tolist() == [mgr.state_slot(e["id"]) for e in entries] + [mgr.num_state_slots] * (S_pad - S)
     assert v["patch_dst"].tolist() == [cu[s + 1] - 1 if e["last_from"] >= 0 else -1 for s, e in enumerate(entries)] + [-1] * (S_pad - S)
     assert v["patch_src"].tolist() == [max(e["last_from"], 0) for e in entries] + [0] * (S_pad - S)
     assert info[5] == int(any(e["last_from"] >= 0 for e in entries))

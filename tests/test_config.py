@@ -44,7 +44,6 @@ def test_rope_parameters_spelling():
     (dict(rope_scaling=dict(rope_type="yarn", factor=2.0)), "yarn"),
     (dict(rope_scaling=dict(rope_type="llama3", factor=2.0)), "lacks"),
     (dict(hidden_act="relu"), "hidden_act"),
-    (dict(attention_bias=True), "bias"),
     (dict(rms_norm_eps=0.0), "rms_norm_eps"),
     (dict(head_dim=15), "head_dim"),
     (dict(torch_dtype="int8"), "torch_dtype"),
@@ -103,6 +102,7 @@ def test_engine_options():
         canonical_dtype("float16")
     assert SchedulerConfig.new(None, 256, 128).max_num_batched_tokens == 2048
     assert SchedulerConfig.new(None, 256, 8192).max_num_batched_tokens == 8192
+    assert SchedulerConfig.new(None, 256, 131072).max_num_batched_tokens == 8192      # prompts are cut into portions
     assert SchedulerConfig.new(48, 4, 128).max_num_batched_tokens == 48
     with pytest.raises(ConfigError):
         CacheConfig(block_size=12)

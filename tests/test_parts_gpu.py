@@ -222,6 +222,104 @@ def test_toy_architecture_is_registered_built_and_stepped(tmp_path, dtype, rel):
         assert worst <= rel * scale, (mode, worst, scale)
 
 
+# ----------------------------------------------------------------------------- a toy with state whose decode steps are replayed from a graph
+
+def _register_toy_graph_state():
+    from lmsf_b200.config.registry import register_architecture
+    from lmsf_b200.parts.base import LayerCall, LayerSpec, Mixer, ModelSpec, PartSpec, StateSpec, WeightSpec, register_part
+    from lmsf_b200.parts.linear import matmul_tn
+
+    @register_part("mixer", "toy_decay_on_device")
+    class ToyDecayOnDevice(Mixer):
+        """The recurrence of toy_decay with every index taken from device tensors, so that a step of single tokens
+        does the same work whatever the requests are and may be replayed from a CUDA graph."""
+        graph_safe = True
+
+        def __init__(self, hidden_size, state_size, decay):
+            self.hidden_size, self.state_size, self.decay = hidden_size, state_size, decay
+
+        def weight_specs(self):
+            return {"w_in": WeightSpec([(self.state_size, self.hidden_size)]),
+                    "w_out": WeightSpec([(self.hidden_size, self.state_size)])}
+
+        def state_spec(self):
+            return StateSpec((self.state_size,))
+
+        def forward(self, ctx, h, cache):
+            u = matmul_tn(h, self.w_in).float()
+            if ctx.n_tokens == ctx.n_seqs:                       # one token per request: all on the device
+                slots = ctx.state_slot.long()
+                s = self.decay * cache.state.index_select(0, slots) + u
+                cache.state.index_copy_(0, slots, s)
+                return matmul_tn(s.to(h.dtype), self.w_out)
+            out, off = torch.empty_like(u), 0
+            for n, slot in zip(ctx.q_lens, ctx.state_slots):
+                s = cache.state[slot]
+                for t in range(off, off + n):
+                    s = self.decay * s + u[t]
+                    out[t] = s
+                cache.state[slot] = s
+                off += n
+            return matmul_tn(out.to(h.dtype), self.w_out)
+
+    def spec(c):
+        H = c["hidden_size"]
+        norm = lambda name: PartSpec("rmsnorm", dict(hidden_size=H, eps=c["eps"]), {"weight": name})
+        layer = LayerSpec("pre_norm", {
+            "mixer_norm": norm("n1"),
+            "mixer": PartSpec("toy_decay_on_device", dict(hidden_size=H, state_size=c["state"], decay=c["decay"]),
+                              {"w_in": "in", "w_out": "out"}),
+            "ffn_norm": norm("n2"),
+            "feed_forward": PartSpec("gated_mlp", dict(hidden_size=H, intermediate_size=c["inter"]),
+                                     {"gate_up": ["g", "u"], "down": "d"})})
+        return ModelSpec(hidden_size=H, vocab_size=c["vocab"], max_model_len=c["max_len"],
+                         embedding=PartSpec("token_embedding", dict(vocab_size=c["vocab"], hidden_size=H), {"weight": "emb"}),
+                         layers=[layer], order=[LayerCall(0)], final_norm=norm("nf"),
+                         lm_head=PartSpec("dense", dict(in_features=H, out_features=c["vocab"], out_dtype="float32"),
+                                          {"weight": "emb"}))
+
+    register_architecture("ToyGraphStateForTests", dict, spec)
+
+
+def test_a_stateful_mixer_in_replayed_decode_steps_keeps_every_request_state(tmp_path):
+    """Three requests decode together; the batch is padded to four with a stand-in request and replayed from a
+    CUDA graph.  The stand-in's state must go to a slot of its own: each request's logits must equal those it
+    gets when it runs alone, step by step, without a graph."""
+    from lmsf_b200.engine.factory import build_model
+    from lmsf_b200.engine.model_runner import ModelRunner, StepEntry
+    _register_toy_graph_state()
+    cfg = dict(architectures=["ToyGraphStateForTests"], hidden_size=40, state=24, decay=0.9, inter=56, vocab=61,
+               eps=1e-5, max_len=64)
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    model, _, tdt = build_model(str(tmp_path), "float32", DEV, load_format="dummy", seed=5)
+    reqs = {f"s{i}": util.random_ids(14, cfg["vocab"], 70 + i) for i in range(3)}
+
+    def run(group, enforce_eager):
+        runner = ModelRunner(model, tdt, DEV, 8, num_blocks=8, max_num_seqs=4, enforce_eager=enforce_eager)
+        mgr = runner.make_cache_manager()
+        for rid in group:
+            mgr.add(rid)
+        rows = {rid: [] for rid in group}
+        lg = runner.step([StepEntry(rid, reqs[rid][:4], [3]) for rid in group], mgr)        # a prompt portion each
+        for j, rid in enumerate(group):
+            rows[rid].append(lg[j].cpu())
+        for t in range(4, 14):                                                               # then one token a step
+            lg = runner.step([StepEntry(rid, [reqs[rid][t]], [0]) for rid in group], mgr)
+            for j, rid in enumerate(group):
+                rows[rid].append(lg[j].cpu())
+        replayed = len(runner._graphs)
+        for rid in group:
+            mgr.free(rid)
+        return rows, replayed
+
+    together, replayed = run(list(reqs), enforce_eager=False)
+    assert replayed > 0                           # the steps of three requests ran from a graph of four
+    for rid in reqs:
+        alone, _ = run([rid], enforce_eager=True)
+        for a, b in zip(together[rid], alone[rid]):
+            assert torch.allclose(a, b, rtol=1e-5, atol=1e-6), rid
+
+
 # ----------------------------------------------------------------------------- a second toy: routing and another position encoding
 
 def _register_toy_routed():

@@ -10,8 +10,6 @@ import util
 
 pytestmark = pytest.mark.gpu
 
-# max |difference| allowed, as a fraction of the largest reference logit
-REL = {"float32": 1e-5, "bfloat16": 5e-2}
 LENGTHS = {"A": [5, 17, 33, 70], "B": [1, 9, 40, 64, 130], "W": [3, 50, 90, 41], "C": [2, 60, 140, 300]}
 
 
@@ -27,15 +25,16 @@ def reference(name, dtype, std, reqs):
     key = (name, dtype, std, tuple(sorted((k, tuple(v)) for k, v in reqs.items())))
     if key not in _ref_cache:
         cfg, w = P.load_model(util.model_folder(name, dtype, std))
-        _ref_cache[key] = {rid: P.forward(cfg, w, toks).numpy() for rid, toks in reqs.items()}
+        _ref_cache[key] = util.oracle_logits(cfg, w, reqs, dtype)
     return _ref_cache[key]
 
 
-def check(rows, ref, dtype, reqs):
+def check(rows, ref, dtype, reqs, std, what=""):
     assert len(rows) == sum(len(t) for t in reqs.values())
-    scale = max(1.0, max(float(np.abs(r).max()) for r in ref.values()))
-    worst = max(float(np.abs(row - ref[rid][pos]).max()) for (rid, pos), row in rows.items())
-    assert worst <= REL[dtype] * scale, f"max |diff| {worst:.3e} at logit scale {scale:.3f}"
+    bound, scale = util.logits_bound(dtype, std, ref)
+    worst = util.worst_difference(rows, ref)
+    util.note_worst(f"replay {what} {dtype} std {std}", worst, bound)
+    assert worst <= bound, f"{what}: max |diff| {worst:.3e} against a bound of {bound:.3e} at logit scale {scale:.3f}"
     return worst
 
 
@@ -54,7 +53,7 @@ def test_every_way_of_cutting_agrees_with_the_plain_implementation(name, dtype, 
         need = traces.max_live_tokens(steps, round_to=bs)      # as few pages as the trace can run with
         out = traces.run_inprocess(folder, dtype, steps, bs, need)
         results[mode] = traces.collect(steps, out)
-        check(results[mode], ref, dtype, reqs)
+        check(results[mode], ref, dtype, reqs, std, f"{name} {mode}")
     if dtype == "float32":
         # the float32 kernels fix the order of every sum: the cut must not change a single bit
         for mode in ("tail32", "portions", "mixed"):
@@ -70,7 +69,7 @@ def test_the_program_itself(dtype):
     steps = traces.mixed(reqs, seed=5, max_live=3)
     folder = util.model_folder(name, dtype, 0.15)
     out = traces.run_program(folder, dtype, steps, traces.max_live_tokens(steps))
-    check(traces.collect(steps, out), reference(name, dtype, 0.15, reqs), dtype, reqs)
+    check(traces.collect(steps, out), reference(name, dtype, 0.15, reqs), dtype, reqs, 0.15, "program")
 
 
 def test_steps_without_wanted_logits_and_requests_that_sit_out():
@@ -92,3 +91,41 @@ def test_steps_without_wanted_logits_and_requests_that_sit_out():
     assert np.abs(out[1][0] - rb[20]).max() < tol
     assert np.abs(out[2] - np.stack([rb[21], rb[22], ra[37]])).max() < tol
     assert np.abs(out[3] - np.stack([ra[39], ra[38]])).max() < tol          # the order of `want` is kept
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("n_live", [21, 40])
+def test_many_live_requests_decoding_together(n_live, dtype):
+    """21 and 40 requests decode at once (decode batches above 16 rows: the graph sizes 24 and 40, one padded with
+    stand-in requests, the products of more than 16 rows with the rotation and the cache write as kernels of
+    their own, one key split per request), each compared with the plain implementation."""
+    name, std = "C", 0.15
+    cfg = util.CONFIGS[name]
+    rng_lengths = [12 + (37 * i) % 90 for i in range(n_live)]
+    reqs = {f"m{i}": util.random_ids(n, cfg["vocab_size"], 500 + i) for i, n in enumerate(rng_lengths)}
+    ref = reference(name, dtype, std, reqs)
+    steps = traces.many_live(reqs, tail=10, per_step=8)
+    bs = util.BLOCK_SIZE[name]
+    out = traces.run_inprocess(util.model_folder(name, dtype, std), dtype, steps, bs,
+                               traces.max_live_tokens(steps, round_to=bs), max_live=n_live)
+    rows = traces.collect(steps, out)
+    full = [s for s in steps if len(s["entries"]) == n_live and all(len(e["tokens"]) == 1 for e in s["entries"])]
+    assert len(full) >= 4                          # steps in which every request brings one token
+    bound, scale = util.logits_bound(dtype, std, ref)
+    worst = util.worst_difference(rows, ref)
+    util.note_worst(f"many live {n_live} {dtype}", worst, bound)
+    assert worst <= bound, (worst, bound, scale)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_request_dropped_in_the_middle_of_its_prompt_and_replayed(dtype):
+    """What preemption by recompute does, at the level of the step function: a live request gives back what it
+    holds after 45 of its 130 tokens, its pages go to the others, and it runs again from its first token."""
+    name, std = "B", 0.15
+    reqs = requests_for(name, seed=4)
+    ref = reference(name, dtype, std, reqs)
+    steps = traces.dropped_and_replayed(reqs, "r4", 45)
+    assert sum(1 for s in steps if "r4" in s["end"]) == 2
+    bs = util.BLOCK_SIZE[name]
+    out = traces.run_inprocess(util.model_folder(name, dtype, std), dtype, steps, bs, traces.max_live_tokens(steps, round_to=bs))
+    check(traces.collect(steps, out), ref, dtype, reqs, std, "dropped and replayed")

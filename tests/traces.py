@@ -71,6 +71,59 @@ def mixed(requests, seed, max_live=4, sizes=(7, 2, 13, 3, 29, 2, 5), tail=12):
     return steps
 
 
+def many_live(requests, tail, per_step=8):
+    """All requests live at once: their prompts (all but the last `tail` tokens) arrive `per_step` requests a step,
+    the newcomers' portions beside single tokens of those that are already decoding; then every step brings one
+    token of every request until all are through."""
+    rids = list(requests)
+    done = {r: 0 for r in rids}
+    steps, k, started = [], 0, 0
+    while any(done[r] < len(requests[r]) for r in rids):
+        entries, end = [], []
+        for r in rids[:started]:
+            if done[r] < len(requests[r]):
+                entries.append({"id": r, "tokens": [requests[r][done[r]]], "want": [0]})
+                done[r] += 1
+        for r in rids[started:started + per_step]:
+            head = max(1, len(requests[r]) - tail)
+            entries.append({"id": r, "tokens": requests[r][:head], "want": [head - 1]})
+            done[r] = head
+        started = min(len(rids), started + per_step)
+        steps.append({"step": k, "entries": entries, "end": []})
+        k += 1
+    steps[-1]["end"] = rids
+    return steps
+
+
+def dropped_and_replayed(requests, victim, cut, sizes=(9, 2, 17, 5)):
+    """Portions of all requests in turn; `victim` is ended after `cut` of its tokens (what it holds is given back,
+    as when a scheduler preempts it) while the others go on, and later starts again from its first token."""
+    steps, k = [], 0
+    done = {r: 0 for r in requests}
+    dropped = False
+    j = 0
+    while any(done[r] < len(requests[r]) for r in requests):
+        entries, end = [], []
+        for r, toks in requests.items():
+            if done[r] >= len(toks):
+                continue
+            n = min(sizes[j % len(sizes)], len(toks) - done[r])
+            j += 1
+            if r == victim and not dropped and done[r] + n >= cut:
+                n = max(1, cut - done[r])
+            entries.append({"id": r, "tokens": toks[done[r]:done[r] + n], "want": list(range(n))})
+            done[r] += n
+            if r == victim and not dropped and done[r] >= cut:
+                end.append(r)                  # freed in the middle of its prompt ...
+                done[r] = 0                    # ... and replayed from token 0 in the steps that follow
+                dropped = True
+            elif done[r] == len(toks):
+                end.append(r)
+        steps.append({"step": k, "entries": entries, "end": end})
+        k += 1
+    return steps
+
+
 def max_live_tokens(steps, round_to=64):
     """The --max-tokens a trace needs: most tokens held at any time, each request rounded up."""
     held, peak = {}, 0

@@ -59,3 +59,70 @@ def cut(tokens, sizes):
         i += n
         k += 1
     return out
+
+
+# ----------------------------------------------------------------------------- bounds of the model-level comparisons
+
+# bfloat16 runs are compared with the plain implementation evaluated with the same stored roundings
+# (plain_llama.forward(stored=torch.bfloat16)); the bound is a fraction of the largest logit, about twice the worst
+# difference seen per standard deviation of the weights (0.0046 at 0.02, 0.017 at 0.15 on the tiny configurations):
+# a page of 16 keys read twice in place of its neighbour moves the logits by 0.2 to 1.2 of their scale, one wrong
+# key by about a sixteenth of that.
+BF16_REL = {0.02: 1.0e-2, 0.05: 2.0e-2, 0.15: 3.5e-2}
+F32_REL = 1e-5
+
+
+def oracle_logits(cfg, weights, reqs, dtype):
+    """{request: logits [T, vocab]} of the plain implementation; for bfloat16 with the engine's stored roundings."""
+    import plain_llama as P
+    import torch
+    stored = torch.bfloat16 if dtype == "bfloat16" else None
+    return {rid: P.forward(cfg, weights, toks, stored=stored).numpy() for rid, toks in reqs.items()}
+
+
+def logits_bound(dtype, std, ref):
+    """The largest |difference| a run in `dtype` may show against `ref` (a dict of logit arrays)."""
+    import numpy as np
+    scale = max(float(np.abs(r).max()) for r in ref.values())
+    if dtype == "float32":
+        return F32_REL * max(1.0, scale), scale
+    return BF16_REL[std] * scale, scale
+
+
+def worst_difference(rows, ref):
+    import numpy as np
+    return max(float(np.abs(row - ref[rid][pos]).max()) for (rid, pos), row in rows.items())
+
+
+def note_worst(what, worst, bound):
+    """Appends the worst difference of a comparison to the file $LMSF_TEST_WORST names (to set bounds by)."""
+    import os
+    path = os.environ.get("LMSF_TEST_WORST")
+    if path:
+        with open(path, "a") as f:
+            f.write(f"{what}\t{worst:.3e}\t{bound:.3e}\t{worst / bound:.3f}\n")
+
+
+def assert_tokens_within_rounding(cfg, weights, prompt, got, dtype, std, temperature=0.0, seed=0):
+    """Every generated token must be the best choice, or within rounding of it, given the tokens generated before
+    it: the plain implementation is run once over prompt + got and the row that predicts got[i] is looked at.
+    float32 runs must pick the best exactly; bfloat16 runs may pick another token whose (noised) score lies within
+    twice the logit bound of the best."""
+    import numpy as np
+    import plain_llama as P
+    import torch
+    stored = torch.bfloat16 if dtype == "bfloat16" else None
+    rows = P.forward(cfg, weights, list(prompt) + list(got), stored=stored)[len(prompt) - 1:len(prompt) - 1 + len(got)]
+    bound, _ = logits_bound(dtype, std, {"x": rows.numpy()})
+    for i, tok in enumerate(got):
+        z = rows[i].double().numpy()
+        if temperature >= 1e-5:
+            z = z / temperature - np.log(P.exponential_noise(seed, i, len(z)))
+            tol = 2.0 * bound / temperature
+        else:
+            tol = 2.0 * bound
+        best = int(np.argmax(z))
+        if dtype == "float32":
+            assert tok == best, (i, tok, best)
+        else:
+            assert z[best] - z[tok] <= tol, (i, tok, best, float(z[best] - z[tok]), tol)
