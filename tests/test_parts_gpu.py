@@ -295,7 +295,7 @@ def test_a_stateful_mixer_in_replayed_decode_steps_keeps_every_request_state(tmp
     reqs = {f"s{i}": util.random_ids(14, cfg["vocab"], 70 + i) for i in range(3)}
 
     def run(group, enforce_eager):
-        runner = ModelRunner(model, tdt, DEV, 8, num_blocks=8, max_num_seqs=4, enforce_eager=enforce_eager)
+        runner = ModelRunner(model, tdt, torch.device(DEV), 8, num_blocks=8, max_num_seqs=4, enforce_eager=enforce_eager)
         mgr = runner.make_cache_manager()
         for rid in group:
             mgr.add(rid)

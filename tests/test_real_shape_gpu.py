@@ -26,7 +26,8 @@ def test_real_layer_sizes(dtype):
     cfg, w = P.load_model(folder)
     reqs = {"a": util.random_ids(300, cfg["vocab_size"], 1), "b": util.random_ids(70, cfg["vocab_size"], 2)}
     ref = util.oracle_logits(cfg, w, reqs, dtype)
-    bound, scale = util.logits_bound(dtype, 0.02, ref)
+    # sums over 4,096 and 14,336 terms round more than the tiny models' do: 0.0103 of the logit scale was seen
+    bound, scale = util.logits_bound(dtype, 0.02, ref, bf16_rel=2.0e-2)
     if dtype == "float32":
         bound *= 2.0                         # sums over 4,096 and 14,336 terms
     # whole; a long portion then single tokens (the decode path and its CUDA graph); mixed portions
