@@ -14,13 +14,17 @@
 //     counted on mbarriers.  Pages of fewer than 8 keys are gathered with cp.async instead;
 //   * an issuing warp launches, for each head, S = Q K^T (M 128, N 128, K head size) into the head's score
 //     buffer in tensor memory and, when the head's P is ready, O += P V (M 128, N head size, K 128) with P
-//     read from tensor memory; completion goes to mbarriers through tcgen05.commit.  The two heads take turns:
-//     one head's products run while the other head's softmax is computed;
+//     read from tensor memory, in two halves of 64 keys: the first half's P V runs while the softmax still works
+//     on the second half; completion goes to mbarriers through tcgen05.commit.  The two heads take turns: one
+//     head's products run while the other head's softmax is computed;
 //   * two groups of four softmax warps, one per head, one query row per thread, with registers moved to them
 //     from the other warps (setmaxnreg): tcgen05.ld of the row's 128 scores, mask where the tile needs one,
 //     running maximum (the accumulator is rescaled only when the maximum grew by more than 2^8, which keeps the
-//     sums exact and saves most read-modify-writes of tensor memory), exponentials in float32, P as bfloat16
-//     pairs written over the first 64 columns of S (tcgen05.st).
+//     sums exact and saves most read-modify-writes of tensor memory), exponentials in float32 with the packed
+//     two-value arithmetic of sm_100 around them, P as bfloat16 pairs written over the first 64 columns of S
+//     (tcgen05.st) and handed over in two halves.
+// The kernel is launched as a programmatic dependent: barriers and tensor memory are set up while the kernel before
+// it drains, and the queries are loaded while the first k and v tiles are already on their way.
 // One block per SM: all 512 columns of tensor memory (S or P of two heads, 128 each; O of two heads, 128 each)
 // and about 193 KB of shared memory (Q of two heads, two stages of k, two of v).  Every wait on an mbarrier is
 // bounded: when one runs out the block raises *error_flag (code 3), frees its tensor memory and returns.
@@ -87,6 +91,23 @@ __device__ __forceinline__ float ex2_approx(float x) {      // 2^x, 0 for -inf
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// Two float32 values in one 64-bit register, for the packed arithmetic of sm_100 (one instruction, two results).
+__device__ __forceinline__ uint64_t pk2(float a, float b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void upk2(uint64_t v, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
 // ---- roles ---------------------------------------------------------------------------------------------
 // warps 0-3: softmax of the first item, one query row per thread (thread t owns lane t % 128 of tensor memory)
 // warps 4-7: softmax of the second item
@@ -120,8 +141,9 @@ __device__ __forceinline__ void gather_tile(uint32_t dst_tile, const PagedKV& kv
 
 __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args a, const __grid_constant__ CUtensorMap kv_map) {
   extern __shared__ unsigned char smem_raw[];
-  // k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages], s_full[item], p_full[item], o_done[item]
-  __shared__ __align__(8) uint64_t bars[4 * kStages + 6];
+  // k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages], s_full[item], p_full[item][half of P],
+  // o_done[item], q_full[item]
+  __shared__ __align__(8) uint64_t bars[4 * kStages + 10];
   __shared__ uint32_t tmem_base_mem;
   __shared__ int failed_mem;
   volatile int* failed = &failed_mem;
@@ -133,9 +155,43 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
   auto v_full = [&](int s) { return bar0 + 8u * (2 * kStages + s); };
   auto v_empty = [&](int s) { return bar0 + 8u * (3 * kStages + s); };
   auto s_full = [&](int x) { return bar0 + 8u * (4 * kStages + x); };
-  auto p_full = [&](int x) { return bar0 + 8u * (4 * kStages + 2 + x); };
-  auto o_done = [&](int x) { return bar0 + 8u * (4 * kStages + 4 + x); };
+  auto p_full = [&](int x, int h) { return bar0 + 8u * (4 * kStages + 2 + 2 * x + h); };
+  auto o_done = [&](int x) { return bar0 + 8u * (4 * kStages + 6 + x); };
+  auto q_full = [&](int x) { return bar0 + 8u * (4 * kStages + 8 + x); };
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  // What needs nothing from global memory comes first, so that it overlaps the tail of the kernel before this
+  // one (programmatic dependent launch): barriers, tensor memory.  Everything that kernel may have written
+  // (q, the pages, the step's tables) is read after pdl_wait().
+  pdl_launch_dependents();
+  if (tid == 0) {
+    // a tile is full after one arrival that announces the copies' bytes (tensor-map copies), or after one
+    // arrival of each producer lane when its cp.async have landed
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(k_full(s), a.use_tma ? 1 : 32);
+      mbar_init(v_full(s), a.use_tma ? 1 : 32);
+      mbar_init(k_empty(s), 1);
+      mbar_init(v_empty(s), 1);
+    }
+    for (int x = 0; x < 2; ++x) {
+      mbar_init(s_full(x), 1);
+      mbar_init(p_full(x, 0), kSoftmaxThreads);
+      mbar_init(p_full(x, 1), kSoftmaxThreads);
+      mbar_init(o_done(x), 1);
+      mbar_init(q_full(x), kSoftmaxThreads);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    failed_mem = 0;
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_mem)), "r"(kTmemCols));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_base_mem;
+  pdl_wait();
 
   // blocks start in the order (all heads of tile 0, all heads of tile 1, ...); the caller lists the tiles that
   // see the most keys first, so the longest blocks are not left for the end
@@ -149,7 +205,10 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
   const int start = ctx - n;
   // A head that is left over (an odd group, or no grouping at all) takes two query tiles instead: this one and
   // the 128 tokens behind it.  The block of that second tile has nothing left to do.
-  if (!two_heads && (q0 & (2 * BM - 1)) != 0) return;
+  if (!two_heads && (q0 & (2 * BM - 1)) != 0) {
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols));
+    return;
+  }
   const bool two = two_heads || q0 + BM < n;                    // the block has a second item
   // item x: a head and 128 query tokens; it sees the keys [lo, hi) in the tiles [tb, te)
   struct Item { int head, q0, rows, hi, lo, tb, te; };
@@ -171,27 +230,6 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
   auto active = [&](int x, int t) { return (x == 0 || two) && t >= it[x].tb && t < it[x].te; };
   const int* table = a.block_table + (size_t)seq * a.max_blocks;
 
-  if (tid == 0) {
-    // a tile is full after one arrival that announces the copies' bytes (tensor-map copies), or after one
-    // arrival of each producer lane when its cp.async have landed
-    for (int s = 0; s < kStages; ++s) {
-      mbar_init(k_full(s), a.use_tma ? 1 : 32);
-      mbar_init(v_full(s), a.use_tma ? 1 : 32);
-      mbar_init(k_empty(s), 1);
-      mbar_init(v_empty(s), 1);
-    }
-    for (int x = 0; x < 2; ++x) {
-      mbar_init(s_full(x), 1);
-      mbar_init(p_full(x), kSoftmaxThreads);
-      mbar_init(o_done(x), 1);
-    }
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    failed_mem = 0;
-  }
-  if (warp == 0) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_mem)), "r"(kTmemCols));
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
-  }
   if (warp < 8 && (warp < 4 || two)) {
     // Q tile of this group's item: [64-wide block][row][128 bytes], rows beyond the portion are zero
     constexpr int kChunks = HD / 8;
@@ -207,11 +245,8 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
     cp_async_commit();
     cp_async_wait<0>();
     fence_async_smem();
+    mbar_arrive(q_full(x));          // the producers' first k and v tiles are on their way meanwhile
   }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = tmem_base_mem;
 
   if (warp >= 8) {
   regs_dec<kRegsOther>();
@@ -278,12 +313,15 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
       }
       umma_commit(leader, s_full(x));
     };
-    auto issue_pv = [&](int x, int j, int jx) {                 // O of item x += P V of tile j, P from tensor memory
+    // O of item x += P V of tile j for the keys of half h (64 of the 128), P from tensor memory
+    auto issue_pv = [&](int x, int j, int jx, int h) {
       const uint64_t dv = dv0 + (uint64_t)(((j % kStages) * kKBytes) >> 4);
 #pragma unroll
-      for (int ks = 0; ks < BN / 16; ++ks)
+      for (int k4 = 0; k4 < BN / 32; ++k4) {
+        const int ks = h * (BN / 32) + k4;
         umma_ts(leader, tmem + kOCol + x * 128, tmem + x * BN + ks * 8, dv + ((ks * 16 * 128) >> 4), idesc_o,
                 (jx > 0 || ks > 0) ? 1u : 0u);
+      }
     };
     // the k tile of tile j is waited for once, before the first S that reads it
     int k_ready = -1;
@@ -295,7 +333,12 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
       k_ready = j;
       return true;
     };
-    bool ok = n_tiles > 0 && k_wait(0);
+    bool ok = n_tiles > 0;
+    for (int x = 0; x < nx && ok; ++x) ok = mbar_wait_f(q_full(x), 0u, failed);
+    if (ok) {
+      fence_async_smem();
+      ok = k_wait(0);
+    }
     if (ok) {
       for (int x = 0; x < nx; ++x)
         if (active(x, tile_begin)) issue_s(x, 0);
@@ -311,13 +354,18 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
       bool v_ready = false;
       for (int x = 0; x < nx && ok; ++x) {
         if (active(x, t)) {
-          ok = mbar_wait_f(p_full(x), (uint32_t)(jx[x] & 1), failed);
+          // the first 64 keys' P is handed over while the softmax still works on the other 64
+          ok = mbar_wait_f(p_full(x, 0), (uint32_t)(jx[x] & 1), failed);
           if (ok && !v_ready) ok = mbar_wait_f(v_full(s), (uint32_t)((j / kStages) & 1), failed);
           if (!ok) break;
           v_ready = true;
           fence_async_smem();
           tc_fence_after();
-          issue_pv(x, j, jx[x]);
+          issue_pv(x, j, jx[x], 0);
+          ok = mbar_wait_f(p_full(x, 1), (uint32_t)(jx[x] & 1), failed);
+          if (!ok) break;
+          tc_fence_after();
+          issue_pv(x, j, jx[x], 1);
           ++jx[x];
           if (!active(x, t + 1)) umma_commit(leader, o_done(x));     // the item's last tile
         }
@@ -368,13 +416,18 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
           if ((key > pos) | (key < row_lo)) sc[i] = -INFINITY;
         }
       }
+      // four chains of three-input maxima: 128 values in 16 dependent steps
       float mx0 = fmax3(sc[0], sc[1], sc[2]), mx1 = fmax3(sc[3], sc[4], sc[5]);
+      float mx2 = fmax3(sc[6], sc[7], sc[8]), mx3 = fmax3(sc[9], sc[10], sc[11]);
 #pragma unroll
-      for (int i = 6; i + 3 < BN; i += 4) {
+      for (int i = 12; i + 7 < BN; i += 8) {
         mx0 = fmax3(mx0, sc[i], sc[i + 1]);
         mx1 = fmax3(mx1, sc[i + 2], sc[i + 3]);
+        mx2 = fmax3(mx2, sc[i + 4], sc[i + 5]);
+        mx3 = fmax3(mx3, sc[i + 6], sc[i + 7]);
       }
-      float mx = fmax3(mx0, mx1, fmaxf(sc[BN - 2], sc[BN - 1]));
+      float mx = fmaxf(fmax3(mx0, mx1, mx2), fmax3(mx3, sc[BN - 4], sc[BN - 3]));
+      mx = fmax3(mx, sc[BN - 2], sc[BN - 1]);
       mx *= sl2;                                                // scores enter the exponent as s * scale * log2(e)
       float alpha = 1.f;
       const bool grow = mx > m_run + kRescaleThreshold;         // also true for the first keys a row sees
@@ -409,23 +462,39 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
       }
       // P as bfloat16 pairs over the first 64 columns of S: keys 2c and 2c + 1 in column c
       const float neg_m = m_run == -INFINITY ? 0.f : -m_run;
-      float l0 = 0.f, l1 = 0.f;
+      // The scaling, the subtraction of the maximum and the row sums are packed (two values per instruction); the
+      // exponentials come from the special-function unit.  (Tried and slower on this kernel: a share of the
+      // exponentials by a polynomial on the FMA pipe, and exponentials of bfloat16 pairs; the softmax warps are
+      // bound by the instructions they issue, not by that unit.)  The first 64 keys' P is handed to the issuing warp
+      // while the other 64 are computed.
+      const uint64_t sl2_2 = pk2(sl2, sl2), neg_m2 = pk2(neg_m, neg_m);
+      uint64_t lsum = pk2(0.f, 0.f);
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         uint32_t w[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const float p0 = ex2_approx(fmaf(sc[h * 64 + 2 * i], sl2, neg_m)), p1 = ex2_approx(fmaf(sc[h * 64 + 2 * i + 1], sl2, neg_m));
-          l0 += p0;
-          l1 += p1;
+          const uint64_t x2 = fma2(pk2(sc[h * 64 + 2 * i], sc[h * 64 + 2 * i + 1]), sl2_2, neg_m2);
+          float p0, p1, x0, x1;
+          upk2(x2, x0, x1);
+          p0 = ex2_approx(x0);
+          p1 = ex2_approx(x1);
+          lsum = add2(lsum, pk2(p0, p1));
           w[i] = pack_bf16(p0, p1);
         }
         tmem_st32_issue(t_s + h * 32, w);
+        if (h == 0) {
+          tmem_wait_st();
+          tc_fence_before();
+          mbar_arrive(p_full(x, 0));
+        }
       }
       tmem_wait_st();
+      float l0, l1;
+      upk2(lsum, l0, l1);
       l_run += l0 + l1;
       tc_fence_before();
-      mbar_arrive(p_full(x));
+      mbar_arrive(p_full(x, 1));
     }
     if (ok && my_tiles > 0) ok = mbar_wait_f(o_done(x), 0u, failed);
     if (ok && my_tiles > 0) {
@@ -535,6 +604,6 @@ LMSF_API int lmsf_attention_prefill_tc(const void* q, long long q_stride, void* 
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  prefill_tc_kernel<<<dim3(n_kv_heads * ((a.group + 1) / 2), n_tiles), kThreadsTotal, kSmemBytes, (cudaStream_t)stream>>>(a, kv_map);
-  return LMSF_LAUNCH_STATUS();
+  return launch_pdl(prefill_tc_kernel, dim3(n_kv_heads * ((a.group + 1) / 2), n_tiles), dim3(kThreadsTotal), kSmemBytes,
+                    (cudaStream_t)stream, a, kv_map);
 }
