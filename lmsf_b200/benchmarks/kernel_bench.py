@@ -162,22 +162,11 @@ def bench_gemm_skinny(args, dev, timer, pk):
     fuse = "silu" if args.fuse_act else None
     out = torch.empty(M, N // 2 if fuse else N, device=dev, dtype=torch.bfloat16)
     t = timer.run(lambda: kernels.gemm_skinny(out, x, w, fuse), args.warmup, args.iters)
+    full = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+    t_lib = timer.run(lambda: torch.mm(x, w.t(), out=full), args.warmup, args.iters)     # the library's plain product
     nbytes = 2 * (M * K + N * K + out.numel())
     return dict(kernel="gemm_skinny", m=M, n=N, k=K, fused_act=bool(fuse), us=t * 1e6, gbs=nbytes / t / 1e9,
-                frac_hbm=nbytes / t / 1e9 / pk["hbm_gbs"])
-
-
-def bench_gemm_stream(args, dev, timer, pk):
-    from lmsf_b200 import kernels
-    M, N, K = args.m, args.n, args.k
-    x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
-    w = torch.randn(N, K, device=dev, dtype=torch.bfloat16)
-    out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
-    t = timer.run(lambda: kernels.gemm_stream(out, x, w), args.warmup, args.iters)
-    t_lib = timer.run(lambda: torch.mm(x, w.t(), out=out), args.warmup, args.iters)
-    nbytes = 2 * (M * K + N * K + out.numel())
-    return dict(kernel="gemm_stream", m=M, n=N, k=K, us=t * 1e6, gbs=nbytes / t / 1e9, frac_hbm=nbytes / t / 1e9 / pk["hbm_gbs"],
-                library_us=t_lib * 1e6)
+                frac_hbm=nbytes / t / 1e9 / pk["hbm_gbs"], library_us=t_lib * 1e6)
 
 
 def bench_sampling(args, dev, timer, pk):
@@ -235,7 +224,7 @@ def bench_gemm_skinny_qkv(args, dev, timer, pk):
 
 BENCHES = {"decode_attention": bench_decode_attention, "prefill_attention": bench_prefill_attention,
            "add_rmsnorm": bench_rmsnorm, "gated_act": bench_gated_act, "rope_cache_write": bench_rope_cache,
-           "gemm": bench_gemm, "gemm_skinny": bench_gemm_skinny, "gemm_stream": bench_gemm_stream, "sampling": bench_sampling, "sampling_filtered": bench_sampling_filtered,
+           "gemm": bench_gemm, "gemm_skinny": bench_gemm_skinny, "sampling": bench_sampling, "sampling_filtered": bench_sampling_filtered,
            "gemm_skinny_qkv": bench_gemm_skinny_qkv}
 
 

@@ -1,5 +1,5 @@
 // tcgen05, tensor memory, mbarrier and tensor-map (TMA) helpers shared by the kernels that run on the
-// 5th-generation tensor cores of sm_100a (attention_tc.cu, gemm_stream.cu).
+// 5th-generation tensor cores of sm_100a (attention_tc.cu).
 #pragma once
 #include <cuda.h>
 

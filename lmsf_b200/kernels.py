@@ -301,11 +301,9 @@ def gemm_skinny_qkv_rope(q_out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, 
     _check(rc, "gemm_skinny.cu", "lmsf_gemm_skinny", SKINNY_DEFINES)
 
 
-# ----------------------------------------------------------------------------- streaming product on tcgen05 (17..128 rows)
+# ----------------------------------------------------------------------------- the device's error word
 
-STREAM_MAX_M = 128
 _ERROR_WORDS = {}
-_STREAM_STATE = {}
 
 
 def error_word(device) -> torch.Tensor:
@@ -316,34 +314,6 @@ def error_word(device) -> torch.Tensor:
     if w is None:
         w = _ERROR_WORDS[key] = torch.zeros(1, dtype=torch.int32, device=device)
     return w
-
-
-def gemm_stream_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
-    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 and 0 < x.shape[0] <= STREAM_MAX_M
-            and x.shape[1] % 8 == 0 and x.stride(1) == 1 and w.stride(1) == 1 and w.stride(0) % 8 == 0
-            and x.stride(0) % 8 == 0 and w.data_ptr() % 16 == 0 and x.data_ptr() % 16 == 0)
-
-
-def gemm_stream(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor):
-    """out[M, N] = x[M, K] w[N, K]^T for M <= 128 (bfloat16 in, bfloat16 or float32 out): W streamed once through
-    tensor-map copies and tcgen05 products by small blocks; the blocks that share a tile of W add up through the
-    shared memory of their thread-block cluster (csrc/gemm_stream.cu)."""
-    M, K = x.shape
-    N = w.shape[0]
-    if not gemm_stream_supported(x, w) or w.shape[1] != K or out.shape != (M, N) or out.stride(1) != 1:
-        raise KernelError(f"gemm_stream: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)} are not taken")
-    if out.dtype not in (torch.bfloat16, torch.float32):
-        raise KernelError("gemm_stream: out must be bfloat16 or float32")
-    key = x.device.index or 0
-    n_sms = _STREAM_STATE.get(key)
-    if n_sms is None:
-        n_sms = _STREAM_STATE[key] = torch.cuda.get_device_properties(x.device).multi_processor_count
-    f = _func("gemm_stream.cu", "lmsf_gemm_stream",
-              [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, c_int,
-               c_void_p, c_void_p])
-    rc = f(_ptr(out), _ptr(x), _ptr(w), M, N, K, x.stride(0), w.stride(0), out.stride(0), int(out.dtype == torch.float32),
-           n_sms, _ptr(error_word(x.device)), _stream())
-    _check(rc, "gemm_stream.cu", "lmsf_gemm_stream")
 
 
 # ----------------------------------------------------------------------------- sampling

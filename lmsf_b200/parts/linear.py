@@ -22,8 +22,6 @@ torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
 
 _MM_HAS_OUT_DTYPE: Optional[bool] = None
 USE_SKINNY = True     # bfloat16 products of up to 16 rows run on this package's weight-streaming kernel
-USE_STREAM = False    # True: products of 17 to 128 rows run on the tcgen05 streaming kernel (csrc/gemm_stream.cu)
-                      # instead of the library; measured slower than the library inside a step, so it is off
 
 
 def matmul_tn(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
@@ -46,11 +44,6 @@ def _product_tn(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtyp
     if USE_SKINNY and kernels.gemm_skinny_supported(x, w) and out_dtype in (torch.bfloat16, torch.float32):
         out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype, device=x.device)
         kernels.gemm_skinny(out, x, w)
-        return out
-    if (USE_STREAM and x.shape[0] <= kernels.STREAM_MAX_M
-            and kernels.gemm_stream_supported(x, w) and out_dtype in (torch.bfloat16, torch.float32)):
-        out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype, device=x.device)
-        kernels.gemm_stream(out, x, w)
         return out
     if out_dtype == x.dtype:
         return torch.mm(x, w.t())

@@ -454,40 +454,6 @@ def test_fused_qkv_rotary_cache_write_equals_the_three_steps(M, nh, nkv, hd, rot
     flag.zero_()
 
 
-@pytest.mark.parametrize("M,N,K", [(64, 4096, 4096), (17, 200, 64), (128, 6144, 1024), (33, 1000, 328), (100, 28, 14336),
-                                   (1, 130, 4096), (48, 128 * 150, 64)])
-def test_gemm_stream_tcgen05_against_its_plain_twin(M, N, K):
-    """The streaming tcgen05 product: tiles held by one block and tiles shared by the 2 to 8 blocks of a cluster,
-    ragged M, N and K; a row's result does not depend on the rows beside it."""
-    from lmsf_b200 import kernels
-    g = torch.Generator().manual_seed(12)
-    d = dev()
-    x = (torch.randn(M, K, generator=g)).bfloat16().to(d)
-    w = (torch.randn(N, K, generator=g) * 0.1).bfloat16().to(d)
-    ref = torch.empty(M, N, device=d)
-    kernels.gemm_tn_simt(ref, x, w)                     # bfloat16 in, float32 FMA accumulation
-    flag = kernels.error_word(d)
-    for odt in (torch.bfloat16, torch.float32):
-        out = torch.full((M, N), float("nan"), dtype=odt, device=d)
-        kernels.gemm_stream(out, x, w)
-        assert flag.item() == 0
-        tol_ = 1e-4 if odt == torch.float32 else 1e-2
-        assert torch.allclose(out.float(), ref, rtol=tol_, atol=tol_ * ref.abs().max().item())
-    if M > 1:
-        alone = torch.empty(M // 2, N, dtype=torch.float32, device=d)
-        kernels.gemm_stream(alone, x[:M // 2], w)
-        assert torch.equal(alone, out[:M // 2])
-    # strided operands (a slice of a wider matrix), as the merged projections are used
-    wide = torch.randn(M, K + 64, generator=g).bfloat16().to(d)
-    out = torch.empty(M, N, dtype=torch.bfloat16, device=d)
-    kernels.gemm_stream(out, wide[:, 8:8 + K], w)
-    ref2 = torch.empty(M, N, device=d)
-    kernels.gemm_tn_simt(ref2, wide[:, 8:8 + K].contiguous(), w)
-    assert torch.allclose(out.float(), ref2, rtol=1e-2, atol=1e-2 * ref2.abs().max().item())
-    with pytest.raises(kernels.KernelError):
-        kernels.gemm_stream(torch.empty(129, N, dtype=torch.bfloat16, device=d), torch.zeros(129, K, dtype=torch.bfloat16, device=d), w)
-
-
 @pytest.mark.parametrize("nh,nkv,hd,bs,window", [(8, 2, 128, 16, 0), (4, 4, 64, 16, 0), (6, 1, 128, 8, 0), (4, 2, 64, 32, 90),
                                                (2, 1, 128, 16, 300), (3, 1, 128, 4, 0), (6, 2, 64, 128, 0), (5, 1, 128, 256, 200),
                                                (2, 2, 64, 2, 70)])
