@@ -177,6 +177,76 @@ def time_prefill(runner, mgr, T, reps, warmup, vocab):
     return statistics.median(times)
 
 
+def measure_shape(cfg, n_layers, ctx_len, batches, steps, warmup, pk, with_prefill=True):
+    """Builds the model of `cfg` with random weights and times decode steps at each batch size of `batches` (requests
+    of ctx_len tokens each) and a prefill of PREFILL_TOKENS tokens.  Returns {batch: (ms per step, launches, clocks)}
+    and the prefill record (or None)."""
+    import torch
+    from lmsf_b200.engine.factory import build_model
+    from lmsf_b200.engine.model_runner import ModelRunner
+    cfg = dict(cfg, num_hidden_layers=n_layers)
+    folder = tempfile.mkdtemp(prefix="lmsf_bench_")
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    nums = model_numbers(cfg, n_layers)
+    dev = torch.device("cuda:0")
+    model, _, dtype = build_model(folder, "bfloat16", dev, load_format="dummy")
+    pages = (max(batches) * (ctx_len + 64) + PREFILL_TOKENS) // BLOCK_SIZE + 64
+    runner = ModelRunner(model, dtype, dev, BLOCK_SIZE, num_blocks=pages, max_num_seqs=max(80, max(batches)),
+                         max_model_len=max(MAX_MODEL_LEN, ctx_len + 64))
+    for t in runner.storage.tensors:
+        t.normal_(0.0, 1.0)
+    mgr = runner.make_cache_manager()
+    V = cfg["vocab_size"]
+    out = {}
+    for b in batches:
+        clocks = ClockSampler()
+        clocks.start()
+        ids = fill_requests(runner, mgr, b, ctx_len, f"b{b}_")
+        ms, launches = time_decode(runner, mgr, ids, steps if b == batches[0] else max(8, steps // 2), warmup, V)
+        rec = clocks.stop()
+        for r in ids:
+            mgr.free(r)
+        out[b] = (ms, launches, rec)
+    prefill = None
+    if with_prefill:
+        pf_ms = time_prefill(runner, mgr, PREFILL_TOKENS, 3, 2, V)
+        pf_flops = prefill_flops(cfg, nums, PREFILL_TOKENS, n_layers)
+        prefill = {"value": round(PREFILL_TOKENS / (pf_ms * 1e-3), 1), "tokens": PREFILL_TOKENS, "ms": round(pf_ms, 3),
+                   "frac": round(pf_flops / (pf_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+    del runner, mgr, model
+    torch.cuda.empty_cache()
+    return out, prefill, nums, folder
+
+
+def other_model_points(pk, steps, warmup):
+    """The other shapes that the baseline names, as points of the same line: Llama-3.2-1B (decode at batch 64 and
+    64 requests under continuous batching) and Llama-2-13B (decode at batch 8 with 4,000-token contexts and a
+    2,048-token prefill).  Each point has its own clock record."""
+    points, clocks = {}, {}
+    cfg = dict(MODELS["llama3.2-1b"])
+    res, _, nums, _ = measure_shape(cfg, cfg["num_hidden_layers"], CONTEXT, [64], steps, warmup, pk, with_prefill=False)
+    ms, _, rec = res[64]
+    points["llama3.2-1b_decode_b64"] = round(64 / (ms * 1e-3), 1)
+    points["llama3.2-1b_decode_b64_hbm_frac"] = round(decode_bytes(nums, 64, CONTEXT) / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+    clocks["llama3.2-1b_decode_b64"] = rec
+    sampler = ClockSampler()
+    sampler.start()
+    srv = serve(cfg, cfg["num_hidden_layers"], 64, 256, 2048, quiet=True)
+    clocks["llama3.2-1b_serve"] = sampler.stop()
+    points["llama3.2-1b_serve_generated_tok_s"] = srv["value"]
+    points["llama3.2-1b_serve_total_tok_s"] = srv["total_tokens_per_s"]
+    cfg = dict(MODELS["llama2-13b"])
+    res, prefill, nums, _ = measure_shape(cfg, cfg["num_hidden_layers"], 4000, [8], steps, warmup, pk)
+    ms, _, rec = res[8]
+    points["llama2-13b_decode_b8_ctx4000"] = round(8 / (ms * 1e-3), 1)
+    points["llama2-13b_decode_b8_ctx4000_hbm_frac"] = round(decode_bytes(nums, 8, 4000) / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+    points["llama2-13b_prefill_2048_tok_s"] = prefill["value"]
+    points["llama2-13b_prefill_2048_frac"] = prefill["frac"]
+    clocks["llama2-13b"] = rec
+    return points, clocks
+
+
 def time_e2e(folder, n_layers, batch, context, steps, warmup, vocab):
     """Decode through the public entry point: every step takes the host's token lists through the scheduler,
     copies the step's inputs from pinned host memory to the device and reads the sampled tokens back."""
@@ -213,7 +283,7 @@ def time_e2e(folder, n_layers, batch, context, steps, warmup, vocab):
     return produced / dt, h2d, batch * 4 + 4
 
 
-def serve(cfg, n_layers, n_requests, decode_tokens, budget):
+def serve(cfg, n_layers, n_requests, decode_tokens, budget, quiet=False):
     """Continuous batching through the engine: requests with seeded uniform-random prompt lengths in [128, 2048],
     `decode_tokens` generated tokens each.  Prints its own JSON line (not the line of the contract)."""
     import random
@@ -243,11 +313,16 @@ def serve(cfg, n_layers, n_requests, decode_tokens, budget):
             steps += 1
         torch.cuda.synchronize()
         dt = time.perf_counter() - t0
-    print(json.dumps({"metric": "generated tokens/s under continuous batching", "value": round(generated / dt, 1),
-                      "unit": "tokens/s", "requests": n_requests, "prompt_tokens": sum(lens), "generated_tokens": generated,
-                      "total_tokens_per_s": round((generated + sum(lens)) / dt, 1), "seconds": round(dt, 3), "steps": steps,
-                      "preemptions": preempted, "max_num_batched_tokens": budget, "layers": n_layers,
-                      "layers_of_model": cfg["num_hidden_layers"], "dtype": "bf16", "data": "synthetic", "impl": "ours"}))
+    rec = {"metric": "generated tokens/s under continuous batching", "value": round(generated / dt, 1),
+           "unit": "tokens/s", "requests": n_requests, "prompt_tokens": sum(lens), "generated_tokens": generated,
+           "total_tokens_per_s": round((generated + sum(lens)) / dt, 1), "seconds": round(dt, 3), "steps": steps,
+           "preemptions": preempted, "max_num_batched_tokens": budget, "layers": n_layers,
+           "layers_of_model": cfg["num_hidden_layers"], "dtype": "bf16", "data": "synthetic", "impl": "ours"}
+    del engine
+    torch.cuda.empty_cache()
+    if quiet:
+        return rec
+    print(json.dumps(rec))
     return 0
 
 
@@ -378,6 +453,7 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--skip-models", action="store_true", help="leave out the points of the 1B and 13B shapes")
     ap.add_argument("--model", default="llama3-8b", choices=sorted(MODELS), help="whose layer sizes to run")
     ap.add_argument("--context", type=int, default=CONTEXT, help="tokens each request holds while decoding is timed")
     ap.add_argument("--serve", action="store_true",
@@ -394,11 +470,6 @@ def main() -> int:
         return 2
     a.warmup = max(a.warmup, 3)
 
-    import torch
-    from lmsf_b200 import kernels
-    from lmsf_b200.engine.factory import build_model
-    from lmsf_b200.engine.model_runner import ModelRunner
-
     pk = peaks()
     cfg = dict(MODELS[a.model])
     if a.serve:
@@ -406,52 +477,28 @@ def main() -> int:
     ctx_len = a.context
     full_layers = cfg["num_hidden_layers"]
     n_layers = a.layers or full_layers
-    cfg["num_hidden_layers"] = n_layers
-    folder = tempfile.mkdtemp(prefix="lmsf_bench_")
-    with open(os.path.join(folder, "config.json"), "w") as f:
-        json.dump(cfg, f)
-    nums = model_numbers(cfg, n_layers)
-    dev = torch.device("cuda:0")
-    model, _, dtype = build_model(folder, "bfloat16", dev, load_format="dummy")
-    max_batch = 64 if not a.skip_points else a.batch
-    pages = (max_batch * (ctx_len + 64) + PREFILL_TOKENS) // BLOCK_SIZE + 64
-    runner = ModelRunner(model, dtype, dev, BLOCK_SIZE, num_blocks=pages, max_num_seqs=80, max_model_len=max(MAX_MODEL_LEN, ctx_len + 64))
-    for t in runner.storage.tensors:
-        t.normal_(0.0, 1.0)
-    mgr = runner.make_cache_manager()
     V = cfg["vocab_size"]
-
-    clocks = ClockSampler()
-    clocks.start()
-    ids = fill_requests(runner, mgr, a.batch, ctx_len, "b")
-    ms, launches = time_decode(runner, mgr, ids, a.steps, a.warmup, V)
-    clock_rec = clocks.stop()
-    for r in ids:
-        mgr.free(r)
+    batches = [a.batch] + ([b for b in (1, 64) if b != a.batch] if not a.skip_points else [])
+    res, prefill, nums, folder = measure_shape(cfg, n_layers, ctx_len, batches, a.steps, a.warmup, pk)
+    ms, launches, clock_rec = res[a.batch]
     value = a.batch / (ms * 1e-3)
     achieved = decode_bytes(nums, a.batch, ctx_len) / (ms * 1e-3) / 1e9
+    points, points_clocks = {}, {}
+    for b in batches[1:]:
+        pms, _, rec = res[b]
+        points[f"decode_b{b}"] = round(b / (pms * 1e-3), 1)
+        points[f"decode_b{b}_hbm_frac"] = round(decode_bytes(nums, b, ctx_len) / (pms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+        points_clocks[f"decode_b{b}"] = rec
 
-    points = {}
-    if not a.skip_points:
-        for b in (1, 64):
-            ids = fill_requests(runner, mgr, b, ctx_len, f"p{b}_")
-            pms, _ = time_decode(runner, mgr, ids, max(8, a.steps // 2), a.warmup, V)
-            for r in ids:
-                mgr.free(r)
-            points[f"decode_b{b}"] = round(b / (pms * 1e-3), 1)
-            points[f"decode_b{b}_hbm_frac"] = round(decode_bytes(nums, b, ctx_len) / (pms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
-
-    pf_ms = time_prefill(runner, mgr, PREFILL_TOKENS, 3, 2, V)
-    pf_flops = prefill_flops(cfg, nums, PREFILL_TOKENS, n_layers)
-    prefill = {"value": round(PREFILL_TOKENS / (pf_ms * 1e-3), 1), "tokens": PREFILL_TOKENS, "ms": round(pf_ms, 3),
-               "frac": round(pf_flops / (pf_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
-
-    del runner, mgr, model
-    torch.cuda.empty_cache()
     e2e = None
     if not a.skip_e2e:
         ev, h2d, d2h = time_e2e(folder, n_layers, a.batch, ctx_len, a.steps, a.warmup, V)
         e2e = {"value": round(ev, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)}
+
+    if not a.skip_points and not a.skip_models and a.model == "llama3-8b" and a.layers is None:
+        more, more_clocks = other_model_points(pk, max(8, a.steps // 2), a.warmup)
+        points.update(more)
+        points_clocks.update(more_clocks)
 
     line = {
         "metric": f"decode tokens/s ({a.model} shape, batch {a.batch}, {ctx_len}-token contexts)", "value": round(value, 1),
@@ -468,7 +515,7 @@ def main() -> int:
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
-        "points": points, "clocks": clock_rec, "gpu_launches": int(launches), "impl": "ours",
+        "points": points, "points_clocks": points_clocks, "clocks": clock_rec, "gpu_launches": int(launches), "impl": "ours",
     }
     if e2e is not None:
         line["e2e"] = e2e

@@ -50,6 +50,8 @@ def main(argv=None) -> int:
             engine.add_request(0, "To be or not to be, ", sp)     # the reference's own prompt
         else:
             engine.add_request(0, None, sp, prompt_token_ids=[1])
+    from ..utils.tracing import profiler_start, profiler_stop
+    profiler_start()                # with LMSF_NVTX=1: the generation is the profiler's region of interest
     start = time.perf_counter()
     steps = generated = 0
     while engine.has_unfinished_requests():
@@ -64,6 +66,7 @@ def main(argv=None) -> int:
         if ns.step_stats:
             print(json.dumps(asdict(engine.last_stats)), file=sys.stderr)
     dt = time.perf_counter() - start
+    profiler_stop()
     print(f"End cost {dt:.3f}s to gen {generated} tokens in {steps} steps ({generated / max(dt, 1e-9):.1f} tok/s)",
           file=sys.stderr)
     return 0

@@ -17,6 +17,7 @@ import torch
 from ..config.engine_config import CacheConfig, EngineArgs, SchedulerConfig, resolve_max_model_len
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler
+from ..utils.tracing import span
 from .factory import build_model
 from .model_runner import ModelRunner, StepEntry
 from .scheduler import Scheduler, SchedulerOutputs
@@ -195,7 +196,8 @@ class LLMEngine:
         t0 = time.perf_counter()
         for seq in self.scheduler.running:
             seq.hold = seq.num_pending > 0 and self._will_finish_by_length(seq)
-        sched: SchedulerOutputs = self.scheduler.schedule()
+        with span("schedule"):
+            sched: SchedulerOutputs = self.scheduler.schedule()
         for seq in sched.ignored:
             seq.finish_time = time.monotonic()
             outputs.append(self._output(seq))
@@ -217,8 +219,9 @@ class LLMEngine:
                     stats.num_decode_tokens += 1
                 else:
                     stats.num_prefill_tokens += e.num_tokens
-            logits = self.runner.step(entries, self.cache, check=False,
-                                      pending_tokens=prev.tokens_dev if prev is not None else None)
+            with span(f"model step ({stats.num_prefill_tokens} prompt + {stats.num_decode_tokens} decoded tokens)"):
+                logits = self.runner.step(entries, self.cache, check=False,
+                                          pending_tokens=prev.tokens_dev if prev is not None else None)
             flight = _InFlight(sampled=sampled, row_of={s.request_id: i for i, s in enumerate(sampled)})
             if prev is not None and any(s.sampling_params.penalties_active for s in sampled):
                 # penalties count the tokens so far: the batch before is retired (its tokens read) between this
@@ -226,9 +229,10 @@ class LLMEngine:
                 self._retire(prev, outputs)
                 self._inflight = None
             if sampled:
-                flight.tokens_dev = self.sampler.sample(
-                    logits, [s.sampling_params for s in sampled], [s.seed for s in sampled],
-                    [len(s.output_token_ids) + s.num_pending for s in sampled], sampled)
+                with span("sample"):
+                    flight.tokens_dev = self.sampler.sample(
+                        logits, [s.sampling_params for s in sampled], [s.seed for s in sampled],
+                        [len(s.output_token_ids) + s.num_pending for s in sampled], sampled)
             # tokens and the device's error word travel to pinned memory behind the step
             n = len(sampled)
             flight.host = self._result_buffer(n + 1)

@@ -12,6 +12,7 @@ from typing import Iterator, List, Optional, Tuple
 import torch
 
 from .. import kernels
+from ..utils.tracing import span
 from .base import (Block, KVCacheSpec, LayerCache, ModelSpec, Part, PartSpec, StateSpec, StepContext, build_part,
                    part_class, with_nested)
 
@@ -69,7 +70,8 @@ class DecoderModel:
         x = self.embedding.forward(ctx)
         res = None
         for j, call in enumerate(self.calls):
-            x, res = self.blocks[call.layer].forward(ctx, x, res, caches[j])
+            with span(f"layer {call.layer}"):
+                x, res = self.blocks[call.layer].forward(ctx, x, res, caches[j])
         n_rows = 0 if logit_rows is None else logit_rows.numel()
         if n_rows == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=x.device)
