@@ -49,6 +49,19 @@ class Timer:
         return statistics.median(times)
 
 
+def reference_kernels():
+    """The reference's own CUDA kernels (baseline/ref_kernels.py, built unmodified for sm_100a), or None where they
+    are not available: the pairs below then carry no `ref_us`."""
+    if ROOT not in sys.path:
+        sys.path.insert(0, ROOT)
+    try:
+        from baseline import ref_kernels
+        ref_kernels.lib()
+        return ref_kernels
+    except Exception:
+        return None
+
+
 def paged(args, dev, batch, ctx):
     """A cache of `batch` requests of `ctx` keys in scattered pages, and one query token each."""
     bs, nkv, hd = args.block_size, args.kv_heads, args.head_dim
@@ -74,8 +87,24 @@ def bench_decode_attention(args, dev, timer, pk):
                                           nh, nkv, hd, splits, scratch)
     t = timer.run(fn, args.warmup, args.iters)
     nbytes = B * ctx * 2 * nkv * hd * 2
-    return dict(kernel="decode_attention", batch=B, ctx=ctx, splits=splits, us=t * 1e6, gbs=nbytes / t / 1e9,
-                frac_hbm=nbytes / t / 1e9 / pk["hbm_gbs"])
+    res = dict(kernel="decode_attention", batch=B, ctx=ctx, splits=splits, us=t * 1e6, gbs=nbytes / t / 1e9,
+               frac_hbm=nbytes / t / 1e9 / pk["hbm_gbs"])
+    rk = reference_kernels()
+    if rk is not None and hd in (64, 80, 96, 112, 128, 256) and args.block_size in (8, 16, 32):
+        # the reference's paged_attention, v1 or v2 by its own rule, on the same keys in its own layout
+        x = 8
+        P, bs = cache.shape[0], args.block_size
+        kc = cache[:, 0].reshape(P, nkv, bs, hd // x, x).permute(0, 1, 3, 2, 4).contiguous()
+        vc = cache[:, 1].permute(0, 1, 3, 2).contiguous()
+        o3, q3 = out.view(B, nh, hd), q.view(B, nh, hd)
+        which = []
+        parts = -(-ctx // rk.PARTITION_SIZE)
+        ws = (torch.empty((B, nh, parts, hd), dtype=q.dtype, device=dev), torch.empty((B, nh, parts), device=dev),
+              torch.empty((B, nh, parts), device=dev))
+        rfn = lambda: which.append(rk.paged_attention(o3, q3, kc, vc, bt, cl, ctx, 1 / math.sqrt(hd), nkv, workspace=ws))
+        res["ref_us"] = timer.run(rfn, args.warmup, args.iters) * 1e6
+        res["ref_kernel"] = "paged_attention_" + which[-1]
+    return res
 
 
 def bench_prefill_attention(args, dev, timer, pk):
@@ -113,7 +142,12 @@ def bench_rmsnorm(args, dev, timer, pk):
     h = torch.empty_like(x)
     t = timer.run(lambda: kernels.add_rmsnorm(h, x, res, w, 1e-5, 2), args.warmup, args.iters)
     nbytes = n * H * (2 + 4 + 4 + 2)
-    return dict(kernel="add_rmsnorm", tokens=n, us=t * 1e6, gbs=nbytes / t / 1e9, frac_hbm=nbytes / t / 1e9 / pk["hbm_gbs"])
+    out = dict(kernel="add_rmsnorm", tokens=n, us=t * 1e6, gbs=nbytes / t / 1e9, frac_hbm=nbytes / t / 1e9 / pk["hbm_gbs"])
+    rk = reference_kernels()
+    if rk is not None:                     # vllm_fused_add_rms_norm: residual in bfloat16, in place
+        xr, rr = x.clone(), res.bfloat16()
+        out["ref_us"] = timer.run(lambda: rk.fused_add_rms_norm(xr, rr, w, 1e-5), args.warmup, args.iters) * 1e6
+    return out
 
 
 def bench_gated_act(args, dev, timer, pk):
@@ -123,7 +157,11 @@ def bench_gated_act(args, dev, timer, pk):
     out = torch.empty(n, I, device=dev, dtype=torch.bfloat16)
     t = timer.run(lambda: kernels.gated_act(out, x, "silu"), args.warmup, args.iters)
     nbytes = n * I * 6
-    return dict(kernel="gated_act", tokens=n, us=t * 1e6, gbs=nbytes / t / 1e9, frac_hbm=nbytes / t / 1e9 / pk["hbm_gbs"])
+    res = dict(kernel="gated_act", tokens=n, us=t * 1e6, gbs=nbytes / t / 1e9, frac_hbm=nbytes / t / 1e9 / pk["hbm_gbs"])
+    rk = reference_kernels()
+    if rk is not None:
+        res["ref_us"] = timer.run(lambda: rk.silu_and_mul(out, x), args.warmup, args.iters) * 1e6
+    return res
 
 
 def bench_rope_cache(args, dev, timer, pk):
@@ -140,7 +178,20 @@ def bench_rope_cache(args, dev, timer, pk):
                                           seq, bt, bs, cache, inv, hd, True, nh, nkv, hd)
     t = timer.run(fn, args.warmup, args.iters)
     nbytes = n * hd * 2 * (2 * nh + 4 * nkv)          # q read+write, k and v read, k and v written to pages
-    return dict(kernel="rope_cache_write", tokens=n, us=t * 1e6, gbs=nbytes / t / 1e9, frac_hbm=nbytes / t / 1e9 / pk["hbm_gbs"])
+    res = dict(kernel="rope_cache_write", tokens=n, us=t * 1e6, gbs=nbytes / t / 1e9, frac_hbm=nbytes / t / 1e9 / pk["hbm_gbs"])
+    rk = reference_kernels()
+    if rk is not None:                     # the reference's two kernels: rotary_embedding, then reshape_and_cache
+        table = rk.cos_sin_cache(500000.0, hd, n, torch.bfloat16, dev, inv)
+        kc, vc = rk.new_caches(blocks, nkv, hd, bs, torch.bfloat16, dev)
+        pos64 = pos.long()
+        slots = (bt[0].long()[pos64 // bs] * bs + pos64 % bs).contiguous()
+        q_, k_, v_ = qkv[:, :nh * hd], qkv[:, nh * hd:(nh + nkv) * hd], qkv[:, (nh + nkv) * hd:]
+
+        def rfn():
+            rk.rotary_embedding(pos64, q_, k_, table, hd, nh, nkv, True)
+            rk.reshape_and_cache(k_, v_, kc, vc, slots, nkv, hd, bs)
+        res["ref_us"] = timer.run(rfn, args.warmup, args.iters) * 1e6
+    return res
 
 
 def bench_gemm(args, dev, timer, pk):
