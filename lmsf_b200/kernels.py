@@ -8,6 +8,7 @@ are an error.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Optional, Sequence, Tuple
 
@@ -241,7 +242,8 @@ def gemm_tn_simt(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor):
 # ----------------------------------------------------------------------------- weight-streaming product (M <= 16)
 
 SKINNY_MAX_M = 16
-SKINNY_DEFINES: Tuple[str, ...] = ()      # build-time constants of gemm_skinny.cu (experiments override them)
+# build-time constants of gemm_skinny.cu; experiments override them, e.g. LMSF_SKINNY_DEFINES=LMSF_SKINNY_XREG=1
+SKINNY_DEFINES: Tuple[str, ...] = tuple(d for d in os.environ.get("LMSF_SKINNY_DEFINES", "").split(",") if d)
 
 
 def gemm_skinny_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
