@@ -85,6 +85,22 @@ class CacheManager:
     def native_id(self, rid) -> int:
         return self._ids[rid]
 
+    # The native scheduler registers and frees requests in the native manager itself; it takes its ids from here
+    # and tells this face afterwards which requests the manager now knows.
+    def new_native_id(self) -> int:
+        nid = self._next_id
+        self._next_id += 1
+        return nid
+
+    def bind(self, rid, nid: int) -> None:
+        self._ids[rid] = nid
+
+    def unbind(self, rid) -> None:
+        self._ids.pop(rid, None)
+
+    def native_has(self, nid: int) -> bool:
+        return bool(self._lib.lmsf_cm_has(self._h, nid))
+
     def _id(self, rid) -> int:
         try:
             return self._ids[rid]

@@ -1,7 +1,7 @@
 """ctypes face of csrc/host_runtime.cpp (compiled with g++ on first use)."""
 from __future__ import annotations
 
-from ctypes import POINTER, c_int, c_int64, c_longlong, c_void_p
+from ctypes import POINTER, c_double, c_int, c_int64, c_longlong, c_void_p
 
 from ..csrc.build import load_library
 
@@ -36,6 +36,16 @@ def lib():
             "lmsf_cm_check": (c_int, [c_void_p]),
             "lmsf_cm_build_batch": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                             c_int, c_int, c_int, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p]),
+            "lmsf_sched_create": (c_void_p, [c_void_p, c_int, c_int, c_int]),
+            "lmsf_sched_destroy": (None, [c_void_p]),
+            "lmsf_sched_add": (c_int, [c_void_p, c_int64, c_double, c_int]),
+            "lmsf_sched_update": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+            "lmsf_sched_remove": (c_int, [c_void_p, c_int64]),
+            "lmsf_sched_queue": (c_int, [c_void_p, c_int, c_void_p, c_int]),
+            "lmsf_sched_num_preemptions": (c_longlong, [c_void_p]),
+            "lmsf_sched_watermark": (c_int, [c_void_p, c_int]),
+            "lmsf_sched_schedule": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                            c_void_p, c_void_p]),
             "lmsf_pool_create": (c_void_p, [c_int]),
             "lmsf_pool_destroy": (None, [c_void_p]),
             "lmsf_pool_allocate": (c_int, [c_void_p]),

@@ -12,6 +12,7 @@
 // Return codes: 0 ok, -1 out of pages / slots, -2 unknown request, -3 request exists, -4 bad argument,
 // -5 page bookkeeping violated (double free, foreign page).
 #include <algorithm>
+#include <cmath>
 #include <cstdint>
 #include <cstring>
 #include <unordered_map>
@@ -401,3 +402,231 @@ LMSF_HOST_API void lmsf_pool_destroy(void* h) { delete static_cast<Pool*>(h); }
 LMSF_HOST_API int lmsf_pool_allocate(void* h) { return static_cast<Pool*>(h)->allocate(); }
 LMSF_HOST_API int lmsf_pool_free(void* h, int b) { return static_cast<Pool*>(h)->release(b); }
 LMSF_HOST_API int lmsf_pool_num_free(void* h) { return (int)static_cast<Pool*>(h)->free_list.size(); }
+
+// ------------------------------------------------------------------------------------------------ the scheduler
+// Role of the reference's Scheduler (core/src/sched/scheduler.rs:336-543, native there): it owns the waiting and
+// running queues and decides every step what runs.  The policy is documented in lmsf_b200/engine/scheduler.py, whose
+// class is a face of this code:
+//   * running requests first, oldest first: one token for a request that decodes, the next portion of its prompt
+//     otherwise, under the token budget; then admissions from the waiting queue, first come first served;
+//   * a running request that cannot get its pages preempts the youngest running request (pages given back, it
+//     returns to the FRONT of the waiting queue and is recomputed later); alone and still too large, it ends;
+//   * admission keeps a watermark of 1 % of the pages free, except into an idle engine; nothing is admitted in a step
+//     that preempted; a prompt beyond max_model_len or the cache's size is ignored;
+//   * a portion that a windowed group could never hold at once is halved until it fits.
+// What the scheduler knows of a request is told before every step (lmsf_sched_update): its length (tokens known or
+// on their way), how many are cached, how many sampled tokens the host has not read yet, whether it is on hold.
+#include <deque>
+
+namespace {
+
+struct SeqState {
+  double arrival = 0.0;
+  int len = 0, num_computed = 0, num_pending = 0, hold = 0;
+};
+
+struct Sched {
+  Manager* cm = nullptr;
+  int max_tokens = 0, max_seqs = 0, max_model_len = 0;
+  std::deque<int64_t> waiting;
+  std::vector<int64_t> running;
+  std::unordered_map<int64_t, SeqState> seqs;
+  std::vector<int> watermark;
+  long long num_preemptions = 0;
+};
+
+Sched* S(void* h) { return static_cast<Sched*>(h); }
+
+void release_request(Sched& s, int64_t rid) {
+  if (s.cm->reqs.count(rid)) lmsf_cm_free(s.cm, rid);
+}
+
+bool fits_alone(const Sched& s, int num_tokens) {
+  const Manager& m = *s.cm;
+  for (size_t g = 0; g < m.pools.size(); ++g) {
+    const int toks = m.windows[g] <= 0 ? num_tokens : std::min(num_tokens, m.windows[g] + 2 * m.block_size);
+    if (m.entries_for(toks) > m.pools[g].n) return false;
+  }
+  return true;
+}
+
+// The portion of n tokens that request rid may run now (see the policy's last point).
+int portion_that_fits(const Sched& s, int64_t rid, int n) {
+  const Manager& m = *s.cm;
+  bool any_window = false;
+  for (int w : m.windows) any_window |= w > 0;
+  if (!any_window) return n;
+  const Request& r = m.reqs.at(rid);
+  bool fits_now = true;
+  for (size_t g = 0; g < m.pools.size(); ++g)
+    if (m.windows[g] > 0 && pages_needed(m, r, n, (int)g) > (int)m.pools[g].free_list.size()) fits_now = false;
+  if (fits_now) return n;
+  std::vector<int> held(m.pools.size(), 0);
+  for (size_t g = 0; g < m.pools.size(); ++g)
+    for (int p : r.tables[g]) held[g] += p >= 0;
+  auto ok = [&](int k) {
+    for (size_t g = 0; g < m.pools.size(); ++g)
+      if (m.windows[g] > 0 && pages_needed(m, r, k, (int)g) + held[g] > m.pools[g].n) return false;
+    return true;
+  };
+  while (n > 1 && !ok(n)) n = std::max(1, n / 2);
+  return n;
+}
+
+}  // namespace
+
+LMSF_HOST_API void* lmsf_sched_create(void* cache_manager, int max_num_batched_tokens, int max_num_seqs, int max_model_len) {
+  if (!cache_manager || max_num_batched_tokens <= 0 || max_num_seqs <= 0) return nullptr;
+  Sched* s = new Sched();
+  s->cm = M(cache_manager);
+  s->max_tokens = max_num_batched_tokens;
+  s->max_seqs = max_num_seqs;
+  s->max_model_len = max_model_len;
+  for (const Pool& p : s->cm->pools) s->watermark.push_back((int)std::nearbyint(0.01 * p.n));   // half to even
+  return s;
+}
+LMSF_HOST_API void lmsf_sched_destroy(void* h) { delete S(h); }
+
+// A new request joins the back of the waiting queue.  Returns -3 if the id is already known.
+LMSF_HOST_API int lmsf_sched_add(void* h, int64_t rid, double arrival, int len) {
+  Sched& s = *S(h);
+  if (s.seqs.count(rid)) return -3;
+  SeqState st;
+  st.arrival = arrival;
+  st.len = len;
+  s.seqs.emplace(rid, st);
+  s.waiting.push_back(rid);
+  return 0;
+}
+
+// What changed about requests since the last step, for n of them.
+LMSF_HOST_API int lmsf_sched_update(void* h, int n, const int64_t* rids, const int* len, const int* num_computed,
+                                    const int* num_pending, const int* hold) {
+  Sched& s = *S(h);
+  for (int i = 0; i < n; ++i) {
+    auto it = s.seqs.find(rids[i]);
+    if (it == s.seqs.end()) return -2;
+    it->second.len = len[i];
+    it->second.num_computed = num_computed[i];
+    it->second.num_pending = num_pending[i];
+    it->second.hold = hold[i];
+  }
+  return 0;
+}
+
+// The request leaves whichever queue holds it (finished or aborted) and gives back what it holds.
+// Returns 1 if it was running, 2 if it was waiting, 0 if it was in neither queue.
+LMSF_HOST_API int lmsf_sched_remove(void* h, int64_t rid) {
+  Sched& s = *S(h);
+  int where = 0;
+  auto r = std::find(s.running.begin(), s.running.end(), rid);
+  if (r != s.running.end()) { s.running.erase(r); where = 1; }
+  else {
+    auto w = std::find(s.waiting.begin(), s.waiting.end(), rid);
+    if (w != s.waiting.end()) { s.waiting.erase(w); where = 2; }
+  }
+  release_request(s, rid);
+  s.seqs.erase(rid);
+  return where;
+}
+
+// which = 0: the waiting queue, 1: the running queue, in their order.  Returns the queue's length.
+LMSF_HOST_API int lmsf_sched_queue(void* h, int which, int64_t* out, int cap) {
+  Sched& s = *S(h);
+  int i = 0;
+  if (which == 0) { for (int64_t r : s.waiting) { if (i < cap) out[i] = r; ++i; } }
+  else { for (int64_t r : s.running) { if (i < cap) out[i] = r; ++i; } }
+  return i;
+}
+LMSF_HOST_API long long lmsf_sched_num_preemptions(void* h) { return S(h)->num_preemptions; }
+LMSF_HOST_API int lmsf_sched_watermark(void* h, int g) { return S(h)->watermark[g]; }
+
+// One step's decisions.  Entries (request, first position, tokens, whether the portion ends the known tokens so that
+// its last place is sampled) go to e_*; requests preempted in this step to pre; requests that end without running
+// (kind 0: the prompt can never fit, "ignored") or because they outgrew the cache (kind 1: "length") to ign_*.
+// counts: entries, preempted, ignored.  cap: room in every output array (the number of requests known is enough).
+// Pages for every entry are reserved in the cache manager.  Returns 0, or -4 when cap is too small.
+LMSF_HOST_API int lmsf_sched_schedule(void* h, int cap, int64_t* e_rid, int* e_start, int* e_n, int* e_wants,
+                                      int64_t* pre, int64_t* ign_rid, int* ign_kind, int* counts) {
+  Sched& s = *S(h);
+  Manager& m = *s.cm;
+  int ne = 0, np = 0, ni = 0;
+  if (cap < (int)s.seqs.size()) return -4;
+  int budget = s.max_tokens;
+  std::stable_sort(s.running.begin(), s.running.end(),
+                   [&](int64_t a, int64_t b) { return s.seqs[a].arrival < s.seqs[b].arrival; });   // age order
+  auto preempt = [&](int64_t victim) {
+    s.running.erase(std::find(s.running.begin(), s.running.end(), victim));
+    release_request(s, victim);
+    s.seqs[victim].num_computed = 0;
+    s.waiting.push_front(victim);
+    pre[np++] = victim;
+    ++s.num_preemptions;
+  };
+  // 1. running requests, oldest first
+  size_t i = 0;
+  while (i < s.running.size() && budget > 0) {
+    const int64_t rid = s.running[i];
+    const SeqState st = s.seqs[rid];
+    const int uncomputed = st.len - st.num_computed;
+    if (st.hold || uncomputed <= 0) { ++i; continue; }        // waits for a token that is still on the device
+    const int n = portion_that_fits(s, rid, std::min(uncomputed, budget));
+    // only the newest pending token can be taken from the device, and only as a portion's last token
+    if (st.num_pending > 1 || (st.num_pending && n < uncomputed)) { ++i; continue; }
+    const int lack = st.num_computed + n - m.reqs.at(rid).num_reserved;
+    bool gone = false;
+    while (lack > 0 && lmsf_cm_can_reserve(&m, rid, lack, 0) != 1) {
+      const int64_t victim = s.running.back();
+      if (victim == rid && s.running.size() == 1 && !fits_alone(s, st.num_computed + n)) {
+        s.running.clear();                                     // alone and still too large for the cache: it ends here
+        release_request(s, rid);
+        s.seqs.erase(rid);
+        ign_rid[ni] = rid;
+        ign_kind[ni++] = 1;
+        gone = true;
+        break;
+      }
+      preempt(victim);
+      if (victim == rid) { gone = true; break; }
+    }
+    if (gone) continue;
+    if (lack > 0 && lmsf_cm_reserve(&m, rid, lack) != 0) return -1;
+    e_rid[ne] = rid; e_start[ne] = st.num_computed; e_n[ne] = n; e_wants[ne++] = n == uncomputed;
+    budget -= n;
+    ++i;
+  }
+  // 2. admissions, first come first served; nothing is admitted in a step that preempted
+  std::vector<int> need(m.pools.size());
+  while (!s.waiting.empty() && budget > 0 && np == 0) {
+    const int64_t rid = s.waiting.front();
+    const SeqState st = s.seqs[rid];
+    if (st.num_pending) break;                                 // preempted with a token still on the device: next step
+    if (st.len > s.max_model_len || !fits_alone(s, st.len)) {
+      s.waiting.pop_front();
+      s.seqs.erase(rid);
+      ign_rid[ni] = rid;
+      ign_kind[ni++] = 0;
+      continue;
+    }
+    if ((int)s.running.size() >= s.max_seqs || m.free_slots.empty()) break;
+    if (lmsf_cm_add(&m, rid) < 0) return -1;
+    const int uncomputed = st.len - st.num_computed;
+    const int n = portion_that_fits(s, rid, std::min(uncomputed, budget));
+    lmsf_cm_pages_needed(&m, rid, n, need.data());
+    const bool idle = s.running.empty();                       // an empty engine admits its first request without a watermark
+    bool room = true;
+    for (size_t g = 0; g < m.pools.size(); ++g)
+      if ((int)m.pools[g].free_list.size() - need[g] < (idle ? 0 : s.watermark[g])) room = false;
+    if (!room) {
+      lmsf_cm_free(&m, rid);
+      break;
+    }
+    if (lmsf_cm_reserve(&m, rid, n) != 0) return -1;
+    s.waiting.pop_front();
+    s.running.push_back(rid);
+    e_rid[ne] = rid; e_start[ne] = st.num_computed; e_n[ne] = n; e_wants[ne++] = n == uncomputed;
+    budget -= n;
+  }
+  counts[0] = ne; counts[1] = np; counts[2] = ni;
+  return 0;
+}

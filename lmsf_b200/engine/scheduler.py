@@ -1,5 +1,8 @@
 """The scheduler: admits requests, cuts prompts into portions under a token budget, keeps decoding,
-and decides what happens when pages run out.  Host only.
+and decides what happens when pages run out.  Host only.  The queues and the decisions live in the native
+runtime (csrc/host_runtime.cpp, lmsf_sched_*), next to the cache manager they act on; the class below is their
+face: it tells the native side what changed about the requests, asks for a step's decisions and hands them out
+as Python objects.
 
 The reference (core/src/sched/scheduler.rs:336-543) runs either a batch of whole prompts or a batch
 of decodes, keeps a third queue for swapped groups and preempts by swap or recompute
@@ -23,8 +26,11 @@ from __future__ import annotations
 
 from collections import deque
 from dataclasses import dataclass, field
-from typing import Deque, Hashable, List, Optional
+from typing import Deque, Dict, Hashable, List, Optional
 
+import numpy as np
+
+from ..cache import native
 from ..cache.manager import CacheManager
 from ..config.engine_config import SchedulerConfig
 from .sequence import Sequence, SequenceStatus
@@ -57,26 +63,60 @@ class Scheduler:
     def __init__(self, config: SchedulerConfig, cache: CacheManager):
         self.config = config
         self.cache = cache
-        self.waiting: Deque[Sequence] = deque()
+        self._lib = native.lib()
+        self._h = self._lib.lmsf_sched_create(cache.handle(), config.max_num_batched_tokens, config.max_num_seqs,
+                                              config.max_model_len)
+        if not self._h:
+            raise ValueError("the scheduler needs a positive token budget and request limit")
+        self._seqs: Dict[int, Sequence] = {}          # native id -> request
+        self._nids: Dict[Hashable, int] = {}          # request id -> native id
+        self.waiting: Deque[Sequence] = deque()       # mirrors of the native queues, in their order
         self.running: List[Sequence] = []
-        self.watermark_pages = [int(round(0.01 * cache.num_total_pages(g))) for g in range(len(cache.groups))]
-        self.num_preemptions = 0
+        self.watermark_pages = [self._lib.lmsf_sched_watermark(self._h, g) for g in range(len(cache.groups))]
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            self._lib.lmsf_sched_destroy(self._h)
+            self._h = None
+
+    @property
+    def num_preemptions(self) -> int:
+        return int(self._lib.lmsf_sched_num_preemptions(self._h))
 
     # ------------------------------------------------------------------ queues
+    def _refresh_queues(self) -> None:
+        n = len(self._seqs)
+        buf = np.empty(max(n, 1), dtype=np.int64)
+        k = self._lib.lmsf_sched_queue(self._h, 0, buf.ctypes.data, n)
+        self.waiting = deque(self._seqs[int(i)] for i in buf[:k])
+        k = self._lib.lmsf_sched_queue(self._h, 1, buf.ctypes.data, n)
+        self.running = [self._seqs[int(i)] for i in buf[:k]]
+
+    def _forget(self, seq: Sequence) -> None:
+        nid = self._nids.pop(seq.request_id)
+        del self._seqs[nid]
+        self.cache.unbind(seq.request_id)
+
     def add_seq(self, seq: Sequence) -> None:
+        nid = self.cache.new_native_id()
+        if self._lib.lmsf_sched_add(self._h, nid, float(seq.arrival_time), len(seq)) != 0:
+            raise KeyError(f"request {seq.request_id!r} is already known to the scheduler")
+        self._seqs[nid] = seq
+        self._nids[seq.request_id] = nid
         seq.status = SequenceStatus.WAITING
         self.waiting.append(seq)
 
     def abort_seq(self, request_id: Hashable) -> Optional[Sequence]:
         """core/src/sched/scheduler.rs:160-196: from whichever queue holds it; pages are given back."""
-        for q in (self.waiting, self.running):
-            for seq in q:
-                if seq.request_id == request_id:
-                    q.remove(seq)
-                    self._release(seq)
-                    seq.status = SequenceStatus.FINISHED_ABORTED
-                    return seq
-        return None
+        nid = self._nids.get(request_id)
+        if nid is None:
+            return None
+        seq = self._seqs[nid]
+        self._lib.lmsf_sched_remove(self._h, nid)
+        self._forget(seq)
+        seq.status = SequenceStatus.FINISHED_ABORTED
+        self._refresh_queues()
+        return seq
 
     def has_unfinished_seqs(self) -> bool:
         return bool(self.waiting or self.running)
@@ -87,119 +127,53 @@ class Scheduler:
     def free_seq(self, seq: Sequence) -> None:
         """A finished request leaves its queue and gives back what it holds.  It is usually running; it waits when
         it was preempted while its last token was still on its way from the device and that token ended it."""
-        for q in (self.running, self.waiting):
-            for i, other in enumerate(q):
-                if other is seq:
-                    del q[i]
-                    break
-        self._release(seq)
-
-    def _release(self, seq: Sequence) -> None:
-        if self.cache.has(seq.request_id):
+        nid = self._nids.get(seq.request_id)
+        if nid is not None and self._seqs[nid] is seq:
+            self._lib.lmsf_sched_remove(self._h, nid)
+            self._forget(seq)
+            self._refresh_queues()
+        elif self.cache.has(seq.request_id):
             self.cache.free(seq.request_id)
 
     # ------------------------------------------------------------------ decisions
-    def _fits_alone(self, num_tokens: int) -> bool:
-        bs = self.cache.block_size
-        for g, spec in enumerate(self.cache.groups):
-            toks = num_tokens if spec.window is None else min(num_tokens, spec.window + 2 * bs)
-            if (toks + bs - 1) // bs > self.cache.num_total_pages(g):
-                return False
-        return True
-
-    def _portion_that_fits(self, seq: Sequence, n: int) -> int:
-        """A portion's pages are all held until its step is over, also those that a window will give back right
-        after it: a portion of n tokens that needs more pages than a windowed group has can never run, however many
-        other requests are preempted.  Such a portion is halved until the pages it adds, beside those the request
-        holds, fit the group; the rest of the prompt follows in the next steps, when the window has moved on."""
-        if all(spec.window is None for spec in self.cache.groups):
-            return n
-        rid = seq.request_id
-        windowed = [g for g, spec in enumerate(self.cache.groups) if spec.window is not None]
-        need = self.cache.pages_needed(rid, n)
-        if all(need[g] <= self.cache.num_free_pages(g) for g in windowed):
-            return n                        # the usual case: the pages are there right now
-        held = {g: sum(1 for p in self.cache.block_table(rid, g) if p >= 0) for g in windowed}
-        while n > 1 and not all(need[g] + held[g] <= self.cache.num_total_pages(g) for g in windowed):
-            n = max(1, n // 2)
-            need = self.cache.pages_needed(rid, n)
-        return n
-
-    def _preempt(self, seq: Sequence, out: SchedulerOutputs) -> None:
-        self.running.remove(seq)
-        self._release(seq)
-        seq.num_computed = 0
-        seq.num_preemptions += 1
-        seq.status = SequenceStatus.WAITING
-        self.waiting.appendleft(seq)
-        out.preempted.append(seq)
-        self.num_preemptions += 1
-
     def schedule(self) -> SchedulerOutputs:
         out = SchedulerOutputs()
-        budget = self.config.max_num_batched_tokens
-        self.running.sort(key=lambda s: s.arrival_time)     # age order (core/src/sched/policy.rs:20-28)
-
-        # 1. running requests, oldest first
-        i = 0
-        while i < len(self.running) and budget > 0:
-            seq = self.running[i]
-            if seq.hold or seq.num_uncomputed <= 0:      # waits for a token that is still on the device
-                i += 1
-                continue
-            n = self._portion_that_fits(seq, min(seq.num_uncomputed, budget))
-            if seq.num_pending > 1 or (seq.num_pending and n < seq.num_uncomputed):
-                # only the newest pending token can be taken from the device, and only as a portion's last token
-                i += 1
-                continue
-            lack = seq.num_computed + n - self.cache.num_reserved(seq.request_id)
-            preempted_self = False
-            while lack > 0 and not self.cache.can_reserve(seq.request_id, lack):
-                victim = self.running[-1]
-                if victim is seq and len(self.running) == 1 and not self._fits_alone(seq.num_computed + n):
-                    # alone and still too large for the cache: it ends here
-                    self.running.remove(seq)
-                    self._release(seq)
-                    seq.status = SequenceStatus.FINISHED_LENGTH
-                    out.ignored.append(seq)
-                    preempted_self = True
-                    break
-                self._preempt(victim, out)
-                if victim is seq:
-                    preempted_self = True
-                    break
-            if preempted_self:
-                continue
-            if lack > 0:
-                self.cache.reserve(seq.request_id, lack)
-            out.entries.append(ScheduledEntry(seq, seq.num_computed, n, n == seq.num_uncomputed))
-            budget -= n
-            i += 1
-
-        # 2. admissions, first come first served; nothing is admitted in a step that preempted
-        while self.waiting and budget > 0 and not out.preempted:
-            seq = self.waiting[0]
-            if seq.num_pending:          # preempted with a token still on the device: next step
-                break
-            if len(seq) > self.config.max_model_len or not self._fits_alone(len(seq)):
-                self.waiting.popleft()
-                seq.status = SequenceStatus.FINISHED_IGNORED
-                out.ignored.append(seq)
-                continue
-            if len(self.running) >= self.config.max_num_seqs or not self.cache.can_add():
-                break
-            self.cache.add(seq.request_id)
-            n = self._portion_that_fits(seq, min(seq.num_uncomputed, budget))
-            need = self.cache.pages_needed(seq.request_id, n)
-            idle = not self.running          # an empty engine admits its first request without a watermark
-            if any(self.cache.num_free_pages(g) - k < (0 if idle else self.watermark_pages[g])
-                   for g, k in enumerate(need)):
-                self.cache.free(seq.request_id)
-                break
-            self.cache.reserve(seq.request_id, n)
-            self.waiting.popleft()
+        n = len(self._seqs)
+        if n == 0:
+            return out
+        seqs = list(self._seqs.items())
+        rids = np.fromiter((nid for nid, _ in seqs), dtype=np.int64, count=n)
+        state = np.empty((4, n), dtype=np.int32)
+        for i, (_, s) in enumerate(seqs):
+            state[0, i], state[1, i], state[2, i], state[3, i] = len(s), s.num_computed, s.num_pending, s.hold
+        ptr = lambda a: a.ctypes.data
+        self._lib.lmsf_sched_update(self._h, n, ptr(rids), ptr(state[0]), ptr(state[1]), ptr(state[2]), ptr(state[3]))
+        e_rid, pre, ign = (np.empty(n, dtype=np.int64) for _ in range(3))
+        e_info = np.empty((3, n), dtype=np.int32)
+        ign_kind = np.empty(n, dtype=np.int32)
+        counts = np.zeros(3, dtype=np.int32)
+        rc = self._lib.lmsf_sched_schedule(self._h, n, ptr(e_rid), ptr(e_info[0]), ptr(e_info[1]), ptr(e_info[2]),
+                                           ptr(pre), ptr(ign), ptr(ign_kind), ptr(counts))
+        if rc != 0:
+            raise RuntimeError(f"the native scheduler failed ({rc})")
+        ne, n_pre, n_ign = (int(c) for c in counts)
+        for i in range(n_pre):
+            seq = self._seqs[int(pre[i])]
+            self.cache.unbind(seq.request_id)
+            seq.num_computed = 0
+            seq.num_preemptions += 1
+            seq.status = SequenceStatus.WAITING
+            out.preempted.append(seq)
+        for i in range(n_ign):
+            seq = self._seqs[int(ign[i])]
+            seq.status = SequenceStatus.FINISHED_LENGTH if ign_kind[i] else SequenceStatus.FINISHED_IGNORED
+            self._forget(seq)
+            out.ignored.append(seq)
+        for i in range(ne):
+            nid = int(e_rid[i])
+            seq = self._seqs[nid]
+            self.cache.bind(seq.request_id, nid)          # the native side has registered it with the cache manager
             seq.status = SequenceStatus.RUNNING
-            self.running.append(seq)
-            out.entries.append(ScheduledEntry(seq, seq.num_computed, n, n == seq.num_uncomputed))
-            budget -= n
+            out.entries.append(ScheduledEntry(seq, int(e_info[0, i]), int(e_info[1, i]), bool(e_info[2, i])))
+        self._refresh_queues()
         return out
