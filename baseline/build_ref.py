@@ -11,8 +11,8 @@ files of its Llama path have torch-free `extern "C"` launchers and compile as th
 
 The flags are the reference's own (vllm/build.rs:118-135: -O3, --default-stream per-thread,
 --use_fast_math, the -U__CUDA_NO_* switches) with the architecture set to sm_100a.  Nothing is
-copied into this repository: the sources are read where the reference lies (`$LMSF_REFERENCE_DIR`,
-default /root/reference) and only the built library is kept, in a folder that git ignores.
+copied into this repository: the sources are read where the reference lies (`$LMSF_REFERENCE_DIR`, by default the
+folder `reference` beside this repository's folder) and only the built library is kept, in a folder that git ignores.
 
     python baseline/build_ref.py        # builds if needed, prints the library's path
 """
@@ -41,7 +41,8 @@ class ReferenceUnavailable(RuntimeError):
 
 
 def reference_dir() -> str:
-    return os.environ.get("LMSF_REFERENCE_DIR", "/root/reference")
+    beside = os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+    return os.environ.get("LMSF_REFERENCE_DIR", beside)
 
 
 def library_path() -> str:
