@@ -10,6 +10,7 @@ its keys from pages, so a portion that starts in the middle of a prompt needs no
 from __future__ import annotations
 
 import math
+import warnings
 from typing import Dict, Optional
 
 import torch
@@ -66,6 +67,11 @@ class PagedAttention(Mixer):
     def prepare(self, dtype, device) -> None:
         if self.position_encoding is not None:
             self.position_encoding.prepare(dtype, device)
+        if dtype == torch.bfloat16 and not kernels.mma_attention_supported(dtype, self.head_dim):
+            # right but slow: said once, so that nobody wonders where the time goes
+            warnings.warn(f"head_dim {self.head_dim} is beyond the tensor-core attention kernels "
+                          f"(up to {kernels.MMA_MAX_HEAD_DIM}); bfloat16 attention runs on the generic kernel",
+                          RuntimeWarning, stacklevel=2)
 
     def forward(self, ctx: StepContext, h: torch.Tensor, cache: LayerCache) -> torch.Tensor:
         group = ctx.groups[cache.group]
