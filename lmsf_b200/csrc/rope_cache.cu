@@ -12,6 +12,10 @@
 
 LMSF_DEFINE_LAST_ERROR(lmsf_rope_cache)
 
+#ifndef LMSF_ROPE_ONE_BLOCK_TOKENS
+#define LMSF_ROPE_ONE_BLOCK_TOKENS 256
+#endif
+
 namespace lmsf {
 
 struct RopeCacheArgs {
@@ -201,9 +205,14 @@ LMSF_API int lmsf_rope_cache_write(void* q, const void* k, const void* v, long l
     const int items = (n_q_heads * (rot / 2) + (cache ? n_kv_heads * (rot / 2 + (head_dim - rot) + head_dim) : 0)) / vec;
     int gy = ceil_div(items > 0 ? items : 1, 128);
     if (gy > 8) gy = 8;
+    // Every block of a token computes the token's angles and looks its page up before it moves a byte: with many
+    // tokens (a prompt portion) one block of 256 threads per token does that once; with few (a decode step) the
+    // token's work is spread over several blocks so that the device is not left empty.
+    int threads = 128;
+    if (n_tokens >= LMSF_ROPE_ONE_BLOCK_TOKENS) { gy = 1; threads = 256; }
     dim3 grid(n_tokens, gy);
-    if (dtype == LMSF_F32) return launch_pdl(rope_cache_vec_kernel<float, 4>, grid, dim3(128), smem, s, a);
-    return launch_pdl(rope_cache_vec_kernel<bf16, 8>, grid, dim3(128), smem, s, a);
+    if (dtype == LMSF_F32) return launch_pdl(rope_cache_vec_kernel<float, 4>, grid, dim3(threads), smem, s, a);
+    return launch_pdl(rope_cache_vec_kernel<bf16, 8>, grid, dim3(threads), smem, s, a);
   }
   const int work = (n_q_heads + 2 * n_kv_heads) * head_dim / 2;
   const int threads = work >= 1024 ? 256 : (work >= 256 ? 128 : 64);
