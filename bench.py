@@ -456,6 +456,7 @@ def main() -> int:
     ap.add_argument("--skip-models", action="store_true", help="leave out the points of the 1B and 13B shapes")
     ap.add_argument("--model", default="llama3-8b", choices=sorted(MODELS), help="whose layer sizes to run")
     ap.add_argument("--context", type=int, default=CONTEXT, help="tokens each request holds while decoding is timed")
+    ap.add_argument("--budget", type=int, default=2048, help="--serve: max_num_batched_tokens of the engine")
     ap.add_argument("--serve", action="store_true",
                     help="instead of the contract's line: 64 requests of 128..2048 prompt tokens and 256 generated "
                          "tokens each through the engine's continuous batching")
@@ -473,7 +474,7 @@ def main() -> int:
     pk = peaks()
     cfg = dict(MODELS[a.model])
     if a.serve:
-        return serve(cfg, a.layers or cfg["num_hidden_layers"], 64, 256, 2048)
+        return serve(cfg, a.layers or cfg["num_hidden_layers"], 64, 256, a.budget)
     ctx_len = a.context
     full_layers = cfg["num_hidden_layers"]
     n_layers = a.layers or full_layers

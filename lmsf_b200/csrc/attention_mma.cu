@@ -26,12 +26,13 @@ namespace fa {
 
 constexpr int HD = LMSF_HEAD_DIM;
 static_assert(HD % 16 == 0 && HD >= 16 && HD <= 128, "head size must be a multiple of 16 between 16 and 128");
-// stages of 64 keys in flight per block: four for head sizes up to 64 (16 KB a stage and less: three blocks still
-// fit an SM, and decoding 64 requests of 2,048 keys gains 10 %), else three
+// stages of 64 keys in flight per block
 #ifdef LMSF_KV_STAGES
 constexpr int kStages = LMSF_KV_STAGES;
 #else
-constexpr int kStages = HD <= 64 ? 4 : 3;
+// head size 64: three stages of 16 KB leave room for four blocks on an SM, so that 64 requests x 8 kv heads run in
+// one wave (with four stages and three blocks per SM they took 72 us a layer in two waves)
+constexpr int kStages = HD < 64 ? 4 : 3;
 #endif
 constexpr int kKSteps = HD / 16;   // k-steps of q k^T; also pairs of 8-wide output tiles of p v
 constexpr float kLog2e = 1.4426950408889634f;
@@ -52,6 +53,7 @@ struct DecodeArgs {
   int n_q_heads, group;                      // group = n_q_heads / n_kv_heads
   int n_splits;
   int cluster;                               // the splits of a request and group of heads form a thread-block cluster
+  int rows;                                  // query heads a block holds at most: min(16, group); sizes the regions in which parts meet
 };
 
 // Online-softmax state of the two rows (lane / 4 and lane / 4 + 8) that a thread holds.
@@ -164,7 +166,7 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(DecodeArgs a) {
         load_stage<HD>(smem_base + (nxt % kStages) * St::kBytes, a.kv, table, kvh, (tile_begin + nxt) * kTileKeys, lo, ctx, table_off);
       cp_async_commit();
     }
-    const uint32_t kbase = smem_base + (i % kStages) * St::kBytes + warp * 16 * St::kRowBytes;
+    const uint32_t kbase = smem_base + (i % kStages) * St::kBytes;       // this warp's rows are warp * 16 ..
     const uint32_t vbase = kbase + kTileKeys * St::kRowBytes;
     const int key0 = (tile_begin + i) * kTileKeys + warp * 16;   // first key of this warp's 16
     if (key0 >= ctx || key0 + 16 <= lo) continue;                // nothing valid (uniform over the warp)
@@ -174,7 +176,7 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(DecodeArgs a) {
     for (int ks = 0; ks < kKSteps; ++ks) {
       uint32_t b[4];
       const int mi = lane >> 3, r = lane & 7;
-      ldmatrix_x4(b, kbase + ((mi >> 1) * 8 + r) * St::kRowBytes + (ks * 16 + (mi & 1) * 8) * 2);
+      ldmatrix_x4(b, kbase + St::off(warp * 16 + (mi >> 1) * 8 + r, ks * 2 + (mi & 1)));
       mma_16816(s[0], qf[ks], b[0], b[1]);
       mma_16816(s[1], qf[ks], b[2], b[3]);
     }
@@ -223,7 +225,7 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(DecodeArgs a) {
       }
       uint32_t b[4];
       const int mi = lane >> 3, r = lane & 7;
-      ldmatrix_x4_trans(b, vbase + ((mi & 1) * 8 + r) * St::kRowBytes + (n2 * 16 + (mi >> 1) * 8) * 2);
+      ldmatrix_x4_trans(b, vbase + St::off(warp * 16 + (mi & 1) * 8 + r, n2 * 2 + (mi >> 1)));
       mma_16816(o[2 * n2], pf, b[0], b[1]);
       mma_16816(o[2 * n2 + 1], pf, b[2], b[3]);
     }
@@ -233,11 +235,14 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(DecodeArgs a) {
   if (a.cluster) cluster_sync_all();        // the stages of every block of the cluster are free: split 0's will hold all parts
 
   // merge the four warps through shared memory (the stages are free now)
+  // (sized by the heads a block really holds, R = min(16, group): 4 for a group of 4, so that the region is a few
+  // KB and the stages alone decide how many blocks an SM takes)
   constexpr int kOS = HD + 8;                                   // padded row: rows fall into different banks
-  float* sm_o = reinterpret_cast<float*>(smem);                 // [4 warps][16 rows][kOS]
-  float* sm_m = sm_o + 4 * 16 * kOS;                            // [4][16]
+  const int R = a.rows;
+  float* sm_o = reinterpret_cast<float*>(smem);                 // [4 warps][R rows][kOS]
+  float* sm_m = sm_o + 4 * R * kOS;                             // [4][16]
   float* sm_l = sm_m + 4 * 16;                                  // [4][16]
-  constexpr int kPS = 16 * HD + 16;                             // one split's part: 16 rows of HD values, 16 log-sum-exp
+  const int kPS = R * HD + 16;                                  // one split's part: R rows of HD values, 16 log-sum-exp
   float* sm_part = sm_l + 4 * 16;                               // [splits][kPS], used in block 0 of a cluster
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
@@ -251,7 +256,7 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(DecodeArgs a) {
   // only the rows of heads that exist are written (4 of the 16 for a group of 4)
 #pragma unroll
   for (int n = 0; n < HD / 8; ++n) {
-    float* row0 = sm_o + (warp * 16 + g4) * kOS + n * 8 + t4 * 2;
+    float* row0 = sm_o + (warp * R + g4) * kOS + n * 8 + t4 * 2;
     if (g4 < n_heads) *reinterpret_cast<float2*>(row0) = make_float2(o[n][0], o[n][1]);
     if (g4 + 8 < n_heads) *reinterpret_cast<float2*>(row0 + 8 * kOS) = make_float2(o[n][2], o[n][3]);
   }
@@ -267,14 +272,14 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(DecodeArgs a) {
       const float mw = sm_m[w * 16 + row];
       const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
       L += sm_l[w * 16 + row] * f;
-      acc += sm_o[(w * 16 + row) * kOS + d] * f;
+      acc += sm_o[(w * R + row) * kOS + d] * f;
     }
     const int head = head0 + row;
     if (a.n_splits == 1) {
       a.out[(size_t)token * a.out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(acc / L);
     } else if (a.cluster) {
       st_cluster_f32(sm_part + split * kPS + row * HD + d, 0, L > 0.f ? acc / L : 0.f);
-      if (d == 0) st_cluster_f32(sm_part + split * kPS + 16 * HD + row, 0, L > 0.f ? M + log2f(L) : -INFINITY);
+      if (d == 0) st_cluster_f32(sm_part + split * kPS + R * HD + row, 0, L > 0.f ? M + log2f(L) : -INFINITY);
     } else {
       const size_t pi = ((size_t)seq * a.n_q_heads + head) * a.n_splits + split;
       a.part_o[pi * HD + d] = L > 0.f ? acc / L : 0.f;
@@ -289,10 +294,10 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(DecodeArgs a) {
     for (int idx = threadIdx.x; idx < n_heads * HD; idx += kThreads) {
       const int row = idx / HD, d = idx % HD;
       float M = -INFINITY;
-      for (int s = 0; s < a.n_splits; ++s) M = fmaxf(M, sm_part[s * kPS + 16 * HD + row]);
+      for (int s = 0; s < a.n_splits; ++s) M = fmaxf(M, sm_part[s * kPS + R * HD + row]);
       float acc = 0.f, L = 0.f;
       for (int s = 0; s < a.n_splits; ++s) {
-        const float lse = sm_part[s * kPS + 16 * HD + row];
+        const float lse = sm_part[s * kPS + R * HD + row];
         const float f = lse == -INFINITY ? 0.f : exp2f(lse - M);
         L += f;
         acc += sm_part[s * kPS + row * HD + d] * f;
@@ -391,23 +396,27 @@ static int cluster_enabled() {
   return v;
 }
 
-static int decode_smem_bytes() {
+static int decode_rows(int group) { return group < 16 ? (group < 1 ? 1 : group) : 16; }
+
+static int decode_smem_bytes(int group) {
   using namespace lmsf::fa;
+  const int R = decode_rows(group);
   const int smem_stages = kStages * St::kBytes;
-  const int smem_merge = (4 * 16 * (HD + 8) + 2 * 4 * 16) * (int)sizeof(float);
+  const int smem_merge = (4 * R * (HD + 8) + 2 * 4 * 16) * (int)sizeof(float);
   const int smem_weights = kMergeWeights * (int)sizeof(float);     // weights of the splits when they are added up
-  const int smem_cluster = smem_merge + kMaxClusterSplits * (16 * HD + 16) * (int)sizeof(float);   // + the parts of a cluster
+  const int smem_cluster = smem_merge + kMaxClusterSplits * (R * HD + 16) * (int)sizeof(float);   // + the parts of a cluster
   int m = smem_stages > smem_merge ? smem_stages : smem_merge;
   if (smem_cluster > m) m = smem_cluster;
   return m > smem_weights ? m : smem_weights;
 }
 
-// Clusters of `cluster_size` blocks of the decode kernel that the device holds at a time (0 on error): the splits of
+// Clusters of `cluster_size` blocks of the decode kernel (for query heads in groups of `group`) that the device holds
+// at a time (0 on error): the splits of
 // a request and kv head form a cluster, and a launch with more clusters than this runs in two waves.
-LMSF_API int lmsf_attention_decode_max_clusters(int cluster_size) {
+LMSF_API int lmsf_attention_decode_max_clusters(int cluster_size, int group) {
   using namespace lmsf::fa;
   if (cluster_size < 1 || cluster_size > kMaxClusterSplits) return 0;
-  const int smem = decode_smem_bytes();
+  const int smem = decode_smem_bytes(group);
   if (cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return 0;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)cluster_size, 1024, 1);
@@ -470,12 +479,13 @@ LMSF_API int lmsf_attention_decode(const void* q, long long q_stride, void* out,
     LMSF_REFUSE("attention: block_size=%d must be a power of two", block_size);
   a.block_table = block_table; a.max_blocks = max_blocks; a.seq_ids = seq_ids; a.cu_q = cu_q; a.ctx_len = ctx_len;
   a.scale = scale; a.window = window; a.n_q_heads = n_q_heads; a.group = group; a.n_splits = n_splits;
-  const int smem = decode_smem_bytes();
-  static bool configured = false;
-  if (!configured) {
+  a.rows = decode_rows(group);
+  const int smem = decode_smem_bytes(group);
+  static int configured = 0;                 // the largest size the kernel has been allowed so far
+  if (smem > configured) {
     cudaError_t e = cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    configured = smem;
   }
   cudaStream_t s = (cudaStream_t)stream;
   a.cluster = n_splits >= 2 && n_splits <= kMaxClusterSplits && cluster_enabled();

@@ -94,7 +94,7 @@ __global__ void __launch_bounds__(kThreads) prefill_kernel(PrefillArgs a) {
       for (int kb = 0; kb < 4; ++kb) {            // 16 keys per ldmatrix
         uint32_t b[4];
         const int mi = lane >> 3, r = lane & 7;
-        ldmatrix_x4(b, kbase + (kb * 16 + (mi >> 1) * 8 + r) * St::kRowBytes + (ks * 16 + (mi & 1) * 8) * 2);
+        ldmatrix_x4(b, kbase + St::off(kb * 16 + (mi >> 1) * 8 + r, ks * 2 + (mi & 1)));
         mma_16816(s[2 * kb], qf[ks], b[0], b[1]);
         mma_16816(s[2 * kb + 1], qf[ks], b[2], b[3]);
       }
@@ -144,7 +144,7 @@ __global__ void __launch_bounds__(kThreads) prefill_kernel(PrefillArgs a) {
       for (int n2 = 0; n2 < kKSteps; ++n2) {
         uint32_t b[4];
         const int mi = lane >> 3, r = lane & 7;
-        ldmatrix_x4_trans(b, vbase + (kb * 16 + (mi & 1) * 8 + r) * St::kRowBytes + (n2 * 16 + (mi >> 1) * 8) * 2);
+        ldmatrix_x4_trans(b, vbase + St::off(kb * 16 + (mi & 1) * 8 + r, n2 * 2 + (mi >> 1)));
         mma_16816(o[2 * n2], pf, b[0], b[1]);
         mma_16816(o[2 * n2 + 1], pf, b[2], b[3]);
       }

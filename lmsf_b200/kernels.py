@@ -413,14 +413,16 @@ def _check_paged(q, out, cache, n_q_heads, n_kv_heads, head_dim, block_size, wha
 _DECODE_MAX_CLUSTERS = {}
 
 
-def decode_max_clusters(head_dim: int) -> Tuple[int, ...]:
-    """For cluster sizes 1..8: how many clusters of that many decode blocks the device holds at a time."""
-    t = _DECODE_MAX_CLUSTERS.get(head_dim)
+def decode_max_clusters(head_dim: int, group: int = 1) -> Tuple[int, ...]:
+    """For cluster sizes 1..8: how many clusters of that many decode blocks the device holds at a time (it depends
+    on the group of query heads per kv head, which sizes a block's shared memory)."""
+    key = (head_dim, min(16, max(1, group)))
+    t = _DECODE_MAX_CLUSTERS.get(key)
     if t is None:
         lib = load_library("attention_mma.cu", _mma_defines(head_dim))
         lib.lmsf_attention_decode_max_clusters.restype = c_int
-        lib.lmsf_attention_decode_max_clusters.argtypes = [c_int]
-        t = _DECODE_MAX_CLUSTERS[head_dim] = tuple(max(1, lib.lmsf_attention_decode_max_clusters(s)) for s in range(1, 9))
+        lib.lmsf_attention_decode_max_clusters.argtypes = [c_int, c_int]
+        t = _DECODE_MAX_CLUSTERS[key] = tuple(max(1, lib.lmsf_attention_decode_max_clusters(s, key[1])) for s in range(1, 9))
     return t
 
 

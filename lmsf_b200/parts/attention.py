@@ -120,7 +120,7 @@ class PagedAttention(Mixer):
                 visible = min(max_ctx, self.window) if self.window else max_ctx
                 splits = kernels.decode_num_splits(ctx.n_decode_seqs, self.num_kv_heads,
                                                    self.num_heads // self.num_kv_heads, visible,
-                                                   kernels.decode_max_clusters(self.head_dim))
+                                                   kernels.decode_max_clusters(self.head_dim, self.num_heads // self.num_kv_heads))
                 need = kernels.attention_decode_scratch_floats(ctx.n_seqs, self.num_heads, splits, self.head_dim)
                 scratch = ctx.extras.get("decode_scratch")
                 if need and (scratch is None or scratch.numel() < need):
