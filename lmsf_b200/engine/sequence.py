@@ -109,7 +109,10 @@ class RequestOutput:
 
     @staticmethod
     def from_sequence(seq: Sequence, text: Optional[str] = None) -> "RequestOutput":
+        """A snapshot of the request.  The generated tokens are copied, since they grow; the prompt is the request's
+        own list, which nothing changes after the request is added (copying it for every request at every step
+        costs more host time than the rest of a step of a small model)."""
         reason = seq.status.value if seq.status.finished else None
-        return RequestOutput(seq.request_id, list(seq.prompt_token_ids),
+        return RequestOutput(seq.request_id, seq.prompt_token_ids,
                              [CompletionOutput(0, text, list(seq.output_token_ids), reason)], seq.status.finished,
                              RequestMetrics(seq.arrival_time, seq.first_token_time, seq.finish_time))
