@@ -28,6 +28,7 @@
 // One block per SM: all 512 columns of tensor memory (S or P of two heads, 128 each; O of two heads, 128 each)
 // and about 193 KB of shared memory (Q of two heads, two stages of k, two of v).  Every wait on an mbarrier is
 // bounded: when one runs out the block raises *error_flag (code 3), frees its tensor memory and returns.
+#include <cstdlib>
 #include <type_traits>
 
 #include "attention_mma.cuh"
@@ -71,6 +72,7 @@ struct Args {
   PagedKV kv;
   const int* block_table; int max_blocks;
   const int* tile_seq; const int* tile_q0;   // one entry per 128 query tokens
+  int n_q_tiles;
   const int* cu_q; const int* ctx_len;
   float scale; int window;
   int n_q_heads, group;
@@ -139,6 +141,49 @@ __device__ __forceinline__ void gather_tile(uint32_t dst_tile, const PagedKV& kv
   }
 }
 
+// A unit of work is a pair of items that share their keys: (a tile of 128 query tokens, a kv head, a pair of its
+// query heads).  Units are numbered with all heads of tile 0 first, then of tile 1, ...; the caller lists the tiles
+// that see the most keys first.
+struct Item { int head, q0, rows, hi, lo, tb, te; };   // a head and 128 query tokens; it sees the keys [lo, hi) in the tiles [tb, te)
+struct Unit {
+  int seq, kvh, head0, q0, tok0, n, start;
+  bool two_heads, two, empty;
+  int lo, hi, tile_begin, n_tiles;           // what either item sees
+  __device__ __forceinline__ Item item(const Args& a, int x) const {
+    Item i;
+    i.head = head0 + (two_heads ? x : 0);
+    i.q0 = q0 + (two_heads ? 0 : x * BM);
+    i.rows = max(0, min(BM, n - i.q0));
+    i.hi = start + i.q0 + i.rows;                               // keys < hi are visible to the item's last row
+    i.lo = a.window > 0 ? max(0, start + i.q0 - a.window + 1) : 0;
+    i.tb = i.lo / BN;
+    i.te = (i.hi + BN - 1) / BN;
+    return i;
+  }
+  __device__ __forceinline__ void load(const Args& a, int unit, int units_per_tile, int pairs) {
+    const int tile = unit / units_per_tile, bx = unit % units_per_tile;
+    seq = a.tile_seq[tile];
+    q0 = a.tile_q0[tile];
+    kvh = bx / pairs;
+    const int pair = bx % pairs;
+    head0 = kvh * a.group + 2 * pair;
+    two_heads = 2 * pair + 1 < a.group;                         // the unit has a second head of the same kv head
+    tok0 = a.cu_q[seq];
+    n = a.cu_q[seq + 1] - tok0;
+    start = a.ctx_len[seq] - n;
+    // A head that is left over (an odd group, or no grouping at all) takes two query tiles instead: this one and
+    // the 128 tokens behind it.  The unit of that second tile is empty.
+    empty = !two_heads && (q0 & (2 * BM - 1)) != 0;
+    two = two_heads || q0 + BM < n;                             // the unit has a second item
+    const Item i0 = item(a, 0), i1 = item(a, 1);
+    lo = i0.lo;                                                 // the second item is never behind the first
+    hi = two ? i1.hi : i0.hi;
+    tile_begin = i0.tb;
+    n_tiles = (two ? i1.te : i0.te) - tile_begin;
+    empty = empty || n_tiles <= 0;
+  }
+};
+
 __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args a, const __grid_constant__ CUtensorMap kv_map) {
   extern __shared__ unsigned char smem_raw[];
   // k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages], s_full[item], p_full[item][half of P],
@@ -193,60 +238,15 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
   const uint32_t tmem = tmem_base_mem;
   pdl_wait();
 
-  // blocks start in the order (all heads of tile 0, all heads of tile 1, ...); the caller lists the tiles that
-  // see the most keys first, so the longest blocks are not left for the end
-  const int tile = blockIdx.y;
-  const int seq = a.tile_seq[tile], q0 = a.tile_q0[tile];
-  const int pairs = (a.group + 1) / 2;                          // blocks per kv head
-  const int kvh = blockIdx.x / pairs, pair = blockIdx.x % pairs;
-  const int head0 = kvh * a.group + 2 * pair;
-  const bool two_heads = 2 * pair + 1 < a.group;                // the block has a second head of the same kv head
-  const int tok0 = a.cu_q[seq], n = a.cu_q[seq + 1] - tok0, ctx = a.ctx_len[seq];
-  const int start = ctx - n;
-  // A head that is left over (an odd group, or no grouping at all) takes two query tiles instead: this one and
-  // the 128 tokens behind it.  The block of that second tile has nothing left to do.
-  if (!two_heads && (q0 & (2 * BM - 1)) != 0) {
-    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols));
-    return;
-  }
-  const bool two = two_heads || q0 + BM < n;                    // the block has a second item
-  // item x: a head and 128 query tokens; it sees the keys [lo, hi) in the tiles [tb, te)
-  struct Item { int head, q0, rows, hi, lo, tb, te; };
-  Item it[2];
-#pragma unroll
-  for (int x = 0; x < 2; ++x) {
-    it[x].head = head0 + (two_heads ? x : 0);
-    it[x].q0 = q0 + (two_heads ? 0 : x * BM);
-    it[x].rows = max(0, min(BM, n - it[x].q0));
-    it[x].hi = start + it[x].q0 + it[x].rows;                   // keys < hi are visible to the item's last row
-    it[x].lo = a.window > 0 ? max(0, start + it[x].q0 - a.window + 1) : 0;
-    it[x].tb = it[x].lo / BN;
-    it[x].te = (it[x].hi + BN - 1) / BN;
-  }
-  // the block walks the tiles that either item sees; item x takes part in tile t when tb <= t < te
-  const int lo = it[0].lo, hi = two ? it[1].hi : it[0].hi;      // the second item is never behind the first
-  const int tile_begin = it[0].tb, tile_end = two ? it[1].te : it[0].te;
-  const int n_tiles = tile_end - tile_begin;
-  auto active = [&](int x, int t) { return (x == 0 || two) && t >= it[x].tb && t < it[x].te; };
-  const int* table = a.block_table + (size_t)seq * a.max_blocks;
-
-  if (warp < 8 && (warp < 4 || two)) {
-    // Q tile of this group's item: [64-wide block][row][128 bytes], rows beyond the portion are zero
-    constexpr int kChunks = HD / 8;
-    const int x = warp >> 2, t = tid & 127;
-#pragma unroll
-    for (int i = 0; i < BM * kChunks / kSoftmaxThreads; ++i) {
-      const int idx = t + i * kSoftmaxThreads;
-      const int row = idx / kChunks, c = idx % kChunks;
-      const bool ok = row < it[x].rows;
-      const bf16* src = ok ? a.q + (size_t)(tok0 + it[x].q0 + row) * a.q_stride + (size_t)it[x].head * HD + c * 8 : a.q;
-      cp_async_16(sQ + x * kQBytes + (c / 8) * (BM * 128) + row * 128 + (((c & 7) ^ (row & 7)) << 4), src, ok ? 16 : 0);
-    }
-    cp_async_commit();
-    cp_async_wait<0>();
-    fence_async_smem();
-    mbar_arrive(q_full(x));          // the producers' first k and v tiles are on their way meanwhile
-  }
+  // The launch has at most one block per SM, and block b of G takes the units b, 2G - 1 - b, 2G + b, 4G - 1 - b,
+  // ...: with a list sorted by length the blocks get nearly equal shares, a block pays for its barriers and tensor
+  // memory once, and its producers fetch the next unit's first keys while the last unit is finished.  The
+  // mbarriers' phases run on through the units, so every role counts what went before (all in the same way).
+  const int pairs = (a.group + 1) / 2;                          // units per kv head and tile
+  const int units_per_tile = a.kv.n_kv_heads * pairs;
+  const int n_units = units_per_tile * a.n_q_tiles;
+  const int G = gridDim.x;
+  auto unit_of = [&](int pass) { return pass * G + ((pass & 1) ? G - 1 - (int)blockIdx.x : (int)blockIdx.x); };
 
   if (warp >= 8) {
   regs_dec<kRegsOther>();
@@ -256,270 +256,346 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
     auto full = [&](int s) { return is_v ? v_full(s) : k_full(s); };
     auto empty = [&](int s) { return is_v ? v_empty(s) : k_empty(s); };
     const uint32_t ring = is_v ? sV : sK;
-    if (a.use_tma) {
-      // Lane i copies box i of a tile: keys [i * rows_box, (i + 1) * rows_box), which lie in one page.  A key
-      // range without a page (beyond the sequence, or before the window) is read from page 0 instead: all its
-      // keys are masked, and the softmax warps clear those rows of v.
-      const int n_box = BN / a.rows_box;
-      const int head_row = (is_v ? a.kv.n_kv_heads : 0) + kvh;
-      auto fetch_page = [&](int t) {
-        const int blk = ((tile_begin + t) * BN + lane * a.rows_box) >> a.kv.block_shift;
-        return (t < n_tiles && lane < n_box && blk < a.max_blocks) ? table[blk] : -1;
-      };
-      int page = fetch_page(0);
-      int issued = 0;                                            // tiles whose copies were issued
-      for (int t = 0; t < n_tiles; ++t) {
-        const int s = t % kStages;
-        const int slot0 = ((tile_begin + t) * BN + lane * a.rows_box) & (a.kv.block_size - 1);
-        const uint32_t dst = ring + s * kKBytes + lane * a.rows_box * 128;
-        if (t >= kStages && !mbar_wait_f(empty(s), (uint32_t)((t / kStages - 1) & 1), failed)) break;
-        const int next_page = fetch_page(t + 1);
-        if (lane == 0) mbar_arrive_expect_tx(full(s), kKBytes);
-        __syncwarp();
-        if (lane < n_box) {
+    int tiles_before = 0;                                        // tiles of the block's earlier units
+    int issued_total = 0;                                        // tiles whose copies were issued
+    bool ok = true;
+    for (int pass = 0; ok; ++pass) {
+      const int unit = unit_of(pass);
+      if (unit >= n_units) break;
+      Unit u;
+      u.load(a, unit, units_per_tile, pairs);
+      if (u.empty) continue;
+      const int* table = a.block_table + (size_t)u.seq * a.max_blocks;
+      if (a.use_tma) {
+        // Lane i copies box i of a tile: keys [i * rows_box, (i + 1) * rows_box), which lie in one page.  A key
+        // range without a page (beyond the sequence, or before the window) is read from page 0 instead: all its
+        // keys are masked, and the softmax warps clear those rows of v.
+        const int n_box = BN / a.rows_box;
+        const int head_row = (is_v ? a.kv.n_kv_heads : 0) + u.kvh;
+        auto fetch_page = [&](int t) {
+          const int blk = ((u.tile_begin + t) * BN + lane * a.rows_box) >> a.kv.block_shift;
+          return (t < u.n_tiles && lane < n_box && blk < a.max_blocks) ? table[blk] : -1;
+        };
+        int page = fetch_page(0);
+        for (int t = 0; t < u.n_tiles; ++t) {
+          const int g = tiles_before + t, s = g % kStages;       // g: the tile counted over all units of the block
+          const int slot0 = ((u.tile_begin + t) * BN + lane * a.rows_box) & (a.kv.block_size - 1);
+          const uint32_t dst = ring + s * kKBytes + lane * a.rows_box * 128;
+          if (g >= kStages && !mbar_wait_f(empty(s), (uint32_t)((g / kStages - 1) & 1), failed)) { ok = false; break; }
+          const int next_page = fetch_page(t + 1);
+          if (lane == 0) mbar_arrive_expect_tx(full(s), kKBytes);
+          __syncwarp();
+          if (lane < n_box) {
 #pragma unroll
-          for (int hb = 0; hb < kHB; ++hb)
-            tma_load_box(dst + hb * (BN * 128), &kv_map, hb * 64, slot0, head_row, max(page, 0), full(s));
+            for (int hb = 0; hb < kHB; ++hb)
+              tma_load_box(dst + hb * (BN * 128), &kv_map, hb * 64, slot0, head_row, max(page, 0), full(s));
+          }
+          issued_total = g + 1;
+          page = next_page;
         }
-        issued = t + 1;
-        page = next_page;
+      } else {
+        for (int t = 0; t < u.n_tiles; ++t) {
+          const int g = tiles_before + t, s = g % kStages;
+          if (g >= kStages && !mbar_wait_f(empty(s), (uint32_t)((g / kStages - 1) & 1), failed)) { ok = false; break; }
+          gather_tile(ring + s * kKBytes, a.kv, table, a.max_blocks, u.kvh, is_v, (u.tile_begin + t) * BN, u.lo, u.hi, lane);
+          cp_async_arrive(full(s));
+        }
       }
-      // no copy of this block may be in flight when it ends, whichever way the loop was left
-      for (int t = max(0, issued - kStages); t < issued; ++t) mbar_wait_drain(full(t % kStages), (uint32_t)((t / kStages) & 1));
+      tiles_before += u.n_tiles;
+    }
+    // no copy of this block may be in flight when it ends, whichever way the loop was left
+    if (a.use_tma) {
+      for (int g = max(0, issued_total - kStages); g < issued_total; ++g) mbar_wait_drain(full(g % kStages), (uint32_t)((g / kStages) & 1));
     } else {
-      for (int t = 0; t < n_tiles; ++t) {
-        const int s = t % kStages;
-        if (t >= kStages && !mbar_wait_f(empty(s), (uint32_t)((t / kStages - 1) & 1), failed)) break;
-        gather_tile(ring + s * kKBytes, a.kv, table, a.max_blocks, kvh, is_v, (tile_begin + t) * BN, lo, hi, lane);
-        cp_async_arrive(full(s));
-      }
       cp_async_wait<0>();
     }
   } else if (warp == 10) {
     // ------------------------------------------------------------------ tensor-core issue
     constexpr uint32_t idesc_s = instr_desc(BM, BN, 0), idesc_o = instr_desc(BM, HD, 1);
-    const int nx = two ? 2 : 1;
     const bool leader = elect_one();
     // descriptors of the first 16 head elements (S) or keys (P V) of each operand; a later slice of 16 adds
     // its byte offset / 16 to the address field
     const uint64_t dq0 = smem_desc(sQ, 16, 1024), dk0 = smem_desc(sK, 16, 1024), dv0 = smem_desc(sV, BN * 128, 1024);
-    // jx: how many tiles item x has had; j: tile counted from the block's first
-    auto issue_s = [&](int x, int j) {                          // S of item x and tile j
-      const uint64_t dq = dq0 + (uint64_t)((x * kQBytes) >> 4), dk = dk0 + (uint64_t)(((j % kStages) * kKBytes) >> 4);
+    int tiles_before = 0;                                        // k (and v) tiles of the block's earlier units
+    int item_tiles_before[2] = {0, 0};                           // tiles that item x has had in them
+    int units_before[2] = {0, 0};                                // earlier units in which item x took part
+    bool ok = true;
+    for (int pass = 0; ok; ++pass) {
+      const int unit = unit_of(pass);
+      if (unit >= n_units) break;
+      Unit u;
+      u.load(a, unit, units_per_tile, pairs);
+      if (u.empty) continue;
+      const Item it0 = u.item(a, 0), it1 = u.item(a, 1);
+      const int nx = u.two ? 2 : 1;
+      const int n_tiles = u.n_tiles, tile_begin = u.tile_begin;
+      auto active = [&](int x, int t) { return x == 0 ? (t >= it0.tb && t < it0.te) : (u.two && t >= it1.tb && t < it1.te); };
+      // jx: how many tiles item x has had in this unit; j: tile counted from the unit's first
+      auto issue_s = [&](int x, int j) {                          // S of item x and tile j
+        const uint64_t dq = dq0 + (uint64_t)((x * kQBytes) >> 4);
+        const uint64_t dk = dk0 + (uint64_t)((((tiles_before + j) % kStages) * kKBytes) >> 4);
 #pragma unroll
-      for (int ks = 0; ks < HD / 16; ++ks) {
-        const uint32_t off_a = (ks / 4) * (BM * 128) + (ks % 4) * 32, off_b = (ks / 4) * (BN * 128) + (ks % 4) * 32;
-        umma(leader, tmem + x * BN, dq + (off_a >> 4), dk + (off_b >> 4), idesc_s, ks > 0);
-      }
-      umma_commit(leader, s_full(x));
-    };
-    // O of item x += P V of tile j for the keys of half h (64 of the 128), P from tensor memory
-    auto issue_pv = [&](int x, int j, int jx, int h) {
-      const uint64_t dv = dv0 + (uint64_t)(((j % kStages) * kKBytes) >> 4);
+        for (int ks = 0; ks < HD / 16; ++ks) {
+          const uint32_t off_a = (ks / 4) * (BM * 128) + (ks % 4) * 32, off_b = (ks / 4) * (BN * 128) + (ks % 4) * 32;
+          umma(leader, tmem + x * BN, dq + (off_a >> 4), dk + (off_b >> 4), idesc_s, ks > 0);
+        }
+        umma_commit(leader, s_full(x));
+      };
+      // O of item x += P V of tile j for the keys of half h (64 of the 128), P from tensor memory
+      auto issue_pv = [&](int x, int j, int jx, int h) {
+        const uint64_t dv = dv0 + (uint64_t)((((tiles_before + j) % kStages) * kKBytes) >> 4);
 #pragma unroll
-      for (int k4 = 0; k4 < BN / 32; ++k4) {
-        const int ks = h * (BN / 32) + k4;
-        umma_ts(leader, tmem + kOCol + x * 128, tmem + x * BN + ks * 8, dv + ((ks * 16 * 128) >> 4), idesc_o,
-                (jx > 0 || ks > 0) ? 1u : 0u);
-      }
-    };
-    // the k tile of tile j is waited for once, before the first S that reads it
-    int k_ready = -1;
-    auto k_wait = [&](int j) {
-      if (k_ready >= j) return true;
-      if (!mbar_wait_f(k_full(j % kStages), (uint32_t)((j / kStages) & 1), failed)) return false;
-      fence_async_smem();
-      tc_fence_after();
-      k_ready = j;
-      return true;
-    };
-    bool ok = n_tiles > 0;
-    for (int x = 0; x < nx && ok; ++x) ok = mbar_wait_f(q_full(x), 0u, failed);
-    if (ok) {
-      fence_async_smem();
-      ok = k_wait(0);
-    }
-    if (ok) {
-      for (int x = 0; x < nx; ++x)
-        if (active(x, tile_begin)) issue_s(x, 0);
-      umma_commit(leader, k_empty(0));
-    }
-    // The two items take turns: while one item's softmax runs, the tensor core works on the other item's
-    // P V and on its next scores.  S of the next tile may overwrite P of this one because the products of one
-    // thread are executed in the order of their issue.
-    int jx[2] = {0, 0};
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      const int s = j % kStages, s1 = (j + 1) % kStages, t = tile_begin + j;
-      const bool more = j + 1 < n_tiles;
-      bool v_ready = false;
-      for (int x = 0; x < nx && ok; ++x) {
-        if (active(x, t)) {
-          // the first 64 keys' P is handed over while the softmax still works on the other 64
-          ok = mbar_wait_f(p_full(x, 0), (uint32_t)(jx[x] & 1), failed);
-          if (ok && !v_ready) ok = mbar_wait_f(v_full(s), (uint32_t)((j / kStages) & 1), failed);
-          if (!ok) break;
-          v_ready = true;
-          fence_async_smem();
-          tc_fence_after();
-          issue_pv(x, j, jx[x], 0);
-          ok = mbar_wait_f(p_full(x, 1), (uint32_t)(jx[x] & 1), failed);
-          if (!ok) break;
-          tc_fence_after();
-          issue_pv(x, j, jx[x], 1);
-          ++jx[x];
-          if (!active(x, t + 1)) umma_commit(leader, o_done(x));     // the item's last tile
+        for (int k4 = 0; k4 < BN / 32; ++k4) {
+          const int ks = h * (BN / 32) + k4;
+          umma_ts(leader, tmem + kOCol + x * 128, tmem + x * BN + ks * 8, dv + ((ks * 16 * 128) >> 4), idesc_o,
+                  (jx > 0 || ks > 0) ? 1u : 0u);
         }
-        if (more && active(x, t + 1)) {
-          ok = k_wait(j + 1);
-          if (!ok) break;
-          issue_s(x, j + 1);
-        }
+      };
+      // the k tile of tile j is waited for once, before the first S that reads it
+      int k_ready = -1;
+      auto k_wait = [&](int j) {
+        if (k_ready >= j) return true;
+        const int g = tiles_before + j;
+        if (!mbar_wait_f(k_full(g % kStages), (uint32_t)((g / kStages) & 1), failed)) return false;
+        fence_async_smem();
+        tc_fence_after();
+        k_ready = j;
+        return true;
+      };
+#pragma unroll
+      for (int x = 0; x < 2; ++x)
+        if (x < nx && ok) ok = mbar_wait_f(q_full(x), (uint32_t)(units_before[x] & 1), failed);
+      if (ok) {
+        fence_async_smem();
+        ok = k_wait(0);
       }
-      if (!ok) break;
-      umma_commit(leader, v_empty(s));
-      if (more) umma_commit(leader, k_empty(s1));
+      if (ok) {
+#pragma unroll
+        for (int x = 0; x < 2; ++x)
+          if (x < nx && active(x, tile_begin)) issue_s(x, 0);
+        umma_commit(leader, k_empty(tiles_before % kStages));
+      }
+      // The two items take turns: while one item's softmax runs, the tensor core works on the other item's
+      // P V and on its next scores.  S of the next tile may overwrite P of this one because the products of one
+      // thread are executed in the order of their issue.
+      int jx[2] = {0, 0};
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int g = tiles_before + j, s = g % kStages, s1 = (g + 1) % kStages, t = tile_begin + j;
+        const bool more = j + 1 < n_tiles;
+        bool v_ready = false;
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          if (x >= nx || !ok) continue;
+          if (active(x, t)) {
+            // the first 64 keys' P is handed over while the softmax still works on the other 64
+            const uint32_t p_phase = (uint32_t)((item_tiles_before[x] + jx[x]) & 1);
+            ok = mbar_wait_f(p_full(x, 0), p_phase, failed);
+            if (ok && !v_ready) ok = mbar_wait_f(v_full(s), (uint32_t)((g / kStages) & 1), failed);
+            if (!ok) continue;
+            v_ready = true;
+            fence_async_smem();
+            tc_fence_after();
+            issue_pv(x, j, jx[x], 0);
+            ok = mbar_wait_f(p_full(x, 1), p_phase, failed);
+            if (!ok) continue;
+            tc_fence_after();
+            issue_pv(x, j, jx[x], 1);
+            ++jx[x];
+            if (!active(x, t + 1)) umma_commit(leader, o_done(x));     // the item's last tile
+          }
+          if (more && active(x, t + 1)) {
+            ok = k_wait(j + 1);
+            if (!ok) continue;
+            issue_s(x, j + 1);
+          }
+        }
+        if (!ok) break;
+        umma_commit(leader, v_empty(s));
+        if (more) umma_commit(leader, k_empty(s1));
+      }
+      tiles_before += n_tiles;
+      item_tiles_before[0] += it0.te - it0.tb;
+      units_before[0] += 1;
+      if (u.two) {
+        item_tiles_before[1] += it1.te - it1.tb;
+        units_before[1] += 1;
+      }
     }
   }
-  } else if (warp < 4 || two) {
-    // ------------------------------------------------------------------ softmax of head x
+  } else {
+    // ------------------------------------------------------------------ softmax of item x
     regs_inc<kRegsSoftmax>();
     const int x = warp >> 2, row = tid & 127;
-    const Item me = it[x];
-    const bool row_ok = row < me.rows;
-    const int pos = start + me.q0 + min(row, me.rows - 1);         // this thread's query position
-    const int row_lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
     const uint32_t t_row = tmem + ((uint32_t)((warp & 3) * 32) << 16);   // this warp's 32 lanes of tensor memory
     const uint32_t t_s = t_row + x * BN, t_o = t_row + kOCol + x * 128;
-    float m_run = -INFINITY, l_run = 0.f;
     const float sl2 = a.scale * kLog2e;
-    const int my_tiles = me.te - me.tb;
+    int tiles_before = 0;                                          // k (and v) tiles of the block's earlier units
+    int my_tiles_before = 0;                                       // tiles that this item has had in them
+    int my_units_before = 0;                                       // earlier units in which this item took part
     bool ok = true;
-    for (int j = 0; j < my_tiles; ++j) {                           // j counts this item's tiles
-      // S of the tile is complete, and with it every product issued before it: P V of the tile before too
-      ok = mbar_wait_f(s_full(x), (uint32_t)(j & 1), failed);
-      if (!ok) break;
-      tc_fence_after();
-      const int key0 = (me.tb + j) * BN;
-      const int ju = me.tb + j - tile_begin;                       // the tile counted from the block's first: its stage
-      // Only tiles that reach past some row's position (the diagonal) or before its window need the mask;
-      // the test is the same for the whole group of warps.
-      const bool need_mask = key0 + BN - 1 > start + me.q0 || (a.window > 0 && key0 < start + me.q0 + me.rows - a.window);
-      // the row's 128 scores: four loads in flight, one wait
-      float sc[BN];
+    for (int pass = 0; ok; ++pass) {
+      const int unit = unit_of(pass);
+      if (unit >= n_units) break;
+      Unit u;
+      u.load(a, unit, units_per_tile, pairs);
+      if (u.empty) continue;
+      if (x == 1 && !u.two) {
+        tiles_before += u.n_tiles;
+        continue;
+      }
+      const Item me = u.item(a, x);
+      {
+        // Q tile of this item: [64-wide block][row][128 bytes], rows beyond the portion are zero.  The products
+        // that read the last unit's queries are complete: the group has waited for the last scores.
+        constexpr int kChunks = HD / 8;
 #pragma unroll
-      for (int c0 = 0; c0 < BN; c0 += 32) tmem_ld32_issue(t_s + c0, sc + c0);
-      tmem_wait_ld();
-      if (need_mask) {      // keys that the row does not see become -inf; most tiles skip the test
-#pragma unroll
-        for (int i = 0; i < BN; ++i) {
-          const int key = key0 + i;
-          if ((key > pos) | (key < row_lo)) sc[i] = -INFINITY;
+        for (int i = 0; i < BM * kChunks / kSoftmaxThreads; ++i) {
+          const int idx = row + i * kSoftmaxThreads;
+          const int r = idx / kChunks, c = idx % kChunks;
+          const bool in = r < me.rows;
+          const bf16* src = in ? a.q + (size_t)(u.tok0 + me.q0 + r) * a.q_stride + (size_t)me.head * HD + c * 8 : a.q;
+          cp_async_16(sQ + x * kQBytes + (c / 8) * (BM * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4), src, in ? 16 : 0);
         }
+        cp_async_commit();
+        cp_async_wait<0>();
+        fence_async_smem();
+        mbar_arrive(q_full(x));          // the producers' first k and v tiles are on their way meanwhile
       }
-      // four chains of three-input maxima: 128 values in 16 dependent steps
-      float mx0 = fmax3(sc[0], sc[1], sc[2]), mx1 = fmax3(sc[3], sc[4], sc[5]);
-      float mx2 = fmax3(sc[6], sc[7], sc[8]), mx3 = fmax3(sc[9], sc[10], sc[11]);
+      const bool row_ok = row < me.rows;
+      const int pos = u.start + me.q0 + min(row, me.rows - 1);       // this thread's query position
+      const int row_lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+      float m_run = -INFINITY, l_run = 0.f;
+      const int my_tiles = me.te - me.tb;
+      for (int j = 0; j < my_tiles; ++j) {                           // j counts this item's tiles
+        // S of the tile is complete, and with it every product issued before it: P V of the tile before too
+        ok = mbar_wait_f(s_full(x), (uint32_t)((my_tiles_before + j) & 1), failed);
+        if (!ok) break;
+        tc_fence_after();
+        const int key0 = (me.tb + j) * BN;
+        const int ju = tiles_before + me.tb + j - u.tile_begin;      // the tile counted over the block's units: its stage
+        // Only tiles that reach past some row's position (the diagonal) or before its window need the mask;
+        // the test is the same for the whole group of warps.
+        const bool need_mask = key0 + BN - 1 > u.start + me.q0 || (a.window > 0 && key0 < u.start + me.q0 + me.rows - a.window);
+        // the row's 128 scores: four loads in flight, one wait
+        float sc[BN];
 #pragma unroll
-      for (int i = 12; i + 7 < BN; i += 8) {
-        mx0 = fmax3(mx0, sc[i], sc[i + 1]);
-        mx1 = fmax3(mx1, sc[i + 2], sc[i + 3]);
-        mx2 = fmax3(mx2, sc[i + 4], sc[i + 5]);
-        mx3 = fmax3(mx3, sc[i + 6], sc[i + 7]);
+        for (int c0 = 0; c0 < BN; c0 += 32) tmem_ld32_issue(t_s + c0, sc + c0);
+        tmem_wait_ld();
+        if (need_mask) {      // keys that the row does not see become -inf; most tiles skip the test
+#pragma unroll
+          for (int i = 0; i < BN; ++i) {
+            const int key = key0 + i;
+            if ((key > pos) | (key < row_lo)) sc[i] = -INFINITY;
+          }
+        }
+        // four chains of three-input maxima: 128 values in 16 dependent steps
+        float mx0 = fmax3(sc[0], sc[1], sc[2]), mx1 = fmax3(sc[3], sc[4], sc[5]);
+        float mx2 = fmax3(sc[6], sc[7], sc[8]), mx3 = fmax3(sc[9], sc[10], sc[11]);
+#pragma unroll
+        for (int i = 12; i + 7 < BN; i += 8) {
+          mx0 = fmax3(mx0, sc[i], sc[i + 1]);
+          mx1 = fmax3(mx1, sc[i + 2], sc[i + 3]);
+          mx2 = fmax3(mx2, sc[i + 4], sc[i + 5]);
+          mx3 = fmax3(mx3, sc[i + 6], sc[i + 7]);
+        }
+        float mx = fmaxf(fmax3(mx0, mx1, mx2), fmax3(mx3, sc[BN - 4], sc[BN - 3]));
+        mx = fmax3(mx, sc[BN - 2], sc[BN - 1]);
+        mx *= sl2;                                                // scores enter the exponent as s * scale * log2(e)
+        float alpha = 1.f;
+        const bool grow = mx > m_run + kRescaleThreshold;         // also true for the first keys a row sees
+        if (grow) {
+          alpha = exp2f(m_run - mx);                              // 0 when m_run is -inf
+          m_run = mx;
+          l_run *= alpha;
+        }
+        if (j > 0 && __any_sync(0xffffffffu, grow)) {             // rescale this warp's rows of O
+#pragma unroll
+          for (int c0 = 0; c0 < HD; c0 += 32) {
+            uint32_t r[32];
+            tmem_ld32(t_o + c0, r);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st32(t_o + c0, r);
+          }
+        }
+        if (key0 < u.lo || key0 + BN > u.hi) {
+          // rows of v whose keys no query of the tile sees hold whatever their page holds: clear them, so that
+          // their zero weights cannot meet a value that is not finite (both items' warps do, with the same zeros)
+          const uint32_t v = sV + (ju % kStages) * kKBytes;
+          const int r_lo = u.lo - key0, r_hi = u.hi - key0;
+          ok = mbar_wait_f(v_full(ju % kStages), (uint32_t)((ju / kStages) & 1), failed);   // the tile's v has landed
+          if (!ok) break;
+          for (int idx = row; idx < kHB * BN * 8; idx += kSoftmaxThreads) {
+            const int r = (idx >> 3) % BN;
+            if (r < r_lo || r >= r_hi)
+              asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(v + (idx >> 3) * 128 + (idx & 7) * 16), "r"(0) : "memory");
+          }
+          fence_async_smem();
+        }
+        // P as bfloat16 pairs over the first 64 columns of S: keys 2c and 2c + 1 in column c
+        const float neg_m = m_run == -INFINITY ? 0.f : -m_run;
+        // The scaling, the subtraction of the maximum and the row sums are packed (two values per instruction); the
+        // exponentials come from the special-function unit.  (Tried and slower on this kernel: a share of the
+        // exponentials by a polynomial on the FMA pipe, and exponentials of bfloat16 pairs; the softmax warps are
+        // bound by the instructions they issue, not by that unit.)  The first 64 keys' P is handed to the issuing warp
+        // while the other 64 are computed.
+        const uint64_t sl2_2 = pk2(sl2, sl2), neg_m2 = pk2(neg_m, neg_m);
+        uint64_t lsum = pk2(0.f, 0.f);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t w[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const uint64_t x2 = fma2(pk2(sc[h * 64 + 2 * i], sc[h * 64 + 2 * i + 1]), sl2_2, neg_m2);
+            float p0, p1, x0, x1;
+            upk2(x2, x0, x1);
+            p0 = ex2_approx(x0);
+            p1 = ex2_approx(x1);
+            lsum = add2(lsum, pk2(p0, p1));
+            w[i] = pack_bf16(p0, p1);
+          }
+          tmem_st32_issue(t_s + h * 32, w);
+          if (h == 0) {
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(p_full(x, 0));
+          }
+        }
+        tmem_wait_st();
+        float l0, l1;
+        upk2(lsum, l0, l1);
+        l_run += l0 + l1;
+        tc_fence_before();
+        mbar_arrive(p_full(x, 1));
       }
-      float mx = fmaxf(fmax3(mx0, mx1, mx2), fmax3(mx3, sc[BN - 4], sc[BN - 3]));
-      mx = fmax3(mx, sc[BN - 2], sc[BN - 1]);
-      mx *= sl2;                                                // scores enter the exponent as s * scale * log2(e)
-      float alpha = 1.f;
-      const bool grow = mx > m_run + kRescaleThreshold;         // also true for the first keys a row sees
-      if (grow) {
-        alpha = exp2f(m_run - mx);                              // 0 when m_run is -inf
-        m_run = mx;
-        l_run *= alpha;
-      }
-      if (j > 0 && __any_sync(0xffffffffu, grow)) {             // rescale this warp's rows of O
+      if (ok && my_tiles > 0) ok = mbar_wait_f(o_done(x), (uint32_t)(my_units_before & 1), failed);
+      if (ok && my_tiles > 0) {
+        tc_fence_after();
+        const float inv = 1.0f / l_run;
+        bf16* dst = a.out + (size_t)(u.tok0 + me.q0 + row) * a.out_stride + (size_t)me.head * HD;
 #pragma unroll
         for (int c0 = 0; c0 < HD; c0 += 32) {
           uint32_t r[32];
-          tmem_ld32(t_o + c0, r);
+          tmem_ld32(t_o + c0, r);                                 // every lane of the warp takes part
+          if (row_ok) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-          tmem_st32(t_o + c0, r);
-        }
-      }
-      if (key0 < lo || key0 + BN > hi) {
-        // rows of v whose keys no query of the tile sees hold whatever their page holds: clear them, so that
-        // their zero weights cannot meet a value that is not finite (both items' warps do, with the same zeros)
-        const uint32_t v = sV + (ju % kStages) * kKBytes;
-        const int r_lo = lo - key0, r_hi = hi - key0;
-        ok = mbar_wait_f(v_full(ju % kStages), (uint32_t)((ju / kStages) & 1), failed);   // the tile's v has landed
-        if (!ok) break;
-        for (int idx = row; idx < kHB * BN * 8; idx += kSoftmaxThreads) {
-          const int r = (idx >> 3) % BN;
-          if (r < r_lo || r >= r_hi)
-            asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(v + (idx >> 3) * 128 + (idx & 7) * 16), "r"(0) : "memory");
-        }
-        fence_async_smem();
-      }
-      // P as bfloat16 pairs over the first 64 columns of S: keys 2c and 2c + 1 in column c
-      const float neg_m = m_run == -INFINITY ? 0.f : -m_run;
-      // The scaling, the subtraction of the maximum and the row sums are packed (two values per instruction); the
-      // exponentials come from the special-function unit.  (Tried and slower on this kernel: a share of the
-      // exponentials by a polynomial on the FMA pipe, and exponentials of bfloat16 pairs; the softmax warps are
-      // bound by the instructions they issue, not by that unit.)  The first 64 keys' P is handed to the issuing warp
-      // while the other 64 are computed.
-      const uint64_t sl2_2 = pk2(sl2, sl2), neg_m2 = pk2(neg_m, neg_m);
-      uint64_t lsum = pk2(0.f, 0.f);
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        uint32_t w[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const uint64_t x2 = fma2(pk2(sc[h * 64 + 2 * i], sc[h * 64 + 2 * i + 1]), sl2_2, neg_m2);
-          float p0, p1, x0, x1;
-          upk2(x2, x0, x1);
-          p0 = ex2_approx(x0);
-          p1 = ex2_approx(x1);
-          lsum = add2(lsum, pk2(p0, p1));
-          w[i] = pack_bf16(p0, p1);
-        }
-        tmem_st32_issue(t_s + h * 32, w);
-        if (h == 0) {
-          tmem_wait_st();
-          tc_fence_before();
-          mbar_arrive(p_full(x, 0));
-        }
-      }
-      tmem_wait_st();
-      float l0, l1;
-      upk2(lsum, l0, l1);
-      l_run += l0 + l1;
-      tc_fence_before();
-      mbar_arrive(p_full(x, 1));
-    }
-    if (ok && my_tiles > 0) ok = mbar_wait_f(o_done(x), 0u, failed);
-    if (ok && my_tiles > 0) {
-      tc_fence_after();
-      const float inv = 1.0f / l_run;
-      bf16* dst = a.out + (size_t)(tok0 + me.q0 + row) * a.out_stride + (size_t)me.head * HD;
-#pragma unroll
-      for (int c0 = 0; c0 < HD; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld32(t_o + c0, r);                                 // every lane of the warp takes part
-        if (row_ok) {
-#pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint4 v;
-            v.x = pack_bf16(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
-            v.y = pack_bf16(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
-            v.z = pack_bf16(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
-            v.w = pack_bf16(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
-            *reinterpret_cast<uint4*>(dst + c0 + i) = v;
+            for (int i = 0; i < 32; i += 8) {
+              uint4 v;
+              v.x = pack_bf16(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
+              v.y = pack_bf16(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+              v.z = pack_bf16(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
+              v.w = pack_bf16(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
+              *reinterpret_cast<uint4*>(dst + c0 + i) = v;
+            }
           }
         }
+        // the next unit's first P V overwrites O: the reads above are complete (tmem_ld32 waits for them)
+        tc_fence_before();
       }
+      tiles_before += u.n_tiles;
+      my_tiles_before += my_tiles;
+      my_units_before += 1;
     }
-  } else {
-    regs_dec<kRegsOther>();
   }
   tc_fence_before();
   __syncthreads();
@@ -585,7 +661,7 @@ LMSF_API int lmsf_attention_prefill_tc(const void* q, long long q_stride, void* 
     LMSF_REFUSE("attention_prefill_tc: block_size=%d must be a power of two", block_size);
   a.block_table = block_table; a.max_blocks = max_blocks; a.tile_seq = tile_seq; a.tile_q0 = tile_q0;
   a.cu_q = cu_q; a.ctx_len = ctx_len; a.scale = scale; a.window = window; a.n_q_heads = n_q_heads;
-  a.group = n_q_heads / n_kv_heads; a.error_flag = error_flag;
+  a.group = n_q_heads / n_kv_heads; a.error_flag = error_flag; a.n_q_tiles = n_tiles;
   // pages of 8 keys and more come by tensor-map copies (a box of rows_box keys starts on a 1024-byte
   // boundary of the swizzled tile); smaller pages by cp.async
   a.rows_box = block_size < BN ? block_size : BN;
@@ -604,6 +680,20 @@ LMSF_API int lmsf_attention_prefill_tc(const void* q, long long q_stride, void* 
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  return launch_pdl(prefill_tc_kernel, dim3(n_kv_heads * ((a.group + 1) / 2), n_tiles), dim3(kThreadsTotal), kSmemBytes,
-                    (cudaStream_t)stream, a, kv_map);
+  // one block per SM at most (a block holds all of an SM's tensor memory); the blocks share the units out among them
+  static int n_sms = 0;
+  if (n_sms == 0) {
+    int dev = 0, v = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0)
+      LMSF_REFUSE("attention_prefill_tc: the device's number of SMs cannot be read");
+    n_sms = v;
+  }
+  const long long n_units = (long long)n_kv_heads * ((a.group + 1) / 2) * n_tiles;
+  long long n_blocks = n_units < n_sms ? n_units : n_sms;
+  // LMSF_TC_MAX_BLOCKS=<n> launches fewer blocks, so that small inputs exercise blocks that take many units in turn
+  if (const char* e = getenv("LMSF_TC_MAX_BLOCKS")) {
+    const long long cap = atoll(e);
+    if (cap > 0 && cap < n_blocks) n_blocks = cap;
+  }
+  return launch_pdl(prefill_tc_kernel, dim3((unsigned)n_blocks), dim3(kThreadsTotal), kSmemBytes, (cudaStream_t)stream, a, kv_map);
 }

@@ -457,11 +457,15 @@ def test_fused_qkv_rotary_cache_write_equals_the_three_steps(M, nh, nkv, hd, rot
 @pytest.mark.parametrize("nh,nkv,hd,bs,window", [(8, 2, 128, 16, 0), (4, 4, 64, 16, 0), (6, 1, 128, 8, 0), (4, 2, 64, 32, 90),
                                                (2, 1, 128, 16, 300), (3, 1, 128, 4, 0), (6, 2, 64, 128, 0), (5, 1, 128, 256, 200),
                                                (2, 2, 64, 2, 70)])
-def test_attention_tcgen05_prefill(nh, nkv, hd, bs, window):
+@pytest.mark.parametrize("max_blocks", [0, 3])
+def test_attention_tcgen05_prefill(nh, nkv, hd, bs, window, max_blocks, monkeypatch):
     """The tcgen05 prefill kernel against float64 and against its mma.sync twin: even and odd groups of heads,
     pages from 2 to 256 keys (tensor-map copies from 8 keys on, cp.async below), windows; slots that hold no key
-    are NaN."""
+    are NaN.  With three blocks only, every block takes many units of work in turn (with one and with two items,
+    and empty ones), so the barriers' phases and the rings of stages run on from unit to unit."""
     from lmsf_b200 import kernels
+    if max_blocks:
+        monkeypatch.setenv("LMSF_TC_MAX_BLOCKS", str(max_blocks))
     assert kernels.tc_attention_supported(torch.bfloat16, hd)
     # a portion in the middle of a long prompt, a whole prompt, a 2-token portion, a portion of exactly one tile, a long one
     ctx_lens, q_lens = [700, 130, 65, 128, 1100], [201, 130, 2, 128, 1000]
