@@ -81,7 +81,7 @@ def bench_decode_attention(args, dev, timer, pk):
     cu = torch.arange(B + 1, dtype=torch.int32, device=dev)
     cl = torch.full((B,), ctx, dtype=torch.int32, device=dev)
     sm = torch.cuda.get_device_properties(dev).multi_processor_count
-    splits = args.splits or kernels.decode_num_splits(B, nkv, nh // nkv, ctx, kernels.decode_max_clusters(hd, nh // nkv))
+    splits = args.splits or kernels.decode_num_splits(B, nkv, nh // nkv, ctx, kernels.decode_max_clusters(hd, nh // nkv, B * nkv * ((nh // nkv + 15) // 16)))
     scratch = torch.zeros(max(1, kernels.attention_decode_scratch_floats(B, nh, splits, hd)), dtype=torch.float32, device=dev)
     fn = lambda: kernels.attention_decode(out, q, cache, bt, args.block_size, None, B, cu, cl, 1 / math.sqrt(hd), 0,
                                           nh, nkv, hd, splits, scratch)

@@ -36,7 +36,11 @@ constexpr int kStages = HD < 64 ? 4 : 3;
 #endif
 constexpr int kKSteps = HD / 16;   // k-steps of q k^T; also pairs of 8-wide output tiles of p v
 constexpr float kLog2e = 1.4426950408889634f;
-using St = Stage<HD>;
+using St = Stage<HD>;                 // the prefill kernel's stages (64 keys)
+// Decode blocks come in two widths, W = 4 or 2 warps; a warp takes 16 keys of a tile, so tiles hold 64 or 32 keys.
+// Above head size 64 a stage of 64 keys is 35 KB and two blocks fit an SM: best for few requests, whose blocks
+// are few and long.  With two warps and stages of 17 KB four blocks fit, and many requests (64 x 8 kv heads) run
+// in one wave instead of two.
 
 struct DecodeArgs {
   const bf16* q; long long q_stride;         // [n_tokens][n_q_heads * HD]
@@ -75,7 +79,10 @@ __device__ __forceinline__ void st_cluster_f32(const float* local, unsigned rank
 constexpr int kTableCache = 512;           // block-table entries of a split that are kept in shared memory
 constexpr int kMergeWeights = 4096;        // (heads of a block) x splits whose weights fit the shared memory used for adding up
 
-__global__ void __launch_bounds__(kThreads) decode_kernel(DecodeArgs a) {
+template <int W>
+__global__ void __launch_bounds__(32 * W) decode_kernel(DecodeArgs a) {
+  constexpr int kDecWarps = W, kDecThreads = 32 * W, kDecTile = 16 * W;
+  using DSt = Stage<HD, kDecTile>;
   extern __shared__ __align__(16) unsigned char smem[];
   __shared__ int s_table[kTableCache];
   __shared__ int s_is_last;
@@ -91,7 +98,7 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(DecodeArgs a) {
   // contexts of up to kTableCache pages no copy of the loop waits for a table entry from global memory, and
   // the entries do not have to wait for the lengths either.
   const int n_head = min(a.max_blocks, kTableCache);
-  for (int i = threadIdx.x; i < n_head; i += kThreads) s_table[i] = table[i];
+  for (int i = threadIdx.x; i < n_head; i += kDecThreads) s_table[i] = table[i];
   const int token = a.cu_q[seq];
   const int ctx = a.ctx_len[seq];
   const int lo = a.window > 0 ? max(0, ctx - a.window) : 0;
@@ -101,7 +108,7 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(DecodeArgs a) {
   const int n_heads = min(16, a.group - hchunk * 16);          // valid rows
 
   // tiles of 64 keys aligned to absolute positions; this split's share of them
-  const int tile_lo = lo / kTileKeys, tile_hi = (ctx + kTileKeys - 1) / kTileKeys;
+  const int tile_lo = lo / kDecTile, tile_hi = (ctx + kDecTile - 1) / kDecTile;
   const int per_split = (tile_hi - tile_lo + a.n_splits - 1) / a.n_splits;
   const int tile_begin = tile_lo + split * per_split;
   const int tile_end = min(tile_hi, tile_begin + per_split);
@@ -111,13 +118,13 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(DecodeArgs a) {
   // in global memory)
   int table_off = 0;
   {
-    const int blk0 = (tile_begin * kTileKeys) >> a.kv.block_shift;
-    const int blk1 = n_tiles > 0 ? min(a.max_blocks, ((min(ctx, tile_end * kTileKeys) - 1) >> a.kv.block_shift) + 1) : 0;
+    const int blk0 = (tile_begin * kDecTile) >> a.kv.block_shift;
+    const int blk1 = n_tiles > 0 ? min(a.max_blocks, ((min(ctx, tile_end * kDecTile) - 1) >> a.kv.block_shift) + 1) : 0;
     __syncthreads();
     if (blk1 <= n_head) {
       table = s_table;
     } else if (blk1 - blk0 <= kTableCache) {
-      for (int i = threadIdx.x; i < blk1 - blk0; i += kThreads) s_table[i] = table[blk0 + i];
+      for (int i = threadIdx.x; i < blk1 - blk0; i += kDecThreads) s_table[i] = table[blk0 + i];
       __syncthreads();
       table = s_table;
       table_off = blk0;
@@ -126,14 +133,14 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(DecodeArgs a) {
 
   const uint32_t smem_base = smem_u32(smem);
   // first stages: tiles that end before the new token are requested now, the others after the wait
-  const int safe_end = (ctx - 1) / kTileKeys;                  // tiles below this index hold only older keys
+  const int safe_end = (ctx - 1) / kDecTile;                  // tiles below this index hold only older keys
   for (int s = 0; s < kStages - 1; ++s)
     if (s < n_tiles && tile_begin + s < safe_end)
-      load_stage<HD>(smem_base + s * St::kBytes, a.kv, table, kvh, (tile_begin + s) * kTileKeys, lo, ctx, table_off);
+      load_stage<HD, kDecTile, kDecThreads>(smem_base + s * DSt::kBytes, a.kv, table, kvh, (tile_begin + s) * kDecTile, lo, ctx, table_off);
   pdl_wait();
   for (int s = 0; s < kStages - 1; ++s) {
     if (s < n_tiles && tile_begin + s >= safe_end)
-      load_stage<HD>(smem_base + s * St::kBytes, a.kv, table, kvh, (tile_begin + s) * kTileKeys, lo, ctx, table_off);
+      load_stage<HD, kDecTile, kDecThreads>(smem_base + s * DSt::kBytes, a.kv, table, kvh, (tile_begin + s) * kDecTile, lo, ctx, table_off);
     cp_async_commit();
   }
 
@@ -163,12 +170,12 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(DecodeArgs a) {
     {
       const int nxt = i + kStages - 1;
       if (nxt < n_tiles)
-        load_stage<HD>(smem_base + (nxt % kStages) * St::kBytes, a.kv, table, kvh, (tile_begin + nxt) * kTileKeys, lo, ctx, table_off);
+        load_stage<HD, kDecTile, kDecThreads>(smem_base + (nxt % kStages) * DSt::kBytes, a.kv, table, kvh, (tile_begin + nxt) * kDecTile, lo, ctx, table_off);
       cp_async_commit();
     }
-    const uint32_t kbase = smem_base + (i % kStages) * St::kBytes;       // this warp's rows are warp * 16 ..
-    const uint32_t vbase = kbase + kTileKeys * St::kRowBytes;
-    const int key0 = (tile_begin + i) * kTileKeys + warp * 16;   // first key of this warp's 16
+    const uint32_t kbase = smem_base + (i % kStages) * DSt::kBytes;       // this warp's rows are warp * 16 ..
+    const uint32_t vbase = kbase + kDecTile * DSt::kRowBytes;
+    const int key0 = (tile_begin + i) * kDecTile + warp * 16;   // first key of this warp's 16
     if (key0 >= ctx || key0 + 16 <= lo) continue;                // nothing valid (uniform over the warp)
 
     float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
@@ -176,7 +183,7 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(DecodeArgs a) {
     for (int ks = 0; ks < kKSteps; ++ks) {
       uint32_t b[4];
       const int mi = lane >> 3, r = lane & 7;
-      ldmatrix_x4(b, kbase + St::off(warp * 16 + (mi >> 1) * 8 + r, ks * 2 + (mi & 1)));
+      ldmatrix_x4(b, kbase + DSt::off(warp * 16 + (mi >> 1) * 8 + r, ks * 2 + (mi & 1)));
       mma_16816(s[0], qf[ks], b[0], b[1]);
       mma_16816(s[1], qf[ks], b[2], b[3]);
     }
@@ -225,7 +232,7 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(DecodeArgs a) {
       }
       uint32_t b[4];
       const int mi = lane >> 3, r = lane & 7;
-      ldmatrix_x4_trans(b, vbase + St::off(warp * 16 + (mi & 1) * 8 + r, n2 * 2 + (mi >> 1)));
+      ldmatrix_x4_trans(b, vbase + DSt::off(warp * 16 + (mi & 1) * 8 + r, n2 * 2 + (mi >> 1)));
       mma_16816(o[2 * n2], pf, b[0], b[1]);
       mma_16816(o[2 * n2 + 1], pf, b[2], b[3]);
     }
@@ -234,16 +241,16 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(DecodeArgs a) {
   __syncthreads();
   if (a.cluster) cluster_sync_all();        // the stages of every block of the cluster are free: split 0's will hold all parts
 
-  // merge the four warps through shared memory (the stages are free now)
+  // merge the warps through shared memory (the stages are free now)
   // (sized by the heads a block really holds, R = min(16, group): 4 for a group of 4, so that the region is a few
   // KB and the stages alone decide how many blocks an SM takes)
   constexpr int kOS = HD + 8;                                   // padded row: rows fall into different banks
   const int R = a.rows;
-  float* sm_o = reinterpret_cast<float*>(smem);                 // [4 warps][R rows][kOS]
-  float* sm_m = sm_o + 4 * R * kOS;                             // [4][16]
-  float* sm_l = sm_m + 4 * 16;                                  // [4][16]
+  float* sm_o = reinterpret_cast<float*>(smem);                 // [warps][R rows][kOS]
+  float* sm_m = sm_o + kDecWarps * R * kOS;                     // [warps][16]
+  float* sm_l = sm_m + kDecWarps * 16;                          // [warps][16]
   const int kPS = R * HD + 16;                                  // one split's part: R rows of HD values, 16 log-sum-exp
-  float* sm_part = sm_l + 4 * 16;                               // [splits][kPS], used in block 0 of a cluster
+  float* sm_part = sm_l + kDecWarps * 16;                       // [splits][kPS], used in block 0 of a cluster
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     st.l[h] += __shfl_xor_sync(0xffffffffu, st.l[h], 1);
@@ -261,14 +268,14 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(DecodeArgs a) {
     if (g4 + 8 < n_heads) *reinterpret_cast<float2*>(row0 + 8 * kOS) = make_float2(o[n][2], o[n][3]);
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < n_heads * HD; idx += kThreads) {
+  for (int idx = threadIdx.x; idx < n_heads * HD; idx += kDecThreads) {
     const int row = idx / HD, d = idx % HD;
     float M = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) M = fmaxf(M, sm_m[w * 16 + row]);
+    for (int w = 0; w < kDecWarps; ++w) M = fmaxf(M, sm_m[w * 16 + row]);
     float L = 0.f, acc = 0.f;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) {
+    for (int w = 0; w < kDecWarps; ++w) {
       const float mw = sm_m[w * 16 + row];
       const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
       L += sm_l[w * 16 + row] * f;
@@ -291,7 +298,7 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(DecodeArgs a) {
     // all parts are in the shared memory of split 0, which adds them up in the order of the splits
     cluster_sync_all();
     if (split != 0) return;
-    for (int idx = threadIdx.x; idx < n_heads * HD; idx += kThreads) {
+    for (int idx = threadIdx.x; idx < n_heads * HD; idx += kDecThreads) {
       const int row = idx / HD, d = idx % HD;
       float M = -INFINITY;
       for (int s = 0; s < a.n_splits; ++s) M = fmaxf(M, sm_part[s * kPS + R * HD + row]);
@@ -325,9 +332,9 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(DecodeArgs a) {
   float* s_w = reinterpret_cast<float*>(smem);                                   // the stages are free
   if (n_w <= kMergeWeights) {
     // weights of all splits first (log-sum-exp values arrive together, not one after the other), then the sums
-    for (int i = threadIdx.x; i < n_w; i += kThreads) s_w[i] = __ldcg(a.part_lse + base0 + i);
+    for (int i = threadIdx.x; i < n_w; i += kDecThreads) s_w[i] = __ldcg(a.part_lse + base0 + i);
     __syncthreads();
-    for (int row = warp; row < n_heads; row += 4) {
+    for (int row = warp; row < n_heads; row += kDecWarps) {
       float* w = s_w + row * a.n_splits;
       float M = -INFINITY;
       for (int s = lane; s < a.n_splits; s += 32) M = fmaxf(M, w[s]);
@@ -345,7 +352,7 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(DecodeArgs a) {
       for (int s = lane; s < a.n_splits; s += 32) w[s] *= inv;
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < n_heads * HD; idx += kThreads) {
+    for (int idx = threadIdx.x; idx < n_heads * HD; idx += kDecThreads) {
       const int row = idx / HD, d = idx % HD;
       const float* po = a.part_o + (base0 + (size_t)row * a.n_splits) * HD + d;
       const float* w = s_w + row * a.n_splits;
@@ -363,7 +370,7 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(DecodeArgs a) {
     }
     return;
   }
-  for (int idx = threadIdx.x; idx < n_heads * HD; idx += kThreads) {
+  for (int idx = threadIdx.x; idx < n_heads * HD; idx += kDecThreads) {
     const int row = idx / HD, d = idx % HD;
     const size_t base = base0 + (size_t)row * a.n_splits;
     float M = -INFINITY;
@@ -398,11 +405,11 @@ static int cluster_enabled() {
 
 static int decode_rows(int group) { return group < 16 ? (group < 1 ? 1 : group) : 16; }
 
-static int decode_smem_bytes(int group) {
+static int decode_smem_bytes(int group, int warps) {
   using namespace lmsf::fa;
   const int R = decode_rows(group);
-  const int smem_stages = kStages * St::kBytes;
-  const int smem_merge = (4 * R * (HD + 8) + 2 * 4 * 16) * (int)sizeof(float);
+  const int smem_stages = kStages * (warps == 2 ? Stage<HD, 32>::kBytes : Stage<HD, 64>::kBytes);
+  const int smem_merge = (warps * R * (HD + 8) + 2 * warps * 16) * (int)sizeof(float);
   const int smem_weights = kMergeWeights * (int)sizeof(float);     // weights of the splits when they are added up
   const int smem_cluster = smem_merge + kMaxClusterSplits * (R * HD + 16) * (int)sizeof(float);   // + the parts of a cluster
   int m = smem_stages > smem_merge ? smem_stages : smem_merge;
@@ -413,14 +420,15 @@ static int decode_smem_bytes(int group) {
 // Clusters of `cluster_size` blocks of the decode kernel (for query heads in groups of `group`) that the device holds
 // at a time (0 on error): the splits of
 // a request and kv head form a cluster, and a launch with more clusters than this runs in two waves.
-LMSF_API int lmsf_attention_decode_max_clusters(int cluster_size, int group) {
+LMSF_API int lmsf_attention_decode_max_clusters(int cluster_size, int group, int warps) {
   using namespace lmsf::fa;
-  if (cluster_size < 1 || cluster_size > kMaxClusterSplits) return 0;
-  const int smem = decode_smem_bytes(group);
-  if (cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return 0;
+  if (cluster_size < 1 || cluster_size > kMaxClusterSplits || (warps != 2 && warps != 4)) return 0;
+  const int smem = decode_smem_bytes(group, warps);
+  void (*kernel)(DecodeArgs) = warps == 2 ? decode_kernel<2> : decode_kernel<4>;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return 0;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)cluster_size, 1024, 1);
-  cfg.blockDim = dim3(kThreads);
+  cfg.blockDim = dim3(32 * warps);
   cfg.dynamicSmemBytes = (size_t)smem;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -430,8 +438,26 @@ LMSF_API int lmsf_attention_decode_max_clusters(int cluster_size, int group) {
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   int n = 0;
-  if (cudaOccupancyMaxActiveClusters(&n, decode_kernel, &cfg) != cudaSuccess) return 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) return 0;
   return n;
+}
+
+// Warps per decode block for a launch of n_pairs (request, group of heads) pairs whose query heads come in groups of
+// `group`: wide blocks (4 warps) while all pairs fit the device at once, narrow ones (2 warps) beyond that if more
+// of them fit (measured with 8 kv heads, groups of 4, head size 128, 2,048 keys: 32 requests 4.99 ms a step wide
+// and 5.14 narrow, 48 requests 6.27 and 5.99).  LMSF_DECODE_WARPS=2 or 4 in the environment fixes the width.
+LMSF_API int lmsf_attention_decode_block_warps(int n_pairs, int group) {
+  const char* e = getenv("LMSF_DECODE_WARPS");      // read at every call: tests switch it
+  if (e && (e[0] == '2' || e[0] == '4') && e[1] == 0) return e[0] - '0';
+  if (LMSF_HEAD_DIM <= 64) return 4;         // stages of 16 KB and less: four wide blocks fit already
+  static int slots[17][2];                   // by rows of a block: blocks of each width that the device holds; 0: not asked yet
+  const int R = decode_rows(group);
+  if (slots[R][0] == 0) {
+    slots[R][1] = lmsf_attention_decode_max_clusters(1, group, 2);
+    slots[R][0] = lmsf_attention_decode_max_clusters(1, group, 4);
+    if (slots[R][0] <= 0) slots[R][0] = 1 << 30;    // the occupancy cannot be read: stay wide
+  }
+  return (n_pairs > slots[R][0] && slots[R][1] > slots[R][0]) ? 2 : 4;
 }
 
 // Bytes of scratch that lmsf_attention_decode needs for the given sizes (0 when n_splits == 1): counters of
@@ -480,19 +506,21 @@ LMSF_API int lmsf_attention_decode(const void* q, long long q_stride, void* out,
   a.block_table = block_table; a.max_blocks = max_blocks; a.seq_ids = seq_ids; a.cu_q = cu_q; a.ctx_len = ctx_len;
   a.scale = scale; a.window = window; a.n_q_heads = n_q_heads; a.group = group; a.n_splits = n_splits;
   a.rows = decode_rows(group);
-  const int smem = decode_smem_bytes(group);
-  static int configured = 0;                 // the largest size the kernel has been allowed so far
-  if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  const int warps = lmsf_attention_decode_block_warps((int)(n_served * gy), group);
+  void (*kernel)(DecodeArgs) = warps == 2 ? decode_kernel<2> : decode_kernel<4>;
+  const int smem = decode_smem_bytes(group, warps);
+  static int configured[2] = {0, 0};         // the largest size each kernel has been allowed so far
+  if (smem > configured[warps == 2]) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
-    configured = smem;
+    configured[warps == 2] = smem;
   }
   cudaStream_t s = (cudaStream_t)stream;
   a.cluster = n_splits >= 2 && n_splits <= kMaxClusterSplits && cluster_enabled();
-  if (!a.cluster) return launch_pdl(decode_kernel, dim3(n_splits, (unsigned)gy, n_served), dim3(kThreads), smem, s, a);
+  if (!a.cluster) return launch_pdl(kernel, dim3(n_splits, (unsigned)gy, n_served), dim3(32 * warps), smem, s, a);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(n_splits, (unsigned)gy, n_served);
-  cfg.blockDim = dim3(kThreads);
+  cfg.blockDim = dim3(32 * warps);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = s;
   cudaLaunchAttribute attr[2];
@@ -504,7 +532,7 @@ LMSF_API int lmsf_attention_decode(const void* q, long long q_stride, void* out,
   attr[1].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 2;
-  return (int)cudaLaunchKernelEx(&cfg, decode_kernel, a);
+  return (int)cudaLaunchKernelEx(&cfg, kernel, a);
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -42,7 +42,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-constexpr int kTileKeys = 64;   // keys per pipeline stage
+constexpr int kTileKeys = 64;   // keys per pipeline stage (prefill; decode blocks may take narrower tiles)
 constexpr int kThreads = 128;   // 4 warps
 
 // Geometry of one layer's cache and of one request's block table.  block_size is a power of two.
@@ -61,15 +61,15 @@ __host__ inline bool make_paged_kv(PagedKV& kv, const void* cache, long long pag
   return true;
 }
 
-// Shared-memory stage: kTileKeys rows of K then kTileKeys rows of V.  Every row carries 16 bytes of padding, which
+// Shared-memory stage: TILE rows of K then TILE rows of V.  Every row carries 16 bytes of padding, which
 // makes the 8 rows of an ldmatrix fall into different banks for any HD.  Head size 64 is the exception: its rows
 // are exactly 128 bytes and the 16-byte chunk c of row r sits at chunk c ^ (r & 7) instead, so that a stage is 16 KB
 // and three stages leave room for four blocks on an SM (at head size 128 the same layout was measured slower than
 // the padding: 108 us against 100 us for 64 requests of 2,048 keys).
-template <int HD> struct Stage {
+template <int HD, int TILE = kTileKeys> struct Stage {
   static constexpr bool kSwizzled = HD == 64;
   static constexpr int kRowBytes = kSwizzled ? HD * 2 : HD * 2 + 16;
-  static constexpr int kBytes = 2 * kTileKeys * kRowBytes;
+  static constexpr int kBytes = 2 * TILE * kRowBytes;
   static constexpr int kChunks = HD / 8;   // 16-byte chunks per row
   // byte offset of chunk `chunk` of row `row` inside the K (or the V) half of a stage
   __device__ static __forceinline__ uint32_t off(int row, int chunk) {
@@ -77,20 +77,20 @@ template <int HD> struct Stage {
   }
 };
 
-// Issues the copies of keys [key0, key0 + 64) of kv head `kvh` into the stage at `stage_base`.
+// Issues the copies of keys [key0, key0 + TILE) of kv head `kvh` into the stage at `stage_base`, by a block of THREADS.
 // Keys outside [lo, hi) and keys whose page entry is negative are zero-filled, never read.
 // A thread copies one 16-byte column of several CONSECUTIVE rows, so that it looks its page up once per
 // page rather than once per row; a warp's copies of one pass cover whole rows (coalesced).
 // `table` may be a copy of a slice of the request's block table: entry i of it is block i + table_off.
-template <int HD>
+template <int HD, int TILE = kTileKeys, int THREADS = kThreads>
 __device__ __forceinline__ void load_stage(uint32_t stage_base, const PagedKV& kv, const int* __restrict__ table, int kvh,
                                            int key0, int lo, int hi, int table_off = 0) {
-  using S = Stage<HD>;
+  using S = Stage<HD, TILE>;
   const size_t v_off = (size_t)kv.n_kv_heads * kv.block_size * HD;
   const size_t head_off = (size_t)kvh * kv.block_size * HD;
   const int mask = kv.block_size - 1;
-  if constexpr (kThreads % S::kChunks == 0) {
-    constexpr int kRowsPerThread = kTileKeys * S::kChunks / kThreads;   // = kChunks / 2
+  if constexpr (THREADS % S::kChunks == 0) {
+    constexpr int kRowsPerThread = TILE * S::kChunks / THREADS;   // = kChunks / 2
     const int c = threadIdx.x % S::kChunks, row0 = (threadIdx.x / S::kChunks) * kRowsPerThread;
     const bf16* page_ptr = nullptr;
     bool have_page = false;                         // page_ptr belongs to the page of the current row
@@ -108,12 +108,13 @@ __device__ __forceinline__ void load_stage(uint32_t stage_base, const PagedKV& k
       const bf16* src = ok ? page_ptr + (size_t)slot * HD : kv.cache;
       const uint32_t dst = stage_base + S::off(row, c);
       cp_async_16(dst, src, ok ? 16 : 0);
-      cp_async_16(dst + kTileKeys * S::kRowBytes, ok ? src + v_off : src, ok ? 16 : 0);
+      cp_async_16(dst + TILE * S::kRowBytes, ok ? src + v_off : src, ok ? 16 : 0);
     }
   } else {
 #pragma unroll
-    for (int it = 0; it < (kTileKeys * S::kChunks) / kThreads; ++it) {
-      const int idx = threadIdx.x + it * kThreads;
+    static_assert((TILE * S::kChunks) % THREADS == 0, "a stage's copies must divide evenly among the threads");
+    for (int it = 0; it < (TILE * S::kChunks) / THREADS; ++it) {
+      const int idx = threadIdx.x + it * THREADS;
       const int row = idx / S::kChunks, c = idx % S::kChunks;
       const int key = key0 + row;
       const bf16* src = kv.cache;
@@ -127,7 +128,7 @@ __device__ __forceinline__ void load_stage(uint32_t stage_base, const PagedKV& k
       }
       const uint32_t dst = stage_base + S::off(row, c);
       cp_async_16(dst, src, bytes);
-      cp_async_16(dst + kTileKeys * S::kRowBytes, bytes ? src + v_off : src, bytes);
+      cp_async_16(dst + TILE * S::kRowBytes, bytes ? src + v_off : src, bytes);
     }
   }
 }

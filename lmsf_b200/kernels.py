@@ -413,16 +413,28 @@ def _check_paged(q, out, cache, n_q_heads, n_kv_heads, head_dim, block_size, wha
 _DECODE_MAX_CLUSTERS = {}
 
 
-def decode_max_clusters(head_dim: int, group: int = 1) -> Tuple[int, ...]:
-    """For cluster sizes 1..8: how many clusters of that many decode blocks the device holds at a time (it depends
-    on the group of query heads per kv head, which sizes a block's shared memory)."""
-    key = (head_dim, min(16, max(1, group)))
+def decode_block_warps(head_dim: int, n_pairs: int, group: int = 1) -> int:
+    """Warps of a decode block (2 or 4) for a launch of n_pairs (request, group of heads) pairs: the kernel's own
+    rule (narrow blocks, of which more fit an SM, when the wide ones would need a second wave)."""
+    lib = load_library("attention_mma.cu", _mma_defines(head_dim))
+    lib.lmsf_attention_decode_block_warps.restype = c_int
+    lib.lmsf_attention_decode_block_warps.argtypes = [c_int, c_int]
+    return lib.lmsf_attention_decode_block_warps(int(n_pairs), int(group))
+
+
+def decode_max_clusters(head_dim: int, group: int = 1, n_pairs: int = 1) -> Tuple[int, ...]:
+    """For cluster sizes 1..8: how many clusters of that many decode blocks the device holds at a time.  It depends
+    on the group of query heads per kv head, which sizes a block's shared memory, and on the width of the blocks,
+    which the kernel chooses by the number of (request, group of heads) pairs of the launch."""
+    warps = decode_block_warps(head_dim, n_pairs, group)
+    key = (head_dim, min(16, max(1, group)), warps)
     t = _DECODE_MAX_CLUSTERS.get(key)
     if t is None:
         lib = load_library("attention_mma.cu", _mma_defines(head_dim))
         lib.lmsf_attention_decode_max_clusters.restype = c_int
-        lib.lmsf_attention_decode_max_clusters.argtypes = [c_int, c_int]
-        t = _DECODE_MAX_CLUSTERS[key] = tuple(max(1, lib.lmsf_attention_decode_max_clusters(s, key[1])) for s in range(1, 9))
+        lib.lmsf_attention_decode_max_clusters.argtypes = [c_int, c_int, c_int]
+        t = _DECODE_MAX_CLUSTERS[key] = tuple(max(1, lib.lmsf_attention_decode_max_clusters(s, key[1], warps))
+                                              for s in range(1, 9))
     return t
 
 

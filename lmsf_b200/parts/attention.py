@@ -118,9 +118,10 @@ class PagedAttention(Mixer):
                 if max_ctx is None:
                     max_ctx = ctx.extras["decode_max_ctx"] = max(c for c, n in zip(ctx.ctx_lens, ctx.q_lens) if n == 1)
                 visible = min(max_ctx, self.window) if self.window else max_ctx
-                splits = kernels.decode_num_splits(ctx.n_decode_seqs, self.num_kv_heads,
-                                                   self.num_heads // self.num_kv_heads, visible,
-                                                   kernels.decode_max_clusters(self.head_dim, self.num_heads // self.num_kv_heads))
+                group_size = self.num_heads // self.num_kv_heads
+                n_pairs = ctx.n_decode_seqs * self.num_kv_heads * ((group_size + 15) // 16)
+                splits = kernels.decode_num_splits(ctx.n_decode_seqs, self.num_kv_heads, group_size, visible,
+                                                   kernels.decode_max_clusters(self.head_dim, group_size, n_pairs))
                 need = kernels.attention_decode_scratch_floats(ctx.n_seqs, self.num_heads, splits, self.head_dim)
                 scratch = ctx.extras.get("decode_scratch")
                 if need and (scratch is None or scratch.numel() < need):

@@ -267,9 +267,12 @@ def test_sampling_greedy_and_temperature():
 
 @pytest.mark.parametrize("nh,nkv,hd,bs,window", [(8, 2, 128, 16, 0), (6, 2, 16, 8, 0), (5, 5, 48, 16, 0), (3, 1, 80, 32, 0),
                                                (20, 1, 64, 16, 0), (4, 2, 112, 16, 70), (4, 4, 96, 4, 200)])
-def test_attention_tensor_core_kernels(nh, nkv, hd, bs, window):
-    """Decode (split over the keys, every split count) and prefill (tiles of 64 queries) against float64."""
+@pytest.mark.parametrize("warps", [4, 2])
+def test_attention_tensor_core_kernels(nh, nkv, hd, bs, window, warps, monkeypatch):
+    """Decode (split over the keys, every split count; blocks of four warps and of two) and prefill (tiles of 64
+    queries) against float64."""
     from lmsf_b200 import kernels
+    monkeypatch.setenv("LMSF_DECODE_WARPS", str(warps))
     assert kernels.mma_attention_supported(torch.bfloat16, hd)
     # a long decode, a first token, a portion in the middle of a prompt, a whole prompt, a 2-token portion, a decode
     ctx_lens, q_lens = [1500, 1, 700, 130, 65, 64], [1, 1, 201, 130, 2, 1]
