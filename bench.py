@@ -476,6 +476,8 @@ def main() -> int:
     if a.serve:
         return serve(cfg, a.layers or cfg["num_hidden_layers"], 64, 256, a.budget)
     ctx_len = a.context
+    # a context beyond the shape's own limit (--context 32000 on the 8B shape): the limit of the random model is raised
+    cfg["max_position_embeddings"] = max(cfg["max_position_embeddings"], ctx_len + 64)
     full_layers = cfg["num_hidden_layers"]
     n_layers = a.layers or full_layers
     V = cfg["vocab_size"]

@@ -81,13 +81,17 @@ def bench_decode_attention(args, dev, timer, pk):
     cu = torch.arange(B + 1, dtype=torch.int32, device=dev)
     cl = torch.full((B,), ctx, dtype=torch.int32, device=dev)
     sm = torch.cuda.get_device_properties(dev).multi_processor_count
-    splits = args.splits or kernels.decode_num_splits(B, nkv, nh // nkv, ctx, kernels.decode_max_clusters(hd, nh // nkv, B * nkv * ((nh // nkv + 15) // 16)))
+    splits, warps = kernels.decode_plan(B, nkv, nh // nkv, ctx, hd, kernels.decode_widths(hd, nh // nkv))
+    if args.splits:
+        splits = args.splits
+    if args.warps:
+        warps = args.warps
     scratch = torch.zeros(max(1, kernels.attention_decode_scratch_floats(B, nh, splits, hd)), dtype=torch.float32, device=dev)
     fn = lambda: kernels.attention_decode(out, q, cache, bt, args.block_size, None, B, cu, cl, 1 / math.sqrt(hd), 0,
-                                          nh, nkv, hd, splits, scratch)
+                                          nh, nkv, hd, splits, scratch, warps)
     t = timer.run(fn, args.warmup, args.iters)
     nbytes = B * ctx * 2 * nkv * hd * 2
-    res = dict(kernel="decode_attention", batch=B, ctx=ctx, splits=splits, us=t * 1e6, gbs=nbytes / t / 1e9,
+    res = dict(kernel="decode_attention", batch=B, ctx=ctx, splits=splits, warps=warps, us=t * 1e6, gbs=nbytes / t / 1e9,
                frac_hbm=nbytes / t / 1e9 / pk["hbm_gbs"])
     rk = reference_kernels()
     if rk is not None and hd in (64, 80, 96, 112, 128, 256) and args.block_size in (8, 16, 32):
@@ -293,6 +297,7 @@ def main() -> int:
     ap.add_argument("--vocab", type=int, default=128256)
     ap.add_argument("--block-size", type=int, default=16)
     ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--warps", type=int, default=0, help="decode_attention: warps of a block, 2 or 4 (default: the plan's)")
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=28672)
     ap.add_argument("--k", type=int, default=4096)

@@ -442,13 +442,25 @@ LMSF_API int lmsf_attention_decode_max_clusters(int cluster_size, int group, int
   return n;
 }
 
-// Warps per decode block for a launch of n_pairs (request, group of heads) pairs whose query heads come in groups of
-// `group`: wide blocks (4 warps) while all pairs fit the device at once, narrow ones (2 warps) beyond that if more
-// of them fit (measured with 8 kv heads, groups of 4, head size 128, 2,048 keys: 32 requests 4.99 ms a step wide
-// and 5.14 narrow, 48 requests 6.27 and 5.99).  LMSF_DECODE_WARPS=2 or 4 in the environment fixes the width.
-LMSF_API int lmsf_attention_decode_block_warps(int n_pairs, int group) {
+// Bytes of keys and values that a decode block of `warps` warps keeps in flight: what sets the rate at which one
+// block streams (0 for a width that does not exist).
+LMSF_API int lmsf_attention_decode_stream_bytes(int warps) {
+  using namespace lmsf::fa;
+  if (warps == 4) return (kStages - 1) * Stage<HD, 64>::kBytes;
+  if (warps == 2) return (kStages - 1) * Stage<HD, 32>::kBytes;
+  return 0;
+}
+
+// The width of the blocks when the caller names none: wide blocks (4 warps) while all (request, group of heads) pairs
+// fit the device at once, narrow ones (2 warps) beyond that if more of them fit.  (The engine chooses the width together
+// with the number of splits, kernels.decode_plan.)  LMSF_DECODE_WARPS=2 or 4 in the environment fixes the width of
+// every launch, whatever the caller says.
+static int forced_block_warps() {
   const char* e = getenv("LMSF_DECODE_WARPS");      // read at every call: tests switch it
-  if (e && (e[0] == '2' || e[0] == '4') && e[1] == 0) return e[0] - '0';
+  return (e && (e[0] == '2' || e[0] == '4') && e[1] == 0) ? e[0] - '0' : 0;
+}
+LMSF_API int lmsf_attention_decode_block_warps(int n_pairs, int group) {
+  if (const int f = forced_block_warps()) return f;
   if (LMSF_HEAD_DIM <= 64) return 4;         // stages of 16 KB and less: four wide blocks fit already
   static int slots[17][2];                   // by rows of a block: blocks of each width that the device holds; 0: not asked yet
   const int R = decode_rows(group);
@@ -473,11 +485,13 @@ LMSF_API long long lmsf_attention_decode_scratch_bytes(int n_seqs_total, int n_q
 // One query token per served request.  seq_ids (may be null) lists the n_served requests among the
 // n_seqs_total rows of block_table / cu_q / ctx_len.  scratch: lmsf_attention_decode_scratch_bytes(), zero when
 // it is first used; a launch that completes leaves its counters zero again, so the same memory serves every call.
-LMSF_API int lmsf_attention_decode(const void* q, long long q_stride, void* out, long long out_stride,
-                                   const void* cache, long long page_stride, int block_size, int n_kv_heads,
-                                   const int* block_table, int max_blocks, const int* seq_ids, int n_served,
-                                   int n_seqs_total, const int* cu_q, const int* ctx_len, float scale, int window,
-                                   int n_q_heads, int head_dim, int n_splits, void* scratch, void* stream) {
+// block_warps: 4 or 2, the width of the blocks; 0: by the rule of lmsf_attention_decode_block_warps.
+LMSF_API int lmsf_attention_decode_width(const void* q, long long q_stride, void* out, long long out_stride,
+                                         const void* cache, long long page_stride, int block_size, int n_kv_heads,
+                                         const int* block_table, int max_blocks, const int* seq_ids, int n_served,
+                                         int n_seqs_total, const int* cu_q, const int* ctx_len, float scale, int window,
+                                         int n_q_heads, int head_dim, int n_splits, int block_warps, void* scratch,
+                                         void* stream) {
   using namespace lmsf;
   using namespace lmsf::fa;
   if (n_served <= 0) return 0;
@@ -506,7 +520,10 @@ LMSF_API int lmsf_attention_decode(const void* q, long long q_stride, void* out,
   a.block_table = block_table; a.max_blocks = max_blocks; a.seq_ids = seq_ids; a.cu_q = cu_q; a.ctx_len = ctx_len;
   a.scale = scale; a.window = window; a.n_q_heads = n_q_heads; a.group = group; a.n_splits = n_splits;
   a.rows = decode_rows(group);
-  const int warps = lmsf_attention_decode_block_warps((int)(n_served * gy), group);
+  if (block_warps != 0 && block_warps != 2 && block_warps != 4)
+    LMSF_REFUSE("attention_decode: blocks have 2 or 4 warps, not %d", block_warps);
+  int warps = forced_block_warps();
+  if (!warps) warps = block_warps ? block_warps : lmsf_attention_decode_block_warps((int)(n_served * gy), group);
   void (*kernel)(DecodeArgs) = warps == 2 ? decode_kernel<2> : decode_kernel<4>;
   const int smem = decode_smem_bytes(group, warps);
   static int configured[2] = {0, 0};         // the largest size each kernel has been allowed so far
@@ -533,6 +550,16 @@ LMSF_API int lmsf_attention_decode(const void* q, long long q_stride, void* out,
   cfg.attrs = attr;
   cfg.numAttrs = 2;
   return (int)cudaLaunchKernelEx(&cfg, kernel, a);
+}
+
+LMSF_API int lmsf_attention_decode(const void* q, long long q_stride, void* out, long long out_stride,
+                                   const void* cache, long long page_stride, int block_size, int n_kv_heads,
+                                   const int* block_table, int max_blocks, const int* seq_ids, int n_served,
+                                   int n_seqs_total, const int* cu_q, const int* ctx_len, float scale, int window,
+                                   int n_q_heads, int head_dim, int n_splits, void* scratch, void* stream) {
+  return lmsf_attention_decode_width(q, q_stride, out, out_stride, cache, page_stride, block_size, n_kv_heads, block_table,
+                                     max_blocks, seq_ids, n_served, n_seqs_total, cu_q, ctx_len, scale, window, n_q_heads,
+                                     head_dim, n_splits, 0, scratch, stream);
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -111,8 +111,8 @@ __device__ __forceinline__ void load_stage(uint32_t stage_base, const PagedKV& k
       cp_async_16(dst + TILE * S::kRowBytes, ok ? src + v_off : src, ok ? 16 : 0);
     }
   } else {
-#pragma unroll
     static_assert((TILE * S::kChunks) % THREADS == 0, "a stage's copies must divide evenly among the threads");
+#pragma unroll
     for (int it = 0; it < (TILE * S::kChunks) / THREADS; ++it) {
       const int idx = threadIdx.x + it * THREADS;
       const int row = idx / S::kChunks, c = idx % S::kChunks;

@@ -283,7 +283,9 @@ class ModelRunner:
         if g is None:
             static_in = self._upload(hb)
             ctx, rows = self._context(hb, static_in)
-            ctx.extras["decode_max_ctx"] = key[1]      # launch geometry must not depend on the step, only on its bucket
+            # launch geometry must not depend on the step, only on its bucket: the decode attention plans its splits
+            # for the middle of the bucket's context lengths (the bucket below ends at half its top)
+            ctx.extras["decode_max_ctx"] = key[1] - key[1] // 4 if key[1] > 1024 else key[1]
             if self._graph_pool is None:
                 self._graph_pool = torch.cuda.graph_pool_handle()
                 self._capture_stream = torch.cuda.Stream(self.device)

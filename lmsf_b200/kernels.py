@@ -31,7 +31,14 @@ def dtype_code(dt: torch.dtype) -> int:
     raise KernelError(f"kernels take float32 or bfloat16, not {dt}")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> int:
+    """The handle of the current stream of the current device (asked at every launch: graphs are captured on
+    another stream).  The raw getter saves building a Stream object, about 2 us a launch."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
@@ -410,61 +417,75 @@ def _check_paged(q, out, cache, n_q_heads, n_kv_heads, head_dim, block_size, wha
 
 
 
-_DECODE_MAX_CLUSTERS = {}
+_DECODE_WIDTHS = {}
 
 
-def decode_block_warps(head_dim: int, n_pairs: int, group: int = 1) -> int:
-    """Warps of a decode block (2 or 4) for a launch of n_pairs (request, group of heads) pairs: the kernel's own
-    rule (narrow blocks, of which more fit an SM, when the wide ones would need a second wave)."""
-    lib = load_library("attention_mma.cu", _mma_defines(head_dim))
-    lib.lmsf_attention_decode_block_warps.restype = c_int
-    lib.lmsf_attention_decode_block_warps.argtypes = [c_int, c_int]
-    return lib.lmsf_attention_decode_block_warps(int(n_pairs), int(group))
-
-
-def decode_max_clusters(head_dim: int, group: int = 1, n_pairs: int = 1) -> Tuple[int, ...]:
-    """For cluster sizes 1..8: how many clusters of that many decode blocks the device holds at a time.  It depends
-    on the group of query heads per kv head, which sizes a block's shared memory, and on the width of the blocks,
-    which the kernel chooses by the number of (request, group of heads) pairs of the launch."""
-    warps = decode_block_warps(head_dim, n_pairs, group)
-    key = (head_dim, min(16, max(1, group)), warps)
-    t = _DECODE_MAX_CLUSTERS.get(key)
+def decode_widths(head_dim: int, group: int = 1) -> Tuple[Tuple[int, float, Tuple[int, ...]], ...]:
+    """The widths a decode block comes in, widest first; for each: its warps, the rate at which one block streams
+    keys (its bytes in flight, in units of 64 KB) and, for cluster sizes 1..8, how many clusters of that many blocks
+    the device holds at a time (it depends on the group of query heads per kv head, which sizes a block's shared
+    memory).  Head sizes up to 64 have one width: four of its blocks fit an SM anyway."""
+    key = (head_dim, min(16, max(1, group)))
+    t = _DECODE_WIDTHS.get(key)
     if t is None:
         lib = load_library("attention_mma.cu", _mma_defines(head_dim))
         lib.lmsf_attention_decode_max_clusters.restype = c_int
         lib.lmsf_attention_decode_max_clusters.argtypes = [c_int, c_int, c_int]
-        t = _DECODE_MAX_CLUSTERS[key] = tuple(max(1, lib.lmsf_attention_decode_max_clusters(s, key[1], warps))
-                                              for s in range(1, 9))
+        lib.lmsf_attention_decode_stream_bytes.restype = c_int
+        lib.lmsf_attention_decode_stream_bytes.argtypes = [c_int]
+        widths = []
+        for warps in ((4,) if head_dim <= 64 else (4, 2)):
+            clusters = tuple(max(1, lib.lmsf_attention_decode_max_clusters(s, key[1], warps)) for s in range(1, 9))
+            widths.append((warps, lib.lmsf_attention_decode_stream_bytes(warps) / 65536.0, clusters))
+        t = _DECODE_WIDTHS[key] = tuple(widths)
     return t
 
 
-DECODE_FIXED_TILES = 4.0      # what a wave of blocks costs before and after its keys, in 64-key tiles of a full device
-DECODE_GLOBAL_MERGE_TILES = 6.0   # extra cost of adding more than 8 splits up through global memory
+# The cost model of decode_plan, in units of the time in which a block with 64 KB in flight streams 32 KB (about
+# 1.5 us on B200); fitted to B200 measurements of 8 and 40 kv heads, 2,048 to 8,000 keys, 16 to 128 requests, both
+# widths, 1 to 8 splits, alone and inside decode steps.
+DECODE_WAVE_COST = 6.0          # what a wave of blocks costs before and after its keys
+DECODE_SPLIT_COST = 4.0         # adding the splits of a request up
+DECODE_GLOBAL_MERGE_COST = 6.0  # more when more than 8 splits add up through global memory
+DECODE_SATURATION = 240.0       # blocks with 64 KB in flight that saturate the memory
+DECODE_MUST_GAIN = 0.95         # a narrower block or a further split is taken when the model gives it 5 % less
 
 
-def decode_num_splits(n_served: int, n_kv_heads: int, group: int, max_ctx: int, max_clusters: Sequence[int]) -> int:
-    """Into how many blocks the keys of a request are split.  Up to 8 splits form a thread-block cluster (they add
-    up through its shared memory) and max_clusters[s - 1] such clusters run at a time; more splits add up through
-    global memory.  The choice minimises waves x (fixed cost + tiles per split): a block streams its tiles at about
-    the same rate whether the device is full or not, so what counts is how short the longest block is and that no
-    second, partly filled wave is needed; every split keeps at least 128 keys.  Measured on B200 (head size 128,
-    2,048 keys): 5 requests x 8 kv heads take 20.5 us with 6 splits (45 clusters fit) and 30.7 us with 7 (37 fit)."""
+def decode_plan(n_served: int, n_kv_heads: int, group: int, max_ctx: int, head_dim: int,
+                widths: Sequence[Tuple[int, float, Sequence[int]]]) -> Tuple[int, int]:
+    """(splits, warps): into how many blocks the keys of a request are split, and how wide the blocks are.  Up to 8
+    splits form a thread-block cluster (they add up through its shared memory) and clusters[s - 1] such clusters
+    run at a time; more splits add up through global memory.  The choice minimises the sum over the waves of
+    (fixed cost + keys per split / rate), where a block streams at the rate of its own bytes in flight or, when more
+    blocks are resident than saturate the memory, at its share of the device: few long requests want wide blocks
+    and many splits, many requests narrow blocks, of which twice as many are resident, and no second, partly filled
+    wave.  Every split keeps at least 128 keys.  Measured on B200 (head size 128, 8 kv heads, 2,048 keys):
+    5 requests take 20.5 us with 6 splits (45 clusters fit) and 30.7 us with 7 (37 fit); 48 requests 100 us at best
+    with wide blocks (2 splits) and 95 us with narrow ones (1 split); a decode step of 20 requests 4.72 ms with wide
+    blocks and one split, 4.42 ms with narrow ones and 3."""
     base = n_served * n_kv_heads * ((group + 15) // 16)
     tiles = -(-max_ctx // 64)
     cap = max(1, -(-max_ctx // 128))
-    slots = max_clusters[0]
-    best, best_cost, best_waves = 1, None, 1
-    for s in list(range(1, 9)) + [12, 16, 24, 32, 48, 64]:
-        if s > cap:
-            break
-        per_wave = max_clusters[s - 1] if s <= 8 else max(1, slots // s)      # (request, head group) pairs per wave
-        waves = -(-base // per_wave)
-        cost = waves * (DECODE_FIXED_TILES + -(-tiles // s)) + (DECODE_GLOBAL_MERGE_TILES if s > 8 else 0.0)
-        # more waves than the best so far must pay off by a quarter: measured, a further wave costs more than the
-        # model says (64 requests at head size 64: 61.5 us with one split in two waves, 63.5 us with two in three)
-        if best_cost is None or cost < best_cost * (0.75 if waves > best_waves else 1.0) - 1e-9:
-            best, best_cost, best_waves = s, cost, waves
-    return best
+    tile_work = head_dim / 128.0                  # a 64-key tile of k and v in units of 32 KB
+    best = None
+    for warps, rate, clusters in widths:
+        slots = clusters[0]
+        for s in list(range(1, 9)) + [12, 16, 24, 32, 48, 64]:
+            if s > cap:
+                break
+            per_wave = clusters[s - 1] if s <= 8 else max(1, slots // s)      # (request, head group) pairs per wave
+            work = -(-tiles // s) * tile_work
+            cost = (DECODE_SPLIT_COST if s > 1 else 0.0) + (DECODE_GLOBAL_MERGE_COST if s > 8 else 0.0)
+            left = base
+            while left > 0:
+                n = min(left, per_wave) * s
+                cost += DECODE_WAVE_COST + work / min(rate, DECODE_SATURATION / n)
+                left -= per_wave
+            # candidates come widest first and with few splits first; a later one must be better by 5 %: measured,
+            # near-ties of the model go to either side by a per cent, and wide blocks with few splits never lose more
+            if best is None or cost < best[0] * DECODE_MUST_GAIN:
+                best = (cost, s, warps)
+    return best[1], best[2]
 
 
 DECODE_COUNTER_SLOTS = 65536     # counters of delivered splits at the start of the scratch (attention_mma.cu)
@@ -477,24 +498,28 @@ def attention_decode_scratch_floats(n_seqs_total: int, n_q_heads: int, n_splits:
 def attention_decode(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                      block_size: int, seq_ids: Optional[torch.Tensor], n_served: int, cu_q: torch.Tensor,
                      ctx_len: torch.Tensor, scale: float, window: int, n_q_heads: int, n_kv_heads: int,
-                     head_dim: int, n_splits: int, scratch: Optional[torch.Tensor]):
+                     head_dim: int, n_splits: int, scratch: Optional[torch.Tensor], warps: int = 0):
     """Attention of requests that bring ONE query token each (row cu_q[s] of q), over their ctx_len[s] keys
     in pages.  seq_ids: int32 [n_served] rows of the block table that are served (None: all, in order).
     scratch: float32, at least attention_decode_scratch_floats(...) values when n_splits > 1, all zero when it is
-    first used (torch.zeros); the kernel leaves its counters zero, so one buffer serves every later call."""
+    first used (torch.zeros); the kernel leaves its counters zero, so one buffer serves every later call.
+    warps: the width of the blocks, 4 or 2 (decode_plan chooses it with n_splits); 0 leaves it to the kernel."""
     _check_paged(q, out, cache, n_q_heads, n_kv_heads, head_dim, block_size, "attention_decode")
     n_total = block_table.shape[0]
     need = attention_decode_scratch_floats(n_total, n_q_heads, n_splits, head_dim)
     if need and (scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need):
         raise KernelError(f"attention_decode: {n_splits} splits need {need} float32 values of scratch")
     d = _mma_defines(head_dim)
-    f = _func("attention_mma.cu", "lmsf_attention_decode",
+    if warps not in (0, 2, 4):
+        raise KernelError(f"attention_decode: blocks have 2 or 4 warps, not {warps}")
+    f = _func("attention_mma.cu", "lmsf_attention_decode_width",
               [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_void_p, c_int,
-               c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_void_p, c_void_p], d)
+               c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_void_p,
+               c_void_p], d)
     rc = f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache), cache.stride(0), block_size, n_kv_heads,
            _i32(block_table, "block_table"), block_table.shape[1], _i32(seq_ids, "seq_ids"), n_served, n_total,
            _i32(cu_q, "cu_q"), _i32(ctx_len, "ctx_len"), float(scale), int(window or 0), n_q_heads, head_dim,
-           n_splits, _ptr(scratch) if need else None, _stream())
+           n_splits, warps, _ptr(scratch) if need else None, _stream())
     _check(rc, "attention_mma.cu", "lmsf_attention_mma", d)
 
 

@@ -119,9 +119,8 @@ class PagedAttention(Mixer):
                     max_ctx = ctx.extras["decode_max_ctx"] = max(c for c, n in zip(ctx.ctx_lens, ctx.q_lens) if n == 1)
                 visible = min(max_ctx, self.window) if self.window else max_ctx
                 group_size = self.num_heads // self.num_kv_heads
-                n_pairs = ctx.n_decode_seqs * self.num_kv_heads * ((group_size + 15) // 16)
-                splits = kernels.decode_num_splits(ctx.n_decode_seqs, self.num_kv_heads, group_size, visible,
-                                                   kernels.decode_max_clusters(self.head_dim, group_size, n_pairs))
+                splits, warps = kernels.decode_plan(ctx.n_decode_seqs, self.num_kv_heads, group_size, visible,
+                                                    self.head_dim, kernels.decode_widths(self.head_dim, group_size))
                 need = kernels.attention_decode_scratch_floats(ctx.n_seqs, self.num_heads, splits, self.head_dim)
                 scratch = ctx.extras.get("decode_scratch")
                 if need and (scratch is None or scratch.numel() < need):
@@ -130,7 +129,7 @@ class PagedAttention(Mixer):
                 kernels.attention_decode(out, q, kv, group.block_table, group.block_size,
                                          None if all_decode else ctx.decode_seq_ids, ctx.n_decode_seqs, ctx.cu_q,
                                          ctx.ctx_len, self.scale, self.window or 0, self.num_heads,
-                                         self.num_kv_heads, self.head_dim, splits, scratch if need else None)
+                                         self.num_kv_heads, self.head_dim, splits, scratch if need else None, warps)
             if ctx.n_q_tiles and USE_TC_PREFILL and kernels.tc_attention_supported(q.dtype, self.head_dim):
                 kernels.attention_prefill_tc(out, q, kv, group.block_table, group.block_size, ctx.q_tile128_seq,
                                              ctx.q_tile128_q0, ctx.n_q_tiles128, ctx.cu_q, ctx.ctx_len, self.scale,

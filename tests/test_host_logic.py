@@ -8,30 +8,40 @@ import numpy as np
 from lmsf_b200 import kernels
 from lmsf_b200.sampling.sampler import _TokenHistory
 
-# clusters of 1..8 decode blocks that a B200 holds at a time (head size 128: two blocks per SM, 148 SMs)
-B200_CLUSTERS = (296, 148, 93, 71, 56, 45, 37, 33)
+# The widths of a decode block on a B200 at head size 128 (148 SMs): wide blocks of four warps with 68 KB in flight,
+# two per SM, and narrow ones of two warps with 34 KB, four per SM; for each the clusters of 1..8 blocks that fit.
+B200_WIDE = (4, 2 * 2 * 64 * 272 / 65536.0, (296, 148, 93, 71, 56, 45, 37, 33))
+B200_NARROW = (2, 2 * 2 * 32 * 272 / 65536.0, (592, 296, 187, 142, 112, 93, 78, 71))
+B200_WIDTHS = (B200_WIDE, B200_NARROW)
 
 
 def test_key_splits_fill_one_wave_when_they_can():
-    pick = lambda n, ctx: kernels.decode_num_splits(n, 8, 4, ctx, B200_CLUSTERS)
-    assert pick(8, 2048) == 4                 # 64 clusters of 4: 71 fit
-    assert pick(5, 2048) == 6                 # 40 clusters: 45 of 6 fit, only 37 of 7
-    assert pick(12, 2048) == 2                # 96 clusters: 93 of 3 would need a second wave
-    assert pick(32, 2048) == 1 and pick(64, 2048) == 1
-    assert pick(1, 2048) == 8                 # the cluster's shared memory beats global memory for short contexts
-    assert pick(1, 32768) > 8                 # a long context wants every slot busy
+    pick = lambda n, ctx, kv=8, group=4: kernels.decode_plan(n, kv, group, ctx, 128, B200_WIDTHS)
+    assert pick(8, 2048) == (4, 4)            # 64 clusters of 4: 71 fit
+    assert pick(5, 2048) in ((5, 4), (6, 4))  # 40 clusters: 45 of 6 fit, only 37 of 7 (5 and 6 splits are a near tie)
+    assert pick(12, 2048) == (2, 4)           # 96 clusters: 93 of 3 would need a second wave
+    assert pick(32, 2048) == (1, 4)           # 256 wide blocks fit at once
+    assert pick(48, 2048) == (1, 2) and pick(64, 2048) == (1, 2)   # 384 and 512 do not; narrow ones do
+    assert pick(8, 4000, 40, 1) == (3, 2)     # 320 pairs of a model without grouping: 187 narrow clusters of 3 fit
+    assert pick(20, 2048) == (3, 2)           # 160 pairs: 187 narrow clusters of 3 fit, wide ones need two waves or no split
+    assert pick(48, 8000) == (2, 4)           # narrow blocks in 4 splits are 4 % better by the model: not enough to leave the wide ones
+    assert pick(1, 2048) == (8, 4)            # the cluster's shared memory beats global memory for short contexts
+    assert pick(1, 32768)[0] > 8              # a long context wants every slot busy
     for n in (1, 2, 3, 7, 8, 20, 64, 200):
         for ctx in (1, 64, 100, 128, 129, 500, 2048, 100000):
-            s = pick(n, ctx)
-            assert 1 <= s <= 64
+            s, w = pick(n, ctx)
+            assert 1 <= s <= 64 and w in (2, 4)
             assert s == 1 or ctx / s >= 64    # a split keeps at least 128 keys (rounded to tiles of 64)
+    # one width only (head sizes up to 64): the same rule among its split counts
+    assert kernels.decode_plan(64, 8, 4, 2048, 64, (B200_NARROW[:1] + (0.5,) + B200_NARROW[2:],))[0] == 1
 
 
 def test_split_choice_does_not_depend_on_what_it_should_not():
+    plan = lambda n, kv, group: kernels.decode_plan(n, kv, group, 2048, 128, B200_WIDTHS)
     # more query heads per kv head up to 16 share a block: same answer
-    assert kernels.decode_num_splits(8, 8, 1, 2048, B200_CLUSTERS) == kernels.decode_num_splits(8, 8, 16, 2048, B200_CLUSTERS)
+    assert plan(8, 8, 1) == plan(8, 8, 16)
     # 17 to 32 heads per kv head need two blocks per kv head: as if there were twice the kv heads
-    assert kernels.decode_num_splits(8, 8, 32, 2048, B200_CLUSTERS) == kernels.decode_num_splits(8, 16, 4, 2048, B200_CLUSTERS)
+    assert plan(8, 8, 32) == plan(8, 16, 4)
 
 
 def test_buckets_of_context_lengths():
