@@ -5,29 +5,36 @@
 // Counterpart in the reference: the dense float32 prompt attention of
 // core/src/model_executor/layers/attention.rs:106-159.
 //
-// One block serves two items that share their keys: 128 query tokens of TWO query heads of one kv head, or, for a
+// A unit of work is two items that share their keys: 128 query tokens of TWO query heads of one kv head, or, for a
 // head that is left over (an odd group, or no grouping), two consecutive tiles of 128 query tokens of that head; so
-// every k and v tile is fetched once for both.  Its warps have three roles:
+// every k and v tile is fetched once for both.  The launch has at most one block per SM (a block holds all of an SM's
+// tensor memory); block b of G takes the units b, 2G - 1 - b, 2G + b, ... of the list that the caller sorted longest
+// first, so the blocks get nearly equal shares, and every mbarrier's phases run on from unit to unit.  The warps
+// of a block have four roles:
 //   * two producer warps, one for k and one for v, bring tiles of 128 keys from their pages into rings of
 //     shared-memory stages with tensor-map copies (cp.async.bulk.tensor, one box per page and 64 head
 //     elements, 128-byte swizzled by the copy engine; k is read K-major, v MN-major); the copies' bytes are
-//     counted on mbarriers.  Pages of fewer than 8 keys are gathered with cp.async instead;
-//   * an issuing warp launches, for each head, S = Q K^T (M 128, N 128, K head size) into the head's score
-//     buffer in tensor memory and, when the head's P is ready, O += P V (M 128, N head size, K 128) with P
+//     counted on mbarriers.  Pages of fewer than 8 keys are gathered with cp.async instead.  They run ahead into
+//     the next unit's keys as far as the rings allow;
+//   * a producer of the queries: the 128 x head-size tile of an item comes by tensor-map copies from the step's
+//     [token][head x head size] matrix as soon as the item's last scores of the unit before are complete, i.e. while
+//     that unit's last softmax, last P V and output are still under way; with the queries it leaves the softmax
+//     warps a note of the unit's geometry in shared memory, so that no global load stands between two units;
+//   * an issuing warp launches, for each item, S = Q K^T (M 128, N 128, K head size) into the item's score
+//     buffer in tensor memory and, when the item's P is ready, O += P V (M 128, N head size, K 128) with P
 //     read from tensor memory, in two halves of 64 keys: the first half's P V runs while the softmax still works
-//     on the second half; completion goes to mbarriers through tcgen05.commit.  The two heads take turns: one
-//     head's products run while the other head's softmax is computed;
-//   * two groups of four softmax warps, one per head, one query row per thread, with registers moved to them
+//     on the second half; completion goes to mbarriers through tcgen05.commit.  The two items take turns: one
+//     item's products run while the other item's softmax is computed;
+//   * two groups of four softmax warps, one per item, one query row per thread, with registers moved to them
 //     from the other warps (setmaxnreg): tcgen05.ld of the row's 128 scores, mask where the tile needs one,
 //     running maximum (the accumulator is rescaled only when the maximum grew by more than 2^8, which keeps the
 //     sums exact and saves most read-modify-writes of tensor memory), exponentials in float32 with the packed
 //     two-value arithmetic of sm_100 around them, P as bfloat16 pairs written over the first 64 columns of S
 //     (tcgen05.st) and handed over in two halves.
 // The kernel is launched as a programmatic dependent: barriers and tensor memory are set up while the kernel before
-// it drains, and the queries are loaded while the first k and v tiles are already on their way.
-// One block per SM: all 512 columns of tensor memory (S or P of two heads, 128 each; O of two heads, 128 each)
-// and about 193 KB of shared memory (Q of two heads, two stages of k, two of v).  Every wait on an mbarrier is
-// bounded: when one runs out the block raises *error_flag (code 3), frees its tensor memory and returns.
+// it drains.  All 512 columns of tensor memory (S or P of two items, 128 each; O of two items, 128 each) and about
+// 193 KB of shared memory (Q of two items, two stages of k, two of v).  Every wait on an mbarrier is bounded: when
+// one runs out the block raises *error_flag (code 3), frees its tensor memory and returns.
 #include <cstdlib>
 #include <type_traits>
 
@@ -184,13 +191,18 @@ struct Unit {
   }
 };
 
-__global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args a, const __grid_constant__ CUtensorMap kv_map) {
+__global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args a, const __grid_constant__ CUtensorMap kv_map,
+                                                                      const __grid_constant__ CUtensorMap q_map) {
   extern __shared__ unsigned char smem_raw[];
   // k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages], s_full[item], p_full[item][half of P],
-  // o_done[item], q_full[item]
-  __shared__ __align__(8) uint64_t bars[4 * kStages + 10];
+  // o_done[item], q_full[item], q_free[item], taken[item]
+  __shared__ __align__(8) uint64_t bars[4 * kStages + 14];
   __shared__ uint32_t tmem_base_mem;
   __shared__ int failed_mem;
+  // What the softmax warps of item x need to know of its next unit, written by the producer of the queries before it
+  // announces the unit's queries on q_full[x]; two slots per item, used in turn.
+  struct __align__(16) UnitNote { int head, q0, rows, tb, te, start, tok0, tile_begin, lo, hi, tiles_before, last; };
+  __shared__ UnitNote notes[2][2];
   volatile int* failed = &failed_mem;
   const uint32_t smem = (smem_u32(smem_raw) + 1023u) & ~1023u;     // the swizzle pattern is a function of the address
   const uint32_t sQ = smem, sK = smem + kOffK, sV = smem + kOffV;
@@ -203,6 +215,8 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
   auto p_full = [&](int x, int h) { return bar0 + 8u * (4 * kStages + 2 + 2 * x + h); };
   auto o_done = [&](int x) { return bar0 + 8u * (4 * kStages + 6 + x); };
   auto q_full = [&](int x) { return bar0 + 8u * (4 * kStages + 8 + x); };
+  auto q_free = [&](int x) { return bar0 + 8u * (4 * kStages + 10 + x); };
+  auto taken = [&](int x) { return bar0 + 8u * (4 * kStages + 12 + x); };
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
   // What needs nothing from global memory comes first, so that it overlaps the tail of the kernel before this
@@ -223,7 +237,9 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
       mbar_init(p_full(x, 0), kSoftmaxThreads);
       mbar_init(p_full(x, 1), kSoftmaxThreads);
       mbar_init(o_done(x), 1);
-      mbar_init(q_full(x), kSoftmaxThreads);
+      mbar_init(q_full(x), 1);
+      mbar_init(q_free(x), 1);
+      mbar_init(taken(x), kSoftmaxThreads);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     failed_mem = 0;
@@ -340,6 +356,8 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
           umma(leader, tmem + x * BN, dq + (off_a >> 4), dk + (off_b >> 4), idesc_s, ks > 0);
         }
         umma_commit(leader, s_full(x));
+        // the item's last scores of this unit: when they are complete its queries may be overwritten by the next unit's
+        if (tile_begin + j == (x == 0 ? it0.te : it1.te) - 1) umma_commit(leader, q_free(x));
       };
       // O of item x += P V of tile j for the keys of half h (64 of the 128), P from tensor memory
       auto issue_pv = [&](int x, int j, int jx, int h) {
@@ -421,6 +439,61 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
         units_before[1] += 1;
       }
     }
+  } else {
+    // ------------------------------------------------------------------ producer of the queries (warp 11)
+    // Q tile of an item: [64-wide block][row][128 bytes], 128-byte swizzled, one tensor-map copy per 64-wide block.
+    // Rows beyond the portion hold the tokens that follow it in the step (zeros beyond the step's last token): their
+    // results are never written.  The queries of a unit are requested as soon as the last scores of the unit before
+    // are complete, so they arrive while that unit's last softmax, its last P V and its output are still under way.
+    // This warp also reads the lists that describe a unit (it runs ahead of the others) and leaves the softmax warps
+    // a note of what they need, so that no global load stands between two units on their path.
+    int units_before[2] = {0, 0};
+    int tiles_before = 0;
+    bool ok = true;
+    int issued[2] = {0, 0};
+    for (int pass = 0; ok; ++pass) {
+      const int unit = unit_of(pass);
+      if (unit >= n_units) break;
+      Unit u;
+      u.load(a, unit, units_per_tile, pairs);
+      if (u.empty) continue;
+#pragma unroll
+      for (int x = 0; x < 2; ++x) {
+        if (x == 1 && !u.two) continue;
+        const Item me = u.item(a, x);
+        // The item's scores of the unit before are complete: its queries may be overwritten.  And its softmax warps
+        // have taken that unit's note: q_full[x] has two kinds of waiters, the issuing warp and the softmax warps, and
+        // must not complete a second phase before both have seen the first (an item with a single tile in a unit
+        // frees its queries before its softmax warps have even finished the unit before); the note of two units
+        // ago is free as well then.
+        if (units_before[x] > 0 && (!mbar_wait_f(q_free(x), (uint32_t)((units_before[x] - 1) & 1), failed) ||
+                                    !mbar_wait_f(taken(x), (uint32_t)((units_before[x] - 1) & 1), failed))) { ok = false; break; }
+        if (lane == 0) {
+          notes[x][units_before[x] & 1] = UnitNote{me.head, me.q0, me.rows, me.tb, me.te, u.start, u.tok0, u.tile_begin, u.lo, u.hi,
+                                                   tiles_before, 0};
+          mbar_arrive_expect_tx(q_full(x), kQBytes);
+#pragma unroll
+          for (int hb = 0; hb < kHB; ++hb)
+            tma_load_box_2d(sQ + x * kQBytes + hb * (BM * 128), &q_map, me.head * HD + hb * 64, u.tok0 + me.q0, q_full(x));
+        }
+        units_before[x] += 1;
+        issued[x] = units_before[x];
+      }
+      tiles_before += u.n_tiles;
+    }
+    // no copy of this block may be in flight when it ends
+    for (int x = 0; x < 2; ++x)
+      if (issued[x] > 0) mbar_wait_drain(q_full(x), (uint32_t)((issued[x] - 1) & 1));
+    // the note that ends the softmax warps' loop
+    for (int x = 0; x < 2; ++x) {
+      if (ok && units_before[x] > 0)
+        ok = mbar_wait_f(q_free(x), (uint32_t)((units_before[x] - 1) & 1), failed) &&
+             mbar_wait_f(taken(x), (uint32_t)((units_before[x] - 1) & 1), failed);
+      if (lane == 0) {
+        notes[x][units_before[x] & 1].last = 1;
+        mbar_arrive(q_full(x));
+      }
+    }
   }
   } else {
     // ------------------------------------------------------------------ softmax of item x
@@ -429,40 +502,23 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
     const uint32_t t_row = tmem + ((uint32_t)((warp & 3) * 32) << 16);   // this warp's 32 lanes of tensor memory
     const uint32_t t_s = t_row + x * BN, t_o = t_row + kOCol + x * 128;
     const float sl2 = a.scale * kLog2e;
-    int tiles_before = 0;                                          // k (and v) tiles of the block's earlier units
-    int my_tiles_before = 0;                                       // tiles that this item has had in them
-    int my_units_before = 0;                                       // earlier units in which this item took part
+    int my_tiles_before = 0;                                       // tiles that this item has had in the units before
     bool ok = true;
-    for (int pass = 0; ok; ++pass) {
-      const int unit = unit_of(pass);
-      if (unit >= n_units) break;
-      Unit u;
-      u.load(a, unit, units_per_tile, pairs);
-      if (u.empty) continue;
-      if (x == 1 && !u.two) {
-        tiles_before += u.n_tiles;
-        continue;
-      }
-      const Item me = u.item(a, x);
-      {
-        // Q tile of this item: [64-wide block][row][128 bytes], rows beyond the portion are zero.  The products
-        // that read the last unit's queries are complete: the group has waited for the last scores.
-        constexpr int kChunks = HD / 8;
-#pragma unroll
-        for (int i = 0; i < BM * kChunks / kSoftmaxThreads; ++i) {
-          const int idx = row + i * kSoftmaxThreads;
-          const int r = idx / kChunks, c = idx % kChunks;
-          const bool in = r < me.rows;
-          const bf16* src = in ? a.q + (size_t)(u.tok0 + me.q0 + r) * a.q_stride + (size_t)me.head * HD + c * 8 : a.q;
-          cp_async_16(sQ + x * kQBytes + (c / 8) * (BM * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4), src, in ? 16 : 0);
-        }
-        cp_async_commit();
-        cp_async_wait<0>();
-        fence_async_smem();
-        mbar_arrive(q_full(x));          // the producers' first k and v tiles are on their way meanwhile
-      }
+    for (int my_units_before = 0; ok; ++my_units_before) {         // the units in which this item takes part
+      // the unit's queries are announced, and with them the note that describes the unit
+      ok = mbar_wait_f(q_full(x), (uint32_t)(my_units_before & 1), failed);
+      if (!ok) break;
+      // the note stays as it is until this item's next unit but one is announced; what is needed once or seldom
+      // is read where it is needed, so that it holds no register through the loop over the tiles
+      const volatile UnitNote* note = &notes[x][my_units_before & 1];
+      if (note->last) break;
+      mbar_arrive(taken(x));
+      struct { int rows, tb, te; } me = {note->rows, note->tb, note->te};
+      const int q_pos0 = note->start + note->q0;                    // position of the item's first query
+      const int stage0 = note->tiles_before + me.tb - note->tile_begin;   // the item's first tile counted over the block's units
+      const int u_lo = note->lo, u_hi = note->hi;
       const bool row_ok = row < me.rows;
-      const int pos = u.start + me.q0 + min(row, me.rows - 1);       // this thread's query position
+      const int pos = q_pos0 + min(row, me.rows - 1);                // this thread's query position
       const int row_lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
       float m_run = -INFINITY, l_run = 0.f;
       const int my_tiles = me.te - me.tb;
@@ -472,10 +528,10 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
         if (!ok) break;
         tc_fence_after();
         const int key0 = (me.tb + j) * BN;
-        const int ju = tiles_before + me.tb + j - u.tile_begin;      // the tile counted over the block's units: its stage
+        const int ju = stage0 + j;                                   // the tile counted over the block's units: its stage
         // Only tiles that reach past some row's position (the diagonal) or before its window need the mask;
         // the test is the same for the whole group of warps.
-        const bool need_mask = key0 + BN - 1 > u.start + me.q0 || (a.window > 0 && key0 < u.start + me.q0 + me.rows - a.window);
+        const bool need_mask = key0 + BN - 1 > q_pos0 || (a.window > 0 && key0 < q_pos0 + me.rows - a.window);
         // the row's 128 scores: four loads in flight, one wait
         float sc[BN];
 #pragma unroll
@@ -518,11 +574,11 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
             tmem_st32(t_o + c0, r);
           }
         }
-        if (key0 < u.lo || key0 + BN > u.hi) {
+        if (key0 < u_lo || key0 + BN > u_hi) {
           // rows of v whose keys no query of the tile sees hold whatever their page holds: clear them, so that
           // their zero weights cannot meet a value that is not finite (both items' warps do, with the same zeros)
           const uint32_t v = sV + (ju % kStages) * kKBytes;
-          const int r_lo = u.lo - key0, r_hi = u.hi - key0;
+          const int r_lo = u_lo - key0, r_hi = u_hi - key0;
           ok = mbar_wait_f(v_full(ju % kStages), (uint32_t)((ju / kStages) & 1), failed);   // the tile's v has landed
           if (!ok) break;
           for (int idx = row; idx < kHB * BN * 8; idx += kSoftmaxThreads) {
@@ -572,7 +628,7 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
       if (ok && my_tiles > 0) {
         tc_fence_after();
         const float inv = 1.0f / l_run;
-        bf16* dst = a.out + (size_t)(u.tok0 + me.q0 + row) * a.out_stride + (size_t)me.head * HD;
+        bf16* dst = a.out + (size_t)(note->tok0 + note->q0 + row) * a.out_stride + (size_t)note->head * HD;
 #pragma unroll
         for (int c0 = 0; c0 < HD; c0 += 32) {
           uint32_t r[32];
@@ -592,9 +648,7 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
         // the next unit's first P V overwrites O: the reads above are complete (tmem_ld32 waits for them)
         tc_fence_before();
       }
-      tiles_before += u.n_tiles;
       my_tiles_before += my_tiles;
-      my_units_before += 1;
     }
   }
   tc_fence_before();
@@ -639,8 +693,8 @@ LMSF_API int lmsf_attention_tc_head_dim() { return LMSF_HEAD_DIM; }
 
 
 // tile_seq / tile_q0: one entry per 128 query tokens of each portion, best listed with the tiles that see the
-// most keys first.  q and out rows must be 16-byte aligned.
-LMSF_API int lmsf_attention_prefill_tc(const void* q, long long q_stride, void* out, long long out_stride,
+// most keys first.  q and out rows must be 16-byte aligned; q has n_tokens rows (all tokens of the step).
+LMSF_API int lmsf_attention_prefill_tc(const void* q, long long q_stride, long long n_tokens, void* out, long long out_stride,
                                        const void* cache, long long page_stride, long long n_pages, int block_size,
                                        int n_kv_heads, const int* block_table, int max_blocks, const int* tile_seq, const int* tile_q0,
                                        int n_tiles, const int* cu_q, const int* ctx_len, float scale, int window,
@@ -653,6 +707,8 @@ LMSF_API int lmsf_attention_prefill_tc(const void* q, long long q_stride, void* 
     LMSF_REFUSE("attention_prefill_tc: %d query heads cannot be grouped over %d kv heads", n_q_heads, n_kv_heads);
   if (n_tiles > 65535) LMSF_REFUSE("attention_prefill_tc: more than 65535 query tiles in one launch");
   if (max_blocks <= 0) LMSF_REFUSE("attention_prefill_tc: bad block table geometry");
+  if (n_tokens <= 0 || q_stride < (long long)n_q_heads * HD)
+    LMSF_REFUSE("attention_prefill_tc: q must have a positive number of rows of at least heads x head size elements");
   if (q_stride % 8 || out_stride % 8 || ((uintptr_t)q | (uintptr_t)out | (uintptr_t)cache) % 16 || page_stride % 8)
     LMSF_REFUSE("attention_prefill_tc: q, out and the cache must be 16-byte aligned with row strides that are multiples of 8");
   Args a;
@@ -673,6 +729,20 @@ LMSF_API int lmsf_attention_prefill_tc(const void* q, long long q_stride, void* 
     const CUtensorMap* m = cache_tensor_map(cache, page_stride, block_size, n_kv_heads, n_pages, a.rows_box, &why);
     if (!m) LMSF_REFUSE("attention_prefill_tc: %s", why);
     kv_map = *m;
+  }
+  // the queries as a 2-d tensor for the copy engine: (head x head size, token), a box of 64 elements x 128 tokens
+  CUtensorMap q_map;
+  {
+    EncodeTiledFn encode = encode_tiled_fn();
+    if (!encode) LMSF_REFUSE("attention_prefill_tc: the driver has no cuTensorMapEncodeTiled");
+    const cuuint64_t dims[2] = {(cuuint64_t)n_q_heads * HD, (cuuint64_t)n_tokens};
+    const cuuint64_t strides[1] = {(cuuint64_t)q_stride * 2};
+    const cuuint32_t box[2] = {64, (cuuint32_t)BM};
+    const cuuint32_t elem_strides[2] = {1, 1};
+    const CUresult r = encode(&q_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(q), dims, strides, box, elem_strides,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) LMSF_REFUSE("attention_prefill_tc: cuTensorMapEncodeTiled refused the queries' geometry");
   }
   static bool configured = false;
   if (!configured) {
@@ -695,5 +765,5 @@ LMSF_API int lmsf_attention_prefill_tc(const void* q, long long q_stride, void* 
     const long long cap = atoll(e);
     if (cap > 0 && cap < n_blocks) n_blocks = cap;
   }
-  return launch_pdl(prefill_tc_kernel, dim3((unsigned)n_blocks), dim3(kThreadsTotal), kSmemBytes, (cudaStream_t)stream, a, kv_map);
+  return launch_pdl(prefill_tc_kernel, dim3((unsigned)n_blocks), dim3(kThreadsTotal), kSmemBytes, (cudaStream_t)stream, a, kv_map, q_map);
 }

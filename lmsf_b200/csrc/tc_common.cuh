@@ -132,7 +132,12 @@ __device__ __forceinline__ void tma_load_box(uint32_t dst, const CUtensorMap* ma
       "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
       ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(mbar) : "memory");
 }
-
+// One box of a 2-d tensor map (64 elements x a number of rows), e.g. of the queries [token][head x head size].
+__device__ __forceinline__ void tma_load_box_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t mbar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(mbar) : "memory");
+}
 
 // ---- tensor maps --------------------------------------------------------------------------------------
 // cuTensorMapEncodeTiled is looked up in the driver at run time, so that the libraries do not link against it.

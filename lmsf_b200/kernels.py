@@ -559,9 +559,10 @@ def attention_prefill_tc(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor
     _check_paged(q, out, cache, n_q_heads, n_kv_heads, head_dim, block_size, "attention_prefill_tc")
     d = _mma_defines(head_dim)[:1]
     f = _func("attention_tc.cu", "lmsf_attention_prefill_tc",
-              [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_longlong, c_int, c_int, c_void_p, c_int,
-               c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_void_p, c_void_p], d)
-    rc = f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache), cache.stride(0), cache.shape[0], block_size,
+              [c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_longlong, c_int, c_int,
+               c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_void_p,
+               c_void_p], d)
+    rc = f(_ptr(q), q.stride(0), q.shape[0], _ptr(out), out.stride(0), _ptr(cache), cache.stride(0), cache.shape[0], block_size,
            n_kv_heads, _i32(block_table, "block_table"), block_table.shape[1], _i32(tile_seq, "tile_seq"),
            _i32(tile_q0, "tile_q0"), n_tiles, _i32(cu_q, "cu_q"), _i32(ctx_len, "ctx_len"), float(scale),
            int(window or 0), n_q_heads, head_dim, _i32(error_flag, "error_flag"), _stream())

@@ -303,6 +303,38 @@ def test_attention_tensor_core_kernels(nh, nkv, hd, bs, window, warps, monkeypat
     assert (out2.float() - out.float()).abs().max().item() <= tol_abs
 
 
+@pytest.mark.parametrize("max_blocks", [2, 0])
+def test_attention_tcgen05_runs_of_short_units(max_blocks, monkeypatch):
+    """Many short prompts beside a long one: a block takes long runs of units of a single key tile, in which an
+    item's queries are free again before its softmax warps have finished the unit before (the hand-over of the
+    next unit's queries must wait for both), mixed with units of many tiles."""
+    from lmsf_b200 import kernels
+    nh, nkv, hd, bs = 8, 2, 128, 16
+    if max_blocks:
+        monkeypatch.setenv("LMSF_TC_MAX_BLOCKS", str(max_blocks))
+    q_lens = [100] * 30 + [900] + [64] * 20 + [129] * 6
+    ctx_lens = list(q_lens)
+    ctx_lens[30] = 1300
+    q, cache, bt, token_seq, positions, ks, vs = _paged_setup("bfloat16", nh, nkv, hd, bs, ctx_lens, q_lens, 21, sharp=True,
+                                                              poison=True)
+    scale = 1.0 / math.sqrt(hd)
+    ref = _attention_reference(q.float(), ks, vs, token_seq, positions, nh, nkv, hd, scale, 0)
+    d = dev()
+    qd, cd, btd = q.to(d), cache.to(d), bt.to(d)
+    cu = torch.tensor([0] + list(np.cumsum(q_lens)), dtype=torch.int32, device=d)
+    cl = torch.tensor(ctx_lens, dtype=torch.int32, device=d)
+    tiles = [(i, q0) for i, n in enumerate(q_lens) for q0 in range(0, n, 128)]
+    flag = torch.zeros(1, dtype=torch.int32, device=d)
+    for _ in range(3):
+        out = torch.zeros(q.shape, dtype=torch.bfloat16, device=d)
+        kernels.attention_prefill_tc(out, qd, cd, btd, bs, torch.tensor([t[0] for t in tiles], dtype=torch.int32, device=d),
+                                     torch.tensor([t[1] for t in tiles], dtype=torch.int32, device=d), len(tiles), cu, cl,
+                                     scale, 0, nh, nkv, hd, flag)
+        assert flag.item() == 0
+        err = (out.float().cpu().double() - ref).abs()
+        assert err.max().item() <= 2e-2 * ref.abs().max().item(), (err.max().item(), int(err.argmax()) // (nh * hd))
+
+
 def test_sampling_filters_and_penalties():
     from lmsf_b200 import kernels
     g = torch.Generator().manual_seed(7)
