@@ -148,9 +148,17 @@ __device__ __forceinline__ void gather_tile(uint32_t dst_tile, const PagedKV& kv
   }
 }
 
-// A unit of work is a pair of items that share their keys: (a tile of 128 query tokens, a kv head, a pair of its
-// query heads).  Units are numbered with all heads of tile 0 first, then of tile 1, ...; the caller lists the tiles
-// that see the most keys first.
+// A unit of work is a pair of items that share their keys.  First come the units of two query heads of one kv head:
+// (a tile of 128 query tokens, a kv head, a pair of its heads), numbered with all heads of tile 0 first, then of tile
+// 1, ...; the caller lists the tiles that see the most keys first.  Then, if a kv head has an odd number of query
+// heads (or one: no grouping), the units of the head that is left over: it takes two consecutive tiles of 128 query
+// tokens, so there is one unit for every tile that leads such a pair (q0 a multiple of 256) and kv head; the block
+// lists the leading tiles in shared memory when it starts.
+constexpr int kMaxLeadTiles = 4096;
+struct UnitMap {
+  int full_pairs, n_kv, units_full_per_tile, n_full, n_units;
+  const unsigned short* lead;       // the tiles that lead a pair, in the order of the caller's list; null: see below
+};
 struct Item { int head, q0, rows, hi, lo, tb, te; };   // a head and 128 query tokens; it sees the keys [lo, hi) in the tiles [tb, te)
 struct Unit {
   int seq, kvh, head0, q0, tok0, n, start;
@@ -167,19 +175,31 @@ struct Unit {
     i.te = (i.hi + BN - 1) / BN;
     return i;
   }
-  __device__ __forceinline__ void load(const Args& a, int unit, int units_per_tile, int pairs) {
-    const int tile = unit / units_per_tile, bx = unit % units_per_tile;
+  // kLeft: the kernel is built twice, for even groups of heads (no unit of a head that is left over: the plain
+  // numbering, which is also a little faster) and for odd ones
+  template <bool kLeft>
+  __device__ __forceinline__ void load(const Args& a, int unit, const UnitMap& m) {
+    int tile, pair;
+    if (!kLeft || unit < m.n_full) {
+      tile = unit / m.units_full_per_tile;
+      const int bx = unit % m.units_full_per_tile;
+      kvh = bx / m.full_pairs;
+      pair = bx % m.full_pairs;
+    } else {
+      const int j = unit - m.n_full;
+      // with more leading tiles than the list holds every tile has a unit, and those of the tiles that do not lead are empty
+      tile = m.lead ? m.lead[j / m.n_kv] : j / m.n_kv;
+      kvh = j % m.n_kv;
+      pair = m.full_pairs;
+    }
     seq = a.tile_seq[tile];
     q0 = a.tile_q0[tile];
-    kvh = bx / pairs;
-    const int pair = bx % pairs;
     head0 = kvh * a.group + 2 * pair;
     two_heads = 2 * pair + 1 < a.group;                         // the unit has a second head of the same kv head
     tok0 = a.cu_q[seq];
     n = a.cu_q[seq + 1] - tok0;
     start = a.ctx_len[seq] - n;
-    // A head that is left over (an odd group, or no grouping at all) takes two query tiles instead: this one and
-    // the 128 tokens behind it.  The unit of that second tile is empty.
+    // A head that is left over takes two query tiles: this one and the 128 tokens behind it.
     empty = !two_heads && (q0 & (2 * BM - 1)) != 0;
     two = two_heads || q0 + BM < n;                             // the unit has a second item
     const Item i0 = item(a, 0), i1 = item(a, 1);
@@ -191,6 +211,7 @@ struct Unit {
   }
 };
 
+template <bool kLeft>
 __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args a, const __grid_constant__ CUtensorMap kv_map,
                                                                       const __grid_constant__ CUtensorMap q_map) {
   extern __shared__ unsigned char smem_raw[];
@@ -199,6 +220,8 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
   __shared__ __align__(8) uint64_t bars[4 * kStages + 14];
   __shared__ uint32_t tmem_base_mem;
   __shared__ int failed_mem;
+  __shared__ unsigned short lead_tiles[kLeft ? kMaxLeadTiles : 1];
+  __shared__ int n_lead_mem;
   // What the softmax warps of item x need to know of its next unit, written by the producer of the queries before it
   // announces the unit's queries on q_full[x]; two slots per item, used in turn.
   struct __align__(16) UnitNote { int head, q0, rows, tb, te, start, tok0, tile_begin, lo, hi, tiles_before, last; };
@@ -248,6 +271,20 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_mem)), "r"(kTmemCols));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
   }
+  if (kLeft && warp == 1) {
+    // The tiles that lead a pair (the tile lists are inputs of the step: no kernel writes them, so they may be read
+    // before the dependency wait).  More than the list holds: n_lead = -1, and every tile gets a unit.
+    int count = 0;
+    for (int base = 0; base < a.n_q_tiles; base += 32) {
+      const int t = base + lane;
+      const bool is_lead = t < a.n_q_tiles && (a.tile_q0[t] & (2 * BM - 1)) == 0;
+      const unsigned mask = __ballot_sync(0xffffffffu, is_lead);
+      const int pos = count + __popc(mask & ((1u << lane) - 1u));
+      if (is_lead && pos < kMaxLeadTiles) lead_tiles[pos] = (unsigned short)t;
+      count += __popc(mask);
+    }
+    if (lane == 0) n_lead_mem = count <= kMaxLeadTiles ? count : -1;
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -258,9 +295,17 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
   // ...: with a list sorted by length the blocks get nearly equal shares, a block pays for its barriers and tensor
   // memory once, and its producers fetch the next unit's first keys while the last unit is finished.  The
   // mbarriers' phases run on through the units, so every role counts what went before (all in the same way).
-  const int pairs = (a.group + 1) / 2;                          // units per kv head and tile
-  const int units_per_tile = a.kv.n_kv_heads * pairs;
-  const int n_units = units_per_tile * a.n_q_tiles;
+  UnitMap um;
+  um.full_pairs = a.group / 2;
+  um.n_kv = a.kv.n_kv_heads;
+  um.units_full_per_tile = um.n_kv * um.full_pairs;
+  um.n_full = um.units_full_per_tile * a.n_q_tiles;
+  {
+    const int n_lead = kLeft ? n_lead_mem : 0;
+    um.lead = n_lead >= 0 ? lead_tiles : nullptr;
+    um.n_units = um.n_full + (kLeft ? um.n_kv * (n_lead >= 0 ? n_lead : a.n_q_tiles) : 0);
+  }
+  const int n_units = um.n_units;
   const int G = gridDim.x;
   auto unit_of = [&](int pass) { return pass * G + ((pass & 1) ? G - 1 - (int)blockIdx.x : (int)blockIdx.x); };
 
@@ -279,7 +324,7 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
       const int unit = unit_of(pass);
       if (unit >= n_units) break;
       Unit u;
-      u.load(a, unit, units_per_tile, pairs);
+      u.template load<kLeft>(a, unit, um);
       if (u.empty) continue;
       const int* table = a.block_table + (size_t)u.seq * a.max_blocks;
       if (a.use_tma) {
@@ -340,7 +385,7 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
       const int unit = unit_of(pass);
       if (unit >= n_units) break;
       Unit u;
-      u.load(a, unit, units_per_tile, pairs);
+      u.template load<kLeft>(a, unit, um);
       if (u.empty) continue;
       const Item it0 = u.item(a, 0), it1 = u.item(a, 1);
       const int nx = u.two ? 2 : 1;
@@ -455,7 +500,7 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
       const int unit = unit_of(pass);
       if (unit >= n_units) break;
       Unit u;
-      u.load(a, unit, units_per_tile, pairs);
+      u.template load<kLeft>(a, unit, um);
       if (u.empty) continue;
 #pragma unroll
       for (int x = 0; x < 2; ++x) {
@@ -744,11 +789,13 @@ LMSF_API int lmsf_attention_prefill_tc(const void* q, long long q_stride, long l
                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) LMSF_REFUSE("attention_prefill_tc: cuTensorMapEncodeTiled refused the queries' geometry");
   }
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+  const bool left = (a.group & 1) != 0;          // a kv head has a query head that no other shares a unit with
+  void (*kernel)(const Args, const CUtensorMap, const CUtensorMap) = left ? prefill_tc_kernel<true> : prefill_tc_kernel<false>;
+  static bool configured[2] = {false, false};
+  if (!configured[left]) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    configured[left] = true;
   }
   // one block per SM at most (a block holds all of an SM's tensor memory); the blocks share the units out among them
   static int n_sms = 0;
@@ -765,5 +812,5 @@ LMSF_API int lmsf_attention_prefill_tc(const void* q, long long q_stride, long l
     const long long cap = atoll(e);
     if (cap > 0 && cap < n_blocks) n_blocks = cap;
   }
-  return launch_pdl(prefill_tc_kernel, dim3((unsigned)n_blocks), dim3(kThreadsTotal), kSmemBytes, (cudaStream_t)stream, a, kv_map, q_map);
+  return launch_pdl(kernel, dim3((unsigned)n_blocks), dim3(kThreadsTotal), kSmemBytes, (cudaStream_t)stream, a, kv_map, q_map);
 }
