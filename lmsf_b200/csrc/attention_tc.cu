@@ -157,7 +157,7 @@ __device__ __forceinline__ void gather_tile(uint32_t dst_tile, const PagedKV& kv
 constexpr int kMaxLeadTiles = 4096;
 struct UnitMap {
   int full_pairs, n_kv, units_full_per_tile, n_full, n_units;
-  const unsigned short* lead;       // the tiles that lead a pair, in the order of the caller's list; null: see below
+  const unsigned short* lead;       // the tiles that lead a pair, in the order of the caller's list
 };
 struct Item { int head, q0, rows, hi, lo, tb, te; };   // a head and 128 query tokens; it sees the keys [lo, hi) in the tiles [tb, te)
 struct Unit {
@@ -187,8 +187,7 @@ struct Unit {
       pair = bx % m.full_pairs;
     } else {
       const int j = unit - m.n_full;
-      // with more leading tiles than the list holds every tile has a unit, and those of the tiles that do not lead are empty
-      tile = m.lead ? m.lead[j / m.n_kv] : j / m.n_kv;
+      tile = m.lead[j / m.n_kv];
       kvh = j % m.n_kv;
       pair = m.full_pairs;
     }
@@ -273,7 +272,7 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
   }
   if (kLeft && warp == 1) {
     // The tiles that lead a pair (the tile lists are inputs of the step: no kernel writes them, so they may be read
-    // before the dependency wait).  More than the list holds: n_lead = -1, and every tile gets a unit.
+    // before the dependency wait).  The launcher takes no more tiles than the list holds.
     int count = 0;
     for (int base = 0; base < a.n_q_tiles; base += 32) {
       const int t = base + lane;
@@ -283,7 +282,7 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
       if (is_lead && pos < kMaxLeadTiles) lead_tiles[pos] = (unsigned short)t;
       count += __popc(mask);
     }
-    if (lane == 0) n_lead_mem = count <= kMaxLeadTiles ? count : -1;
+    if (lane == 0) n_lead_mem = min(count, kMaxLeadTiles);
   }
   tc_fence_before();
   __syncthreads();
@@ -301,9 +300,8 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
   um.units_full_per_tile = um.n_kv * um.full_pairs;
   um.n_full = um.units_full_per_tile * a.n_q_tiles;
   {
-    const int n_lead = kLeft ? n_lead_mem : 0;
-    um.lead = n_lead >= 0 ? lead_tiles : nullptr;
-    um.n_units = um.n_full + (kLeft ? um.n_kv * (n_lead >= 0 ? n_lead : a.n_q_tiles) : 0);
+    um.lead = lead_tiles;
+    um.n_units = um.n_full + (kLeft ? um.n_kv * n_lead_mem : 0);
   }
   const int n_units = um.n_units;
   const int G = gridDim.x;
@@ -323,7 +321,7 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
     for (int pass = 0; ok; ++pass) {
       const int unit = unit_of(pass);
       if (unit >= n_units) break;
-      Unit u;
+      Unit u = {};
       u.template load<kLeft>(a, unit, um);
       if (u.empty) continue;
       const int* table = a.block_table + (size_t)u.seq * a.max_blocks;
@@ -384,7 +382,7 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
     for (int pass = 0; ok; ++pass) {
       const int unit = unit_of(pass);
       if (unit >= n_units) break;
-      Unit u;
+      Unit u = {};
       u.template load<kLeft>(a, unit, um);
       if (u.empty) continue;
       const Item it0 = u.item(a, 0), it1 = u.item(a, 1);
@@ -499,7 +497,7 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
     for (int pass = 0; ok; ++pass) {
       const int unit = unit_of(pass);
       if (unit >= n_units) break;
-      Unit u;
+      Unit u = {};
       u.template load<kLeft>(a, unit, um);
       if (u.empty) continue;
 #pragma unroll
@@ -790,6 +788,9 @@ LMSF_API int lmsf_attention_prefill_tc(const void* q, long long q_stride, long l
     if (r != CUDA_SUCCESS) LMSF_REFUSE("attention_prefill_tc: cuTensorMapEncodeTiled refused the queries' geometry");
   }
   const bool left = (a.group & 1) != 0;          // a kv head has a query head that no other shares a unit with
+  if (left && n_tiles > kMaxLeadTiles)
+    LMSF_REFUSE("attention_prefill_tc: with an odd number of query heads per kv head a launch takes %d query tiles at most, not %d",
+                kMaxLeadTiles, n_tiles);
   void (*kernel)(const Args, const CUtensorMap, const CUtensorMap) = left ? prefill_tc_kernel<true> : prefill_tc_kernel<false>;
   static bool configured[2] = {false, false};
   if (!configured[left]) {
