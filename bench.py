@@ -220,10 +220,17 @@ def measure_shape(cfg, n_layers, ctx_len, batches, steps, warmup, pk, with_prefi
 
 
 def other_model_points(pk, steps, warmup):
-    """The other shapes that the baseline names, as points of the same line: Llama-3.2-1B (decode at batch 64 and
-    64 requests under continuous batching) and Llama-2-13B (decode at batch 8 with 4,000-token contexts and a
+    """The other workloads that the baseline names, as points of the same line: 64 requests under continuous batching
+    on the headline shape; Llama-3.2-1B (decode at batch 64 and the same 64 requests) and Llama-2-13B (decode at batch 8 with 4,000-token contexts and a
     2,048-token prefill).  Each point has its own clock record."""
     points, clocks = {}, {}
+    cfg = dict(MODELS["llama3-8b"])
+    sampler = ClockSampler()
+    sampler.start()
+    srv = serve(cfg, cfg["num_hidden_layers"], 64, 256, 2048, quiet=True)
+    clocks["llama3-8b_serve"] = sampler.stop()
+    points["llama3-8b_serve_generated_tok_s"] = srv["value"]
+    points["llama3-8b_serve_total_tok_s"] = srv["total_tokens_per_s"]
     cfg = dict(MODELS["llama3.2-1b"])
     res, _, nums, _ = measure_shape(cfg, cfg["num_hidden_layers"], CONTEXT, [64], steps, warmup, pk, with_prefill=False)
     ms, _, rec = res[64]
@@ -301,7 +308,9 @@ def serve(cfg, n_layers, n_requests, decode_tokens, budget, quiet=False):
     lens = [rng.randint(128, 2048) for _ in range(n_requests)]
     g = torch.Generator().manual_seed(3)
     sp = SamplingParams(temperature=0.0, max_tokens=decode_tokens, ignore_eos=True)
-    for rep in range(2):                       # the first pass warms up (compilation, graphs); the second is timed
+    # Two passes warm up (compilation; a decode graph is captured the second time its size is seen, and the sizes of
+    # the last steps, when requests run out, are seen once or twice a pass); the third is timed.
+    for rep in range(3):
         for i, n in enumerate(lens):
             engine.add_request((rep, i), None, sp, prompt_token_ids=torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist())
         torch.cuda.synchronize()
