@@ -235,6 +235,17 @@ class ModelRunner:
             b *= 2
         return min(b, max(self.max_model_len, 1))
 
+    @staticmethod
+    def graph_skew_class(bucket: int, mean_ctx: float) -> int:
+        """How far the mean context of a decode batch lies below its bucket: 0 when within a factor of 4, else the
+        number of further doublings, up to 4 (a 64th and less).  One long request among short ones is split into more
+        blocks than a batch of long requests would be; the class is part of a graph's key because the split is
+        part of its geometry."""
+        c = 0
+        while c < 4 and mean_ctx * (8 << c) <= bucket:
+            c += 1
+        return c
+
     def _graph_eligible(self, entries: Sequence[StepEntry]) -> bool:
         return (not self.enforce_eager and self.graph_safe and len(entries) <= self.max_graph_batch
                 and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries))
@@ -259,12 +270,16 @@ class ModelRunner:
         the pair is seen); the returned tensor is then a view
         of the graph's own output buffer and holds its values until the next step of the same size."""
         graph_mode = self._graph_eligible(entries)
-        bucket = self.graph_context_bucket(max(mgr.num_tokens(e.request_id) + 1 for e in entries)) if graph_mode else 0
+        bucket = skew = 0
+        if graph_mode:
+            lens = [mgr.num_tokens(e.request_id) + 1 for e in entries]
+            bucket = self.graph_context_bucket(max(lens))
+            skew = self.graph_skew_class(bucket, sum(lens) / len(lens))
         # a graph's block tables are as wide as its bucket of context lengths needs, not as the longest context allowed
         hb = self._prepare(entries, mgr, (bucket + self.block_size - 1) // self.block_size if graph_mode else None,
                            self.graph_batch_size(len(entries)) if graph_mode else 0)
         self.storage.zero_state_slots(mgr.take_fresh_slots())
-        key = (hb.S, bucket) if graph_mode else None
+        key = (hb.S, bucket, skew) if graph_mode else None
         if graph_mode and (key in self._graphs or key in self._seen_sizes):
             logits = self._replay(hb, key, pending_tokens)
         else:
@@ -280,7 +295,7 @@ class ModelRunner:
             self.check_device_errors()
         return logits[:len(entries)] if graph_mode else logits
 
-    def _replay(self, hb: "_HostBatch", key: Tuple[int, int], pending_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def _replay(self, hb: "_HostBatch", key: Tuple[int, int, int], pending_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         g = self._graphs.get(key)
         if g is None:
             static_in = self._upload(hb)
@@ -288,6 +303,9 @@ class ModelRunner:
             # launch geometry must not depend on the step, only on its bucket: the decode attention plans its splits
             # for the middle of the bucket's context lengths (the bucket below ends at half its top)
             ctx.extras["decode_max_ctx"] = key[1] - key[1] // 4 if key[1] > 1024 else key[1]
+            # the middle of the graph's class of means: between bucket / (8 << c) and twice that (the last class: and
+            # below); class 0 plans as if all contexts were as long as the longest
+            ctx.extras["decode_mean_ctx"] = key[1] * 3 / (16 << key[2]) if key[2] else ctx.extras["decode_max_ctx"]
             if self._graph_pool is None:
                 self._graph_pool = torch.cuda.graph_pool_handle()
                 self._capture_stream = torch.cuda.Stream(self.device)

@@ -448,22 +448,31 @@ DECODE_WAVE_COST = 6.0          # what a wave of blocks costs before and after i
 DECODE_SPLIT_COST = 4.0         # adding the splits of a request up
 DECODE_GLOBAL_MERGE_COST = 6.0  # more when more than 8 splits add up through global memory
 DECODE_SATURATION = 240.0       # blocks with 64 KB in flight that saturate the memory
+DECODE_BLOCK_COST = 1.3         # what a block costs the slot it runs in, beside its keys (tables, first loads, its part of the sum)
 DECODE_MUST_GAIN = 0.95         # a narrower block or a further split is taken when the model gives it 5 % less
 
 
 def decode_plan(n_served: int, n_kv_heads: int, group: int, max_ctx: int, head_dim: int,
-                widths: Sequence[Tuple[int, float, Sequence[int]]]) -> Tuple[int, int]:
+                widths: Sequence[Tuple[int, float, Sequence[int]]], mean_ctx: Optional[float] = None) -> Tuple[int, int]:
     """(splits, warps): into how many blocks the keys of a request are split, and how wide the blocks are.  Up to 8
     splits form a thread-block cluster (they add up through its shared memory) and clusters[s - 1] such clusters
     run at a time; more splits add up through global memory.  The choice minimises the sum over the waves of
     (fixed cost + keys per split / rate), where a block streams at the rate of its own bytes in flight or, when more
     blocks are resident than saturate the memory, at its share of the device: few long requests want wide blocks
     and many splits, many requests narrow blocks, of which twice as many are resident, and no second, partly filled
-    wave.  Every split keeps at least 128 keys.  Measured on B200 (head size 128, 8 kv heads, 2,048 keys):
+    wave.  Every split keeps at least 128 keys.  mean_ctx: the requests' mean number of keys, when it is far below
+    max_ctx (one long request among short ones): every request gets the same number of splits, so the longest one
+    sets the time of a wave unless it is split as if it were nearly alone; the short requests' extra blocks find
+    no keys and cost only their slots (64 requests of the 8B shape, one with 30,000 keys among 63 with 500, took
+    0.8 ms a layer planned for 64 requests of 30,000 keys, the long request's 8 blocks streaming alone).  Measured on B200 (head size 128, 8 kv heads, 2,048 keys):
     5 requests take 20.5 us with 6 splits (45 clusters fit) and 30.7 us with 7 (37 fit); 48 requests 100 us at best
     with wide blocks (2 splits) and 95 us with narrow ones (1 split); a decode step of 20 requests 4.72 ms with wide
     blocks and one split, 4.42 ms with narrow ones and 3."""
-    base = n_served * n_kv_heads * ((group + 15) // 16)
+    per_request = n_kv_heads * ((group + 15) // 16)
+    n_blocks1 = n_served * per_request                            # blocks of the launch per split
+    # the requests that matter for the time of a wave: all of them, or as many as would hold the keys at max_ctx each
+    work_served = n_served if not mean_ctx else max(1, min(n_served, -(-int(n_served * mean_ctx) // max(1, max_ctx))))
+    base = work_served * per_request
     tiles = -(-max_ctx // 64)
     cap = max(1, -(-max_ctx // 128))
     tile_work = head_dim / 128.0                  # a 64-key tile of k and v in units of 32 KB
@@ -476,6 +485,7 @@ def decode_plan(n_served: int, n_kv_heads: int, group: int, max_ctx: int, head_d
             per_wave = clusters[s - 1] if s <= 8 else max(1, slots // s)      # (request, head group) pairs per wave
             work = -(-tiles // s) * tile_work
             cost = (DECODE_SPLIT_COST if s > 1 else 0.0) + (DECODE_GLOBAL_MERGE_COST if s > 8 else 0.0)
+            cost += DECODE_BLOCK_COST * n_blocks1 * s / (per_wave * s)
             left = base
             while left > 0:
                 n = min(left, per_wave) * s

@@ -118,9 +118,16 @@ class PagedAttention(Mixer):
                 if max_ctx is None:
                     max_ctx = ctx.extras["decode_max_ctx"] = max(c for c, n in zip(ctx.ctx_lens, ctx.q_lens) if n == 1)
                 visible = min(max_ctx, self.window) if self.window else max_ctx
+                # the mean matters to the plan only where it is far below the longest context (a graph names its class)
+                mean_ctx = ctx.extras.get("decode_mean_ctx")
+                if mean_ctx is None:
+                    lens = [c for c, n in zip(ctx.ctx_lens, ctx.q_lens) if n == 1]
+                    mean_ctx = ctx.extras["decode_mean_ctx"] = sum(lens) / len(lens)
+                mean_visible = min(mean_ctx, visible)
                 group_size = self.num_heads // self.num_kv_heads
                 splits, warps = kernels.decode_plan(ctx.n_decode_seqs, self.num_kv_heads, group_size, visible,
-                                                    self.head_dim, kernels.decode_widths(self.head_dim, group_size))
+                                                    self.head_dim, kernels.decode_widths(self.head_dim, group_size),
+                                                    mean_ctx=mean_visible if mean_visible * 2 <= visible else None)
                 need = kernels.attention_decode_scratch_floats(ctx.n_seqs, self.num_heads, splits, self.head_dim)
                 scratch = ctx.extras.get("decode_scratch")
                 if need and (scratch is None or scratch.numel() < need):

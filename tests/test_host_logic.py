@@ -36,6 +36,18 @@ def test_key_splits_fill_one_wave_when_they_can():
     assert kernels.decode_plan(64, 8, 4, 2048, 64, (B200_NARROW[:1] + (0.5,) + B200_NARROW[2:],))[0] == 1
 
 
+def test_one_long_request_among_short_ones_is_split_as_if_nearly_alone():
+    plan = lambda n, ctx, mean=None: kernels.decode_plan(n, 8, 4, ctx, 128, B200_WIDTHS, mean_ctx=mean)
+    alone = plan(1, 30000)
+    assert alone[0] >= 16
+    assert plan(64, 30000)[0] == 1                        # 64 long requests fill the device without a split
+    s, w = plan(64, 30000, mean=960)                      # one of them long: its keys are split
+    assert s >= 6
+    from lmsf_b200.engine.model_runner import ModelRunner
+    c = ModelRunner.graph_skew_class
+    assert [c(4096, m) for m in (4096, 600, 512, 256, 100, 64, 1)] == [0, 0, 1, 2, 3, 4, 4]
+
+
 def test_split_choice_does_not_depend_on_what_it_should_not():
     plan = lambda n, kv, group: kernels.decode_plan(n, kv, group, 2048, 128, B200_WIDTHS)
     # more query heads per kv head up to 16 share a block: same answer

@@ -118,6 +118,26 @@ def test_many_live_requests_decoding_together(n_live, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_one_long_request_decoding_among_short_ones(dtype):
+    """A request of 480 tokens decodes beside eleven of 12 to 30: the decode graph of such a batch splits every
+    request's keys as the long one needs it, so most blocks of the short ones find no keys."""
+    name, std = "C", 0.15
+    cfg = util.CONFIGS[name]
+    lengths = [480] + [12 + (7 * i) % 19 for i in range(11)]
+    reqs = {f"k{i}": util.random_ids(n, cfg["vocab_size"], 700 + i) for i, n in enumerate(lengths)}
+    ref = reference(name, dtype, std, reqs)
+    steps = traces.many_live(reqs, tail=10, per_step=12)
+    bs = util.BLOCK_SIZE[name]
+    out = traces.run_inprocess(util.model_folder(name, dtype, std), dtype, steps, bs,
+                               traces.max_live_tokens(steps, round_to=bs), max_live=len(lengths))
+    rows = traces.collect(steps, out)
+    bound, scale = util.logits_bound(dtype, std, ref)
+    worst = util.worst_difference(rows, ref)
+    util.note_worst(f"one long among short {dtype}", worst, bound)
+    assert worst <= bound, (worst, bound, scale)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_a_request_dropped_in_the_middle_of_its_prompt_and_replayed(dtype):
     """What preemption by recompute does, at the level of the step function: a live request gives back what it
     holds after 45 of its 130 tokens, its pages go to the others, and it runs again from its first token."""
