@@ -237,12 +237,12 @@ class ModelRunner:
 
     @staticmethod
     def graph_skew_class(bucket: int, mean_ctx: float) -> int:
-        """How far the mean context of a decode batch lies below its bucket: 0 when within a factor of 4, else the
-        number of further doublings, up to 4 (a 64th and less).  One long request among short ones is split into more
-        blocks than a batch of long requests would be; the class is part of a graph's key because the split is
-        part of its geometry."""
+        """How far the mean context of a decode batch lies below its bucket: 0 when above half of it (all batches of
+        equal contexts), else the number of halvings, up to 6 (a 64th and less).  A long request among short ones is
+        split into more blocks than a batch of long requests would be; the class is part of a graph's key because
+        the split is part of its geometry."""
         c = 0
-        while c < 4 and mean_ctx * (8 << c) <= bucket:
+        while c < 6 and mean_ctx * (2 << c) <= bucket:
             c += 1
         return c
 
@@ -303,9 +303,9 @@ class ModelRunner:
             # launch geometry must not depend on the step, only on its bucket: the decode attention plans its splits
             # for the middle of the bucket's context lengths (the bucket below ends at half its top)
             ctx.extras["decode_max_ctx"] = key[1] - key[1] // 4 if key[1] > 1024 else key[1]
-            # the middle of the graph's class of means: between bucket / (8 << c) and twice that (the last class: and
+            # the middle of the graph's class of means: between bucket / (2 << c) and twice that (the last class: and
             # below); class 0 plans as if all contexts were as long as the longest
-            ctx.extras["decode_mean_ctx"] = key[1] * 3 / (16 << key[2]) if key[2] else ctx.extras["decode_max_ctx"]
+            ctx.extras["decode_mean_ctx"] = key[1] * 3 / (4 << key[2]) if key[2] else ctx.extras["decode_max_ctx"]
             if self._graph_pool is None:
                 self._graph_pool = torch.cuda.graph_pool_handle()
                 self._capture_stream = torch.cuda.Stream(self.device)

@@ -127,7 +127,7 @@ class PagedAttention(Mixer):
                 group_size = self.num_heads // self.num_kv_heads
                 splits, warps = kernels.decode_plan(ctx.n_decode_seqs, self.num_kv_heads, group_size, visible,
                                                     self.head_dim, kernels.decode_widths(self.head_dim, group_size),
-                                                    mean_ctx=mean_visible if mean_visible * 2 <= visible else None)
+                                                    mean_ctx=mean_visible if mean_visible * 4 <= visible * 3 else None)
                 need = kernels.attention_decode_scratch_floats(ctx.n_seqs, self.num_heads, splits, self.head_dim)
                 scratch = ctx.extras.get("decode_scratch")
                 if need and (scratch is None or scratch.numel() < need):

@@ -45,7 +45,7 @@ def test_one_long_request_among_short_ones_is_split_as_if_nearly_alone():
     assert s >= 6
     from lmsf_b200.engine.model_runner import ModelRunner
     c = ModelRunner.graph_skew_class
-    assert [c(4096, m) for m in (4096, 600, 512, 256, 100, 64, 1)] == [0, 0, 1, 2, 3, 4, 4]
+    assert [c(4096, m) for m in (4096, 2049, 2048, 1024, 600, 512, 100, 64, 1)] == [0, 0, 1, 2, 2, 3, 5, 6, 6]
 
 
 def test_split_choice_does_not_depend_on_what_it_should_not():
