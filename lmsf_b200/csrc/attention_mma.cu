@@ -58,6 +58,9 @@ struct DecodeArgs {
   int n_splits;
   int cluster;                               // the splits of a request and group of heads form a thread-block cluster
   int rows;                                  // query heads a block holds at most: min(16, group); sizes the regions in which parts meet
+  // Splits per request instead of one number for all: blockIdx.x is an entry of this list, {request, split, splits of
+  // the request, splits of the requests before it}; a request of -1 is padding.  Null: every request has n_splits.
+  const int4* items;
 };
 
 // Online-softmax state of the two rows (lane / 4 and lane / 4 + 8) that a thread holds.
@@ -86,13 +89,22 @@ __global__ void __launch_bounds__(32 * W) decode_kernel(DecodeArgs a) {
   extern __shared__ __align__(16) unsigned char smem[];
   __shared__ int s_table[kTableCache];
   __shared__ int s_is_last;
-  const int split = blockIdx.x;
   pdl_launch_dependents();
+  int split = blockIdx.x, n_splits = a.n_splits, item_seq = 0, splits_before = 0;
+  if (a.items) {
+    // the list was written by a kernel of this step (the first attention layer's, before its own launch): it may be
+    // read only after the dependency wait, so a launch with a list has no prologue that overlaps the kernel before
+    pdl_wait();
+    const int4 item = a.items[blockIdx.x];
+    if (item.x < 0) return;
+    item_seq = item.x; split = item.y; n_splits = item.z; splits_before = item.w;
+  }
   // Until pdl_wait() only what no kernel of this step writes is read: the step's tables, and keys that were
   // cached before this step.  The kernel before this one writes the new token's key, value and query.
   const int chunks_per_kvh = (a.group + 15) / 16;
   const int kvh = blockIdx.y / chunks_per_kvh, hchunk = blockIdx.y % chunks_per_kvh;
-  const int seq = a.seq_ids ? a.seq_ids[blockIdx.z] : blockIdx.z;
+  const int seq = a.items ? item_seq : (a.seq_ids ? a.seq_ids[blockIdx.z] : blockIdx.z);
+  if (!a.items) splits_before = seq * n_splits;                // where the request's partial results start, in splits
   const int* table = a.block_table + (size_t)seq * a.max_blocks;
   // The head of the request's block table goes to shared memory at once, beside the loads of its lengths: for
   // contexts of up to kTableCache pages no copy of the loop waits for a table entry from global memory, and
@@ -109,7 +121,7 @@ __global__ void __launch_bounds__(32 * W) decode_kernel(DecodeArgs a) {
 
   // tiles of 64 keys aligned to absolute positions; this split's share of them
   const int tile_lo = lo / kDecTile, tile_hi = (ctx + kDecTile - 1) / kDecTile;
-  const int per_split = (tile_hi - tile_lo + a.n_splits - 1) / a.n_splits;
+  const int per_split = (tile_hi - tile_lo + n_splits - 1) / n_splits;
   const int tile_begin = tile_lo + split * per_split;
   const int tile_end = min(tile_hi, tile_begin + per_split);
   const int n_tiles = max(0, tile_end - tile_begin);
@@ -282,18 +294,18 @@ __global__ void __launch_bounds__(32 * W) decode_kernel(DecodeArgs a) {
       acc += sm_o[(w * R + row) * kOS + d] * f;
     }
     const int head = head0 + row;
-    if (a.n_splits == 1) {
+    if (n_splits == 1) {
       a.out[(size_t)token * a.out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(acc / L);
     } else if (a.cluster) {
       st_cluster_f32(sm_part + split * kPS + row * HD + d, 0, L > 0.f ? acc / L : 0.f);
       if (d == 0) st_cluster_f32(sm_part + split * kPS + R * HD + row, 0, L > 0.f ? M + log2f(L) : -INFINITY);
     } else {
-      const size_t pi = ((size_t)seq * a.n_q_heads + head) * a.n_splits + split;
+      const size_t pi = (size_t)splits_before * a.n_q_heads + (size_t)head * n_splits + split;
       a.part_o[pi * HD + d] = L > 0.f ? acc / L : 0.f;
       if (d == 0) a.part_lse[pi] = L > 0.f ? M + log2f(L) : -INFINITY;   // base-2 log-sum-exp
     }
   }
-  if (a.n_splits == 1) return;
+  if (n_splits == 1) return;
   if (a.cluster) {
     // all parts are in the shared memory of split 0, which adds them up in the order of the splits
     cluster_sync_all();
@@ -301,9 +313,9 @@ __global__ void __launch_bounds__(32 * W) decode_kernel(DecodeArgs a) {
     for (int idx = threadIdx.x; idx < n_heads * HD; idx += kDecThreads) {
       const int row = idx / HD, d = idx % HD;
       float M = -INFINITY;
-      for (int s = 0; s < a.n_splits; ++s) M = fmaxf(M, sm_part[s * kPS + R * HD + row]);
+      for (int s = 0; s < n_splits; ++s) M = fmaxf(M, sm_part[s * kPS + R * HD + row]);
       float acc = 0.f, L = 0.f;
-      for (int s = 0; s < a.n_splits; ++s) {
+      for (int s = 0; s < n_splits; ++s) {
         const float lse = sm_part[s * kPS + R * HD + row];
         const float f = lse == -INFINITY ? 0.f : exp2f(lse - M);
         L += f;
@@ -321,27 +333,27 @@ __global__ void __launch_bounds__(32 * W) decode_kernel(DecodeArgs a) {
   if (threadIdx.x == 0) {
     unsigned* cnt = a.counters + (size_t)seq * gridDim.y + blockIdx.y;
     const unsigned before = atomicAdd(cnt, 1u);
-    s_is_last = before == (unsigned)a.n_splits - 1;
+    s_is_last = before == (unsigned)n_splits - 1;
     if (s_is_last) *cnt = 0;                 // every split has counted: the counter is left as it was found
   }
   __syncthreads();
   if (!s_is_last) return;
   __threadfence();
-  const size_t base0 = ((size_t)seq * a.n_q_heads + head0) * a.n_splits;      // the block's heads are consecutive
-  const int n_w = n_heads * a.n_splits;
+  const size_t base0 = (size_t)splits_before * a.n_q_heads + (size_t)head0 * n_splits;   // the block's heads are consecutive
+  const int n_w = n_heads * n_splits;
   float* s_w = reinterpret_cast<float*>(smem);                                   // the stages are free
   if (n_w <= kMergeWeights) {
     // weights of all splits first (log-sum-exp values arrive together, not one after the other), then the sums
     for (int i = threadIdx.x; i < n_w; i += kDecThreads) s_w[i] = __ldcg(a.part_lse + base0 + i);
     __syncthreads();
     for (int row = warp; row < n_heads; row += kDecWarps) {
-      float* w = s_w + row * a.n_splits;
+      float* w = s_w + row * n_splits;
       float M = -INFINITY;
-      for (int s = lane; s < a.n_splits; s += 32) M = fmaxf(M, w[s]);
+      for (int s = lane; s < n_splits; s += 32) M = fmaxf(M, w[s]);
 #pragma unroll
       for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
       float L = 0.f;
-      for (int s = lane; s < a.n_splits; s += 32) {
+      for (int s = lane; s < n_splits; s += 32) {
         const float f = w[s] == -INFINITY ? 0.f : exp2f(w[s] - M);
         w[s] = f;
         L += f;
@@ -349,34 +361,34 @@ __global__ void __launch_bounds__(32 * W) decode_kernel(DecodeArgs a) {
 #pragma unroll
       for (int off = 16; off > 0; off >>= 1) L += __shfl_xor_sync(0xffffffffu, L, off);
       const float inv = 1.0f / L;
-      for (int s = lane; s < a.n_splits; s += 32) w[s] *= inv;
+      for (int s = lane; s < n_splits; s += 32) w[s] *= inv;
     }
     __syncthreads();
     for (int idx = threadIdx.x; idx < n_heads * HD; idx += kDecThreads) {
       const int row = idx / HD, d = idx % HD;
-      const float* po = a.part_o + (base0 + (size_t)row * a.n_splits) * HD + d;
-      const float* w = s_w + row * a.n_splits;
+      const float* po = a.part_o + (base0 + (size_t)row * n_splits) * HD + d;
+      const float* w = s_w + row * n_splits;
       float acc = 0.f;
       int s = 0;
-      for (; s + 8 <= a.n_splits; s += 8) {
+      for (; s + 8 <= n_splits; s += 8) {
         float v[8];
 #pragma unroll
         for (int u = 0; u < 8; ++u) v[u] = __ldcg(po + (size_t)(s + u) * HD);
 #pragma unroll
         for (int u = 0; u < 8; ++u) acc += v[u] * w[s + u];
       }
-      for (; s < a.n_splits; ++s) acc += __ldcg(po + (size_t)s * HD) * w[s];
+      for (; s < n_splits; ++s) acc += __ldcg(po + (size_t)s * HD) * w[s];
       a.out[(size_t)token * a.out_stride + (size_t)(head0 + row) * HD + d] = __float2bfloat16_rn(acc);
     }
     return;
   }
   for (int idx = threadIdx.x; idx < n_heads * HD; idx += kDecThreads) {
     const int row = idx / HD, d = idx % HD;
-    const size_t base = base0 + (size_t)row * a.n_splits;
+    const size_t base = base0 + (size_t)row * n_splits;
     float M = -INFINITY;
-    for (int s = 0; s < a.n_splits; ++s) M = fmaxf(M, __ldcg(a.part_lse + base + s));
+    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, __ldcg(a.part_lse + base + s));
     float acc = 0.f, L = 0.f;
-    for (int s = 0; s < a.n_splits; ++s) {
+    for (int s = 0; s < n_splits; ++s) {
       const float lse = __ldcg(a.part_lse + base + s);
       const float f = lse == -INFINITY ? 0.f : exp2f(lse - M);
       L += f;
@@ -384,6 +396,60 @@ __global__ void __launch_bounds__(32 * W) decode_kernel(DecodeArgs a) {
     }
     a.out[(size_t)token * a.out_stride + (size_t)(head0 + row) * HD + d] = __float2bfloat16_rn(acc / L);
   }
+}
+
+// ---- splits per request ------------------------------------------------------------------------------------
+// The list of work items of a decode launch whose requests differ much in length: request i gets
+// s_i = round(keys_i / T) splits (1..kMaxItemSplits), with T the share of keys that a block would get if all keys
+// were dealt evenly to the `slots` blocks that the device holds at a time (a multiple of 64 keys, at least 128).
+// One warp: the requests are few.  items[k] for k >= sum of s_i is padding.
+constexpr int kMaxItemSplits = 64;
+struct ItemArgs {
+  const int* ctx_len; const int* seq_ids; int n_served; int window;
+  int blocks_per_split, slots, capacity;
+  int4* items;
+};
+__global__ void __launch_bounds__(32) decode_items_kernel(ItemArgs a) {
+  const int lane = threadIdx.x;
+  auto keys_of = [&](int i) {
+    const int seq = a.seq_ids ? a.seq_ids[i] : i;
+    const int ctx = a.ctx_len[seq];
+    return max(1, a.window > 0 ? min(ctx, a.window) : ctx);
+  };
+  auto warp_sum = [&](long long v) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    return v;
+  };
+  long long total = 0;
+  for (int i = lane; i < a.n_served; i += 32) total += keys_of(i);
+  total = warp_sum(total);
+  // A block's share if the keys were dealt evenly to the blocks that run at a time; a request is cut into pieces of
+  // about that many keys (rounded to the nearest count, so a piece has at most 1.5 shares).  The pieces of all
+  // requests are then at most slots / blocks_per_split + n_served / 2: short requests' blocks are over quickly, so
+  // that the launch may hold more blocks than run at a time as long as none is long.
+  const long long share = (total * a.blocks_per_split + a.slots - 1) / a.slots;
+  const int Ti = (int)min(1ll << 30, max(128ll, (share + 63) / 64 * 64));
+  auto splits_of = [&](int keys) { return max(1, min(kMaxItemSplits, (keys + Ti / 2) / Ti)); };
+  int before = 0;                                        // splits of the requests before this pass
+  for (int base = 0; base < a.n_served; base += 32) {
+    const int i = base + lane;
+    const int s_i = i < a.n_served ? splits_of(keys_of(i)) : 0;
+    int incl = s_i;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, off);
+      if (lane >= off) incl += v;
+    }
+    const int mine = before + incl - s_i;
+    if (i < a.n_served) {
+      const int seq = a.seq_ids ? a.seq_ids[i] : i;
+      for (int j = 0; j < s_i; ++j)
+        if (mine + j < a.capacity) a.items[mine + j] = make_int4(seq, j, s_i, mine);
+    }
+    before += __shfl_sync(0xffffffffu, incl, 31);
+  }
+  for (int k = before + lane; k < a.capacity; k += 32) a.items[k] = make_int4(-1, 0, 0, 0);
 }
 
 }  // namespace fa
@@ -485,6 +551,8 @@ LMSF_API long long lmsf_attention_decode_scratch_bytes(int n_seqs_total, int n_q
 // One query token per served request.  seq_ids (may be null) lists the n_served requests among the
 // n_seqs_total rows of block_table / cu_q / ctx_len.  scratch: lmsf_attention_decode_scratch_bytes(), zero when
 // it is first used; a launch that completes leaves its counters zero again, so the same memory serves every call.
+static int decode_launch(lmsf::fa::DecodeArgs& a, int gy, int grid_x, int grid_z, int warps, cudaStream_t s);
+
 // block_warps: 4 or 2, the width of the blocks; 0: by the rule of lmsf_attention_decode_block_warps.
 LMSF_API int lmsf_attention_decode_width(const void* q, long long q_stride, void* out, long long out_stride,
                                          const void* cache, long long page_stride, int block_size, int n_kv_heads,
@@ -524,19 +592,27 @@ LMSF_API int lmsf_attention_decode_width(const void* q, long long q_stride, void
     LMSF_REFUSE("attention_decode: blocks have 2 or 4 warps, not %d", block_warps);
   int warps = forced_block_warps();
   if (!warps) warps = block_warps ? block_warps : lmsf_attention_decode_block_warps((int)(n_served * gy), group);
+  a.items = nullptr;
+  a.cluster = n_splits >= 2 && n_splits <= kMaxClusterSplits && cluster_enabled();
+  return decode_launch(a, (int)gy, n_splits, n_served, warps, (cudaStream_t)stream);
+}
+
+// The launch itself: grid (grid_x, gy, grid_z) of blocks of `warps` warps; a.cluster: the grid_x blocks of a row form a
+// thread-block cluster.
+static int decode_launch(lmsf::fa::DecodeArgs& a, int gy, int grid_x, int grid_z, int warps, cudaStream_t s) {
+  using namespace lmsf;
+  using namespace lmsf::fa;
   void (*kernel)(DecodeArgs) = warps == 2 ? decode_kernel<2> : decode_kernel<4>;
-  const int smem = decode_smem_bytes(group, warps);
+  const int smem = decode_smem_bytes(a.group, warps);
   static int configured[2] = {0, 0};         // the largest size each kernel has been allowed so far
   if (smem > configured[warps == 2]) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     configured[warps == 2] = smem;
   }
-  cudaStream_t s = (cudaStream_t)stream;
-  a.cluster = n_splits >= 2 && n_splits <= kMaxClusterSplits && cluster_enabled();
-  if (!a.cluster) return launch_pdl(kernel, dim3(n_splits, (unsigned)gy, n_served), dim3(32 * warps), smem, s, a);
+  if (!a.cluster) return launch_pdl(kernel, dim3(grid_x, (unsigned)gy, grid_z), dim3(32 * warps), smem, s, a);
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(n_splits, (unsigned)gy, n_served);
+  cfg.gridDim = dim3(grid_x, (unsigned)gy, grid_z);
   cfg.blockDim = dim3(32 * warps);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = s;
@@ -544,12 +620,73 @@ LMSF_API int lmsf_attention_decode_width(const void* q, long long q_stride, void
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled();
   attr[1].id = cudaLaunchAttributeClusterDimension;
-  attr[1].val.clusterDim.x = n_splits;
+  attr[1].val.clusterDim.x = grid_x;
   attr[1].val.clusterDim.y = 1;
   attr[1].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 2;
   return (int)cudaLaunchKernelEx(&cfg, kernel, a);
+}
+
+// ---- a launch with splits per request -----------------------------------------------------------------------
+// lmsf_attention_decode_build_items writes the list (capacity entries of 4 ints) from the requests' context lengths;
+// lmsf_attention_decode_items runs the attention over it.  slots: blocks of the chosen width that the device holds at
+// a time (lmsf_attention_decode_max_clusters(1, group, warps)); capacity >= n_served.  Scratch of
+// lmsf_attention_decode_items_scratch_bytes(capacity, n_q_heads), zero when first used.
+LMSF_API int lmsf_attention_decode_build_items(const int* ctx_len, const int* seq_ids, int n_served, int window,
+                                               int n_q_heads, int n_kv_heads, int slots, int capacity, void* items,
+                                               void* stream) {
+  using namespace lmsf::fa;
+  if (n_served <= 0) return 0;
+  if (n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads)
+    LMSF_REFUSE("attention_decode_build_items: %d query heads cannot be grouped over %d kv heads", n_q_heads, n_kv_heads);
+  if (capacity < n_served || slots <= 0 || !items || ((uintptr_t)items & 15))
+    LMSF_REFUSE("attention_decode_build_items: the list needs room for one entry per request (%d), 16-byte aligned", n_served);
+  const int group = n_q_heads / n_kv_heads;
+  ItemArgs a{ctx_len, seq_ids, n_served, window, n_kv_heads * ((group + 15) / 16), slots, capacity, (int4*)items};
+  decode_items_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(a);
+  return (int)cudaGetLastError();
+}
+
+LMSF_API long long lmsf_attention_decode_items_scratch_bytes(int capacity, int n_q_heads) {
+  return kDecodeCounterBytes + (long long)capacity * n_q_heads * (lmsf::fa::HD + 1) * (long long)sizeof(float);
+}
+
+LMSF_API int lmsf_attention_decode_items(const void* q, long long q_stride, void* out, long long out_stride,
+                                         const void* cache, long long page_stride, int block_size, int n_kv_heads,
+                                         const int* block_table, int max_blocks, const void* items, int capacity,
+                                         int n_seqs_total, const int* cu_q, const int* ctx_len, float scale, int window,
+                                         int n_q_heads, int head_dim, int block_warps, void* scratch, void* stream) {
+  using namespace lmsf;
+  using namespace lmsf::fa;
+  if (capacity <= 0) return 0;
+  if (head_dim != HD) LMSF_REFUSE("attention_decode: built for head_dim=%d, called with %d", HD, head_dim);
+  if (n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads)
+    LMSF_REFUSE("attention_decode: %d query heads cannot be grouped over %d kv heads", n_q_heads, n_kv_heads);
+  if (!items || !scratch) LMSF_REFUSE("attention_decode_items: the list of work items and scratch memory are needed");
+  if (block_size <= 0 || max_blocks <= 0) LMSF_REFUSE("attention_decode: bad block table geometry");
+  if (block_warps != 2 && block_warps != 4) LMSF_REFUSE("attention_decode_items: blocks have 2 or 4 warps, not %d", block_warps);
+  const int group = n_q_heads / n_kv_heads;
+  const long long gy = (long long)n_kv_heads * ((group + 15) / 16);
+  if (gy > 65535) LMSF_REFUSE("attention_decode: too many heads for one launch");
+  if ((long long)n_seqs_total * gy > kDecodeCounterSlots)
+    LMSF_REFUSE("attention_decode_items: %d requests x %lld head groups exceed the %lld split counters", n_seqs_total, gy,
+                kDecodeCounterSlots);
+  DecodeArgs a;
+  a.q = (const bf16*)q; a.q_stride = q_stride; a.out = (bf16*)out; a.out_stride = out_stride;
+  a.counters = (unsigned*)scratch;
+  a.part_o = reinterpret_cast<float*>((unsigned char*)scratch + kDecodeCounterBytes);
+  a.part_lse = a.part_o + (size_t)capacity * n_q_heads * HD;
+  if (!make_paged_kv(a.kv, cache, page_stride, block_size, n_kv_heads))
+    LMSF_REFUSE("attention: block_size=%d must be a power of two", block_size);
+  a.block_table = block_table; a.max_blocks = max_blocks; a.seq_ids = nullptr; a.cu_q = cu_q; a.ctx_len = ctx_len;
+  a.scale = scale; a.window = window; a.n_q_heads = n_q_heads; a.group = group; a.n_splits = 1;
+  a.rows = decode_rows(group);
+  a.items = (const int4*)items;
+  a.cluster = 0;
+  int warps = forced_block_warps();
+  if (!warps) warps = block_warps;
+  return decode_launch(a, (int)gy, capacity, 1, warps, (cudaStream_t)stream);
 }
 
 LMSF_API int lmsf_attention_decode(const void* q, long long q_stride, void* out, long long out_stride,

@@ -533,6 +533,53 @@ def attention_decode(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, bl
     _check(rc, "attention_mma.cu", "lmsf_attention_mma", d)
 
 
+def decode_items_capacity(n_served: int, n_kv_heads: int, group: int, slots: int) -> int:
+    """Entries of the list of work items of a launch with splits per request: one per request and as many more as
+    the device holds blocks for."""
+    return n_served + slots // (n_kv_heads * ((group + 15) // 16)) + 1
+
+
+def attention_decode_items_scratch_floats(capacity: int, n_q_heads: int, head_dim: int) -> int:
+    return DECODE_COUNTER_SLOTS + capacity * n_q_heads * (head_dim + 1)
+
+
+def decode_build_items(items: torch.Tensor, ctx_len: torch.Tensor, seq_ids: Optional[torch.Tensor], n_served: int,
+                       window: int, n_q_heads: int, n_kv_heads: int, head_dim: int, slots: int):
+    """Fills `items` (int32 [capacity, 4]) on the device: request s gets ceil(keys_s / T) splits, with T the smallest
+    number of keys for which all blocks fit the `slots` blocks that the device holds at a time; entries that are
+    left over are padding.  The attention of requests that differ much in length runs over this list
+    (attention_decode_items): each block then has about the same number of keys."""
+    if items.dtype != torch.int32 or items.dim() != 2 or items.shape[1] != 4 or not items.is_contiguous():
+        raise KernelError("decode_build_items: items must be a contiguous int32 tensor [capacity, 4]")
+    d = _mma_defines(head_dim)
+    f = _func("attention_mma.cu", "lmsf_attention_decode_build_items",
+              [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p], d)
+    rc = f(_i32(ctx_len, "ctx_len"), _i32(seq_ids, "seq_ids"), n_served, int(window or 0), n_q_heads, n_kv_heads,
+           int(slots), items.shape[0], _ptr(items), _stream())
+    _check(rc, "attention_mma.cu", "lmsf_attention_mma", d)
+
+
+def attention_decode_items(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
+                           block_size: int, items: torch.Tensor, cu_q: torch.Tensor, ctx_len: torch.Tensor,
+                           scale: float, window: int, n_q_heads: int, n_kv_heads: int, head_dim: int, warps: int,
+                           scratch: torch.Tensor):
+    """attention_decode with splits per request, over a list made by decode_build_items.  scratch: float32, at
+    least attention_decode_items_scratch_floats(capacity, ...) values, zero when first used."""
+    _check_paged(q, out, cache, n_q_heads, n_kv_heads, head_dim, block_size, "attention_decode_items")
+    need = attention_decode_items_scratch_floats(items.shape[0], n_q_heads, head_dim)
+    if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need:
+        raise KernelError(f"attention_decode_items: a list of {items.shape[0]} entries needs {need} float32 values of scratch")
+    d = _mma_defines(head_dim)
+    f = _func("attention_mma.cu", "lmsf_attention_decode_items",
+              [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_void_p, c_int,
+               c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_void_p, c_void_p], d)
+    rc = f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache), cache.stride(0), block_size, n_kv_heads,
+           _i32(block_table, "block_table"), block_table.shape[1], _ptr(items), items.shape[0], block_table.shape[0],
+           _i32(cu_q, "cu_q"), _i32(ctx_len, "ctx_len"), float(scale), int(window or 0), n_q_heads, head_dim, int(warps),
+           _ptr(scratch), _stream())
+    _check(rc, "attention_mma.cu", "lmsf_attention_mma", d)
+
+
 def attention_prefill(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                       block_size: int, tile_seq: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int, cu_q: torch.Tensor,
                       ctx_len: torch.Tensor, scale: float, window: int, n_q_heads: int, n_kv_heads: int, head_dim: int):

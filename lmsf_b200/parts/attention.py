@@ -10,6 +10,7 @@ its keys from pages, so a portion that starts in the middle of a prompt needs no
 from __future__ import annotations
 
 import math
+import os
 import warnings
 from typing import Dict, Optional
 
@@ -21,6 +22,7 @@ from . import linear
 from .linear import matmul_tn
 
 
+SPLITS_PER_REQUEST = os.environ.get("LMSF_DECODE_ITEMS", "1") != "0"   # decode batches of very different lengths: splits per request
 USE_TC_PREFILL = True     # head sizes 64 and 128: prompt portions run on the tcgen05 kernel (csrc/attention_tc.cu)
 FUSE_QKV_ROPE = True      # up to 16 single tokens: rotary encoding and cache write in the q/k/v product's epilogue
 
@@ -125,18 +127,48 @@ class PagedAttention(Mixer):
                     mean_ctx = ctx.extras["decode_mean_ctx"] = sum(lens) / len(lens)
                 mean_visible = min(mean_ctx, visible)
                 group_size = self.num_heads // self.num_kv_heads
-                splits, warps = kernels.decode_plan(ctx.n_decode_seqs, self.num_kv_heads, group_size, visible,
-                                                    self.head_dim, kernels.decode_widths(self.head_dim, group_size),
-                                                    mean_ctx=mean_visible if mean_visible * 4 <= visible * 3 else None)
-                need = kernels.attention_decode_scratch_floats(ctx.n_seqs, self.num_heads, splits, self.head_dim)
-                scratch = ctx.extras.get("decode_scratch")
-                if need and (scratch is None or scratch.numel() < need):
-                    scratch = ctx.extras["decode_scratch"] = torch.zeros(need, dtype=torch.float32, device=q.device)
                 all_decode = ctx.n_decode_seqs == ctx.n_seqs
-                kernels.attention_decode(out, q, kv, group.block_table, group.block_size,
-                                         None if all_decode else ctx.decode_seq_ids, ctx.n_decode_seqs, ctx.cu_q,
-                                         ctx.ctx_len, self.scale, self.window or 0, self.num_heads,
-                                         self.num_kv_heads, self.head_dim, splits, scratch if need else None, warps)
+                if SPLITS_PER_REQUEST and ctx.n_decode_seqs >= 2 and mean_visible * 4 <= visible:
+                    # Requests that differ much in length (a mean of a quarter of the longest and less): splits per
+                    # request, from a list of work items that a kernel makes from the step's context lengths (once a
+                    # step, for all layers of this geometry).  Measured, 8 layers of the 8B shape: one request at
+                    # 30,000 tokens beside 63 at 500: 1.64 ms a step against 2.11 ms with one number of splits for all;
+                    # one at 2,300 beside 63 at 1,200: 1.54 against 1.50 (the list's launch starts after the kernel
+                    # before it and adds up through global memory), hence the threshold.
+                    widths = kernels.decode_widths(self.head_dim, group_size)
+                    pairs = ctx.n_decode_seqs * self.num_kv_heads * ((group_size + 15) // 16)
+                    warps, slots = widths[0][0], widths[0][2][0]
+                    if len(widths) > 1 and pairs > slots:
+                        warps, slots = widths[1][0], widths[1][2][0]
+                    key = ("decode_items", self.num_kv_heads, group_size, slots, self.window or 0)
+                    items = ctx.extras.get(key)
+                    if items is None:
+                        capacity = kernels.decode_items_capacity(ctx.n_decode_seqs, self.num_kv_heads, group_size, slots)
+                        items = ctx.extras[key] = torch.empty((capacity, 4), dtype=torch.int32, device=q.device)
+                        kernels.decode_build_items(items, ctx.ctx_len, None if all_decode else ctx.decode_seq_ids,
+                                                   ctx.n_decode_seqs, self.window or 0, self.num_heads, self.num_kv_heads,
+                                                   self.head_dim, slots)
+                    need = kernels.attention_decode_items_scratch_floats(items.shape[0], self.num_heads, self.head_dim)
+                    scratch = ctx.extras.get("decode_items_scratch")
+                    if scratch is None or scratch.numel() < need:
+                        scratch = ctx.extras["decode_items_scratch"] = torch.zeros(need, dtype=torch.float32, device=q.device)
+                    kernels.attention_decode_items(out, q, kv, group.block_table, group.block_size, items, ctx.cu_q,
+                                                   ctx.ctx_len, self.scale, self.window or 0, self.num_heads,
+                                                   self.num_kv_heads, self.head_dim, warps, scratch)
+                    splits = None
+                else:
+                    splits, warps = kernels.decode_plan(ctx.n_decode_seqs, self.num_kv_heads, group_size, visible,
+                                                        self.head_dim, kernels.decode_widths(self.head_dim, group_size),
+                                                        mean_ctx=mean_visible if mean_visible * 4 <= visible * 3 else None)
+                if splits is not None:
+                    need = kernels.attention_decode_scratch_floats(ctx.n_seqs, self.num_heads, splits, self.head_dim)
+                    scratch = ctx.extras.get("decode_scratch")
+                    if need and (scratch is None or scratch.numel() < need):
+                        scratch = ctx.extras["decode_scratch"] = torch.zeros(need, dtype=torch.float32, device=q.device)
+                    kernels.attention_decode(out, q, kv, group.block_table, group.block_size,
+                                             None if all_decode else ctx.decode_seq_ids, ctx.n_decode_seqs, ctx.cu_q,
+                                             ctx.ctx_len, self.scale, self.window or 0, self.num_heads,
+                                             self.num_kv_heads, self.head_dim, splits, scratch if need else None, warps)
             if ctx.n_q_tiles and USE_TC_PREFILL and kernels.tc_attention_supported(q.dtype, self.head_dim):
                 kernels.attention_prefill_tc(out, q, kv, group.block_table, group.block_size, ctx.q_tile128_seq,
                                              ctx.q_tile128_q0, ctx.n_q_tiles128, ctx.cu_q, ctx.ctx_len, self.scale,

@@ -335,6 +335,55 @@ def test_attention_tcgen05_runs_of_short_units(max_blocks, monkeypatch):
         assert err.max().item() <= 2e-2 * ref.abs().max().item(), (err.max().item(), int(err.argmax()) // (nh * hd))
 
 
+@pytest.mark.parametrize("nh,nkv,hd,warps", [(8, 2, 128, 4), (8, 2, 128, 2), (6, 2, 64, 4), (5, 5, 48, 4), (20, 1, 96, 2)])
+def test_attention_decode_with_splits_per_request(nh, nkv, hd, warps):
+    """Decode attention over a list of work items: requests of 1 to 3,000 keys side by side, each split by its own
+    length; the list for few and for many slots (one split each; up to 64 splits for the longest), with a prompt
+    portion in the batch (the list names only the requests that decode).  Against float64, and the list itself."""
+    from lmsf_b200 import kernels
+    bs = 16
+    ctx_lens, q_lens = [3000, 40, 1, 700, 300, 65, 64, 130, 17, 2048], [1, 1, 1, 1, 37, 1, 1, 1, 1, 1]
+    q, cache, bt, token_seq, positions, ks, vs = _paged_setup("bfloat16", nh, nkv, hd, bs, ctx_lens, q_lens, 33, sharp=True,
+                                                              poison=True)
+    scale = 1.0 / math.sqrt(hd)
+    ref = _attention_reference(q.float(), ks, vs, token_seq, positions, nh, nkv, hd, scale, 0)
+    d = dev()
+    qd, cd, btd = q.to(d), cache.to(d), bt.to(d)
+    cu = torch.tensor([0] + list(np.cumsum(q_lens)), dtype=torch.int32, device=d)
+    cl = torch.tensor(ctx_lens, dtype=torch.int32, device=d)
+    dec = [i for i, n in enumerate(q_lens) if n == 1]
+    dec_ids = torch.tensor(dec, dtype=torch.int32, device=d)
+    rows = [int(cu[i]) for i in dec]
+    group = nh // nkv
+    per_split = nkv * ((group + 15) // 16)
+    tol_abs = 2e-2 * ref.abs().max().item()
+    for slots in (1, 9 * per_split, 40 * per_split, 592, 100000):
+        capacity = kernels.decode_items_capacity(len(dec), nkv, group, slots)
+        items = torch.full((capacity, 4), -7, dtype=torch.int32, device=d)
+        kernels.decode_build_items(items, cl, dec_ids, len(dec), 0, nh, nkv, hd, slots)
+        it = items.cpu().tolist()
+        real = [e for e in it if e[0] >= 0]
+        assert all(e == [-1, 0, 0, 0] for e in it[len(real):])
+        assert len(real) <= len(dec) + slots // per_split      # pieces of about an even share of the keys, at least one a request
+        k = 0
+        for i in dec:                                          # every request: its splits in order, one after the other
+            s_i = real[k][2]
+            assert 1 <= s_i <= 64 and (s_i == 1 or ctx_lens[i] / s_i > 64)
+            assert [e[:4] for e in real[k:k + s_i]] == [[i, j, s_i, k] for j in range(s_i)]
+            k += s_i
+        assert k == len(real)
+        if slots == 1:
+            assert len(real) == len(dec)
+        if slots == 100000:
+            assert real[0][2] == (3000 + 64) // 128            # the longest: pieces of 128 keys
+        scratch = torch.zeros(kernels.attention_decode_items_scratch_floats(capacity, nh, hd), dtype=torch.float32, device=d)
+        for _ in range(2):                                     # twice: the counters are left as they were found
+            out = torch.zeros(q.shape, dtype=torch.bfloat16, device=d)
+            kernels.attention_decode_items(out, qd, cd, btd, bs, items, cu, cl, scale, 0, nh, nkv, hd, warps, scratch)
+            err = (out.float().cpu().double()[rows] - ref[rows]).abs()
+            assert err.max().item() <= tol_abs, (slots, err.max().item(), int(err.argmax()) // (nh * hd))
+
+
 def test_sampling_filters_and_penalties():
     from lmsf_b200 import kernels
     g = torch.Generator().manual_seed(7)
