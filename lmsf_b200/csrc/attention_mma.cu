@@ -486,12 +486,24 @@ static int decode_smem_bytes(int group, int warps) {
 // Clusters of `cluster_size` blocks of the decode kernel (for query heads in groups of `group`) that the device holds
 // at a time (0 on error): the splits of
 // a request and kv head form a cluster, and a launch with more clusters than this runs in two waves.
+// The decode kernel of a width is allowed as much dynamic shared memory as the largest request so far: the attribute is
+// only ever raised (a query for a small group of heads must not lower what a launch for a large group was given).
+static cudaError_t decode_allow_smem(int warps, int smem) {
+  using namespace lmsf::fa;
+  static int allowed[2] = {0, 0};
+  if (smem <= allowed[warps == 2]) return cudaSuccess;
+  void (*kernel)(DecodeArgs) = warps == 2 ? decode_kernel<2> : decode_kernel<4>;
+  const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e == cudaSuccess) allowed[warps == 2] = smem;
+  return e;
+}
+
 LMSF_API int lmsf_attention_decode_max_clusters(int cluster_size, int group, int warps) {
   using namespace lmsf::fa;
   if (cluster_size < 1 || cluster_size > kMaxClusterSplits || (warps != 2 && warps != 4)) return 0;
   const int smem = decode_smem_bytes(group, warps);
   void (*kernel)(DecodeArgs) = warps == 2 ? decode_kernel<2> : decode_kernel<4>;
-  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return 0;
+  if (decode_allow_smem(warps, smem) != cudaSuccess) return 0;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)cluster_size, 1024, 1);
   cfg.blockDim = dim3(32 * warps);
@@ -604,12 +616,7 @@ static int decode_launch(lmsf::fa::DecodeArgs& a, int gy, int grid_x, int grid_z
   using namespace lmsf::fa;
   void (*kernel)(DecodeArgs) = warps == 2 ? decode_kernel<2> : decode_kernel<4>;
   const int smem = decode_smem_bytes(a.group, warps);
-  static int configured[2] = {0, 0};         // the largest size each kernel has been allowed so far
-  if (smem > configured[warps == 2]) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return (int)e;
-    configured[warps == 2] = smem;
-  }
+  if (const cudaError_t e = decode_allow_smem(warps, smem)) return (int)e;
   if (!a.cluster) return launch_pdl(kernel, dim3(grid_x, (unsigned)gy, grid_z), dim3(32 * warps), smem, s, a);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid_x, (unsigned)gy, grid_z);

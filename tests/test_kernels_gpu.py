@@ -384,6 +384,35 @@ def test_attention_decode_with_splits_per_request(nh, nkv, hd, warps):
             assert err.max().item() <= tol_abs, (slots, err.max().item(), int(err.argmax()) // (nh * hd))
 
 
+def test_decode_attention_of_a_large_group_after_a_query_for_a_small_one():
+    """A block's shared memory grows with the query heads it holds.  A launch for 17 heads per kv head, then the
+    question how many blocks of a small group fit (which sets the kernel up for less), then the large group again:
+    what the kernel is allowed is only ever raised."""
+    from lmsf_b200 import kernels
+    hd, nkv, bs, n_req, ctx_n = 64, 2, 16, 5, 300
+    d = dev()
+    pages = (ctx_n + bs - 1) // bs
+    cache = torch.randn(n_req * pages, 2, nkv, bs, hd, device=d).to(torch.bfloat16)
+    bt = torch.arange(n_req * pages, dtype=torch.int32, device=d).view(n_req, pages).contiguous()
+    cu = torch.arange(n_req + 1, dtype=torch.int32, device=d)
+    cl = torch.full((n_req,), ctx_n, dtype=torch.int32, device=d)
+    token_seq = torch.arange(n_req, dtype=torch.int32, device=d)
+    positions = (cl - 1).to(torch.int32)
+    def run(group):
+        nh = nkv * group
+        q = torch.randn(n_req, nh * hd, device=d).to(torch.bfloat16)
+        out, ref = torch.zeros_like(q), torch.zeros_like(q)
+        scratch = torch.zeros(kernels.attention_decode_scratch_floats(n_req, nh, 2, hd), dtype=torch.float32, device=d)
+        kernels.attention_decode(out, q, cache, bt, bs, None, n_req, cu, cl, 0.125, 0, nh, nkv, hd, 2, scratch, 4)
+        kernels.attention_generic(ref, q, cache, bt, bs, token_seq, positions, 0.125, 0, nh, nkv, hd)
+        assert (out.float() - ref.float()).abs().max().item() <= 2e-2 * ref.float().abs().max().item()
+    run(17)
+    kernels._DECODE_WIDTHS.pop((hd, 1), None)
+    kernels.decode_widths(hd, 1)
+    run(1)
+    run(17)
+
+
 def test_sampling_filters_and_penalties():
     from lmsf_b200 import kernels
     g = torch.Generator().manual_seed(7)
