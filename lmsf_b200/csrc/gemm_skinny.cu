@@ -65,14 +65,14 @@ __device__ __forceinline__ float act_apply(float g, int act) {
 // features i and i + rot/2 in one block).
 template <int N_ROWS>
 __device__ __forceinline__ void issue_rows(uint32_t stage, const bf16* __restrict__ base, long long ld, int n_valid,
-                                           int k0, int K, int lane, int hi_off = 0) {
+                                           int k0, int K, int lane, int hi_off = 0, bool paired = false) {
   constexpr int kLanesPerRow = kCPR < 32 ? kCPR : 32;
   constexpr int kRowsPerInstr = 32 / kLanesPerRow;
   constexpr int kChunkPasses = kCPR / kLanesPerRow;
 #pragma unroll
   for (int i = 0; i < N_ROWS / kRowsPerInstr; ++i) {
     const int r = lane / kLanesPerRow + kRowsPerInstr * i;
-    const bool ok = (hi_off ? (r & 7) : r) < n_valid;   // paired rows (hi_off): rows r and r + 8 are valid together
+    const bool ok = (paired ? (r & 7) : r) < n_valid;   // paired: rows r and r + 8 belong together, n_valid counts pairs
 #pragma unroll
     for (int j = 0; j < kChunkPasses; ++j) {
       const int c = lane % kLanesPerRow + j * kLanesPerRow;
@@ -126,7 +126,7 @@ __global__ void __launch_bounds__(kWarps * 32) skinny_kernel(Args a) {
     const uint32_t st = ring + (c % STAGES) * kStage;
     const int k0 = (c_begin + c * c_stride) * kChunkK;
     if (ROPE) issue_rows<16>(st, a.w + (size_t)f0 * a.ldw, a.ldw, 16, k0, a.K, lane, hi_off);
-    else if (PAIR) issue_rows<16>(st, a.w + (size_t)n0 * a.ldw, a.ldw, min(8, rows_total - n0), k0, a.K, lane, a.up_offset - 8);
+    else if (PAIR) issue_rows<16>(st, a.w + (size_t)n0 * a.ldw, a.ldw, min(8, rows_total - n0), k0, a.K, lane, a.up_offset - 8, true);
     else issue_rows<16>(st, a.w + (size_t)n0 * a.ldw, a.ldw, rows_total - n0, k0, a.K, lane);
     if (GROUPS == 2)
       issue_rows<16>(st + kStageBytes, a.w + (size_t)(a.up_offset + n0) * a.ldw, a.ldw, rows_total - n0, k0, a.K, lane);

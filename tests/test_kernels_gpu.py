@@ -463,7 +463,8 @@ def test_sampling_filters_and_penalties():
     assert torch.equal(ld[0].cpu(), logits[0]) and torch.allclose(ld[1].cpu(), want, rtol=1e-6, atol=1e-6)
 
 
-@pytest.mark.parametrize("M,N,K", [(1, 48, 64), (8, 4096, 4096), (5, 1000, 320), (16, 6144, 1024), (13, 28, 14336 // 7)])
+@pytest.mark.parametrize("M,N,K", [(1, 48, 64), (8, 4096, 4096), (5, 1000, 320), (16, 6144, 1024), (13, 28, 14336 // 7),
+                                   (3, 16, 1976), (8, 2, 64), (7, 18, 72), (12, 16, 128)])    # gated: 8, 1, 9 and 8 pairs of rows
 def test_gemm_skinny_against_its_plain_twin(M, N, K):
     from lmsf_b200 import kernels
     g = torch.Generator().manual_seed(11)
