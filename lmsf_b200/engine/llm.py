@@ -6,7 +6,7 @@ keywords named like the reference's flags (core/src/common/config.rs:11-87).
 """
 from __future__ import annotations
 
-from typing import List, Optional, Sequence, Union
+from typing import Hashable, List, Optional, Sequence, Tuple, Union
 
 from ..config.engine_config import EngineArgs
 from ..sampling.params import SamplingParams
@@ -60,3 +60,26 @@ class LLM:
                 if out.finished:
                     done[out.request_id] = out
         return [done[r] for r in ids]
+
+    def step_logits(self, entries: Sequence[Tuple[Hashable, Sequence[int], Sequence[int]]],
+                    end: Sequence[Hashable] = ()) -> "torch.Tensor":
+        """One call of the step function, as `bin/trace_run` makes it, for tests and for looking at a model: each
+        entry is (request id, its next tokens, the places among them whose logits are wanted); all entries run as
+        one batch from the cache that earlier calls left.  Returns float32 logits [wanted, vocab] on the host, in the
+        order of the entries and of their wanted places.  Requests named in `end` give back what they hold after the
+        step.  Nothing is sampled.  The requests live in the engine's own cache manager under ids of their own
+        (("step_logits", id)), so the pages they hold until they are ended are not available to generate()."""
+        from .model_runner import StepEntry
+        mgr = self.engine.cache
+        batch = []
+        for rid, tokens, want in entries:
+            key = ("step_logits", rid)
+            if not mgr.has(key):
+                mgr.add(key)
+            batch.append(StepEntry(key, list(tokens), list(want)))
+        logits = self.engine.runner.step(batch, mgr) if batch else None
+        out = logits.to("cpu", copy=True) if logits is not None else None
+        for rid in end:
+            if mgr.has(("step_logits", rid)):
+                mgr.free(("step_logits", rid))
+        return out

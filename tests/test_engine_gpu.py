@@ -28,6 +28,32 @@ def test_greedy_generation_matches_the_plain_implementation(name, lengths, steps
         assert o.prompt_token_ids == p
 
 
+def test_step_logits_through_the_entry_point():
+    """`LLM.step_logits`: the step function behind the public class, two requests in portions and single tokens,
+    against the plain implementation; the pages it held are free again when its requests are ended, and
+    generation goes on as before."""
+    from lmsf_b200 import SamplingParams
+    name = "A"
+    cfg, w = P.load_model(util.model_folder(name, "float32", 0.15))
+    a, b = util.random_ids(23, cfg["vocab_size"], 41), util.random_ids(9, cfg["vocab_size"], 42)
+    ref_a = P.forward(cfg, w, torch.tensor(a), torch.float32)
+    ref_b = P.forward(cfg, w, torch.tensor(b), torch.float32)
+    llm = _llm(name, "float32", num_gpu_blocks=32, max_num_seqs=4)
+    free0 = llm.engine.cache.num_free_pages(0)
+    got = llm.step_logits([("a", a[:15], [0, 14]), ("b", b[:7], [6])])
+    assert got.shape == (3, cfg["vocab_size"]) and got.dtype == torch.float32 and not got.is_cuda
+    want = torch.stack([ref_a[0], ref_a[14], ref_b[6]])
+    scale = want.abs().max().item()
+    assert (got - want).abs().max().item() <= util.F32_REL * scale
+    got = llm.step_logits([("a", a[15:22], []), ("b", b[7:8], [0])])
+    assert (got - ref_b[7:8]).abs().max().item() <= util.F32_REL * scale
+    got = llm.step_logits([("a", a[22:], [0]), ("b", b[8:], [0])], end=["a", "b"])
+    assert (got - torch.stack([ref_a[22], ref_b[8]])).abs().max().item() <= util.F32_REL * scale
+    assert llm.engine.cache.num_free_pages(0) == free0
+    out = llm.generate(prompt_token_ids=[a], sampling_params=SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))
+    assert out[0].outputs[0].token_ids == P.generate(cfg, w, a, 4)[0]
+
+
 def test_temperature_sampling_is_reproducible_and_independent_of_the_batch():
     from lmsf_b200 import SamplingParams
     name = "B"
