@@ -1,2 +1,1 @@
-from .block_allocator import BlockAllocator, OutOfPages
-from .manager import CacheManager, GroupSpec
+from .manager import CacheManager, GroupSpec, OutOfPages

@@ -26,7 +26,10 @@ from dataclasses import dataclass
 from typing import Dict, Hashable, List, Optional, Sequence
 
 from . import native
-from .block_allocator import OutOfPages
+
+
+class OutOfPages(RuntimeError):
+    """The reference's "Out of memory! No free blocks" (core/src/sched/block_manager.rs:36-43)."""
 
 
 @dataclass(frozen=True)

@@ -46,11 +46,6 @@ def lib():
             "lmsf_sched_watermark": (c_int, [c_void_p, c_int]),
             "lmsf_sched_schedule": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                             c_void_p, c_void_p]),
-            "lmsf_pool_create": (c_void_p, [c_int]),
-            "lmsf_pool_destroy": (None, [c_void_p]),
-            "lmsf_pool_allocate": (c_int, [c_void_p]),
-            "lmsf_pool_free": (c_int, [c_void_p, c_int]),
-            "lmsf_pool_num_free": (c_int, [c_void_p]),
         }
         for name, (res, args) in sig.items():
             f = getattr(l, name)

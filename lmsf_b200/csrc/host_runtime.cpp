@@ -388,21 +388,6 @@ LMSF_HOST_API int lmsf_cm_build_batch(void* h, int S, const int64_t* rids, const
   return 0;
 }
 
-// ------------------------------------------------------------------------------------------------ a lone pool
-LMSF_HOST_API void* lmsf_pool_create(int n) {
-  if (n <= 0) return nullptr;
-  Pool* p = new Pool();
-  p->n = n;
-  p->is_free.assign(n, 1);
-  p->free_list.resize(n);
-  for (int i = 0; i < n; ++i) p->free_list[i] = n - 1 - i;
-  return p;
-}
-LMSF_HOST_API void lmsf_pool_destroy(void* h) { delete static_cast<Pool*>(h); }
-LMSF_HOST_API int lmsf_pool_allocate(void* h) { return static_cast<Pool*>(h)->allocate(); }
-LMSF_HOST_API int lmsf_pool_free(void* h, int b) { return static_cast<Pool*>(h)->release(b); }
-LMSF_HOST_API int lmsf_pool_num_free(void* h) { return (int)static_cast<Pool*>(h)->free_list.size(); }
-
 // ------------------------------------------------------------------------------------------------ the scheduler
 // Role of the reference's Scheduler (core/src/sched/scheduler.rs:336-543, native there): it owns the waiting and
 // running queues and decides every step what runs.  The policy is documented in lmsf_b200/engine/scheduler.py, whose

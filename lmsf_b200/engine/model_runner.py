@@ -13,7 +13,7 @@ from typing import Hashable, List, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
-from ..cache.block_allocator import OutOfPages
+from ..cache.manager import OutOfPages
 from ..cache import native
 from ..cache.manager import CacheManager
 from ..cache.storage import CacheStorage, plan_groups, split_pages

@@ -3,22 +3,32 @@ import random
 
 import pytest
 
-from lmsf_b200.cache import BlockAllocator, CacheManager, GroupSpec, OutOfPages
+from lmsf_b200.cache import CacheManager, GroupSpec, OutOfPages
 
 
-def test_allocator_reuses_the_page_just_freed_and_refuses_double_free():
-    a = BlockAllocator(4)
-    got = [a.allocate() for _ in range(4)]
-    assert sorted(got) == [0, 1, 2, 3] and a.num_free == 0
+def test_the_page_just_given_back_is_used_next_and_nothing_is_given_back_twice():
+    """The pool of a group (core/src/sched/block_manager.rs:14-58): pages come from the back of the free list and
+    return to it, so the page that was freed last is the next one handed out."""
+    m = CacheManager([GroupSpec()], [4], block_size=4, num_state_slots=4)
+    for r in "ab":
+        m.add(r)
+        m.reserve(r, 8)
+    pa, pb = m.block_table("a", 0), m.block_table("b", 0)
+    assert sorted(pa + pb) == [0, 1, 2, 3] and m.num_free_pages(0) == 0
+    m.add("c")
     with pytest.raises(OutOfPages):
-        a.allocate()
-    a.free(got[1])
-    assert a.allocate() == got[1]
-    a.free(got[0])
-    with pytest.raises(ValueError):
-        a.free(got[0])
-    with pytest.raises(ValueError):
-        a.free(17)
+        m.reserve("c", 1)
+    m.free("a")
+    assert m.num_free_pages(0) == 2
+    m.reserve("c", 1)
+    assert m.block_table("c", 0)[0] in pa
+    m.free("b")
+    m.add("d")
+    m.reserve("d", 4)
+    assert m.block_table("d", 0)[0] in pb            # b's pages were given back after a's: they come first
+    with pytest.raises(KeyError):
+        m.free("a")                                  # not live any more: nothing of it can be given back again
+    m.check_invariants()
 
 
 def test_pages_follow_the_tokens():
