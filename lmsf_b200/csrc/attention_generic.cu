@@ -30,6 +30,7 @@ struct GenericAttnArgs {
   const int* token_seq; const int* positions;
   float scale; int window;                     // window <= 0: all keys
   int n_q_heads, n_kv_heads, head_dim;
+  float softcap;                               // > 0: scores become softcap * tanh(score / softcap) before the softmax
 };
 
 template <typename T>
@@ -72,6 +73,7 @@ __global__ void __launch_bounds__(kWarps * 32) attention_generic_kernel(GenericA
         float dot = 0.f;
         for (int d = 0; d < hd; ++d) dot = fmaf(qs[d], to_f32(kr[d]), dot);
         s = dot * a.scale;
+        if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
       }
     }
     const float m_new = fmaxf(m, warp_max(s));
@@ -121,11 +123,13 @@ __global__ void __launch_bounds__(kWarps * 32) attention_generic_kernel(GenericA
 
 }  // namespace lmsf
 
-LMSF_API int lmsf_attention_generic(const void* q, long long q_stride, void* out, long long out_stride,
-                                    const void* cache, long long page_stride, const int* block_table, int max_blocks,
-                                    int block_size, const int* token_seq, const int* positions, float scale,
-                                    int window, int n_tokens, int n_q_heads, int n_kv_heads, int head_dim, int dtype,
-                                    void* stream) {
+// softcap > 0: the scaled scores are capped smoothly, softcap * tanh(score / softcap), before the softmax (a constant
+// of some architectures' attention; only this kernel takes it).
+LMSF_API int lmsf_attention_generic_softcap(const void* q, long long q_stride, void* out, long long out_stride,
+                                            const void* cache, long long page_stride, const int* block_table, int max_blocks,
+                                            int block_size, const int* token_seq, const int* positions, float scale,
+                                            float softcap, int window, int n_tokens, int n_q_heads, int n_kv_heads,
+                                            int head_dim, int dtype, void* stream) {
   using namespace lmsf;
   if (n_tokens <= 0) return 0;
   if (head_dim <= 0 || head_dim > kMaxHeadDim || head_dim % 16)
@@ -136,10 +140,20 @@ LMSF_API int lmsf_attention_generic(const void* q, long long q_stride, void* out
   if (block_size <= 0 || max_blocks <= 0) LMSF_REFUSE("attention: bad block table geometry");
   if (dtype != LMSF_F32 && dtype != LMSF_BF16) LMSF_REFUSE("attention: unknown dtype code %d", dtype);
   GenericAttnArgs a{q, q_stride, out, out_stride, cache, page_stride, block_table, max_blocks, block_size,
-                    token_seq, positions, scale, window, n_q_heads, n_kv_heads, head_dim};
+                    token_seq, positions, scale, window, n_q_heads, n_kv_heads, head_dim, softcap > 0.f ? softcap : 0.f};
   dim3 grid(n_tokens, n_q_heads);
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == LMSF_F32) attention_generic_kernel<float><<<grid, kWarps * 32, 0, s>>>(a);
   else attention_generic_kernel<bf16><<<grid, kWarps * 32, 0, s>>>(a);
   return LMSF_LAUNCH_STATUS();
+}
+
+LMSF_API int lmsf_attention_generic(const void* q, long long q_stride, void* out, long long out_stride,
+                                    const void* cache, long long page_stride, const int* block_table, int max_blocks,
+                                    int block_size, const int* token_seq, const int* positions, float scale,
+                                    int window, int n_tokens, int n_q_heads, int n_kv_heads, int head_dim, int dtype,
+                                    void* stream) {
+  return lmsf_attention_generic_softcap(q, q_stride, out, out_stride, cache, page_stride, block_table, max_blocks, block_size,
+                                        token_seq, positions, scale, 0.f, window, n_tokens, n_q_heads, n_kv_heads, head_dim,
+                                        dtype, stream);
 }

@@ -101,11 +101,19 @@ def _check(rc: int, source: str, prefix: str, defines: Tuple[str, ...] = ()):
 
 # ----------------------------------------------------------------------------- embedding
 
-def embedding(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, error_flag: Optional[torch.Tensor] = None):
-    """out[t, :] = table[ids[t], :]; out and table share one dtype."""
+def embedding(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, error_flag: Optional[torch.Tensor] = None,
+              scale: float = 1.0):
+    """out[t, :] = table[ids[t], :] (times `scale`, if it is not 1); out and table share one dtype."""
     n, hidden = out.shape
     if table.dtype != out.dtype or table.shape[1] != hidden or not (out.is_contiguous() and table.is_contiguous()):
         raise KernelError("embedding: out and table must be contiguous, of one dtype and one width")
+    if scale != 1.0:
+        f = _func("embedding.cu", "lmsf_embedding_scaled",
+                  [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p])
+        rc = f(_ptr(out), _ptr(table), _i32(ids, "ids"), n, hidden, table.shape[0], float(scale), dtype_code(out.dtype),
+               _i32(error_flag, "error_flag"), _stream())
+        _check(rc, "embedding.cu", "lmsf_embedding")
+        return
     f = _func("embedding.cu", "lmsf_embedding",
               [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
     rc = f(_ptr(out), _ptr(table), _i32(ids, "ids"), n, hidden, table.shape[0], dtype_code(out.dtype),
@@ -182,22 +190,23 @@ def rope_cache_write(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[tor
 
 def attention_generic(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                       block_size: int, token_seq: torch.Tensor, positions: torch.Tensor, scale: float, window: int,
-                      n_q_heads: int, n_kv_heads: int, head_dim: int):
+                      n_q_heads: int, n_kv_heads: int, head_dim: int, softcap: float = 0.0):
     """out[t] = softmax(scale q[t] K^T) V over the keys lo..positions[t] of token t's request, read from pages.
-    q, out: [n, n_q_heads * head_dim] (last dimension contiguous); window <= 0 means all keys."""
+    q, out: [n, n_q_heads * head_dim] (last dimension contiguous); window <= 0 means all keys; softcap > 0 caps the
+    scaled scores smoothly, softcap * tanh(score / softcap)."""
     n = q.shape[0]
     if q.stride(1) != 1 or out.stride(1) != 1 or q.shape[1] != n_q_heads * head_dim or out.shape != q.shape:
         raise KernelError("attention: q and out must be [n, heads * head_dim] with a contiguous last dimension")
     if cache.dtype != q.dtype or out.dtype != q.dtype or not cache.is_contiguous() or \
             tuple(cache.shape[1:]) != (2, n_kv_heads, block_size, head_dim):
         raise KernelError(f"attention: cache of shape {tuple(cache.shape)} / {cache.dtype} does not match the heads")
-    f = _func("attention_generic.cu", "lmsf_attention_generic",
+    f = _func("attention_generic.cu", "lmsf_attention_generic_softcap",
               [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_int, c_void_p,
-               c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+               c_void_p, c_float, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
     rc = f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache), cache.stride(0),
            _i32(block_table, "block_table"), block_table.shape[1], block_size, _i32(token_seq, "token_seq"),
-           _i32(positions, "positions"), float(scale), int(window or 0), n, n_q_heads, n_kv_heads, head_dim,
-           dtype_code(q.dtype), _stream())
+           _i32(positions, "positions"), float(scale), float(softcap or 0.0), int(window or 0), n, n_q_heads, n_kv_heads,
+           head_dim, dtype_code(q.dtype), _stream())
     _check(rc, "attention_generic.cu", "lmsf_attention_generic")
 
 

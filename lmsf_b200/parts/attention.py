@@ -33,7 +33,7 @@ class PagedAttention(Mixer):
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position_encoding: Optional[PositionEncoding] = None, window: Optional[int] = None,
-                 scale: Optional[float] = None, bias: bool = False):
+                 scale: Optional[float] = None, bias: bool = False, softcap: Optional[float] = None):
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} query heads cannot be grouped over {num_kv_heads} kv heads")
         if head_dim % 16 or not (16 <= head_dim <= 256):
@@ -43,6 +43,9 @@ class PagedAttention(Mixer):
         self.position_encoding = position_encoding
         self.window = int(window) if window else None
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
+        # scores capped smoothly, softcap * tanh(score / softcap), before the softmax (not a Llama constant).  Only the
+        # generic kernel takes it: a part built with a cap runs on that kernel in bfloat16 too, which is right and slow
+        self.softcap = float(softcap) if softcap else 0.0
         self.q_size = num_heads * head_dim
         self.kv_size = num_kv_heads * head_dim
         self.has_bias = bool(bias)
@@ -73,6 +76,9 @@ class PagedAttention(Mixer):
             # right but slow: said once, so that nobody wonders where the time goes
             warnings.warn(f"head_dim {self.head_dim} is beyond the tensor-core attention kernels "
                           f"(up to {kernels.MMA_MAX_HEAD_DIM}); bfloat16 attention runs on the generic kernel",
+                          RuntimeWarning, stacklevel=2)
+        elif dtype == torch.bfloat16 and self.softcap:
+            warnings.warn("a cap on the attention scores is taken by the generic kernel only; bfloat16 attention runs on it",
                           RuntimeWarning, stacklevel=2)
 
     def forward(self, ctx: StepContext, h: torch.Tensor, cache: LayerCache) -> torch.Tensor:
@@ -114,7 +120,8 @@ class PagedAttention(Mixer):
         to a tiled prefill kernel (tcgen05 with accumulators in tensor memory for head sizes 64 and 128,
         mma.sync otherwise).  Everything else, float32 included, runs on the
         generic kernel, which is also their plain twin."""
-        if kernels.mma_attention_supported(q.dtype, self.head_dim) and not ctx.extras.get("force_generic_attention"):
+        if kernels.mma_attention_supported(q.dtype, self.head_dim) and not self.softcap and \
+                not ctx.extras.get("force_generic_attention"):
             if ctx.n_decode_seqs:
                 max_ctx = ctx.extras.get("decode_max_ctx")
                 if max_ctx is None:
@@ -180,4 +187,5 @@ class PagedAttention(Mixer):
                                           self.window or 0, self.num_heads, self.num_kv_heads, self.head_dim)
             return
         kernels.attention_generic(out, q, kv, group.block_table, group.block_size, ctx.token_seq, ctx.positions,
-                                  self.scale, self.window or 0, self.num_heads, self.num_kv_heads, self.head_dim)
+                                  self.scale, self.window or 0, self.num_heads, self.num_kv_heads, self.head_dim,
+                                  softcap=self.softcap)

@@ -13,8 +13,9 @@ from .base import Part, StepContext, WeightSpec, register_part
 class TokenEmbedding(Part):
     graph_safe = True
 
-    def __init__(self, vocab_size: int, hidden_size: int):
+    def __init__(self, vocab_size: int, hidden_size: int, scale: float = 1.0):
         self.vocab_size, self.hidden_size = int(vocab_size), int(hidden_size)
+        self.scale = float(scale)      # every embedding is multiplied by it (1 for Llama; sqrt(width) elsewhere)
         self.weight: Optional[torch.Tensor] = None
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
@@ -22,5 +23,5 @@ class TokenEmbedding(Part):
 
     def forward(self, ctx: StepContext) -> torch.Tensor:
         x = torch.empty((ctx.n_tokens, self.hidden_size), dtype=self.weight.dtype, device=self.weight.device)
-        kernels.embedding(x, self.weight, ctx.token_ids, ctx.error_flag)
+        kernels.embedding(x, self.weight, ctx.token_ids, ctx.error_flag, scale=self.scale)
         return x

@@ -135,7 +135,7 @@ def _paged_setup(dtype, n_q_heads, n_kv_heads, hd, bs, ctx_lens, q_lens, seed, s
     return q, cache.to(DT[dtype]), bt, token_seq, positions, ks, vs
 
 
-def _attention_reference(q, ks, vs, token_seq, positions, n_q_heads, n_kv_heads, hd, scale, window):
+def _attention_reference(q, ks, vs, token_seq, positions, n_q_heads, n_kv_heads, hd, scale, window, softcap=0.0):
     out = torch.empty(q.shape[0], n_q_heads, hd, dtype=torch.float64)
     r = n_q_heads // n_kv_heads
     qf = q.double().reshape(-1, n_q_heads, hd)
@@ -144,9 +144,43 @@ def _attention_reference(q, ks, vs, token_seq, positions, n_q_heads, n_kv_heads,
         lo = max(0, p - window + 1) if window else 0
         for h in range(n_q_heads):
             k, v = ks[s][lo:p + 1, h // r].double(), vs[s][lo:p + 1, h // r].double()
-            w = torch.softmax((k @ qf[t, h]) * scale, dim=0)
+            sc = (k @ qf[t, h]) * scale
+            if softcap:
+                sc = softcap * torch.tanh(sc / softcap)
+            w = torch.softmax(sc, dim=0)
             out[t, h] = w @ v
     return out.reshape(q.shape[0], -1)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_constants_that_llama_leaves_at_their_defaults(dtype):
+    """A cap on the attention scores (softcap * tanh(score / softcap); the generic kernel takes it) and a scale on the
+    embeddings: parameters of the parts that another architecture would set."""
+    from lmsf_b200 import kernels
+    nh, nkv, hd, bs, cap = 4, 2, 64, 16, 7.5
+    ctx_lens, q_lens = [90, 1, 40], [90, 1, 3]
+    q, cache, bt, token_seq, positions, ks, vs = _paged_setup(dtype, nh, nkv, hd, bs, ctx_lens, q_lens, 6, sharp=True)
+    out = torch.empty(q.shape, dtype=DT[dtype], device=dev())
+    scale = 1.0 / math.sqrt(hd)
+    kernels.attention_generic(out, q.to(dev()), cache.to(dev()), bt.to(dev()), bs, token_seq.to(dev()),
+                              positions.to(dev()), scale, 0, nh, nkv, hd, softcap=cap)
+    ref = _attention_reference(q.float(), ks, vs, token_seq, positions, nh, nkv, hd, scale, 0, softcap=cap)
+    plain = _attention_reference(q.float(), ks, vs, token_seq, positions, nh, nkv, hd, scale, 0)
+    tol_ = (1e-4 if dtype == "float32" else 2e-2) * ref.abs().max().item()
+    assert (out.float().cpu().double() - ref).abs().max().item() <= tol_
+    assert (plain - ref).abs().max().item() > 5 * tol_               # the cap matters on these scores
+    g = torch.Generator().manual_seed(3)
+    table = torch.randn(50, 72, generator=g).to(DT[dtype])
+    ids = torch.tensor([3, 49, 0, 17], dtype=torch.int32)
+    got = torch.empty(4, 72, dtype=DT[dtype], device=dev())
+    flag = torch.zeros(1, dtype=torch.int32, device=dev())
+    kernels.embedding(got, table.to(dev()), ids.to(dev()), flag, scale=8.5)
+    want = (table[ids.long()].float() * 8.5).to(DT[dtype])
+    assert torch.equal(got.cpu(), want) and flag.item() == 0
+    kernels.embedding(got, table.to(dev()), torch.tensor([3, 50, 0, -1], dtype=torch.int32, device=dev()), flag, scale=8.5)
+    assert flag.item() == 1 and got[1].abs().max().item() == 0 and got[3].abs().max().item() == 0
+    assert torch.equal(got[0].cpu(), want[0])
+    flag.zero_()
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -482,17 +482,33 @@ def _hand_context(q_lens, ctx_lens, block_size, n_pages, seed=0):
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 4e-2)])
-@pytest.mark.parametrize("nh,nkv,hd,window", [(4, 2, 16, None), (3, 1, 64, None), (2, 2, 48, 7)])
-def test_attention_mixer_alone_over_two_steps(dtype, tol, nh, nkv, hd, window):
+@pytest.mark.parametrize("nh,nkv,hd,window,softcap", [(4, 2, 16, None, None), (3, 1, 64, None, None), (2, 2, 48, 7, None),
+                                                      (4, 2, 64, None, 2.5)])
+@pytest.mark.filterwarnings("ignore:a cap on the attention scores")
+def test_attention_mixer_alone_over_two_steps(dtype, tol, nh, nkv, hd, window, softcap, monkeypatch):
     """The mixer part by itself: a whole prompt in step one, then a portion and a decoded token of two requests in
-    step two, against the plain attention block on whole sequences."""
+    step two, against the plain attention block on whole sequences.  One case caps the scores (a constant of the
+    part that Llama leaves unset): the plain block then caps them too."""
     from lmsf_b200.parts.attention import PagedAttention
+    if softcap:
+        def capped(q, k, v, scale, window=None):
+            T, n_heads, _ = q.shape
+            rep = n_heads // k.shape[1]
+            out = torch.empty_like(q)
+            dead = torch.arange(T)[None, :] > torch.arange(T)[:, None]
+            for h in range(n_heads):
+                sc = (q[:, h, :] @ k[:, h // rep, :].T) * scale
+                sc = (softcap * torch.tanh(sc / softcap)).masked_fill(dead, float("-inf"))
+                out[:, h, :] = torch.softmax(sc, dim=-1) @ v[:, h // rep, :]
+            return out
+        monkeypatch.setattr(P, "causal_attention", capped)
     from lmsf_b200.parts.base import LayerCache
     from lmsf_b200.parts.rope import RotaryEmbedding
     H, bs = 40, 8
     g = torch.Generator().manual_seed(5)
     rope = RotaryEmbedding(rot_dim=hd, theta=1000.0)
-    att = PagedAttention(hidden_size=H, num_heads=nh, num_kv_heads=nkv, head_dim=hd, position_encoding=rope, window=window)
+    att = PagedAttention(hidden_size=H, num_heads=nh, num_kv_heads=nkv, head_dim=hd, position_encoding=rope, window=window,
+                         softcap=softcap)
     wq, wk, wv = (torch.randn(nh * hd, H, generator=g) * 0.3, torch.randn(nkv * hd, H, generator=g) * 0.3,
                   torch.randn(nkv * hd, H, generator=g) * 0.3)
     wo = torch.randn(H, nh * hd, generator=g) * 0.3
@@ -538,6 +554,9 @@ def test_embedding_rotary_apply_and_block_arrangement():
     ids = torch.tensor([3, 36, 0, 7, 7], dtype=torch.int32, device=dev)
     ctx.token_ids.copy_(ids)
     assert torch.equal(emb.forward(ctx).cpu(), table[ids.cpu().long()])
+    scaled = TokenEmbedding(vocab_size=37, hidden_size=24, scale=24 ** 0.5)      # a constant that Llama leaves at 1
+    scaled.set_weights({"weight": table.to(dev)})
+    assert torch.equal(scaled.forward(ctx).cpu(), table[ids.cpu().long()] * torch.tensor(24 ** 0.5, dtype=torch.float32))
     # rotary applied on its own (the path of a mixer that cannot fuse it): partial width, interleaved pairs
     rope = RotaryEmbedding(rot_dim=8, theta=50.0, is_neox=False)
     rope.prepare(torch.float32, dev)
