@@ -18,10 +18,18 @@ from .base import Norm, WeightSpec, register_part
 class RMSNorm(Norm):
     graph_safe = True
 
-    def __init__(self, hidden_size: int, eps: float):
+    def __init__(self, hidden_size: int, eps: float, weight_offset: float = 0.0):
         self.hidden_size = int(hidden_size)
         self.eps = float(eps)
+        # architectures that scale by (1 + w) store w: the offset is folded into the weight when it is set, as the
+        # reference's loader does (vllm/src/rms_norm.rs:45-56); 0 for Llama
+        self.weight_offset = float(weight_offset)
         self.weight: Optional[torch.Tensor] = None
+
+    def set_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
+        super().set_weights(tensors)
+        if self.weight_offset and "weight" in tensors:
+            self.weight = (tensors["weight"].float() + self.weight_offset).to(tensors["weight"].dtype)
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         return {"weight": WeightSpec([(self.hidden_size,)], keep_fp32=True)}

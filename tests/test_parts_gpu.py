@@ -27,6 +27,10 @@ def test_rmsnorm_part_keeps_a_32bit_weight():
     assert torch.allclose(h.float().cpu(), P.rms_norm(x.float(), w, 1e-6), rtol=1e-2, atol=1e-2)
     h2, res2 = n.forward_residual(x.to(DEV), res)
     assert res2 is res and torch.equal(res.cpu(), x.float() * 2)
+    # the (1 + w) form of other architectures: the offset is folded into the weight when it is set
+    n1 = RMSNorm(hidden_size=100, eps=1e-6, weight_offset=1.0)
+    n1.set_weights({"weight": (w - 1).to(DEV)})
+    assert torch.allclose(n1.forward(x.to(DEV)).float().cpu(), P.rms_norm(x.float(), w, 1e-6), rtol=1e-2, atol=1e-2)
 
 
 def test_rotary_part_frequencies_match_the_plain_rule():
