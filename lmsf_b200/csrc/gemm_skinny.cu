@@ -7,6 +7,13 @@
 // epilogue (rotary position encoding), q goes to its buffer and k and v straight into their cache pages, so that
 // no kernel has to run between the projection and the attention.
 //
+// Two more forms take the RMSNorm between two products of a decode step into the products themselves.  The product
+// before the norm adds its result to the float32 residual stream, stores residual x norm weight (bfloat16) and leaves,
+// per block, the sum of the squares of its 16 residual values of every token ("residual form").  The product after
+// the norm reads that as its x and multiplies its sums by 1 / sqrt(mean of squares + eps) of the token before
+// anything else is done with them ("prenormed input"): the factor is common to a row of x, so it can wait until
+// after the product.  The partial sums of squares are added in a fixed order.
+//
 // Counterpart in the reference: cublasLtMatmul for every M (tops/csrc/tops/tensorrt_llm/common/
 // cublasMMWrapper.cpp:122-209) followed by silu_and_mul_kernel (vllm/kernels/activation_kernels.cu:26-41).
 //
@@ -50,6 +57,12 @@ struct Args {
   const float* inv_freq; int rot_dim, is_neox;
   int n_q_heads, n_kv_heads, head_dim;
   int* error_flag;
+  // prenormed input: x is residual x norm weight; token m's sums are multiplied by
+  // 1 / sqrt(sum_p in_sumsq[m * in_ld + p] / in_width + in_eps), p < in_parts
+  const float* in_sumsq; int in_parts; long long in_ld; float in_eps; int in_width;
+  // residual form: res[m, n] += bfloat16(sum); out[m, n] = bfloat16(res[m, n] * norm_w[n]);
+  // out_sumsq[m * out_ld + block] = sum of res[m, n]^2 over the block's n
+  float* res; long long ldres; const void* norm_w; int norm_w_f32; float* out_sumsq; long long out_ld;
 };
 
 __device__ __forceinline__ float act_apply(float g, int act) {
@@ -147,6 +160,42 @@ __global__ void __launch_bounds__(kWarps * 32) skinny_kernel(Args a) {
     cp_async_commit();
   }
 
+  // prenormed input: 128 / (8 NT) threads share a token's partial sums of squares.  The first 16 of a thread are asked
+  // for here (16-byte loads) and added after the loop, so that nothing waits for them; more parts than that (a width
+  // above 4,096 x NT) are read then.  The order of the sum depends on the number of parts only.
+  constexpr int kTPR = kWarps * 32 / (8 * NT);
+  float4 ss_v[4];
+  auto load_ss = [&](int q0) {
+    const int m = threadIdx.x / kTPR, j = threadIdx.x % kTPR;
+    const float* src = a.in_sumsq + (size_t)m * a.in_ld;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int q = q0 + u * kTPR + j;
+      ss_v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (m >= a.M) continue;
+      if (q * 4 + 3 < a.in_parts) ss_v[u] = *reinterpret_cast<const float4*>(src + q * 4);
+      else if (q * 4 < a.in_parts) {
+        ss_v[u].x = src[q * 4];
+        if (q * 4 + 1 < a.in_parts) ss_v[u].y = src[q * 4 + 1];
+        if (q * 4 + 2 < a.in_parts) ss_v[u].z = src[q * 4 + 2];
+      }
+    }
+  };
+  if (a.in_sumsq) load_ss(0);
+  // residual form: the residual values and norm weights of this thread's results, asked for before the loop
+  float e_res[NT], e_nw[NT];
+  if (!ROPE && !PAIR && GROUPS == 1 && a.res) {
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+      const int idx = threadIdx.x + t * kWarps * 32;
+      const int m = idx / 16, n = n0 + idx % 16;
+      const bool ok = m < a.M && n < a.N;
+      e_res[t] = ok ? a.res[(size_t)m * a.ldres + n] : 0.f;
+      e_nw[t] = !ok ? 0.f : (a.norm_w_f32 ? reinterpret_cast<const float*>(a.norm_w)[n]
+                                           : __bfloat162float(reinterpret_cast<const bf16*>(a.norm_w)[n]));
+    }
+  }
+
   // ROPE: where this thread's results go (one token per pass of the epilogue), asked for before the loop
   int e_pos[NT], e_page[NT];
   if (ROPE) {
@@ -222,7 +271,28 @@ __global__ void __launch_bounds__(kWarps * 32) skinny_kernel(Args a) {
       base[(g4 + 8) * (8 * NT) + t * 8 + t4 * 2] = acc[g][t][2];
       base[(g4 + 8) * (8 * NT) + t * 8 + t4 * 2 + 1] = acc[g][t][3];
     }
+  // prenormed input: token m's factor, kept in the region of the warp that summed it
+  constexpr int kFactorOff = 2048;                                 // behind the largest set of partial sums
+  if (a.in_sumsq) {
+    float row_ss = 0.f;
+    for (int q0 = 0;;) {
+#pragma unroll
+      for (int u = 0; u < 4; ++u) row_ss += (ss_v[u].x + ss_v[u].y) + (ss_v[u].z + ss_v[u].w);
+      q0 += 4 * kTPR;
+      if (q0 * 4 >= a.in_parts) break;
+      load_ss(q0);
+    }
+#pragma unroll
+    for (int o = kTPR / 2; o > 0; o >>= 1) row_ss += __shfl_xor_sync(0xffffffffu, row_ss, o);
+    if (threadIdx.x % kTPR == 0 && threadIdx.x / kTPR < a.M)
+      reinterpret_cast<float*>(smem + warp * (STAGES * kStage) + kFactorOff)[threadIdx.x / kTPR] =
+          1.0f / sqrtf(row_ss / (float)a.in_width + a.in_eps);
+  }
   __syncthreads();
+  auto factor = [&](int m) -> float {
+    if (!a.in_sumsq || m >= a.M) return 1.0f;
+    return reinterpret_cast<const float*>(smem + ((m * kTPR) >> 5) * (STAGES * kStage) + kFactorOff)[m];
+  };
   if constexpr (ROPE) {
     // one (token, feature) per thread and pass; the partner of a rotated pair is 8 lanes away (NeoX) or the neighbour
     const int q_size = a.n_q_heads * a.head_dim, kv_size = a.n_kv_heads * a.head_dim;
@@ -234,6 +304,7 @@ __global__ void __launch_bounds__(kWarps * 32) skinny_kernel(Args a) {
 #pragma unroll
       for (int w = 0; w < kWarps; ++w)
         sum += reinterpret_cast<const float*>(smem + w * (STAGES * kStage))[row * (8 * NT) + m];
+      sum *= factor(m);
       const float val = __bfloat162float(__float2bfloat16_rn(sum));      // what the plain product would have stored
       const float other = __shfl_xor_sync(0xffffffffu, val, pair8 ? 8 : 1);
       if (m >= a.M) continue;
@@ -269,6 +340,7 @@ __global__ void __launch_bounds__(kWarps * 32) skinny_kernel(Args a) {
 #pragma unroll
       for (int w = 0; w < kWarps; ++w)
         sum += reinterpret_cast<const float*>(smem + w * (STAGES * kStage))[row * (8 * NT) + m];
+      sum *= factor(m);
       const float up = __shfl_down_sync(0xffffffffu, sum, 8);
       if (row >= 8 || m >= a.M || n0 + row >= rows_total) continue;
       const float r = act_apply(sum, a.act) * up;
@@ -276,22 +348,38 @@ __global__ void __launch_bounds__(kWarps * 32) skinny_kernel(Args a) {
       else reinterpret_cast<bf16*>(a.out)[(size_t)m * a.ldo + n0 + row] = __float2bfloat16_rn(r);
     }
   } else {
-  for (int idx = threadIdx.x; idx < 16 * 8 * NT; idx += kWarps * 32) {
-    const int m = idx / 16, row = idx % 16;          // consecutive threads write consecutive n
-    if (m >= a.M || n0 + row >= rows_total) continue;
-    float v[GROUPS];
 #pragma unroll
-    for (int g = 0; g < GROUPS; ++g) {
-      float s = 0.f;
+    for (int t = 0; t < NT; ++t) {
+      const int idx = threadIdx.x + t * kWarps * 32;
+      const int m = idx / 16, row = idx % 16;          // consecutive threads write consecutive n
+      const bool ok = m < a.M && n0 + row < rows_total;
+      const float f = factor(m);
+      float v[GROUPS];
 #pragma unroll
-      for (int w = 0; w < kWarps; ++w)
-        s += reinterpret_cast<const float*>(smem + w * (STAGES * kStage))[g * (16 * 8 * NT) + row * (8 * NT) + m];
-      v[g] = s;
+      for (int g = 0; g < GROUPS; ++g) {
+        float s = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w)
+          s += reinterpret_cast<const float*>(smem + w * (STAGES * kStage))[g * (16 * 8 * NT) + row * (8 * NT) + m];
+        v[g] = s * f;
+      }
+      const float r = GROUPS == 2 ? act_apply(v[0], a.act) * v[GROUPS - 1] : v[0];
+      if (GROUPS == 1 && a.res) {
+        float nr = 0.f;
+        if (ok) {
+          nr = e_res[t] + __bfloat162float(__float2bfloat16_rn(r));   // the plain product's bfloat16 result, added in float32
+          a.res[(size_t)m * a.ldres + n0 + row] = nr;
+          reinterpret_cast<bf16*>(a.out)[(size_t)m * a.ldo + n0 + row] = __float2bfloat16_rn(nr * e_nw[t]);
+        }
+        float sq = nr * nr;
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        if (row == 0 && m < a.M) a.out_sumsq[(size_t)m * a.out_ld + blockIdx.x] = sq;
+      } else if (ok) {
+        if (a.out_f32) reinterpret_cast<float*>(a.out)[(size_t)m * a.ldo + n0 + row] = r;
+        else reinterpret_cast<bf16*>(a.out)[(size_t)m * a.ldo + n0 + row] = __float2bfloat16_rn(r);
+      }
     }
-    const float r = GROUPS == 2 ? act_apply(v[0], a.act) * v[GROUPS - 1] : v[0];
-    if (a.out_f32) reinterpret_cast<float*>(a.out)[(size_t)m * a.ldo + n0 + row] = r;
-    else reinterpret_cast<bf16*>(a.out)[(size_t)m * a.ldo + n0 + row] = __float2bfloat16_rn(r);
-  }
   }
 }
 
@@ -325,46 +413,86 @@ constexpr int kStagesFused = LMSF_SKINNY_STAGES_FUSED;
 }  // namespace skinny
 }  // namespace lmsf
 
-// x: [M, K] bfloat16 (M <= 16), w: [N, K] bfloat16, out: [M, N] bfloat16 or float32.  K % 8 == 0.
-// fuse_act < 0: plain product.  fuse_act = 0 (silu) or 1 (gelu_tanh): w is [2 * N_out, K] (gate rows first),
-// out is [M, N_out] = act(x gate^T) * (x up^T), N = 2 * N_out.
-LMSF_API int lmsf_gemm_skinny(void* out, const void* x, const void* w, int M, int N, int K, long long ldx, long long ldw,
-                              long long ldo, int fuse_act, int out_f32, void* stream) {
-  using namespace lmsf;
-  using namespace lmsf::skinny;
+namespace lmsf {
+namespace skinny {
+
+// What the product forms have in common: checks, then the kernel for the number of rows and the form.
+static int run_product(Args& a, int fuse_act, cudaStream_t s) {
+  const int M = a.M, N = a.N, K = a.K;
   if (M <= 0 || N <= 0) return 0;
   if (M > 16) LMSF_REFUSE("gemm_skinny: M=%d, this kernel takes at most 16 rows", M);
   if (K <= 0 || K % 8) LMSF_REFUSE("gemm_skinny: K=%d must be a positive multiple of 8", K);
   if (fuse_act > 1) LMSF_REFUSE("gemm_skinny: unknown activation code %d", fuse_act);
   if (fuse_act >= 0 && N % 2) LMSF_REFUSE("gemm_skinny: a gated product needs an even N, got %d", N);
-  if (ldx < K || ldw < K || ldx % 8 || ldw % 8 || ((uintptr_t)x % 16) || ((uintptr_t)w % 16))
+  if (a.ldx < K || a.ldw < K || a.ldx % 8 || a.ldw % 8 || ((uintptr_t)a.x % 16) || ((uintptr_t)a.w % 16))
     LMSF_REFUSE("gemm_skinny: the rows of x and w must be 16-byte aligned");
-  Args a{};
-  a.x = (const bf16*)x; a.ldx = ldx; a.w = (const bf16*)w; a.ldw = ldw; a.out = out; a.ldo = ldo; a.M = M; a.N = N; a.K = K;
-  a.up_offset = fuse_act >= 0 ? N / 2 : 0; a.act = fuse_act; a.out_f32 = out_f32;
-  cudaStream_t s = (cudaStream_t)stream;
+  if (a.in_sumsq && (a.in_parts <= 0 || a.in_ld < a.in_parts || a.in_ld % 4 || ((uintptr_t)a.in_sumsq % 16) ||
+                     a.in_width <= 0 || !(a.in_eps > 0.f)))
+    LMSF_REFUSE("gemm_skinny: the sums of squares of a prenormed input need rows of a multiple of 4 floats, 16-byte "
+                "aligned, a width and a positive eps");
+  a.up_offset = fuse_act >= 0 ? N / 2 : 0; a.act = fuse_act;
   if (fuse_act >= 0) {
-    if (ldo < N / 2) LMSF_REFUSE("gemm_skinny: ldo is smaller than the output row");
+    if (a.ldo < N / 2) LMSF_REFUSE("gemm_skinny: ldo is smaller than the output row");
     // Up to 8 rows: gate and up rows paired in one group, blocks of half the size (Llama-3-8B sizes: a decode step of
     // 8 requests 3.45 -> 3.40 ms, of one 3.23 -> 3.16: 896 blocks were 2.02 waves of 444, and the last 8 cost a whole
     // block's time).  9 to 16 rows: a group of gate rows beside a group of up rows (a step of 16 requests 4.09 ms
     // against 4.15 paired).
     return M <= 8 ? launch<1, 1, kStagesPlain, false, true>(a, N / 2, s) : launch<2, 2, kStagesFused>(a, N / 2, s);
   }
-  if (ldo < N) LMSF_REFUSE("gemm_skinny: ldo is smaller than the output row");
+  if (a.ldo < N) LMSF_REFUSE("gemm_skinny: ldo is smaller than the output row");
   return M <= 8 ? launch<1, 1, kStagesPlain>(a, N, s) : launch<2, 1, kStagesPlain16>(a, N, s);
+}
+
+}  // namespace skinny
+}  // namespace lmsf
+
+// x: [M, K] bfloat16 (M <= 16), w: [N, K] bfloat16, out: [M, N] bfloat16 or float32.  K % 8 == 0.
+// fuse_act < 0: plain product.  fuse_act = 0 (silu) or 1 (gelu_tanh): w is [2 * N_out, K] (gate rows first),
+// out is [M, N_out] = act(x gate^T) * (x up^T), N = 2 * N_out.
+// in_sumsq (may be null): x is a prenormed input, a residual stream times a norm weight; the sums of token m are
+// multiplied by 1 / sqrt(sum of in_sumsq[m * in_ld + 0 .. in_parts) / in_width + in_eps) first.
+LMSF_API int lmsf_gemm_skinny(void* out, const void* x, const void* w, int M, int N, int K, long long ldx, long long ldw,
+                              long long ldo, int fuse_act, int out_f32, const float* in_sumsq, int in_parts,
+                              long long in_ld, float in_eps, int in_width, void* stream) {
+  using namespace lmsf;
+  using namespace lmsf::skinny;
+  Args a{};
+  a.x = (const bf16*)x; a.ldx = ldx; a.w = (const bf16*)w; a.ldw = ldw; a.out = out; a.ldo = ldo; a.M = M; a.N = N; a.K = K;
+  a.out_f32 = out_f32;
+  a.in_sumsq = in_sumsq; a.in_parts = in_parts; a.in_ld = in_ld; a.in_eps = in_eps; a.in_width = in_width;
+  return run_product(a, fuse_act, (cudaStream_t)stream);
+}
+
+// How many partial sums of squares per token the residual form leaves for N output features.
+LMSF_API int lmsf_gemm_skinny_residual_parts(int N) { return (N + 15) / 16; }
+
+// The residual form: res[M, N] (float32) += bfloat16(x w^T); out[M, N] (bfloat16) = res * norm_w (norm_w: [N], float32
+// or bfloat16); out_sumsq[m * out_ld + b], b < lmsf_gemm_skinny_residual_parts(N): the sums of squares of token m's
+// new residual values, 16 features each.  What a product, a residual add and the first half of an RMSNorm would do.
+LMSF_API int lmsf_gemm_skinny_residual(void* out, long long ldo, const void* x, long long ldx, const void* w, long long ldw,
+                                       int M, int N, int K, float* res, long long ldres, const void* norm_w,
+                                       int norm_w_f32, float* out_sumsq, long long out_ld, void* stream) {
+  using namespace lmsf;
+  using namespace lmsf::skinny;
+  if (!res || !norm_w || !out_sumsq || !out) LMSF_REFUSE("gemm_skinny_residual: a buffer is missing");
+  if (ldres < N || out_ld < (N + 15) / 16) LMSF_REFUSE("gemm_skinny_residual: a row of the residual or of the sums is too short");
+  Args a{};
+  a.x = (const bf16*)x; a.ldx = ldx; a.w = (const bf16*)w; a.ldw = ldw; a.out = out; a.ldo = ldo; a.M = M; a.N = N; a.K = K;
+  a.res = res; a.ldres = ldres; a.norm_w = norm_w; a.norm_w_f32 = norm_w_f32; a.out_sumsq = out_sumsq; a.out_ld = out_ld;
+  return run_product(a, -1, (cudaStream_t)stream);
 }
 
 // The merged q, k, v projection of M <= 16 single tokens with the rotary encoding and the cache write in its
 // epilogue.  w: [(n_q_heads + 2 n_kv_heads) * head_dim, K]; q_out: [M, n_q_heads * head_dim] bfloat16, rotated;
 // k (rotated) and v go to the pages of `cache` ([page][2][kv_head][slot][head_dim]) that block_table names for
 // positions[m] of request token_seq[m].  inv_freq: [rot_dim / 2] float32 or null (no rotation).  Results are those
-// of lmsf_gemm_skinny (bfloat16 out) followed by the rotary / cache-write kernel, bit for bit.
+// of lmsf_gemm_skinny (bfloat16 out) followed by the rotary / cache-write kernel, bit for bit.  in_sumsq: as there.
 LMSF_API int lmsf_gemm_skinny_qkv_rope(void* q_out, long long ldq, const void* x, long long ldx, const void* w, long long ldw,
                                        int M, int K, const int* positions, const int* token_seq, const int* block_table,
                                        int max_blocks, int block_size, void* cache, long long page_stride,
                                        const float* inv_freq, int rot_dim, int is_neox, int n_q_heads, int n_kv_heads,
-                                       int head_dim, int* error_flag, void* stream) {
+                                       int head_dim, int* error_flag, const float* in_sumsq, int in_parts,
+                                       long long in_ld, float in_eps, int in_width, void* stream) {
   using namespace lmsf;
   using namespace lmsf::skinny;
   if (M <= 0) return 0;
@@ -385,6 +513,10 @@ LMSF_API int lmsf_gemm_skinny_qkv_rope(void* q_out, long long ldq, const void* x
   a.block_size = block_size; a.cache = (bf16*)cache; a.page_stride = page_stride; a.inv_freq = inv_freq;
   a.rot_dim = inv_freq ? rot_dim : 0; a.is_neox = is_neox; a.n_q_heads = n_q_heads; a.n_kv_heads = n_kv_heads;
   a.head_dim = head_dim; a.error_flag = error_flag;
+  if (in_sumsq && (in_parts <= 0 || in_ld < in_parts || in_ld % 4 || ((uintptr_t)in_sumsq % 16) || in_width <= 0 || !(in_eps > 0.f)))
+    LMSF_REFUSE("gemm_skinny_qkv_rope: the sums of squares of a prenormed input need rows of a multiple of 4 floats, "
+                "16-byte aligned, a width and a positive eps");
+  a.in_sumsq = in_sumsq; a.in_parts = in_parts; a.in_ld = in_ld; a.in_eps = in_eps; a.in_width = in_width;
   cudaStream_t s = (cudaStream_t)stream;
   return M <= 8 ? launch<1, 1, kStagesPlain, true>(a, a.N, s) : launch<2, 1, kStagesPlain16, true>(a, a.N, s);
 }

@@ -127,6 +127,21 @@ __global__ void add_rmsnorm_vec_kernel(T* __restrict__ h_out, const T* __restric
   }
 }
 
+// The second half of an RMSNorm whose first half another kernel did (the residual form of the weight-streaming
+// product): h = (res / rms) * w, the row's sum of squares given as `parts` partial sums.  One block per row.
+template <typename T, typename WT>
+__global__ void finish_rmsnorm_kernel(T* __restrict__ h_out, const float* __restrict__ res, const float* __restrict__ sumsq,
+                                      int parts, long long ld, const WT* __restrict__ w, int hidden, float eps) {
+  __shared__ float scratch[33];
+  float ss = 0.f;
+  for (int p = threadIdx.x; p < parts; p += blockDim.x) ss += sumsq[(size_t)blockIdx.x * ld + p];
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+  const size_t base = (size_t)blockIdx.x * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+    h_out[base + i] = from_f32<T>((res[base + i] * inv) * to_f32(w[i]));
+}
+
 template <typename T, typename WT>
 static int launch(void* h, const void* x, float* res, const void* w, int n, int hidden, float eps, int mode,
                   cudaStream_t s) {
@@ -166,4 +181,21 @@ LMSF_API int lmsf_add_rmsnorm(void* h, const void* x, float* res, const void* w,
   if (dtype == LMSF_BF16 && w_dtype == LMSF_BF16) return launch<bf16, bf16>(h, x, res, w, n, hidden, eps, mode, s);
   if (dtype == LMSF_BF16 && w_dtype == LMSF_F32) return launch<bf16, float>(h, x, res, w, n, hidden, eps, mode, s);
   LMSF_REFUSE("rmsnorm: unsupported dtype pair (x %d, w %d)", dtype, w_dtype);
+}
+
+// h: [n, hidden] of `dtype` = (res / rms) * w, where sumsq[m * ld + 0 .. parts) add up to the sum of squares of row m
+// of res (float32 [n, hidden]).
+LMSF_API int lmsf_finish_rmsnorm(void* h, const float* res, const float* sumsq, int parts, long long ld, const void* w,
+                                 int n, int hidden, float eps, int dtype, int w_dtype, void* stream) {
+  using namespace lmsf;
+  if (n <= 0) return 0;
+  if (hidden <= 0 || parts <= 0 || ld < parts) LMSF_REFUSE("finish_rmsnorm: hidden=%d parts=%d", hidden, parts);
+  if (!(eps > 0.f)) LMSF_REFUSE("finish_rmsnorm: eps must be positive");
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == LMSF_BF16 && w_dtype == LMSF_BF16)
+    finish_rmsnorm_kernel<bf16, bf16><<<n, 256, 0, s>>>((bf16*)h, res, sumsq, parts, ld, (const bf16*)w, hidden, eps);
+  else if (dtype == LMSF_BF16 && w_dtype == LMSF_F32)
+    finish_rmsnorm_kernel<bf16, float><<<n, 256, 0, s>>>((bf16*)h, res, sumsq, parts, ld, (const float*)w, hidden, eps);
+  else LMSF_REFUSE("finish_rmsnorm: unsupported dtype pair (h %d, w %d)", dtype, w_dtype);
+  return LMSF_LAUNCH_STATUS();
 }

@@ -147,6 +147,23 @@ def add_rmsnorm(h: torch.Tensor, x: torch.Tensor, res: Optional[torch.Tensor], w
     _check(rc, "rmsnorm.cu", "lmsf_rmsnorm")
 
 
+def finish_rmsnorm(h: torch.Tensor, res: torch.Tensor, sumsq: torch.Tensor, w: torch.Tensor, eps: float):
+    """h = (res / rms) w, where sumsq[m] adds up to the sum of squares of row m of res: the second half of a norm whose
+    first half `gemm_skinny_residual` did, for a product that cannot take a prenormed input."""
+    n, hidden = res.shape
+    if h.shape != res.shape or h.dtype != torch.bfloat16 or not (h.is_contiguous() and res.is_contiguous()) or res.dtype != torch.float32:
+        raise KernelError("finish_rmsnorm: h must be bfloat16 and res float32, contiguous and of one shape")
+    if sumsq.dtype != torch.float32 or sumsq.dim() != 2 or sumsq.shape[0] < n or sumsq.stride(1) != 1:
+        raise KernelError("finish_rmsnorm: the sums of squares must be float32 [rows, parts]")
+    if w.shape != (hidden,) or not w.is_contiguous():
+        raise KernelError(f"finish_rmsnorm: weight of shape {tuple(w.shape)} for width {hidden}")
+    f = _func("rmsnorm.cu", "lmsf_finish_rmsnorm",
+              [c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_int, c_int, c_float, c_int, c_int, c_void_p])
+    rc = f(_ptr(h), _ptr(res), _ptr(sumsq), sumsq.shape[1], sumsq.stride(0), _ptr(w), n, hidden, float(eps),
+           dtype_code(h.dtype), dtype_code(w.dtype), _stream())
+    _check(rc, "rmsnorm.cu", "lmsf_rmsnorm")
+
+
 # ----------------------------------------------------------------------------- rope + cache write
 
 def rope_cache_write(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Tensor], positions: torch.Tensor,
@@ -268,9 +285,21 @@ def gemm_skinny_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
             and x.stride(0) % 8 == 0 and w.data_ptr() % 16 == 0 and x.data_ptr() % 16 == 0)
 
 
-def gemm_skinny(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, fuse_act: Optional[str] = None):
+def _prenorm_args(prenorm, M: int, what: str):
+    """(sums of squares [>= M, parts] float32, eps, width) of a prenormed input -> the kernel's five arguments."""
+    if prenorm is None:
+        return None, 0, 0, 0.0, 0
+    sumsq, eps, width = prenorm
+    if sumsq.dtype != torch.float32 or sumsq.dim() != 2 or sumsq.shape[0] < M or sumsq.stride(1) != 1:
+        raise KernelError(f"{what}: the sums of squares must be float32 [rows, parts]")
+    return _ptr(sumsq), sumsq.shape[1], sumsq.stride(0), float(eps), int(width)
+
+
+def gemm_skinny(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, fuse_act: Optional[str] = None, prenorm=None):
     """out[M, N] = x[M, K] w[N, K]^T for M <= 16 (bfloat16 in, bfloat16 or float32 out).  With fuse_act
-    ("silu", "gelu_tanh") w is [2 N_out, K] (gate rows, then up rows) and out[M, N_out] = act(x gate^T) * (x up^T)."""
+    ("silu", "gelu_tanh") w is [2 N_out, K] (gate rows, then up rows) and out[M, N_out] = act(x gate^T) * (x up^T).
+    prenorm = (sumsq, eps, width): x is a residual stream times a norm weight and the sums of row m are multiplied by
+    1 / sqrt(sum(sumsq[m]) / width + eps) first (what `gemm_skinny_residual` leaves)."""
     M, K = x.shape
     N = w.shape[0]
     n_out = N // 2 if fuse_act else N
@@ -281,10 +310,40 @@ def gemm_skinny(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, fuse_act: O
     if fuse_act is not None and fuse_act not in ACT_CODES:
         raise KernelError(f"gemm_skinny: unknown activation {fuse_act!r}")
     f = _func("gemm_skinny.cu", "lmsf_gemm_skinny",
-              [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, c_int, c_void_p],
-              SKINNY_DEFINES)
+              [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, c_int,
+               c_void_p, c_int, c_longlong, c_float, c_int, c_void_p], SKINNY_DEFINES)
     rc = f(_ptr(out), _ptr(x), _ptr(w), M, N, K, x.stride(0), w.stride(0), out.stride(0),
-           ACT_CODES[fuse_act] if fuse_act else -1, int(out.dtype == torch.float32), _stream())
+           ACT_CODES[fuse_act] if fuse_act else -1, int(out.dtype == torch.float32),
+           *_prenorm_args(prenorm, M, "gemm_skinny"), _stream())
+    _check(rc, "gemm_skinny.cu", "lmsf_gemm_skinny", SKINNY_DEFINES)
+
+
+def gemm_skinny_residual_parts(n: int) -> int:
+    """Partial sums of squares per row that `gemm_skinny_residual` leaves for n output features."""
+    return (n + 15) // 16
+
+
+def gemm_skinny_residual(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, res: torch.Tensor, norm_w: torch.Tensor,
+                         sumsq: torch.Tensor):
+    """A product, the residual add after it and the first half of the RMSNorm after that, for M <= 16 rows:
+    res[M, N] (float32) += bfloat16(x w^T); out[M, N] (bfloat16) = res * norm_w; sumsq[m, b] = the sum of squares of
+    row m's new residual values 16 b .. 16 b + 15.  `gemm_skinny(..., prenorm=(sumsq, eps, N))` is the other half."""
+    M, K = x.shape
+    N = w.shape[0]
+    if not gemm_skinny_supported(x, w) or w.shape[1] != K or out.shape != (M, N) or out.stride(1) != 1 or out.dtype != torch.bfloat16:
+        raise KernelError(f"gemm_skinny_residual: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)} are not taken")
+    if res.dtype != torch.float32 or res.shape != (M, N) or res.stride(1) != 1:
+        raise KernelError("gemm_skinny_residual: the residual must be float32 of the output's shape")
+    if norm_w.shape != (N,) or not norm_w.is_contiguous() or norm_w.dtype not in (torch.float32, torch.bfloat16):
+        raise KernelError("gemm_skinny_residual: the norm weight must be [N], float32 or bfloat16")
+    if (sumsq.dtype != torch.float32 or sumsq.dim() != 2 or sumsq.shape[0] < M or sumsq.stride(1) != 1
+            or sumsq.shape[1] != gemm_skinny_residual_parts(N)):
+        raise KernelError("gemm_skinny_residual: the sums of squares must be float32 [rows, gemm_skinny_residual_parts(N)]")
+    f = _func("gemm_skinny.cu", "lmsf_gemm_skinny_residual",
+              [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p, c_longlong,
+               c_void_p, c_int, c_void_p, c_longlong, c_void_p], SKINNY_DEFINES)
+    rc = f(_ptr(out), out.stride(0), _ptr(x), x.stride(0), _ptr(w), w.stride(0), M, N, K, _ptr(res), res.stride(0),
+           _ptr(norm_w), int(norm_w.dtype == torch.float32), _ptr(sumsq), sumsq.stride(0), _stream())
     _check(rc, "gemm_skinny.cu", "lmsf_gemm_skinny", SKINNY_DEFINES)
 
 
@@ -296,10 +355,11 @@ def gemm_skinny_qkv_rope_supported(x: torch.Tensor, w: torch.Tensor, head_dim: i
 def gemm_skinny_qkv_rope(q_out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, positions: torch.Tensor, token_seq: torch.Tensor,
                          block_table: torch.Tensor, block_size: int, cache: torch.Tensor, inv_freq: Optional[torch.Tensor],
                          rot_dim: int, is_neox: bool, n_q_heads: int, n_kv_heads: int, head_dim: int,
-                         error_flag: Optional[torch.Tensor] = None):
+                         error_flag: Optional[torch.Tensor] = None, prenorm=None):
     """The merged q, k, v projection of up to 16 single tokens (x [M, K] bfloat16, w [(heads + 2 kv heads) * head_dim, K])
     with the rotary encoding and the cache write in its epilogue: q_out [M, heads * head_dim] gets the rotated q, the
-    pages of `cache` the rotated k and v.  The same values as gemm_skinny followed by rope_cache_write."""
+    pages of `cache` the rotated k and v.  The same values as gemm_skinny followed by rope_cache_write.  prenorm: as in
+    `gemm_skinny`."""
     M, K = x.shape
     if (not gemm_skinny_qkv_rope_supported(x, w, head_dim, rot_dim if inv_freq is not None else 0, is_neox)
             or w.shape != ((n_q_heads + 2 * n_kv_heads) * head_dim, K) or q_out.shape != (M, n_q_heads * head_dim)
@@ -311,11 +371,12 @@ def gemm_skinny_qkv_rope(q_out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, 
         raise KernelError("gemm_skinny_qkv_rope: inv_freq must be float32 [rot_dim / 2]")
     f = _func("gemm_skinny.cu", "lmsf_gemm_skinny_qkv_rope",
               [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p,
-               c_int, c_int, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p], SKINNY_DEFINES)
+               c_int, c_int, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
+               c_void_p, c_int, c_longlong, c_float, c_int, c_void_p], SKINNY_DEFINES)
     rc = f(_ptr(q_out), q_out.stride(0), _ptr(x), x.stride(0), _ptr(w), w.stride(0), M, K, _i32(positions, "positions"),
            _i32(token_seq, "token_seq"), _i32(block_table, "block_table"), block_table.shape[1], block_size, _ptr(cache),
            cache.stride(0), _ptr(inv_freq) if inv_freq is not None else None, int(rot_dim), int(bool(is_neox)), n_q_heads,
-           n_kv_heads, head_dim, _i32(error_flag, "error_flag"), _stream())
+           n_kv_heads, head_dim, _i32(error_flag, "error_flag"), *_prenorm_args(prenorm, M, "gemm_skinny_qkv_rope"), _stream())
     _check(rc, "gemm_skinny.cu", "lmsf_gemm_skinny", SKINNY_DEFINES)
 
 

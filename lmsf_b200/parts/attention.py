@@ -17,9 +17,10 @@ from typing import Dict, Optional
 import torch
 
 from .. import kernels
-from .base import KVCacheSpec, LayerCache, Mixer, PositionEncoding, StepContext, WeightSpec, register_part
+from .base import (KVCacheSpec, LayerCache, Mixer, NormAfter, PositionEncoding, Prenormed, StepContext, WeightSpec,
+                   register_part)
 from . import linear
-from .linear import matmul_tn
+from .linear import matmul_tn, matmul_tn_residual
 
 
 SPLITS_PER_REQUEST = os.environ.get("LMSF_DECODE_ITEMS", "1") != "0"   # decode batches of very different lengths: splits per request
@@ -30,6 +31,8 @@ FUSE_QKV_ROPE = True      # up to 16 single tokens: rotary encoding and cache wr
 @register_part("mixer", "paged_attention")
 class PagedAttention(Mixer):
     graph_safe = True      # launch geometry depends on the batch's size only: a decode step can be replayed
+    takes_prenormed = True
+    fuses_norm = True
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position_encoding: Optional[PositionEncoding] = None, window: Optional[int] = None,
@@ -81,21 +84,23 @@ class PagedAttention(Mixer):
             warnings.warn("a cap on the attention scores is taken by the generic kernel only; bfloat16 attention runs on it",
                           RuntimeWarning, stacklevel=2)
 
-    def forward(self, ctx: StepContext, h: torch.Tensor, cache: LayerCache) -> torch.Tensor:
+    def forward(self, ctx: StepContext, h, cache: LayerCache, then: Optional[NormAfter] = None):
         group = ctx.groups[cache.group]
         fused = self.position_encoding.fused_rotary() if self.position_encoding is not None else None
+        hx = h.x if isinstance(h, Prenormed) else h
         if (FUSE_QKV_ROPE and cache.owner and linear.USE_SKINNY and self.qkv_bias is None and (fused is not None or self.position_encoding is None)
-                and kernels.gemm_skinny_qkv_rope_supported(h, self.qkv, self.head_dim, fused[1] if fused else 0,
+                and kernels.gemm_skinny_qkv_rope_supported(hx, self.qkv, self.head_dim, fused[1] if fused else 0,
                                                            fused[2] if fused else True)):
             # a few single tokens (a decode step): projection, rotation and cache write in one kernel
             inv_freq, rot_dim, is_neox = fused if fused is not None else (None, 0, True)
-            q = torch.empty((ctx.n_tokens, self.q_size), dtype=h.dtype, device=h.device)
-            kernels.gemm_skinny_qkv_rope(q, h, self.qkv, ctx.positions, ctx.token_seq, group.block_table, group.block_size,
+            q = torch.empty((ctx.n_tokens, self.q_size), dtype=hx.dtype, device=hx.device)
+            kernels.gemm_skinny_qkv_rope(q, hx, self.qkv, ctx.positions, ctx.token_seq, group.block_table, group.block_size,
                                          cache.kv, inv_freq, rot_dim, is_neox, self.num_heads, self.num_kv_heads,
-                                         self.head_dim, ctx.error_flag)
-            out = torch.empty((ctx.n_tokens, self.q_size), dtype=h.dtype, device=h.device)
+                                         self.head_dim, ctx.error_flag,
+                                         prenorm=(h.sumsq, h.eps, h.width) if isinstance(h, Prenormed) else None)
+            out = torch.empty((ctx.n_tokens, self.q_size), dtype=hx.dtype, device=hx.device)
             self.attend(ctx, out, q, cache.kv, group)
-            return matmul_tn(out, self.o, bias=self.o_bias)
+            return self._project_out(out, then)
         if cache.owner:
             qkv = matmul_tn(h, self.qkv, bias=self.qkv_bias)
             q = qkv[:, :self.q_size]
@@ -111,8 +116,15 @@ class PagedAttention(Mixer):
             kernels.rope_cache_write(q, k, v, ctx.positions, ctx.token_seq, group.block_table, group.block_size,
                                      cache.kv if cache.owner else None, inv_freq, rot_dim, is_neox, self.num_heads,
                                      self.num_kv_heads, self.head_dim, ctx.error_flag)
-        out = torch.empty((ctx.n_tokens, self.q_size), dtype=h.dtype, device=h.device)
+        out = torch.empty((ctx.n_tokens, self.q_size), dtype=q.dtype, device=q.device)
         self.attend(ctx, out, q, cache.kv, group)
+        return self._project_out(out, then)
+
+    def _project_out(self, out: torch.Tensor, then: Optional[NormAfter]):
+        if then is not None and self.o_bias is None:
+            p = matmul_tn_residual(out, self.o, then)
+            if p is not None:
+                return p
         return matmul_tn(out, self.o, bias=self.o_bias)
 
     def attend(self, ctx: StepContext, out: torch.Tensor, q: torch.Tensor, kv: torch.Tensor, group) -> None:

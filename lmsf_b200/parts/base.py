@@ -176,12 +176,41 @@ class Part:
 
 
 class Norm(Part):
+    # True when the norm is a factor per row times a weight per column, so that the products around it can share its
+    # work (`NormAfter`, `Prenormed`); such a norm has `weight`, `eps`, `hidden_size` and `finish`.
+    splittable = False
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
 
     def forward_residual(self, x: torch.Tensor, res: Optional[torch.Tensor]) -> Tuple[torch.Tensor, torch.Tensor]:
-        """res' = res + x in float32 (res None: res' = x); returns (norm(res'), res')."""
+        """res' = res + x in float32 (res None: res' = x); returns (norm(res'), res').  A splittable norm is also
+        handed its own `Prenormed` (the add is done): it returns it as it is."""
         raise NotImplementedError
+
+
+@dataclass
+class NormAfter:
+    """What a block hands to a mixer or feed-forward that says `fuses_norm`: the norm that follows the part and the
+    residual stream.  If the part's last product can, it adds its result to `res` itself, does the first half of the
+    norm and returns a `Prenormed` instead of a tensor (`linear.matmul_tn_residual`).  A step of a few tokens saves a
+    kernel and a round trip through memory between two products that way."""
+    norm: Norm
+    res: torch.Tensor
+
+
+@dataclass
+class Prenormed:
+    """A norm's output before the division: `x` = residual x norm weight (bfloat16), `sumsq` [rows, parts] float32
+    partial sums of the squares of the residual's rows.  The factor 1 / sqrt(sum / width + eps) is common to a row, so
+    a product that takes a Prenormed (a part that says `takes_prenormed`; `linear.matmul_tn`) applies it to its
+    sums.  `norm.finish(p)` gives the ordinary normed tensor."""
+    x: torch.Tensor
+    sumsq: torch.Tensor
+    eps: float
+    width: int
+    norm: Norm
+    res: torch.Tensor
 
 
 class PositionEncoding(Part):
@@ -197,6 +226,11 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    # takes_prenormed: `forward` accepts a `Prenormed` as h.  fuses_norm: `forward` accepts `then=NormAfter(...)` and
+    # may return a `Prenormed`.  A part that says neither is always given and asked for plain tensors.
+    takes_prenormed = False
+    fuses_norm = False
+
     def cache_spec(self) -> Optional[KVCacheSpec]:
         return None
 
@@ -208,6 +242,9 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    takes_prenormed = False     # as for a mixer
+    fuses_norm = False
+
     def forward(self, ctx: StepContext, h: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
 
@@ -228,6 +265,14 @@ class Block:
                 ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
         """(x, res) -> (x, res): x is the branch output not yet added, res the float32 residual sum."""
         raise NotImplementedError
+
+    def entry(self) -> Optional[Tuple[Norm, Part]]:
+        """(the norm that the block's input meets first, the part that reads that norm's output), for the block that
+        runs before this one and says `fuses_next_norm`: its `forward` is then called with `next_entry=` this pair
+        and may return a `Prenormed` for that norm as x.  None (the default): the block wants a plain tensor."""
+        return None
+
+    fuses_next_norm = False
 
 
 # ----------------------------------------------------------------------------- registries

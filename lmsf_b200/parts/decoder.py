@@ -70,8 +70,14 @@ class DecoderModel:
         x = self.embedding.forward(ctx)
         res = None
         for j, call in enumerate(self.calls):
+            block = self.blocks[call.layer]
+            # a block that can take the next block's first norm into its last product is told that norm and its reader
+            entry = self.blocks[self.calls[j + 1].layer].entry() if block.fuses_next_norm and j + 1 < len(self.calls) else None
             with span(f"layer {call.layer}"):
-                x, res = self.blocks[call.layer].forward(ctx, x, res, caches[j])
+                if entry is not None:
+                    x, res = block.forward(ctx, x, res, caches[j], next_entry=entry)
+                else:
+                    x, res = block.forward(ctx, x, res, caches[j])
         n_rows = 0 if logit_rows is None else logit_rows.numel()
         if n_rows == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=x.device)

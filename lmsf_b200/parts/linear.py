@@ -14,7 +14,7 @@ from typing import Dict, List, Optional, Sequence, Union
 import torch
 
 from .. import kernels
-from .base import Part, WeightSpec, register_part
+from .base import NormAfter, Part, Prenormed, WeightSpec, register_part
 
 # Library products must add up in float32: with torch's default a split-k bfloat16 product may add its partial sums
 # in bfloat16, and a row's result would then depend on how many rows share the product (on how a prompt was cut).
@@ -25,11 +25,26 @@ USE_SKINNY = True     # bfloat16 products of up to 16 rows run on this package's
 SKINNY_TALL_FROM = 65536   # ... except 9 to 16 rows against this many output features and more
 
 
-def matmul_tn(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+def _skinny_takes(x: torch.Tensor, w: torch.Tensor) -> bool:
+    # (9 to 16 rows against a very tall matrix, the head: a stage of the kernel then holds as much of x as of w, and the
+    # library is faster: 162 against 182 us for 128,256 x 4,096 at 16 rows)
+    return USE_SKINNY and kernels.gemm_skinny_supported(x, w) and not (x.shape[0] > 8 and w.shape[0] >= SKINNY_TALL_FROM)
+
+
+def matmul_tn(x: Union[torch.Tensor, Prenormed], w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
               bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """x [M, K] times w [N, K] transposed -> [M, N] in `out_dtype` (default: x's dtype), plus `bias` [N] if given
-    (added by a kernel of its own after the product, as the reference adds it: layers/linear.rs:100-104)."""
-    y = _product_tn(x, w, out_dtype)
+    (added by a kernel of its own after the product, as the reference adds it: layers/linear.rs:100-104).  x may be a
+    `Prenormed`: the weight-streaming kernel divides its sums by the rows' root mean square."""
+    if isinstance(x, Prenormed):
+        dt = out_dtype or x.x.dtype
+        if _skinny_takes(x.x, w) and dt in (torch.bfloat16, torch.float32):
+            y = torch.empty((x.x.shape[0], w.shape[0]), dtype=dt, device=w.device)
+            kernels.gemm_skinny(y, x.x, w, prenorm=(x.sumsq, x.eps, x.width))
+        else:
+            y = _product_tn(x.norm.finish(x), w, out_dtype)
+    else:
+        y = _product_tn(x, w, out_dtype)
     if bias is not None:
         kernels.bias_add(y, bias if bias.dtype == y.dtype else bias.to(y.dtype))
     return y
@@ -42,10 +57,7 @@ def _product_tn(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtyp
         out = torch.empty((x.shape[0], w.shape[0]), dtype=torch.float32, device=x.device)
         kernels.gemm_tn_simt(out, x, w)
         return out if out_dtype == torch.float32 else out.to(out_dtype)
-    # (9 to 16 rows against a very tall matrix, the head: a stage of the kernel then holds as much of x as of w, and the
-    # library is faster: 162 against 182 us for 128,256 x 4,096 at 16 rows)
-    if USE_SKINNY and kernels.gemm_skinny_supported(x, w) and out_dtype in (torch.bfloat16, torch.float32) and \
-            not (x.shape[0] > 8 and w.shape[0] >= SKINNY_TALL_FROM):
+    if _skinny_takes(x, w) and out_dtype in (torch.bfloat16, torch.float32):
         out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype, device=x.device)
         kernels.gemm_skinny(out, x, w)
         return out
@@ -63,6 +75,21 @@ def _product_tn(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtyp
     out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype, device=x.device)
     kernels.gemm_tn_simt(out, x, w)
     return out
+
+
+def matmul_tn_residual(x: torch.Tensor, w: torch.Tensor, then: NormAfter) -> Optional[Prenormed]:
+    """The product before a norm, for a few rows: then.res += x w^T, and the first half of then.norm on the new
+    residual.  None when this product cannot do it (the caller then multiplies as usual and the norm runs whole)."""
+    norm, res = then.norm, then.res
+    weight = getattr(norm, "weight", None)
+    if not (norm.splittable and _skinny_takes(x, w) and weight is not None and res.dtype == torch.float32
+            and res.shape == (x.shape[0], w.shape[0]) and res.is_contiguous() and weight.shape == (w.shape[0],)):
+        return None
+    parts = kernels.gemm_skinny_residual_parts(w.shape[0])
+    sumsq = torch.empty((x.shape[0], (parts + 3) // 4 * 4), dtype=torch.float32, device=x.device)[:, :parts]
+    xg = torch.empty((x.shape[0], w.shape[0]), dtype=torch.bfloat16, device=x.device)
+    kernels.gemm_skinny_residual(xg, x, w, res, weight, sumsq)
+    return Prenormed(xg, sumsq, norm.eps, w.shape[0], norm, res)
 
 
 @register_part("linear", "dense")

@@ -11,14 +11,16 @@ from typing import Dict, Optional
 import torch
 
 from .. import kernels
-from .base import FeedForward, StepContext, WeightSpec, register_part
+from .base import FeedForward, NormAfter, Prenormed, StepContext, WeightSpec, register_part
 from . import linear
-from .linear import matmul_tn
+from .linear import matmul_tn, matmul_tn_residual
 
 
 @register_part("feed_forward", "gated_mlp")
 class GatedMLP(FeedForward):
     graph_safe = True
+    takes_prenormed = True
+    fuses_norm = True
 
     def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu", bias: bool = False):
         if activation not in kernels.ACT_CODES:
@@ -41,13 +43,22 @@ class GatedMLP(FeedForward):
     def activation_width(self) -> int:
         return 3 * self.intermediate_size                    # gate, up and their product
 
-    def forward(self, ctx: StepContext, h: torch.Tensor) -> torch.Tensor:
-        if linear.USE_SKINNY and self.gate_up_bias is None and kernels.gemm_skinny_supported(h, self.gate_up):
+    def forward(self, ctx: StepContext, h, then: Optional[NormAfter] = None):
+        hx = h.x if isinstance(h, Prenormed) else h
+        if linear.USE_SKINNY and self.gate_up_bias is None and kernels.gemm_skinny_supported(hx, self.gate_up):
             # a decode step: gate, up and the activation in one pass over the weights
-            m = torch.empty((h.shape[0], self.intermediate_size), dtype=h.dtype, device=h.device)
-            kernels.gemm_skinny(m, h, self.gate_up, fuse_act=self.activation)
-            return matmul_tn(m, self.down)
+            m = torch.empty((hx.shape[0], self.intermediate_size), dtype=hx.dtype, device=hx.device)
+            kernels.gemm_skinny(m, hx, self.gate_up, fuse_act=self.activation,
+                                prenorm=(h.sumsq, h.eps, h.width) if isinstance(h, Prenormed) else None)
+            return self._down(m, then)
         gu = matmul_tn(h, self.gate_up, bias=self.gate_up_bias)
-        m = torch.empty((h.shape[0], self.intermediate_size), dtype=h.dtype, device=h.device)
+        m = torch.empty((gu.shape[0], self.intermediate_size), dtype=gu.dtype, device=gu.device)
         kernels.gated_act(m, gu, self.activation)
+        return self._down(m, then)
+
+    def _down(self, m: torch.Tensor, then: Optional[NormAfter]):
+        if then is not None and self.down_bias is None:
+            p = matmul_tn_residual(m, self.down, then)
+            if p is not None:
+                return p
         return matmul_tn(m, self.down, bias=self.down_bias)

@@ -11,12 +11,13 @@ from typing import Dict, Optional, Tuple
 import torch
 
 from .. import kernels
-from .base import Norm, WeightSpec, register_part
+from .base import Norm, Prenormed, WeightSpec, register_part
 
 
 @register_part("norm", "rmsnorm")
 class RMSNorm(Norm):
     graph_safe = True
+    splittable = True
 
     def __init__(self, hidden_size: int, eps: float, weight_offset: float = 0.0):
         self.hidden_size = int(hidden_size)
@@ -39,7 +40,11 @@ class RMSNorm(Norm):
         kernels.add_rmsnorm(h, x, None, self.weight, self.eps, 0)
         return h
 
-    def forward_residual(self, x: torch.Tensor, res: Optional[torch.Tensor]) -> Tuple[torch.Tensor, torch.Tensor]:
+    def forward_residual(self, x, res: Optional[torch.Tensor]):
+        if isinstance(x, Prenormed):
+            if x.norm is not self or x.res is not res:
+                raise ValueError("a Prenormed activation was prepared for another norm or residual stream")
+            return x, res
         h = torch.empty_like(x)
         if res is None:
             res = torch.empty(x.shape, dtype=torch.float32, device=x.device)
@@ -47,3 +52,9 @@ class RMSNorm(Norm):
         else:
             kernels.add_rmsnorm(h, x, res, self.weight, self.eps, 2)
         return h, res
+
+    def finish(self, p: Prenormed) -> torch.Tensor:
+        """The ordinary output of the norm from a `Prenormed`, for a product that cannot take one."""
+        h = torch.empty_like(p.x)
+        kernels.finish_rmsnorm(h, p.res, p.sumsq, self.weight, self.eps)
+        return h

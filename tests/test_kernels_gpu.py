@@ -523,6 +523,64 @@ def test_gemm_skinny_against_its_plain_twin(M, N, K):
                             torch.zeros(17, K, dtype=torch.bfloat16, device=d), w)
 
 
+@pytest.mark.parametrize("M,N,K,N2", [(8, 4096, 512, 1024), (1, 48, 64, 32), (5, 1000, 320, 30), (16, 1032, 256, 512),
+                                      (13, 5120, 128, 64), (3, 16, 1976, 18)])
+@pytest.mark.parametrize("w_dtype", [torch.float32, torch.bfloat16])
+def test_a_norm_split_between_the_products_around_it(M, N, K, N2, w_dtype):
+    """The residual form (product, residual add, residual x norm weight, partial sums of squares) and a product that
+    takes that as a prenormed input, plain and gated, and the finishing kernel, against float64; widths whose number
+    of partial sums is no multiple of 4, of 8 or of 16 among them.  The residual itself is what the three separate
+    steps give, bit for bit."""
+    from lmsf_b200 import kernels
+    g = torch.Generator().manual_seed(17)
+    d = dev()
+    eps = 1e-5
+    x = torch.randn(M, K, generator=g).bfloat16().to(d)
+    w = (torch.randn(N, K, generator=g) * 0.1).bfloat16().to(d)
+    res0 = (torch.randn(M, N, generator=g) * 2).to(d)
+    nw = (1 + 0.3 * torch.randn(N, generator=g)).to(w_dtype).to(d)
+    w2 = (torch.randn(2 * N2, N, generator=g) * 0.05).bfloat16().to(d)
+    parts = kernels.gemm_skinny_residual_parts(N)
+    sumsq = torch.full((M, (parts + 3) // 4 * 4), float("nan"), device=d)[:, :parts]
+    res = res0.clone()
+    xg = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=d)
+    kernels.gemm_skinny_residual(xg, x, w, res, nw, sumsq)
+    # the three steps: product (bfloat16 out), add into the float32 residual, norm
+    delta = torch.empty(M, N, dtype=torch.bfloat16, device=d)
+    kernels.gemm_skinny(delta, x, w)
+    res_ref = res0.clone()
+    h_ref = torch.empty_like(delta)
+    kernels.add_rmsnorm(h_ref, delta, res_ref, nw, eps, 2)
+    assert torch.equal(res, res_ref)
+    r64 = res_ref.double()
+    assert torch.allclose(sumsq.double().sum(1), (r64 * r64).sum(1), rtol=1e-5)
+    assert torch.allclose(xg.float().double(), r64 * nw.double(), rtol=1e-2, atol=1e-2)
+    normed = r64 / torch.sqrt((r64 * r64).mean(1, keepdim=True) + eps) * nw.double()
+    # the finishing kernel gives the norm's output
+    h = torch.empty_like(xg)
+    kernels.finish_rmsnorm(h, res, sumsq, nw, eps)
+    assert torch.allclose(h.float().double(), normed, rtol=1e-2, atol=1e-2)
+    assert (h.float() - h_ref.float()).abs().max().item() <= 2 ** -7 * h_ref.float().abs().max().item()
+    # products of the prenormed input: plain (both output types) and gated
+    want = normed @ w2.double().t()
+    for odt in (torch.bfloat16, torch.float32):
+        y = torch.full((M, 2 * N2), float("nan"), dtype=odt, device=d)
+        kernels.gemm_skinny(y, xg, w2, prenorm=(sumsq, eps, N))
+        assert (y.double() - want).abs().max().item() <= 1.5e-2 * want.abs().max().item()
+    gte, up = want[:, :N2], want[:, N2:]
+    y = torch.full((M, N2), float("nan"), dtype=torch.bfloat16, device=d)
+    kernels.gemm_skinny(y, xg, w2, fuse_act="silu", prenorm=(sumsq, eps, N))
+    want_g = gte / (1 + torch.exp(-gte)) * up
+    assert (y.double() - want_g).abs().max().item() <= 2e-2 * want_g.abs().max().item()
+    # as good as the unfused way: the same product of the ordinary norm's output
+    y_ref = torch.empty(M, 2 * N2, dtype=torch.float32, device=d)
+    kernels.gemm_skinny(y_ref, h_ref, w2)
+    y_new = torch.empty_like(y_ref)
+    kernels.gemm_skinny(y_new, xg, w2, prenorm=(sumsq, eps, N))
+    e_ref, e_new = (y_ref.double() - want).abs().max().item(), (y_new.double() - want).abs().max().item()
+    assert e_new <= 2 * e_ref + 1e-6 * want.abs().max().item(), (e_new, e_ref)
+
+
 def test_attention_kernels_on_a_long_prompt_and_a_long_context():
     """6,000 tokens in one portion (47 key tiles per block: the rings of stages and the barriers' phases wrap many
     times) on both prefill kernels, and one decoded token over 16,000 keys in 1, 7 and 64 splits; a sample of rows
@@ -590,6 +648,24 @@ def test_fused_qkv_rotary_cache_write_equals_the_three_steps(M, nh, nkv, hd, rot
     cache = torch.zeros_like(cache_ref)
     q = torch.full((M, q_size), float("nan"), dtype=torch.bfloat16, device=d)
     kernels.gemm_skinny_qkv_rope(q, x, w, positions, token_seq, bt, bs, cache, inv_freq, rot, neox, nh, nkv, hd, flag)
+    assert flag.item() == 0
+    assert torch.equal(q.view(torch.int16), q_ref.contiguous().view(torch.int16))
+    assert torch.equal(cache.view(torch.int16), cache_ref.view(torch.int16))
+    # the same with a prenormed input: the factor of a row is applied before the sums are rounded
+    sumsq = (torch.rand(M, 7, generator=g) * 50).to(d)
+    sumsq_padded = torch.zeros(M, 8, device=d)
+    sumsq_padded[:, :7] = sumsq
+    pn = (sumsq_padded[:, :7], 1e-6, K)
+    kernels.gemm_skinny(qkv, x, w, prenorm=pn)
+    plain = torch.empty_like(qkv)
+    kernels.gemm_skinny(plain, x, w)
+    assert not torch.equal(plain, qkv)
+    cache_ref.zero_()
+    q_ref = qkv[:, :q_size]
+    kernels.rope_cache_write(q_ref, qkv[:, q_size:q_size + kv_size], qkv[:, q_size + kv_size:], positions, token_seq, bt, bs,
+                             cache_ref, inv_freq, rot, neox, nh, nkv, hd, flag)
+    cache.zero_()
+    kernels.gemm_skinny_qkv_rope(q, x, w, positions, token_seq, bt, bs, cache, inv_freq, rot, neox, nh, nkv, hd, flag, prenorm=pn)
     assert flag.item() == 0
     assert torch.equal(q.view(torch.int16), q_ref.contiguous().view(torch.int16))
     assert torch.equal(cache.view(torch.int16), cache_ref.view(torch.int16))

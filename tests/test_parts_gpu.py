@@ -543,6 +543,82 @@ def test_attention_mixer_alone_over_two_steps(dtype, tol, nh, nkv, hd, window, s
     assert ctx.error_flag.item() == 0 and ctx2.error_flag.item() == 0
 
 
+def test_a_decode_step_splits_its_norms_between_the_products_around_them(monkeypatch):
+    """Two blocks of the package's parts on a step of five single tokens in bfloat16: the norm between the output
+    projection and the gated product, and the one between the down product and the next block's q/k/v product, are
+    done by those products (a `Prenormed` travels instead of a tensor) and four launches fewer run; the result is the
+    one of whole norms within rounding.  A next block whose mixer does not say `takes_prenormed` (a toy, defined
+    here) is handed a plain tensor."""
+    from lmsf_b200 import kernels
+    from lmsf_b200.parts import block as block_mod
+    from lmsf_b200.parts.attention import PagedAttention
+    from lmsf_b200.parts.base import LayerCache, Mixer, Prenormed
+    from lmsf_b200.parts.block import PreNormBlock
+    from lmsf_b200.parts.mlp import GatedMLP
+    from lmsf_b200.parts.norm import RMSNorm
+    from lmsf_b200.parts.rope import RotaryEmbedding
+    H, nh, nkv, hd, inter, bs, n = 72, 4, 2, 16, 104, 8, 5
+    g = torch.Generator().manual_seed(3)
+    dt = torch.bfloat16
+
+    def make_block(mixer=None):
+        n1, n2 = RMSNorm(H, 1e-5), RMSNorm(H, 1e-6)
+        n1.set_weights({"weight": (1 + 0.2 * torch.randn(H, generator=g)).to(DEV)})          # a 32-bit weight
+        n2.set_weights({"weight": (1 + 0.2 * torch.randn(H, generator=g)).to(dt).to(DEV)})   # a bfloat16 one
+        if mixer is None:
+            mixer = PagedAttention(hidden_size=H, num_heads=nh, num_kv_heads=nkv, head_dim=hd,
+                                   position_encoding=RotaryEmbedding(rot_dim=hd, theta=1000.0))
+            mixer.set_weights({"qkv": (torch.randn((nh + 2 * nkv) * hd, H, generator=g) * 0.2).to(dt).to(DEV),
+                               "o": (torch.randn(H, nh * hd, generator=g) * 0.2).to(dt).to(DEV)})
+            mixer.prepare(dt, torch.device(DEV))
+        ff = GatedMLP(hidden_size=H, intermediate_size=inter)
+        ff.set_weights({"gate_up": (torch.randn(2 * inter, H, generator=g) * 0.2).to(dt).to(DEV),
+                        "down": (torch.randn(H, inter, generator=g) * 0.2).to(dt).to(DEV)})
+        return PreNormBlock({"mixer_norm": n1, "mixer": mixer, "ffn_norm": n2, "feed_forward": ff})
+
+    b1, b2 = make_block(), make_block()
+    x0 = torch.randn(n, H, generator=g).to(dt).to(DEV)
+    ctx_lens = [9, 3, 17, 1, 8]
+
+    def run(split):
+        monkeypatch.setattr(block_mod, "FUSE_NORMS", split)
+        ctx, _ = _hand_context([1] * n, ctx_lens, bs, 16, seed=2)
+        ctx.dtype = dt
+        caches = [LayerCache(kv=torch.zeros(16, 2, nkv, bs, hd, dtype=dt, device=DEV), group=0, owner=True) for _ in range(2)]
+        before = kernels.launch_count()
+        x1, res = b1.forward(ctx, x0, None, caches[0], next_entry=b2.entry())
+        launches = kernels.launch_count() - before
+        # what the next block's first norm gives: from the Prenormed, or by the whole norm
+        h_mid = (b2.mixer_norm.finish(x1) if isinstance(x1, Prenormed) else b2.mixer_norm.forward_residual(x1, res.clone())[0]).float()
+        before = kernels.launch_count()
+        x2, res2 = b2.forward(ctx, x1, res, caches[1])
+        assert ctx.error_flag.item() == 0 and res2 is res
+        return x1, h_mid, x2.float(), res.clone(), launches + kernels.launch_count() - before
+
+    mid_s, h_s, x_s, res_s, launches_s = run(True)
+    mid_w, h_w, x_w, res_w, launches_w = run(False)
+    assert isinstance(mid_s, Prenormed) and isinstance(mid_w, torch.Tensor)
+    assert launches_w - launches_s == 3              # the norms after the two output projections and after one down product
+    tol = 2e-2 * res_w.abs().max().item()
+    assert (res_s - res_w).abs().max().item() <= tol and (x_s - x_w).abs().max().item() <= tol
+    assert (h_s - h_w).abs().max().item() <= 2e-2 * h_w.abs().max().item()     # the normed tensor that the Prenormed stands for
+
+    class Toy(Mixer):
+        def forward(self, ctx, h, cache):
+            assert isinstance(h, torch.Tensor)
+            return h
+
+    b3 = make_block(Toy())
+    monkeypatch.setattr(block_mod, "FUSE_NORMS", True)
+    ctx, _ = _hand_context([1] * n, ctx_lens, bs, 16, seed=2)
+    ctx.dtype = dt
+    cache = LayerCache(kv=torch.zeros(16, 2, nkv, bs, hd, dtype=dt, device=DEV), group=0, owner=True)
+    x1, res = b1.forward(ctx, x0, None, cache, next_entry=b3.entry())
+    assert isinstance(x1, torch.Tensor)
+    x3, _ = b3.forward(ctx, x1, res, LayerCache())
+    assert isinstance(x3, torch.Tensor)
+
+
 def test_embedding_rotary_apply_and_block_arrangement():
     from lmsf_b200.parts.base import FeedForward, LayerCache, Mixer, Norm, PartSpec
     from lmsf_b200.parts.block import PreNormBlock
