@@ -1,8 +1,9 @@
 """Kernels against their plain twins on many random shapes (seeded): the tcgen05 prefill attention against the
 mma.sync one, the decode attention (planned splits and widths, and splits per request) against the generic kernel,
-the weight-streaming product against float64.  Longer runs of the same loops found an order of calls in which a
+the weight-streaming product, its residual form and its prenormed input against float64.  Longer runs of the same loops found an order of calls in which a
 decode launch was refused and a gated product of exactly 8 features that read zeros; the suite keeps a short run."""
 import math
+import os
 import random
 
 import numpy as np
@@ -10,6 +11,8 @@ import pytest
 import torch
 
 pytestmark = pytest.mark.gpu
+
+SOAK = int(os.environ.get("LMSF_TEST_SOAK", "1"))     # a longer run of the same loops: LMSF_TEST_SOAK=10
 
 
 def dev():
@@ -37,7 +40,7 @@ def test_prefill_attention_on_random_shapes(seed, monkeypatch):
     torch.manual_seed(seed)
     d = dev()
     i32 = lambda l: torch.tensor(l, dtype=torch.int32, device=d)
-    for case in range(200):
+    for case in range(200 * SOAK):
         hd = rng.choice([64, 128])
         nkv = rng.choice([1, 2, 3, 4, 8])
         group = rng.choice([1, 2, 3, 4, 5, 8])
@@ -81,7 +84,7 @@ def test_decode_attention_on_random_shapes(seed):
     rng = random.Random(seed)
     torch.manual_seed(seed)
     d = dev()
-    for case in range(300):
+    for case in range(300 * SOAK):
         hd = rng.choice([16, 32, 48, 64, 80, 96, 112, 128])
         nkv = rng.choice([1, 2, 4, 8])
         group = rng.choice([1, 2, 3, 4, 8, 17])
@@ -132,7 +135,7 @@ def test_weight_streaming_product_on_random_shapes(seed):
     rng = random.Random(seed)
     torch.manual_seed(seed)
     d = dev()
-    for case in range(600):
+    for case in range(600 * SOAK):
         M = rng.randint(1, 16)
         K = 8 * rng.randint(1, 700)
         fuse = rng.choice([None, None, "silu", "gelu_tanh"])
@@ -150,3 +153,35 @@ def test_weight_streaming_product_on_random_shapes(seed):
             y = act * u
         err = (out.double() - y).abs().max().item()
         assert err <= (2e-3 if f32 else 2e-2) * max(y.abs().max().item(), 1e-2), (seed, case, M, N, K, fuse, f32, err)
+        if case % 3:
+            continue
+        # the norm split between two products: the residual form of this one (plain cases), then the same weights
+        # again, transposed in role, as the product of the prenormed input
+        if fuse is None:
+            eps = 10.0 ** -rng.randint(5, 6)
+            res0 = torch.randn(M, N, device=d) * 2
+            nw = (1 + 0.3 * torch.randn(N, device=d)).to(torch.float32 if rng.random() < 0.5 else torch.bfloat16)
+            parts = kernels.gemm_skinny_residual_parts(N)
+            sumsq = torch.full((M, (parts + 3) // 4 * 4), float("nan"), device=d)[:, :parts]
+            res, xg = res0.clone(), torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=d)
+            kernels.gemm_skinny_residual(xg, x, w, res, nw, sumsq)
+            delta = torch.empty(M, N, dtype=torch.bfloat16, device=d)
+            kernels.gemm_skinny(delta, x, w)
+            want_res = res0 + delta.float()
+            what = (seed, case, M, N, K, "residual form")
+            assert torch.equal(res, want_res), what
+            r64 = want_res.double()
+            assert torch.allclose(sumsq.double().sum(1), (r64 * r64).sum(1), rtol=1e-5), what
+            assert (xg.double() - r64 * nw.double()).abs().max().item() <= 8e-3 * (r64 * nw.double()).abs().max().item(), what
+            if N % 8 == 0:
+                normed = r64 / torch.sqrt((r64 * r64).mean(1, keepdim=True) + eps) * nw.double()
+                n2 = rng.choice([rng.randint(1, 40), 16 * rng.randint(1, 60)])
+                act = rng.choice([None, "silu"])
+                w2 = (torch.randn((2 if act else 1) * n2, N, device=d) / math.sqrt(N)).to(torch.bfloat16)
+                y2 = normed @ w2.double().t()
+                if act:
+                    y2 = y2[:, :n2] / (1 + torch.exp(-y2[:, :n2])) * y2[:, n2:]
+                out2 = torch.full((M, n2), float("nan"), dtype=torch.float32, device=d)
+                kernels.gemm_skinny(out2, xg, w2, fuse_act=act, prenorm=(sumsq, eps, N))
+                err = (out2.double() - y2).abs().max().item()
+                assert err <= 2e-2 * max(y2.abs().max().item(), 1e-2), (seed, case, M, N, K, n2, act, "prenormed input", err)
