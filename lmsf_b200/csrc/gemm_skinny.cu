@@ -91,11 +91,7 @@ __device__ __forceinline__ void issue_rows(uint32_t stage, const bf16* __restric
       const int c = lane % kLanesPerRow + j * kLanesPerRow;
       const bool okc = ok && k0 + c * 8 < K;          // K is a multiple of 8: a chunk is inside or outside
       const bf16* src = okc ? base + (size_t)(r + (r >= 8 ? hi_off : 0)) * ld + k0 + c * 8 : base;
-#ifdef LMSF_SKINNY_L2_HINT
-      cp_async_16_l2_256(stage + r * kRowBytes + ((c ^ (r & 7)) << 4), src, okc ? 16 : 0);
-#else
       cp_async_16(stage + r * kRowBytes + ((c ^ (r & 7)) << 4), src, okc ? 16 : 0);
-#endif
     }
   }
 }
@@ -111,15 +107,9 @@ __global__ void __launch_bounds__(kWarps * 32) skinny_kernel(Args a) {
   const int g4 = lane >> 2, t4 = lane & 3;
   const int n0 = blockIdx.x * (PAIR ? 8 : 16);
   const int n_chunks_total = (a.K + kChunkK - 1) / kChunkK;
-#ifdef LMSF_SKINNY_CONTIGUOUS_K
-  const int per_warp = (n_chunks_total + kWarps - 1) / kWarps;
-  const int c_begin = warp * per_warp, c_stride = 1;
-  const int n_chunks = max(0, min(n_chunks_total, c_begin + per_warp) - c_begin);
-#else
   // chunk c of warp w is chunk w + 4 c of the row: the four warps walk the same kilobyte of every row together
   const int c_begin = warp, c_stride = kWarps;
   const int n_chunks = (n_chunks_total - warp + kWarps - 1) / kWarps;
-#endif
   const uint32_t ring = smem_u32(smem) + warp * (STAGES * kStage);
   const int rows_total = (GROUPS == 2 || PAIR) ? a.up_offset : a.N;       // rows of one group
   // ROPE: rows 0..7 of the block are features f0.., rows 8..15 features f1..: a rotated pair sits 8 rows apart

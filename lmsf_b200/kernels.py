@@ -275,7 +275,7 @@ def gemm_tn_simt(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor):
 # ----------------------------------------------------------------------------- weight-streaming product (M <= 16)
 
 SKINNY_MAX_M = 16
-# build-time constants of gemm_skinny.cu; experiments override them, e.g. LMSF_SKINNY_DEFINES=LMSF_SKINNY_XREG=1
+# build-time constants of gemm_skinny.cu; experiments override them, e.g. LMSF_SKINNY_DEFINES=LMSF_SKINNY_STAGES=5
 SKINNY_DEFINES: Tuple[str, ...] = tuple(d for d in os.environ.get("LMSF_SKINNY_DEFINES", "").split(",") if d)
 
 
