@@ -603,6 +603,20 @@ def test_a_decode_step_splits_its_norms_between_the_products_around_them(monkeyp
     assert (res_s - res_w).abs().max().item() <= tol and (x_s - x_w).abs().max().item() <= tol
     assert (h_s - h_w).abs().max().item() <= 2e-2 * h_w.abs().max().item()     # the normed tensor that the Prenormed stands for
 
+    # a product that cannot take a Prenormed itself has the norm finished first (`matmul_tn`)
+    from lmsf_b200.parts import linear as linear_mod
+    w2 = (torch.randn(24, H, generator=g) * 0.2).to(dt).to(DEV)
+    monkeypatch.setattr(block_mod, "FUSE_NORMS", True)
+    ctx, _ = _hand_context([1] * n, ctx_lens, bs, 16, seed=2)
+    ctx.dtype = dt
+    cache = LayerCache(kv=torch.zeros(16, 2, nkv, bs, hd, dtype=dt, device=DEV), group=0, owner=True)
+    p, _ = b1.forward(ctx, x0, None, cache, next_entry=b2.entry())
+    y_split = linear_mod.matmul_tn(p, w2, torch.float32)
+    monkeypatch.setattr(linear_mod, "USE_SKINNY", False)
+    y_whole = linear_mod.matmul_tn(p, w2, torch.float32)
+    monkeypatch.setattr(linear_mod, "USE_SKINNY", True)
+    assert (y_split - y_whole).abs().max().item() <= 2e-2 * y_whole.abs().max().item()
+
     class Toy(Mixer):
         def forward(self, ctx, h, cache):
             assert isinstance(h, torch.Tensor)
