@@ -31,6 +31,7 @@ struct GenericAttnArgs {
   float scale; int window;                     // window <= 0: all keys
   int n_q_heads, n_kv_heads, head_dim;
   float softcap;                               // > 0: scores become softcap * tanh(score / softcap) before the softmax
+  const float* slopes;                         // [n_q_heads] or null: slope * (key position - query position) is added to the scores
 };
 
 template <typename T>
@@ -74,6 +75,7 @@ __global__ void __launch_bounds__(kWarps * 32) attention_generic_kernel(GenericA
         for (int d = 0; d < hd; ++d) dot = fmaf(qs[d], to_f32(kr[d]), dot);
         s = dot * a.scale;
         if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
+        if (a.slopes) s = fmaf(a.slopes[head], (float)(key - pos), s);
       }
     }
     const float m_new = fmaxf(m, warp_max(s));
@@ -123,13 +125,15 @@ __global__ void __launch_bounds__(kWarps * 32) attention_generic_kernel(GenericA
 
 }  // namespace lmsf
 
-// softcap > 0: the scaled scores are capped smoothly, softcap * tanh(score / softcap), before the softmax (a constant
-// of some architectures' attention; only this kernel takes it).
-LMSF_API int lmsf_attention_generic_softcap(const void* q, long long q_stride, void* out, long long out_stride,
-                                            const void* cache, long long page_stride, const int* block_table, int max_blocks,
-                                            int block_size, const int* token_seq, const int* positions, float scale,
-                                            float softcap, int window, int n_tokens, int n_q_heads, int n_kv_heads,
-                                            int head_dim, int dtype, void* stream) {
+// Two changes to the scores that some architectures make and only this kernel takes.  softcap > 0: the scaled scores
+// are capped smoothly, softcap * tanh(score / softcap).  slopes ([n_q_heads] float32, may be null): a position encoding
+// by a bias that grows with distance, slope[head] * (key position - query position), added to the scaled score as the
+// reference's decode kernel adds it (vllm/kernels/attention/attention_kernels.cu:144-145, :232-234).
+LMSF_API int lmsf_attention_generic_scores(const void* q, long long q_stride, void* out, long long out_stride,
+                                           const void* cache, long long page_stride, const int* block_table, int max_blocks,
+                                           int block_size, const int* token_seq, const int* positions, float scale,
+                                           float softcap, const float* slopes, int window, int n_tokens, int n_q_heads,
+                                           int n_kv_heads, int head_dim, int dtype, void* stream) {
   using namespace lmsf;
   if (n_tokens <= 0) return 0;
   if (head_dim <= 0 || head_dim > kMaxHeadDim || head_dim % 16)
@@ -140,7 +144,7 @@ LMSF_API int lmsf_attention_generic_softcap(const void* q, long long q_stride, v
   if (block_size <= 0 || max_blocks <= 0) LMSF_REFUSE("attention: bad block table geometry");
   if (dtype != LMSF_F32 && dtype != LMSF_BF16) LMSF_REFUSE("attention: unknown dtype code %d", dtype);
   GenericAttnArgs a{q, q_stride, out, out_stride, cache, page_stride, block_table, max_blocks, block_size,
-                    token_seq, positions, scale, window, n_q_heads, n_kv_heads, head_dim, softcap > 0.f ? softcap : 0.f};
+                    token_seq, positions, scale, window, n_q_heads, n_kv_heads, head_dim, softcap > 0.f ? softcap : 0.f, slopes};
   dim3 grid(n_tokens, n_q_heads);
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == LMSF_F32) attention_generic_kernel<float><<<grid, kWarps * 32, 0, s>>>(a);
@@ -153,7 +157,7 @@ LMSF_API int lmsf_attention_generic(const void* q, long long q_stride, void* out
                                     int block_size, const int* token_seq, const int* positions, float scale,
                                     int window, int n_tokens, int n_q_heads, int n_kv_heads, int head_dim, int dtype,
                                     void* stream) {
-  return lmsf_attention_generic_softcap(q, q_stride, out, out_stride, cache, page_stride, block_table, max_blocks, block_size,
-                                        token_seq, positions, scale, 0.f, window, n_tokens, n_q_heads, n_kv_heads, head_dim,
-                                        dtype, stream);
+  return lmsf_attention_generic_scores(q, q_stride, out, out_stride, cache, page_stride, block_table, max_blocks, block_size,
+                                       token_seq, positions, scale, 0.f, nullptr, window, n_tokens, n_q_heads, n_kv_heads,
+                                       head_dim, dtype, stream);
 }

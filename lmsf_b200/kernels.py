@@ -207,23 +207,27 @@ def rope_cache_write(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[tor
 
 def attention_generic(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                       block_size: int, token_seq: torch.Tensor, positions: torch.Tensor, scale: float, window: int,
-                      n_q_heads: int, n_kv_heads: int, head_dim: int, softcap: float = 0.0):
+                      n_q_heads: int, n_kv_heads: int, head_dim: int, softcap: float = 0.0,
+                      slopes: Optional[torch.Tensor] = None):
     """out[t] = softmax(scale q[t] K^T) V over the keys lo..positions[t] of token t's request, read from pages.
     q, out: [n, n_q_heads * head_dim] (last dimension contiguous); window <= 0 means all keys; softcap > 0 caps the
-    scaled scores smoothly, softcap * tanh(score / softcap)."""
+    scaled scores smoothly, softcap * tanh(score / softcap); slopes (float32 [n_q_heads]) adds
+    slopes[head] * (key position - query position) to the scaled scores."""
     n = q.shape[0]
     if q.stride(1) != 1 or out.stride(1) != 1 or q.shape[1] != n_q_heads * head_dim or out.shape != q.shape:
         raise KernelError("attention: q and out must be [n, heads * head_dim] with a contiguous last dimension")
     if cache.dtype != q.dtype or out.dtype != q.dtype or not cache.is_contiguous() or \
             tuple(cache.shape[1:]) != (2, n_kv_heads, block_size, head_dim):
         raise KernelError(f"attention: cache of shape {tuple(cache.shape)} / {cache.dtype} does not match the heads")
-    f = _func("attention_generic.cu", "lmsf_attention_generic_softcap",
+    if slopes is not None and (slopes.dtype != torch.float32 or slopes.shape != (n_q_heads,) or not slopes.is_contiguous()):
+        raise KernelError("attention: slopes must be float32 [n_q_heads]")
+    f = _func("attention_generic.cu", "lmsf_attention_generic_scores",
               [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_int, c_void_p,
-               c_void_p, c_float, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+               c_void_p, c_float, c_float, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
     rc = f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache), cache.stride(0),
            _i32(block_table, "block_table"), block_table.shape[1], block_size, _i32(token_seq, "token_seq"),
-           _i32(positions, "positions"), float(scale), float(softcap or 0.0), int(window or 0), n, n_q_heads, n_kv_heads,
-           head_dim, dtype_code(q.dtype), _stream())
+           _i32(positions, "positions"), float(scale), float(softcap or 0.0), _ptr(slopes), int(window or 0), n, n_q_heads,
+           n_kv_heads, head_dim, dtype_code(q.dtype), _stream())
     _check(rc, "attention_generic.cu", "lmsf_attention_generic")
 
 

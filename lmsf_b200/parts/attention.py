@@ -80,9 +80,15 @@ class PagedAttention(Mixer):
             warnings.warn(f"head_dim {self.head_dim} is beyond the tensor-core attention kernels "
                           f"(up to {kernels.MMA_MAX_HEAD_DIM}); bfloat16 attention runs on the generic kernel",
                           RuntimeWarning, stacklevel=2)
-        elif dtype == torch.bfloat16 and self.softcap:
-            warnings.warn("a cap on the attention scores is taken by the generic kernel only; bfloat16 attention runs on it",
-                          RuntimeWarning, stacklevel=2)
+        elif dtype == torch.bfloat16 and (self.softcap or self._slopes() is not None):
+            warnings.warn("a cap on the attention scores, or a bias on them, is taken by the generic kernel only; "
+                          "bfloat16 attention runs on it", RuntimeWarning, stacklevel=2)
+        slopes = self._slopes()
+        if slopes is not None and slopes.numel() != self.num_heads:
+            raise ValueError(f"{slopes.numel()} slopes for {self.num_heads} query heads")
+
+    def _slopes(self) -> Optional[torch.Tensor]:
+        return self.position_encoding.score_slopes() if self.position_encoding is not None else None
 
     def forward(self, ctx: StepContext, h, cache: LayerCache, then: Optional[NormAfter] = None):
         group = ctx.groups[cache.group]
@@ -132,7 +138,8 @@ class PagedAttention(Mixer):
         to a tiled prefill kernel (tcgen05 with accumulators in tensor memory for head sizes 64 and 128,
         mma.sync otherwise).  Everything else, float32 included, runs on the
         generic kernel, which is also their plain twin."""
-        if kernels.mma_attention_supported(q.dtype, self.head_dim) and not self.softcap and \
+        slopes = self._slopes()
+        if kernels.mma_attention_supported(q.dtype, self.head_dim) and not self.softcap and slopes is None and \
                 not ctx.extras.get("force_generic_attention"):
             if ctx.n_decode_seqs:
                 max_ctx = ctx.extras.get("decode_max_ctx")
@@ -200,4 +207,4 @@ class PagedAttention(Mixer):
             return
         kernels.attention_generic(out, q, kv, group.block_table, group.block_size, ctx.token_seq, ctx.positions,
                                   self.scale, self.window or 0, self.num_heads, self.num_kv_heads, self.head_dim,
-                                  softcap=self.softcap)
+                                  softcap=self.softcap, slopes=slopes)

@@ -224,6 +224,11 @@ class PositionEncoding(Part):
         cache-write kernel can apply itself; None otherwise."""
         return None
 
+    def score_slopes(self) -> Optional[torch.Tensor]:
+        """float32 [query heads] when the encoding is a bias on the attention scores that grows with distance,
+        slope * (key position - query position); None otherwise."""
+        return None
+
 
 class Mixer(Part):
     # takes_prenormed: `forward` accepts a `Prenormed` as h.  fuses_norm: `forward` accepts `then=NormAfter(...)` and

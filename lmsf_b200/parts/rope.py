@@ -85,3 +85,28 @@ class NoPositionEncoding(PositionEncoding):
 
     def apply(self, ctx, q, k, n_q_heads, n_kv_heads, head_dim) -> None:
         return None
+
+
+@register_part("position_encoding", "distance_bias")
+class DistanceBias(PositionEncoding):
+    """Positions enter the scores, not q and k: slope[head] * (key position - query position) is added to every scaled
+    score (the reference's decode kernel takes such slopes, vllm/kernels/attention/attention_kernels.cu:144-145,
+    :232-234, through layers/attention.rs:58-83; no model of its Llama path sets them).  The slopes are parameters, one
+    per query head.  Only the generic attention kernel takes them, so an attention part with this encoding runs on that
+    kernel in bfloat16 too: right, and slow."""
+    graph_safe = True
+
+    def __init__(self, slopes):
+        self.slopes_host = [float(v) for v in slopes]
+        if not self.slopes_host:
+            raise ValueError("a distance bias needs one slope per query head")
+        self.slopes: Optional[torch.Tensor] = None
+
+    def prepare(self, dtype, device) -> None:
+        self.slopes = torch.tensor(self.slopes_host, dtype=torch.float32, device=device)
+
+    def apply(self, ctx, q, k, n_q_heads, n_kv_heads, head_dim) -> None:
+        return None
+
+    def score_slopes(self) -> Optional[torch.Tensor]:
+        return self.slopes

@@ -135,7 +135,7 @@ def _paged_setup(dtype, n_q_heads, n_kv_heads, hd, bs, ctx_lens, q_lens, seed, s
     return q, cache.to(DT[dtype]), bt, token_seq, positions, ks, vs
 
 
-def _attention_reference(q, ks, vs, token_seq, positions, n_q_heads, n_kv_heads, hd, scale, window, softcap=0.0):
+def _attention_reference(q, ks, vs, token_seq, positions, n_q_heads, n_kv_heads, hd, scale, window, softcap=0.0, slopes=None):
     out = torch.empty(q.shape[0], n_q_heads, hd, dtype=torch.float64)
     r = n_q_heads // n_kv_heads
     qf = q.double().reshape(-1, n_q_heads, hd)
@@ -147,6 +147,8 @@ def _attention_reference(q, ks, vs, token_seq, positions, n_q_heads, n_kv_heads,
             sc = (k @ qf[t, h]) * scale
             if softcap:
                 sc = softcap * torch.tanh(sc / softcap)
+            if slopes is not None:                        # a bias that grows with the distance to the query
+                sc = sc + slopes[h] * (torch.arange(lo, p + 1, dtype=torch.float64) - p)
             w = torch.softmax(sc, dim=0)
             out[t, h] = w @ v
     return out.reshape(q.shape[0], -1)
@@ -154,8 +156,9 @@ def _attention_reference(q, ks, vs, token_seq, positions, n_q_heads, n_kv_heads,
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_constants_that_llama_leaves_at_their_defaults(dtype):
-    """A cap on the attention scores (softcap * tanh(score / softcap); the generic kernel takes it) and a scale on the
-    embeddings: parameters of the parts that another architecture would set."""
+    """A cap on the attention scores (softcap * tanh(score / softcap)), a bias on them that grows with distance (both
+    taken by the generic kernel) and a scale on the embeddings: parameters of the parts that another architecture
+    would set."""
     from lmsf_b200 import kernels
     nh, nkv, hd, bs, cap = 4, 2, 64, 16, 7.5
     ctx_lens, q_lens = [90, 1, 40], [90, 1, 3]
@@ -169,6 +172,20 @@ def test_constants_that_llama_leaves_at_their_defaults(dtype):
     tol_ = (1e-4 if dtype == "float32" else 2e-2) * ref.abs().max().item()
     assert (out.float().cpu().double() - ref).abs().max().item() <= tol_
     assert (plain - ref).abs().max().item() > 5 * tol_               # the cap matters on these scores
+    # slope[head] * (key position - query position) on the scaled scores, with a window as well
+    slopes = [0.5, 0.0625, 0.0, 1.25]
+    for window in (0, 30):
+        kernels.attention_generic(out, q.to(dev()), cache.to(dev()), bt.to(dev()), bs, token_seq.to(dev()), positions.to(dev()),
+                                  scale, window, nh, nkv, hd, slopes=torch.tensor(slopes, device=dev()))
+        ref = _attention_reference(q.float(), ks, vs, token_seq, positions, nh, nkv, hd, scale, window, slopes=slopes)
+        plain = _attention_reference(q.float(), ks, vs, token_seq, positions, nh, nkv, hd, scale, window)
+        tol_ = (1e-4 if dtype == "float32" else 2e-2) * ref.abs().max().item()
+        assert (out.float().cpu().double() - ref).abs().max().item() <= tol_
+        hs = slice(2 * hd, 3 * hd)                                    # the head with slope 0 is the plain one
+        assert (plain[:, hs] - ref[:, hs]).abs().max().item() == 0 and (plain - ref).abs().max().item() > 5 * tol_
+    with pytest.raises(kernels.KernelError):
+        kernels.attention_generic(out, q.to(dev()), cache.to(dev()), bt.to(dev()), bs, token_seq.to(dev()), positions.to(dev()),
+                                  scale, 0, nh, nkv, hd, slopes=torch.tensor(slopes[:3], device=dev()))
     g = torch.Generator().manual_seed(3)
     table = torch.randn(50, 72, generator=g).to(DT[dtype])
     ids = torch.tensor([3, 49, 0, 17], dtype=torch.int32)

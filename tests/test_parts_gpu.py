@@ -543,6 +543,62 @@ def test_attention_mixer_alone_over_two_steps(dtype, tol, nh, nkv, hd, window, s
     assert ctx.error_flag.item() == 0 and ctx2.error_flag.item() == 0
 
 
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 4e-2)])
+@pytest.mark.filterwarnings("ignore:a cap on the attention scores")
+def test_attention_mixer_with_a_position_encoding_on_the_scores(dtype, tol):
+    """Another position encoding of the package: nothing is done to q and k, a bias slope[head] * (key - query) goes on
+    the scores.  The mixer over two steps (a whole prompt; then a portion beside a decoded token) against plain
+    attention with that bias on whole sequences."""
+    from lmsf_b200.parts.attention import PagedAttention
+    from lmsf_b200.parts.base import LayerCache, build_part, PartSpec
+    H, nh, nkv, hd, bs = 40, 4, 2, 32, 8
+    slopes = [0.5, 0.25, 0.125, 0.0625]
+    g = torch.Generator().manual_seed(9)
+    enc = build_part("position_encoding", PartSpec("distance_bias", {"slopes": slopes}))
+    att = PagedAttention(hidden_size=H, num_heads=nh, num_kv_heads=nkv, head_dim=hd, position_encoding=enc)
+    wq, wk, wv = (torch.randn(nh * hd, H, generator=g) * 0.3, torch.randn(nkv * hd, H, generator=g) * 0.3,
+                  torch.randn(nkv * hd, H, generator=g) * 0.3)
+    wo = torch.randn(H, nh * hd, generator=g) * 0.3
+    r = lambda t: t.to(dtype).float()
+    att.set_weights({"qkv": torch.cat([wq, wk, wv]).to(dtype).to(DEV), "o": wo.to(dtype).to(DEV)})
+    att.prepare(dtype, torch.device(DEV))
+    with pytest.raises(ValueError):
+        bad = PagedAttention(hidden_size=H, num_heads=nh, num_kv_heads=nkv, head_dim=hd,
+                             position_encoding=build_part("position_encoding", PartSpec("distance_bias", {"slopes": slopes[:3]})))
+        bad.prepare(dtype, torch.device(DEV))
+    lens = [21, 13]
+    hs = [torch.randn(n, H, generator=g).to(dtype) for n in lens]
+
+    def plain(h):
+        T = h.shape[0]
+        q, k, v = (h @ r(wq).T).view(T, nh, hd), (h @ r(wk).T).view(T, nkv, hd), (h @ r(wv).T).view(T, nkv, hd)
+        out = torch.empty(T, nh, hd)
+        dist = (torch.arange(T)[None, :] - torch.arange(T)[:, None]).float()          # key - query
+        for hh in range(nh):
+            sc = (q[:, hh] @ k[:, hh // (nh // nkv)].T) / math.sqrt(hd) + slopes[hh] * dist
+            sc = sc.masked_fill(dist > 0, float("-inf"))
+            out[:, hh] = torch.softmax(sc, dim=-1) @ v[:, hh // (nh // nkv)]
+        return out.reshape(T, nh * hd) @ r(wo).T
+
+    refs = [plain(h.float()) for h in hs]
+    kv = torch.zeros(12, 2, nkv, bs, hd, dtype=dtype, device=DEV)
+    cache = LayerCache(kv=kv, group=0, owner=True)
+    ctx, bt = _hand_context([15, 12], [21, 13], bs, 12)
+    ctx.dtype = dtype
+    ctx.ctx_len.copy_(torch.tensor([15, 12], dtype=torch.int32))
+    ctx.positions.copy_(torch.tensor(list(range(15)) + list(range(12)), dtype=torch.int32))
+    ctx.ctx_lens[:] = [15, 12]
+    out1 = att.forward(ctx, torch.cat([hs[0][:15], hs[1][:12]]).to(DEV), cache).float().cpu()
+    ctx2, _ = _hand_context([6, 1], [21, 13], bs, 12)
+    ctx2.dtype = dtype
+    ctx2.groups[0].block_table.copy_(bt)
+    out2 = att.forward(ctx2, torch.cat([hs[0][15:], hs[1][12:]]).to(DEV), cache).float().cpu()
+    got = [torch.cat([out1[:15], out2[:6]]), torch.cat([out1[15:], out2[6:]])]
+    for a, b in zip(got, refs):
+        assert (a - b).abs().max() <= tol * max(1.0, b.abs().max()), (a - b).abs().max()
+    assert ctx.error_flag.item() == 0 and ctx2.error_flag.item() == 0
+
+
 def test_a_decode_step_splits_its_norms_between_the_products_around_them(monkeypatch):
     """Two blocks of the package's parts on a step of five single tokens in bfloat16: the norm between the output
     projection and the gated product, and the one between the down product and the next block's q/k/v product, are
