@@ -6,7 +6,7 @@ float32 here whatever the activation dtype.
 """
 from __future__ import annotations
 
-from typing import Dict, Optional, Tuple
+from typing import Dict, Optional, Tuple, Union
 
 import torch
 
@@ -40,7 +40,8 @@ class RMSNorm(Norm):
         kernels.add_rmsnorm(h, x, None, self.weight, self.eps, 0)
         return h
 
-    def forward_residual(self, x, res: Optional[torch.Tensor]):
+    def forward_residual(self, x: Union[torch.Tensor, Prenormed], res: Optional[torch.Tensor]
+                         ) -> Tuple[Union[torch.Tensor, Prenormed], torch.Tensor]:
         if isinstance(x, Prenormed):
             if x.norm is not self or x.res is not res:
                 raise ValueError("a Prenormed activation was prepared for another norm or residual stream")
