@@ -399,6 +399,49 @@ constexpr int kStagesPlain16 = LMSF_SKINNY_STAGES_M16;
 #define LMSF_SKINNY_STAGES_FUSED (CH == 1 ? 3 : 2)
 #endif
 constexpr int kStagesFused = LMSF_SKINNY_STAGES_FUSED;
+// A launch of so few blocks that at most two of them fall to an SM, or one, leaves shared memory unused and has few
+// bytes in flight per SM: such launches get deeper rings (the 4,096-row output and down products of Llama-3-8B, 256
+// blocks: a decode step of 8 requests 3.37 -> 3.21 ms with eight stages instead of six, 3.24 with seven or nine; ten,
+// with which one block fits an SM and the 256 run in two waves: 3.70 ms; 9 to 16 rows: six stages instead of four,
+// a step of 16 requests 4.07 -> 3.95 ms).  Launches of at most one block an SM (2,048-row products, 128 blocks) are
+// no faster with 12 or 16 stages than with eight.
+#ifndef LMSF_SKINNY_STAGES_FEW
+#define LMSF_SKINNY_STAGES_FEW 8
+#endif
+#ifndef LMSF_SKINNY_STAGES_ONE
+#define LMSF_SKINNY_STAGES_ONE LMSF_SKINNY_STAGES_FEW
+#endif
+#ifndef LMSF_SKINNY_STAGES_FEW_M16
+#define LMSF_SKINNY_STAGES_FEW_M16 (CH == 1 ? 6 : LMSF_SKINNY_STAGES_M16)
+#endif
+#ifndef LMSF_SKINNY_STAGES_ONE_M16
+#define LMSF_SKINNY_STAGES_ONE_M16 LMSF_SKINNY_STAGES_FEW_M16
+#endif
+constexpr int kStagesFew = LMSF_SKINNY_STAGES_FEW, kStagesOne = LMSF_SKINNY_STAGES_ONE;
+constexpr int kStagesFew16 = LMSF_SKINNY_STAGES_FEW_M16, kStagesOne16 = LMSF_SKINNY_STAGES_ONE_M16;
+
+static int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 1;
+  }
+  return n;
+}
+
+// The plain, residual, prenormed and q/k/v forms (one group of 16 rows a block): the ring's depth by the number of blocks.
+template <bool ROPE>
+static int launch_by_blocks(const Args& a, int rows, cudaStream_t s) {
+  const int blocks = ceil_div(rows, 16), sms = sm_count();
+  if (a.M <= 8) {
+    if (kStagesOne != kStagesFew && blocks <= sms) return launch<1, 1, kStagesOne, ROPE>(a, rows, s);
+    if (kStagesFew != kStagesPlain && blocks <= 2 * sms) return launch<1, 1, kStagesFew, ROPE>(a, rows, s);
+    return launch<1, 1, kStagesPlain, ROPE>(a, rows, s);
+  }
+  if (kStagesOne16 != kStagesFew16 && blocks <= sms) return launch<2, 1, kStagesOne16, ROPE>(a, rows, s);
+  if (kStagesFew16 != kStagesPlain16 && blocks <= 2 * sms) return launch<2, 1, kStagesFew16, ROPE>(a, rows, s);
+  return launch<2, 1, kStagesPlain16, ROPE>(a, rows, s);
+}
 
 }  // namespace skinny
 }  // namespace lmsf
@@ -430,7 +473,7 @@ static int run_product(Args& a, int fuse_act, cudaStream_t s) {
     return M <= 8 ? launch<1, 1, kStagesPlain, false, true>(a, N / 2, s) : launch<2, 2, kStagesFused>(a, N / 2, s);
   }
   if (a.ldo < N) LMSF_REFUSE("gemm_skinny: ldo is smaller than the output row");
-  return M <= 8 ? launch<1, 1, kStagesPlain>(a, N, s) : launch<2, 1, kStagesPlain16>(a, N, s);
+  return launch_by_blocks<false>(a, N, s);
 }
 
 }  // namespace skinny
@@ -508,5 +551,5 @@ LMSF_API int lmsf_gemm_skinny_qkv_rope(void* q_out, long long ldq, const void* x
                 "16-byte aligned, a width and a positive eps");
   a.in_sumsq = in_sumsq; a.in_parts = in_parts; a.in_ld = in_ld; a.in_eps = in_eps; a.in_width = in_width;
   cudaStream_t s = (cudaStream_t)stream;
-  return M <= 8 ? launch<1, 1, kStagesPlain, true>(a, a.N, s) : launch<2, 1, kStagesPlain16, true>(a, a.N, s);
+  return launch_by_blocks<true>(a, a.N, s);
 }
