@@ -103,3 +103,43 @@ def test_histories_go_with_their_requests():
     p.prompt_token_ids, p.output_token_ids = [1, 2], [2]
     t, c = sampler._history(p).update(p.output_token_ids)
     assert dict(zip(t.tolist(), c.tolist())) == {1: 0, 2: 1} and len(sampler._histories) == 1
+
+
+def test_a_norm_is_split_between_products_only_when_everybody_can():
+    """The offer a block makes to the part before a norm (parts/block.py: norm_after): the producer says fuses_norm,
+    the reader of the norm says takes_prenormed, the norm says splittable, the step is bfloat16 and has at most 16
+    tokens, and there is a residual stream already."""
+    import types
+
+    import torch
+
+    from lmsf_b200.parts import block as block_mod
+    from lmsf_b200.parts.base import FeedForward, Mixer, Norm, NormAfter
+
+    class Able(Mixer):
+        fuses_norm = True
+        takes_prenormed = True
+
+    class Plain(FeedForward):
+        pass
+
+    class Split(Norm):
+        splittable = True
+
+    res = torch.zeros(2, 4)
+    step = lambda n, dt=torch.bfloat16: types.SimpleNamespace(dtype=dt, n_tokens=n)
+    offer = block_mod.norm_after(step(16), Able(), Split(), Able(), res)
+    assert isinstance(offer, NormAfter) and offer.res is res
+    assert block_mod.norm_after(step(17), Able(), Split(), Able(), res) is None              # the library's products
+    assert block_mod.norm_after(step(8, torch.float32), Able(), Split(), Able(), res) is None
+    assert block_mod.norm_after(step(8), Able(), Split(), Able(), None) is None               # the first norm of a step
+    assert block_mod.norm_after(step(8), Plain(), Split(), Able(), res) is None
+    assert block_mod.norm_after(step(8), Able(), Split(), Plain(), res) is None
+    assert block_mod.norm_after(step(8), Able(), Norm(), Able(), res) is None
+    assert block_mod.norm_after(None, Plain(), Norm(), Plain(), res) is None                   # parts are asked first
+    old = block_mod.FUSE_NORMS
+    try:
+        block_mod.FUSE_NORMS = False
+        assert block_mod.norm_after(step(8), Able(), Split(), Able(), res) is None
+    finally:
+        block_mod.FUSE_NORMS = old
