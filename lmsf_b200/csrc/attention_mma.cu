@@ -82,7 +82,9 @@ __device__ __forceinline__ void st_cluster_f32(const float* local, unsigned rank
 constexpr int kTableCache = 512;           // block-table entries of a split that are kept in shared memory
 constexpr int kMergeWeights = 4096;        // (heads of a block) x splits whose weights fit the shared memory used for adding up
 
-template <int W>
+// S: stages of the ring of key/value tiles (kStages; one more in the variant for launches of so few blocks that each
+// has an SM to itself, below)
+template <int W, int S = kStages>
 __global__ void __launch_bounds__(32 * W) decode_kernel(DecodeArgs a) {
   constexpr int kDecWarps = W, kDecThreads = 32 * W, kDecTile = 16 * W;
   using DSt = Stage<HD, kDecTile>;
@@ -146,11 +148,11 @@ __global__ void __launch_bounds__(32 * W) decode_kernel(DecodeArgs a) {
   const uint32_t smem_base = smem_u32(smem);
   // first stages: tiles that end before the new token are requested now, the others after the wait
   const int safe_end = (ctx - 1) / kDecTile;                  // tiles below this index hold only older keys
-  for (int s = 0; s < kStages - 1; ++s)
+  for (int s = 0; s < S - 1; ++s)
     if (s < n_tiles && tile_begin + s < safe_end)
       load_stage<HD, kDecTile, kDecThreads>(smem_base + s * DSt::kBytes, a.kv, table, kvh, (tile_begin + s) * kDecTile, lo, ctx, table_off);
   pdl_wait();
-  for (int s = 0; s < kStages - 1; ++s) {
+  for (int s = 0; s < S - 1; ++s) {
     if (s < n_tiles && tile_begin + s >= safe_end)
       load_stage<HD, kDecTile, kDecThreads>(smem_base + s * DSt::kBytes, a.kv, table, kvh, (tile_begin + s) * kDecTile, lo, ctx, table_off);
     cp_async_commit();
@@ -177,15 +179,15 @@ __global__ void __launch_bounds__(32 * W) decode_kernel(DecodeArgs a) {
   const float sl2 = a.scale * kLog2e;
 
   for (int i = 0; i < n_tiles; ++i) {
-    cp_async_wait<kStages - 2>();
+    cp_async_wait<S - 2>();
     __syncthreads();
     {
-      const int nxt = i + kStages - 1;
+      const int nxt = i + S - 1;
       if (nxt < n_tiles)
-        load_stage<HD, kDecTile, kDecThreads>(smem_base + (nxt % kStages) * DSt::kBytes, a.kv, table, kvh, (tile_begin + nxt) * kDecTile, lo, ctx, table_off);
+        load_stage<HD, kDecTile, kDecThreads>(smem_base + (nxt % S) * DSt::kBytes, a.kv, table, kvh, (tile_begin + nxt) * kDecTile, lo, ctx, table_off);
       cp_async_commit();
     }
-    const uint32_t kbase = smem_base + (i % kStages) * DSt::kBytes;       // this warp's rows are warp * 16 ..
+    const uint32_t kbase = smem_base + (i % S) * DSt::kBytes;       // this warp's rows are warp * 16 ..
     const uint32_t vbase = kbase + kDecTile * DSt::kRowBytes;
     const int key0 = (tile_begin + i) * kDecTile + warp * 16;   // first key of this warp's 16
     if (key0 >= ctx || key0 + 16 <= lo) continue;                // nothing valid (uniform over the warp)
@@ -471,10 +473,12 @@ static int cluster_enabled() {
 
 static int decode_rows(int group) { return group < 16 ? (group < 1 ? 1 : group) : 16; }
 
-static int decode_smem_bytes(int group, int warps) {
+constexpr int kDeepStages = lmsf::fa::kStages + 1;      // the ring of the variant for few blocks
+
+static int decode_smem_bytes(int group, int warps, int stages = lmsf::fa::kStages) {
   using namespace lmsf::fa;
   const int R = decode_rows(group);
-  const int smem_stages = kStages * (warps == 2 ? Stage<HD, 32>::kBytes : Stage<HD, 64>::kBytes);
+  const int smem_stages = stages * (warps == 2 ? Stage<HD, 32>::kBytes : Stage<HD, 64>::kBytes);
   const int smem_merge = (warps * R * (HD + 8) + 2 * warps * 16) * (int)sizeof(float);
   const int smem_weights = kMergeWeights * (int)sizeof(float);     // weights of the splits when they are added up
   const int smem_cluster = smem_merge + kMaxClusterSplits * (R * HD + 16) * (int)sizeof(float);   // + the parts of a cluster
@@ -488,22 +492,28 @@ static int decode_smem_bytes(int group, int warps) {
 // a request and kv head form a cluster, and a launch with more clusters than this runs in two waves.
 // The decode kernel of a width is allowed as much dynamic shared memory as the largest request so far: the attribute is
 // only ever raised (a query for a small group of heads must not lower what a launch for a large group was given).
-static cudaError_t decode_allow_smem(int warps, int smem) {
+typedef void (*DecodeKernel)(lmsf::fa::DecodeArgs);
+static DecodeKernel decode_variant(int warps, bool deep) {
   using namespace lmsf::fa;
-  static int allowed[2] = {0, 0};
-  if (smem <= allowed[warps == 2]) return cudaSuccess;
-  void (*kernel)(DecodeArgs) = warps == 2 ? decode_kernel<2> : decode_kernel<4>;
-  const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-  if (e == cudaSuccess) allowed[warps == 2] = smem;
+  if (warps == 2) return decode_kernel<2>;
+  return deep ? (DecodeKernel)decode_kernel<4, kDeepStages> : (DecodeKernel)decode_kernel<4>;
+}
+
+static cudaError_t decode_allow_smem(int warps, int smem, bool deep = false) {
+  static int allowed[3] = {0, 0, 0};
+  const int v = warps == 2 ? 0 : (deep ? 2 : 1);
+  if (smem <= allowed[v]) return cudaSuccess;
+  const cudaError_t e = cudaFuncSetAttribute(decode_variant(warps, deep), cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e == cudaSuccess) allowed[v] = smem;
   return e;
 }
 
-LMSF_API int lmsf_attention_decode_max_clusters(int cluster_size, int group, int warps) {
+static int decode_max_clusters(int cluster_size, int group, int warps, bool deep) {
   using namespace lmsf::fa;
   if (cluster_size < 1 || cluster_size > kMaxClusterSplits || (warps != 2 && warps != 4)) return 0;
-  const int smem = decode_smem_bytes(group, warps);
-  void (*kernel)(DecodeArgs) = warps == 2 ? decode_kernel<2> : decode_kernel<4>;
-  if (decode_allow_smem(warps, smem) != cudaSuccess) return 0;
+  const int smem = decode_smem_bytes(group, warps, deep ? kDeepStages : kStages);
+  DecodeKernel kernel = decode_variant(warps, deep);
+  if (decode_allow_smem(warps, smem, deep) != cudaSuccess) return 0;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)cluster_size, 1024, 1);
   cfg.blockDim = dim3(32 * warps);
@@ -518,6 +528,10 @@ LMSF_API int lmsf_attention_decode_max_clusters(int cluster_size, int group, int
   int n = 0;
   if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) return 0;
   return n;
+}
+
+LMSF_API int lmsf_attention_decode_max_clusters(int cluster_size, int group, int warps) {
+  return decode_max_clusters(cluster_size, group, warps, false);
 }
 
 // Bytes of keys and values that a decode block of `warps` warps keeps in flight: what sets the rate at which one
@@ -614,9 +628,23 @@ LMSF_API int lmsf_attention_decode_width(const void* q, long long q_stride, void
 static int decode_launch(lmsf::fa::DecodeArgs& a, int gy, int grid_x, int grid_z, int warps, cudaStream_t s) {
   using namespace lmsf;
   using namespace lmsf::fa;
-  void (*kernel)(DecodeArgs) = warps == 2 ? decode_kernel<2> : decode_kernel<4>;
-  const int smem = decode_smem_bytes(a.group, warps);
-  if (const cudaError_t e = decode_allow_smem(warps, smem)) return (int)e;
+  // A launch of wide blocks that all run at once with one more stage each (one or two requests of Llama-3-8B's 8 kv
+  // heads in 8 splits: 64 or 128 blocks on 148 SMs) gets that stage: more keys are asked for before the dependency
+  // wait and more bytes are in flight (a decode step of one request 2.98 -> 2.90 ms, of two 2.98 -> 2.93).
+  bool deep = false;
+  if (warps == 4 && !a.items) {
+    static int fit[kMaxClusterSplits + 1][17];             // by cluster size and rows of a block; 0: not asked yet
+    const int cs = a.cluster ? grid_x : 1, R = decode_rows(a.group);
+    if (fit[cs][R] == 0) {
+      const int n = decode_max_clusters(cs, a.group, 4, true);
+      fit[cs][R] = n > 0 ? n : -1;
+    }
+    const long long clusters = (long long)gy * grid_z * (a.cluster ? 1 : grid_x);
+    deep = fit[cs][R] > 0 && clusters <= fit[cs][R];
+  }
+  DecodeKernel kernel = decode_variant(warps, deep);
+  const int smem = decode_smem_bytes(a.group, warps, deep ? kDeepStages : kStages);
+  if (const cudaError_t e = decode_allow_smem(warps, smem, deep)) return (int)e;
   if (!a.cluster) return launch_pdl(kernel, dim3(grid_x, (unsigned)gy, grid_z), dim3(32 * warps), smem, s, a);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid_x, (unsigned)gy, grid_z);
