@@ -151,8 +151,8 @@ __global__ void __launch_bounds__(kWarps * 32) skinny_kernel(Args a) {
   }
 
   // prenormed input: 128 / (8 NT) threads share a token's partial sums of squares.  The first 16 of a thread are asked
-  // for here (16-byte loads) and added after the loop, so that nothing waits for them; more parts than that (a width
-  // above 4,096 x NT) are read then.  The order of the sum depends on the number of parts only.
+  // for here (16-byte loads) and added after the loop, so that nothing waits for them; more parts than those 256 / NT (a
+  // width above 4,096 / NT) are read then.  The order of the sum depends on the number of parts only.
   constexpr int kTPR = kWarps * 32 / (8 * NT);
   float4 ss_v[4];
   auto load_ss = [&](int q0) {
